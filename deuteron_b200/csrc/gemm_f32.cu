@@ -1,0 +1,145 @@
+// Plain FP32 GEMM (contraction_precision = "f32"): C = A*B with FP32 FMA on the CUDA cores.
+// 128x128 CTA tile, 8x8 register micro-tile per thread, K advanced 16 at a time through
+// double-buffered shared memory. A is stored transposed in shared memory so that both
+// operand reads in the inner loop are conflict-free 128-bit loads. Any M, N, K and any
+// leading dimensions; the vector global loads are used when pointers and strides allow.
+#include "dtn_common.cuh"
+
+namespace dtn {
+
+constexpr int F_BM = 128, F_BN = 128, F_BK = 16, F_THREADS = 256;
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(F_THREADS)
+gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C,
+                int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc) {
+  __shared__ __align__(16) float As[2][F_BK][F_BM + 4];
+  __shared__ __align__(16) float Bs[2][F_BK][F_BN + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * F_BM, n0 = blockIdx.x * F_BN;
+  const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads, each 8 x 8 outputs
+
+  // Global -> register staging assignment.
+  // A tile: 128 rows x 16 k  = 512 float4 (along k); thread loads 2.
+  // B tile: 16 k x 128 cols = 512 float4 (along n); thread loads 2.
+  float4 ra[2], rb[2];
+  auto load_tiles = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = tid + i * F_THREADS;   // 0..511
+      const int ar = v >> 2, ak = (v & 3) * 4;
+      const int gr = m0 + ar, gk = k0 + ak;
+      float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (gr < M) {
+        const float* p = A + (int64_t)gr * lda + gk;
+        if (ALIGNED && gk + 3 < K) {
+          t = *reinterpret_cast<const float4*>(p);
+        } else {
+          if (gk + 0 < K) t.x = p[0];
+          if (gk + 1 < K) t.y = p[1];
+          if (gk + 2 < K) t.z = p[2];
+          if (gk + 3 < K) t.w = p[3];
+        }
+      }
+      ra[i] = t;
+      const int bk = v >> 5, bn = (v & 31) * 4;
+      const int gkb = k0 + bk, gn = n0 + bn;
+      float4 u = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (gkb < K) {
+        const float* p = B + (int64_t)gkb * ldb + gn;
+        if (ALIGNED && gn + 3 < N) {
+          u = *reinterpret_cast<const float4*>(p);
+        } else {
+          if (gn + 0 < N) u.x = p[0];
+          if (gn + 1 < N) u.y = p[1];
+          if (gn + 2 < N) u.z = p[2];
+          if (gn + 3 < N) u.w = p[3];
+        }
+      }
+      rb[i] = u;
+    }
+  };
+  auto store_tiles = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = tid + i * F_THREADS;
+      const int ar = v >> 2, ak = (v & 3) * 4;
+      As[buf][ak + 0][ar] = ra[i].x;
+      As[buf][ak + 1][ar] = ra[i].y;
+      As[buf][ak + 2][ar] = ra[i].z;
+      As[buf][ak + 3][ar] = ra[i].w;
+      const int bk = v >> 5, bn = (v & 31) * 4;
+      *reinterpret_cast<float4*>(&Bs[buf][bk][bn]) = rb[i];
+    }
+  };
+
+  float acc[8][8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+
+  const int ktiles = (K + F_BK - 1) / F_BK;
+  if (ktiles > 0) {
+    load_tiles(0);
+    store_tiles(0);
+  }
+  __syncthreads();
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ktiles) load_tiles((kt + 1) * F_BK);
+#pragma unroll
+    for (int k = 0; k < F_BK; ++k) {
+      float a[8], b[8];
+      const float4 a0 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+      const float4 a1 = *reinterpret_cast<const float4*>(&As[buf][k][64 + ty * 4]);
+      const float4 b0 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+      const float4 b1 = *reinterpret_cast<const float4*>(&Bs[buf][k][64 + tx * 4]);
+      a[0] = a0.x; a[1] = a0.y; a[2] = a0.z; a[3] = a0.w;
+      a[4] = a1.x; a[5] = a1.y; a[6] = a1.z; a[7] = a1.w;
+      b[0] = b0.x; b[1] = b0.y; b[2] = b0.z; b[3] = b0.w;
+      b[4] = b1.x; b[5] = b1.y; b[6] = b1.z; b[7] = b1.w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (kt + 1 < ktiles) store_tiles(buf ^ 1);
+    __syncthreads();
+  }
+
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const int r = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+    if (r >= M) continue;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int c = n0 + h * 64 + tx * 4;
+      float* p = C + (int64_t)r * ldc + c;
+      if (ALIGNED && c + 3 < N) {
+        *reinterpret_cast<float4*>(p) =
+            make_float4(acc[i][h * 4 + 0], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (c + j < N) p[j] = acc[i][h * 4 + j];
+      }
+    }
+  }
+}
+
+int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s) {
+  dim3 grid((unsigned)((N + F_BN - 1) / F_BN), (unsigned)((M + F_BM - 1) / F_BM));
+  DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm f32: M too large");
+  const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 16) && lda % 4 == 0 &&
+                       ldb % 4 == 0 && ldc % 4 == 0;
+  if (aligned)
+    gemm_f32_kernel<true><<<grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+  else
+    gemm_f32_kernel<false><<<grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+  DTN_LAUNCH_CHECK("gemm_f32_kernel");
+  return DTN_OK;
+}
+
+}  // namespace dtn

@@ -1,0 +1,596 @@
+// Compensated FP32 GEMM on the sm_100a tensor cores: C = A*B with every FP32 operand split
+// into a rounded high part and a rounded residual (bf16 or tf32) and the three products
+// lo*hi, hi*lo, hi*hi accumulated in FP32 in tensor memory.
+//
+// Two passes:
+//   1. split kernels turn A[M,K] and B[K,N] into K-major planes in the caller's workspace:
+//      A_hi, A_lo [M, Kp] and (B transposed) Bt_hi, Bt_lo [N, Kp]. The split costs one read
+//      of each operand and is not repeated per tile.
+//   2. a persistent, warp-specialised kernel: one thread issues TMA tile loads of the four
+//      planes into a shared-memory ring (128-byte swizzle), one thread issues the
+//      tcgen05.mma instructions (three per k-step) into a double-buffered tensor-memory
+//      accumulator, four warps drain finished accumulators with tcgen05.ld and store C
+//      while the next tile's products run.
+// Variants: one CTA per 128xBN tile (BN = 128 or 256) or a CTA pair per 256x256 tile
+// (cta_group::2: each CTA loads its own 128 rows of A and its own half of B; no load is
+// shared between CTAs by multicast).
+#include <cuda.h>
+
+#include <mutex>
+
+#include "dtn_common.cuh"
+#include "sm100_ptx.cuh"
+
+namespace dtn {
+
+int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s);
+
+// ---------------------------------------------------------------------------------------
+// Operand split
+// ---------------------------------------------------------------------------------------
+struct Bf16Kind {
+  using elem = __nv_bfloat16;
+  static constexpr int kElemBytes = 2;
+  static constexpr int kBlockK = 64;  // elements per 128-byte row
+  __device__ static __forceinline__ void split(float v, elem& hi, elem& lo) {
+    hi = __float2bfloat16_rn(v);
+    lo = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+  __device__ static __forceinline__ elem zero() { return __float2bfloat16_rn(0.f); }
+};
+struct Tf32Kind {
+  using elem = float;  // tf32 value held in an FP32 container (low 13 mantissa bits zero)
+  static constexpr int kElemBytes = 4;
+  static constexpr int kBlockK = 32;
+  __device__ static __forceinline__ float rna(float v) {
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+    return __uint_as_float(r);
+  }
+  __device__ static __forceinline__ void split(float v, elem& hi, elem& lo) {
+    hi = rna(v);
+    lo = rna(v - hi);
+  }
+  __device__ static __forceinline__ elem zero() { return 0.f; }
+};
+
+// A[rows, cols] (ld = ldx) -> hi/lo [rows, colsP]; columns >= cols are written as zero.
+template <class KIND>
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const float* __restrict__ X, int64_t ldx, int rows, int cols, int colsP,
+                  typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo,
+                  int vec_ok) {
+  using E = typename KIND::elem;
+  const int row = blockIdx.y;
+  const int c4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (c4 >= colsP) return;
+  const float* xr = X + (int64_t)row * ldx;
+  float v[4] = {0.f, 0.f, 0.f, 0.f};
+  if (vec_ok && c4 + 3 < cols) {
+    const float4 t = ld_stream_f4(reinterpret_cast<const float4*>(xr + c4));
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  } else {
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (c4 + j < cols) v[j] = xr[c4 + j];
+  }
+  E h[4], l[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) KIND::split(v[j], h[j], l[j]);
+  E* hp = hi + (int64_t)row * colsP + c4;
+  E* lp = lo + (int64_t)row * colsP + c4;
+  if constexpr (KIND::kElemBytes == 2) {
+    *reinterpret_cast<uint2*>(hp) = *reinterpret_cast<uint2*>(h);
+    *reinterpret_cast<uint2*>(lp) = *reinterpret_cast<uint2*>(l);
+  } else {
+    *reinterpret_cast<uint4*>(hp) = *reinterpret_cast<uint4*>(h);
+    *reinterpret_cast<uint4*>(lp) = *reinterpret_cast<uint4*>(l);
+  }
+}
+
+// B[K, N] (ld = ldb) -> transposed hi/lo [N, Kp]; k >= K written as zero.
+// One CTA transposes a kBlockK x 64 tile through shared memory.
+template <class KIND>
+__global__ void __launch_bounds__(256)
+split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
+                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo) {
+  using E = typename KIND::elem;
+  constexpr int TK = KIND::kBlockK;          // 64 (bf16) or 32 (tf32): 128 bytes of k per row
+  constexpr int PAD = (KIND::kElemBytes == 2) ? 2 : 1;
+  __shared__ E s_hi[64][TK + PAD];
+  __shared__ E s_lo[64][TK + PAD];
+  const int k0 = blockIdx.x * TK, n0 = blockIdx.y * 64;
+  const int tid = threadIdx.x;
+  {
+    const int nn = tid & 63, kr = tid >> 6;  // 4 k-rows per pass
+#pragma unroll 4
+    for (int p = 0; p < TK / 4; ++p) {
+      const int k = k0 + p * 4 + kr, n = n0 + nn;
+      float v = 0.f;
+      if (k < K && n < N) v = B[(int64_t)k * ldb + n];
+      E h, l;
+      KIND::split(v, h, l);
+      s_hi[nn][p * 4 + kr] = h;
+      s_lo[nn][p * 4 + kr] = l;
+    }
+  }
+  __syncthreads();
+  {
+    // each thread writes 4 bytes of k; 32 threads cover one 128-byte row; 8 rows per pass
+    constexpr int EPT = 4 / KIND::kElemBytes;  // elements per thread (2 bf16 or 1 tf32)
+    const int kk = (tid & 31) * EPT, nr = tid >> 5;
+#pragma unroll
+    for (int p = 0; p < 8; ++p) {
+      const int nn = p * 8 + nr, n = n0 + nn;
+      if (n < N && k0 + kk < Kp) {
+        const int64_t o = (int64_t)n * Kp + k0 + kk;
+        *reinterpret_cast<uint32_t*>(hi + o) = *reinterpret_cast<const uint32_t*>(&s_hi[nn][kk]);
+        *reinterpret_cast<uint32_t*>(lo + o) = *reinterpret_cast<const uint32_t*>(&s_lo[nn][kk]);
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Tensor-core kernel
+// ---------------------------------------------------------------------------------------
+constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2-5: epilogue
+constexpr int kTileRowBytes = 128; // one swizzle row = one k-block of either kind
+constexpr int kGroupM = 8;         // m-tiles per raster group (L2 reuse of the B planes)
+
+template <int CTAS, int BN>
+struct GemmCfg {
+  static constexpr int kBnLoad = BN / CTAS;                       // B rows this CTA loads
+  static constexpr int kABytes = 128 * kTileRowBytes;             // one A plane tile
+  static constexpr int kBBytes = kBnLoad * kTileRowBytes;         // one B plane tile
+  static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;   // hi+lo of both
+  static constexpr int kStages = (200 * 1024) / kStageBytes;      // ring depth
+  static constexpr int kTmemCols = 2 * BN;                        // double-buffered accumulator
+  static constexpr int kBarrierBytes = 256;
+  static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
+  static_assert(kStages >= 2, "ring too shallow");
+  static_assert(kTmemCols == 256 || kTmemCols == 512, "tensor memory columns must be a power of two");
+};
+
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = kGroupM * tiles_n;
+  const int g = t / per_group;
+  const int first = g * kGroupM;
+  const int gsize = min(kGroupM, tiles_m - first);
+  const int r = t - g * per_group;
+  tm = first + r % gsize;
+  tn = r / gsize;
+}
+
+template <int KIND /*0 = bf16, 1 = tf32*/, int CTAS, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+               const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+               float* __restrict__ C, int64_t ldc, int M, int N, int num_kb, int tiles_m, int tiles_n,
+               int c_vec_ok, int* __restrict__ status) {
+  using Cfg = GemmCfg<CTAS, BN>;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kBlockKElems = (KIND == 0) ? 64 : 32;
+  constexpr uint32_t kIdesc = ptx::umma_idesc(KIND == 0 ? 1 : 2, 128 * CTAS, BN);
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
+  uint8_t* bar_ptr = tiles_ptr + kStages * Cfg::kStageBytes;
+  const uint32_t bar_addr = tiles_addr + kStages * Cfg::kStageBytes;
+  // barrier block layout (8-byte slots): full[kStages], empty[kStages], tmem_full[2], tmem_empty[2]
+  auto full_bar = [&](int s) { return bar_addr + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_addr + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = (CTAS == 2) ? ptx::cluster_ctarank() : 0u;
+  const int unit = (CTAS == 2) ? (blockIdx.x >> 1) : blockIdx.x;        // tile worker index
+  const int num_units = (CTAS == 2) ? (gridDim.x >> 1) : gridDim.x;
+  const int num_tiles = tiles_m * tiles_n;
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 4 * CTAS);
+    }
+    ptx::mbar_fence_init();
+    ptx::fence_proxy_async_smem();
+    ptx::tma_prefetch_desc(&tm_a_hi);
+    ptx::tma_prefetch_desc(&tm_a_lo);
+    ptx::tma_prefetch_desc(&tm_b_hi);
+    ptx::tma_prefetch_desc(&tm_b_lo);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<CTAS>(smem_u32(tmem_holder), Cfg::kTmemCols);
+    ptx::tmem_relinquish<CTAS>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if constexpr (CTAS == 2) ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer --------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      const uint32_t leader_full0 = (CTAS == 2) ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
+      for (int t = unit; t < num_tiles && ok; t += num_units) {
+        int tm, tn;
+        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        const int row_a = tm * (128 * CTAS) + (int)rank * 128;
+        const int row_b = tn * BN + (int)rank * Cfg::kBnLoad;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            atomicExch(status, 0x100 | (int)(blockIdx.x & 0xff));
+            ok = false;
+            break;
+          }
+          const uint32_t sa_hi = tiles_addr + stage * Cfg::kStageBytes;
+          const uint32_t sa_lo = sa_hi + Cfg::kABytes;
+          const uint32_t sb_hi = sa_lo + Cfg::kABytes;
+          const uint32_t sb_lo = sb_hi + Cfg::kBBytes;
+          const int kx = kb * kBlockKElems;
+          if constexpr (CTAS == 1) {
+            ptx::mbar_expect_tx(full_bar(stage), Cfg::kStageBytes);
+            ptx::tma_load_2d(sa_hi, &tm_a_hi, kx, row_a, full_bar(stage));
+            ptx::tma_load_2d(sa_lo, &tm_a_lo, kx, row_a, full_bar(stage));
+            ptx::tma_load_2d(sb_hi, &tm_b_hi, kx, row_b, full_bar(stage));
+            ptx::tma_load_2d(sb_lo, &tm_b_lo, kx, row_b, full_bar(stage));
+          } else {
+            // Both CTAs' loads are counted on the leader CTA's barrier; the leader posts the
+            // byte count of the pair.
+            const uint32_t fb = leader_full0 + 8u * stage;
+            if (rank == 0) ptx::mbar_expect_tx(full_bar(stage), 2 * Cfg::kStageBytes);
+            ptx::tma_load_2d_pair(sa_hi, &tm_a_hi, kx, row_a, fb);
+            ptx::tma_load_2d_pair(sa_lo, &tm_a_lo, kx, row_a, fb);
+            ptx::tma_load_2d_pair(sb_hi, &tm_b_hi, kx, row_b, fb);
+            ptx::tma_load_2d_pair(sb_lo, &tm_b_lo, kx, row_b, fb);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int t = unit; t < num_tiles && ok; t += num_units, ++iter) {
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          atomicExch(status, 0x200 | (int)(blockIdx.x & 0xff));
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+            atomicExch(status, 0x300 | (int)(blockIdx.x & 0xff));
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa_hi = tiles_addr + stage * Cfg::kStageBytes;
+          const uint32_t sa_lo = sa_hi + Cfg::kABytes;
+          const uint32_t sb_hi = sa_lo + Cfg::kABytes;
+          const uint32_t sb_lo = sb_hi + Cfg::kBBytes;
+          const uint64_t da_hi = ptx::umma_desc_sw128(sa_hi), da_lo = ptx::umma_desc_sw128(sa_lo);
+          const uint64_t db_hi = ptx::umma_desc_sw128(sb_hi), db_lo = ptx::umma_desc_sw128(sb_lo);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // one k-step = 32 bytes along the swizzled row = +2 in the descriptor's address field
+            const uint64_t o = (uint64_t)(2 * k);
+            ptx::umma_ss<KIND, CTAS>(d_tmem, da_lo + o, db_hi + o, kIdesc, (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_ss<KIND, CTAS>(d_tmem, da_hi + o, db_lo + o, kIdesc, 1u);
+            ptx::umma_ss<KIND, CTAS>(d_tmem, da_hi + o, db_hi + o, kIdesc, 1u);
+          }
+          ptx::umma_commit<CTAS>(empty_bar(stage));  // frees this ring slot once the MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::umma_commit<CTAS>(tfull_bar(acc));  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // ------------------------------- epilogue ------------------------------------------
+    const int quarter = warp & 3;  // tensor-memory lanes [32*quarter, +32) belong to this warp
+    const uint32_t leader_tempty0 = (CTAS == 2) ? ptx::map_to_cta(tempty_bar(0), 0) : tempty_bar(0);
+    int iter = 0;
+    for (int t = unit; t < num_tiles; t += num_units, ++iter) {
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+      int tm, tn;
+      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      const bool ready = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) {  // leave together: the loads below are warp-wide
+        if (lane == 0) atomicExch(status, 0x400 | (int)(blockIdx.x & 0xff));
+        break;
+      }
+      ptx::tc_fence_after();
+      const int row = tm * (128 * CTAS) + (int)rank * 128 + quarter * 32 + lane;
+      const int col0 = tn * BN;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+      float* crow = C + (int64_t)row * ldc + col0;
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
+        ptx::tmem_ld_wait();
+        if (row < M) {
+          if (c_vec_ok && col0 + c * 32 + 32 <= N) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(crow + c * 32 + 4 * j) =
+                  make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + c * 32 + j < N) crow[c * 32 + j] = __uint_as_float(r[j]);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (CTAS == 2)
+          ptx::mbar_arrive_cluster(leader_tempty0 + 8u * acc);
+        else
+          ptx::mbar_arrive(tempty_bar(acc));
+      }
+    }
+  }
+
+  // ------------------------------- teardown --------------------------------------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // A wait ran out: give copies already in flight time to land before the CTA's shared
+    // memory and tensor memory are released.
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if constexpr (CTAS == 2) ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<CTAS>(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Host side
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// Tensor map of a K-major plane [rows, Kp] of `elem_bytes` elements; box = 128 bytes x box_rows.
+static int make_plane_map(CUtensorMap* map, const void* base, int elem_bytes, int64_t rows, int64_t K,
+                          int64_t Kp, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  DTN_REQUIRE(enc != nullptr, DTN_ERR_CUDA, "gemm: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)Kp * (cuuint64_t)elem_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(kTileRowBytes / elem_bytes), (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = enc(map, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DTN_REQUIRE(r == CUDA_SUCCESS, DTN_ERR_CUDA, "gemm: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return DTN_OK;
+}
+
+static int g_gemm_variant = 0;
+
+struct PlaneLayout {
+  int64_t Kp;
+  size_t a_plane, b_plane;  // bytes of one plane, rounded to 1024
+  size_t total;
+};
+static PlaneLayout plane_layout(int mode, int64_t M, int64_t N, int64_t K) {
+  PlaneLayout L;
+  const int eb = (mode == DTN_GEMM_BF16X3) ? 2 : 4;
+  const int bk = kTileRowBytes / eb;
+  L.Kp = (K + bk - 1) / bk * bk;
+  auto round1k = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
+  L.a_plane = round1k((size_t)M * L.Kp * eb);
+  L.b_plane = round1k((size_t)N * L.Kp * eb);
+  L.total = 2 * L.a_plane + 2 * L.b_plane;
+  return L;
+}
+
+template <int KIND, int CTAS, int BN>
+static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const void* b_lo, float* C,
+                     int64_t M, int64_t N, int64_t K, int64_t Kp, int64_t ldc, cudaStream_t s) {
+  using Cfg = GemmCfg<CTAS, BN>;
+  constexpr int eb = (KIND == 0) ? 2 : 4;
+  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+  int rc;
+  if ((rc = make_plane_map(&ma_hi, a_hi, eb, M, K, Kp, 128))) return rc;
+  if ((rc = make_plane_map(&ma_lo, a_lo, eb, M, K, Kp, 128))) return rc;
+  if ((rc = make_plane_map(&mb_hi, b_hi, eb, N, K, Kp, Cfg::kBnLoad))) return rc;
+  if ((rc = make_plane_map(&mb_lo, b_lo, eb, N, K, Kp, Cfg::kBnLoad))) return rc;
+
+  auto kernel = gemm_x3_kernel<KIND, CTAS, BN>;
+  // The attribute is per device; set it on every device the first time it is seen.
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  DTN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_dev = dev;
+  }
+
+  int* status = device_status_word();
+  DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "gemm: could not allocate the device status word");
+  const int bm = 128 * CTAS;
+  const int tiles_m = (int)((M + bm - 1) / bm), tiles_n = (int)((N + BN - 1) / BN);
+  const int num_kb = (int)(Kp / (kTileRowBytes / eb));
+  const int64_t num_tiles = (int64_t)tiles_m * tiles_n;
+  const int sms = sm_count();
+  int units = CTAS == 2 ? sms / 2 : sms;
+  if (num_tiles < units) units = (int)num_tiles;
+  const int c_vec_ok = aligned_to(C, 16) && (ldc % 4 == 0);
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(units * CTAS));
+  cfg.blockDim = dim3(kGemmThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTAS;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, C, ldc, (int)M, (int)N, num_kb,
+                                    tiles_m, tiles_n, c_vec_ok, status));
+  return DTN_OK;
+}
+
+template <class KIND>
+static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                     const PlaneLayout& L, uint8_t* ws, cudaStream_t s) {
+  using E = typename KIND::elem;
+  E* a_hi = reinterpret_cast<E*>(ws);
+  E* a_lo = reinterpret_cast<E*>(ws + L.a_plane);
+  E* b_hi = reinterpret_cast<E*>(ws + 2 * L.a_plane);
+  E* b_lo = reinterpret_cast<E*>(ws + 2 * L.a_plane + L.b_plane);
+  {
+    const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
+    dim3 grid((unsigned)((L.Kp / 4 + 255) / 256), (unsigned)M);
+    DTN_REQUIRE(M <= 65535 * 1024LL, DTN_ERR_UNSUPPORTED, "gemm: M too large");
+    // grid.y is limited to 65535 rows per launch
+    for (int64_t r0 = 0; r0 < M; r0 += 65535) {
+      const int rows = (int)((M - r0) < 65535 ? (M - r0) : 65535);
+      grid.y = (unsigned)rows;
+      split_rows_kernel<KIND><<<grid, 256, 0, s>>>(A + r0 * lda, lda, rows, (int)K, (int)L.Kp, a_hi + r0 * L.Kp,
+                                                   a_lo + r0 * L.Kp, vec_ok);
+      DTN_LAUNCH_CHECK("split_rows_kernel");
+    }
+  }
+  {
+    const int64_t ny = (N + 63) / 64;
+    for (int64_t y0 = 0; y0 < ny; y0 += 65535) {
+      const int cnt = (int)((ny - y0) < 65535 ? (ny - y0) : 65535);
+      dim3 grid((unsigned)(L.Kp / KIND::kBlockK), (unsigned)cnt);
+      const int64_t n_off = y0 * 64;
+      split_transpose_kernel<KIND><<<grid, 256, 0, s>>>(B + n_off, ldb, (int)K, (int)(N - n_off), (int)L.Kp,
+                                                        b_hi + n_off * L.Kp, b_lo + n_off * L.Kp);
+      DTN_LAUNCH_CHECK("split_transpose_kernel");
+    }
+  }
+  return DTN_OK;
+}
+
+template <int KIND>
+static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C, int64_t M, int64_t N, int64_t K,
+                  int64_t ldc, cudaStream_t s) {
+  const void* a_hi = ws;
+  const void* a_lo = ws + L.a_plane;
+  const void* b_hi = ws + 2 * L.a_plane;
+  const void* b_lo = ws + 2 * L.a_plane + L.b_plane;
+  if (variant == 0) {
+    // Small problems: more, smaller tiles keep more SMs busy; large ones: the widest tile.
+    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
+    variant = (tiles256 >= sm_count()) ? 2 : 1;
+  }
+  switch (variant) {
+    case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
+    case 2: return launch_tc<KIND, 1, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
+    case 3: return launch_tc<KIND, 2, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
+    default:
+      set_error("gemm: unknown variant %d", variant);
+      return DTN_ERR_INVALID;
+  }
+}
+
+}  // namespace dtn
+
+extern "C" {
+
+int dtn_gemm_set_variant(int variant) {
+  DTN_REQUIRE(variant >= 0 && variant <= 3, DTN_ERR_INVALID, "gemm: variant must be 0..3");
+  dtn::g_gemm_variant = variant;
+  return DTN_OK;
+}
+
+int dtn_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, size_t* bytes_out) {
+  using namespace dtn;
+  DTN_REQUIRE(bytes_out != nullptr, DTN_ERR_INVALID, "gemm: bytes_out is null");
+  DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm: negative extent");
+  DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
+              "gemm: unknown mode %d", mode);
+  *bytes_out = (mode == DTN_GEMM_F32 || M == 0 || N == 0 || K == 0) ? 0 : plane_layout(mode, M, N, K).total;
+  return DTN_OK;
+}
+
+int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, void* stream) {
+  using namespace dtn;
+  DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
+              "gemm: unknown mode %d", mode);
+  DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm: negative extent");
+  if (M == 0 || N == 0) return DTN_OK;
+  DTN_REQUIRE(C != nullptr, DTN_ERR_INVALID, "gemm: C is null");
+  DTN_REQUIRE(lda >= K && ldb >= N && ldc >= N, DTN_ERR_INVALID, "gemm: leading dimension smaller than the row");
+  DTN_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), DTN_ERR_UNSUPPORTED,
+              "gemm: extents must fit 31 bits");
+  cudaStream_t s = as_stream(stream);
+  if (K == 0) {
+    DTN_CUDA_CHECK(cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, s));
+    return DTN_OK;
+  }
+  DTN_REQUIRE(A != nullptr && B != nullptr, DTN_ERR_INVALID, "gemm: operand pointer is null");
+  DTN_REQUIRE(aligned_to(A, 4) && aligned_to(B, 4) && aligned_to(C, 4), DTN_ERR_INVALID,
+              "gemm: pointers must be 4-byte aligned");
+  if (mode == DTN_GEMM_F32) return gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s);
+
+  const PlaneLayout L = plane_layout(mode, M, N, K);
+  DTN_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, DTN_ERR_WORKSPACE,
+              "gemm: workspace of %zu bytes needed, %zu given", L.total, workspace_bytes);
+  DTN_REQUIRE(aligned_to(workspace, 1024), DTN_ERR_WORKSPACE, "gemm: workspace must be 1024-byte aligned");
+  uint8_t* ws = static_cast<uint8_t*>(workspace);
+  int rc;
+  if (mode == DTN_GEMM_BF16X3) {
+    if ((rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
+    return run_tc<0>(g_gemm_variant, ws, L, C, M, N, K, ldc, s);
+  }
+  if ((rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
+  return run_tc<1>(g_gemm_variant, ws, L, C, M, N, K, ldc, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,115 @@
+"""ctypes binding of libdeuteron_b200.so (the C ABI declared in include/deuteron_b200.h).
+
+The library is the product's only compute path: if it is missing or fails to load, importing this
+module's `lib()` raises. There is no CPU or PyTorch fallback.
+"""
+from __future__ import annotations
+
+import ctypes as ct
+import threading
+from pathlib import Path
+
+LIBRARY_PATH = Path(__file__).resolve().parent / 'libdeuteron_b200.so'
+
+OK, ERR_INVALID, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_DEVICE = range(6)
+
+GEMM_MODES = {'f32': 0, 'tf32x3': 1, 'bf16x3': 2}
+REDUCE_OPS = {'sum': 0, 'max': 1, 'sumsq': 2}
+STORAGE = {'f32': 0, 'f16': 1}
+ELEMENTWISE_OPS = {
+    'add': 0, 'subtract': 1, 'multiply': 2, 'divide': 3, 'maximum': 4, 'minimum': 5, 'relu': 6, 'exp': 7,
+    'sqrt': 8, 'rsqrt': 9, 'reciprocal': 10, 'negative': 11, 'absolute': 12, 'copy': 13, 'exp_fast': 7,
+}
+BINARY_OPS = frozenset(('add', 'subtract', 'multiply', 'divide', 'maximum', 'minimum'))
+
+
+class CudaError(RuntimeError):
+    """A CUDA call inside the library failed (mirrors benchmark.py:31-32 of the reference)."""
+
+
+class DeviceWaitError(RuntimeError):
+    """A kernel's bounded wait ran out and the kernel returned early with a status code."""
+
+
+_I64, _P, _F, _I = ct.c_int64, ct.c_void_p, ct.c_float, ct.c_int
+_SIGNATURES = {
+    'dtn_version': [],
+    'dtn_last_error': [ct.c_char_p, ct.c_size_t],
+    'dtn_device_status': [ct.POINTER(ct.c_int), _P],
+    'dtn_add_f32': [_P, _P, _P, _I64, _P],
+    'dtn_elementwise_f32': [_I, _P, _P, _P, _I64, _P],
+    'dtn_f16_copy': [_P, _P, _I64, _P],
+    'dtn_f16_widen': [_P, _P, _I64, _P],
+    'dtn_f16_narrow': [_P, _P, _I64, _P],
+    'dtn_row_reduce_f32': [_I, _P, _P, _I64, _I64, _I64, _P],
+    'dtn_gemm_workspace_bytes': [_I, _I64, _I64, _I64, ct.POINTER(ct.c_size_t)],
+    'dtn_gemm_x3': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, ct.c_size_t, _P],
+    'dtn_gemm_set_variant': [_I],
+    'dtn_attention_f32': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _F, _P],
+    'dtn_gqa_fwd': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _I64, _I64, _P],
+    'dtn_gqa_set_variant': [_I],
+}
+
+_lock = threading.Lock()
+_library = None
+
+
+def exported_symbols() -> tuple[str, ...]:
+    """Names this binding expects the shared library to export."""
+    return tuple(_SIGNATURES)
+
+
+def lib() -> ct.CDLL:
+    """The loaded shared library. Raises RuntimeError when it has not been built."""
+    global _library
+    with _lock:
+        if _library is None:
+            if not LIBRARY_PATH.exists():
+                raise RuntimeError(
+                    f'{LIBRARY_PATH} is missing: build it with `python -m deuteron_b200.csrc.build` '
+                    '(there is no fallback path)')
+            library = ct.CDLL(str(LIBRARY_PATH))
+            for name, argtypes in _SIGNATURES.items():
+                function = getattr(library, name)
+                function.argtypes = argtypes
+                function.restype = ct.c_int
+            _library = library
+        return _library
+
+
+def last_error() -> str:
+    buffer = ct.create_string_buffer(512)
+    lib().dtn_last_error(buffer, len(buffer))
+    return buffer.value.decode(errors='replace')
+
+
+def check(status: int) -> None:
+    """Turns a non-zero status into the exception the reference's surface would raise."""
+    if status == OK:
+        return
+    message = last_error() or f'deuteron_b200 status {status}'
+    if status in (ERR_INVALID, ERR_WORKSPACE):
+        raise ValueError(message)
+    if status == ERR_UNSUPPORTED:
+        raise NotImplementedError(message)
+    if status == ERR_DEVICE:
+        raise DeviceWaitError(message)
+    raise CudaError(message)
+
+
+def call(name: str, *args) -> None:
+    check(getattr(lib(), name)(*args))
+
+
+def device_status(stream: int = 0) -> int:
+    """Synchronises `stream` and returns (and clears) the device status word; 0 means clean."""
+    value = ct.c_int(0)
+    call('dtn_device_status', ct.byref(value), stream)
+    return value.value
+
+
+def raise_on_device_status(stream: int = 0) -> None:
+    status = device_status(stream)
+    if status:
+        role = {1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
+        raise DeviceWaitError(f'bounded wait ran out in the {role}, CTA {status & 0xff} (status {status:#x})')

@@ -1,0 +1,236 @@
+"""Device-resident operators: thin wrappers that hand torch CUDA tensors' pointers to the C ABI.
+
+torch is used for device memory and streams only; every computation below runs in
+libdeuteron_b200.so on the current torch stream. Tensors must live on the current CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as ct
+
+import torch
+
+from . import native
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for tensor in tensors:
+        if not isinstance(tensor, torch.Tensor) or not tensor.is_cuda:
+            raise ValueError('deuteron_b200 operators take CUDA tensors')
+
+
+def _flat(tensor: torch.Tensor, dtype: torch.dtype, label: str) -> torch.Tensor:
+    if tensor.dtype != dtype:
+        raise ValueError(f'{label} must have dtype {dtype}, got {tensor.dtype}')
+    if not tensor.is_contiguous():
+        raise ValueError(f'{label} must be contiguous')
+    return tensor
+
+
+# ------------------------------------------------------------------------------------------------
+# elementwise / f16
+# ------------------------------------------------------------------------------------------------
+
+
+def elementwise(op: str, x: torch.Tensor, y: torch.Tensor | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out = op(x, y) or op(x) elementwise in FP32 (operator names of the reference's ElementwiseImpl)."""
+    if op not in native.ELEMENTWISE_OPS:
+        raise NotImplementedError(f'elementwise operation {op}')
+    binary = op in native.BINARY_OPS
+    _require_cuda(x)
+    _flat(x, torch.float32, 'x')
+    if binary:
+        if y is None:
+            raise ValueError(f'{op} needs two operands')
+        _require_cuda(y)
+        _flat(y, torch.float32, 'y')
+        if y.shape != x.shape:
+            raise ValueError('operand shapes differ')
+    if out is None:
+        out = torch.empty_like(x)
+    _require_cuda(out)
+    _flat(out, torch.float32, 'out')
+    if out.shape != x.shape:
+        raise ValueError('output shape differs')
+    native.call('dtn_elementwise_f32', native.ELEMENTWISE_OPS[op], x.data_ptr(), y.data_ptr() if binary else None,
+                out.data_ptr(), x.numel(), _stream())
+    return out
+
+
+def add(x: torch.Tensor, y: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    return elementwise('add', x, y, out)
+
+
+def f16_copy(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(src)
+    _flat(src, torch.float16, 'src')
+    out = torch.empty_like(src) if out is None else _flat(out, torch.float16, 'out')
+    native.call('dtn_f16_copy', src.data_ptr(), out.data_ptr(), src.numel(), _stream())
+    return out
+
+
+def f16_widen(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(src)
+    _flat(src, torch.float16, 'src')
+    out = torch.empty(src.shape, dtype=torch.float32, device=src.device) if out is None else _flat(out, torch.float32, 'out')
+    native.call('dtn_f16_widen', src.data_ptr(), out.data_ptr(), src.numel(), _stream())
+    return out
+
+
+def f16_narrow(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    _require_cuda(src)
+    _flat(src, torch.float32, 'src')
+    out = torch.empty(src.shape, dtype=torch.float16, device=src.device) if out is None else _flat(out, torch.float16, 'out')
+    native.call('dtn_f16_narrow', src.data_ptr(), out.data_ptr(), src.numel(), _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# row reductions
+# ------------------------------------------------------------------------------------------------
+
+
+def row_reduce(op: str, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = sum / max / sumsq of row r of the 2-D FP32 tensor x (rows may be strided)."""
+    if op not in native.REDUCE_OPS:
+        raise NotImplementedError(f'row reduction {op}')
+    _require_cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or (x.shape[1] > 1 and x.stride(1) != 1):
+        raise ValueError('row_reduce takes a 2-D float32 tensor with unit column stride')
+    rows, cols = x.shape
+    ldx = x.stride(0) if rows > 1 else max(cols, 1)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.float32, device=x.device)
+    _flat(out, torch.float32, 'out')
+    native.call('dtn_row_reduce_f32', native.REDUCE_OPS[op], x.data_ptr(), out.data_ptr(), rows, cols, max(ldx, cols), _stream())
+    return out
+
+
+# ------------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------------
+
+_workspaces: dict[tuple[int, int], torch.Tensor] = {}
+
+
+def gemm_workspace_bytes(mode: str, m: int, n: int, k: int) -> int:
+    size = ct.c_size_t(0)
+    native.call('dtn_gemm_workspace_bytes', native.GEMM_MODES[mode], m, n, k, ct.byref(size))
+    return size.value
+
+
+def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    """Scratch for the operand planes, cached per (device, stream) and grown on demand."""
+    key = (device.index if device.index is not None else torch.cuda.current_device(), _stream())
+    buffer = _workspaces.get(key)
+    if buffer is None or buffer.numel() < nbytes + 1024:
+        buffer = torch.empty(nbytes + 1024, dtype=torch.uint8, device=device)
+        _workspaces[key] = buffer
+    return buffer
+
+
+def _row_major(tensor: torch.Tensor, label: str) -> int:
+    if tensor.dtype != torch.float32 or tensor.dim() != 2:
+        raise ValueError(f'{label} must be a 2-D float32 tensor')
+    if tensor.shape[1] > 1 and tensor.stride(1) != 1:
+        raise ValueError(f'{label} must be row-major (unit column stride)')
+    return tensor.stride(0) if tensor.shape[0] > 1 else max(tensor.shape[1], 1)
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, mode: str = 'bf16x3', out: torch.Tensor | None = None,
+         workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """C = A @ B with FP32 storage and the reference's contraction_precision `mode`.
+
+    a[M,K], b[K,N], out[M,N]: row-major; rows may be strided (a column block of a wider matrix).
+    """
+    if mode not in native.GEMM_MODES:
+        raise ValueError(f'unsupported contraction precision {mode!r}')
+    _require_cuda(a, b)
+    lda, ldb = _row_major(a, 'a'), _row_major(b, 'b')
+    m, k = a.shape
+    k2, n = b.shape
+    if k != k2:
+        raise ValueError(f'inner dimensions differ: {k} vs {k2}')
+    if out is None:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+    _require_cuda(out)
+    ldc = _row_major(out, 'out')
+    if tuple(out.shape) != (m, n):
+        raise ValueError('output shape differs')
+    nbytes = gemm_workspace_bytes(mode, m, n, k)
+    ws_ptr, ws_bytes = None, 0
+    if nbytes:
+        if workspace is None:
+            workspace = _workspace(nbytes, a.device)
+        base = workspace.data_ptr()
+        ws_ptr = (base + 1023) // 1024 * 1024
+        ws_bytes = workspace.numel() * workspace.element_size() - (ws_ptr - base)
+    native.call('dtn_gemm_x3', native.GEMM_MODES[mode], a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k,
+                max(lda, k), max(ldb, n), max(ldc, n), ws_ptr, ws_bytes, _stream())
+    return out
+
+
+def set_gemm_variant(variant: int) -> None:
+    native.call('dtn_gemm_set_variant', variant)
+
+
+# ------------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------------
+
+
+def attention(q: torch.Tensor, kt: torch.Tensor, v: torch.Tensor, scale: float, out: torch.Tensor | None = None) -> torch.Tensor:
+    """Single-head attention in the reference's example layout: q[rows,depth], kt[depth,keys], v[keys,cols]."""
+    _require_cuda(q, kt, v)
+    for tensor, label in ((q, 'q'), (kt, 'kt'), (v, 'v')):
+        _flat(tensor, torch.float32, label)
+        if tensor.dim() != 2:
+            raise ValueError(f'{label} must be 2-D')
+    rows, depth = q.shape
+    depth2, keys = kt.shape
+    keys2, cols = v.shape
+    if depth != depth2 or keys != keys2:
+        raise ValueError('attention operand shapes disagree')
+    if out is None:
+        out = torch.empty((rows, cols), dtype=torch.float32, device=q.device)
+    _flat(out, torch.float32, 'out')
+    native.call('dtn_attention_f32', q.data_ptr(), kt.data_ptr(), v.data_ptr(), out.data_ptr(), rows, keys, depth, cols,
+                float(scale), _stream())
+    return out
+
+
+def gqa_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, out: torch.Tensor | None = None,
+                  groups: tuple[int, int] | None = None) -> torch.Tensor:
+    """Grouped-query attention forward, non-causal: q[B,Hq,S,D], k/v[B,Hkv,S,D] (f16 or f32) -> out[B,Hq,S,D] f32.
+
+    `groups=(begin, end)` restricts the computation to that range of the B*Hkv (batch, kv-head) groups.
+    """
+    _require_cuda(q, k, v)
+    if q.dtype not in (torch.float16, torch.float32) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError('q, k, v must share dtype float16 or float32')
+    for tensor, label in ((q, 'q'), (k, 'k'), (v, 'v')):
+        if tensor.dim() != 4 or not tensor.is_contiguous():
+            raise ValueError(f'{label} must be a contiguous [B,H,S,D] tensor')
+    b, hq, s, d = q.shape
+    if k.shape != v.shape or k.shape[0] != b or k.shape[2] != s or k.shape[3] != d:
+        raise ValueError('k/v shapes disagree with q')
+    hkv = k.shape[1]
+    if out is None:
+        out = torch.empty((b, hq, s, d), dtype=torch.float32, device=q.device)
+    _flat(out, torch.float32, 'out')
+    begin, end = groups if groups is not None else (0, b * hkv)
+    native.call('dtn_gqa_fwd', q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), b, hq, hkv, s, d, float(scale),
+                native.STORAGE['f16' if q.dtype == torch.float16 else 'f32'], begin, end, _stream())
+    return out
+
+
+def set_gqa_variant(variant: int) -> None:
+    native.call('dtn_gqa_set_variant', variant)
+
+
+def check_device_status() -> None:
+    """Synchronises the current stream and raises if a kernel reported a wait that ran out."""
+    native.raise_on_device_status(_stream())

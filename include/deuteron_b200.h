@@ -1,0 +1,162 @@
+/*
+ * deuteron_b200 — C ABI of the B200 (sm_100a) kernels that stand in for the code the
+ * Deuteron compiler emits for its hot workloads.
+ *
+ * Conventions
+ *   - Every function returns an int status: 0 = ok, non-zero = DTN_ERR_* below.
+ *     dtn_last_error() gives the text of the calling thread's last failure.
+ *   - Pointers are DEVICE pointers unless a parameter says "host". The caller owns every
+ *     buffer. Buffers must not overlap. Nothing here allocates or frees device memory
+ *     (except where a function's comment says otherwise) and nothing synchronises the
+ *     stream: work is enqueued on `stream` (a cudaStream_t passed as void*, NULL = the
+ *     legacy default stream) and the call returns.
+ *   - Matrices are row-major with a leading dimension in ELEMENTS.
+ *   - Functions are re-entrant per stream. One-time kernel attribute set-up is guarded
+ *     internally.
+ *
+ * Each entry point names the part of the reference (stashuk-olek/deuteron, paths relative
+ * to that project) whose emitted kernel it replaces.
+ */
+#ifndef DEUTERON_B200_H
+#define DEUTERON_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define DTN_OK 0
+#define DTN_ERR_INVALID 1   /* bad argument (null pointer, negative size, bad enum, misalignment) */
+#define DTN_ERR_CUDA 2      /* a CUDA runtime/driver call failed; see dtn_last_error */
+#define DTN_ERR_WORKSPACE 3 /* workspace missing or too small */
+#define DTN_ERR_UNSUPPORTED 4 /* shape outside what the kernels implement */
+#define DTN_ERR_DEVICE 5    /* a kernel reported a bounded wait that ran out */
+
+/* contraction_precision of compiler/options.py:5-28 */
+#define DTN_GEMM_F32 0
+#define DTN_GEMM_TF32X3 1
+#define DTN_GEMM_BF16X3 2
+
+/* reduction operator of dtn_row_reduce_f32 */
+#define DTN_REDUCE_SUM 0
+#define DTN_REDUCE_MAX 1
+#define DTN_REDUCE_SUMSQ 2
+
+/* storage type of attention operands */
+#define DTN_STORAGE_F32 0
+#define DTN_STORAGE_F16 1
+
+/* binary / unary elementwise operators (compiler/codegen/lower.py:258-291) */
+#define DTN_EW_ADD 0
+#define DTN_EW_SUB 1
+#define DTN_EW_MUL 2
+#define DTN_EW_DIV 3
+#define DTN_EW_MAX 4
+#define DTN_EW_MIN 5
+#define DTN_EW_RELU 6
+#define DTN_EW_EXP 7
+#define DTN_EW_SQRT 8
+#define DTN_EW_RSQRT 9
+#define DTN_EW_RCP 10
+#define DTN_EW_NEG 11
+#define DTN_EW_ABS 12
+#define DTN_EW_COPY 13
+
+/* Library version: major*10000 + minor*100 + patch. No reference counterpart
+ * (the reference reports compiler/_version.py). */
+int dtn_version(void);
+
+/* Copies the calling thread's last error text (NUL terminated, truncated to n) into buf.
+ * Mirrors the name+string that benchmark.py:46-52 attaches to CudaError. */
+int dtn_last_error(char* buf, size_t n);
+
+/* Reads and clears the device-side status word that kernels with bounded waits write
+ * when a wait runs out. This call synchronises `stream`. *status_out = 0 when clean.
+ * No reference counterpart (its kernels have no device-side waits on async units). */
+int dtn_device_status(int* status_out /* host */, void* stream);
+
+/* out[i] = x[i] + y[i], i < n.  Replaces the elementwise kernel emitted by
+ * Lowering.tile / Load / Write (compiler/codegen/lower.py:434-495, 600-638) after
+ * vectorize_elementwise (compiler/passes/vectorize.py:160-178) for
+ * examples/vector_add/vector_add.ir.json. Bit-exact IEEE add. Any 4-byte aligned pointers. */
+int dtn_add_f32(const float* x, const float* y, float* out, int64_t n, void* stream);
+
+/* out[i] = op(x[i], y[i]) (binary ops) or op(x[i]) (unary ops, y ignored, may be NULL).
+ * Operator table of Lowering.arithmetic (compiler/codegen/lower.py:258-291). exp uses
+ * ex2.approx(x*log2(e)) and rcp/rsqrt the approximate forms, as approximate_math=True does. */
+int dtn_elementwise_f32(int op, const float* x, const float* y, float* out, int64_t n, void* stream);
+
+/* f16 storage kernels (compiler/storage.py:5-59, Lowering.convert compiler/codegen/lower.py:249-256,
+ * shapes of examples/f16_storage.py:19-60). f16 values travel as uint16_t bit patterns.
+ *   copy  : bit-preserving 16-bit move
+ *   widen : exact f16 -> f32
+ *   narrow: f32 -> f16 round-to-nearest-even, overflow to +-inf, subnormals kept, NaN -> NaN
+ * Pointers need only their natural alignment (2 bytes for f16, 4 for f32), like the
+ * scalar-aligned accesses of compiler/codegen/lower.py:604,623. */
+int dtn_f16_copy(const uint16_t* src, uint16_t* dst, int64_t n, void* stream);
+int dtn_f16_widen(const uint16_t* src, float* dst, int64_t n, void* stream);
+int dtn_f16_narrow(const float* src, uint16_t* dst, int64_t n, void* stream);
+
+/* out[r] = reduce_op over x[r, 0..cols) for r < rows; x has leading dimension ldx.
+ * Replaces the coalesced reduction of striped_reduction (compiler/transforms.py:62-95),
+ * Lowering.loop / register_reduction (compiler/codegen/lower.py:293-327, 348-421) and the
+ * warp-shuffle + tree tail (compiler/codegen/lower.py:517-569). SUM and SUMSQ are
+ * reassociated FP32 sums; MAX is the NaN-suppressing maxnum of lower.py:275-278 with
+ * identity -inf. */
+int dtn_row_reduce_f32(int op, const float* x, float* out, int64_t rows, int64_t cols,
+                       int64_t ldx, void* stream);
+
+/* Bytes of scratch dtn_gemm_x3 needs for (mode, M, N, K): the bf16 (or tf32) high and
+ * residual planes of A and of B transposed. 0 for DTN_GEMM_F32. */
+int dtn_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, size_t* bytes_out /* host */);
+
+/* C[M,N] = A[M,K] * B[K,N], FP32 in / FP32 out / FP32 accumulate, row-major.
+ *   DTN_GEMM_BF16X3: each operand v is split hi = bf16_rn(v), lo = bf16_rn(v - hi) and the
+ *     products lo_A*hi_B, hi_A*lo_B, hi_A*hi_B are accumulated in that order per k-step
+ *     (TensorEmitter.bf16 / packed_store / _emit_packed, compiler/codegen/tensor.py:55-64,
+ *     104-119, 121-190; stage_register_loads, compiler/passes/regstage.py:70-245).
+ *   DTN_GEMM_TF32X3: hi = tf32_rna(v), lo = tf32_rna(v - hi), same three products
+ *     (compiler/codegen/tensor.py:50-53, 192-245).
+ *   DTN_GEMM_F32: plain FP32 FMA (generic Lowering.body, compiler/codegen/lower.py:600-653).
+ * The result store replaces TensorEmitter._store (compiler/codegen/tensor.py:255-267).
+ * `workspace` must be 1024-byte aligned and at least dtn_gemm_workspace_bytes large for the
+ * x3 modes (ignored for F32). A column block of B / C is addressed by offsetting the
+ * pointers and keeping ldb / ldc. */
+int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
+                int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
+                size_t workspace_bytes, void* stream);
+
+/* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
+ *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile.
+ * No reference counterpart. */
+int dtn_gemm_set_variant(int variant);
+
+/* Single-head attention in the reference's example layout (examples/attention.py:59-66):
+ * q[rows,depth], kt[depth,keys], v[keys,cols], out[rows,cols], all FP32 row-major.
+ * out = softmax(q*kt*scale) * v with the staged recurrence of RecurrenceEmitter.emit
+ * (compiler/passes/recurrence.py:609-706): scores, warp max, ex2.approx((s-m)*log2e),
+ * warp sum, probability*value pass, reciprocal suffix (compiler/codegen/lower.py:264-270). */
+int dtn_attention_f32(const float* q, const float* kt, const float* v, float* out,
+                      int64_t rows, int64_t keys, int64_t depth, int64_t cols, float scale,
+                      void* stream);
+
+/* Grouped-query attention forward, non-causal.
+ * q[B,Hq,S,D], k[B,Hkv,S,D], v[B,Hkv,S,D] in `storage` (f16 bit patterns or f32),
+ * out[B,Hq,S,D] FP32. Query head h reads kv head h / (Hq/Hkv). FP32 compute with the online
+ * form of the recurrence above (stage_recurrences, compiler/passes/recurrence.py:47-388).
+ * `group_begin`/`group_end` select a range of the B*Hkv (batch, kv-head) groups, so that a
+ * rank of a multi-GPU job computes only its groups; pass 0 and B*Hkv for all. */
+int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq,
+                int64_t Hkv, int64_t S, int64_t D, float scale, int storage,
+                int64_t group_begin, int64_t group_end, void* stream);
+
+/* Selects the attention kernel: 0 = automatic, 1 = FP32 CUDA-core kernel,
+ * 2 = tensor-core kernel (f16 storage, D = 128). No reference counterpart. */
+int dtn_gqa_set_variant(int variant);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* DEUTERON_B200_H */
