@@ -1,0 +1,374 @@
+"""Benchmark of the hot path: compensated BF16x3 GEMM, M = N = K = 8192, FP32 in/out, on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+
+A step is one full pass of the hot path over one batch of seeded synthetic input: the operand
+split plus the tensor-core product kernel for C = A @ B with A, B uniform[-1, 1) (seeds 7, 11),
+through the C ABI. With N GPUs every rank owns one 8192-wide block of output columns of an
+8192 x (8192*N) product (weak scaling, no collective in the data path); the value is the aggregate
+TFLOP/s of 2*M*N*K useful flops, timed on the device with CUDA events, max over ranks.
+
+Printed JSON (one line, rank 0): the driver's contract keys plus
+  roofline     the product kernel's achieved TFLOP/s (its own launch time, measured with events
+               inside the timed steps) against the measured dense BF16 peak / 3
+  cpu_baseline the float64 NumPy product (the reference's own CPU check) timed on a bounded sample
+  e2e          the same metric through compile_kernel + LocalRunner.execute with HOST buffers
+               (pinned host -> device copies of A and B and the device -> host copy of C inside the
+               timed region)
+  extras       the other hot kernels (tf32x3 GEMM, attention, memory-bound kernels) at their
+               benchmark sizes, for context
+
+`--impl reference` times the reference's CPU implementation of the path (NumPy float64 product of
+the same operands, all host cores) on a bounded sample per step and prints the same line shape.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+M = N = K = 8192
+FLOPS_PER_GEMM = 2.0 * M * N * K
+WORKLOAD = 'gemm_bf16x3_8192x8192x8192_f32io'
+
+
+def measured_peaks() -> dict:
+    path = ROOT / 'MEASURED_PEAKS.json'
+    if path.exists():
+        data = json.loads(path.read_text())
+        return {'hbm_gbs': data['hbm_gbs'], 'bf16_tflops': data['bf16_tflops'],
+                'bf16_tflops_sustained': data.get('bf16_tflops_sustained', data['bf16_tflops']), 'source': 'measured'}
+    return {'hbm_gbs': 6650.0, 'bf16_tflops': 1590.0, 'bf16_tflops_sustained': 1400.0, 'source': 'fallback'}
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    QUERY = ('clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,'
+             'clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap')
+
+    def __init__(self, index: int) -> None:
+        self.index, self.samples, self.process, self.thread = index, [], None, None
+
+    def start(self) -> None:
+        try:
+            self.process = subprocess.Popen(['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.QUERY}',
+                                             '--format=csv,noheader,nounits', '-lms', '100'], stdout=subprocess.PIPE,
+                                            stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.process = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self) -> None:
+        for line in self.process.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def stop(self, begin: float, end: float) -> dict:
+        if self.process is None:
+            return {'sm_mhz': None, 'sm_max_mhz': None, 'reasons': ['nvidia-smi unavailable']}
+        time.sleep(0.15)
+        self.process.terminate()
+        try:
+            self.process.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.process.kill()
+        rows = [line for stamp, line in self.samples if begin - 0.05 <= stamp <= end + 0.15] or [line for _, line in self.samples]
+        clocks, maxima, power, reasons = [], [], [], set()
+        names = ('hw_slowdown', 'hw_thermal_slowdown', 'sw_thermal_slowdown', 'sw_power_cap')
+        for row in rows:
+            parts = [p.strip() for p in row.split(',')]
+            if len(parts) < 7:
+                continue
+            try:
+                clocks.append(float(parts[0])); maxima.append(float(parts[1])); power.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith('active'):
+                    reasons.add(name)
+        return {'sm_mhz': statistics.median(clocks) if clocks else None, 'sm_max_mhz': max(maxima) if maxima else None,
+                'power_w_max': max(power) if power else None, 'samples': len(clocks), 'reasons': sorted(reasons)}
+
+
+def cpu_gemm_sample(seconds_target: float = 12.0) -> dict:
+    """The reference's CPU check of this path (float64 NumPy product of the FP32 operands,
+    tests/test_tensor_copy.py:52) on a slab of A's rows sized to take roughly `seconds_target`."""
+    import numpy as np
+    from oracle import reference_math as oracle
+    cores = os.cpu_count() or 1
+    right = oracle.seeded_uniform(11, (K, N)).astype(np.float64)
+    rows = 64
+    probe = oracle.seeded_uniform(7, (rows, K))
+    started = time.perf_counter()
+    oracle.gemm_f64(probe, right)
+    elapsed = time.perf_counter() - started
+    rows = int(min(M, max(64, rows * seconds_target / max(elapsed, 1e-3)) // 64 * 64))
+    left = oracle.seeded_uniform(7, (rows, K))
+    started = time.perf_counter()
+    oracle.gemm_f64(left, right)
+    elapsed = time.perf_counter() - started
+    return {'value': 2.0 * rows * N * K / elapsed / 1e12, 'unit': 'TFLOP/s', 'cores': cores, 'kind': 'port',
+            'sample': f'float64 NumPy product of {rows} of the {M} rows of A with the full B ({elapsed:.1f} s)',
+            'rows': rows, 'seconds': elapsed}
+
+
+def run_reference(args) -> None:
+    """The reference arm: its CPU implementation of the path, on the host cores, rank 0 only."""
+    rank = int(os.environ.get('RANK', '0'))
+    if rank != 0:
+        return
+    import numpy as np
+    from oracle import reference_math as oracle
+    cores = os.cpu_count() or 1
+    right = oracle.seeded_uniform(11, (K, N)).astype(np.float64)
+    probe = oracle.seeded_uniform(7, (64, K))
+    started = time.perf_counter()
+    oracle.gemm_f64(probe, right)
+    per_row = (time.perf_counter() - started) / 64
+    total_steps = args.steps + args.warmup
+    budget = 150.0 / max(total_steps, 1)                       # keep the whole run within a few minutes
+    rows = int(min(M, max(64, budget / max(per_row, 1e-6)) // 64 * 64))
+    left = oracle.seeded_uniform(7, (rows, K))
+    for _ in range(args.warmup):
+        oracle.gemm_f64(left, right)
+    started = time.perf_counter()
+    for _ in range(args.steps):
+        oracle.gemm_f64(left, right)
+    elapsed = time.perf_counter() - started
+    value = 2.0 * rows * N * K * args.steps / elapsed / 1e12
+    sample = f'each step: float64 NumPy product of {rows} of the {M} rows of A with the full B'
+    print(json.dumps({
+        'impl': 'reference', 'metric': 'bf16x3_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': args.gpus,
+        'steps': args.steps, 'warmup': args.warmup, 'ms_per_step': elapsed / args.steps * 1e3, 'higher_is_better': True,
+        'scaling': 'weak', 'vs_baseline': None, 'dtype': 'f64', 'data': 'synthetic',
+        'config': {'workload': WORKLOAD, 'm': M, 'n': N, 'k': K, 'inputs': 'uniform[-1,1) seeds 7/11', 'sample': sample},
+        'cpu_baseline': {'value': value, 'unit': 'TFLOP/s', 'cores': cores, 'kind': 'port', 'sample': sample},
+        'e2e': {'value': value, 'unit': 'TFLOP/s', 'h2d_bytes_per_step': 0, 'd2h_bytes_per_step': 0},
+        'gpu_launches': 0,
+    }))
+
+
+def timed(torch, fn, iters: int, warmup: int = 3) -> float:
+    """Milliseconds per call of fn on the current stream (CUDA events, after warm-up)."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for _ in range(iters):
+        fn()
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / iters
+
+
+def extras(torch, ops, peaks: dict) -> dict:
+    """Other hot kernels at their benchmark sizes (inputs larger than L2), resident inputs."""
+    out = {}
+    device = torch.device('cuda', torch.cuda.current_device())
+    generator = torch.Generator(device=device).manual_seed(7)
+    a = torch.rand((M, K), device=device, generator=generator) * 2 - 1
+    b = torch.rand((K, N), device=device, generator=generator) * 2 - 1
+    c = torch.empty((M, N), device=device)
+    ms = timed(torch, lambda: ops.gemm(a, b, 'tf32x3', out=c), 5)
+    out['gemm_tf32x3_8192'] = {'ms': ms, 'tflops': FLOPS_PER_GEMM / ms / 1e9}
+    del a, b, c
+    n = 1 << 28
+    x = torch.randn(n, device=device, generator=generator)
+    y = torch.randn(n, device=device, generator=generator)
+    z = torch.empty_like(x)
+    half = torch.empty(n, dtype=torch.float16, device=device)
+    half2 = torch.empty_like(half)
+    rows = torch.empty(65536, device=device)
+    peak = peaks['hbm_gbs']
+    for name, fn, nbytes in (
+            ('add_f32_2^28', lambda: ops.add(x, y, z), 12 * n),
+            ('f16_narrow_2^28', lambda: ops.f16_narrow(x, half), 6 * n),
+            ('f16_widen_2^28', lambda: ops.f16_widen(half, z), 6 * n),
+            ('f16_copy_2^28', lambda: ops.f16_copy(half, half2), 4 * n),
+            ('row_sum_65536x4096', lambda: ops.row_reduce('sum', x.view(65536, 4096), rows), 4 * n + 4 * 65536),
+            ('row_max_65536x4096', lambda: ops.row_reduce('max', x.view(65536, 4096), rows), 4 * n + 4 * 65536)):
+        ms = timed(torch, fn, 10)
+        out[name] = {'ms': ms, 'gbs': nbytes / ms / 1e6, 'frac_of_hbm_peak': nbytes / ms / 1e6 / peak}
+    del x, y, z, half, half2
+    batch, hq, hkv, s, d = 4, 32, 8, 4096, 128
+    q = (torch.randn((batch, hq, s, d), device=device, generator=generator) / d ** 0.5).half()
+    k = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
+    v = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
+    o = torch.empty((batch, hq, s, d), device=device)
+    ms = timed(torch, lambda: ops.gqa_attention(q, k, v, d ** -0.5, out=o), 2, warmup=1)
+    flops = 4.0 * batch * hq * s * s * d
+    out['gqa_fwd_b4_h32_kv8_s4096_d128_f16'] = {'ms': ms, 'tflops': flops / ms / 1e9,
+                                               'frac_of_bf16_peak': flops / ms / 1e9 / peaks['bf16_tflops']}
+    return out
+
+
+def run_ours(args) -> None:
+    import numpy as np
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the kernels have no CPU path')
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    from deuteron_b200 import LocalRunner, Options, compile_kernel, native, ops, schedules, sharding
+    native.lib()
+    peaks = measured_peaks()
+
+    # Seeded inputs: rank r owns output columns [r*N, (r+1)*N) of an M x (N*world) product.
+    generator = torch.Generator(device=device)
+    generator.manual_seed(7)
+    a = torch.rand((M, K), device=device, generator=generator) * 2 - 1
+    generator.manual_seed(11 + rank)
+    b = torch.rand((K, N), device=device, generator=generator) * 2 - 1
+    c = torch.empty((M, N), device=device)
+    blocks = sharding.column_blocks(N * world, world)
+    assert blocks[rank] == (rank * N, (rank + 1) * N)
+
+    def barrier() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        ops.gemm(a, b, 'bf16x3', out=c)
+    ops.check_device_status()
+
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    events = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    wall_begin = time.perf_counter()
+    for step in range(args.steps):
+        events[step][0].record()
+        ops.gemm(a, b, 'bf16x3', out=c, phase=1)      # operand split: 2 kernels
+        events[step][1].record()
+        ops.gemm(a, b, 'bf16x3', out=c, phase=2)      # tensor-core product kernel: 1 kernel
+        events[step][2].record()
+    barrier()
+    wall_end = time.perf_counter()
+    total_ms = events[0][0].elapsed_time(events[-1][2])
+    product_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in events)
+    split_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in events)
+    ops.check_device_status()
+    clocks = sampler.stop(wall_begin, wall_end) if rank == 0 else None
+    if world > 1:
+        gathered = torch.tensor([total_ms], device=device)
+        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+        total_ms = float(gathered.item())
+    value = FLOPS_PER_GEMM * world * args.steps / total_ms / 1e9
+
+    # Parity spot check inside the bench: 32 sampled rows against a float64 product on the GPU's own data.
+    sample_rows = torch.arange(0, M, M // 32, device=device)
+    exact = a[sample_rows].double() @ b.double()
+    rel_error = float(((c[sample_rows].double() - exact).abs().max() / exact.abs().max()).item())
+    del exact
+
+    # End to end through the reference-facing surface, host buffers in, host buffers out.
+    e2e = None
+    if True:
+        graph, meta = schedules.matmul_example(M, N, K)
+        compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3, options=Options(contraction_precision='bf16x3'))
+        with LocalRunner(local_rank) as runner:
+            host = {'left': runner.pinned((M, K), np.float32), 'right': runner.pinned((K, N), np.float32)}
+            host['left'][:] = a.cpu().numpy()
+            host['right'][:] = b.cpu().numpy()
+            result = {'result': runner.pinned((M, N), np.float32)}
+            e2e_steps = max(3, min(args.steps, 10))
+            for _ in range(2):
+                runner.execute(compiled, host, result)
+            barrier()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(runner.stream)
+            for _ in range(e2e_steps):
+                runner.execute(compiled, host, result, synchronize=True)
+            end.record(runner.stream)
+            end.synchronize()
+            e2e_ms = begin.elapsed_time(end)
+            if world > 1:
+                gathered = torch.tensor([e2e_ms], device=device)
+                dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+                e2e_ms = float(gathered.item())
+            e2e_match = bool(np.array_equal(result['result'][:64], c[:64].cpu().numpy()))
+            e2e = {'value': FLOPS_PER_GEMM * world * e2e_steps / e2e_ms / 1e9, 'unit': 'TFLOP/s',
+                   'h2d_bytes_per_step': 4 * (M * K + K * N), 'd2h_bytes_per_step': 4 * M * N, 'steps': e2e_steps,
+                   'ms_per_step': e2e_ms / e2e_steps, 'call': 'compile_kernel + LocalRunner.execute (pinned host buffers)',
+                   'matches_resident_result': e2e_match}
+            del host, result
+
+    if rank == 0:
+        peak = peaks['bf16_tflops'] / 3.0
+        achieved = FLOPS_PER_GEMM / product_ms / 1e9
+        line = {
+            'metric': 'bf16x3_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
+            'warmup': max(args.warmup, 3), 'ms_per_step': total_ms / args.steps, 'higher_is_better': True, 'scaling': 'weak',
+            'vs_baseline': None, 'dtype': 'bf16x3 (bf16 hi/lo operands, f32 accumulate, f32 in/out)', 'data': 'synthetic',
+            'config': {'workload': WORKLOAD, 'm': M, 'n_per_gpu': N, 'k': K, 'inputs': 'uniform[-1,1), seeds 7 and 11+rank',
+                       'parallelism': f'output column blocks x{world}, no collective',
+                       'l2': 'inputs (512 MiB) and operand planes (512 MiB) exceed the 126 MB L2; no flush between steps',
+                       'step': 'operand split (2 kernels) + tcgen05 product kernel (1 kernel)'},
+            'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak,
+                         'traffic': None, 'kernel': 'gemm_x3_kernel (product kernel only)', 'ms_per_launch': product_ms,
+                         'split_ms_per_step': split_ms,
+                         'peak_source': f"{peaks['source']} dense bf16 burst peak {peaks['bf16_tflops']} TFLOP/s / 3 products"},
+            'clocks': clocks,
+            'e2e': e2e,
+            'gpu_launches': 3 * args.steps,
+            'max_rel_error_vs_f64_sampled_rows': rel_error,
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line['cpu_baseline'] = cpu_gemm_sample()
+        if world == 1 and not args.no_extras:
+            del a, b, c
+            torch.cuda.empty_cache()
+            line['extras'] = extras(torch, ops, peaks)
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument('--gpus', type=int, default=1)
+    parser.add_argument('--steps', type=int, default=20)
+    parser.add_argument('--warmup', type=int, default=3)
+    parser.add_argument('--impl', choices=('ours', 'reference'), default='ours')
+    parser.add_argument('--no-cpu-baseline', action='store_true')
+    parser.add_argument('--no-extras', action='store_true')
+    args = parser.parse_args()
+    if args.steps < 1 or args.warmup < 0:
+        raise SystemExit('steps must be positive and warmup nonnegative')
+    if args.impl == 'reference':
+        run_reference(args)
+        return
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if args.gpus > 1 and world == 1:
+        # convenience: relaunch under torchrun when called directly with --gpus N
+        command = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={args.gpus}',
+                   '--master-addr', '127.0.0.1', '--master-port', '29511', __file__, *sys.argv[1:]]
+        raise SystemExit(subprocess.call(command))
+    run_ours(args)
+
+
+if __name__ == '__main__':
+    main()

@@ -1,0 +1,368 @@
+"""Workload classifier: maps a parsed, scheduled kernel to the native kernel that computes it.
+
+The reference recognises the same structures before it emits specialised code: a dense
+shared-memory contraction (compiler/passes/contraction.py:58-213), the online-softmax recurrence
+(compiler/passes/recurrence.py:193-388), thread-strided reductions (compiler/transforms.py:62-95) and
+Load/Assign/Write elementwise tiles (compiler/passes/vectorize.py:31-128, compiler/storage.py:27-58).
+Here the recognised structure selects a hand-written sm_100a kernel; anything else raises
+NotImplementedError. Classification reads structure and buffer shapes, never names.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+from typing import Any
+
+from . import ir
+from .native import BINARY_OPS, ELEMENTWISE_OPS
+
+
+@dataclass(frozen=True)
+class Plan:
+    """What to run: `kind` picks the C-ABI entry point, `params` its shape arguments, `buffers` the
+    role of each meta.json buffer (role -> (buffer name, element offset))."""
+    kind: str
+    params: dict[str, Any] = field(default_factory=dict)
+    buffers: dict[str, tuple[str, int]] = field(default_factory=dict)
+
+    def describe(self) -> str:
+        roles = ', '.join(f'{role}={name}+{offset}' if offset else f'{role}={name}' for role, (name, offset) in self.buffers.items())
+        settings = ', '.join(f'{key}={value}' for key, value in self.params.items())
+        return f'{self.kind}({settings}; {roles})'
+
+
+def _op_name(op: Any) -> str:
+    return op.name if isinstance(op, ir.Node) else str(op)
+
+
+def _dtype_name(dtype: Any) -> str | None:
+    if isinstance(dtype, ir.Node) and dtype.kind == 'DataType':
+        return dtype.name
+    return None
+
+
+def _single_tile(kernel: ir.Kernel) -> ir.Node:
+    tiles = [stmt for stmt in kernel.body if stmt.kind == 'Tile']
+    if len(tiles) != 1 or len(kernel.body) != 1:
+        raise NotImplementedError('expected a kernel body of exactly one Tile')
+    return tiles[0]
+
+
+def _shape(specs: dict, name: str) -> tuple[int, ...]:
+    return tuple(specs[name]['shape'])
+
+
+# ------------------------------------------------------------------------------------------------
+# contraction
+# ------------------------------------------------------------------------------------------------
+
+
+def _classify_gemm(tile: ir.Node, specs: dict, precision: str) -> Plan | None:
+    statements = list(ir.walk([tile]))
+    accums = [s for s in statements if s.kind == 'Accum' and _op_name(s.op) == 'add']
+    assigns = {s.name: s for s in statements if s.kind == 'Assign'}
+    products = [assigns[a.value] for a in accums if a.value in assigns and _op_name(assigns[a.value].op) == 'multiply'
+                and len(assigns[a.value].args) == 2]
+    writes = [s for s in statements if s.kind == 'Write']
+    if not products or not writes or any(len(w.index) != 2 for w in writes):
+        return None
+    if any(_op_name(s.op) in ('exp', 'maximum') for s in assigns.values()):
+        return None
+    if any(w.atomic for w in writes):
+        raise NotImplementedError('atomic (split-K) contractions are outside the supported subset')
+    output = writes[0].output
+    if any(w.output != output for w in writes):
+        return None
+    loads = {}
+    for stmt in statements:
+        if stmt.kind == 'Load':
+            for name in stmt.names:
+                loads[name] = stmt
+    copies: dict[str, str] = {}
+    for stmt in statements:
+        if stmt.kind == 'CpAsyncCopy':
+            if copies.setdefault(stmt.smem, stmt.src) != stmt.src:
+                return None
+    # the reduction axis is the loop variable that indexes both operands of the product
+    accum_axes = set()
+    for accum in accums:
+        accum_axes.update(accum.axes or ())
+    left = right = None
+    for product in products:
+        for operand in product.args:
+            load = loads.get(operand)
+            if load is None or len(load.index) != 2:
+                return None
+            source = copies.get(load.input, load.input)
+            if source not in specs:
+                return None
+            in_row = bool(ir.expression_vars(load.index[0]) & accum_axes)
+            in_col = bool(ir.expression_vars(load.index[1]) & accum_axes)
+            if in_col and not in_row:      # indexed [row, k]
+                if left not in (None, source):
+                    return None
+                left = source
+            elif in_row and not in_col:    # indexed [k, col]
+                if right not in (None, source):
+                    return None
+                right = source
+            else:
+                return None
+    if left is None or right is None or left == right:
+        return None
+    (m, k), (k2, n), out_shape = _shape(specs, left), _shape(specs, right), _shape(specs, output)
+    if k != k2 or out_shape != (m, n):
+        raise ValueError(f'contraction shapes disagree: {left}{[m, k]} @ {right}{[k2, n]} -> {output}{list(out_shape)}')
+    for name in (left, right, output):
+        if specs[name]['dtype'] != 'f32':
+            raise NotImplementedError('contractions take f32 buffers')
+    return Plan('gemm', {'mode': precision, 'm': m, 'n': n, 'k': k},
+                {'left': (left, 0), 'right': (right, 0), 'out': (output, 0)})
+
+
+# ------------------------------------------------------------------------------------------------
+# attention recurrence
+# ------------------------------------------------------------------------------------------------
+
+
+def _classify_attention(tile: ir.Node, specs: dict) -> Plan | None:
+    statements = list(ir.walk([tile]))
+    assigns = [s for s in statements if s.kind == 'Assign']
+    ops = [_op_name(s.op) for s in assigns]
+    if ops.count('exp') + ops.count('exp_fast') < 2 or 'reciprocal' not in ops:
+        return None
+    if not any(s.kind == 'Accum' and _op_name(s.op) == 'maximum' for s in statements):
+        return None
+    outer = [s for s in tile.body if s.kind == 'Loop']
+    if len(outer) != 1:
+        return None
+    key_axis = outer[0].axis.name
+    inner = [s for s in outer[0].body if s.kind == 'Loop']
+    if len(inner) != 1:
+        return None
+    dot_axis = inner[0].axis.name
+    q = kt = v = None
+    for load in (s for s in inner[0].body if s.kind == 'Load'):
+        if len(load.index) != 2:
+            return None
+        first, second = (ir.expression_vars(e) for e in load.index)
+        if dot_axis in second and key_axis not in first | second:
+            q = load.input
+        elif dot_axis in first and key_axis in second:
+            kt = load.input
+    for load in (s for s in outer[0].body if s.kind == 'Load'):
+        if len(load.index) == 2 and key_axis in ir.expression_vars(load.index[0]):
+            v = load.input
+    writes = [s for s in tile.body if s.kind == 'Write']
+    if None in (q, kt, v) or len(writes) != 1:
+        return None
+    out = writes[0].output
+    (rows, depth), (depth2, keys), (keys2, cols) = _shape(specs, q), _shape(specs, kt), _shape(specs, v)
+    if depth != depth2 or keys != keys2 or _shape(specs, out) != (rows, cols):
+        raise ValueError('attention buffer shapes disagree')
+    if outer[0].axis.extent.value != keys or inner[0].axis.extent.value != depth:
+        raise ValueError('attention loop extents disagree with the buffer shapes')
+    for name in (q, kt, v, out):
+        if specs[name]['dtype'] != 'f32':
+            raise NotImplementedError('the attention recurrence takes f32 buffers')
+    # the uniform score scale: a Let literal that multiplies the score, or a one-element data buffer
+    # the score is multiplied or divided by
+    scale = None
+    lets = {s.name: s for s in tile.body if s.kind == 'Let'}
+    scalar_loads = {}
+    for load in (s for s in tile.body if s.kind == 'Load'):
+        if math.prod(_shape(specs, load.input)) == 1 and 'data' in specs[load.input]:
+            for name in load.names:
+                scalar_loads[name] = float(specs[load.input]['data'][0] if isinstance(specs[load.input]['data'], (list, tuple)) else specs[load.input]['data'])
+    score_sums = {s.name for s in inner[0].body if s.kind == 'Accum'}
+    for assign in (s for s in outer[0].body if s.kind == 'Assign'):
+        op = _op_name(assign.op)
+        if op in ('multiply', 'divide') and len(assign.args) == 2 and set(assign.args) & score_sums:
+            other = next(a for a in assign.args if a not in score_sums) if len(set(assign.args) & score_sums) == 1 else None
+            if other in lets and isinstance(lets[other].value, ir.Node) and lets[other].value.kind == 'Literal':
+                value = float(lets[other].value.value)
+            elif other in scalar_loads:
+                value = scalar_loads[other]
+            else:
+                return None
+            if op == 'divide':
+                if assign.args[0] not in score_sums:
+                    return None
+                value = 1.0 / value
+            scale = value
+            break
+    if scale is None:
+        scale = 1.0
+    return Plan('attention', {'rows': rows, 'keys': keys, 'depth': depth, 'cols': cols, 'scale': scale},
+                {'q': (q, 0), 'kt': (kt, 0), 'v': (v, 0), 'out': (out, 0)})
+
+
+# ------------------------------------------------------------------------------------------------
+# row reductions
+# ------------------------------------------------------------------------------------------------
+
+
+def _classify_reduction(tile: ir.Node, specs: dict) -> Plan | None:
+    statements = list(ir.walk([tile]))
+    if any(s.kind in ('Smem', 'CpAsyncCopy') for s in statements):
+        return None
+    loops = [s for s in statements if s.kind in ('StridedLoop', 'Loop')]
+    accums = [s for s in statements if s.kind == 'Accum']
+    writes = [s for s in statements if s.kind == 'Write']
+    loads = [s for s in statements if s.kind == 'Load']
+    if len(loops) != 1 or not accums or len(writes) != 1 or len(loads) != 1:
+        return None
+    if not all(s.kind in ('Load', 'Assign', 'Accum') for s in loops[0].body):
+        return None
+    ops = {_op_name(a.op) for a in accums}
+    if len(ops) != 1:
+        return None
+    op = {'add': 'sum', 'maximum': 'max'}.get(ops.pop())
+    if op is None:
+        raise NotImplementedError('row reductions implement add and maximum')
+    body_assigns = [s for s in loops[0].body if s.kind == 'Assign']
+    if body_assigns:
+        square = (len(body_assigns) == 1 and _op_name(body_assigns[0].op) == 'multiply'
+                  and len(set(body_assigns[0].args)) == 1 and op == 'sum')
+        if not square:
+            raise NotImplementedError('row reductions accept a plain value or its square')
+        op = 'sumsq'
+    source, output = loads[0].input, writes[0].output
+    in_shape, out_shape = _shape(specs, source), _shape(specs, output)
+    if specs[source]['dtype'] != 'f32' or specs[output]['dtype'] != 'f32':
+        raise NotImplementedError('row reductions take f32 buffers')
+    if len(in_shape) == 2 and out_shape in ((in_shape[0],), (in_shape[0], 1)):
+        rows, cols = in_shape
+    elif len(in_shape) == 1 and math.prod(out_shape) == 1:
+        rows, cols = 1, in_shape[0]
+    else:
+        raise NotImplementedError('row reductions map x[rows, cols] to out[rows] or x[n] to out[1]')
+    return Plan('row_reduce', {'op': op, 'rows': rows, 'cols': cols}, {'x': (source, 0), 'out': (output, 0)})
+
+
+# ------------------------------------------------------------------------------------------------
+# elementwise / f16 storage
+# ------------------------------------------------------------------------------------------------
+
+
+def _flat_access(index: tuple, element_vars: dict[str, int], width: int, label: str) -> int | None:
+    """Offset of a 1-D access `element * width + offset`, None for a constant (broadcast) index;
+    raises when the access has another form."""
+    if len(index) != 1:
+        raise NotImplementedError(f'{label}: elementwise kernels take 1-D buffers')
+    form = ir.affine(index[0])
+    if form is None:
+        raise NotImplementedError(f'{label}: index is not affine')
+    coefficients, offset = form
+    if not coefficients:
+        return None
+    if len(coefficients) != 1 or next(iter(coefficients)) not in element_vars or next(iter(coefficients.values())) != width:
+        raise NotImplementedError(f'{label}: access is not a contiguous run of {width} elements per tile item')
+    if offset < 0:
+        raise ValueError(f'{label}: negative origin')
+    return offset
+
+
+def _classify_elementwise(tile: ir.Node, specs: dict) -> Plan | None:
+    body = tuple(tile.body)
+    element_vars = {axis.name: axis.extent.value for axis in tile.axes}
+    count_items = math.prod(element_vars.values())
+    if len(body) == 1 and body[0].kind == 'StridedLoop' and len(tile.axes) == 1:
+        loop = body[0]
+        # thread-strided walk over the items: the loop axis replaces the tile axis
+        start = ir.affine(loop.start)
+        if start is None or start[0] != {tile.axes[0].name: 1} or start[1] != 0:
+            raise NotImplementedError('strided elementwise loops start at the tile item')
+        element_vars = {loop.axis.name: loop.axis.extent.value}
+        count_items = loop.axis.extent.value
+        body = tuple(loop.body)
+    if not body or any(s.kind not in ('Load', 'Assign', 'Write') for s in body):
+        return None
+    if len(element_vars) != 1:
+        raise NotImplementedError('elementwise kernels use one tile axis')
+    loads = [s for s in body if s.kind == 'Load']
+    writes = [s for s in body if s.kind == 'Write']
+    assigns = [s for s in body if s.kind == 'Assign']
+    if len(writes) != 1 or not loads:
+        return None
+    write = writes[0]
+    width = len(write.values)
+    n = count_items * width
+    out_offset = _flat_access(write.index, element_vars, width, write.output)
+    if out_offset is None:
+        raise NotImplementedError('elementwise output must advance with the tile item')
+    # symbolic value of every name: ('load', buffer, lane) or ('op', name, args)
+    values: dict[str, tuple] = {}
+    origins: dict[str, int | None] = {}
+    for load in loads:
+        offset = _flat_access(load.index, element_vars, len(load.names), load.input)
+        if offset is not None and len(load.names) != width:
+            raise NotImplementedError('vector loads and stores must have the same width')
+        if origins.setdefault(load.input, offset) != offset:
+            raise NotImplementedError('one origin per input buffer')
+        for lane, name in enumerate(load.names):
+            values[name] = ('load', load.input, lane if offset is not None else None)
+    for assign in assigns:
+        values[assign.name] = ('op', _op_name(assign.op), tuple(assign.args))
+
+    def resolve(name: str, lane: int) -> tuple:
+        if name not in values:
+            raise ValueError(f'undefined value {name}')
+        entry = values[name]
+        if entry[0] == 'load':
+            if entry[2] is not None and entry[2] != lane:
+                raise NotImplementedError('elementwise lanes must not mix vector elements')
+            return ('load', entry[1])
+        op, args = entry[1], entry[2]
+        if op == 'copy':
+            return resolve(args[0], lane)
+        return ('op', op, tuple(resolve(a, lane) for a in args))
+
+    trees = {resolve(name, lane) for lane, name in enumerate(write.values)}
+    if len(trees) != 1:
+        raise NotImplementedError('every vector lane must compute the same expression')
+    tree = trees.pop()
+    out_dtype = specs[write.output]['dtype']
+    check = [(write.output, out_offset)] + [(name, offset) for name, offset in origins.items() if offset is not None]
+    for name, offset in check:
+        if math.prod(_shape(specs, name)) < offset + n:
+            raise ValueError(f'{name}: access runs past the end of the buffer')
+    if tree[0] == 'load':
+        source = tree[1]
+        in_dtype = specs[source]['dtype']
+        kind = {('f16', 'f16'): 'f16_copy', ('f16', 'f32'): 'f16_widen', ('f32', 'f16'): 'f16_narrow',
+                ('f32', 'f32'): 'elementwise'}[(in_dtype, out_dtype)]
+        params = {'n': n} if kind != 'elementwise' else {'op': 'copy', 'n': n}
+        return Plan(kind, params, {'x': (source, origins[source]), 'out': (write.output, out_offset)})
+    op, args = tree[1], tree[2]
+    if op not in ELEMENTWISE_OPS:
+        raise NotImplementedError(f'elementwise operation {op}')
+    if any(arg[0] != 'load' for arg in args):
+        raise NotImplementedError('chained elementwise expressions are outside the supported subset')
+    names = [arg[1] for arg in args]
+    if any(origins[name] is None for name in names):
+        raise NotImplementedError('broadcast scalar operands are outside the supported subset')
+    if out_dtype != 'f32' or any(specs[name]['dtype'] != 'f32' for name in names):
+        raise NotImplementedError('f16 buffers support copy, widen and narrow; arithmetic takes f32 buffers')
+    if op in BINARY_OPS:
+        if len(names) != 2:
+            raise ValueError(f'{op} takes two operands')
+        return Plan('elementwise', {'op': op, 'n': n},
+                    {'x': (names[0], origins[names[0]]), 'y': (names[1], origins[names[1]]), 'out': (write.output, out_offset)})
+    if len(names) != 1:
+        raise ValueError(f'{op} takes one operand')
+    return Plan('elementwise', {'op': op, 'n': n}, {'x': (names[0], origins[names[0]]), 'out': (write.output, out_offset)})
+
+
+# ------------------------------------------------------------------------------------------------
+
+
+def classify(kernel: ir.Kernel, launch: dict, specs: dict, precision: str) -> Plan:
+    """Returns the native plan of a validated kernel or raises NotImplementedError."""
+    tile = _single_tile(kernel)
+    for recogniser in (lambda: _classify_attention(tile, specs), lambda: _classify_gemm(tile, specs, precision),
+                       lambda: _classify_reduction(tile, specs), lambda: _classify_elementwise(tile, specs)):
+        plan = recogniser()
+        if plan is not None:
+            return plan
+    raise NotImplementedError(f'kernel {kernel.name}: no native sm_100a kernel matches this schedule')

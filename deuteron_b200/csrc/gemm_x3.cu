@@ -558,9 +558,11 @@ int dtn_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, size_t* 
   return DTN_OK;
 }
 
-int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, void* stream) {
+int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                      int64_t lda, int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, int phase,
+                      void* stream) {
   using namespace dtn;
+  DTN_REQUIRE(phase >= 1 && phase <= 3, DTN_ERR_INVALID, "gemm: phase must be 1 (split), 2 (products) or 3 (both)");
   DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
               "gemm: unknown mode %d", mode);
   DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm: negative extent");
@@ -577,7 +579,7 @@ int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, i
   DTN_REQUIRE(A != nullptr && B != nullptr, DTN_ERR_INVALID, "gemm: operand pointer is null");
   DTN_REQUIRE(aligned_to(A, 4) && aligned_to(B, 4) && aligned_to(C, 4), DTN_ERR_INVALID,
               "gemm: pointers must be 4-byte aligned");
-  if (mode == DTN_GEMM_F32) return gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s);
+  if (mode == DTN_GEMM_F32) return (phase & 2) ? gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s) : DTN_OK;
 
   const PlaneLayout L = plane_layout(mode, M, N, K);
   DTN_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, DTN_ERR_WORKSPACE,
@@ -586,11 +588,16 @@ int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, i
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int rc;
   if (mode == DTN_GEMM_BF16X3) {
-    if ((rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
-    return run_tc<0>(g_gemm_variant, ws, L, C, M, N, K, ldc, s);
+    if ((phase & 1) && (rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
+    return (phase & 2) ? run_tc<0>(g_gemm_variant, ws, L, C, M, N, K, ldc, s) : DTN_OK;
   }
-  if ((rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
-  return run_tc<1>(g_gemm_variant, ws, L, C, M, N, K, ldc, s);
+  if ((phase & 1) && (rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
+  return (phase & 2) ? run_tc<1>(g_gemm_variant, ws, L, C, M, N, K, ldc, s) : DTN_OK;
+}
+
+int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, void* stream) {
+  return dtn_gemm_x3_phase(mode, A, B, C, M, N, K, lda, ldb, ldc, workspace, workspace_bytes, 3, stream);
 }
 
 }  // extern "C"

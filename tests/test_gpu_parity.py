@@ -1,0 +1,457 @@
+"""Parity of the CUDA path against the oracle and the reference's fixtures, through the C ABI.
+
+Every test here launches kernels of libdeuteron_b200.so (via ctypes) on cuda:0. Bars:
+  * bit-exact for vector add, f16 copy / widen / narrow, row max, and the FP32 contraction (whose
+    output must hash to the reference's own published GPU output);
+  * compensated GEMM: within the reference's rtol = atol = 1e-3 of the float64 product and max error
+    no worse than 2x the reference's published error on its 128^3 example; elsewhere no worse than 2x
+    the error floor of the three-product scheme plus the FP32 accumulation allowance stated below;
+  * attention: the reference's rtol 1e-3 / atol 1e-4 against float64 and max error within 2x its published
+    1.10e-7 on its example;
+  * FP32 sums: within the order-independent bound (n-1) * eps * sum|x|.
+"""
+import hashlib
+import math
+
+import numpy as np
+import pytest
+
+from deuteron_b200 import LocalRunner, Options, compile_kernel, native, ops, schedules
+from oracle import reference_math as R
+
+pytestmark = pytest.mark.gpu
+
+
+def sha(array):
+    return hashlib.sha256(np.ascontiguousarray(array).tobytes()).hexdigest()
+
+
+@pytest.fixture(scope='module')
+def dev(cuda):
+    return cuda.device('cuda', 0)
+
+
+@pytest.fixture(scope='module')
+def runner(cuda):
+    with LocalRunner(0) as local:
+        yield local
+
+
+def to_device(cuda, array):
+    return cuda.from_numpy(np.ascontiguousarray(array)).to('cuda:0')
+
+
+def run_with_data(runner, graph, meta, values, **timing):
+    """tests/test_f16_storage.py:110-117: replace seeded inputs by explicit data, one launch."""
+    import copy
+    launch = copy.deepcopy(meta['kernels'][0])
+    for arg in launch['args']:
+        if arg['name'] in values:
+            arg.pop('seed', None)
+            arg['data'] = values[arg['name']]
+    meta = dict(meta, kernels=[launch])
+    compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3)
+    timing = timing or {'warmup': 0, 'iters': 1, 'samples': 1}
+    return runner.run_kernel(launch, compiled, **timing)['outputs']
+
+
+# ------------------------------------------------------------------------------------------------
+# elementwise and f16 storage
+# ------------------------------------------------------------------------------------------------
+
+
+def test_vector_add_example_is_exact_and_hashes_to_the_reference_output(runner, golden, published):
+    graph, meta = schedules.vector_add_example()
+    compiled = compile_kernel(graph, meta)
+    result = runner.run_kernel(meta['kernels'][0], compiled, warmup=1, iters=3, samples=2)
+    produced = result['outputs']['sum']
+    np.testing.assert_array_equal(produced, np.load(golden / 'vector_add_expected.npz')['sum'])
+    assert sha(produced) == published['results']['vector_add']['output_sha256']['sum']
+    assert result['median_us'] > 0 and result['timing_method'] == 'cuda_graph_batch_events'
+
+
+def test_f16_examples_hash_to_the_reference_outputs(runner, published):
+    for kind in ('copy', 'widen', 'narrow'):
+        graph, meta = schedules.f16_storage_example(kind)
+        compiled = compile_kernel(graph, meta)
+        produced = runner.run_kernel(meta['kernels'][0], compiled, warmup=0, iters=1, samples=1)['outputs']['result']
+        assert sha(produced) == published['results'][kind]['output_sha256']['result'], kind
+
+
+def test_all_half_bits_copy_exactly_at_scalar_and_vector_widths(runner):
+    data = np.arange(65536, dtype=np.uint16).view(np.float16)
+    for width in (1, 2, 4):
+        graph, meta = schedules.f16_storage_example('copy', count=data.size, width=width)
+        actual = run_with_data(runner, graph, meta, {'x': data})['result']
+        np.testing.assert_array_equal(actual.view(np.uint16), data.view(np.uint16))
+
+
+def test_half_widening_is_exact_on_every_pattern(runner):
+    data = np.arange(65536, dtype=np.uint16).view(np.float16)
+    graph, meta = schedules.f16_storage_example('widen', count=data.size)
+    actual = run_with_data(runner, graph, meta, {'x': data})['result']
+    expected = R.f16_widen_bits(data.view(np.uint16))
+    finite = ~np.isnan(expected)
+    np.testing.assert_array_equal(actual[finite].view(np.uint32), expected[finite].view(np.uint32))
+    np.testing.assert_array_equal(np.isnan(actual), np.isnan(expected))
+
+
+def test_round_to_nearest_even_half_boundaries(runner):
+    points = R.f16_boundary_points()
+    graph, meta = schedules.f16_storage_example('narrow', count=points.size)
+    actual = run_with_data(runner, graph, meta, {'x': points})['result']
+    expected = R.f16_narrow_bits(points)
+    finite = ~np.isnan(points)
+    np.testing.assert_array_equal(actual.view(np.uint16)[finite], expected[finite])
+    assert np.isnan(actual[~finite]).all()
+
+
+def test_unaligned_vector_half_access(runner):
+    for kind in ('copy', 'narrow'):
+        graph, meta = schedules.f16_storage_example(kind, count=512, offset=1)
+        data = np.arange(513, dtype=np.float16 if kind == 'copy' else np.float32)
+        actual = run_with_data(runner, graph, meta, {'x': data})['result']
+        np.testing.assert_array_equal(actual, data[1:].astype(np.float16))
+
+
+def test_f16_kernels_at_every_relative_misalignment(cuda):
+    n = 100_003
+    source32 = R.seeded_normal(3, (n + 16,), np.float32, 100.0)
+    source16 = source32.astype(np.float16)
+    d32, d16 = to_device(cuda, source32), to_device(cuda, source16)
+    for a in (0, 1, 3, 8):
+        for b in (0, 1, 5):
+            out16 = cuda.zeros(n + 16, dtype=cuda.float16, device='cuda:0')
+            out32 = cuda.zeros(n + 16, dtype=cuda.float32, device='cuda:0')
+            ops.f16_narrow(d32[a:a + n], out16[b:b + n])
+            np.testing.assert_array_equal(out16[b:b + n].cpu().numpy().view(np.uint16), R.f16_narrow_bits(source32[a:a + n]))
+            ops.f16_widen(d16[a:a + n], out32[b:b + n])
+            np.testing.assert_array_equal(out32[b:b + n].cpu().numpy(), source16[a:a + n].astype(np.float32))
+            ops.f16_copy(d16[a:a + n], out16[b:b + n])
+            np.testing.assert_array_equal(out16[b:b + n].cpu().numpy().view(np.uint16), source16[a:a + n].view(np.uint16))
+            assert float(out16[b + n:].abs().sum()) == 0.0 and float(out16[:b].abs().sum()) == 0.0  # no overrun
+
+
+def test_elementwise_operators_and_empty_input(cuda):
+    x, y = R.seeded_normal(1, (70_001,)), R.seeded_normal(2, (70_001,))
+    dx, dy = to_device(cuda, x), to_device(cuda, y)
+    exact = {'add': x + y, 'subtract': x - y, 'multiply': x * y, 'maximum': np.fmax(x, y), 'minimum': np.fmin(x, y)}
+    for op, expected in exact.items():
+        np.testing.assert_array_equal(ops.elementwise(op, dx, dy).cpu().numpy(), expected, err_msg=op)
+    np.testing.assert_array_equal(ops.elementwise('relu', dx).cpu().numpy(), np.maximum(x, 0))
+    np.testing.assert_array_equal(ops.elementwise('negative', dx).cpu().numpy(), -x)
+    np.testing.assert_array_equal(ops.elementwise('absolute', dx).cpu().numpy(), np.abs(x))
+    np.testing.assert_array_equal(ops.elementwise('copy', dx).cpu().numpy(), x)
+    np.testing.assert_allclose(ops.elementwise('exp', dx).cpu().numpy(), np.exp(x.astype(np.float64)), rtol=2e-6)
+    np.testing.assert_allclose(ops.elementwise('divide', dx, dy).cpu().numpy(), x.astype(np.float64) / y, rtol=1e-6)
+    np.testing.assert_allclose(ops.elementwise('reciprocal', dy).cpu().numpy(), 1 / y.astype(np.float64), rtol=1e-6)
+    np.testing.assert_allclose(ops.elementwise('sqrt', ops.elementwise('absolute', dx)).cpu().numpy(), np.sqrt(np.abs(x.astype(np.float64))), rtol=1e-6)
+    empty = cuda.empty(0, device='cuda:0')
+    assert ops.add(empty, empty).numel() == 0
+    with pytest.raises(ValueError):
+        ops.add(dx, dy[:-1])
+    with pytest.raises(NotImplementedError):
+        ops.elementwise('tanh', dx)
+
+
+def test_vector_add_full_size_is_exact(cuda):
+    n = 1 << 28
+    generator = cuda.Generator(device='cuda:0').manual_seed(21)
+    x = cuda.randn(n, device='cuda:0', generator=generator)
+    y = cuda.randn(n, device='cuda:0', generator=generator)
+    out = ops.add(x, y)
+    reference = x + y   # torch's own IEEE add: the same single rounding
+    assert bool(cuda.equal(out, reference))
+    # a checksum of checksums independent of torch's add: float64 sums of slices agree to rounding
+    assert abs(float(out.double().sum()) - float(x.double().sum() + y.double().sum())) < 1e-2 * math.sqrt(n)
+
+
+# ------------------------------------------------------------------------------------------------
+# row reductions
+# ------------------------------------------------------------------------------------------------
+
+
+@pytest.mark.parametrize('rows,cols', [(64, 512), (300, 4096), (77, 1001), (5, 65539), (1, 65536), (3, 1), (9, 33)])
+def test_row_reductions_against_float64(cuda, rows, cols):
+    x = R.seeded_normal(7, (rows, cols))
+    dx = to_device(cuda, x)
+    bound = R.row_sum_error_bound(x) + 1e-30
+    assert np.all(np.abs(ops.row_reduce('sum', dx).cpu().numpy() - R.row_sum_f64(x)) <= bound)
+    assert np.all(np.abs(ops.row_reduce('sumsq', dx).cpu().numpy() - R.row_sumsq_f64(x)) <= R.row_sum_error_bound(x * x) * 2 + 1e-30)
+    np.testing.assert_array_equal(ops.row_reduce('max', dx).cpu().numpy(), R.row_max(x))
+
+
+def test_row_reduction_edge_cases(cuda, runner):
+    x = R.seeded_normal(7, (4, 1000))
+    x[1, 17] = np.nan
+    x[2, :] = np.nan
+    x[3, 5] = np.inf
+    got = ops.row_reduce('max', to_device(cuda, x)).cpu().numpy()
+    np.testing.assert_array_equal(got, R.row_max(x))          # NaN-suppressing, all-NaN row -> -inf
+    wide = to_device(cuda, R.seeded_normal(1, (16, 4100)))
+    view = wide[:, 4:4 + 4000]                                  # strided rows, 16-byte aligned origin
+    np.testing.assert_array_equal(ops.row_reduce('max', view).cpu().numpy(), view.cpu().numpy().max(axis=1))
+    view = wide[:, 1:1 + 4000]                                  # unaligned origin: scalar path
+    np.testing.assert_array_equal(ops.row_reduce('max', view).cpu().numpy(), view.cpu().numpy().max(axis=1))
+    assert ops.row_reduce('sum', cuda.empty((0, 8), device='cuda:0')).numel() == 0
+    zero_cols = ops.row_reduce('max', cuda.empty((3, 0), device='cuda:0')).cpu().numpy()
+    assert np.all(zero_cols == -np.inf)
+    # through the compile/launch surface, in the reference's row-sum launch shape
+    for op, oracle in (('sum', R.row_sum_f64), ('max', R.row_max)):
+        graph, meta = schedules.row_reduce_example(64, 512, op)
+        produced = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta), warmup=0, iters=1, samples=1)['outputs']['out']
+        np.testing.assert_allclose(produced, oracle(R.seeded_normal(7, (64, 512))), rtol=1e-5, atol=1e-4)
+
+
+def test_row_reductions_full_size(cuda):
+    rows, cols = 65536, 4096
+    generator = cuda.Generator(device='cuda:0').manual_seed(7)
+    x = cuda.randn((rows, cols), device='cuda:0', generator=generator)
+    sums, maxima = ops.row_reduce('sum', x), ops.row_reduce('max', x)
+    assert bool(cuda.equal(maxima, x.max(dim=1).values))
+    exact = x.double().sum(dim=1)
+    bound = (cols - 1) * np.finfo(np.float32).eps * x.double().abs().sum(dim=1)
+    assert bool(((sums.double() - exact).abs() <= bound).all())
+    # sum of the row sums equals the sum of everything (float64, order-free up to rounding)
+    assert abs(float(sums.double().sum()) - float(exact.sum())) < 1.0
+
+
+# ------------------------------------------------------------------------------------------------
+# GEMM
+# ------------------------------------------------------------------------------------------------
+
+
+def test_tensor_matmul_example_all_modes(runner, golden, published):
+    graph, meta = schedules.matmul_example()
+    expected = np.load(golden / 'tensor_matmul_expected.npz')['result']
+    names = {'bf16x3': 'tensor_bf16x3', 'tf32x3': 'tensor_tf32x3', 'f32': 'tensor_f32'}
+    for mode, record in names.items():
+        compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3, options=Options(contraction_precision=mode))
+        produced = runner.run_kernel(meta['kernels'][0], compiled, warmup=1, iters=2, samples=1)['outputs']['result']
+        np.testing.assert_allclose(produced, expected, rtol=meta['rtol'], atol=meta['atol'])
+        error = float(np.max(np.abs(produced.astype(np.float64) - expected)))
+        assert error <= 2 * published['results'][record]['max_absolute_errors']['result'], (mode, error)
+    # the FP32 mode accumulates k in the reference's order: identical bits to its published GPU output
+    assert sha(produced) == published['results']['tensor_f32']['output_sha256']['result']
+
+
+def test_reference_committed_ir_runs_unchanged(runner, golden, published):
+    import json
+    graph = json.loads((golden / 'tensor_matmul.ir.json').read_text())
+    meta = published['meta']['tensor_matmul']
+    compiled = compile_kernel(graph, meta, arch='sm_100a')
+    produced = runner.run_kernel(meta['kernels'][0], compiled, warmup=0, iters=1, samples=1)['outputs']['result']
+    np.testing.assert_allclose(produced, np.load(golden / 'tensor_matmul_expected.npz')['result'], rtol=1e-3, atol=1e-3)
+
+
+SHAPES = [(128, 128, 128), (256, 256, 64), (384, 768, 1000), (200, 136, 77), (16, 512, 512), (1, 1, 1), (129, 257, 65),
+          (1024, 1024, 1024)]
+
+
+@pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
+@pytest.mark.parametrize('variant', [1, 2, 3])
+def test_compensated_gemm_shapes_and_variants(cuda, mode, variant):
+    ops.set_gemm_variant(variant)
+    try:
+        for m, n, k in SHAPES:
+            a, b = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+            produced = ops.gemm(to_device(cuda, a), to_device(cuda, b), mode)
+            ops.check_device_status()
+            exact = R.gemm_f64(a, b)
+            floor = R.max_relative_error(R.gemm_x3_exact_products(a, b, mode), exact)
+            # FP32 accumulation of 3 * k / (k-step) partial sums in the tensor core, the same count the
+            # reference's mma.sync loop performs: allow one truncated unit in the last place per accumulation
+            steps = 3 * math.ceil(k / (16 if mode == 'bf16x3' else 8))
+            allowance = steps * 2.0 ** -24
+            error = R.max_relative_error(produced.cpu().numpy(), exact)
+            assert error <= 2 * floor + allowance, (m, n, k, error, floor, allowance)
+    finally:
+        ops.set_gemm_variant(0)
+
+
+def test_gemm_f32_mode_shapes(cuda):
+    for m, n, k in SHAPES[:-1]:
+        a, b = R.seeded_normal(7, (m, k)), R.seeded_normal(11, (k, n))
+        produced = ops.gemm(to_device(cuda, a), to_device(cuda, b), 'f32').cpu().numpy()
+        if m * n * k <= 128 ** 3:
+            np.testing.assert_array_equal(produced, R.gemm_f32_fma(a, b))  # sequential FMA over k: bit-exact
+        assert R.max_relative_error(produced, R.gemm_f64(a, b)) < 2e-6
+
+
+def test_gemm_edge_cases_and_errors(cuda):
+    a, b = to_device(cuda, R.seeded_uniform(1, (64, 32))), to_device(cuda, R.seeded_uniform(2, (32, 48)))
+    assert ops.gemm(a[:0], b, 'bf16x3').shape == (0, 48)
+    assert ops.gemm(a, b[:, :0], 'bf16x3').shape == (64, 0)
+    zero_k = ops.gemm(a[:, :0], b[:0], 'bf16x3')
+    assert float(zero_k.abs().sum()) == 0.0
+    with pytest.raises(ValueError):
+        ops.gemm(a, b[:16], 'bf16x3')
+    with pytest.raises(ValueError):
+        ops.gemm(a, b, 'fp8')
+    too_small = cuda.empty(2048, dtype=cuda.uint8, device='cuda:0')
+    with pytest.raises(ValueError, match='workspace'):
+        ops.gemm(a, b, 'bf16x3', workspace=too_small)
+    # special values propagate like the reference's arithmetic (inf stays inf, NaN poisons its row/column)
+    special = R.seeded_uniform(3, (128, 64))
+    special[5, 7] = np.inf
+    special[9, 3] = np.nan
+    other = np.abs(R.seeded_uniform(4, (64, 128))) + 0.5
+    produced = ops.gemm(to_device(cuda, special), to_device(cuda, other), 'bf16x3').cpu().numpy()
+    assert np.isnan(produced[9]).all() and np.isnan(produced[5]).all()   # inf - inf residual is NaN, as in the reference's split
+    assert np.isfinite(produced[[0, 1, 2, 3, 4, 6, 7, 8]]).all()
+
+
+def test_gemm_column_blocks_equal_the_full_product(cuda):
+    # the multi-GPU partition: a column block computed in place (leading dimensions kept) is bit-identical
+    from deuteron_b200 import sharding
+    a, b = to_device(cuda, R.seeded_uniform(7, (512, 768))), to_device(cuda, R.seeded_uniform(11, (768, 1024)))
+    full = ops.gemm(a, b, 'bf16x3').clone()
+    for world in (2, 4):
+        parts = []
+        for rank in range(world):
+            local, (begin, end) = sharding.gemm_column_shard(a, b, rank, world)
+            parts.append(local.clone())
+            assert (begin, end) == sharding.column_blocks(1024, world)[rank]
+        assert bool(cuda.equal(cuda.cat(parts, dim=1), full))
+    into = cuda.zeros((512, 1024), device='cuda:0')
+    ops.gemm(a, b[:, 256:512], 'bf16x3', out=into[:, 256:512])
+    assert bool(cuda.equal(into[:, 256:512], full[:, 256:512])) and float(into[:, :256].abs().sum()) == 0.0
+
+
+@pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
+def test_gemm_8192_properties(cuda, mode):
+    n = 8192
+    generator = cuda.Generator(device='cuda:0').manual_seed(7)
+    a = cuda.rand((n, n), device='cuda:0', generator=generator) * 2 - 1
+    b = cuda.rand((n, n), device='cuda:0', generator=generator) * 2 - 1
+    c = ops.gemm(a, b, mode).clone()
+    ops.check_device_status()
+    rows = cuda.arange(0, n, n // 64, device='cuda:0')
+    exact = a[rows].double() @ b.double()
+    error = float(((c[rows].double() - exact).abs().max() / exact.abs().max()).item())
+    steps = 3 * n // (16 if mode == 'bf16x3' else 8)
+    assert error <= 1e-5 + steps * 2.0 ** -24, error
+    # scaling an operand by a power of two commutes exactly with both splits and with every accumulation
+    scaled = ops.gemm(a * 4.0, b * 0.5, mode)
+    assert bool(cuda.equal(scaled, c * 2.0))
+    # deterministic: a second run gives the same bits
+    assert bool(cuda.equal(ops.gemm(a, b, mode), c))
+    # identity on the right returns the compensated reconstruction hi + lo of A (exact to 2^-16 / 2^-21)
+    eye = cuda.eye(n, device='cuda:0')
+    back = ops.gemm(a[:256], eye, mode)
+    assert float((back - a[:256]).abs().max()) <= (2.0 ** -16 if mode == 'bf16x3' else 2.0 ** -20)
+
+
+# ------------------------------------------------------------------------------------------------
+# attention
+# ------------------------------------------------------------------------------------------------
+
+
+def test_attention_example_error_level(runner, published):
+    graph, meta = schedules.attention_example()
+    compiled = compile_kernel(graph, meta)
+    produced = runner.run_kernel(meta['kernels'][0], compiled, warmup=0, iters=1, samples=1)['outputs']['out']
+    q, kt, v = R.seeded_normal(7, (3, 32)), R.seeded_normal(8, (32, 64)), R.seeded_normal(9, (64, 32))
+    exact = R.attention_f64(q, kt, v)
+    np.testing.assert_allclose(produced, exact, rtol=meta['rtol'], atol=meta['atol'])
+    assert float(np.max(np.abs(produced - exact))) <= 2 * published['results']['attention']['max_absolute_errors']['out']
+
+
+def test_all_key_groups_and_inplace_denominator(runner):
+    # tests/test_attention.py:106-122
+    for keys in range(32, 257, 32):
+        outputs = []
+        rows, depth, seed = 1 + keys // 32, 32 if keys % 64 else 64, keys + 7
+        q, kt, v = R.seeded_normal(seed, (rows, depth)), R.seeded_normal(seed + 1, (depth, keys)), R.seeded_normal(seed + 2, (keys, 32))
+        exact = R.attention_f64(q, kt, v)
+        for alias in (False, True):
+            graph, meta = schedules.attention_example(rows=rows, keys=keys, depth=depth, inplace_denominator=alias, seed=seed)
+            produced = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta), warmup=0, iters=1, samples=1)['outputs']['out']
+            np.testing.assert_allclose(produced, exact, rtol=1e-3, atol=1e-4)
+            outputs.append(produced)
+        np.testing.assert_array_equal(outputs[0], outputs[1])
+
+
+def test_attention_beyond_one_stage_and_wide_values(cuda):
+    for rows, keys, depth, cols in ((5, 600, 48, 40), (2, 1000, 128, 128), (1, 1, 8, 3), (7, 257, 16, 256)):
+        q, kt, v = R.seeded_normal(7, (rows, depth)), R.seeded_normal(8, (depth, keys)), R.seeded_normal(9, (keys, cols))
+        scale = float(np.float32(1 / math.sqrt(depth)))
+        produced = ops.attention(to_device(cuda, q), to_device(cuda, kt), to_device(cuda, v), scale).cpu().numpy()
+        np.testing.assert_allclose(produced, R.attention_f64(q, kt, v), rtol=1e-3, atol=1e-4)
+    with pytest.raises(NotImplementedError):
+        ops.attention(to_device(cuda, q), to_device(cuda, kt), to_device(cuda, np.zeros((257, 300), np.float32)), 1.0)
+
+
+GQA_CASES = [(1, 4, 2, 128, 128), (2, 4, 2, 300, 128), (1, 8, 8, 512, 128), (1, 2, 1, 64, 64), (1, 4, 1, 1000, 128)]
+
+
+@pytest.mark.parametrize('variant', [0, 1])
+@pytest.mark.parametrize('storage', [np.float16, np.float32])
+def test_gqa_attention_against_float64(cuda, storage, variant):
+    ops.set_gqa_variant(variant)
+    try:
+        for batch, hq, hkv, s, d in GQA_CASES:
+            scale = float(np.float32(1 / math.sqrt(d)))
+            q = R.seeded_normal(7, (batch, hq, s, d), storage, scale)
+            k = R.seeded_normal(8, (batch, hkv, s, d), storage, scale)
+            v = R.seeded_normal(9, (batch, hkv, s, d), storage, scale)
+            produced = ops.gqa_attention(to_device(cuda, q), to_device(cuda, k), to_device(cuda, v), scale).cpu().numpy()
+            ops.check_device_status()
+            exact = R.gqa_attention_f64(q, k, v, scale)
+            np.testing.assert_allclose(produced, exact, rtol=1e-3, atol=1e-4)
+            assert R.max_relative_error(produced, exact) <= 4e-6, (batch, hq, hkv, s, d)
+    finally:
+        ops.set_gqa_variant(0)
+
+
+def test_gqa_group_ranges_partition_the_output(cuda):
+    from deuteron_b200 import sharding
+    batch, hq, hkv, s, d = 2, 8, 2, 256, 128
+    scale = float(np.float32(1 / math.sqrt(d)))
+    q = to_device(cuda, R.seeded_normal(7, (batch, hq, s, d), np.float16, scale))
+    k = to_device(cuda, R.seeded_normal(8, (batch, hkv, s, d), np.float16, scale))
+    v = to_device(cuda, R.seeded_normal(9, (batch, hkv, s, d), np.float16, scale))
+    full = ops.gqa_attention(q, k, v, scale).clone()
+    for world in (2, 4):
+        assembled = cuda.full_like(full, float('nan'))
+        for rank in range(world):
+            sharding.gqa_group_shard(q, k, v, scale, rank, world, out=assembled)
+        assert bool(cuda.equal(assembled, full))
+    assert ops.gqa_attention(q, k, v, scale, groups=(1, 1)) is not None
+    with pytest.raises(ValueError):
+        ops.gqa_attention(q, k, v, scale, groups=(0, 5))
+    with pytest.raises(ValueError):
+        ops.gqa_attention(q, k[:, :1].repeat(1, 3, 1, 1), v[:, :1].repeat(1, 3, 1, 1), scale)
+
+
+def test_gqa_full_size_properties(cuda):
+    # batch 4, 32 query / 8 kv heads, head_dim 128, 4096 keys: sampled rows against float64, plus softmax identities
+    batch, hq, hkv, s, d = 4, 32, 8, 4096, 128
+    scale = float(np.float32(1 / math.sqrt(d)))
+    generator = cuda.Generator(device='cuda:0').manual_seed(7)
+    q = (cuda.randn((batch, hq, s, d), device='cuda:0', generator=generator) * scale).half()
+    k = (cuda.randn((batch, hkv, s, d), device='cuda:0', generator=generator) * scale).half()
+    v = (cuda.randn((batch, hkv, s, d), device='cuda:0', generator=generator) * scale).half()
+    out = ops.gqa_attention(q, k, v, scale)
+    ops.check_device_status()
+    rows = [0, 1, 777, 2048, 4095]
+    for b, h in ((0, 0), (1, 13), (3, 31)):
+        exact = R.attention_f64(q[b, h, rows].cpu().numpy(), k[b, h // 4].cpu().numpy().astype(np.float64).T, v[b, h // 4].cpu().numpy(), scale)
+        produced = out[b, h, rows].cpu().numpy()
+        np.testing.assert_allclose(produced, exact, rtol=1e-3, atol=1e-4)
+        assert R.max_relative_error(produced, exact) <= 4e-6
+    # rows of the softmax sum to one: constant values come back unchanged
+    ones = ops.gqa_attention(q, k, cuda.ones_like(v), scale)
+    assert float((ones - 1).abs().max()) <= 2e-6
+    # outputs are convex combinations of the values
+    assert float(out.max()) <= float(v.float().max()) + 1e-6 and float(out.min()) >= float(v.float().min()) - 1e-6
+
+
+def test_native_errors_are_python_exceptions(cuda):
+    with pytest.raises(ValueError):
+        native.call('dtn_row_reduce_f32', 9, 1, 1, 1, 1, 1, None)
+    with pytest.raises(ValueError):
+        ops.row_reduce('sum', cuda.zeros(4, device='cuda:0'))
+    with pytest.raises(ValueError):
+        ops.add(cuda.zeros(4), cuda.zeros(4))
+    assert native.device_status(0) == 0

@@ -1,0 +1,88 @@
+"""Multi-GPU partition logic on CPU: world_size-2 gloo ranks, the oracle standing in for the kernels.
+
+The data path has no collective; what is tested is that the column-block / group partition covers the
+output exactly once and that the optional all-gather reassembles it, with the same functions
+(sharding.*) the GPU path uses.
+"""
+import multiprocessing as mp
+import os
+
+import numpy as np
+import pytest
+
+from deuteron_b200 import sharding
+from oracle import reference_math as R
+
+
+def test_column_blocks_cover_exactly_once():
+    for n, world in ((8192, 1), (8192, 2), (8192, 8), (1000, 4), (256, 8), (0, 3), (777, 2)):
+        blocks = sharding.column_blocks(n, world)
+        assert len(blocks) == world and blocks[0][0] == 0 and blocks[-1][1] == n
+        assert all(blocks[i][1] == blocks[i + 1][0] for i in range(world - 1))
+        assert all(begin % 256 == 0 for begin, end in blocks if begin < n)
+    assert sharding.column_blocks(8192, 8) == [(1024 * r, 1024 * (r + 1)) for r in range(8)]
+    with pytest.raises(ValueError):
+        sharding.column_blocks(10, 0)
+
+
+def test_group_ranges_cover_exactly_once():
+    for groups, world in ((32, 1), (32, 2), (32, 8), (5, 4), (0, 2)):
+        ranges = [sharding.group_range(groups, world, r) for r in range(world)]
+        assert ranges[0][0] == 0 and ranges[-1][1] == groups
+        assert all(ranges[i][1] == ranges[i + 1][0] for i in range(world - 1))
+    with pytest.raises(ValueError):
+        sharding.group_range(4, 2, 2)
+
+
+def _worker(rank: int, world: int, port: int, queue) -> None:
+    import torch
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR='127.0.0.1', MASTER_PORT=str(port))
+    dist.init_process_group('gloo', rank=rank, world_size=world)
+    try:
+        a = torch.from_numpy(R.seeded_uniform(7, (64, 96)))
+        b = torch.from_numpy(R.seeded_uniform(11, (96, 512)))
+
+        def cpu_gemm(left, right, mode, out):
+            return torch.from_numpy(R.gemm_f64(left.numpy(), right.numpy()).astype(np.float32))
+
+        local, (begin, end) = sharding.gemm_column_shard(a, b, rank, world, gemm=cpu_gemm)
+        full = sharding.all_gather_columns(local, sharding.column_blocks(512, world))
+        expected = R.gemm_f64(a.numpy(), b.numpy()).astype(np.float32)
+        gemm_ok = bool(np.array_equal(full.numpy(), expected)) and (begin, end) == (256 * rank, 256 * (rank + 1))
+
+        q = torch.from_numpy(R.seeded_normal(1, (2, 4, 16, 8)))
+        k = torch.from_numpy(R.seeded_normal(2, (2, 2, 16, 8)))
+        v = torch.from_numpy(R.seeded_normal(3, (2, 2, 16, 8)))
+
+        def cpu_attention(q, k, v, scale, out=None, groups=None):
+            out = torch.zeros(q.shape, dtype=torch.float32) if out is None else out
+            ratio = q.shape[1] // k.shape[1]
+            heads = [(g // k.shape[1], (g % k.shape[1]) * ratio + j) for g in range(*groups) for j in range(ratio)]
+            result = R.gqa_attention_f64(q.numpy(), k.numpy(), v.numpy(), scale, heads=heads)
+            for bi, hi in heads:
+                out[bi, hi] = torch.from_numpy(result[bi, hi].astype(np.float32))
+            return out
+
+        mine, owned = sharding.gqa_group_shard(q, k, v, 0.35, rank, world, attention=cpu_attention)
+        ranges = [sharding.group_range(4, world, r) for r in range(world)]
+        gathered = sharding.all_gather_groups(mine, 2, ranges)
+        expected = R.gqa_attention_f64(q.numpy(), k.numpy(), v.numpy(), 0.35).astype(np.float32)
+        attention_ok = bool(np.array_equal(gathered.numpy(), expected)) and owned == ranges[rank]
+        queue.put((rank, gemm_ok, attention_ok))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_gloo_ranks_assemble_sharded_outputs():
+    context = mp.get_context('spawn')
+    queue = context.Queue()
+    port = 29500 + os.getpid() % 400
+    workers = [context.Process(target=_worker, args=(rank, 2, port, queue)) for rank in range(2)]
+    for worker in workers:
+        worker.start()
+    results = sorted(queue.get(timeout=120) for _ in workers)
+    for worker in workers:
+        worker.join(timeout=60)
+        assert worker.exitcode == 0
+    assert results == [(0, True, True), (1, True, True)]
