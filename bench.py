@@ -62,7 +62,7 @@ class ClockSampler:
     def start(self) -> None:
         try:
             self.process = subprocess.Popen(['nvidia-smi', f'--id={self.index}', f'--query-gpu={self.QUERY}',
-                                             '--format=csv,noheader,nounits', '-lms', '100'], stdout=subprocess.PIPE,
+                                             '--format=csv,noheader,nounits', '-lms', '50'], stdout=subprocess.PIPE,
                                             stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.process = None
@@ -347,10 +347,55 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max')
+
+
+def run_profile_case(name: str, launches: int) -> None:
+    """A small, self-ending case of one kernel for a profiler capture: inputs larger than the L2 where
+    the kernel is memory-bound, well under a GB on the device, `launches` launches, then exit."""
+    import torch
+    from deuteron_b200 import ops
+    torch.cuda.set_device(0)
+    device = torch.device('cuda', 0)
+    generator = torch.Generator(device=device).manual_seed(7)
+    if name.startswith('gemm_'):
+        n = 4096
+        a = torch.rand((n, n), device=device, generator=generator) * 2 - 1
+        b = torch.rand((n, n), device=device, generator=generator) * 2 - 1
+        c = torch.empty((n, n), device=device)
+        call = lambda: ops.gemm(a, b, name[5:], out=c)
+    elif name == 'attention':
+        batch, hq, hkv, s, d = 1, 16, 4, 4096, 128
+        q = (torch.randn((batch, hq, s, d), device=device, generator=generator) / d ** 0.5).half()
+        k = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
+        v = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
+        o = torch.empty((batch, hq, s, d), device=device)
+        call = lambda: ops.gqa_attention(q, k, v, d ** -0.5, out=o)
+    else:
+        n = 1 << 26
+        x = torch.randn(n, device=device, generator=generator)
+        y = torch.randn(n, device=device, generator=generator)
+        z = torch.empty_like(x)
+        half = torch.empty(n, dtype=torch.float16, device=device)
+        half2 = torch.empty_like(half)
+        rows = torch.empty(16384, device=device)
+        call = {'add': lambda: ops.add(x, y, z), 'f16_narrow': lambda: ops.f16_narrow(x, half),
+                'f16_widen': lambda: ops.f16_widen(half, z), 'f16_copy': lambda: ops.f16_copy(half, half2),
+                'row_sum': lambda: ops.row_reduce('sum', x.view(16384, 4096), rows),
+                'row_max': lambda: ops.row_reduce('max', x.view(16384, 4096), rows)}[name]
+    for _ in range(launches):
+        call()
+    torch.cuda.synchronize()
+    ops.check_device_status()
+    print(json.dumps({'profile_case': name, 'launches': launches}))
+
+
 def main() -> None:
     parser = argparse.ArgumentParser()
+    parser.add_argument('--profile-case', choices=PROFILE_CASES, help='run a small case of one kernel and exit')
+    parser.add_argument('--launches', type=int, default=3)
     parser.add_argument('--gpus', type=int, default=1)
-    parser.add_argument('--steps', type=int, default=20)
+    parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=3)
     parser.add_argument('--impl', choices=('ours', 'reference'), default='ours')
     parser.add_argument('--no-cpu-baseline', action='store_true')
@@ -358,6 +403,9 @@ def main() -> None:
     args = parser.parse_args()
     if args.steps < 1 or args.warmup < 0:
         raise SystemExit('steps must be positive and warmup nonnegative')
+    if args.profile_case:
+        run_profile_case(args.profile_case, max(args.launches, 1))
+        return
     if args.impl == 'reference':
         run_reference(args)
         return

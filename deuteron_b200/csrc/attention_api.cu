@@ -5,8 +5,8 @@ namespace dtn {
 
 int gqa_f32_launch(const void* q, const void* k, const void* v, float* out, int64_t Hq, int64_t Hkv, int64_t S,
                    int64_t D, float scale, int storage, int64_t gb, int64_t ge, cudaStream_t s);
-int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t Hq, int64_t Hkv, int64_t S,
-                  float scale, int64_t gb, int64_t ge, cudaStream_t s);
+int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
+                  int64_t S, float scale, int64_t gb, int64_t ge, cudaStream_t s);
 bool gqa_tc_supported(int64_t S, int64_t D, int storage);
 
 static int g_gqa_variant = 0;
@@ -43,8 +43,8 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 2 : 1;
   if (variant == 2) {
     DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
-                "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 128");
-    return gqa_tc_launch(q, k, v, out, Hq, Hkv, S, scale, group_begin, group_end, s);
+                "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");
+    return gqa_tc_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, s);
   }
   return gqa_f32_launch(q, k, v, out, Hq, Hkv, S, D, scale, storage, group_begin, group_end, s);
 }

@@ -524,9 +524,11 @@ static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C
   const void* b_hi = ws + 2 * L.a_plane;
   const void* b_lo = ws + 2 * L.a_plane + L.b_plane;
   if (variant == 0) {
-    // Small problems: more, smaller tiles keep more SMs busy; large ones: the widest tile.
-    const int64_t tiles256 = ((M + 127) / 128) * ((N + 255) / 256);
-    variant = (tiles256 >= sm_count()) ? 2 : 1;
+    // Large problems: a CTA pair per 256x256 tile (least shared-memory traffic per flop); smaller
+    // ones: more, smaller tiles keep more SMs busy.
+    const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t wide_tiles = ((M + 127) / 128) * ((N + 255) / 256);
+    variant = (pair_tiles >= sm_count() / 2) ? 3 : (wide_tiles >= sm_count()) ? 2 : 1;
   }
   switch (variant) {
     case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
