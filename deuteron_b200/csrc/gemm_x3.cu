@@ -433,7 +433,8 @@ static PlaneLayout plane_layout(int mode, int64_t M, int64_t N, int64_t K) {
 
 template <int KIND, int CTAS, int BN>
 static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const void* b_lo, float* C,
-                     int64_t M, int64_t N, int64_t K, int64_t Kp, int64_t ldc, cudaStream_t s) {
+                     int64_t M, int64_t N, int64_t K, int64_t Kp, int64_t ldc, cudaStream_t s,
+                     int* status_word = nullptr) {
   using Cfg = GemmCfg<CTAS, BN>;
   constexpr int eb = (KIND == 0) ? 2 : 4;
   CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
@@ -453,7 +454,7 @@ static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const
     attr_dev = dev;
   }
 
-  int* status = device_status_word();
+  int* status = status_word ? status_word : device_status_word();
   DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "gemm: could not allocate the device status word");
   const int bm = 128 * CTAS;
   const int tiles_m = (int)((M + bm - 1) / bm), tiles_n = (int)((N + BN - 1) / BN);
@@ -518,7 +519,7 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
 
 template <int KIND>
 static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C, int64_t M, int64_t N, int64_t K,
-                  int64_t ldc, cudaStream_t s) {
+                  int64_t ldc, cudaStream_t s, int* status_word = nullptr) {
   const void* a_hi = ws;
   const void* a_lo = ws + L.a_plane;
   const void* b_hi = ws + 2 * L.a_plane;
@@ -531,18 +532,90 @@ static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C
     variant = (pair_tiles >= sm_count() / 2) ? 3 : (wide_tiles >= sm_count()) ? 2 : 1;
   }
   switch (variant) {
-    case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
-    case 2: return launch_tc<KIND, 1, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
-    case 3: return launch_tc<KIND, 2, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s);
+    case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
+    case 2: return launch_tc<KIND, 1, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
+    case 3: return launch_tc<KIND, 2, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
     default:
       set_error("gemm: unknown variant %d", variant);
       return DTN_ERR_INVALID;
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Allocation-free variant: the operand planes live in a fixed array inside the library image.
+// ---------------------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = (size_t)32 << 20;   // largest set of operand planes the array can hold
+// The planes must start on a 1024-byte boundary; the array is 256-byte aligned, so it carries
+// 1024 bytes of slack and the usable part starts at the first 1024-byte boundary inside it.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes + 1024];
+static __device__ int g_static_status;   // where this variant's kernels report a wait that ran out
+
+struct StaticScratch {
+  uint8_t* planes = nullptr;   // device address of the usable, 1024-byte aligned part
+  int* status = nullptr;
+};
+static std::mutex g_static_mutex;
+static StaticScratch g_static_by_device[64];
+
+// Device addresses of the two symbols on the current device, resolved once per device. In host code
+// the symbols' names are host-side stand-ins, never device addresses: only cudaGetSymbolAddress,
+// called with the device current, yields a pointer a kernel may use.
+static int static_scratch_for_current_device(StaticScratch* out) {
+  int dev = 0;
+  DTN_CUDA_CHECK(cudaGetDevice(&dev));
+  DTN_REQUIRE(dev >= 0 && dev < 64, DTN_ERR_UNSUPPORTED, "gemm: device ordinal %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticScratch& entry = g_static_by_device[dev];
+  if (entry.planes == nullptr) {
+    void* scratch = nullptr;
+    void* status = nullptr;
+    DTN_CUDA_CHECK(cudaGetSymbolAddress(&scratch, g_static_scratch));
+    DTN_CUDA_CHECK(cudaGetSymbolAddress(&status, g_static_status));
+    const uintptr_t aligned = (reinterpret_cast<uintptr_t>(scratch) + 1023) & ~(uintptr_t)1023;
+    entry.status = static_cast<int*>(status);
+    entry.planes = reinterpret_cast<uint8_t*>(aligned);
+  }
+  *out = entry;
+  return DTN_OK;
+}
+
 }  // namespace dtn
 
 extern "C" {
+
+int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
+                       int64_t lda, int64_t ldb, int64_t ldc, void* stream) {
+  using namespace dtn;
+  DTN_REQUIRE(mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
+              "gemm (static scratch): mode must be DTN_GEMM_BF16X3 or DTN_GEMM_TF32X3, got %d", mode);
+  DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm (static scratch): negative extent");
+  if (M == 0 || N == 0) return DTN_OK;
+  DTN_REQUIRE(K > 0, DTN_ERR_INVALID, "gemm (static scratch): K must be positive");
+  DTN_REQUIRE(A != nullptr && B != nullptr && C != nullptr, DTN_ERR_INVALID, "gemm (static scratch): null pointer");
+  DTN_REQUIRE(lda >= K && ldb >= N && ldc >= N, DTN_ERR_INVALID,
+              "gemm (static scratch): leading dimension smaller than the row");
+  DTN_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), DTN_ERR_UNSUPPORTED,
+              "gemm (static scratch): extents must fit 31 bits");
+  DTN_REQUIRE(aligned_to(A, 4) && aligned_to(B, 4) && aligned_to(C, 4), DTN_ERR_INVALID,
+              "gemm (static scratch): pointers must be 4-byte aligned");
+  const PlaneLayout L = plane_layout(mode, M, N, K);
+  DTN_REQUIRE(L.total <= kStaticScratchBytes, DTN_ERR_WORKSPACE,
+              "gemm (static scratch): %lld x %lld x %lld needs %zu bytes of operand planes, the built-in array holds %zu; "
+              "use dtn_gemm_x3 with a caller-owned workspace",
+              (long long)M, (long long)N, (long long)K, L.total, kStaticScratchBytes);
+  StaticScratch scratch;
+  int rc;
+  if ((rc = static_scratch_for_current_device(&scratch))) return rc;
+  cudaStream_t s = as_stream(stream);
+  // Nothing in the array has to start at zero: the split kernels overwrite every byte of the planes the
+  // product kernel reads, padding included. The status word is only ever set by a kernel that gave up.
+  if (mode == DTN_GEMM_BF16X3) {
+    if ((rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, scratch.planes, s))) return rc;
+    return run_tc<0>(g_gemm_variant, scratch.planes, L, C, M, N, K, ldc, s, scratch.status);
+  }
+  if ((rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, scratch.planes, s))) return rc;
+  return run_tc<1>(g_gemm_variant, scratch.planes, L, C, M, N, K, ldc, s, scratch.status);
+}
 
 int dtn_gemm_set_variant(int variant) {
   DTN_REQUIRE(variant >= 0 && variant <= 3, DTN_ERR_INVALID, "gemm: variant must be 0..3");

@@ -136,6 +136,28 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
                       size_t workspace_bytes, int phase, void* stream);
 
+/* The compensated GEMM for callers that must not allocate device memory. It has no counterpart in
+ * the reference; it exists for hosts that cannot give dtn_gemm_x3 a workspace: programs that
+ * handed all device memory to their own pool at start-up and forbid cudaMalloc afterwards (an
+ * inference server's arena, a plugin sandbox), and latency-critical loops that cannot afford the
+ * device-wide synchronisation a cudaMalloc or cudaFree implies. Same arithmetic, same kernels
+ * and the same results as dtn_gemm_x3(mode, ...) for DTN_GEMM_BF16X3 and DTN_GEMM_TF32X3, but the
+ * operand planes go to a fixed 32 MiB array that is part of the library image (every GPU that
+ * loads the library holds those 32 MiB until the process exits). This function calls no
+ * cudaMalloc, cudaFree or any other allocating routine.
+ *   - Limit: the planes of (mode, M, N, K) — dtn_gemm_workspace_bytes tells how many bytes — must
+ *     fit 32 MiB (bf16x3: 2048^3; tf32x3: about 1448^3). Larger problems are rejected with
+ *     DTN_ERR_WORKSPACE and a message that names both sizes.
+ *   - The first call on a device looks up the array's device address (with that device current).
+ *     Make that first call outside any stream capture.
+ *   - All calls on a device share the one array. Calls that can overlap on the GPU (different
+ *     streams, or graphs replayed concurrently) race on it: serialise them. Nothing in the
+ *     array needs clearing between calls; every byte that is read is rewritten first.
+ *   - A bounded wait that runs out inside this variant is recorded in a status word of its own,
+ *     which dtn_device_status does not read. */
+int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
+                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
 /* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile.
  * No reference counterpart. */
