@@ -484,13 +484,13 @@ static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const
 
 template <class KIND>
 static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                     const PlaneLayout& L, uint8_t* ws, cudaStream_t s) {
+                     const PlaneLayout& L, uint8_t* ws, cudaStream_t s, bool do_a = true, bool do_b = true) {
   using E = typename KIND::elem;
   E* a_hi = reinterpret_cast<E*>(ws);
   E* a_lo = reinterpret_cast<E*>(ws + L.a_plane);
   E* b_hi = reinterpret_cast<E*>(ws + 2 * L.a_plane);
   E* b_lo = reinterpret_cast<E*>(ws + 2 * L.a_plane + L.b_plane);
-  {
+  if (do_a) {
     const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
     dim3 grid((unsigned)((L.Kp / 4 + 255) / 256), (unsigned)M);
     DTN_REQUIRE(M <= 65535 * 1024LL, DTN_ERR_UNSUPPORTED, "gemm: M too large");
@@ -503,7 +503,7 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
       DTN_LAUNCH_CHECK("split_rows_kernel");
     }
   }
-  {
+  if (do_b) {
     const int64_t ny = (N + 63) / 64;
     for (int64_t y0 = 0; y0 < ny; y0 += 65535) {
       const int cnt = (int)((ny - y0) < 65535 ? (ny - y0) : 65535);
@@ -637,7 +637,9 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
                       int64_t lda, int64_t ldb, int64_t ldc, void* workspace, size_t workspace_bytes, int phase,
                       void* stream) {
   using namespace dtn;
-  DTN_REQUIRE(phase >= 1 && phase <= 3, DTN_ERR_INVALID, "gemm: phase must be 1 (split), 2 (products) or 3 (both)");
+  DTN_REQUIRE(phase >= 1 && phase <= 15 && (phase & 3) != 0, DTN_ERR_INVALID,
+              "gemm: phase is a mask of 1 (split), 2 (products), 4 (keep A planes), 8 (keep B planes)");
+  const bool split_a = (phase & 1) && !(phase & 4), split_b = (phase & 1) && !(phase & 8);
   DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
               "gemm: unknown mode %d", mode);
   DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm: negative extent");
@@ -663,10 +665,10 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int rc;
   if (mode == DTN_GEMM_BF16X3) {
-    if ((phase & 1) && (rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
+    if ((phase & 1) && (rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s, split_a, split_b))) return rc;
     return (phase & 2) ? run_tc<0>(g_gemm_variant, ws, L, C, M, N, K, ldc, s) : DTN_OK;
   }
-  if ((phase & 1) && (rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s))) return rc;
+  if ((phase & 1) && (rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s, split_a, split_b))) return rc;
   return (phase & 2) ? run_tc<1>(g_gemm_variant, ws, L, C, M, N, K, ldc, s) : DTN_OK;
 }
 

@@ -95,6 +95,8 @@ class LocalRunner:
         self.torch_device = torch.device('cuda', device)
         self.pid, self.thread = os.getpid(), threading.get_ident()
         self.stream = torch.cuda.Stream(device=self.torch_device)
+        self._copy_in = torch.cuda.Stream(device=self.torch_device)
+        self._copy_out = torch.cuda.Stream(device=self.torch_device)
         properties = torch.cuda.get_device_properties(device)
         self.device_info = {'name': properties.name, 'arch': f'sm_{properties.major}{properties.minor}',
                             'multiprocessors': properties.multi_processor_count}
@@ -204,9 +206,22 @@ class LocalRunner:
             for name, arg in by_name.items():
                 if arg.get('output'):
                     continue
-                host = np.ascontiguousarray(arrays[name])
+                host = arrays[name]
                 if host.dtype != np.dtype(DTYPES[arg['dtype']]) or list(host.shape) != list(arg['shape']):
                     raise ValueError(f'buffer {name} must have shape {arg["shape"]} and dtype {arg["dtype"]}')
+            blocks = self._gemm_row_blocks(plan) if plan.kind == 'gemm' and not launch.get('zero_outputs') else 1
+            if blocks > 1:
+                out_name = plan.buffers['out'][0]
+                out_arg = by_name[out_name]
+                host_out = outputs[out_name] if outputs is not None and out_name in outputs else np.empty(out_arg['shape'], dtype=np.float32)
+                self._execute_gemm_blocks(plan, tensors, pointers, workspace, arrays, host_out, blocks)
+                if synchronize:
+                    self.stream.synchronize()
+                return {out_name: host_out}
+            for name, arg in by_name.items():
+                if arg.get('output'):
+                    continue
+                host = np.ascontiguousarray(arrays[name])
                 if host.nbytes:
                     tensors[name][:host.nbytes].copy_(torch.from_numpy(host.reshape(-1).view(np.uint8)), non_blocking=True)
             for name in launch.get('zero_outputs', []):
@@ -223,6 +238,61 @@ class LocalRunner:
             if synchronize:
                 self.stream.synchronize()
         return results
+
+    def _gemm_row_blocks(self, plan: Any) -> int:
+        """Number of equal row blocks a large compensated GEMM is walked in when its operands come from
+        the host, so that copies and products overlap; 1 = no blocking."""
+        m, n, k = plan.params['m'], plan.params['n'], plan.params['k']
+        if plan.params['mode'] == 'f32' or m * k * 4 < (32 << 20):
+            return 1
+        for blocks in (8, 4, 2):
+            if m % blocks == 0 and (m // blocks) % 256 == 0 and (m // blocks) >= 512:
+                return blocks
+        return 1
+
+    def _execute_gemm_blocks(self, plan: Any, tensors: dict, pointers: dict, workspace: Any, arrays: dict, host_out: np.ndarray,
+                             blocks: int) -> None:
+        """Host-fed compensated GEMM as a three-stream pipeline over row blocks of A and C.
+
+        B goes to the device first and is split once; then, block by block, A_i is copied in on the
+        copy-in stream while A_(i-1) is split and multiplied on the compute stream and C_(i-2) returns to
+        the host on the copy-out stream. All copies are contiguous. Per-element arithmetic (and so every
+        bit of the result) is the same as in the one-launch path.
+        """
+        torch = self._torch
+        m, n, k = plan.params['m'], plan.params['n'], plan.params['k']
+        mode = native.GEMM_MODES[plan.params['mode']]
+        rows = m // blocks
+        left_name, right_name, out_name = plan.buffers['left'][0], plan.buffers['right'][0], plan.buffers['out'][0]
+        compute, copy_in, copy_out = self.stream, self._copy_in, self._copy_out
+        copy_in.wait_stream(compute)       # earlier launches may still read the operand buffers
+        left_host = torch.from_numpy(np.ascontiguousarray(arrays[left_name]).reshape(-1).view(np.uint8))
+        right_host = torch.from_numpy(np.ascontiguousarray(arrays[right_name]).reshape(-1).view(np.uint8))
+        out_host = torch.from_numpy(host_out.reshape(-1).view(np.uint8))
+        block_in, block_out = rows * k * 4, rows * n * 4
+        ready = []
+        with torch.cuda.stream(copy_in):
+            tensors[right_name][:right_host.numel()].copy_(right_host, non_blocking=True)
+            right_ready = torch.cuda.Event()
+            right_ready.record(copy_in)
+            for i in range(blocks):
+                tensors[left_name][i * block_in:(i + 1) * block_in].copy_(left_host[i * block_in:(i + 1) * block_in], non_blocking=True)
+                event = torch.cuda.Event()
+                event.record(copy_in)
+                ready.append(event)
+        ws_ptr, ws_bytes = workspace
+        compute.wait_event(right_ready)
+        for i in range(blocks):
+            compute.wait_event(ready[i])
+            native.call('dtn_gemm_x3_phase', mode, pointers[left_name] + i * block_in, pointers[right_name],
+                        pointers[out_name] + i * block_out, rows, n, k, k, n, n, ws_ptr, ws_bytes, 3 | (8 if i else 0),
+                        compute.cuda_stream)
+            done = torch.cuda.Event()
+            done.record(compute)
+            copy_out.wait_event(done)
+            with torch.cuda.stream(copy_out):
+                out_host[i * block_out:(i + 1) * block_out].copy_(tensors[out_name][i * block_out:(i + 1) * block_out], non_blocking=True)
+        compute.wait_stream(copy_out)      # a synchronize of the runner's stream now covers the whole call
 
     def run_kernel(self, launch: Any, compiled: Any, produced: Any = None, *, warmup: Any = 10, iters: Any = 100,
                    samples: Any = 7) -> dict[str, Any]:

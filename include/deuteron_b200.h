@@ -128,10 +128,14 @@ int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, i
                 int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
                 size_t workspace_bytes, void* stream);
 
-/* dtn_gemm_x3 in separately launchable halves, so that a caller can time them apart or reuse
- * the operand planes: phase 1 = operand split into the workspace only, 2 = the product kernel
- * on planes already in the workspace, 3 = both (what dtn_gemm_x3 does). No reference
- * counterpart (the reference splits inside its single kernel). */
+/* dtn_gemm_x3 in separately launchable parts, so that a caller can time them apart or reuse
+ * operand planes between calls. `phase` is a mask: 1 = split the operands into the workspace,
+ * 2 = run the product kernel on the planes in the workspace (3 = both, what dtn_gemm_x3 does);
+ * with 4 the A planes already in the workspace are kept (A is not split again), with 8 the B
+ * planes are kept. The A planes sit at the start of the workspace and the B planes after them,
+ * at an offset that depends on (mode, M, K) only, so a caller that walks row blocks of equal
+ * height can split B once and pass 3|8 for every later block. No reference counterpart (the
+ * reference splits inside its single kernel). */
 int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
                       size_t workspace_bytes, int phase, void* stream);

@@ -318,6 +318,30 @@ def test_gemm_column_blocks_equal_the_full_product(cuda):
     assert bool(cuda.equal(into[:, 256:512], full[:, 256:512])) and float(into[:, :256].abs().sum()) == 0.0
 
 
+def test_execute_on_host_buffers_matches_the_resident_path(cuda, runner):
+    # small product: one launch; large product: the row-block pipeline (copies overlapped with products)
+    for m, n, k in ((128, 128, 128), (4096, 1024, 2048)):
+        graph, meta = schedules.matmul_example(m, n, k)
+        compiled = compile_kernel(graph, meta, options=Options(contraction_precision='bf16x3'))
+        left, right = runner.pinned((m, k), np.float32), runner.pinned((k, n), np.float32)
+        left[:], right[:] = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+        result = runner.pinned((m, n), np.float32)
+        for _ in range(2):   # the second call reuses the resident device buffers
+            result[:] = 0
+            produced = runner.execute(compiled, {'left': left, 'right': right}, {'result': result})['result']
+            assert produced is result
+            resident = ops.gemm(to_device(cuda, left), to_device(cuda, right), 'bf16x3').cpu().numpy()
+            np.testing.assert_array_equal(produced, resident)
+    unpinned = runner.execute(compiled, {'left': np.array(left), 'right': np.array(right)})['result']
+    np.testing.assert_array_equal(unpinned, resident)
+    graph, meta = schedules.vector_add_example(4096)
+    x, y = R.seeded_normal(1, (4096,)), R.seeded_normal(2, (4096,))
+    produced = runner.execute(compile_kernel(graph, meta), {'lhs': x, 'rhs': y})['sum']
+    np.testing.assert_array_equal(produced, x + y)
+    with pytest.raises(ValueError):
+        runner.execute(compile_kernel(graph, meta), {'lhs': x[:-1], 'rhs': y})
+
+
 @pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
 def test_gemm_8192_properties(cuda, mode):
     n = 8192
