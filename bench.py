@@ -222,6 +222,10 @@ def run_ours(args) -> None:
     rank = int(os.environ.get('RANK', '0'))
     local_rank = int(os.environ.get('LOCAL_RANK', '0'))
     world = int(os.environ.get('WORLD_SIZE', '1'))
+    # Libraries (NCCL's version banner) write to stdout; keep stdout for the one JSON line.
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
     if not torch.cuda.is_available():
         raise SystemExit('bench.py needs a CUDA device: the kernels have no CPU path')
     torch.cuda.set_device(local_rank)
@@ -341,7 +345,9 @@ def run_ours(args) -> None:
             del a, b, c
             torch.cuda.empty_cache()
             line['extras'] = extras(torch, ops, peaks)
-        print(json.dumps(line))
+        sys.stdout.flush()
+        os.dup2(json_fd, 1)
+        print(json.dumps(line), flush=True)
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
