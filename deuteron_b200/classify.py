@@ -294,8 +294,13 @@ def _classify_elementwise(tile: ir.Node, specs: dict) -> Plan | None:
     # symbolic value of every name: ('load', buffer, lane) or ('op', name, args)
     values: dict[str, tuple] = {}
     origins: dict[str, int | None] = {}
+    constants: dict[str, int] = {}
     for load in loads:
         offset = _flat_access(load.index, element_vars, len(load.names), load.input)
+        if offset is None:
+            constants[load.input] = ir.affine(load.index[0])[1]
+            if not 0 <= constants[load.input] < math.prod(_shape(specs, load.input)):
+                raise ValueError(f'{load.input}: constant index outside the buffer')
         if offset is not None and len(load.names) != width:
             raise NotImplementedError('vector loads and stores must have the same width')
         if origins.setdefault(load.input, offset) != offset:
@@ -337,13 +342,11 @@ def _classify_elementwise(tile: ir.Node, specs: dict) -> Plan | None:
     op, args = tree[1], tree[2]
     if op not in ELEMENTWISE_OPS:
         raise NotImplementedError(f'elementwise operation {op}')
-    if any(arg[0] != 'load' for arg in args):
-        raise NotImplementedError('chained elementwise expressions are outside the supported subset')
+    simple = (all(arg[0] == 'load' and origins[arg[1]] is not None and specs[arg[1]]['dtype'] == 'f32' for arg in args)
+              and out_dtype == 'f32')
+    if not simple:
+        return _program_plan(tree, specs, origins, constants, write.output, out_offset, n)
     names = [arg[1] for arg in args]
-    if any(origins[name] is None for name in names):
-        raise NotImplementedError('broadcast scalar operands are outside the supported subset')
-    if out_dtype != 'f32' or any(specs[name]['dtype'] != 'f32' for name in names):
-        raise NotImplementedError('f16 buffers support copy, widen and narrow; arithmetic takes f32 buffers')
     if op in BINARY_OPS:
         if len(names) != 2:
             raise ValueError(f'{op} takes two operands')
@@ -352,6 +355,67 @@ def _classify_elementwise(tile: ir.Node, specs: dict) -> Plan | None:
     if len(names) != 1:
         raise ValueError(f'{op} takes one operand')
     return Plan('elementwise', {'op': op, 'n': n}, {'x': (names[0], origins[names[0]]), 'out': (write.output, out_offset)})
+
+
+PROGRAM_REGISTERS, PROGRAM_INSTRUCTIONS, PROGRAM_INPUTS = 8, 24, 6
+
+
+def _program_plan(tree: tuple, specs: dict, origins: dict, constants: dict, output: str, out_offset: int, n: int) -> Plan:
+    """Linearises an expression tree into the register program dtn_elementwise_program interprets.
+
+    Inputs take registers 0..k-1 in order of first use; every operator result takes the lowest free
+    register; a register is free again after the last instruction that reads it.
+    """
+    order: list[tuple] = []          # unique nodes, operands before users
+
+    def visit(node: tuple) -> None:
+        if node in order:
+            return
+        if node[0] == 'op':
+            if node[1] not in ELEMENTWISE_OPS:
+                raise NotImplementedError(f'elementwise operation {node[1]}')
+            arity = 2 if node[1] in BINARY_OPS else 1
+            if len(node[2]) != arity:
+                raise ValueError(f'{node[1]} takes {arity} operand(s)')
+            for operand in node[2]:
+                visit(operand)
+        order.append(node)
+
+    visit(tree)
+    inputs = [node for node in order if node[0] == 'load']
+    operators = [node for node in order if node[0] == 'op']
+    if len(inputs) > PROGRAM_INPUTS or len(operators) > PROGRAM_INSTRUCTIONS:
+        raise NotImplementedError('elementwise expression is too large for the fused kernel')
+    last_use = {}
+    for position, node in enumerate(operators):
+        for operand in node[2]:
+            last_use[operand] = position
+    register = {node: index for index, node in enumerate(inputs)}
+    free = [r for r in range(PROGRAM_REGISTERS) if r >= len(inputs)]
+    program = {'ops': [], 'dst': [], 'a': [], 'b': []}
+    for position, node in enumerate(operators):
+        sources = [register[operand] for operand in node[2]]
+        for operand in set(node[2]):
+            if last_use[operand] == position:
+                free.append(register[operand])
+        if not free:
+            raise NotImplementedError('elementwise expression needs more than 8 live values')
+        free.sort()
+        target = free.pop(0)
+        register[node] = target
+        program['ops'].append(ELEMENTWISE_OPS[node[1]])
+        program['dst'].append(target)
+        program['a'].append(sources[0])
+        program['b'].append(sources[-1])
+    buffers = {'out': (output, out_offset)}
+    described = []
+    for index, node in enumerate(inputs):
+        name = node[1]
+        scalar = origins[name] is None
+        buffers[f'in{index}'] = (name, constants[name] if scalar else origins[name])
+        described.append({'f16': specs[name]['dtype'] == 'f16', 'scalar': scalar})
+    params = {'n': n, 'inputs': described, 'out_reg': register[tree], 'out_f16': specs[output]['dtype'] == 'f16', **program}
+    return Plan('elementwise_program', params, buffers)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -6,7 +6,7 @@ namespace dtn {
 int gqa_f32_launch(const void* q, const void* k, const void* v, float* out, int64_t Hq, int64_t Hkv, int64_t S,
                    int64_t D, float scale, int storage, int64_t gb, int64_t ge, cudaStream_t s);
 int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
-                  int64_t S, float scale, int64_t gb, int64_t ge, cudaStream_t s);
+                  int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s);
 bool gqa_tc_supported(int64_t S, int64_t D, int storage);
 
 static int g_gqa_variant = 0;
@@ -16,7 +16,7 @@ static int g_gqa_variant = 0;
 extern "C" {
 
 int dtn_gqa_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 2, DTN_ERR_INVALID, "gqa: variant must be 0..2");
+  DTN_REQUIRE(variant >= 0 && variant <= 3, DTN_ERR_INVALID, "gqa: variant must be 0..3");
   dtn::g_gqa_variant = variant;
   return DTN_OK;
 }
@@ -41,10 +41,10 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   cudaStream_t s = as_stream(stream);
   int variant = g_gqa_variant;
   if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 2 : 1;
-  if (variant == 2) {
+  if (variant >= 2) {
     DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
                 "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");
-    return gqa_tc_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, s);
+    return gqa_tc_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, variant == 3 ? 2 : 1, s);
   }
   return gqa_f32_launch(q, k, v, out, Hq, Hkv, S, D, scale, storage, group_begin, group_end, s);
 }

@@ -27,7 +27,7 @@
 
 namespace dtn {
 
-constexpr int A_THREADS = 320;
+constexpr int attn_threads(int split) { return (8 * split + 2) * 32; }   // softmax warps + TMA warp + MMA warp
 constexpr int A_BM = 128;          // query rows per tile (two tiles per CTA)
 constexpr int A_BN = 128;          // keys per step
 constexpr int A_D = 128;           // head dimension
@@ -35,7 +35,8 @@ constexpr int A_HALF_BYTES = 128 * 128;           // one [128 rows][64 f16] swiz
 constexpr int A_TILE_BYTES = 2 * A_HALF_BYTES;    // one [128][128] f16 tile
 constexpr int A_KV_STAGES = 2;
 constexpr int A_SMEM_TILES = 2 /*Q*/ + 2 * A_KV_STAGES /*K,V*/;
-constexpr int A_SMEM_BYTES = A_SMEM_TILES * A_TILE_BYTES + 256 + 1024;
+constexpr int A_XCHG_BYTES = 2 * 2 * 128 * 8;   // [tile][column share][row] (value, sequence) slots
+constexpr int A_SMEM_BYTES = A_SMEM_TILES * A_TILE_BYTES + 256 + A_XCHG_BYTES + 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;   // in log2 units
 constexpr float A_BIAS = 4.0f;                // probabilities are kept scaled by 2^4 (f16 residuals stay normal)
 
@@ -52,12 +53,45 @@ __device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr) {
   return d;
 }
 
+// max(a, b, c) in one instruction (sm_100 has a three-input FP32 max).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+
 // idesc: f16 operands, FP32 accumulate, M = 128, N = 128; b_mn = 1 when B is MN-major.
 __host__ __device__ constexpr uint32_t attn_idesc(int b_mn) {
   return ptx::umma_idesc(0, 128, 128) | ((uint32_t)b_mn << 16);
 }
 
-__global__ void __launch_bounds__(A_THREADS, 1)
+// Hands `value` to the thread that owns the other column share of the same row and returns that
+// thread's value in `other`. A slot holds (value, sequence number); the 8-byte store makes both
+// visible together. The wait is bounded like every other wait in this file.
+__device__ __forceinline__ bool exchange_with_peer(volatile float2* mine, volatile float2* theirs, float value, int seq,
+                                                   volatile int* abort_flag, float& other) {
+  float2 packed = make_float2(value, __int_as_float(seq));
+  asm volatile("st.volatile.shared.v2.f32 [%0], {%1, %2};" ::"r"(smem_u32((const void*)mine)), "f"(packed.x), "f"(packed.y)
+               : "memory");
+  const uint32_t addr = smem_u32((const void*)theirs);
+  const long long start = clock64();
+  while (true) {
+    float a, b;
+    asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr) : "memory");
+    if (__float_as_int(b) == seq) {
+      other = a;
+      return true;
+    }
+    if (*abort_flag) return false;
+    if (clock64() - start > ptx::kWaitBudgetCycles) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+template <int SPLIT /*warpgroups per 128-row tile: 1 or 2*/>
+__global__ void __launch_bounds__(attn_threads(SPLIT), 1)
 gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, float* __restrict__ out, int Hq, int Hkv, int S,
               float scale_log2e, int group_begin, int* __restrict__ status) {
@@ -81,6 +115,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   auto o_done = [&](int t) { return bar_addr + 8u * (13 + t); };
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * 15);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 15 + 8);
+  volatile float2* xchg = reinterpret_cast<volatile float2*>(bar_ptr + 256);
+  constexpr int kTmaWarp = 8 * SPLIT, kMmaWarp = 8 * SPLIT + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int heads_per_group = Hq / Hkv;
@@ -91,6 +127,10 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int kv_row0 = (b * Hkv + hkv) * S;
   const int num_kv = S / A_BN;
 
+  for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) {   // sequence 0 = empty
+    xchg[i].x = 0.f;
+    xchg[i].y = 0.f;
+  }
   if (threadIdx.x == 0) {
     *abort_flag = 0;
     ptx::mbar_init(q_full, 1);
@@ -102,7 +142,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     }
     for (int t = 0; t < 2; ++t) {
       ptx::mbar_init(s_full(t), 1);
-      ptx::mbar_init(p_full(t), 4);   // one arrival per softmax warp
+      ptx::mbar_init(p_full(t), 4 * SPLIT);   // one arrival per softmax warp
       ptx::mbar_init(o_done(t), 1);
     }
     ptx::mbar_fence_init();
@@ -111,7 +151,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     ptx::tma_prefetch_desc(&tm_k);
     ptx::tma_prefetch_desc(&tm_v);
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     ptx::tmem_alloc<1>(smem_u32(tmem_holder), 512);
     ptx::tmem_relinquish<1>();
   }
@@ -120,7 +160,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp == 8) {
+  if (warp == kTmaWarp) {
     // ------------------------------------ TMA producer ---------------------------------------
     if (lane == 0) {
       ptx::mbar_expect_tx(q_full, 2 * A_TILE_BYTES);
@@ -141,7 +181,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     }
     __syncwarp();
-  } else if (warp == 9) {
+  } else if (warp == kMmaWarp) {
     // ------------------------------------ MMA issuer -----------------------------------------
     if (lane == 0) {
       constexpr uint32_t kIdescQK = attn_idesc(0);
@@ -211,11 +251,20 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     __syncwarp();
   } else {
     // ------------------------------------ softmax + output -----------------------------------
-    const int t = warp >> 2;                       // tile of this warpgroup
+    // SPLIT warpgroups share one tile: each owns 128 / SPLIT score columns (and the same share of
+    // the output columns) of all 128 rows. Partner threads of a row agree on the row maximum
+    // through a shared-memory slot (bounded spin, no block-wide barrier).
+    constexpr int kChunks = 4 / SPLIT;             // 32-column chunks per thread
+    const int t = warp / (4 * SPLIT);              // tile
+    const int part = (warp >> 2) % SPLIT;          // column share of this warpgroup
     const int quarter = warp & 3;
+    const int row_in_tile = quarter * 32 + lane;
+    const int c0 = part * kChunks;
     const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
     const uint32_t s_tmem = tmem_base + lane_field + (uint32_t)(t * 128);
     const uint32_t o_tmem = tmem_base + lane_field + (uint32_t)(256 + t * 128);
+    volatile float2* my_slot = xchg + ((t * 2 + part) * 128 + row_in_tile);
+    volatile float2* peer_slot = xchg + ((t * 2 + (part ^ 1)) * 128 + row_in_tile);
     float m_used = -INFINITY;   // log2-domain maximum the current probabilities are scaled by
     float mass = 0.f;
     bool ok = true;
@@ -227,15 +276,25 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         break;
       }
       ptx::tc_fence_after();
-      // pass 1: row maximum of the raw scores
+      // pass 1: row maximum of the raw scores (three-input max: two scores per instruction)
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c0; c < c0 + kChunks; ++c) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(s_tmem + (uint32_t)(c * 32), r);
         ptx::tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(r[i]));
+        for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      }
+      if constexpr (SPLIT == 2) {
+        float other;
+        const bool got = exchange_with_peer(my_slot, peer_slot, mx, j + 1, abort_flag, other);
+        if (!__all_sync(0xffffffffu, got)) {
+          if (lane == 0) atomicExch(status, 0x3300 | t);
+          ok = false;
+          break;
+        }
+        mx = fmaxf(mx, other);
       }
       const float mx2 = mx * scale_log2e;
       const bool grow = (j == 0) || (mx2 > m_used + A_RESCALE_THRESHOLD);
@@ -245,7 +304,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (j > 0) {
           // All earlier products into O_t are complete: s_full(t) of this step was committed after them.
 #pragma unroll 1
-          for (int c = 0; c < 4; ++c) {
+          for (int c = c0; c < c0 + kChunks; ++c) {
             uint32_t r[32];
             ptx::tmem_ld_32x32(o_tmem + (uint32_t)(c * 32), r);
             ptx::tmem_ld_wait();
@@ -261,7 +320,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       // pass 2: probabilities, row sum, f16 high/residual split written over the scores
       const float shift = A_BIAS - m_used;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = c0; c < c0 + kChunks; ++c) {
         uint32_t r[32], w[32];
         ptx::tmem_ld_32x32(s_tmem + (uint32_t)(c * 32), r);
         ptx::tmem_ld_wait();
@@ -284,16 +343,21 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (lane == 0) ptx::mbar_arrive(p_full(t));
     }
     if (ok) {
-      const bool ready = ptx::mbar_wait(o_done(t), 0, abort_flag);
+      bool ready = ptx::mbar_wait(o_done(t), 0, abort_flag);
+      if constexpr (SPLIT == 2) {
+        float other = 0.f;
+        ready = ready && exchange_with_peer(my_slot, peer_slot, mass, num_kv + 1, abort_flag, other);
+        mass += other;
+      }
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) atomicExch(status, 0x3200 | t);
       } else {
         ptx::tc_fence_after();
         const float inv = 1.0f / mass;
-        const int row = (int)blockIdx.x * (2 * A_BM) + t * A_BM + quarter * 32 + lane;
+        const int row = (int)blockIdx.x * (2 * A_BM) + t * A_BM + row_in_tile;
         float* orow = out + ((int64_t)(b * Hq + hq) * S + row) * A_D;
 #pragma unroll 1
-        for (int c = 0; c < 4; ++c) {
+        for (int c = c0; c < c0 + kChunks; ++c) {
           uint32_t r[32];
           ptx::tmem_ld_32x32(o_tmem + (uint32_t)(c * 32), r);
           ptx::tmem_ld_wait();
@@ -313,7 +377,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == 9) {
+  if (warp == kMmaWarp) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc<1>(tmem_base, 512);
   }
@@ -356,8 +420,9 @@ bool gqa_tc_supported(int64_t S, int64_t D, int storage) {
   return storage == DTN_STORAGE_F16 && D == A_D && S >= 2 * A_BM && S % (2 * A_BM) == 0;
 }
 
-int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
-                  int64_t S, float scale, int64_t gb, int64_t ge, cudaStream_t s) {
+template <int SPLIT>
+static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
+                           int64_t S, float scale, int64_t gb, int64_t ge, cudaStream_t s) {
   CUtensorMap mq, mk, mv;
   int rc;
   if ((rc = make_rows_map(&mq, q, B * Hq * S))) return rc;
@@ -367,7 +432,7 @@ int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64
   int dev = 0;
   DTN_CUDA_CHECK(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    DTN_CUDA_CHECK(cudaFuncSetAttribute(gqa_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM_BYTES));
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(gqa_tc_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM_BYTES));
     attr_dev = dev;
   }
   int* status = device_status_word();
@@ -376,10 +441,16 @@ int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64
   DTN_REQUIRE(heads <= 65535, DTN_ERR_UNSUPPORTED, "gqa: too many heads for one launch");
   dim3 grid((unsigned)(S / (2 * A_BM)), (unsigned)heads);
   const float scale_log2e = scale * 1.4426950408889634f;
-  gqa_tc_kernel<<<grid, A_THREADS, A_SMEM_BYTES, s>>>(mq, mk, mv, out, (int)Hq, (int)Hkv, (int)S, scale_log2e, (int)gb,
+  gqa_tc_kernel<SPLIT><<<grid, attn_threads(SPLIT), A_SMEM_BYTES, s>>>(mq, mk, mv, out, (int)Hq, (int)Hkv, (int)S, scale_log2e, (int)gb,
                                                       status);
   DTN_LAUNCH_CHECK("gqa_tc_kernel");
   return DTN_OK;
+}
+
+int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
+                  int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s) {
+  return split == 2 ? gqa_tc_launch_t<2>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s)
+                    : gqa_tc_launch_t<1>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s);
 }
 
 }  // namespace dtn

@@ -1,0 +1,239 @@
+// Fused elementwise expressions over f16 / f32 buffers: one pass over memory for a whole chain of
+// operators (for example the reference's f16 "affine" kernel, f16(x * scale + bias), and its
+// "cancellation" kernel, f16((x + y) - x), both computed in explicit FP32).
+//
+// The expression arrives as a short register program (at most 24 instructions over 8 virtual
+// registers). Every thread interprets it on 8 consecutive elements at a time: the operand
+// decode is uniform across the grid (no divergence) and is paid once per 8 elements, so the
+// kernel stays bandwidth-bound. Vector inputs are read with 128-bit loads, one-element inputs
+// are broadcast, arithmetic is FP32 with one rounding per operator (no contraction into fma, so
+// results equal the reference's operator-by-operator NumPy expectation), and the result is
+// narrowed to f16 with round-to-nearest-even when the output buffer is f16.
+#include "dtn_common.cuh"
+
+namespace dtn {
+
+constexpr int kProgMaxInstr = 24;
+constexpr int kProgRegs = 8;
+constexpr int kProgMaxInputs = 6;
+
+struct EwProgram {
+  int n_inputs;                      // registers 0..n_inputs-1 are loaded from the inputs
+  int n_instr;
+  int out_reg;
+  int out_f16;                       // 1: narrow the result to f16
+  const void* input[kProgMaxInputs];
+  unsigned char input_f16[kProgMaxInputs];
+  unsigned char input_scalar[kProgMaxInputs];   // 1: one-element buffer, broadcast
+  unsigned char op[kProgMaxInstr], dst[kProgMaxInstr], a[kProgMaxInstr], b[kProgMaxInstr];
+};
+
+template <int W>
+struct RegFile {
+  float r[kProgRegs][W];
+  __device__ __forceinline__ void get(int idx, float (&out)[W]) const {
+#pragma unroll
+    for (int k = 0; k < kProgRegs; ++k)
+      if (idx == k) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) out[e] = r[k][e];
+      }
+  }
+  __device__ __forceinline__ void put(int idx, const float (&in)[W]) {
+#pragma unroll
+    for (int k = 0; k < kProgRegs; ++k)
+      if (idx == k) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) r[k][e] = in[e];
+      }
+  }
+};
+
+__device__ __forceinline__ float prog_apply(int op, float a, float b) {
+  switch (op) {
+    case DTN_EW_ADD: return __fadd_rn(a, b);
+    case DTN_EW_SUB: return __fsub_rn(a, b);
+    case DTN_EW_MUL: return __fmul_rn(a, b);
+    case DTN_EW_DIV: return __fdividef(a, b);
+    case DTN_EW_MAX: return fmaxf(a, b);
+    case DTN_EW_MIN: return fminf(a, b);
+    case DTN_EW_RELU: return fmaxf(a, 0.0f);
+    case DTN_EW_EXP: return exp_ref(a);
+    case DTN_EW_SQRT: {
+      float y;
+      asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(a));
+      return y;
+    }
+    case DTN_EW_RSQRT: {
+      float y;
+      asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(a));
+      return y;
+    }
+    case DTN_EW_RCP: return rcp_approx(a);
+    case DTN_EW_NEG: return -a;
+    case DTN_EW_ABS: return fabsf(a);
+    default: return a;
+  }
+}
+
+// W = 8: vector body (every vector pointer 16-byte aligned at `first`); W = 1: scalar elements.
+template <int W>
+__global__ void __launch_bounds__(256)
+ew_program_kernel(const EwProgram prog, void* __restrict__ out, int64_t first, int64_t count) {
+  const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  for (int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; item < count; item += stride) {
+    const int64_t base = first + item * W;
+    RegFile<W> regs;
+#pragma unroll
+    for (int i = 0; i < kProgMaxInputs; ++i) {
+      if (i >= prog.n_inputs) break;
+      float v[W];
+      if (prog.input_scalar[i]) {
+        const float s = prog.input_f16[i] ? __half2float(*static_cast<const __half*>(prog.input[i]))
+                                          : *static_cast<const float*>(prog.input[i]);
+#pragma unroll
+        for (int e = 0; e < W; ++e) v[e] = s;
+      } else if (prog.input_f16[i]) {
+        const __half* p = static_cast<const __half*>(prog.input[i]) + base;
+        if constexpr (W == 8) {
+          uint4 raw = ld_stream_u4(reinterpret_cast<const uint4*>(p));
+          const __half2* h = reinterpret_cast<const __half2*>(&raw);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 f = __half22float2(h[e]);
+            v[2 * e] = f.x;
+            v[2 * e + 1] = f.y;
+          }
+        } else {
+          v[0] = __half2float(p[0]);
+        }
+      } else {
+        const float* p = static_cast<const float*>(prog.input[i]) + base;
+        if constexpr (W == 8) {
+          const float4 lo = ld_stream_f4(reinterpret_cast<const float4*>(p));
+          const float4 hi = ld_stream_f4(reinterpret_cast<const float4*>(p) + 1);
+          v[0] = lo.x; v[1] = lo.y; v[2] = lo.z; v[3] = lo.w;
+          v[4] = hi.x; v[5] = hi.y; v[6] = hi.z; v[7] = hi.w;
+        } else {
+          v[0] = p[0];
+        }
+      }
+      regs.put(i, v);
+    }
+    for (int n = 0; n < prog.n_instr; ++n) {
+      float a[W], b[W], d[W];
+      regs.get(prog.a[n], a);
+      regs.get(prog.b[n], b);
+      const int op = prog.op[n];
+#pragma unroll
+      for (int e = 0; e < W; ++e) d[e] = prog_apply(op, a[e], b[e]);
+      regs.put(prog.dst[n], d);
+    }
+    float result[W];
+    regs.get(prog.out_reg, result);
+    if (prog.out_f16) {
+      __half* q = static_cast<__half*>(out) + base;
+      if constexpr (W == 8) {
+        uint4 packed;
+        __half2* h = reinterpret_cast<__half2*>(&packed);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2half2_rn(result[2 * e], result[2 * e + 1]);
+        st_stream_u4(reinterpret_cast<uint4*>(q), packed);
+      } else {
+        q[0] = __float2half_rn(result[0]);
+      }
+    } else {
+      float* q = static_cast<float*>(out) + base;
+      if constexpr (W == 8) {
+        st_stream_f4(reinterpret_cast<float4*>(q), make_float4(result[0], result[1], result[2], result[3]));
+        st_stream_f4(reinterpret_cast<float4*>(q) + 1, make_float4(result[4], result[5], result[6], result[7]));
+      } else {
+        q[0] = result[0];
+      }
+    }
+  }
+}
+
+}  // namespace dtn
+
+extern "C" int dtn_elementwise_program(const unsigned char* ops, const unsigned char* dsts, const unsigned char* as,
+                                       const unsigned char* bs, int n_instr, const void* const* inputs,
+                                       const unsigned char* input_f16, const unsigned char* input_scalar, int n_inputs,
+                                       int out_reg, void* out, int out_f16, int64_t n, void* stream) {
+  using namespace dtn;
+  DTN_REQUIRE(n >= 0, DTN_ERR_INVALID, "elementwise program: negative n");
+  DTN_REQUIRE(n_instr >= 0 && n_instr <= kProgMaxInstr, DTN_ERR_UNSUPPORTED, "elementwise program: at most %d instructions",
+              kProgMaxInstr);
+  DTN_REQUIRE(n_inputs >= 1 && n_inputs <= kProgMaxInputs, DTN_ERR_UNSUPPORTED, "elementwise program: 1..%d inputs",
+              kProgMaxInputs);
+  DTN_REQUIRE(out_reg >= 0 && out_reg < kProgRegs, DTN_ERR_INVALID, "elementwise program: bad output register");
+  if (n == 0) return DTN_OK;
+  DTN_REQUIRE(out && inputs && input_f16 && input_scalar && (n_instr == 0 || (ops && dsts && as && bs)), DTN_ERR_INVALID,
+              "elementwise program: null pointer");
+  EwProgram prog = {};
+  prog.n_inputs = n_inputs;
+  prog.n_instr = n_instr;
+  prog.out_reg = out_reg;
+  prog.out_f16 = out_f16 ? 1 : 0;
+  const void* vec_ptrs[kProgMaxInputs + 1];
+  int vec_sizes[kProgMaxInputs + 1];
+  int vec_count = 0;
+  for (int i = 0; i < n_inputs; ++i) {
+    DTN_REQUIRE(inputs[i] != nullptr, DTN_ERR_INVALID, "elementwise program: input %d is null", i);
+    const int size = input_f16[i] ? 2 : 4;
+    DTN_REQUIRE(aligned_to(inputs[i], size), DTN_ERR_INVALID, "elementwise program: input %d is misaligned", i);
+    prog.input[i] = inputs[i];
+    prog.input_f16[i] = input_f16[i] ? 1 : 0;
+    prog.input_scalar[i] = input_scalar[i] ? 1 : 0;
+    if (!input_scalar[i]) {
+      vec_ptrs[vec_count] = inputs[i];
+      vec_sizes[vec_count++] = size;
+    }
+  }
+  for (int k = 0; k < n_instr; ++k) {
+    DTN_REQUIRE(ops[k] <= DTN_EW_COPY && dsts[k] < kProgRegs && as[k] < kProgRegs && bs[k] < kProgRegs, DTN_ERR_INVALID,
+                "elementwise program: instruction %d is malformed", k);
+    prog.op[k] = ops[k];
+    prog.dst[k] = dsts[k];
+    prog.a[k] = as[k];
+    prog.b[k] = bs[k];
+  }
+  const int out_size = out_f16 ? 2 : 4;
+  DTN_REQUIRE(aligned_to(out, out_size), DTN_ERR_INVALID, "elementwise program: output is misaligned");
+  vec_ptrs[vec_count] = out;
+  vec_sizes[vec_count++] = out_size;
+  cudaStream_t s = as_stream(stream);
+  // smallest head (in elements) after which every vector pointer is 16-byte aligned
+  int head = -1;
+  for (int h = 0; h < 16 && head < 0; ++h) {
+    bool ok = true;
+    for (int i = 0; i < vec_count && ok; ++i)
+      ok = ((reinterpret_cast<uintptr_t>(vec_ptrs[i]) + (uintptr_t)h * vec_sizes[i]) & 15) == 0;
+    if (ok) head = h;
+  }
+  auto grid_for = [](int64_t items) {
+    int64_t blocks = (items + 255) / 256;
+    const int64_t cap = (int64_t)sm_count() * 16;
+    return (unsigned)(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+  };
+  if (head < 0 || n < 64) {
+    ew_program_kernel<1><<<grid_for(n), 256, 0, s>>>(prog, out, 0, n);
+    DTN_LAUNCH_CHECK("ew_program_kernel<1>");
+    return DTN_OK;
+  }
+  const int64_t body = (n - head) / 8;
+  const int64_t tail_start = head + body * 8;
+  if (head > 0) {
+    ew_program_kernel<1><<<1, 32, 0, s>>>(prog, out, 0, head);
+    DTN_LAUNCH_CHECK("ew_program_kernel<1>(head)");
+  }
+  if (body > 0) {
+    ew_program_kernel<8><<<grid_for(body), 256, 0, s>>>(prog, out, head, body);
+    DTN_LAUNCH_CHECK("ew_program_kernel<8>");
+  }
+  if (tail_start < n) {
+    ew_program_kernel<1><<<1, 32, 0, s>>>(prog, out, tail_start, n - tail_start);
+    DTN_LAUNCH_CHECK("ew_program_kernel<1>(tail)");
+  }
+  return DTN_OK;
+}

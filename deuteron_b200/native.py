@@ -38,6 +38,7 @@ _SIGNATURES = {
     'dtn_device_status': [ct.POINTER(ct.c_int), _P],
     'dtn_add_f32': [_P, _P, _P, _I64, _P],
     'dtn_elementwise_f32': [_I, _P, _P, _P, _I64, _P],
+    'dtn_elementwise_program': [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I64, _P],
     'dtn_f16_copy': [_P, _P, _I64, _P],
     'dtn_f16_widen': [_P, _P, _I64, _P],
     'dtn_f16_narrow': [_P, _P, _I64, _P],
@@ -101,6 +102,17 @@ def check(status: int) -> None:
 
 def call(name: str, *args) -> None:
     check(getattr(lib(), name)(*args))
+
+
+def elementwise_program(params: dict, input_pointers: list[int], out_pointer: int, stream: int) -> None:
+    """Launches dtn_elementwise_program for a classifier-built register program (classify._program_plan)."""
+    count = len(params['ops'])
+    as_bytes = lambda values: (ct.c_ubyte * max(len(values), 1))(*values)
+    inputs = (ct.c_void_p * len(input_pointers))(*input_pointers)
+    call('dtn_elementwise_program', as_bytes(params['ops']), as_bytes(params['dst']), as_bytes(params['a']),
+         as_bytes(params['b']), count, inputs, as_bytes([int(i['f16']) for i in params['inputs']]),
+         as_bytes([int(i['scalar']) for i in params['inputs']]), len(input_pointers), params['out_reg'], out_pointer,
+         int(params['out_f16']), params['n'], stream)
 
 
 def device_status(stream: int = 0) -> int:

@@ -136,6 +136,10 @@ class LocalRunner:
             binary = 'y' in plan.buffers
             native.call('dtn_elementwise_f32', native.ELEMENTWISE_OPS[p['op']], ptr('x', 4), ptr('y', 4) if binary else None,
                         ptr('out', 4), p['n'], stream)
+        elif kind == 'elementwise_program':
+            sizes = [2 if spec['f16'] else 4 for spec in p['inputs']]
+            native.elementwise_program(p, [ptr(f'in{i}', size) for i, size in enumerate(sizes)],
+                                       ptr('out', 2 if p['out_f16'] else 4), stream)
         elif kind == 'f16_copy':
             native.call('dtn_f16_copy', ptr('x', 2), ptr('out', 2), p['n'], stream)
         elif kind == 'f16_widen':

@@ -122,26 +122,45 @@ def vector_add_example(count: int = 1030, seeds=(21, 22)) -> tuple[dict, dict]:
 
 
 def f16_storage_example(kind: str = 'copy', count: int = 512, width: int = 4, offset: int = 0) -> tuple[dict, dict]:
-    """copy / widen / narrow of examples/f16_storage.py:19-60 (same entry names, widths and launch)."""
-    if kind not in ('copy', 'widen', 'narrow') or width not in (1, 2, 4) or count <= 0 or count % width:
+    """The five f16 storage kernels of examples/f16_storage.py:19-60 (same entry names, widths, launch,
+    seeds and constant buffers): copy, widen, narrow, affine f16(x * 1.5 - 0.25) and cancellation
+    f16((x + y) - x), the last two computed in explicit FP32."""
+    if kind not in ('copy', 'widen', 'narrow', 'affine', 'cancellation') or width not in (1, 2, 4) or count <= 0 or count % width:
         raise ValueError('unsupported example configuration')
     source, destination = ('f32', F32) if kind == 'narrow' else ('f16', F16), ('f32', F32) if kind == 'widen' else ('f16', F16)
     index = mul(var('element'), lit(width))
     names = tuple(f'input_{i}' for i in range(width))
     body = [load(names, 'x', [add(index, lit(offset))], source[1])]
-    values = names
-    if kind == 'widen':
+    args = [{'name': 'x', 'dtype': source[0], 'shape': [count + offset], 'seed': 7}]
+    values, value_dtype = names, source[1]
+    if kind == 'affine':
+        args += [{'name': 'scale', 'dtype': 'f32', 'shape': [1], 'data': [1.5]}, {'name': 'bias', 'dtype': 'f32', 'shape': [1], 'data': [-0.25]}]
+        body += [load(('scale_value',), 'scale', [lit(0)]), load(('bias_value',), 'bias', [lit(0)])]
+        values = tuple(f'result_{i}' for i in range(width))
+        for i, name in enumerate(names):
+            body += [assign(f'product_{i}', 'multiply', (name, 'scale_value')), assign(values[i], 'add', (f'product_{i}', 'bias_value'))]
+        value_dtype = F32
+    elif kind == 'cancellation':
+        args.append({'name': 'y', 'dtype': 'f16', 'shape': [count], 'seed': 8})
+        second = tuple(f'other_{i}' for i in range(width))
+        body.append(load(second, 'y', [index], F16))
+        values = tuple(f'result_{i}' for i in range(width))
+        for i, name in enumerate(names):
+            body += [assign(f'sum_{i}', 'add', (name, second[i])), assign(values[i], 'subtract', (f'sum_{i}', name))]
+        value_dtype = F32
+    elif kind == 'widen':
         values = tuple(f'result_{i}' for i in range(width))
         body += [assign(value, 'copy', (name,)) for value, name in zip(values, names)]
-    body.append(write('result', [index], values, F32 if kind == 'widen' else source[1]))
+        value_dtype = F32
+    body.append(write('result', [index], values, value_dtype))
+    args.append({'name': 'result', 'dtype': destination[0], 'shape': [count], 'output': True})
     entry = 'f16_storage_' + kind
     text = tile([axis('element', count // width)], body, 128)
-    graph = _graph(entry, text, {'x': ([count + offset], source[0])}, ('result', [count], destination[0]))
-    launch = {'node': 'result', 'entry': entry, 'arg_order': ['x', 'result'], 'grid': [math.ceil(count / width / 128), 1, 1],
-              'block': [128, 1, 1], 'smem_bytes': 0, 'zero_outputs': [],
-              'args': [{'name': 'x', 'dtype': source[0], 'shape': [count + offset], 'seed': 7},
-                       {'name': 'result', 'dtype': destination[0], 'shape': [count], 'output': True}], 'final': True}
-    return graph, _metadata(entry, launch, 0.001, 0.00001, ['x'], ['result'])
+    inputs = {a['name']: (a['shape'], a['dtype']) for a in args if not a.get('output')}
+    graph = _graph(entry, text, inputs, ('result', [count], destination[0]))
+    launch = {'node': 'result', 'entry': entry, 'arg_order': [a['name'] for a in args], 'grid': [math.ceil(count / width / 128), 1, 1],
+              'block': [128, 1, 1], 'smem_bytes': 0, 'zero_outputs': [], 'args': args, 'final': True}
+    return graph, _metadata(entry, launch, 0.001, 0.00001, list(inputs), ['result'])
 
 
 def attention_example(rows: int = 3, keys: int = 64, depth: int = 32, inplace_denominator: bool = False, seed: int = 7,

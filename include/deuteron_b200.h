@@ -88,6 +88,23 @@ int dtn_add_f32(const float* x, const float* y, float* out, int64_t n, void* str
  * ex2.approx(x*log2(e)) and rcp/rsqrt the approximate forms, as approximate_math=True does. */
 int dtn_elementwise_f32(int op, const float* x, const float* y, float* out, int64_t n, void* stream);
 
+/* A chain of elementwise operators over f16 / f32 buffers in one pass: out[i] = program(inputs[..][i]).
+ * Replaces the kernels the reference emits for Load / Assign... / Write tiles with more than one
+ * operator, among them the f16 storage "affine" and "cancellation" kernels of
+ * examples/f16_storage.py:36-54 (typing rules compiler/storage.py:27-58: arithmetic only in explicit
+ * FP32, conversion at the load and at the store, Lowering.convert compiler/codegen/lower.py:249-256).
+ *   inputs[k] (host array of n_inputs device pointers) fills register k: f16 (input_f16[k] = 1) or
+ *   f32, a buffer of n elements or, with input_scalar[k] = 1, one element that is broadcast.
+ *   Instruction j computes register dsts[j] = ops[j](register as[j], register bs[j]) (DTN_EW_* codes,
+ *   unary operators ignore bs[j]); 8 registers, at most 24 instructions, each operator rounds once in
+ *   FP32 (no fused multiply-add). Register out_reg is stored to out[i] as f32, or narrowed to f16
+ *   (round-to-nearest-even) when out_f16 = 1. ops/dsts/as/bs/input_f16/input_scalar are host arrays.
+ * Pointers need only their natural alignment. */
+int dtn_elementwise_program(const unsigned char* ops, const unsigned char* dsts, const unsigned char* as,
+                            const unsigned char* bs, int n_instr, const void* const* inputs,
+                            const unsigned char* input_f16, const unsigned char* input_scalar,
+                            int n_inputs, int out_reg, void* out, int out_f16, int64_t n, void* stream);
+
 /* f16 storage kernels (compiler/storage.py:5-59, Lowering.convert compiler/codegen/lower.py:249-256,
  * shapes of examples/f16_storage.py:19-60). f16 values travel as uint16_t bit patterns.
  *   copy  : bit-preserving 16-bit move
@@ -187,7 +204,8 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
                 int64_t group_begin, int64_t group_end, void* stream);
 
 /* Selects the attention kernel: 0 = automatic, 1 = FP32 CUDA-core kernel,
- * 2 = tensor-core kernel (f16 storage, D = 128). No reference counterpart. */
+ * 2 = tensor-core kernel (f16 storage, D = 128, S a multiple of 256), 3 = the same with two
+ * softmax warpgroups per query tile. No reference counterpart. */
 int dtn_gqa_set_variant(int variant);
 
 #ifdef __cplusplus

@@ -296,3 +296,17 @@ def row_sum_error_bound(x: np.ndarray) -> np.ndarray:
     """Bound on |fp32 tree sum - exact| per row for any summation order: (n-1) * eps * sum|x|."""
     x64 = np.abs(np.asarray(x, dtype=np.float64))
     return (x.shape[1] - 1) * np.finfo(np.float32).eps * x64.sum(axis=1)
+
+
+def f16_affine(x: np.ndarray, scale: float = 1.5, bias: float = -0.25) -> np.ndarray:
+    """examples/f16_storage.py:79-82: f16(f32(x) * scale + bias), each operator rounded once in FP32."""
+    widened = np.asarray(x, dtype=np.float16).astype(np.float32)
+    return (widened * np.float32(scale) + np.float32(bias)).astype(np.float32).astype(np.float16)
+
+
+def f16_cancellation(x: np.ndarray, y: np.ndarray) -> np.ndarray:
+    """examples/f16_storage.py:83-84: f16((f32(x) + f32(y)) - f32(x)): the sum is kept in FP32, never rounded to f16."""
+    a = np.asarray(x, dtype=np.float16).astype(np.float32)
+    b = np.asarray(y, dtype=np.float16).astype(np.float32)
+    with np.errstate(over='ignore'):
+        return ((a + b) - a).astype(np.float16)

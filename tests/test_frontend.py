@@ -63,6 +63,12 @@ def test_generated_schedules_classify(golden):
         (schedules.f16_storage_example('copy', 512, 1), 'f16_copy', {'n': 512}),
         (schedules.f16_storage_example('widen', 512, 2), 'f16_widen', {'n': 512}),
         (schedules.f16_storage_example('narrow', 512, 4, offset=1), 'f16_narrow', {'n': 512}),
+        (schedules.f16_storage_example('affine', 512, 4), 'elementwise_program',
+         {'n': 512, 'inputs': [{'f16': True, 'scalar': False}, {'f16': False, 'scalar': True}, {'f16': False, 'scalar': True}],
+          'out_reg': 0, 'out_f16': True, 'ops': [2, 0], 'dst': [0, 0], 'a': [0, 0], 'b': [1, 2]}),
+        (schedules.f16_storage_example('cancellation', 512, 2), 'elementwise_program',
+         {'n': 512, 'inputs': [{'f16': True, 'scalar': False}, {'f16': True, 'scalar': False}], 'out_reg': 0, 'out_f16': True,
+          'ops': [0, 1], 'dst': [1, 0], 'a': [0, 1], 'b': [1, 0]}),
         (schedules.attention_example(9, 256, 64, True), 'attention', {'rows': 9, 'keys': 256, 'depth': 64, 'cols': 32, 'scale': 0.125}),
         (schedules.row_reduce_example(64, 512, 'sum'), 'row_reduce', {'op': 'sum', 'rows': 64, 'cols': 512}),
         (schedules.row_reduce_example(8, 4096, 'max'), 'row_reduce', {'op': 'max', 'rows': 8, 'cols': 4096}),

@@ -70,11 +70,48 @@ def test_vector_add_example_is_exact_and_hashes_to_the_reference_output(runner, 
 
 
 def test_f16_examples_hash_to_the_reference_outputs(runner, published):
-    for kind in ('copy', 'widen', 'narrow'):
-        graph, meta = schedules.f16_storage_example(kind)
-        compiled = compile_kernel(graph, meta)
-        produced = runner.run_kernel(meta['kernels'][0], compiled, warmup=0, iters=1, samples=1)['outputs']['result']
-        assert sha(produced) == published['results'][kind]['output_sha256']['result'], kind
+    for kind in ('copy', 'widen', 'narrow', 'affine', 'cancellation'):
+        for width in (4, 1):
+            graph, meta = schedules.f16_storage_example(kind, width=width)
+            compiled = compile_kernel(graph, meta)
+            produced = runner.run_kernel(meta['kernels'][0], compiled, warmup=0, iters=1, samples=1)['outputs']['result']
+            assert sha(produced) == published['results'][kind]['output_sha256']['result'], kind
+
+
+def test_explicit_float_compute_avoids_half_intermediate_rounding(runner):
+    # tests/test_f16_storage.py:150-155
+    graph, meta = schedules.f16_storage_example('cancellation')
+    x = np.resize(np.array([2048., 4096., 65504., -2048.], dtype=np.float16), 512)
+    y = np.ones(512, dtype=np.float16)
+    actual = run_with_data(runner, graph, meta, {'x': x, 'y': y})['result']
+    np.testing.assert_array_equal(actual, y)
+
+
+def test_fused_elementwise_programs_at_size_and_misalignment(runner, cuda):
+    # large, odd-sized and offset buffers through the same compile/launch surface
+    count = 1_000_004
+    for kind, oracle in (('affine', lambda x, y: R.f16_affine(x)), ('cancellation', R.f16_cancellation)):
+        for offset in (0, 1):
+            if kind == 'cancellation' and offset:
+                continue
+            graph, meta = schedules.f16_storage_example(kind, count=count, width=4, offset=offset)
+            x = R.seeded_normal(3, (count + offset,), np.float16, 30.0)
+            y = R.seeded_normal(4, (count,), np.float16, 30.0)
+            produced = run_with_data(runner, graph, meta, {'x': x, 'y': y})['result']
+            np.testing.assert_array_equal(produced.view(np.uint16), oracle(x[offset:], y).view(np.uint16))
+    # a longer chain on f32 buffers: relu(x * y + x) - |y|, then exp
+    from deuteron_b200 import native
+    n = 70_003
+    x, y = R.seeded_normal(1, (n,)), R.seeded_normal(2, (n,))
+    dx, dy = to_device(cuda, x), to_device(cuda, y)
+    out = cuda.empty(n, device='cuda:0')
+    ops_ = native.ELEMENTWISE_OPS
+    program = {'ops': [ops_['multiply'], ops_['add'], ops_['relu'], ops_['absolute'], ops_['subtract']],
+               'dst': [2, 2, 2, 3, 2], 'a': [0, 2, 2, 1, 2], 'b': [1, 0, 2, 1, 3], 'out_reg': 2, 'out_f16': False, 'n': n,
+               'inputs': [{'f16': False, 'scalar': False}, {'f16': False, 'scalar': False}]}
+    native.elementwise_program(program, [dx.data_ptr(), dy.data_ptr()], out.data_ptr(), cuda.cuda.current_stream().cuda_stream)
+    expected = np.maximum((x * y).astype(np.float32) + x, 0).astype(np.float32) - np.abs(y)
+    np.testing.assert_array_equal(out.cpu().numpy(), expected)
 
 
 def test_all_half_bits_copy_exactly_at_scalar_and_vector_widths(runner):
@@ -418,12 +455,15 @@ def gqa_error_bound(keys, tensor_core):
     return 3e-6 + (2 * keys / 16) * 2.0 ** -24 if tensor_core else 3e-6
 
 
-@pytest.mark.parametrize('variant', [0, 1])
+@pytest.mark.parametrize('variant', [0, 1, 3])   # automatic, all-FP32, tensor core with two warpgroups per tile
 @pytest.mark.parametrize('storage', [np.float16, np.float32])
 def test_gqa_attention_against_float64(cuda, storage, variant):
     ops.set_gqa_variant(variant)
     try:
         for batch, hq, hkv, s, d in GQA_CASES:
+            eligible = storage == np.float16 and d == 128 and s % 256 == 0
+            if variant == 3 and not eligible:
+                continue
             scale = float(np.float32(1 / math.sqrt(d)))
             q = R.seeded_normal(7, (batch, hq, s, d), storage, scale)
             k = R.seeded_normal(8, (batch, hkv, s, d), storage, scale)
@@ -432,7 +472,7 @@ def test_gqa_attention_against_float64(cuda, storage, variant):
             ops.check_device_status()
             exact = R.gqa_attention_f64(q, k, v, scale)
             np.testing.assert_allclose(produced, exact, rtol=1e-3, atol=1e-4)
-            tensor_core = variant == 0 and storage == np.float16 and d == 128 and s % 256 == 0
+            tensor_core = variant != 1 and eligible
             assert R.max_relative_error(produced, exact) <= gqa_error_bound(s, tensor_core), (batch, hq, hkv, s, d)
     finally:
         ops.set_gqa_variant(0)

@@ -35,6 +35,16 @@ def test_f16_conversions_reproduce_published_output_hashes(published):
     assert sha(R.f16_narrow_bits(single)) == results['narrow']['output_sha256']['result']
 
 
+def test_f16_fused_expressions_reproduce_published_output_hashes(published):
+    # examples/f16_storage.py affine (scale 1.5, bias -0.25) and cancellation (y from seed 8)
+    x, y = R.seeded_normal(7, (512,), np.float16), R.seeded_normal(8, (512,), np.float16)
+    assert sha(R.f16_affine(x)) == published['results']['affine']['output_sha256']['result']
+    assert sha(R.f16_cancellation(x, y)) == published['results']['cancellation']['output_sha256']['result']
+    # tests/test_f16_storage.py:150-155: the FP32 intermediate keeps the small addend
+    big = np.resize(np.array([2048., 4096., 65504., -2048.], dtype=np.float16), 512)
+    np.testing.assert_array_equal(R.f16_cancellation(big, np.ones(512, np.float16)), np.ones(512, np.float16))
+
+
 def test_f16_narrow_bits_equal_numpy_on_every_rounding_boundary():
     points = R.f16_boundary_points()
     assert points.size == 190468
