@@ -39,6 +39,10 @@ sys.path.insert(0, str(ROOT))
 M = N = K = 8192
 FLOPS_PER_GEMM = 2.0 * M * N * K
 WORKLOAD = 'gemm_bf16x3_8192x8192x8192_f32io'
+# dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of the product kernel, from the ncu capture
+# summarised in profiles/gemm_x3_kernel_bf16_8192_dram.md (2.32 GB read + 0.26 GB written)
+PRODUCT_KERNEL_DRAM_BYTES = 2.58e9
+PRODUCT_KERNEL_ALGORITHMIC_BYTES = 4 * M * K * 2 + 4 * M * N   # four bf16 planes read once + C written once
 
 
 def measured_peaks() -> dict:
@@ -183,6 +187,14 @@ def extras(torch, ops, peaks: dict) -> dict:
     c = torch.empty((M, N), device=device)
     ms = timed(torch, lambda: ops.gemm(a, b, 'tf32x3', out=c), 5)
     out['gemm_tf32x3_8192'] = {'ms': ms, 'tflops': FLOPS_PER_GEMM / ms / 1e9}
+    # The pool's measured peaks have no TF32 figure: time the library TF32 GEMM here as that denominator.
+    previous = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    library_ms = timed(torch, lambda: torch.matmul(a, b, out=c), 5)
+    torch.backends.cuda.matmul.allow_tf32 = previous
+    tf32_peak = FLOPS_PER_GEMM / library_ms / 1e9
+    out['gemm_tf32x3_8192'].update({'library_tf32_gemm_tflops': tf32_peak,
+                                    'frac_of_library_tf32_peak_over_3': out['gemm_tf32x3_8192']['tflops'] / (tf32_peak / 3)})
     del a, b, c
     n = 1 << 28
     x = torch.randn(n, device=device, generator=generator)
@@ -331,7 +343,9 @@ def run_ours(args) -> None:
                        'l2': 'inputs (512 MiB) and operand planes (512 MiB) exceed the 126 MB L2; no flush between steps',
                        'step': 'operand split (2 kernels) + tcgen05 product kernel (1 kernel)'},
             'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak,
-                         'traffic': None, 'kernel': 'gemm_x3_kernel (product kernel only)', 'ms_per_launch': product_ms,
+                         'traffic': PRODUCT_KERNEL_DRAM_BYTES, 'traffic_note': 'bytes per launch from the committed ncu capture; algorithmic '
+                         f'bytes per launch {PRODUCT_KERNEL_ALGORITHMIC_BYTES:.3e} (planes re-read 4x, DRAM at 20 % of its peak)',
+                         'kernel': 'gemm_x3_kernel (product kernel only)', 'ms_per_launch': product_ms,
                          'split_ms_per_step': split_ms,
                          'peak_source': f"{peaks['source']} dense bf16 burst peak {peaks['bf16_tflops']} TFLOP/s / 3 products"},
             'clocks': clocks,

@@ -16,6 +16,8 @@
 // shared between CTAs by multicast).
 #include <cuda.h>
 
+#include <stdlib.h>
+
 #include <mutex>
 
 #include "dtn_common.cuh"
@@ -137,7 +139,7 @@ split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, i
 // ---------------------------------------------------------------------------------------
 constexpr int kGemmThreads = 192;  // warp 0: TMA, warp 1: MMA + tensor-memory owner, warps 2-5: epilogue
 constexpr int kTileRowBytes = 128; // one swizzle row = one k-block of either kind
-constexpr int kGroupM = 8;         // m-tiles per raster group (L2 reuse of the B planes)
+constexpr int kDefaultGroupM = 8;  // m-tiles per raster group (L2 reuse of the B planes)
 
 template <int CTAS, int BN>
 struct GemmCfg {
@@ -153,11 +155,11 @@ struct GemmCfg {
   static_assert(kTmemCols == 256 || kTmemCols == 512, "tensor memory columns must be a power of two");
 };
 
-__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int per_group = kGroupM * tiles_n;
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
+  const int per_group = group_m * tiles_n;
   const int g = t / per_group;
-  const int first = g * kGroupM;
-  const int gsize = min(kGroupM, tiles_m - first);
+  const int first = g * group_m;
+  const int gsize = min(group_m, tiles_m - first);
   const int r = t - g * per_group;
   tm = first + r % gsize;
   tn = r / gsize;
@@ -168,7 +170,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
                const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
                float* __restrict__ C, int64_t ldc, int M, int N, int num_kb, int tiles_m, int tiles_n,
-               int c_vec_ok, int* __restrict__ status) {
+               int group_m, int c_vec_ok, int* __restrict__ status) {
   using Cfg = GemmCfg<CTAS, BN>;
   constexpr int kStages = Cfg::kStages;
   constexpr int kBlockKElems = (KIND == 0) ? 64 : 32;
@@ -230,7 +232,7 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
       const uint32_t leader_full0 = (CTAS == 2) ? ptx::map_to_cta(full_bar(0), 0) : full_bar(0);
       for (int t = unit; t < num_tiles && ok; t += num_units) {
         int tm, tn;
-        tile_coords(t, tiles_m, tiles_n, tm, tn);
+        tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
         const int row_a = tm * (128 * CTAS) + (int)rank * 128;
         const int row_b = tn * BN + (int)rank * Cfg::kBnLoad;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -318,7 +320,7 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
       const int acc = iter & 1;
       const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
       int tm, tn;
-      tile_coords(t, tiles_m, tiles_n, tm, tn);
+      tile_coords(t, tiles_m, tiles_n, group_m, tm, tn);
       const bool ready = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) {  // leave together: the loads below are warp-wide
         if (lane == 0) atomicExch(status, 0x400 | (int)(blockIdx.x & 0xff));
@@ -414,6 +416,16 @@ static int make_plane_map(CUtensorMap* map, const void* base, int elem_bytes, in
 
 static int g_gemm_variant = 0;
 
+// m-tiles per raster group. DTN_GEMM_GROUP_M overrides the default for experiments.
+static int raster_group_m() {
+  static int value = [] {
+    const char* text = getenv("DTN_GEMM_GROUP_M");
+    const int parsed = text ? atoi(text) : 0;
+    return parsed > 0 && parsed <= 64 ? parsed : kDefaultGroupM;
+  }();
+  return value;
+}
+
 struct PlaneLayout {
   int64_t Kp;
   size_t a_plane, b_plane;  // bytes of one plane, rounded to 1024
@@ -478,7 +490,7 @@ static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, C, ldc, (int)M, (int)N, num_kb,
-                                    tiles_m, tiles_n, c_vec_ok, status));
+                                    tiles_m, tiles_n, raster_group_m(), c_vec_ok, status));
   return DTN_OK;
 }
 
