@@ -142,6 +142,9 @@ def _classify_attention(tile: ir.Node, specs: dict) -> Plan | None:
         return None
     dot_axis = inner[0].axis.name
     q = kt = v = None
+    ranks = {len(load.index) for load in statements if load.kind == 'Load' and math.prod(_shape(specs, load.input)) != 1}
+    if ranks == {4}:
+        return _classify_gqa(tile, outer[0], inner[0], specs)
     for load in (s for s in inner[0].body if s.kind == 'Load'):
         if len(load.index) != 2:
             return None
@@ -165,6 +168,58 @@ def _classify_attention(tile: ir.Node, specs: dict) -> Plan | None:
     for name in (q, kt, v, out):
         if specs[name]['dtype'] != 'f32':
             raise NotImplementedError('the attention recurrence takes f32 buffers')
+    scale = _attention_scale(tile, outer[0], inner[0], specs)
+    if scale is None:
+        return None
+    return Plan('attention', {'rows': rows, 'keys': keys, 'depth': depth, 'cols': cols, 'scale': scale},
+                {'q': (q, 0), 'kt': (kt, 0), 'v': (v, 0), 'out': (out, 0)})
+
+
+def _classify_gqa(tile: ir.Node, outer: ir.Node, inner: ir.Node, specs: dict) -> Plan | None:
+    """The same recurrence over [batch, head, position, depth] buffers with grouped key/value heads:
+    q[B,Hq,S,D], k[B,Hkv,S,D], v[B,Hkv,S,D] -> out[B,Hq,S,D], the key/value head of query head h being
+    h / (Hq / Hkv). The reference's own attention IR is the single-head 2-D form; this 4-D form is how the
+    batched grouped-query workload is written against the same statement vocabulary. Operands may be f16
+    (widened by `copy` Assigns) or f32; the output is f32."""
+    key_axis, dot_axis = outer.axis.name, inner.axis.name
+    q = k = v = None
+    for load in (s for s in inner.body if s.kind == 'Load'):
+        if len(load.index) != 4:
+            return None
+        position, depth = ir.expression_vars(load.index[2]), ir.expression_vars(load.index[3])
+        if dot_axis not in depth:
+            return None
+        if key_axis in position:
+            k = load.input
+        else:
+            q = load.input
+    for load in (s for s in outer.body if s.kind == 'Load'):
+        if len(load.index) == 4 and key_axis in ir.expression_vars(load.index[2]):
+            v = load.input
+    writes = [s for s in tile.body if s.kind == 'Write']
+    if None in (q, k, v) or len(writes) != 1 or len(writes[0].index) != 4:
+        return None
+    out = writes[0].output
+    (batch, hq, s, d), k_shape, v_shape = _shape(specs, q), _shape(specs, k), _shape(specs, v)
+    if k_shape != v_shape or k_shape[0] != batch or k_shape[2:] != (s, d) or _shape(specs, out) != (batch, hq, s, d):
+        raise ValueError('grouped-query attention buffer shapes disagree')
+    hkv = k_shape[1]
+    if hkv == 0 or hq % hkv:
+        raise ValueError('query heads must be a multiple of key/value heads')
+    if outer.axis.extent.value != s or inner.axis.extent.value != d:
+        raise ValueError('attention loop extents disagree with the buffer shapes')
+    storage = {specs[name]['dtype'] for name in (q, k, v)}
+    if len(storage) != 1 or specs[out]['dtype'] != 'f32':
+        raise NotImplementedError('grouped-query attention takes q, k, v of one storage type and an f32 output')
+    scale = _attention_scale(tile, outer, inner, specs)
+    if scale is None:
+        return None
+    return Plan('gqa', {'batch': batch, 'hq': hq, 'hkv': hkv, 's': s, 'd': d, 'scale': scale, 'storage': storage.pop()},
+                {'q': (q, 0), 'k': (k, 0), 'v': (v, 0), 'out': (out, 0)})
+
+
+def _attention_scale(tile: ir.Node, outer_loop: ir.Node, inner_loop: ir.Node, specs: dict) -> float | None:
+    outer, inner = [outer_loop], [inner_loop]
     # the uniform score scale: a Let literal that multiplies the score, or a one-element data buffer
     # the score is multiplied or divided by
     scale = None
@@ -191,10 +246,7 @@ def _classify_attention(tile: ir.Node, specs: dict) -> Plan | None:
                 value = 1.0 / value
             scale = value
             break
-    if scale is None:
-        scale = 1.0
-    return Plan('attention', {'rows': rows, 'keys': keys, 'depth': depth, 'cols': cols, 'scale': scale},
-                {'q': (q, 0), 'kt': (kt, 0), 'v': (v, 0), 'out': (out, 0)})
+    return 1.0 if scale is None else scale
 
 
 # ------------------------------------------------------------------------------------------------

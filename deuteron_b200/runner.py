@@ -156,6 +156,11 @@ class LocalRunner:
         elif kind == 'attention':
             native.call('dtn_attention_f32', ptr('q', 4), ptr('kt', 4), ptr('v', 4), ptr('out', 4), p['rows'], p['keys'],
                         p['depth'], p['cols'], float(np.float32(p['scale'])), stream)
+        elif kind == 'gqa':
+            size = 2 if p['storage'] == 'f16' else 4
+            native.call('dtn_gqa_fwd', ptr('q', size), ptr('k', size), ptr('v', size), ptr('out', 4), p['batch'], p['hq'],
+                        p['hkv'], p['s'], p['d'], float(np.float32(p['scale'])), native.STORAGE[p['storage']], 0,
+                        p['batch'] * p['hkv'], stream)
         else:
             raise NotImplementedError(f'no launcher for plan kind {kind}')
 

@@ -309,3 +309,66 @@ def matmul_example(m: int = 128, n: int = 128, k: int = 128, seeds=(7, 11)) -> t
                        {'name': 'left', 'dtype': 'f32', 'shape': [m, k], 'seed': seeds[0]},
                        {'name': 'result', 'dtype': 'f32', 'shape': [m, n], 'output': True}], 'final': True}
     return graph, _metadata('tensor_matmul', launch, 0.001, 0.001, ['left', 'right'], ['result'])
+
+
+def gqa_attention_example(batch: int = 4, query_heads: int = 32, kv_heads: int = 8, positions: int = 4096, depth: int = 128,
+                          storage: str = 'f16', seed: int = 7) -> tuple[dict, dict]:
+    """Grouped-query attention forward, non-causal, in the statement vocabulary of examples/attention.py.
+
+    q[B,Hq,S,D], k[B,Hkv,S,D], v[B,Hkv,S,D] in `storage` ('f16' or 'f32'), out[B,Hq,S,D] f32; query head h
+    reads key/value head h / (Hq / Hkv). The body is the reference example's online-softmax chain with
+    four-dimensional indices; f16 operands are widened by `copy` Assigns before any arithmetic, every
+    arithmetic statement is FP32. (The reference's own backend declines f16 buffers in a recurrence,
+    compiler/storage.py:29-30; this form is the batched workload written against the same IR.)
+    One thread block per (batch, head, row), one thread per output column, like the example.
+    """
+    if storage not in ('f16', 'f32') or min(batch, query_heads, kv_heads, positions, depth) <= 0 or query_heads % kv_heads:
+        raise ValueError('unsupported grouped-query attention configuration')
+    dtype = F16 if storage == 'f16' else F32
+    ratio = query_heads // kv_heads
+    kv_head = binary('/', var('head'), lit(ratio))
+
+    def widened(name: str, source: str, index) -> list[str]:
+        if storage == 'f32':
+            return [load((name,), source, index)]
+        return [load((name + '_stored',), source, index, dtype), assign(name, 'copy', (name + '_stored',))]
+
+    dot = loop(axis('dot', depth), [
+        *widened('query', 'q', [var('batch'), var('head'), var('row'), var('dot')]),
+        *widened('key_value', 'k', [var('batch'), kv_head, var('key'), var('dot')]),
+        assign('product', 'multiply', ('query', 'key_value')),
+        accum('score_sum', 'product', 'add', ('dot',)),
+    ])
+    outer = loop(axis('key', positions), [
+        dot,
+        assign('score', 'multiply', ('score_sum', 'scale')),
+        assign('next_maximum', 'maximum', ('maximum', 'score')),
+        assign('old_delta', 'subtract', ('maximum', 'next_maximum')),
+        assign('alpha', 'exp', ('old_delta',)),
+        assign('new_delta', 'subtract', ('score', 'next_maximum')),
+        assign('beta', 'exp', ('new_delta',)),
+        assign('mass_carry', 'multiply', ('mass', 'alpha')),
+        accum('mass', 'beta', 'add', ('key',), 'mass_carry'),
+        assign('weighted_carry', 'multiply', ('weighted', 'alpha')),
+        *widened('value', 'v', [var('batch'), kv_head, var('key'), var('column')]),
+        assign('weighted_new', 'multiply', ('value', 'beta')),
+        accum('weighted', 'weighted_new', 'add', ('key',), 'weighted_carry'),
+        accum('maximum', 'score', 'maximum', ('key',)),
+    ])
+    scale = float(np.float32(1 / math.sqrt(depth)))
+    body = tile([axis('batch', batch), axis('head', query_heads), axis('row', positions), axis('column', depth)], [
+        f"Let(name='scale', value={lit(scale)}, dtype={F32})",
+        outer,
+        assign('inverse', 'reciprocal', ('mass',)),
+        assign('normalized', 'multiply', ('weighted', 'inverse')),
+        write('out', [var('batch'), var('head'), var('row'), var('column')], ('normalized',)),
+    ], depth)
+    shapes = {'q': [batch, query_heads, positions, depth], 'k': [batch, kv_heads, positions, depth],
+              'v': [batch, kv_heads, positions, depth], 'out': [batch, query_heads, positions, depth]}
+    entry = 'gqa_attention'
+    graph = _graph(entry, body, {name: (shapes[name], storage) for name in ('q', 'k', 'v')}, ('out', shapes['out'], 'f32'))
+    args = [{'name': name, 'dtype': storage, 'shape': shapes[name], 'seed': seed + i} for i, name in enumerate(('q', 'k', 'v'))]
+    args.append({'name': 'out', 'dtype': 'f32', 'shape': shapes['out'], 'output': True})
+    launch = {'node': 'out', 'entry': entry, 'arg_order': ['q', 'k', 'v', 'out'], 'grid': [batch * query_heads * positions, 1, 1],
+              'block': [depth, 1, 1], 'smem_bytes': 0, 'zero_outputs': [], 'args': args, 'final': True}
+    return graph, _metadata(entry, launch, 0.001, 0.0001, ['q', 'k', 'v'], ['out'])

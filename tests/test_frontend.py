@@ -70,6 +70,10 @@ def test_generated_schedules_classify(golden):
          {'n': 512, 'inputs': [{'f16': True, 'scalar': False}, {'f16': True, 'scalar': False}], 'out_reg': 0, 'out_f16': True,
           'ops': [0, 1], 'dst': [1, 0], 'a': [0, 1], 'b': [1, 0]}),
         (schedules.attention_example(9, 256, 64, True), 'attention', {'rows': 9, 'keys': 256, 'depth': 64, 'cols': 32, 'scale': 0.125}),
+        (schedules.gqa_attention_example(4, 32, 8, 4096, 128, 'f16'), 'gqa',
+         {'batch': 4, 'hq': 32, 'hkv': 8, 's': 4096, 'd': 128, 'scale': 0.0883883461356163, 'storage': 'f16'}),
+        (schedules.gqa_attention_example(1, 6, 2, 100, 64, 'f32'), 'gqa',
+         {'batch': 1, 'hq': 6, 'hkv': 2, 's': 100, 'd': 64, 'scale': 0.125, 'storage': 'f32'}),
         (schedules.row_reduce_example(64, 512, 'sum'), 'row_reduce', {'op': 'sum', 'rows': 64, 'cols': 512}),
         (schedules.row_reduce_example(8, 4096, 'max'), 'row_reduce', {'op': 'max', 'rows': 8, 'cols': 4096}),
         (schedules.row_reduce_example(8, 4096, 'sumsq'), 'row_reduce', {'op': 'sumsq', 'rows': 8, 'cols': 4096}),

@@ -478,6 +478,23 @@ def test_gqa_attention_against_float64(cuda, storage, variant):
         ops.set_gqa_variant(0)
 
 
+def test_gqa_through_the_compile_and_launch_surface(cuda, runner):
+    # scheduled IR with [batch, head, position, depth] buffers -> the native grouped-query kernels
+    for storage, s, d in (('f16', 512, 128), ('f32', 300, 64)):
+        graph, meta = schedules.gqa_attention_example(2, 4, 2, s, d, storage)
+        compiled = compile_kernel(graph, meta, arch='sm_100a')
+        assert compiled.plan.kind == 'gqa'
+        scale = float(np.float32(1 / math.sqrt(d)))
+        dtype = np.float16 if storage == 'f16' else np.float32
+        q, k, v = (R.seeded_normal(7 + i, shape, dtype) for i, shape in enumerate(((2, 4, s, d), (2, 2, s, d), (2, 2, s, d))))
+        result = runner.run_kernel(meta['kernels'][0], compiled, warmup=1, iters=2, samples=1)
+        exact = R.gqa_attention_f64(q, k, v, scale)
+        np.testing.assert_allclose(result['outputs']['out'], exact, rtol=meta['rtol'], atol=meta['atol'])
+        assert R.max_relative_error(result['outputs']['out'], exact) <= gqa_error_bound(s, storage == 'f16')
+        hosted = runner.execute(compiled, {'q': q, 'k': k, 'v': v})['out']
+        np.testing.assert_array_equal(hosted, result['outputs']['out'])
+
+
 def test_gqa_group_ranges_partition_the_output(cuda):
     from deuteron_b200 import sharding
     batch, hq, hkv, s, d = 2, 8, 2, 256, 128
