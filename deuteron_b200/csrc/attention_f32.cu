@@ -89,6 +89,146 @@ attention_rows_kernel(const float* __restrict__ q, const float* __restrict__ kt,
     if (lane + 32 * c < cols) out[(int64_t)row * cols + lane + 32 * c] = acc[c] * inv;
 }
 
+// Same computation with the key and value stages held in shared memory: the CTA's threads fetch a
+// stage of SK keys (kt[:, k0:k0+SK] and v[k0:k0+SK, :]) together, then each warp runs the staged
+// recurrence of its row out of shared memory. Small problems (the reference's example shapes) are
+// latency-bound, and this turns a chain of dependent global loads per row into one round trip per stage.
+template <int SK, int CG /*value-column groups of 32 per lane*/>
+__global__ void __launch_bounds__(kRowWarps * 32)
+attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ kt, const float* __restrict__ v,
+                        float* __restrict__ out, int rows, int keys, int depth, int cols, float scale) {
+  extern __shared__ __align__(16) float asm_[];
+  float* kts = asm_;                         // [depth][SK]
+  float* vs = kts + (size_t)depth * SK;      // [SK][cols]
+  float* qs = vs + (size_t)SK * cols;        // [kRowWarps][depth]
+  float* ws = qs + kRowWarps * depth;        // [kRowWarps][SK]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
+  const int row = blockIdx.x * kRowWarps + warp;
+  const bool active = row < rows;
+  for (int i = tid; i < kRowWarps * depth; i += kRowWarps * 32) {
+    const int r = blockIdx.x * kRowWarps + i / depth;
+    qs[i] = r < rows ? __ldg(q + (int64_t)r * depth + i % depth) : 0.f;
+  }
+  float acc[CG];
+#pragma unroll
+  for (int c = 0; c < CG; ++c) acc[c] = 0.f;
+  float run_max = -INFINITY, mass = 0.f;
+  constexpr int kRounds = SK / 32;
+  // vector loads need 16-byte aligned rows of kt and stages of v
+  const bool vec_ok = ((reinterpret_cast<uintptr_t>(kt) | reinterpret_cast<uintptr_t>(v)) & 15) == 0 && keys % 4 == 0 &&
+                      (SK * cols) % 4 == 0 && (depth * SK) % 4 == 0;
+
+  for (int k0 = 0; k0 < keys; k0 += SK) {
+    const int stage_keys = min(SK, keys - k0);
+    __syncthreads();   // the previous stage is no longer read (and qs is written before the first use)
+    const float* v_stage = v + (int64_t)k0 * cols;
+    const int v_count = stage_keys * cols;
+    if (vec_ok && stage_keys == SK) {
+      // 128-bit loads, all of a thread's loads in flight before the first store
+      constexpr int kPerRow = SK / 4;
+#pragma unroll 4
+      for (int i = tid; i < depth * kPerRow; i += kRowWarps * 32) {
+        const int d = i / kPerRow, k4 = i % kPerRow;
+        const float4 x = __ldg(reinterpret_cast<const float4*>(kt + (int64_t)d * keys + k0) + k4);
+        *reinterpret_cast<float4*>(kts + d * SK + 4 * k4) = x;
+      }
+#pragma unroll 4
+      for (int i = tid; i < v_count / 4; i += kRowWarps * 32)
+        *reinterpret_cast<float4*>(vs + 4 * i) = __ldg(reinterpret_cast<const float4*>(v_stage) + i);
+    } else {
+#pragma unroll 8
+      for (int i = tid; i < depth * SK; i += kRowWarps * 32) {
+        const int d = i / SK, k = i % SK;
+        kts[i] = k < stage_keys ? __ldg(kt + (int64_t)d * keys + k0 + k) : 0.f;
+      }
+#pragma unroll 8
+      for (int i = tid; i < v_count; i += kRowWarps * 32) vs[i] = __ldg(v_stage + i);
+    }
+    __syncthreads();
+    if (active) {
+      float s[kRounds];
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) s[r] = 0.f;
+      const float* qrow = qs + warp * depth;
+      for (int d = 0; d < depth; ++d) {
+        const float qv = qrow[d];
+        const float* kr = kts + d * SK + lane;
+#pragma unroll
+        for (int r = 0; r < kRounds; ++r) s[r] = fmaf(qv, kr[32 * r], s[r]);
+      }
+      float local_max = -INFINITY;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        s[r] = (lane + 32 * r < stage_keys) ? s[r] * scale : -INFINITY;
+        local_max = fmaxf(local_max, s[r]);
+      }
+      const float new_max = fmaxf(run_max, warp_max(local_max));
+      const float alpha = (run_max == -INFINITY) ? 0.f : ex2_approx((run_max - new_max) * kLog2e);
+      float local_mass = 0.f;
+#pragma unroll
+      for (int r = 0; r < kRounds; ++r) {
+        const float w = (lane + 32 * r < stage_keys) ? ex2_approx((s[r] - new_max) * kLog2e) : 0.f;
+        ws[warp * SK + lane + 32 * r] = w;
+        local_mass += w;
+      }
+      mass = mass * alpha + warp_sum(local_mass);
+      run_max = new_max;
+      __syncwarp();
+#pragma unroll
+      for (int c = 0; c < CG; ++c) acc[c] *= alpha;
+      const float* wrow = ws + warp * SK;
+      for (int k = 0; k < stage_keys; ++k) {
+        const float w = wrow[k];
+        const float* vr = vs + k * cols + lane;
+#pragma unroll
+        for (int c = 0; c < CG; ++c)
+          if (lane + 32 * c < cols) acc[c] = fmaf(w, vr[32 * c], acc[c]);
+      }
+    }
+  }
+  if (active) {
+    const float inv = rcp_approx(mass);
+#pragma unroll
+    for (int c = 0; c < CG; ++c)
+      if (lane + 32 * c < cols) out[(int64_t)row * cols + lane + 32 * c] = acc[c] * inv;
+  }
+}
+
+static size_t staged_smem_bytes(int sk, int64_t depth, int64_t cols) {
+  return sizeof(float) * ((size_t)depth * sk + (size_t)sk * cols + (size_t)kRowWarps * depth + (size_t)kRowWarps * sk);
+}
+
+template <int SK, int CG>
+static int attention_staged_launch_cg(const float* q, const float* kt, const float* v, float* out, int64_t rows, int64_t keys,
+                                   int64_t depth, int64_t cols, float scale, cudaStream_t s) {
+  const size_t smem = staged_smem_bytes(SK, depth, cols);
+  auto kernel = attention_staged_kernel<SK, CG>;
+  static thread_local int attr_dev = -1;
+  static thread_local size_t attr_bytes = 0;
+  int dev = 0;
+  DTN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (smem > 48 * 1024 && (attr_dev != dev || attr_bytes < smem)) {
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr_dev = dev;
+    attr_bytes = 200 * 1024;
+  }
+  const int64_t blocks = (rows + kRowWarps - 1) / kRowWarps;
+  kernel<<<(unsigned)blocks, kRowWarps * 32, smem, s>>>(q, kt, v, out, (int)rows, (int)keys, (int)depth, (int)cols, scale);
+  DTN_LAUNCH_CHECK("attention_staged_kernel");
+  return DTN_OK;
+}
+
+template <int SK>
+static int attention_staged_launch(const float* q, const float* kt, const float* v, float* out, int64_t rows, int64_t keys,
+                                   int64_t depth, int64_t cols, float scale, cudaStream_t s) {
+  if (cols <= 32) return attention_staged_launch_cg<SK, 1>(q, kt, v, out, rows, keys, depth, cols, scale, s);
+  if (cols <= 64) return attention_staged_launch_cg<SK, 2>(q, kt, v, out, rows, keys, depth, cols, scale, s);
+  if (cols <= 96) return attention_staged_launch_cg<SK, 3>(q, kt, v, out, rows, keys, depth, cols, scale, s);
+  if (cols <= 128) return attention_staged_launch_cg<SK, 4>(q, kt, v, out, rows, keys, depth, cols, scale, s);
+  if (cols <= 192) return attention_staged_launch_cg<SK, 6>(q, kt, v, out, rows, keys, depth, cols, scale, s);
+  return attention_staged_launch_cg<SK, 8>(q, kt, v, out, rows, keys, depth, cols, scale, s);
+}
+
 // ---------------------------------------------------------------------------------------
 // Grouped-query attention, FP32 math, tiled
 // ---------------------------------------------------------------------------------------
@@ -279,6 +419,18 @@ extern "C" int dtn_attention_f32(const float* q, const float* kt, const float* v
               32 * kMaxColGroups);
   DTN_REQUIRE(rows < (1LL << 31) && keys < (1LL << 31) && depth < (1LL << 31), DTN_ERR_UNSUPPORTED,
               "attention: extents must fit 31 bits");
+  // Stage keys through shared memory when a stage fits (the largest stage of 256, 128, 64 or 32 keys
+  // within 200 KiB); otherwise stream from global memory.
+  constexpr size_t kStageLimit = 200 * 1024;
+  const int64_t wanted = keys < 32 ? 32 : keys;
+  if (wanted > 128 && staged_smem_bytes(256, depth, cols) <= kStageLimit)
+    return attention_staged_launch<256>(q, kt, v, out, rows, keys, depth, cols, scale, as_stream(stream));
+  if (wanted > 64 && staged_smem_bytes(128, depth, cols) <= kStageLimit)
+    return attention_staged_launch<128>(q, kt, v, out, rows, keys, depth, cols, scale, as_stream(stream));
+  if (wanted > 32 && staged_smem_bytes(64, depth, cols) <= kStageLimit)
+    return attention_staged_launch<64>(q, kt, v, out, rows, keys, depth, cols, scale, as_stream(stream));
+  if (staged_smem_bytes(32, depth, cols) <= kStageLimit)
+    return attention_staged_launch<32>(q, kt, v, out, rows, keys, depth, cols, scale, as_stream(stream));
   const int64_t blocks = (rows + kRowWarps - 1) / kRowWarps;
   attention_rows_kernel<<<(unsigned)blocks, kRowWarps * 32, 0, as_stream(stream)>>>(
       q, kt, v, out, (int)rows, (int)keys, (int)depth, (int)cols, scale);

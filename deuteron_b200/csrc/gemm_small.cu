@@ -1,0 +1,246 @@
+// Compensated FP32 GEMM for small and skinny problems: one kernel, operand split inside it.
+//
+// A tcgen05 GEMM needs a split pass over the operands, tensor-memory allocation and 128-row
+// tiles; for a 128^3 or 512^3 product, or for 16 rows, that set-up is most of the run time.
+// This kernel keeps the structure of the reference's emitted code instead: FP32 tiles go to
+// shared memory through a 4-slot cp.async ring, every warp converts the fragments it needs to a
+// rounded high part and a rounded residual in registers, and issues the three warp-level
+// products per k-step in the reference's order (lo*hi, hi*lo, hi*hi; mma.sync m16n8k16 for
+// bf16, m16n8k8 for tf32) into FP32 accumulators. 64x64 CTA tile, 4 warps of 32x32, k-tile 32.
+// Any M, N, K and leading dimensions: out-of-range elements are zero-filled by the copies.
+#include "dtn_common.cuh"
+
+namespace dtn {
+
+constexpr int S_BM = 64, S_BN = 64, S_BK = 32, S_STAGES = 4, S_THREADS = 128;
+
+template <int MODE>
+struct SmallCfg {
+  // leading dimensions chosen so that the fragment reads below are bank-conflict free
+  static constexpr int kLda = (MODE == 0) ? 40 : 36;   // A tile [64][kLda]
+  static constexpr int kLdb = (MODE == 0) ? 68 : 72;   // B tile [32][kLdb]
+  static constexpr int kStageFloats = S_BM * kLda + S_BK * kLdb;
+  static constexpr int kSmemBytes = S_STAGES * kStageFloats * 4;
+};
+
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int valid_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int valid_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(low, high);   // .x (low half) = first k index
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+// hi = bf16_rn(v) pairs, lo = bf16_rn(v - hi) pairs
+__device__ __forceinline__ void split_bf16_pair(float a, float b, uint32_t& hi, uint32_t& lo) {
+  const __nv_bfloat16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(b);
+  hi = pack_bf16(__bfloat162float(ha), __bfloat162float(hb));
+  lo = pack_bf16(a - __bfloat162float(ha), b - __bfloat162float(hb));
+}
+__device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
+  const float rest = v - __uint_as_float(hi);
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+__device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+template <int MODE /*0 = bf16x3, 1 = tf32x3*/, bool ALIGNED>
+__global__ void __launch_bounds__(S_THREADS)
+gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
+                     int64_t lda, int64_t ldb, int64_t ldc) {
+  using Cfg = SmallCfg<MODE>;
+  extern __shared__ __align__(16) float small_smem[];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int m0 = blockIdx.y * S_BM, n0 = blockIdx.x * S_BN;
+  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  const uint32_t smem_base = smem_u32(small_smem);
+
+  auto load_tile = [&](int kt, int slot) {
+    const int k0 = kt * S_BK;
+    const uint32_t a_s = smem_base + (uint32_t)(slot * Cfg::kStageFloats) * 4u;
+    const uint32_t b_s = a_s + (uint32_t)(S_BM * Cfg::kLda) * 4u;
+    if constexpr (ALIGNED) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int v = tid + i * S_THREADS;            // 512 16-byte pieces per tile
+        const int ar = v >> 3, ak = (v & 7) * 4;      // A: 64 rows x 8 pieces
+        const int gr = m0 + ar, gk = k0 + ak;
+        int bytes = (gr < M) ? (K - gk) * 4 : 0;
+        bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
+        cp_async_16(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, bytes ? (const void*)(A + (int64_t)gr * lda + gk) : (const void*)A, bytes);
+        const int br = v >> 4, bn = (v & 15) * 4;     // B: 32 rows x 16 pieces
+        const int gkb = k0 + br, gn = n0 + bn;
+        int bbytes = (gkb < K) ? (N - gn) * 4 : 0;
+        bbytes = bbytes < 0 ? 0 : (bbytes > 16 ? 16 : bbytes);
+        cp_async_16(b_s + (uint32_t)(br * Cfg::kLdb + bn) * 4u, bbytes ? (const void*)(B + (int64_t)gkb * ldb + gn) : (const void*)B, bbytes);
+      }
+    } else {
+#pragma unroll 4
+      for (int i = 0; i < 16; ++i) {
+        const int v = tid + i * S_THREADS;            // 2048 elements per tile
+        const int ar = v >> 5, ak = v & 31;
+        const bool ain = (m0 + ar < M) && (k0 + ak < K);
+        cp_async_4(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, ain ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, ain ? 4 : 0);
+        const int br = v >> 6, bn = v & 63;
+        const bool bin = (k0 + br < K) && (n0 + bn < N);
+        cp_async_4(b_s + (uint32_t)(br * Cfg::kLdb + bn) * 4u, bin ? (const void*)(B + (int64_t)(k0 + br) * ldb + n0 + bn) : (const void*)B, bin ? 4 : 0);
+      }
+    }
+  };
+
+  float acc[2][4][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
+
+  const int ktiles = (K + S_BK - 1) / S_BK;
+#pragma unroll
+  for (int s = 0; s < S_STAGES - 1; ++s) {
+    if (s < ktiles) load_tile(s, s);
+    cp_async_commit();
+  }
+  for (int kt = 0; kt < ktiles; ++kt) {
+    cp_async_wait<S_STAGES - 2>();
+    __syncthreads();
+    if (kt + S_STAGES - 1 < ktiles) load_tile(kt + S_STAGES - 1, (kt + S_STAGES - 1) % S_STAGES);
+    cp_async_commit();
+    const float* As = small_smem + (kt % S_STAGES) * Cfg::kStageFloats;
+    const float* Bs = As + S_BM * Cfg::kLda;
+    if constexpr (MODE == 0) {
+#pragma unroll
+      for (int kk = 0; kk < S_BK; kk += 16) {
+        uint32_t a_hi[2][4], a_lo[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float* ap = As + (wm + i * 16 + g) * Cfg::kLda + kk + 2 * t;
+          const float2 v0 = *reinterpret_cast<const float2*>(ap);                      // row g,   k 2t..
+          const float2 v1 = *reinterpret_cast<const float2*>(ap + 8 * Cfg::kLda);      // row g+8
+          const float2 v2 = *reinterpret_cast<const float2*>(ap + 8);                  // row g,   k 2t+8..
+          const float2 v3 = *reinterpret_cast<const float2*>(ap + 8 * Cfg::kLda + 8);  // row g+8
+          split_bf16_pair(v0.x, v0.y, a_hi[i][0], a_lo[i][0]);
+          split_bf16_pair(v1.x, v1.y, a_hi[i][1], a_lo[i][1]);
+          split_bf16_pair(v2.x, v2.y, a_hi[i][2], a_lo[i][2]);
+          split_bf16_pair(v3.x, v3.y, a_hi[i][3], a_lo[i][3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float* bp = Bs + (kk + 2 * t) * Cfg::kLdb + wn + j * 8 + g;
+          uint32_t b_hi[2], b_lo[2];
+          split_bf16_pair(bp[0], bp[Cfg::kLdb], b_hi[0], b_lo[0]);
+          split_bf16_pair(bp[8 * Cfg::kLdb], bp[9 * Cfg::kLdb], b_hi[1], b_lo[1]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            mma_bf16(acc[i][j], a_lo[i], b_hi);
+            mma_bf16(acc[i][j], a_hi[i], b_lo);
+            mma_bf16(acc[i][j], a_hi[i], b_hi);
+          }
+        }
+      }
+    } else {
+#pragma unroll
+      for (int kk = 0; kk < S_BK; kk += 8) {
+        uint32_t a_hi[2][4], a_lo[2][4];
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+          const float* ap = As + (wm + i * 16 + g) * Cfg::kLda + kk + t;
+          split_tf32(ap[0], a_hi[i][0], a_lo[i][0]);
+          split_tf32(ap[8 * Cfg::kLda], a_hi[i][1], a_lo[i][1]);
+          split_tf32(ap[4], a_hi[i][2], a_lo[i][2]);
+          split_tf32(ap[8 * Cfg::kLda + 4], a_hi[i][3], a_lo[i][3]);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float* bp = Bs + (kk + t) * Cfg::kLdb + wn + j * 8 + g;
+          uint32_t b_hi[2], b_lo[2];
+          split_tf32(bp[0], b_hi[0], b_lo[0]);
+          split_tf32(bp[4 * Cfg::kLdb], b_hi[1], b_lo[1]);
+#pragma unroll
+          for (int i = 0; i < 2; ++i) {
+            mma_tf32(acc[i][j], a_lo[i], b_hi);
+            mma_tf32(acc[i][j], a_hi[i], b_lo);
+            mma_tf32(acc[i][j], a_hi[i], b_hi);
+          }
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int col = n0 + wn + j * 8 + 2 * t;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int row = m0 + wm + i * 16 + g + h * 8;
+        if (row >= M) continue;
+        float* p = C + (int64_t)row * ldc + col;
+        if (ALIGNED && col + 1 < N) {
+          *reinterpret_cast<float2*>(p) = make_float2(acc[i][j][2 * h], acc[i][j][2 * h + 1]);
+        } else {
+          if (col < N) p[0] = acc[i][j][2 * h];
+          if (col + 1 < N) p[1] = acc[i][j][2 * h + 1];
+        }
+      }
+    }
+}
+
+template <int MODE>
+static int gemm_small_launch_mode(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                  int64_t ldb, int64_t ldc, cudaStream_t s) {
+  using Cfg = SmallCfg<MODE>;
+  const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 8) && lda % 4 == 0 && ldb % 4 == 0 && ldc % 2 == 0;
+  dim3 grid((unsigned)((N + S_BN - 1) / S_BN), (unsigned)((M + S_BM - 1) / S_BM));
+  DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm: M too large for the small-problem kernel");
+  static thread_local int attr_dev[2] = {-1, -1};
+  int dev = 0;
+  DTN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (aligned) {
+    if (attr_dev[0] != dev) {
+      DTN_CUDA_CHECK(cudaFuncSetAttribute(gemm_x3_small_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      attr_dev[0] = dev;
+    }
+    gemm_x3_small_kernel<MODE, true><<<grid, S_THREADS, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+  } else {
+    if (attr_dev[1] != dev) {
+      DTN_CUDA_CHECK(cudaFuncSetAttribute(gemm_x3_small_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+      attr_dev[1] = dev;
+    }
+    gemm_x3_small_kernel<MODE, false><<<grid, S_THREADS, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+  }
+  DTN_LAUNCH_CHECK("gemm_x3_small_kernel");
+  return DTN_OK;
+}
+
+// mode: DTN_GEMM_BF16X3 or DTN_GEMM_TF32X3
+int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldb, int64_t ldc, cudaStream_t s) {
+  return mode == DTN_GEMM_BF16X3 ? gemm_small_launch_mode<0>(A, B, C, M, N, K, lda, ldb, ldc, s)
+                                 : gemm_small_launch_mode<1>(A, B, C, M, N, K, lda, ldb, ldc, s);
+}
+
+}  // namespace dtn

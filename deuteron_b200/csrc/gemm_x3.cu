@@ -27,6 +27,15 @@ namespace dtn {
 
 int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s);
+int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldb, int64_t ldc, cudaStream_t s);
+
+// Problems for which the single-kernel path (operand split inside the kernel, no workspace) is
+// faster than split pass + tcgen05 kernel: so little work that launches and set-up dominate
+// (measured on B200: 5.3 vs 9.9 us at 128^3, 8.8 vs 11.8 us at 256^3, 15.5 vs 14.1 us at 512^3).
+static bool prefers_small_kernel(int64_t M, int64_t N, int64_t K) {
+  return (double)M * (double)N * (double)K <= 320.0 * 320.0 * 320.0;
+}
 
 // ---------------------------------------------------------------------------------------
 // Operand split
@@ -59,13 +68,11 @@ struct Tf32Kind {
 
 // A[rows, cols] (ld = ldx) -> hi/lo [rows, colsP]; columns >= cols are written as zero.
 template <class KIND>
-__global__ void __launch_bounds__(256)
-split_rows_kernel(const float* __restrict__ X, int64_t ldx, int rows, int cols, int colsP,
-                  typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo,
-                  int vec_ok) {
+__device__ __forceinline__ void split_rows_body(const float* __restrict__ X, int64_t ldx, int cols, int colsP,
+                                                typename KIND::elem* __restrict__ hi,
+                                                typename KIND::elem* __restrict__ lo, int vec_ok, int row, int block_x) {
   using E = typename KIND::elem;
-  const int row = blockIdx.y;
-  const int c4 = (blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  const int c4 = (block_x * 256 + (int)threadIdx.x) * 4;
   if (c4 >= colsP) return;
   const float* xr = X + (int64_t)row * ldx;
   float v[4] = {0.f, 0.f, 0.f, 0.f};
@@ -91,18 +98,25 @@ split_rows_kernel(const float* __restrict__ X, int64_t ldx, int rows, int cols, 
   }
 }
 
+template <class KIND>
+__global__ void __launch_bounds__(256)
+split_rows_kernel(const float* __restrict__ X, int64_t ldx, int rows, int cols, int colsP,
+                  typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo, int vec_ok) {
+  split_rows_body<KIND>(X, ldx, cols, colsP, hi, lo, vec_ok, (int)blockIdx.y, (int)blockIdx.x);
+}
+
 // B[K, N] (ld = ldb) -> transposed hi/lo [N, Kp]; k >= K written as zero.
 // One CTA transposes a kBlockK x 64 tile through shared memory.
 template <class KIND>
-__global__ void __launch_bounds__(256)
-split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
-                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo) {
+__device__ __forceinline__ void split_transpose_body(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
+                                                     typename KIND::elem* __restrict__ hi,
+                                                     typename KIND::elem* __restrict__ lo, int block_x, int block_y) {
   using E = typename KIND::elem;
   constexpr int TK = KIND::kBlockK;          // 64 (bf16) or 32 (tf32): 128 bytes of k per row
   constexpr int PAD = (KIND::kElemBytes == 2) ? 2 : 1;
   __shared__ E s_hi[64][TK + PAD];
   __shared__ E s_lo[64][TK + PAD];
-  const int k0 = blockIdx.x * TK, n0 = blockIdx.y * 64;
+  const int k0 = block_x * TK, n0 = block_y * 64;
   const int tid = threadIdx.x;
   {
     const int nn = tid & 63, kr = tid >> 6;  // 4 k-rows per pass
@@ -131,6 +145,31 @@ split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, i
         *reinterpret_cast<uint32_t*>(lo + o) = *reinterpret_cast<const uint32_t*>(&s_lo[nn][kk]);
       }
     }
+  }
+}
+
+template <class KIND>
+__global__ void __launch_bounds__(256)
+split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
+                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo) {
+  split_transpose_body<KIND>(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
+}
+
+// Both splits in one launch (one launch less on the latency of small and medium problems): the first
+// a_blocks CTAs split rows of A, the rest transpose-split tiles of B.
+template <class KIND>
+__global__ void __launch_bounds__(256)
+split_both_kernel(const float* __restrict__ A, int64_t lda, int K, int Kp, typename KIND::elem* __restrict__ a_hi,
+                  typename KIND::elem* __restrict__ a_lo, int a_vec_ok, int a_blocks_x, int a_blocks,
+                  const float* __restrict__ B, int64_t ldb, int N, typename KIND::elem* __restrict__ b_hi,
+                  typename KIND::elem* __restrict__ b_lo, int b_blocks_x) {
+  ptx::launch_dependents();   // the product kernel may begin its set-up; it waits for this grid before it loads
+  const int id = blockIdx.x;
+  if (id < a_blocks) {
+    split_rows_body<KIND>(A, lda, K, Kp, a_hi, a_lo, a_vec_ok, id / a_blocks_x, id % a_blocks_x);
+  } else {
+    const int b = id - a_blocks;
+    split_transpose_body<KIND>(B, ldb, K, N, Kp, b_hi, b_lo, b % b_blocks_x, b / b_blocks_x);
   }
 }
 
@@ -222,6 +261,9 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
   if constexpr (CTAS == 2) ptx::cluster_sync_all();
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Everything above touched only this CTA's shared and tensor memory; the operand planes are written by
+  // the kernel before this one in the stream.
+  ptx::grid_dependency_wait();
 
   if (warp == 0) {
     // ------------------------------- TMA producer --------------------------------------
@@ -482,13 +524,15 @@ static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const
   cfg.blockDim = dim3(kGemmThreads);
   cfg.dynamicSmemBytes = Cfg::kSmemBytes;
   cfg.stream = s;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = CTAS;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;   // overlap this kernel's set-up with the split kernel
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = 2;
   DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, C, ldc, (int)M, (int)N, num_kb,
                                     tiles_m, tiles_n, raster_group_m(), c_vec_ok, status));
   return DTN_OK;
@@ -502,6 +546,18 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
   E* a_lo = reinterpret_cast<E*>(ws + L.a_plane);
   E* b_hi = reinterpret_cast<E*>(ws + 2 * L.a_plane);
   E* b_lo = reinterpret_cast<E*>(ws + 2 * L.a_plane + L.b_plane);
+  {
+    const int64_t ax = (L.Kp / 4 + 255) / 256, a_blocks = ax * M;
+    const int64_t bx = L.Kp / KIND::kBlockK, b_blocks = bx * ((N + 63) / 64);
+    if (do_a && do_b && a_blocks + b_blocks < (int64_t)2000000000) {
+      const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
+      split_both_kernel<KIND><<<(unsigned)(a_blocks + b_blocks), 256, 0, s>>>(A, lda, (int)K, (int)L.Kp, a_hi, a_lo, vec_ok,
+                                                                             (int)ax, (int)a_blocks, B, ldb, (int)N, b_hi,
+                                                                             b_lo, (int)bx);
+      DTN_LAUNCH_CHECK("split_both_kernel");
+      return DTN_OK;
+    }
+  }
   if (do_a) {
     const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
     dim3 grid((unsigned)((L.Kp / 4 + 255) / 256), (unsigned)M);
@@ -630,7 +686,7 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
 }
 
 int dtn_gemm_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 3, DTN_ERR_INVALID, "gemm: variant must be 0..3");
+  DTN_REQUIRE(variant >= 0 && variant <= 4, DTN_ERR_INVALID, "gemm: variant must be 0..4");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
 }
@@ -669,6 +725,10 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   DTN_REQUIRE(aligned_to(A, 4) && aligned_to(B, 4) && aligned_to(C, 4), DTN_ERR_INVALID,
               "gemm: pointers must be 4-byte aligned");
   if (mode == DTN_GEMM_F32) return (phase & 2) ? gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s) : DTN_OK;
+
+  if (phase == 3 && (g_gemm_variant == 4 || (g_gemm_variant == 0 && prefers_small_kernel(M, N, K))))
+    return gemm_small_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s);
+  DTN_REQUIRE(g_gemm_variant != 4, DTN_ERR_INVALID, "gemm: the single-kernel variant has no separate phases");
 
   const PlaneLayout L = plane_layout(mode, M, N, K);
   DTN_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, DTN_ERR_WORKSPACE,

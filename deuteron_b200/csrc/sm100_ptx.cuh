@@ -80,6 +80,12 @@ __device__ __forceinline__ void cluster_sync_all() {
                    : "memory");
 }
 
+// Programmatic dependent launch: a kernel launched with the programmatic-serialization attribute may
+// start while the kernel before it in the stream is still running; grid_dependency_wait() blocks until
+// that kernel has completed and its writes are visible. launch_dependents() lets the next kernel start.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* m) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(m)) : "memory");
 }

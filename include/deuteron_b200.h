@@ -180,7 +180,9 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
                        int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
 /* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
- *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile.
+ *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile,
+ *   4 = the single-kernel path for small problems (operand split inside the kernel, warp-level
+ *   mma.sync products, no workspace; what automatic picks below about 320^3 multiply-adds).
  * No reference counterpart. */
 int dtn_gemm_set_variant(int variant);
 

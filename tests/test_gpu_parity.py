@@ -272,6 +272,22 @@ def test_tensor_matmul_example_all_modes(runner, golden, published):
     assert sha(produced) == published['results']['tensor_f32']['output_sha256']['result']
 
 
+@pytest.mark.parametrize('variant', [0, 1, 3, 4])
+def test_compensated_modes_hash_to_the_reference_gpu_outputs(cuda, published, variant):
+    # Same split, same three products in the same order per k-step, FP32 tensor-core accumulation: every kernel
+    # variant reproduces the bits of the reference's own run of its 128^3 example (published SHA-256 and max error).
+    left, right = R.seeded_normal(7, (128, 128)), R.seeded_normal(11, (128, 128))
+    exact = R.gemm_f64(left, right)
+    ops.set_gemm_variant(variant)
+    try:
+        for mode, record in (('bf16x3', 'tensor_bf16x3'), ('tf32x3', 'tensor_tf32x3')):
+            produced = ops.gemm(to_device(cuda, left), to_device(cuda, right), mode).cpu().numpy()
+            assert sha(produced) == published['results'][record]['output_sha256']['result'], (mode, variant)
+            assert float(np.max(np.abs(produced - exact))) == published['results'][record]['max_absolute_errors']['result']
+    finally:
+        ops.set_gemm_variant(0)
+
+
 def test_reference_committed_ir_runs_unchanged(runner, golden, published):
     import json
     graph = json.loads((golden / 'tensor_matmul.ir.json').read_text())
@@ -286,7 +302,7 @@ SHAPES = [(128, 128, 128), (256, 256, 64), (384, 768, 1000), (200, 136, 77), (16
 
 
 @pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
-@pytest.mark.parametrize('variant', [1, 2, 3])
+@pytest.mark.parametrize('variant', [1, 2, 3, 4])   # tcgen05 tiles 128x128, 128x256, CTA pair 256x256; single-kernel
 def test_compensated_gemm_shapes_and_variants(cuda, mode, variant):
     ops.set_gemm_variant(variant)
     try:
@@ -326,8 +342,10 @@ def test_gemm_edge_cases_and_errors(cuda):
     with pytest.raises(ValueError):
         ops.gemm(a, b, 'fp8')
     too_small = cuda.empty(2048, dtype=cuda.uint8, device='cuda:0')
+    big_a, big_b = to_device(cuda, R.seeded_uniform(1, (512, 512))), to_device(cuda, R.seeded_uniform(2, (512, 512)))
     with pytest.raises(ValueError, match='workspace'):
-        ops.gemm(a, b, 'bf16x3', workspace=too_small)
+        ops.gemm(big_a, big_b, 'bf16x3', workspace=too_small)
+    assert ops.gemm(a, b, 'bf16x3', workspace=too_small).shape == (64, 48)   # tiny products need no workspace
     # special values propagate like the reference's arithmetic (inf stays inf, NaN poisons its row/column)
     special = R.seeded_uniform(3, (128, 64))
     special[5, 7] = np.inf
