@@ -354,8 +354,14 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       } else {
         ptx::tc_fence_after();
         const float inv = 1.0f / mass;
-        const int row = (int)blockIdx.x * (2 * A_BM) + t * A_BM + row_in_tile;
-        float* orow = out + ((int64_t)(b * Hq + hq) * S + row) * A_D;
+        // Output through a 4 KiB per-warp staging block (in this tile's Q buffer, which no MMA reads any
+        // more): each thread owns one row in tensor memory, but a warp-wide store should cover whole rows,
+        // so the 32x32 block is written row-per-thread with an XOR swizzle and read back four rows per
+        // instruction, 128 contiguous bytes per row.
+        float* stage = reinterpret_cast<float*>(base_ptr + t * A_TILE_BYTES) + (warp % (4 * SPLIT)) * (32 * 32);
+        const int tile_row0 = (int)blockIdx.x * (2 * A_BM) + t * A_BM + quarter * 32;
+        float* obase = out + ((int64_t)(b * Hq + hq) * S + tile_row0) * A_D;
+        const int sub_row = lane >> 3, piece = lane & 7;
 #pragma unroll 1
         for (int c = c0; c < c0 + kChunks; ++c) {
           uint32_t r[32];
@@ -363,9 +369,17 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ptx::tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(orow + c * 32 + 4 * i) =
+            *reinterpret_cast<float4*>(stage + lane * 32 + 4 * (i ^ (lane & 7))) =
                 make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
                             __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+          __syncwarp();
+#pragma unroll
+          for (int rr = 0; rr < 32; rr += 4) {
+            const int rloc = rr + sub_row;
+            const float4 val = *reinterpret_cast<const float4*>(stage + rloc * 32 + 4 * (piece ^ (rloc & 7)));
+            *reinterpret_cast<float4*>(obase + (int64_t)rloc * A_D + c * 32 + 4 * piece) = val;
+          }
+          __syncwarp();
         }
       }
     }
