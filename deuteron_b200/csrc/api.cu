@@ -78,3 +78,44 @@ int dtn_device_status(int* status_out, void* stream) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Self-test of the bounded-wait reporting path: a CTA waits on an mbarrier that nothing ever
+// completes, with a small cycle budget; when the budget runs out it records a status code and
+// returns normally, exactly as the tensor-core kernels do when one of their waits runs out.
+// ---------------------------------------------------------------------------------------
+namespace dtn {
+
+__global__ void bounded_wait_selftest_kernel(long long budget_cycles, int* status) {
+  __shared__ __align__(8) unsigned long long barrier;
+  const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(&barrier));
+  if (threadIdx.x == 0) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(addr) : "memory");
+    const long long start = clock64();
+    bool completed = false;
+    while (!completed) {
+      unsigned ok;
+      asm volatile(
+          "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], 0;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(ok)
+          : "r"(addr)
+          : "memory");
+      completed = ok != 0;
+      if (!completed && clock64() - start > budget_cycles) break;
+    }
+    if (!completed) atomicExch(status, 0x7100);
+  }
+}
+
+}  // namespace dtn
+
+extern "C" int dtn_selftest_wait_timeout(long long budget_cycles, void* stream) {
+  using namespace dtn;
+  DTN_REQUIRE(budget_cycles > 0 && budget_cycles <= 2000000000LL, DTN_ERR_INVALID,
+              "selftest: budget must be between 1 and 2e9 cycles");
+  int* status = device_status_word();
+  DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "selftest: no status word on this device");
+  bounded_wait_selftest_kernel<<<1, 32, 0, as_stream(stream)>>>(budget_cycles, status);
+  DTN_LAUNCH_CHECK("bounded_wait_selftest_kernel");
+  return DTN_OK;
+}

@@ -40,9 +40,10 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   DTN_REQUIRE(S < (1LL << 31), DTN_ERR_UNSUPPORTED, "gqa: sequence length must fit 31 bits");
   cudaStream_t s = as_stream(stream);
   int variant = g_gqa_variant;
-  // Two softmax warpgroups per tile pay off while the fixed per-CTA cost matters (measured: 708 vs 671 TFLOP/s at
-  // 1024 keys, 841 vs 826 at 4096); for long sequences one warpgroup draws less power and sustains higher clocks.
-  if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? (S <= 4096 ? 3 : 2) : 1;
+  // Two softmax warpgroups per tile are the default: measured 700 vs 666 TFLOP/s at 1024 keys, 831 vs 815 at 4096
+  // and 871 vs 864 at 16384 (each measured first in its process; whichever variant runs second on a warm GPU loses
+  // ~10 % to the power cap, so back-to-back comparisons must alternate the order).
+  if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 3 : 1;
   if (variant >= 2) {
     DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
                 "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");

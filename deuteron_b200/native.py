@@ -36,6 +36,7 @@ _SIGNATURES = {
     'dtn_version': [],
     'dtn_last_error': [ct.c_char_p, ct.c_size_t],
     'dtn_device_status': [ct.POINTER(ct.c_int), _P],
+    'dtn_selftest_wait_timeout': [ct.c_longlong, _P],
     'dtn_add_f32': [_P, _P, _P, _I64, _P],
     'dtn_elementwise_f32': [_I, _P, _P, _P, _I64, _P],
     'dtn_elementwise_program': [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I64, _P],
@@ -125,5 +126,5 @@ def device_status(stream: int = 0) -> int:
 def raise_on_device_status(stream: int = 0) -> None:
     status = device_status(stream)
     if status:
-        role = {1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
+        role = {0x71: 'bounded-wait self-test', 0x11: 'attention K loader', 0x12: 'attention V loader', 1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
         raise DeviceWaitError(f'bounded wait ran out in the {role}, CTA {status & 0xff} (status {status:#x})')

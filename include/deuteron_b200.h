@@ -77,6 +77,11 @@ int dtn_last_error(char* buf, size_t n);
  * No reference counterpart (its kernels have no device-side waits on async units). */
 int dtn_device_status(int* status_out /* host */, void* stream);
 
+/* Exercises the bounded-wait reporting path without any fault: one CTA waits, for at most
+ * `budget_cycles` clock cycles, on a barrier that nothing completes, then records status 0x7100 in
+ * the device status word and returns. dtn_device_status then reports it. No reference counterpart. */
+int dtn_selftest_wait_timeout(long long budget_cycles, void* stream);
+
 /* out[i] = x[i] + y[i], i < n.  Replaces the elementwise kernel emitted by
  * Lowering.tile / Load / Write (compiler/codegen/lower.py:434-495, 600-638) after
  * vectorize_elementwise (compiler/passes/vectorize.py:160-178) for

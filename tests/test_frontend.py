@@ -251,3 +251,13 @@ def test_argument_checks_need_no_gpu():
         native.check(native.ERR_UNSUPPORTED)
     with pytest.raises(native.CudaError):
         native.check(native.ERR_CUDA)
+
+
+def test_missing_library_fails_loudly(monkeypatch, tmp_path):
+    # there is no fallback path: without the built library every entry into the native layer raises
+    monkeypatch.setattr(native, '_library', None)
+    monkeypatch.setattr(native, 'LIBRARY_PATH', tmp_path / 'libdeuteron_b200.so')
+    with pytest.raises(RuntimeError, match='no fallback'):
+        native.lib()
+    with pytest.raises(RuntimeError, match='no fallback'):
+        native.call('dtn_version')

@@ -568,3 +568,25 @@ def test_native_errors_are_python_exceptions(cuda):
     with pytest.raises(ValueError):
         ops.add(cuda.zeros(4), cuda.zeros(4))
     assert native.device_status(0) == 0
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(cuda):
+    # Failure detection without a fault: a kernel waits about a millisecond on a barrier nothing completes,
+    # records a status code and returns; the host sees it as DeviceWaitError, the word is cleared, and the
+    # next kernel on the same context runs normally.
+    stream = cuda.cuda.current_stream().cuda_stream
+    assert native.device_status(stream) == 0
+    native.call('dtn_selftest_wait_timeout', 2_000_000, stream)
+    with pytest.raises(native.DeviceWaitError, match='self-test'):
+        native.raise_on_device_status(stream)
+    assert native.device_status(stream) == 0
+    a, b = to_device(cuda, R.seeded_uniform(7, (256, 256))), to_device(cuda, R.seeded_uniform(11, (256, 256)))
+    ops.set_gemm_variant(1)
+    try:
+        produced = ops.gemm(a, b, 'bf16x3')
+        ops.check_device_status()
+    finally:
+        ops.set_gemm_variant(0)
+    assert R.max_relative_error(produced.cpu().numpy(), R.gemm_f64(a.cpu().numpy(), b.cpu().numpy())) < 1e-5
+    with pytest.raises(ValueError):
+        native.call('dtn_selftest_wait_timeout', 0, stream)
