@@ -105,12 +105,28 @@ class ClockSampler:
                 'power_w_max': max(power) if power else None, 'samples': len(clocks), 'reasons': sorted(reasons)}
 
 
+def use_all_host_threads() -> int:
+    """Lets the BLAS behind NumPy use every host core (torchrun exports OMP_NUM_THREADS=1 to its workers).
+    Returns the thread count in effect."""
+    cores = os.cpu_count() or 1
+    for name in ('OMP_NUM_THREADS', 'OPENBLAS_NUM_THREADS', 'MKL_NUM_THREADS'):
+        os.environ[name] = str(cores)
+    try:
+        import threadpoolctl
+        import numpy  # noqa: F401  (the pools exist once NumPy is loaded)
+        threadpoolctl.threadpool_limits(limits=cores)
+        pools = [pool.get('num_threads', 1) for pool in threadpoolctl.threadpool_info() if pool.get('user_api') == 'blas']
+        return max(pools) if pools else cores
+    except Exception:
+        return cores
+
+
 def cpu_gemm_sample(seconds_target: float = 12.0) -> dict:
     """The reference's CPU check of this path (float64 NumPy product of the FP32 operands,
     tests/test_tensor_copy.py:52) on a slab of A's rows sized to take roughly `seconds_target`."""
+    cores = use_all_host_threads()
     import numpy as np
     from oracle import reference_math as oracle
-    cores = os.cpu_count() or 1
     right = oracle.seeded_uniform(11, (K, N)).astype(np.float64)
     rows = 64
     probe = oracle.seeded_uniform(7, (rows, K))
@@ -132,9 +148,9 @@ def run_reference(args) -> None:
     rank = int(os.environ.get('RANK', '0'))
     if rank != 0:
         return
+    cores = use_all_host_threads()
     import numpy as np
     from oracle import reference_math as oracle
-    cores = os.cpu_count() or 1
     right = oracle.seeded_uniform(11, (K, N)).astype(np.float64)
     probe = oracle.seeded_uniform(7, (64, K))
     started = time.perf_counter()
