@@ -6,21 +6,29 @@
 // shared memory through a 4-slot cp.async ring, every warp converts the fragments it needs to a
 // rounded high part and a rounded residual in registers, and issues the three warp-level
 // products per k-step in the reference's order (lo*hi, hi*lo, hi*hi; mma.sync m16n8k16 for
-// bf16, m16n8k8 for tf32) into FP32 accumulators. 64x64 CTA tile, 4 warps of 32x32, k-tile 32.
+// bf16, m16n8k8 for tf32) into FP32 accumulators. Two configurations: a 64x64 CTA tile with 4 warps
+// of 32x32 and a 32-deep k-tile (small square problems; the reference's accumulation order, so its
+// published outputs are reproduced bit for bit), and a 16x64 tile with a 64-deep k-tile and two
+// groups of four warps that each take half of the k-tile (at most 16 rows).
 // Any M, N, K and leading dimensions: out-of-range elements are zero-filled by the copies.
 #include "dtn_common.cuh"
 
 namespace dtn {
 
-constexpr int S_BM = 64, S_BN = 64, S_BK = 32, S_STAGES = 4, S_THREADS = 128;
+constexpr int S_BN = 64, S_THREADS = 128;   // 4 warps; the tile height, k-tile and ring depth are template parameters
 
-template <int MODE>
+// BM = 64: 2 x 2 warps of 32 x 32 (general small problems). BM = 16: 1 x 4 warps of 16 x 16 for skinny
+// products (at most 16 rows), which are bound by streaming B once from HBM: a 64-deep k-tile and four
+// slots keep ~50 KB of loads in flight per CTA.
+template <int MODE, int BM, int BK, int STAGES>
 struct SmallCfg {
   // leading dimensions chosen so that the fragment reads below are bank-conflict free
-  static constexpr int kLda = (MODE == 0) ? 40 : 36;   // A tile [64][kLda]
-  static constexpr int kLdb = (MODE == 0) ? 68 : 72;   // B tile [32][kLdb]
-  static constexpr int kStageFloats = S_BM * kLda + S_BK * kLdb;
-  static constexpr int kSmemBytes = S_STAGES * kStageFloats * 4;
+  static constexpr int kLda = (MODE == 0) ? BK + 8 : BK + 4;   // A tile [BM][kLda]
+  static constexpr int kLdb = (MODE == 0) ? 68 : 72;           // B tile [BK][kLdb]
+  static constexpr int kStageFloats = BM * kLda + BK * kLdb;
+  static constexpr int kSmemBytes = STAGES * kStageFloats * 4;
+  static constexpr int kMI = BM == 64 ? 2 : 1;                 // m16 tiles per warp
+  static constexpr int kNI = BM == 64 ? 4 : 2;                 // n8 tiles per warp
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int valid_bytes) {
@@ -63,32 +71,39 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
       : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
 }
 
-template <int MODE /*0 = bf16x3, 1 = tf32x3*/, bool ALIGNED>
-__global__ void __launch_bounds__(S_THREADS)
+// KSPLIT = 2: eight warps, the second group of four takes the upper half of every k-tile and the two partial
+// accumulators are added through shared memory at the end (twice the warps to hide conversion and MMA latency).
+template <int MODE /*0 = bf16x3, 1 = tf32x3*/, bool ALIGNED, int BM, int BK, int STAGES, int KSPLIT>
+__global__ void __launch_bounds__(S_THREADS * KSPLIT)
 gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                      int64_t lda, int64_t ldb, int64_t ldc) {
-  using Cfg = SmallCfg<MODE>;
+  using Cfg = SmallCfg<MODE, BM, BK, STAGES>;
+  constexpr int MI = Cfg::kMI, NI = Cfg::kNI;
   extern __shared__ __align__(16) float small_smem[];
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  constexpr int kThreads = S_THREADS * KSPLIT;
+  const int tid = threadIdx.x, warp = (tid >> 5) & 3, kgroup = tid >> 7, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  const int m0 = blockIdx.y * S_BM, n0 = blockIdx.x * S_BN;
-  const int wm = (warp >> 1) * 32, wn = (warp & 1) * 32;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * S_BN;
+  const int wm = BM == 64 ? (warp >> 1) * 32 : 0, wn = BM == 64 ? (warp & 1) * 32 : warp * 16;
   const uint32_t smem_base = smem_u32(small_smem);
 
   auto load_tile = [&](int kt, int slot) {
-    const int k0 = kt * S_BK;
+    const int k0 = kt * BK;
     const uint32_t a_s = smem_base + (uint32_t)(slot * Cfg::kStageFloats) * 4u;
-    const uint32_t b_s = a_s + (uint32_t)(S_BM * Cfg::kLda) * 4u;
+    const uint32_t b_s = a_s + (uint32_t)(BM * Cfg::kLda) * 4u;
     if constexpr (ALIGNED) {
+      constexpr int kAPerRow = BK / 4;                  // 16-byte pieces per A row
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int v = tid + i * S_THREADS;            // 512 16-byte pieces per tile
-        const int ar = v >> 3, ak = (v & 7) * 4;      // A: 64 rows x 8 pieces
+      for (int v = tid; v < BM * kAPerRow; v += kThreads) {
+        const int ar = v / kAPerRow, ak = (v % kAPerRow) * 4;
         const int gr = m0 + ar, gk = k0 + ak;
         int bytes = (gr < M) ? (K - gk) * 4 : 0;
         bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
         cp_async_16(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, bytes ? (const void*)(A + (int64_t)gr * lda + gk) : (const void*)A, bytes);
-        const int br = v >> 4, bn = (v & 15) * 4;     // B: 32 rows x 16 pieces
+      }
+#pragma unroll
+      for (int v = tid; v < BK * 16; v += kThreads) {  // B: BK rows x 16 pieces
+        const int br = v >> 4, bn = (v & 15) * 4;
         const int gkb = k0 + br, gn = n0 + bn;
         int bbytes = (gkb < K) ? (N - gn) * 4 : 0;
         bbytes = bbytes < 0 ? 0 : (bbytes > 16 ? 16 : bbytes);
@@ -96,11 +111,13 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
       }
     } else {
 #pragma unroll 4
-      for (int i = 0; i < 16; ++i) {
-        const int v = tid + i * S_THREADS;            // 2048 elements per tile
-        const int ar = v >> 5, ak = v & 31;
+      for (int v = tid; v < BM * BK; v += kThreads) {
+        const int ar = v / BK, ak = v % BK;
         const bool ain = (m0 + ar < M) && (k0 + ak < K);
         cp_async_4(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, ain ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, ain ? 4 : 0);
+      }
+#pragma unroll 4
+      for (int v = tid; v < BK * 64; v += kThreads) {
         const int br = v >> 6, bn = v & 63;
         const bool bin = (k0 + br < K) && (n0 + bn < N);
         cp_async_4(b_s + (uint32_t)(br * Cfg::kLdb + bn) * 4u, bin ? (const void*)(B + (int64_t)(k0 + br) * ldb + n0 + bn) : (const void*)B, bin ? 4 : 0);
@@ -108,33 +125,33 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     }
   };
 
-  float acc[2][4][4];
+  float acc[MI][NI][4];
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
+    for (int j = 0; j < NI; ++j)
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
 
-  const int ktiles = (K + S_BK - 1) / S_BK;
+  const int ktiles = (K + BK - 1) / BK;
 #pragma unroll
-  for (int s = 0; s < S_STAGES - 1; ++s) {
+  for (int s = 0; s < STAGES - 1; ++s) {
     if (s < ktiles) load_tile(s, s);
     cp_async_commit();
   }
   for (int kt = 0; kt < ktiles; ++kt) {
-    cp_async_wait<S_STAGES - 2>();
+    cp_async_wait<STAGES - 2>();
     __syncthreads();
-    if (kt + S_STAGES - 1 < ktiles) load_tile(kt + S_STAGES - 1, (kt + S_STAGES - 1) % S_STAGES);
+    if (kt + STAGES - 1 < ktiles) load_tile(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
-    const float* As = small_smem + (kt % S_STAGES) * Cfg::kStageFloats;
-    const float* Bs = As + S_BM * Cfg::kLda;
+    const float* As = small_smem + (kt % STAGES) * Cfg::kStageFloats;
+    const float* Bs = As + BM * Cfg::kLda;
     if constexpr (MODE == 0) {
 #pragma unroll
-      for (int kk = 0; kk < S_BK; kk += 16) {
-        uint32_t a_hi[2][4], a_lo[2][4];
+      for (int kk = kgroup * (BK / KSPLIT); kk < (kgroup + 1) * (BK / KSPLIT); kk += 16) {
+        uint32_t a_hi[MI][4], a_lo[MI][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < MI; ++i) {
           const float* ap = As + (wm + i * 16 + g) * Cfg::kLda + kk + 2 * t;
           const float2 v0 = *reinterpret_cast<const float2*>(ap);                      // row g,   k 2t..
           const float2 v1 = *reinterpret_cast<const float2*>(ap + 8 * Cfg::kLda);      // row g+8
@@ -146,13 +163,13 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
           split_bf16_pair(v3.x, v3.y, a_hi[i][3], a_lo[i][3]);
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NI; ++j) {
           const float* bp = Bs + (kk + 2 * t) * Cfg::kLdb + wn + j * 8 + g;
           uint32_t b_hi[2], b_lo[2];
           split_bf16_pair(bp[0], bp[Cfg::kLdb], b_hi[0], b_lo[0]);
           split_bf16_pair(bp[8 * Cfg::kLdb], bp[9 * Cfg::kLdb], b_hi[1], b_lo[1]);
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < MI; ++i) {
             mma_bf16(acc[i][j], a_lo[i], b_hi);
             mma_bf16(acc[i][j], a_hi[i], b_lo);
             mma_bf16(acc[i][j], a_hi[i], b_hi);
@@ -161,10 +178,10 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
       }
     } else {
 #pragma unroll
-      for (int kk = 0; kk < S_BK; kk += 8) {
-        uint32_t a_hi[2][4], a_lo[2][4];
+      for (int kk = kgroup * (BK / KSPLIT); kk < (kgroup + 1) * (BK / KSPLIT); kk += 8) {
+        uint32_t a_hi[MI][4], a_lo[MI][4];
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
+        for (int i = 0; i < MI; ++i) {
           const float* ap = As + (wm + i * 16 + g) * Cfg::kLda + kk + t;
           split_tf32(ap[0], a_hi[i][0], a_lo[i][0]);
           split_tf32(ap[8 * Cfg::kLda], a_hi[i][1], a_lo[i][1]);
@@ -172,13 +189,13 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
           split_tf32(ap[8 * Cfg::kLda + 4], a_hi[i][3], a_lo[i][3]);
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
+        for (int j = 0; j < NI; ++j) {
           const float* bp = Bs + (kk + t) * Cfg::kLdb + wn + j * 8 + g;
           uint32_t b_hi[2], b_lo[2];
           split_tf32(bp[0], b_hi[0], b_lo[0]);
           split_tf32(bp[4 * Cfg::kLdb], b_hi[1], b_lo[1]);
 #pragma unroll
-          for (int i = 0; i < 2; ++i) {
+          for (int i = 0; i < MI; ++i) {
             mma_tf32(acc[i][j], a_lo[i], b_hi);
             mma_tf32(acc[i][j], a_hi[i], b_lo);
             mma_tf32(acc[i][j], a_hi[i], b_hi);
@@ -188,11 +205,32 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     }
   }
   cp_async_wait<0>();
+  if constexpr (KSPLIT == 2) {
+    // the upper k-half hands its partial sums to the lower half through the (now idle) ring memory
+    __syncthreads();
+    float* exchange = small_smem + (warp * 32 + lane) * (MI * NI * 4);
+    if (kgroup == 1) {
+#pragma unroll
+      for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < NI; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) exchange[(i * NI + j) * 4 + e] = acc[i][j][e];
+    }
+    __syncthreads();
+    if (kgroup == 1) return;
+#pragma unroll
+    for (int i = 0; i < MI; ++i)
+#pragma unroll
+      for (int j = 0; j < NI; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[i][j][e] += exchange[(i * NI + j) * 4 + e];
+  }
 
 #pragma unroll
-  for (int i = 0; i < 2; ++i)
+  for (int i = 0; i < MI; ++i)
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
+    for (int j = 0; j < NI; ++j) {
       const int col = n0 + wn + j * 8 + 2 * t;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
@@ -209,31 +247,35 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     }
 }
 
+template <int MODE, bool ALIGNED, int BM, int BK, int STAGES, int KSPLIT>
+static int gemm_small_launch_cfg(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                 int64_t ldb, int64_t ldc, cudaStream_t s) {
+  using Cfg = SmallCfg<MODE, BM, BK, STAGES>;
+  dim3 grid((unsigned)((N + S_BN - 1) / S_BN), (unsigned)((M + BM - 1) / BM));
+  DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm: M too large for the small-problem kernel");
+  auto kernel = gemm_x3_small_kernel<MODE, ALIGNED, BM, BK, STAGES, KSPLIT>;
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  DTN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_dev = dev;
+  }
+  kernel<<<grid, S_THREADS * KSPLIT, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+  DTN_LAUNCH_CHECK("gemm_x3_small_kernel");
+  return DTN_OK;
+}
+
 template <int MODE>
 static int gemm_small_launch_mode(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                                   int64_t ldb, int64_t ldc, cudaStream_t s) {
-  using Cfg = SmallCfg<MODE>;
   const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 8) && lda % 4 == 0 && ldb % 4 == 0 && ldc % 2 == 0;
-  dim3 grid((unsigned)((N + S_BN - 1) / S_BN), (unsigned)((M + S_BM - 1) / S_BM));
-  DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm: M too large for the small-problem kernel");
-  static thread_local int attr_dev[2] = {-1, -1};
-  int dev = 0;
-  DTN_CUDA_CHECK(cudaGetDevice(&dev));
-  if (aligned) {
-    if (attr_dev[0] != dev) {
-      DTN_CUDA_CHECK(cudaFuncSetAttribute(gemm_x3_small_kernel<MODE, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-      attr_dev[0] = dev;
-    }
-    gemm_x3_small_kernel<MODE, true><<<grid, S_THREADS, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
-  } else {
-    if (attr_dev[1] != dev) {
-      DTN_CUDA_CHECK(cudaFuncSetAttribute(gemm_x3_small_kernel<MODE, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
-      attr_dev[1] = dev;
-    }
-    gemm_x3_small_kernel<MODE, false><<<grid, S_THREADS, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
-  }
-  DTN_LAUNCH_CHECK("gemm_x3_small_kernel");
-  return DTN_OK;
+  const bool skinny = M <= 16 && K >= 256;
+  if (skinny)
+    return aligned ? gemm_small_launch_cfg<MODE, true, 16, 64, 4, 2>(A, B, C, M, N, K, lda, ldb, ldc, s)
+                   : gemm_small_launch_cfg<MODE, false, 16, 64, 4, 2>(A, B, C, M, N, K, lda, ldb, ldc, s);
+  return aligned ? gemm_small_launch_cfg<MODE, true, 64, 32, 4, 1>(A, B, C, M, N, K, lda, ldb, ldc, s)
+                 : gemm_small_launch_cfg<MODE, false, 64, 32, 4, 1>(A, B, C, M, N, K, lda, ldb, ldc, s);
 }
 
 // mode: DTN_GEMM_BF16X3 or DTN_GEMM_TF32X3
