@@ -193,6 +193,33 @@ def timed(torch, fn, iters: int, warmup: int = 3) -> float:
     return begin.elapsed_time(end) / iters
 
 
+def open_workload_latencies() -> dict:
+    """Warm latency of the reference's fifteen open workloads (the shapes of its README table), each compiled from
+    scheduled IR and timed as the reference times them: a CUDA graph of 200 launches, median of 6 event timings
+    (benchmark.py:244-268). `reference_rtx5090_us` is the reference's published number on other hardware."""
+    import math
+    from deuteron_b200 import LocalRunner, compile_kernel, schedules as S
+    cases = (
+        ('p00_add_128', S.vector_add_example(128), 2.976), ('p01_add_1024', S.vector_add_example(1024), 2.976),
+        ('p02_affine_4096', S.pointwise_example('affine', 4096), 3.040), ('p03_relu_multiply_2048', S.pointwise_example('relu_multiply', 2048), 2.976),
+        ('r01_sum_1024', S.row_reduce_example(1, 1024, 'sum'), 2.960), ('r02_sum_65536', S.row_reduce_example(1, 65536, 'sum'), 6.816),
+        ('r03_mean_32768', S.mean_example(32768), 4.784), ('r04_row_sum_64x512', S.row_reduce_example(64, 512, 'sum'), 2.960),
+        ('m01_matmul_512', S.matmul_example(512, 512, 512), 8.896), ('m02_matmul_128x256x64', S.split_k_matmul_example(128, 64, 256), 3.144),
+        ('f01_rms_norm_64x1024', S.rms_norm_example(64, 1024), 3.152), ('f02_softmax_64x256', S.row_softmax_example(64, 256), 2.976),
+        ('f03_l2_norm_64x512', S.l2_norm_example(64, 512), 2.976),
+        ('a01_attention_64x64_d64', S.attention_example(64, 64, 64, columns=64), 4.800),
+        ('a02_attention_128_d32', S.attention_example(128, 128, 32), 4.800))
+    out = {}
+    with LocalRunner(0) as runner:
+        for name, (graph, meta), published in cases:
+            compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3)
+            result = runner.run_kernel(meta['kernels'][0], compiled, warmup=20, iters=200, samples=6)
+            out[name] = {'median_us': result['median_us'], 'reference_rtx5090_us': published}
+    out['geometric_mean_us'] = math.exp(sum(math.log(v['median_us']) for v in out.values()) / len(out))
+    out['reference_rtx5090_geometric_mean_us'] = 3.752
+    return out
+
+
 def extras(torch, ops, peaks: dict) -> dict:
     """Other hot kernels at their benchmark sizes (inputs larger than L2), resident inputs."""
     out = {}
@@ -226,7 +253,10 @@ def extras(torch, ops, peaks: dict) -> dict:
             ('f16_widen_2^28', lambda: ops.f16_widen(half, z), 6 * n),
             ('f16_copy_2^28', lambda: ops.f16_copy(half, half2), 4 * n),
             ('row_sum_65536x4096', lambda: ops.row_reduce('sum', x.view(65536, 4096), rows), 4 * n + 4 * 65536),
-            ('row_max_65536x4096', lambda: ops.row_reduce('max', x.view(65536, 4096), rows), 4 * n + 4 * 65536)):
+            ('row_max_65536x4096', lambda: ops.row_reduce('max', x.view(65536, 4096), rows), 4 * n + 4 * 65536),
+            ('row_softmax_65536x4096', lambda: ops.row_softmax(x.view(65536, 4096), z.view(65536, 4096)), 8 * n),
+            ('rms_norm_65536x4096', lambda: ops.rms_norm(x.view(65536, 4096), y[:4096], 1e-5, z.view(65536, 4096)), 8 * n + 4 * 4096),
+            ('l2_norm_65536x4096', lambda: ops.l2_norm(x.view(65536, 4096), z.view(65536, 4096)), 8 * n)):
         ms = timed(torch, fn, 10)
         out[name] = {'ms': ms, 'gbs': nbytes / ms / 1e6, 'frac_of_hbm_peak': nbytes / ms / 1e6 / peak}
     del x, y, z, half, half2
@@ -375,6 +405,7 @@ def run_ours(args) -> None:
             del a, b, c
             torch.cuda.empty_cache()
             line['extras'] = extras(torch, ops, peaks)
+            line['extras']['open_workload_latency'] = open_workload_latencies()
         sys.stdout.flush()
         os.dup2(json_fd, 1)
         print(json.dumps(line), flush=True)
@@ -383,7 +414,7 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max')
+PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max', 'row_softmax', 'rms_norm')
 
 
 def run_profile_case(name: str, launches: int) -> None:
@@ -418,7 +449,9 @@ def run_profile_case(name: str, launches: int) -> None:
         call = {'add': lambda: ops.add(x, y, z), 'f16_narrow': lambda: ops.f16_narrow(x, half),
                 'f16_widen': lambda: ops.f16_widen(half, z), 'f16_copy': lambda: ops.f16_copy(half, half2),
                 'row_sum': lambda: ops.row_reduce('sum', x.view(16384, 4096), rows),
-                'row_max': lambda: ops.row_reduce('max', x.view(16384, 4096), rows)}[name]
+                'row_max': lambda: ops.row_reduce('max', x.view(16384, 4096), rows),
+                'row_softmax': lambda: ops.row_softmax(x.view(16384, 4096), z.view(16384, 4096)),
+                'rms_norm': lambda: ops.rms_norm(x.view(16384, 4096), y[:4096], 1e-5, z.view(16384, 4096))}[name]
     for _ in range(launches):
         call()
     torch.cuda.synchronize()

@@ -14,6 +14,7 @@ from dataclasses import dataclass, field
 from typing import Any
 
 from . import ir
+from .classify_rows import classify_rows
 from .native import BINARY_OPS, ELEMENTWISE_OPS
 
 
@@ -57,7 +58,7 @@ def _shape(specs: dict, name: str) -> tuple[int, ...]:
 # ------------------------------------------------------------------------------------------------
 
 
-def _classify_gemm(tile: ir.Node, specs: dict, precision: str) -> Plan | None:
+def _classify_gemm(tile: ir.Node, specs: dict, precision: str, launch: dict) -> Plan | None:
     statements = list(ir.walk([tile]))
     accums = [s for s in statements if s.kind == 'Accum' and _op_name(s.op) == 'add']
     assigns = {s.name: s for s in statements if s.kind == 'Assign'}
@@ -68,11 +69,10 @@ def _classify_gemm(tile: ir.Node, specs: dict, precision: str) -> Plan | None:
         return None
     if any(_op_name(s.op) in ('exp', 'maximum') for s in assigns.values()):
         return None
-    if any(w.atomic for w in writes):
-        raise NotImplementedError('atomic (split-K) contractions are outside the supported subset')
     output = writes[0].output
     if any(w.output != output for w in writes):
         return None
+    split_depth = _split_k_depth(tile, writes, launch) if any(w.atomic for w in writes) else None
     loads = {}
     for stmt in statements:
         if stmt.kind == 'Load':
@@ -113,11 +113,34 @@ def _classify_gemm(tile: ir.Node, specs: dict, precision: str) -> Plan | None:
     (m, k), (k2, n), out_shape = _shape(specs, left), _shape(specs, right), _shape(specs, output)
     if k != k2 or out_shape != (m, n):
         raise ValueError(f'contraction shapes disagree: {left}{[m, k]} @ {right}{[k2, n]} -> {output}{list(out_shape)}')
+    if split_depth is not None and split_depth != k:
+        raise NotImplementedError(f'split-K partial products cover {split_depth} of the {k} reduction steps')
     for name in (left, right, output):
         if specs[name]['dtype'] != 'f32':
             raise NotImplementedError('contractions take f32 buffers')
     return Plan('gemm', {'mode': precision, 'm': m, 'n': n, 'k': k},
                 {'left': (left, 0), 'right': (right, 0), 'out': (output, 0)})
+
+
+def _split_k_depth(tile: ir.Node, writes: list, launch: dict) -> int:
+    """Reduction steps covered by an atomic (split-K) contraction: every CTA adds a partial product into an output
+    that the launch zeroes first (zero_outputs, benchmark.py:240-243), so the sum over the split axis is the full
+    product and one overwriting GEMM computes the same matrix. The split axis is the grid axis the stores do not
+    depend on (compiler/passes/gridfold.py:66-70); the steps per CTA are the extent of the loop around the products."""
+    output = writes[0].output
+    if not all(w.atomic for w in writes):
+        raise NotImplementedError('atomic and plain stores of a contraction must not be mixed')
+    if output not in (launch.get('zero_outputs') or []):
+        raise NotImplementedError('atomic (split-K) contractions need their output in zero_outputs')
+    stored = set()
+    for w in writes:
+        for expr in w.index:
+            stored |= ir.expression_vars(expr)
+    split_axes = [a for a in tile.axes if a.extent.value > 1 and a.name not in stored]
+    outer = [s for s in tile.body if s.kind in ('Loop', 'StridedLoop') and any(c.kind == 'Accum' for c in ir.walk(s.body))]
+    if len(split_axes) != 1 or len(outer) != 1:
+        raise NotImplementedError('atomic (split-K) contractions have one split axis and one reduction loop nest')
+    return split_axes[0].extent.value * outer[0].axis.extent.value
 
 
 # ------------------------------------------------------------------------------------------------
@@ -255,41 +278,8 @@ def _attention_scale(tile: ir.Node, outer_loop: ir.Node, inner_loop: ir.Node, sp
 
 
 def _classify_reduction(tile: ir.Node, specs: dict) -> Plan | None:
-    statements = list(ir.walk([tile]))
-    if any(s.kind in ('Smem', 'CpAsyncCopy') for s in statements):
-        return None
-    loops = [s for s in statements if s.kind in ('StridedLoop', 'Loop')]
-    accums = [s for s in statements if s.kind == 'Accum']
-    writes = [s for s in statements if s.kind == 'Write']
-    loads = [s for s in statements if s.kind == 'Load']
-    if len(loops) != 1 or not accums or len(writes) != 1 or len(loads) != 1:
-        return None
-    if not all(s.kind in ('Load', 'Assign', 'Accum') for s in loops[0].body):
-        return None
-    ops = {_op_name(a.op) for a in accums}
-    if len(ops) != 1:
-        return None
-    op = {'add': 'sum', 'maximum': 'max'}.get(ops.pop())
-    if op is None:
-        raise NotImplementedError('row reductions implement add and maximum')
-    body_assigns = [s for s in loops[0].body if s.kind == 'Assign']
-    if body_assigns:
-        square = (len(body_assigns) == 1 and _op_name(body_assigns[0].op) == 'multiply'
-                  and len(set(body_assigns[0].args)) == 1 and op == 'sum')
-        if not square:
-            raise NotImplementedError('row reductions accept a plain value or its square')
-        op = 'sumsq'
-    source, output = loads[0].input, writes[0].output
-    in_shape, out_shape = _shape(specs, source), _shape(specs, output)
-    if specs[source]['dtype'] != 'f32' or specs[output]['dtype'] != 'f32':
-        raise NotImplementedError('row reductions take f32 buffers')
-    if len(in_shape) == 2 and out_shape in ((in_shape[0],), (in_shape[0], 1)):
-        rows, cols = in_shape
-    elif len(in_shape) == 1 and math.prod(out_shape) == 1:
-        rows, cols = 1, in_shape[0]
-    else:
-        raise NotImplementedError('row reductions map x[rows, cols] to out[rows] or x[n] to out[1]')
-    return Plan('row_reduce', {'op': op, 'rows': rows, 'cols': cols}, {'x': (source, 0), 'out': (output, 0)})
+    """Row reductions and the fused row kernels built on them (classify_rows.py)."""
+    return classify_rows(tile, specs, Plan)
 
 
 # ------------------------------------------------------------------------------------------------
@@ -476,7 +466,7 @@ def _program_plan(tree: tuple, specs: dict, origins: dict, constants: dict, outp
 def classify(kernel: ir.Kernel, launch: dict, specs: dict, precision: str) -> Plan:
     """Returns the native plan of a validated kernel or raises NotImplementedError."""
     tile = _single_tile(kernel)
-    for recogniser in (lambda: _classify_attention(tile, specs), lambda: _classify_gemm(tile, specs, precision),
+    for recogniser in (lambda: _classify_attention(tile, specs), lambda: _classify_gemm(tile, specs, precision, launch),
                        lambda: _classify_reduction(tile, specs), lambda: _classify_elementwise(tile, specs)):
         plan = recogniser()
         if plan is not None:

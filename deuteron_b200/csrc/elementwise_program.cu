@@ -10,6 +10,7 @@
 // results equal the reference's operator-by-operator NumPy expectation), and the result is
 // narrowed to f16 with round-to-nearest-even when the output buffer is f16.
 #include "dtn_common.cuh"
+#include "program.cuh"
 
 namespace dtn {
 
@@ -28,54 +29,6 @@ struct EwProgram {
   unsigned char op[kProgMaxInstr], dst[kProgMaxInstr], a[kProgMaxInstr], b[kProgMaxInstr];
 };
 
-template <int W>
-struct RegFile {
-  float r[kProgRegs][W];
-  __device__ __forceinline__ void get(int idx, float (&out)[W]) const {
-#pragma unroll
-    for (int k = 0; k < kProgRegs; ++k)
-      if (idx == k) {
-#pragma unroll
-        for (int e = 0; e < W; ++e) out[e] = r[k][e];
-      }
-  }
-  __device__ __forceinline__ void put(int idx, const float (&in)[W]) {
-#pragma unroll
-    for (int k = 0; k < kProgRegs; ++k)
-      if (idx == k) {
-#pragma unroll
-        for (int e = 0; e < W; ++e) r[k][e] = in[e];
-      }
-  }
-};
-
-__device__ __forceinline__ float prog_apply(int op, float a, float b) {
-  switch (op) {
-    case DTN_EW_ADD: return __fadd_rn(a, b);
-    case DTN_EW_SUB: return __fsub_rn(a, b);
-    case DTN_EW_MUL: return __fmul_rn(a, b);
-    case DTN_EW_DIV: return __fdividef(a, b);
-    case DTN_EW_MAX: return fmaxf(a, b);
-    case DTN_EW_MIN: return fminf(a, b);
-    case DTN_EW_RELU: return fmaxf(a, 0.0f);
-    case DTN_EW_EXP: return exp_ref(a);
-    case DTN_EW_SQRT: {
-      float y;
-      asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(a));
-      return y;
-    }
-    case DTN_EW_RSQRT: {
-      float y;
-      asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(a));
-      return y;
-    }
-    case DTN_EW_RCP: return rcp_approx(a);
-    case DTN_EW_NEG: return -a;
-    case DTN_EW_ABS: return fabsf(a);
-    default: return a;
-  }
-}
-
 // W = 8: vector body (every vector pointer 16-byte aligned at `first`); W = 1: scalar elements.
 template <int W>
 __global__ void __launch_bounds__(256)
@@ -83,7 +36,7 @@ ew_program_kernel(const EwProgram prog, void* __restrict__ out, int64_t first, i
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t item = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; item < count; item += stride) {
     const int64_t base = first + item * W;
-    RegFile<W> regs;
+    RegFile<kProgRegs, W> regs;
 #pragma unroll
     for (int i = 0; i < kProgMaxInputs; ++i) {
       if (i >= prog.n_inputs) break;

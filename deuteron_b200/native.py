@@ -14,7 +14,8 @@ LIBRARY_PATH = Path(__file__).resolve().parent / 'libdeuteron_b200.so'
 OK, ERR_INVALID, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_DEVICE = range(6)
 
 GEMM_MODES = {'f32': 0, 'tf32x3': 1, 'bf16x3': 2}
-REDUCE_OPS = {'sum': 0, 'max': 1, 'sumsq': 2}
+REDUCE_OPS = {'sum': 0, 'max': 1, 'sumsq': 2, 'softmax': 3}
+ROW_INPUT_KINDS = {'scalar': 0, 'columns': 1, 'immediate': 2}
 STORAGE = {'f32': 0, 'f16': 1}
 ELEMENTWISE_OPS = {
     'add': 0, 'subtract': 1, 'multiply': 2, 'divide': 3, 'maximum': 4, 'minimum': 5, 'relu': 6, 'exp': 7,
@@ -44,6 +45,7 @@ _SIGNATURES = {
     'dtn_f16_widen': [_P, _P, _I64, _P],
     'dtn_f16_narrow': [_P, _P, _I64, _P],
     'dtn_row_reduce_f32': [_I, _P, _P, _I64, _I64, _I64, _P],
+    'dtn_row_fused': [_I, _P, _I64, _I64, _I64, _P, _P, _P, _I, _P, _P, _P, _P, _I, _I, _I, _P, _I64, _P],
     'dtn_gemm_workspace_bytes': [_I, _I64, _I64, _I64, ct.POINTER(ct.c_size_t)],
     'dtn_gemm_x3': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, ct.c_size_t, _P],
     'dtn_gemm_x3_phase': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, ct.c_size_t, _I, _P],
@@ -114,6 +116,20 @@ def elementwise_program(params: dict, input_pointers: list[int], out_pointer: in
          as_bytes(params['b']), count, inputs, as_bytes([int(i['f16']) for i in params['inputs']]),
          as_bytes([int(i['scalar']) for i in params['inputs']]), len(input_pointers), params['out_reg'], out_pointer,
          int(params['out_f16']), params['n'], stream)
+
+
+def row_fused(params: dict, x_pointer: int, input_pointers: list[int | None], out_pointer: int, ldx: int, ldo: int, stream: int) -> None:
+    """Launches dtn_row_fused for a classifier-built row program (classify_rows._row_program).
+    input_pointers holds one device pointer per extra input, None for immediates."""
+    count = len(params['ops'])
+    as_bytes = lambda values: (ct.c_ubyte * max(len(values), 1))(*values)
+    described = params['inputs']
+    inputs = (ct.c_void_p * max(len(described), 1))(*[p or 0 for p in input_pointers])
+    immediates = (ct.c_float * max(len(described), 1))(*[float(i.get('value', 0.0)) for i in described])
+    call('dtn_row_fused', REDUCE_OPS[params['reduce']], x_pointer, params['rows'], params['cols'], ldx, inputs,
+         as_bytes([ROW_INPUT_KINDS[i['kind']] for i in described]), immediates, len(described), as_bytes(params['ops']),
+         as_bytes(params['dst']), as_bytes(params['a']), as_bytes(params['b']), params['n_scalar'], count, params['out_reg'],
+         out_pointer, ldo, stream)
 
 
 def device_status(stream: int = 0) -> int:

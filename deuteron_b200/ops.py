@@ -95,7 +95,7 @@ def f16_narrow(src: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tens
 
 def row_reduce(op: str, x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     """out[r] = sum / max / sumsq of row r of the 2-D FP32 tensor x (rows may be strided)."""
-    if op not in native.REDUCE_OPS:
+    if op not in ('sum', 'max', 'sumsq'):
         raise NotImplementedError(f'row reduction {op}')
     _require_cuda(x)
     if x.dtype != torch.float32 or x.dim() != 2 or (x.shape[1] > 1 and x.stride(1) != 1):
@@ -107,6 +107,62 @@ def row_reduce(op: str, x: torch.Tensor, out: torch.Tensor | None = None) -> tor
     _flat(out, torch.float32, 'out')
     native.call('dtn_row_reduce_f32', native.REDUCE_OPS[op], x.data_ptr(), out.data_ptr(), rows, cols, max(ldx, cols), _stream())
     return out
+
+
+def _row_matrix(x: torch.Tensor, label: str) -> tuple[int, int, int]:
+    _require_cuda(x)
+    if x.dtype != torch.float32 or x.dim() != 2 or (x.shape[1] > 1 and x.stride(1) != 1):
+        raise ValueError(f'{label} takes a 2-D float32 tensor with unit column stride')
+    rows, cols = x.shape
+    return rows, cols, max(x.stride(0) if rows > 1 else cols, cols, 1)
+
+
+def _row_fused(reduce: str, x: torch.Tensor, program: list[tuple[str, int, int, int]], n_scalar: int, out_reg: int, inputs=(),
+               per_row: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    """One launch of the fused row kernel. program: (operator, destination, a, b) over the registers
+    0 = reduced value, 1 = sum of exponentials, 2 = row element, 3 + i = inputs[i]; inputs: a float
+    (immediate), a one-element tensor (scalar) or a tensor of `cols` values (one per column)."""
+    rows, cols, ldx = _row_matrix(x, 'row kernel')
+    described, pointers = [], []
+    for item in inputs:
+        if isinstance(item, (int, float)):
+            described.append({'kind': 'immediate', 'value': float(item)})
+            pointers.append(None)
+            continue
+        _flat(item, torch.float32, 'row kernel input')
+        if item.numel() not in (1, cols):
+            raise ValueError('row kernel inputs hold one value or one value per column')
+        described.append({'kind': 'columns' if item.numel() == cols and cols != 1 else 'scalar'})
+        pointers.append(item.data_ptr())
+    if out is None:
+        out = torch.empty(rows if per_row else (rows, cols), dtype=torch.float32, device=x.device)
+    _flat(out, torch.float32, 'out')
+    params = {'reduce': reduce, 'rows': rows, 'cols': cols, 'inputs': described, 'n_scalar': n_scalar, 'out_reg': out_reg,
+              'ops': [native.ELEMENTWISE_OPS[p[0]] for p in program], 'dst': [p[1] for p in program],
+              'a': [p[2] for p in program], 'b': [p[3] for p in program]}
+    native.row_fused(params, x.data_ptr(), pointers, out.data_ptr(), ldx, 0 if per_row else max(cols, 1), _stream())
+    return out
+
+
+def row_softmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, c] = exp(x[r, c] - max_r) / sum_c exp(x[r, c] - max_r), one launch."""
+    return _row_fused('softmax', x, [('reciprocal', 3, 1, 1), ('subtract', 4, 2, 0), ('exp', 4, 4, 4), ('multiply', 4, 4, 3)], 1, 4, out=out)
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, epsilon: float = 1e-5, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, c] = x[r, c] * rsqrt(mean_c(x[r, :]^2) + epsilon) * weight[c], one launch."""
+    program = [('divide', 6, 0, 4), ('add', 6, 6, 5), ('rsqrt', 6, 6, 6), ('multiply', 7, 2, 6), ('multiply', 7, 7, 3)]
+    return _row_fused('sumsq', x, program, 3, 7, inputs=(weight, float(x.shape[1]), float(epsilon)), out=out)
+
+
+def l2_norm(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r, c] = x[r, c] * rsqrt(sum_c x[r, :]^2), one launch."""
+    return _row_fused('sumsq', x, [('rsqrt', 3, 0, 0), ('multiply', 4, 2, 3)], 1, 4, out=out)
+
+
+def row_mean(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """out[r] = sum_c x[r, c] / cols, one launch."""
+    return _row_fused('sum', x, [('divide', 4, 0, 3)], 1, 4, inputs=(float(x.shape[1]),), per_row=True, out=out)
 
 
 # ------------------------------------------------------------------------------------------------

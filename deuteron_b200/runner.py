@@ -149,6 +149,9 @@ class LocalRunner:
         elif kind == 'row_reduce':
             native.call('dtn_row_reduce_f32', native.REDUCE_OPS[p['op']], ptr('x', 4), ptr('out', 4), p['rows'], p['cols'],
                         max(p['cols'], 1), stream)
+        elif kind == 'row_fused':
+            extra = [None if item['kind'] == 'immediate' else ptr(f'in{i}', 4) for i, item in enumerate(p['inputs'])]
+            native.row_fused(p, ptr('x', 4), extra, ptr('out', 4), max(p['cols'], 1), 0 if p['per_row'] else max(p['cols'], 1), stream)
         elif kind == 'gemm':
             ws_ptr, ws_bytes = workspace
             native.call('dtn_gemm_x3', native.GEMM_MODES[p['mode']], ptr('left', 4), ptr('right', 4), ptr('out', 4), p['m'],

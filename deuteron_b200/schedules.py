@@ -121,6 +121,38 @@ def vector_add_example(count: int = 1030, seeds=(21, 22)) -> tuple[dict, dict]:
     return graph, _metadata('vector_add', launch, 0.0, 0.0, ['lhs', 'rhs'], ['sum'])
 
 
+def pointwise_example(kind: str = 'affine', count: int = 4096, block: int = 256) -> tuple[dict, dict]:
+    """The reference's two fused FP32 pointwise workloads, in their launch shapes: 'affine' is
+    add = x * mul_c1 + add_c1 with both constants as one-element buffers (mul_c1[1] = 2, add_c1[1] = 1, x[4096],
+    grid 4 x block 256, four values per thread); 'relu_multiply' is mul = relu(x) * y (x[2048], y[2048], grid 2)."""
+    if kind not in ('affine', 'relu_multiply') or count <= 0 or count % 4:
+        raise ValueError('unsupported example configuration')
+    index = mul(var('element'), lit(4))
+    names = tuple(f'x{i}' for i in range(4))
+    results = tuple(f'result{i}' for i in range(4))
+    if kind == 'affine':
+        output, entry = 'add', 'k_add_pointwise'
+        args = [{'name': 'mul_c1', 'dtype': 'f32', 'shape': [1], 'data': [2.0]}, {'name': 'add_c1', 'dtype': 'f32', 'shape': [1], 'data': [1.0]},
+                {'name': 'x', 'dtype': 'f32', 'shape': [count], 'seed': 0}]
+        body = [load(('scale',), 'mul_c1', [lit(0)]), load(('shift',), 'add_c1', [lit(0)]), load(names, 'x', [index])]
+        for i in range(4):
+            body += [assign(f'scaled{i}', 'multiply', (names[i], 'scale')), assign(results[i], 'add', (f'scaled{i}', 'shift'))]
+    else:
+        output, entry = 'mul', 'k_mul_pointwise'
+        args = [{'name': 'x', 'dtype': 'f32', 'shape': [count], 'seed': 0}, {'name': 'y', 'dtype': 'f32', 'shape': [count], 'seed': 1}]
+        others = tuple(f'y{i}' for i in range(4))
+        body = [load(names, 'x', [index]), load(others, 'y', [index])]
+        for i in range(4):
+            body += [assign(f'positive{i}', 'relu', (names[i],)), assign(results[i], 'multiply', (f'positive{i}', others[i]))]
+    body.append(write(output, [index], results))
+    args.append({'name': output, 'dtype': 'f32', 'shape': [count], 'output': True})
+    inputs = {a['name']: (a['shape'], a['dtype']) for a in args if not a.get('output')}
+    graph = _graph(entry, tile([axis('element', count // 4)], body, block), inputs, (output, [count], 'f32'))
+    launch = {'node': output, 'entry': entry, 'arg_order': [a['name'] for a in args], 'grid': [math.ceil(count / 4 / block), 1, 1],
+              'block': [block, 1, 1], 'smem_bytes': 0, 'zero_outputs': [], 'args': args, 'final': True}
+    return graph, _metadata(entry, launch, 1e-5, 1e-6, list(inputs), [output])
+
+
 def f16_storage_example(kind: str = 'copy', count: int = 512, width: int = 4, offset: int = 0) -> tuple[dict, dict]:
     """The five f16 storage kernels of examples/f16_storage.py:19-60 (same entry names, widths, launch,
     seeds and constant buffers): copy, widen, narrow, affine f16(x * 1.5 - 0.25) and cancellation
@@ -209,12 +241,44 @@ def attention_example(rows: int = 3, keys: int = 64, depth: int = 32, inplace_de
     return graph, _metadata(entry, launch, 0.001, 0.0001, ['q', 'kt', 'v'], ['out'])
 
 
+def _int_eq(left: str, right: str) -> str:
+    return binary('==', left, right)
+
+
+def reduction_tail(states, others, combines, warps: int) -> list[str]:
+    """The statements that fold per-thread partial states into one value per CTA, in the form the
+    reference matches (compiler/transforms.py:88-94, compiler/passes/hybrid_normalizer.py:53-66,
+    compiler/passes/tailtree.py:63-110): a 32-lane WarpShuffle, one shared-memory slot per warp and state
+    written by lane 0, a barrier, and a TreeHalve over the warp partials."""
+    combine_body = _tuple(combines)
+    buffers = [f'{state}_partials' for state in states]
+    out = [f"WarpShuffle(state={_names(states)}, state_b={_names(others)}, combine_states={combine_body}, length=32, dtype={F32})"]
+    out += [f"Smem(name={buffer!r}, extents=({warps},), dtype='float', align=0)" for buffer in buffers]
+    stores = [write(buffer, [var('warp')], (state,)) for buffer, state in zip(buffers, states)]
+    out.append(f"Cond(cond={_int_eq(var('lane'), lit(0))}, body={_tuple(stores)}, else_body=())")
+    out.append('Sync(barrier_id=0, count=None, warp=False)')
+    out.append(f"TreeHalve(bufs={_names(buffers)}, state={_names(states)}, state_b={_names(others)}, combine_states={combine_body}, "
+               f"length={warps}, tid_var='warp', inner=None, barrier_id=0, barrier_count=None, dtype={F32})")
+    return out
+
+
+def _row_launch(entry: str, rows: int, block: int, args: list[dict], node: str) -> dict:
+    return {'node': node, 'entry': entry, 'arg_order': [a['name'] for a in args], 'grid': [rows, 1, 1], 'block': [block, 1, 1],
+            'smem_bytes': 0, 'zero_outputs': [], 'args': args, 'final': True}
+
+
+def _check_rows(rows: int, cols: int, block: int) -> None:
+    if rows <= 0 or cols <= 0 or block % 32 or not 32 <= block <= 1024:
+        raise ValueError('unsupported row kernel configuration')
+
+
 def row_reduce_example(rows: int, cols: int, op: str = 'sum', block: int = 128, seed: int = 7) -> tuple[dict, dict]:
     """One CTA per row: a thread-strided loop folded by a warp shuffle and a cross-warp tree, the
     structure compiler/transforms.py:62-95 recognises (launch shape of the reference's row-sum
     workload: grid = rows, block = 128). op: 'sum', 'max' or 'sumsq'."""
-    if op not in ('sum', 'max', 'sumsq') or rows <= 0 or cols <= 0 or block % 32 or not 32 <= block <= 1024:
+    if op not in ('sum', 'max', 'sumsq'):
         raise ValueError('unsupported reduction configuration')
+    _check_rows(rows, cols, block)
     combine, identity = ('maximum', '-inf') if op == 'max' else ('add', '0.0')
     inner = [load(('value',), 'x', [var('row'), var('col')])]
     folded = 'value'
@@ -222,22 +286,142 @@ def row_reduce_example(rows: int, cols: int, op: str = 'sum', block: int = 128, 
         inner.append(assign('square', 'multiply', ('value', 'value')))
         folded = 'square'
     inner.append(accum('state', folded, combine, ('col',)))
-    warps = block // 32
     body = tile([axis('row', rows), axis('lane_id', block)], [
         f"Init(name='state', identity={identity}, dtype={F32})",
-        strided_loop(axis('col', cols), var('lane_id'), lit(block), inner),
-        f"WarpShuffle(state='state', state_b=None, combine_states=ElementwiseImpl({combine!r}), length=32, dtype={F32})",
-        f"TreeHalve(bufs=('partials',), state='state', state_b=None, combine_states=ElementwiseImpl({combine!r}), length={warps}, "
-        f"tid_var='warp', inner=None, barrier_id=0, barrier_count=None, dtype={F32})",
+        strided_loop(axis('col', cols), var('lane_id'), lit(block), inner, seed=True),
+        *reduction_tail(('state',), ('state_b',), [assign('state', combine, ('state', 'state_b'))], block // 32),
         write('out', [var('row')], ('state',)),
     ], block)
     entry = f'row_{op}'
     graph = _graph(entry, body, {'x': ([rows, cols], 'f32')}, ('out', [rows], 'f32'))
-    launch = {'node': 'out', 'entry': entry, 'arg_order': ['x', 'out'], 'grid': [rows, 1, 1], 'block': [block, 1, 1],
-              'smem_bytes': 0, 'zero_outputs': [],
-              'args': [{'name': 'x', 'dtype': 'f32', 'shape': [rows, cols], 'seed': seed},
-                       {'name': 'out', 'dtype': 'f32', 'shape': [rows], 'output': True}], 'final': True}
+    launch = _row_launch(entry, rows, block, [{'name': 'x', 'dtype': 'f32', 'shape': [rows, cols], 'seed': seed},
+                                              {'name': 'out', 'dtype': 'f32', 'shape': [rows], 'output': True}], 'out')
     return graph, _metadata(entry, launch, 1e-4, 1e-4, ['x'], ['out'])
+
+
+def mean_example(count: int = 32768, block: int = 128, seed: int = 0) -> tuple[dict, dict]:
+    """Mean of a vector with the element count as a one-element buffer, the shape of the reference's
+    mean workload (x[32768], mean_keepdim_count[1] -> mean[1], one CTA of 128 threads)."""
+    _check_rows(1, count, block)
+    body = tile([axis('lane_id', block)], [
+        f"Init(name='state', identity=0.0, dtype={F32})",
+        strided_loop(axis('i', count), var('lane_id'), lit(block), [load(('value',), 'x', [var('i')]), accum('state', 'value', 'add', ('i',))],
+                     seed=True),
+        *reduction_tail(('state',), ('state_b',), [assign('state', 'add', ('state', 'state_b'))], block // 32),
+        load(('count',), 'mean_keepdim_count', [lit(0)]),
+        assign('result', 'divide', ('state', 'count')),
+        write('mean', [lit(0)], ('result',)),
+    ], block)
+    graph = _graph('k_mean', body, {'x': ([count], 'f32'), 'mean_keepdim_count': ([1], 'f32')}, ('mean', [1], 'f32'))
+    launch = _row_launch('k_mean', 1, block, [{'name': 'x', 'dtype': 'f32', 'shape': [count], 'seed': seed},
+                                              {'name': 'mean_keepdim_count', 'dtype': 'f32', 'shape': [1], 'data': [float(count)]},
+                                              {'name': 'mean', 'dtype': 'f32', 'shape': [1], 'output': True}], 'mean')
+    return graph, _metadata('k_mean', launch, 1e-4, 1e-5, ['x'], ['mean'])
+
+
+def _vector_consumer(rows_index: list[str], cols: int, block: int, width: int, loads: list[tuple[str, str, bool]], steps, result: str,
+                     output: str) -> str:
+    """The elementwise loop of a row kernel: `width` consecutive columns per thread step. loads:
+    (value prefix, buffer, indexed by row too); steps(lane) -> list of (name, op, args) for that lane."""
+    column = mul(lit(width), var('j')) if width > 1 else var('j')
+    body = []
+    for prefix, buffer, by_row in loads:
+        body.append(load(tuple(f'{prefix}{lane}' for lane in range(width)), buffer, [*(rows_index if by_row else []), column]))
+    for lane in range(width):
+        body += [assign(name, op, args) for name, op, args in steps(lane)]
+    body.append(write(output, [*rows_index, column], tuple(f'{result}{lane}' for lane in range(width))))
+    return strided_loop(axis('j', cols // width), var('lane_id'), lit(block), body)
+
+
+def rms_norm_example(rows: int = 64, cols: int = 1024, block: int = 128, epsilon: float = 1e-5, seeds=(0, 1)) -> tuple[dict, dict]:
+    """RMS norm, out = x * rsqrt(sum(x^2) / count + eps) * w, in the reference's kernel shape: arguments
+    mean_count[1], add_c1[1], x[rows, cols], w[cols] -> mul_1[rows, cols], one CTA of 128 threads per row, a
+    sum-of-squares loop, the shuffle/tree tail, and a four-wide consumer loop that reloads the row (the form
+    compiler/passes/regforward.py:88-148 forwards through registers)."""
+    _check_rows(rows, cols, block)
+    if cols % (4 * block):
+        raise ValueError('the four-wide consumer needs cols to be a multiple of 4 * block')
+    steps = lambda lane: [(f'scaled{lane}', 'multiply', (f'x{lane}', 'inverse')), (f'y{lane}', 'multiply', (f'scaled{lane}', f'w{lane}'))]
+    body = tile([axis('row', rows), axis('lane_id', block)], [
+        f"Init(name='state', identity=0.0, dtype={F32})",
+        strided_loop(axis('col', cols), var('lane_id'), lit(block),
+                     [load(('value',), 'x', [var('row'), var('col')]), assign('square', 'multiply', ('value', 'value')),
+                      accum('state', 'square', 'add', ('col',))], seed=True),
+        *reduction_tail(('state',), ('state_b',), [assign('state', 'add', ('state', 'state_b'))], block // 32),
+        load(('count',), 'mean_count', [lit(0)]), load(('eps',), 'add_c1', [lit(0)]),
+        assign('mean_square', 'divide', ('state', 'count')), assign('shifted', 'add', ('mean_square', 'eps')),
+        assign('inverse', 'rsqrt', ('shifted',)),
+        _vector_consumer([var('row')], cols, block, 4, [('x', 'x', True), ('w', 'w', False)], steps, 'y', 'mul_1'),
+    ], block)
+    inputs = {'mean_count': ([1], 'f32'), 'add_c1': ([1], 'f32'), 'x': ([rows, cols], 'f32'), 'w': ([cols], 'f32')}
+    graph = _graph('k_rms_norm', body, inputs, ('mul_1', [rows, cols], 'f32'))
+    launch = _row_launch('k_rms_norm', rows, block, [
+        {'name': 'mean_count', 'dtype': 'f32', 'shape': [1], 'data': [float(cols)]},
+        {'name': 'add_c1', 'dtype': 'f32', 'shape': [1], 'data': [float(epsilon)]},
+        {'name': 'x', 'dtype': 'f32', 'shape': [rows, cols], 'seed': seeds[0]},
+        {'name': 'w', 'dtype': 'f32', 'shape': [cols], 'seed': seeds[1]},
+        {'name': 'mul_1', 'dtype': 'f32', 'shape': [rows, cols], 'output': True}], 'mul_1')
+    return graph, _metadata('k_rms_norm', launch, 1e-4, 1e-5, ['x', 'w'], ['mul_1'])
+
+
+def l2_norm_example(rows: int = 64, cols: int = 512, block: int = 128, seed: int = 0) -> tuple[dict, dict]:
+    """L2 norm, out = x / sqrt(sum(x^2)), in the reference's kernel shape (x[64, 512] -> div[64, 512], grid 64 x
+    block 128): sqrt followed by reciprocal, which the reference fuses into rsqrt (compiler/transforms.py:6-9)."""
+    _check_rows(rows, cols, block)
+    if cols % (4 * block):
+        raise ValueError('the four-wide consumer needs cols to be a multiple of 4 * block')
+    steps = lambda lane: [(f'y{lane}', 'multiply', (f'x{lane}', 'inverse'))]
+    body = tile([axis('row', rows), axis('lane_id', block)], [
+        f"Init(name='state', identity=0.0, dtype={F32})",
+        strided_loop(axis('col', cols), var('lane_id'), lit(block),
+                     [load(('value',), 'x', [var('row'), var('col')]), assign('square', 'multiply', ('value', 'value')),
+                      accum('state', 'square', 'add', ('col',))], seed=True),
+        *reduction_tail(('state',), ('state_b',), [assign('state', 'add', ('state', 'state_b'))], block // 32),
+        assign('norm', 'sqrt', ('state',)), assign('inverse', 'reciprocal', ('norm',)),
+        _vector_consumer([var('row')], cols, block, 4, [('x', 'x', True)], steps, 'y', 'div'),
+    ], block)
+    graph = _graph('k_div_reduce', body, {'x': ([rows, cols], 'f32')}, ('div', [rows, cols], 'f32'))
+    launch = _row_launch('k_div_reduce', rows, block, [{'name': 'x', 'dtype': 'f32', 'shape': [rows, cols], 'seed': seed},
+                                                        {'name': 'div', 'dtype': 'f32', 'shape': [rows, cols], 'output': True}], 'div')
+    return graph, _metadata('k_div_reduce', launch, 1e-4, 1e-5, ['x'], ['div'])
+
+
+def row_softmax_example(rows: int = 64, cols: int = 256, block: int = 128, seed: int = 0) -> tuple[dict, dict]:
+    """Row softmax in the form compiler/passes/hybrid_normalizer.py:45-120 matches: an online (maximum, sum)
+    pair in the reduction loop, the pair combined by the shuffle/tree tail, a reciprocal of the sum, and a
+    consumer loop computing reciprocal * exp(x - maximum). Launch shape of the reference's workload:
+    x[64, 256] -> softmax[64, 256], grid 64 x block 128."""
+    _check_rows(rows, cols, block)
+    if cols % block:
+        raise ValueError('cols must be a multiple of block')
+    online = [
+        load(('value',), 'x', [var('row'), var('col')]),
+        assign('top', 'maximum', ('m', 'value')), assign('shift_old', 'subtract', ('m', 'top')), assign('alpha', 'exp', ('shift_old',)),
+        assign('shift_new', 'subtract', ('value', 'top')), assign('beta', 'exp', ('shift_new',)),
+        assign('scaled', 'multiply', ('s', 'alpha')),
+        accum('s', 'beta', 'add', ('col',), base='scaled'), accum('m', 'value', 'maximum', ('col',)),
+    ]
+    merge = [
+        assign('top_b', 'maximum', ('m', 'm_b')), assign('da', 'subtract', ('m', 'top_b')), assign('ea', 'exp', ('da',)),
+        assign('db', 'subtract', ('m_b', 'top_b')), assign('eb', 'exp', ('db',)),
+        assign('sa', 'multiply', ('s', 'ea')), assign('sb', 'multiply', ('s_b', 'eb')),
+        assign('s', 'add', ('sa', 'sb')), assign('m', 'copy', ('top_b',)),
+    ]
+    consumer = strided_loop(axis('j', cols), var('lane_id'), lit(block), [
+        load(('again',), 'x', [var('row'), var('j')]), assign('delta', 'subtract', ('again', 'm')), assign('weight', 'exp', ('delta',)),
+        assign('probability', 'multiply', ('inverse', 'weight')), write('softmax', [var('row'), var('j')], ('probability',)),
+    ])
+    body = tile([axis('row', rows), axis('lane_id', block)], [
+        f"Init(name='m', identity=-3.4028234663852886e+38, dtype={F32})", f"Init(name='s', identity=0.0, dtype={F32})",
+        strided_loop(axis('col', cols), var('lane_id'), lit(block), online, seed=True),
+        *reduction_tail(('m', 's'), ('m_b', 's_b'), merge, block // 32),
+        assign('inverse', 'reciprocal', ('s',)),
+        consumer,
+    ], block)
+    graph = _graph('k_softmax', body, {'x': ([rows, cols], 'f32')}, ('softmax', [rows, cols], 'f32'))
+    launch = _row_launch('k_softmax', rows, block, [{'name': 'x', 'dtype': 'f32', 'shape': [rows, cols], 'seed': seed},
+                                                     {'name': 'softmax', 'dtype': 'f32', 'shape': [rows, cols], 'output': True}], 'softmax')
+    return graph, _metadata('k_softmax', launch, 1e-4, 1e-6, ['x'], ['softmax'])
 
 
 def matmul_example(m: int = 128, n: int = 128, k: int = 128, seeds=(7, 11)) -> tuple[dict, dict]:
@@ -309,6 +493,64 @@ def matmul_example(m: int = 128, n: int = 128, k: int = 128, seeds=(7, 11)) -> t
                        {'name': 'left', 'dtype': 'f32', 'shape': [m, k], 'seed': seeds[0]},
                        {'name': 'result', 'dtype': 'f32', 'shape': [m, n], 'output': True}], 'final': True}
     return graph, _metadata('tensor_matmul', launch, 0.001, 0.001, ['left', 'right'], ['result'])
+
+
+def split_k_matmul_example(m: int = 128, n: int = 64, k: int = 256, depth: int = 4, seeds=(0, 1)) -> tuple[dict, dict]:
+    """Split-K contraction with atomic stores into a zeroed output, in the statement order
+    compiler/passes/gridfold.py:60-62 matches (two copy loops, commit, wait, barrier, product loop, barrier) and
+    with the launch shape of the reference's rectangular matmul workload (x1[256, 64], x0[128, 256] ->
+    matmul[128, 64], zero_outputs = [matmul], grid 512 x block 256).
+
+    The grid is (tile_m, tile_n, split): every CTA multiplies a 32 x depth slice of x0 by a depth x 32 slice of
+    x1 and adds its 32 x 32 partial product into the output; 16 x 16 threads hold 2 x 2 micro-tiles."""
+    if m % 32 or n % 32 or k % depth or depth % 4 or min(m, n, k) <= 0:
+        raise ValueError('the schedule needs M % 32 == 0, N % 32 == 0, K % depth == 0 and depth % 4 == 0')
+    splits = k // depth
+    thread = add(mul(var('thread_m'), lit(16)), var('thread_n'))
+    flat = mul(var('piece'), lit(4))
+
+    def copy_loop(smem: str, source: str, shape: tuple[int, int], origin: tuple[str, str]) -> str:
+        inside = (binary('/', flat, lit(shape[1])), binary('%', flat, lit(shape[1])))
+        copy = (f"CpAsyncCopy(smem={smem!r}, smem_index={_tuple(inside)}, src={source!r}, "
+                f"src_index={_tuple([add(origin[0], inside[0]), add(origin[1], inside[1])])}, nbytes=16, swizzle='NONE', "
+                f"lane_index=None, lane_rows=None)")
+        return strided_loop(axis('piece', shape[0] * shape[1] // 4), thread, lit(256), [copy])
+
+    k_origin = add(mul(var('split'), lit(depth)), var('k0'))
+    inner = []
+    for j in range(2):
+        inner.append(load((f'b{j}',), 'rhs_tile', [var('inner_k'), add(mul(var('thread_n'), lit(2)), lit(j))], 'None'))
+    for i in range(2):
+        inner.append(load((f'a{i}',), 'lhs_tile', [add(mul(var('thread_m'), lit(2)), lit(i)), var('inner_k')], 'None'))
+    for i in range(2):
+        for j in range(2):
+            inner += [assign(f'p{i}{j}', 'multiply', (f'b{j}', f'a{i}')), accum(f'acc{i}{j}', f'p{i}{j}', 'add', ('inner_k',))]
+    outer = strided_loop(axis('k0', depth), lit(0), lit(depth), [
+        copy_loop('lhs_tile', 'x0', (32, depth), (mul(var('tile_m'), lit(32)), k_origin)),
+        copy_loop('rhs_tile', 'x1', (depth, 32), (k_origin, mul(var('tile_n'), lit(32)))),
+        'CpAsyncCommit()', 'CpAsyncWait(group=0)', 'Sync(barrier_id=0, count=None, warp=False)',
+        loop(axis('inner_k', depth), inner, unroll=True),
+        'Sync(barrier_id=0, count=None, warp=False)',
+    ])
+    stores = []
+    for i in range(2):
+        row = add(add(mul(var('tile_m'), lit(32)), mul(var('thread_m'), lit(2))), lit(i))
+        col = add(mul(var('tile_n'), lit(32)), mul(var('thread_n'), lit(2)))
+        stores.append(write('matmul', [row, col], (f'acc{i}0', f'acc{i}1'), atomic=True))
+    body = tile([axis('tile_m', m // 32), axis('tile_n', n // 32), axis('split', splits), axis('thread_m', 16), axis('thread_n', 16)], [
+        *[f"Init(name='acc{i}{j}', identity=0.0, dtype={F32})" for i in range(2) for j in range(2)],
+        f"Smem(name='lhs_tile', extents=(32, {depth}), dtype='float', align=16)",
+        f"Smem(name='rhs_tile', extents=({depth}, 32), dtype='float', align=16)",
+        outer, *stores,
+    ], 256)
+    graph = _graph('k_matmul', body, {'x0': ([m, k], 'f32'), 'x1': ([k, n], 'f32')}, ('matmul', [m, n], 'f32'))
+    graph['nodes']['matmul']['inputs'] = ['x1', 'x0']
+    launch = {'node': 'matmul', 'entry': 'k_matmul', 'arg_order': ['x1', 'x0', 'matmul'], 'grid': [(m // 32) * (n // 32) * splits, 1, 1],
+              'block': [256, 1, 1], 'smem_bytes': 0, 'zero_outputs': ['matmul'],
+              'args': [{'name': 'x1', 'dtype': 'f32', 'shape': [k, n], 'seed': seeds[1]},
+                       {'name': 'x0', 'dtype': 'f32', 'shape': [m, k], 'seed': seeds[0]},
+                       {'name': 'matmul', 'dtype': 'f32', 'shape': [m, n], 'output': True}], 'final': True}
+    return graph, _metadata('k_matmul', launch, 0.001, 0.001, ['x0', 'x1'], ['matmul'])
 
 
 def gqa_attention_example(batch: int = 4, query_heads: int = 32, kv_heads: int = 8, positions: int = 4096, depth: int = 128,

@@ -43,6 +43,12 @@ extern "C" {
 #define DTN_REDUCE_SUM 0
 #define DTN_REDUCE_MAX 1
 #define DTN_REDUCE_SUMSQ 2
+#define DTN_REDUCE_SOFTMAX 3 /* dtn_row_fused only: row maximum and the sum of exp(x - maximum) */
+
+/* kind of an extra input of dtn_row_fused */
+#define DTN_ROW_INPUT_SCALAR 0    /* one-element f32 buffer, broadcast (constants arrive this way) */
+#define DTN_ROW_INPUT_COLUMNS 1   /* f32[cols], indexed by the column (a weight vector) */
+#define DTN_ROW_INPUT_IMMEDIATE 2 /* a literal of the IR; the value is taken from input_immediate */
 
 /* storage type of attention operands */
 #define DTN_STORAGE_F32 0
@@ -129,6 +135,28 @@ int dtn_f16_narrow(const float* src, uint16_t* dst, int64_t n, void* stream);
  * identity -inf. */
 int dtn_row_reduce_f32(int op, const float* x, float* out, int64_t rows, int64_t cols,
                        int64_t ldx, void* stream);
+
+/* Row reduction, a scalar stage and an elementwise stage over the same row in one launch:
+ * row softmax, RMS norm, L2 norm, mean. Replaces the kernels the reference builds from a reduction
+ * loop, a shuffle/tree tail and a consumer loop with load forwarding
+ * (compiler/passes/regforward.py:150-269) and with the softmax normaliser
+ * (compiler/passes/hybrid_normalizer.py:45-183).
+ *   reduce_op: DTN_REDUCE_SUM / SUMSQ / MAX / SOFTMAX over x[r, 0..cols), leading dimension ldx.
+ *   Program registers (12): 0 = reduced value, 1 = sum of exp(x - max) (SOFTMAX, else 0),
+ *   2 = the row element (elementwise stage), 3 + i = extra input i, the rest are temporaries.
+ *   Instructions [0, n_scalar_instr) run once per row, [n_scalar_instr, n_instr) once per element;
+ *   instruction j is dsts[j] = ops[j](as[j], bs[j]) with DTN_EW_* codes. At most 32 instructions
+ *   and 5 extra inputs.
+ *   ldo > 0: out[r, c] = register out_reg after the elementwise stage. ldo == 0: out[r] = register
+ *   out_reg after the scalar stage (n_scalar_instr must equal n_instr).
+ * exp is ex2.approx(x * log2 e), sqrt/rsqrt/reciprocal/divide are the approximate instructions, as in
+ * the reference's default approximate_math lowering (compiler/codegen/lower.py:259-289,
+ * compiler/ptx.py:41). Rows of up to 8192 aligned values are read from memory once. */
+int dtn_row_fused(int reduce_op, const float* x, int64_t rows, int64_t cols, int64_t ldx,
+                  const void* const* inputs, const unsigned char* input_kind,
+                  const float* input_immediate, int n_inputs, const unsigned char* ops,
+                  const unsigned char* dsts, const unsigned char* as, const unsigned char* bs,
+                  int n_scalar_instr, int n_instr, int out_reg, float* out, int64_t ldo, void* stream);
 
 /* Bytes of scratch dtn_gemm_x3 needs for (mode, M, N, K): the bf16 (or tf32) high and
  * residual planes of A and of B transposed. 0 for DTN_GEMM_F32. */

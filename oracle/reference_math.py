@@ -292,6 +292,35 @@ def row_max(x: np.ndarray) -> np.ndarray:
     return np.fmax(np.fmax.reduce(x, axis=1), np.float32(-np.inf)).astype(np.float32)
 
 
+def row_softmax_f64(x: np.ndarray) -> np.ndarray:
+    """exp(x - max) / sum(exp(x - max)) per row in float64: what the reference's row-softmax kernel
+    (compiler/passes/hybrid_normalizer.py:139-183: maximum, sum of exponentials, reciprocal, product) approximates."""
+    x64 = np.asarray(x, dtype=np.float64)
+    weights = np.exp(x64 - x64.max(axis=1, keepdims=True))
+    return weights / weights.sum(axis=1, keepdims=True)
+
+
+def rms_norm_f64(x: np.ndarray, weight: np.ndarray, count: float, epsilon: float) -> np.ndarray:
+    """x * rsqrt(sum(x^2) / count + epsilon) * weight in float64 (the reference's RMS-norm workload: a sum of squares
+    (compiler/transforms.py:62-95), scalar divide / add / rsqrt (compiler/codegen/lower.py:259-289), a forwarded
+    consumer loop (compiler/passes/regforward.py:150-269))."""
+    x64 = np.asarray(x, dtype=np.float64)
+    scale = 1.0 / np.sqrt((x64 * x64).sum(axis=1, keepdims=True) / float(count) + float(epsilon))
+    return x64 * scale * np.asarray(weight, dtype=np.float64)[None, :]
+
+
+def l2_norm_f64(x: np.ndarray) -> np.ndarray:
+    """x / sqrt(sum(x^2)) per row in float64 (sqrt followed by reciprocal, fused by compiler/transforms.py:6-9)."""
+    x64 = np.asarray(x, dtype=np.float64)
+    return x64 / np.sqrt((x64 * x64).sum(axis=1, keepdims=True))
+
+
+def row_mean_f64(x: np.ndarray, count: float | None = None) -> np.ndarray:
+    """sum(x) / count per row in float64 (the count arrives as a one-element buffer in the reference's mean workload)."""
+    x64 = np.asarray(x, dtype=np.float64)
+    return x64.sum(axis=1) / float(x64.shape[1] if count is None else count)
+
+
 def row_sum_error_bound(x: np.ndarray) -> np.ndarray:
     """Bound on |fp32 tree sum - exact| per row for any summation order: (n-1) * eps * sum|x|."""
     x64 = np.abs(np.asarray(x, dtype=np.float64))

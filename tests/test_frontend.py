@@ -78,10 +78,24 @@ def test_generated_schedules_classify(golden):
         (schedules.row_reduce_example(8, 4096, 'max'), 'row_reduce', {'op': 'max', 'rows': 8, 'cols': 4096}),
         (schedules.row_reduce_example(8, 4096, 'sumsq'), 'row_reduce', {'op': 'sumsq', 'rows': 8, 'cols': 4096}),
         (schedules.matmul_example(256, 512, 1024), 'gemm', {'mode': 'bf16x3', 'm': 256, 'n': 512, 'k': 1024}),
+        (schedules.split_k_matmul_example(), 'gemm', {'mode': 'bf16x3', 'm': 128, 'n': 64, 'k': 256}),
+        (schedules.mean_example(), 'row_fused',
+         {'reduce': 'sum', 'rows': 1, 'cols': 32768, 'per_row': True, 'inputs': [{'kind': 'scalar'}], 'n_scalar': 1, 'out_reg': 4,
+          'ops': [3], 'dst': [4], 'a': [0], 'b': [3]}),
+        (schedules.l2_norm_example(), 'row_fused',
+         {'reduce': 'sumsq', 'rows': 64, 'cols': 512, 'per_row': False, 'inputs': [], 'n_scalar': 2, 'out_reg': 4,
+          'ops': [8, 10, 2], 'dst': [3, 3, 4], 'a': [0, 3, 3], 'b': [0, 3, 2]}),
+        (schedules.row_softmax_example(), 'row_fused',
+         {'reduce': 'softmax', 'rows': 64, 'cols': 256, 'per_row': False, 'inputs': [], 'n_scalar': 1, 'out_reg': 4,
+          'ops': [10, 1, 7, 2], 'dst': [3, 4, 4, 4], 'a': [1, 2, 4, 4], 'b': [1, 0, 4, 3]}),
     ]
     for (graph, meta), kind, params in cases:
         plan = compile_kernel(graph, meta).plan
         assert plan.kind == kind and plan.params == params
+    rms = compile_kernel(*schedules.rms_norm_example()).plan
+    assert rms.kind == 'row_fused' and rms.params['reduce'] == 'sumsq' and rms.params['n_scalar'] == 3
+    assert [i['kind'] for i in rms.params['inputs']] == ['columns', 'scalar', 'scalar']
+    assert rms.buffers == {'x': ('x', 0), 'out': ('mul_1', 0), 'in0': ('w', 0), 'in1': ('mean_count', 0), 'in2': ('add_c1', 0)}
     narrow = compile_kernel(*schedules.f16_storage_example('narrow', 512, 4, offset=1)).plan
     assert narrow.buffers['x'] == ('x', 1)  # the unaligned origin travels as an element offset
     # the generated 128^3 schedule has the statement census of the reference's committed IR
@@ -102,6 +116,24 @@ def test_unsupported_schedules_raise_not_implemented(vector_add):
     body = graph['nodes']['result']['op_fields']['body'][0].replace('atomic=False', 'atomic=True')
     set_body(graph, body)
     with pytest.raises(NotImplementedError, match='atomic'):
+        compile_kernel(graph, meta)
+    # split-K: the output must be zeroed by the launch, and the splits must cover the whole reduction
+    graph, meta = schedules.split_k_matmul_example()
+    meta['kernels'][0]['zero_outputs'] = []
+    with pytest.raises(NotImplementedError, match='zero_outputs'):
+        compile_kernel(graph, meta)
+    graph, meta = schedules.split_k_matmul_example()
+    set_body(graph, graph['nodes']['matmul']['op_fields']['body'][0].replace("Axis(name='split', extent=Dim(64)", "Axis(name='split', extent=Dim(32)"))
+    with pytest.raises(NotImplementedError, match='cover'):
+        compile_kernel(graph, meta)
+    # row kernels: a two-state reduction that is not the online softmax pair, and lanes that mix vector elements
+    graph, meta = schedules.row_softmax_example()
+    set_body(graph, graph['nodes']['softmax']['op_fields']['body'][0].replace("Assign(name='alpha', op=ElementwiseImpl('exp')", "Assign(name='alpha', op=ElementwiseImpl('sqrt')", 1))
+    with pytest.raises(NotImplementedError, match='online maximum'):
+        compile_kernel(graph, meta)
+    graph, meta = schedules.l2_norm_example()
+    set_body(graph, graph['nodes']['div']['op_fields']['body'][0].replace("values=('y0', 'y1', 'y2', 'y3')", "values=('y1', 'y0', 'y2', 'y3')"))
+    with pytest.raises(NotImplementedError, match='mix vector elements'):
         compile_kernel(graph, meta)
 
 

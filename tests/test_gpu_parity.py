@@ -114,6 +114,18 @@ def test_fused_elementwise_programs_at_size_and_misalignment(runner, cuda):
     np.testing.assert_array_equal(out.cpu().numpy(), expected)
 
 
+def test_pointwise_workloads_are_exact(runner):
+    """x * 2 + 1 and relu(x) * y in the reference's launch shapes: one rounding per operator, so NumPy's FP32 result
+    is reproduced bit for bit."""
+    normal = lambda seed, n: np.random.default_rng(seed).standard_normal(n).astype(np.float32)
+    graph, meta = schedules.pointwise_example('affine', 4096)
+    got = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta), warmup=0, iters=1, samples=1)['outputs']['add']
+    np.testing.assert_array_equal(got, normal(0, 4096) * np.float32(2.0) + np.float32(1.0))
+    graph, meta = schedules.pointwise_example('relu_multiply', 2048)
+    got = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta), warmup=0, iters=1, samples=1)['outputs']['mul']
+    np.testing.assert_array_equal(got, np.maximum(normal(0, 2048), np.float32(0.0)) * normal(1, 2048))
+
+
 def test_all_half_bits_copy_exactly_at_scalar_and_vector_widths(runner):
     data = np.arange(65536, dtype=np.uint16).view(np.float16)
     for width in (1, 2, 4):
@@ -251,6 +263,96 @@ def test_row_reductions_full_size(cuda):
     assert bool(((sums.double() - exact).abs() <= bound).all())
     # sum of the row sums equals the sum of everything (float64, order-free up to rounding)
     assert abs(float(sums.double().sum()) - float(exact.sum())) < 1.0
+
+
+# ------------------------------------------------------------------------------------------------
+# fused row kernels: softmax, RMS norm, L2 norm, mean
+# Bars: relative 1e-5 of the float64 result (ex2.approx, rsqrt.approx, rcp.approx and div.approx are each good to
+# about 2^-22 and at most three of them are chained), plus an absolute floor for values that underflow in FP32.
+# ------------------------------------------------------------------------------------------------
+
+ROW_RTOL = 1e-5
+
+
+def test_row_kernels_in_the_reference_launch_shapes(runner):
+    run = lambda graph, meta: runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta, arch='sm_100a'), warmup=0, iters=1,
+                                                samples=1)['outputs']
+    normal = lambda seed, shape: np.random.default_rng(seed).standard_normal(shape).astype(np.float32)
+    got = run(*schedules.row_softmax_example())['softmax']
+    np.testing.assert_allclose(got, R.row_softmax_f64(normal(0, (64, 256))), rtol=ROW_RTOL, atol=1e-12)
+    np.testing.assert_allclose(got.astype(np.float64).sum(axis=1), 1.0, rtol=0, atol=1e-5)
+    got = run(*schedules.rms_norm_example())['mul_1']
+    np.testing.assert_allclose(got, R.rms_norm_f64(normal(0, (64, 1024)), normal(1, (1024,)), 1024.0, 1e-5), rtol=ROW_RTOL, atol=1e-7)
+    got = run(*schedules.l2_norm_example())['div']
+    np.testing.assert_allclose(got, R.l2_norm_f64(normal(0, (64, 512))), rtol=ROW_RTOL, atol=1e-9)
+    got = run(*schedules.mean_example())['mean']
+    x = normal(0, (1, 32768))
+    assert abs(float(got[0]) - float(R.row_mean_f64(x)[0])) <= float(R.row_sum_error_bound(x)[0]) / 32768 + 1e-9
+
+
+@pytest.mark.parametrize('rows,cols', [(64, 256), (5, 1000), (3, 1001), (1, 8192), (2, 8196), (7, 40000), (300, 33), (1, 1), (1100, 512)])
+def test_row_kernels_against_float64_at_many_shapes(cuda, rows, cols):
+    x = R.seeded_normal(7, (rows, cols)) * np.float32(3.0)
+    w = R.seeded_normal(8, (cols,))
+    dx, dw = to_device(cuda, x), to_device(cuda, w)
+    np.testing.assert_allclose(ops.row_softmax(dx).cpu().numpy(), R.row_softmax_f64(x), rtol=ROW_RTOL, atol=1e-12)
+    np.testing.assert_allclose(ops.rms_norm(dx, dw, 1e-5).cpu().numpy(), R.rms_norm_f64(x, w, cols, 1e-5), rtol=ROW_RTOL, atol=1e-7)
+    np.testing.assert_allclose(ops.l2_norm(dx).cpu().numpy(), R.l2_norm_f64(x), rtol=ROW_RTOL, atol=1e-9)
+    bound = R.row_sum_error_bound(x) / cols + 5e-7 * np.abs(R.row_mean_f64(x)) + 1e-12   # div.approx is good to 2 ulp
+    assert np.all(np.abs(ops.row_mean(dx).cpu().numpy() - R.row_mean_f64(x)) <= bound)
+
+
+def test_row_kernel_edge_cases(cuda):
+    # strided rows and a misaligned origin take the scalar path and give the same values as the aligned path
+    base = cuda.randn((16, 1030), device='cuda:0', generator=cuda.Generator(device='cuda:0').manual_seed(3))
+    view = base[:, 1:1025]
+    dense = view.contiguous()
+    for op in (ops.row_softmax, ops.l2_norm):
+        np.testing.assert_allclose(op(view).cpu().numpy(), op(dense).cpu().numpy(), rtol=2e-6, atol=1e-12)
+    # a row of equal values, a row with one dominant value, large magnitudes (no overflow: the maximum is subtracted first)
+    x = np.zeros((3, 512), dtype=np.float32)
+    x[0, :] = 5.0
+    x[1, 17] = 80.0
+    x[2, :] = np.linspace(-3.0e4, 3.0e4, 512, dtype=np.float32)
+    got = ops.row_softmax(to_device(cuda, x)).cpu().numpy()
+    np.testing.assert_allclose(got, R.row_softmax_f64(x), rtol=ROW_RTOL, atol=1e-30)
+    assert np.isfinite(got).all() and got[1, 17] == 1.0
+    # empty inputs
+    assert ops.row_softmax(cuda.empty((0, 8), device='cuda:0')).shape == (0, 8)
+    assert ops.row_mean(cuda.empty((0, 8), device='cuda:0')).numel() == 0
+    with pytest.raises(ValueError):
+        ops.row_softmax(cuda.zeros(4, device='cuda:0'))
+    with pytest.raises(ValueError):
+        ops.rms_norm(cuda.zeros((4, 8), device='cuda:0'), cuda.zeros(3, device='cuda:0'))
+
+
+def test_row_kernels_full_size(cuda):
+    """65536 x 4096 (1 GiB): size-independent properties. Softmax rows sum to one and are invariant under a shift of the
+    row; normalised rows have unit norm; the RMS norm with unit weight has mean square one."""
+    rows, cols = 65536, 4096
+    x = cuda.randn((rows, cols), device='cuda:0', generator=cuda.Generator(device='cuda:0').manual_seed(7))
+    out = ops.row_softmax(x)
+    assert float((out.double().sum(dim=1) - 1.0).abs().max()) < 1e-5
+    reference = cuda.softmax(x[:64].double(), dim=1)
+    assert bool(((out[:64].double() - reference).abs() <= ROW_RTOL * reference + 1e-12).all())
+    x.add_(100.0)
+    shifted = ops.row_softmax(x)
+    assert float((shifted - out).abs().max()) < 2e-4 * float(out.max())   # x + 100 rounds the inputs to 2^-17
+    x.sub_(100.0)
+    del shifted
+    ops.l2_norm(x, out=out)
+    assert float(((out.double() ** 2).sum(dim=1) - 1.0).abs().max()) < 1e-5
+    ops.rms_norm(x, cuda.ones(cols, device='cuda:0'), 0.0, out=out)
+    assert float(((out.double() ** 2).mean(dim=1) - 1.0).abs().max()) < 1e-5
+    means = ops.row_mean(x)
+    assert float((means.double() - x.double().mean(dim=1)).abs().max()) < 1e-5
+
+
+def test_split_k_contraction_is_the_full_product(runner):
+    graph, meta = schedules.split_k_matmul_example()
+    produced = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta, arch='sm_100a'), warmup=0, iters=1, samples=1)['outputs']['matmul']
+    normal = lambda seed, shape: np.random.default_rng(seed).standard_normal(shape).astype(np.float32)
+    np.testing.assert_allclose(produced, R.gemm_f64(normal(0, (128, 256)), normal(1, (256, 64))), rtol=1e-3, atol=1e-3)
 
 
 # ------------------------------------------------------------------------------------------------

@@ -140,3 +140,17 @@ def test_row_reductions():
     assert R.row_max(np.full((1, 4), np.nan, np.float32))[0] == -np.inf
     assert R.row_max(np.zeros((2, 0), np.float32)).tolist() == [-np.inf, -np.inf]
     np.testing.assert_allclose(R.row_sum_f64(x[:2]), x[:2].astype(np.float64).sum(axis=1))
+
+
+def test_row_kernel_oracles():
+    x = R.seeded_normal(7, (5, 300)) * np.float32(4.0)
+    soft = R.row_softmax_f64(x)
+    assert np.allclose(soft.sum(axis=1), 1.0, rtol=0, atol=1e-14) and (soft > 0).all()
+    assert np.allclose(R.row_softmax_f64(x + np.float32(2.0)), soft, rtol=1e-5)        # shift invariance (inputs re-rounded)
+    assert np.allclose((R.l2_norm_f64(x) ** 2).sum(axis=1), 1.0, rtol=0, atol=1e-13)
+    unit = R.rms_norm_f64(x, np.ones(300, dtype=np.float32), 300.0, 0.0)
+    assert np.allclose((unit ** 2).mean(axis=1), 1.0, rtol=0, atol=1e-13)
+    w = R.seeded_normal(8, (300,))
+    assert np.allclose(R.rms_norm_f64(x, w, 300.0, 0.0), unit * w.astype(np.float64)[None, :], rtol=1e-15)
+    assert np.allclose(R.row_mean_f64(x), x.astype(np.float64).mean(axis=1), rtol=1e-15)
+    assert np.allclose(R.row_mean_f64(x, 150.0), 2.0 * R.row_mean_f64(x), rtol=1e-15)
