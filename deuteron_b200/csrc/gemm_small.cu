@@ -11,6 +11,8 @@
 // published outputs are reproduced bit for bit), and a 16x64 tile with a 64-deep k-tile and two
 // groups of four warps that each take half of the k-tile (at most 16 rows).
 // Any M, N, K and leading dimensions: out-of-range elements are zero-filled by the copies.
+#include <stdlib.h>
+
 #include "dtn_common.cuh"
 
 namespace dtn {
@@ -28,7 +30,7 @@ struct SmallCfg {
   static constexpr int kStageFloats = BM * kLda + BK * kLdb;
   static constexpr int kSmemBytes = STAGES * kStageFloats * 4;
   static constexpr int kMI = BM == 64 ? 2 : 1;                 // m16 tiles per warp
-  static constexpr int kNI = BM == 64 ? 4 : 2;                 // n8 tiles per warp
+  static constexpr int kNI = BM == 16 ? 2 : 4;                 // n8 tiles per warp
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src, int valid_bytes) {
@@ -84,7 +86,7 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   const int tid = threadIdx.x, warp = (tid >> 5) & 3, kgroup = tid >> 7, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * S_BN;
-  const int wm = BM == 64 ? (warp >> 1) * 32 : 0, wn = BM == 64 ? (warp & 1) * 32 : warp * 16;
+  const int wm = BM == 64 ? (warp >> 1) * 32 : (BM == 32 ? (warp >> 1) * 16 : 0), wn = BM == 16 ? warp * 16 : (warp & 1) * 32;
   const uint32_t smem_base = smem_u32(small_smem);
 
   auto load_tile = [&](int kt, int slot) {
@@ -270,12 +272,35 @@ template <int MODE>
 static int gemm_small_launch_mode(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                                   int64_t ldb, int64_t ldc, cudaStream_t s) {
   const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 8) && lda % 4 == 0 && ldb % 4 == 0 && ldc % 2 == 0;
-  const bool skinny = M <= 16 && K >= 256;
-  if (skinny)
-    return aligned ? gemm_small_launch_cfg<MODE, true, 16, 64, 4, 2>(A, B, C, M, N, K, lda, ldb, ldc, s)
-                   : gemm_small_launch_cfg<MODE, false, 16, 64, 4, 2>(A, B, C, M, N, K, lda, ldb, ldc, s);
-  return aligned ? gemm_small_launch_cfg<MODE, true, 64, 32, 4, 1>(A, B, C, M, N, K, lda, ldb, ldc, s)
-                 : gemm_small_launch_cfg<MODE, false, 64, 32, 4, 1>(A, B, C, M, N, K, lda, ldb, ldc, s);
+  static const int forced = [] {
+    const char* text = getenv("DTN_GEMM_SMALL_CFG");   // tuning aid: 1..7 pick a configuration, anything else = automatic
+    return text ? atoi(text) : 0;
+  }();
+#define DTN_SMALL_CFG(BM, BK, KS)                                                                             \
+  return aligned ? gemm_small_launch_cfg<MODE, true, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s)        \
+                 : gemm_small_launch_cfg<MODE, false, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s)
+  int choice = forced;
+  if (choice < 1 || choice > 7) {
+    // Measured on B200 (us, bf16x3): 128^3 3.1 with 16-row tiles against 5.2 with 64-row tiles, 128x64x256 4.8 / 8.5,
+    // 256^3 5.2 / 8.8, 512^3 10.4 (32-row tiles, two k groups) / 15.5, 16x8192x8192 95 (two k groups) / 215.
+    // The 16-row single-group configuration keeps the sequential-k accumulation order, so small products stay
+    // bit-identical to the reference's emitted kernel.
+    const double volume = (double)M * (double)N * (double)K;
+    if (M <= 16 && K >= 256) choice = 2;
+    else if (volume <= 320.0 * 320.0 * 320.0) choice = 3;
+    else if (volume <= 520.0 * 520.0 * 520.0 && M >= 32) choice = 6;
+    else choice = 1;
+  }
+  switch (choice) {
+    case 2: DTN_SMALL_CFG(16, 64, 2);
+    case 3: DTN_SMALL_CFG(16, 64, 1);
+    case 4: DTN_SMALL_CFG(32, 32, 1);
+    case 5: DTN_SMALL_CFG(32, 64, 1);
+    case 6: DTN_SMALL_CFG(32, 64, 2);
+    case 7: DTN_SMALL_CFG(16, 32, 1);
+    default: DTN_SMALL_CFG(64, 32, 1);
+  }
+#undef DTN_SMALL_CFG
 }
 
 // mode: DTN_GEMM_BF16X3 or DTN_GEMM_TF32X3

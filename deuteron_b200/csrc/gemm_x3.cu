@@ -32,10 +32,10 @@ int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_
 
 // Problems for which the single-kernel path (operand split inside the kernel, no workspace) is
 // faster than split pass + tcgen05 kernel: so little work that launches and set-up dominate
-// (measured on B200: 5.3 vs 9.9 us at 128^3, 8.8 vs 11.8 us at 256^3, 15.5 vs 14.1 us at 512^3).
+// (measured on B200: 3.1 vs 9.9 us at 128^3, 5.2 vs 11.8 us at 256^3, 10.4 vs 11.7 us at 512^3).
 static bool prefers_small_kernel(int64_t M, int64_t N, int64_t K) {
   if (M <= 16) return true;   // skinny: bound by one pass over B, which only the single-kernel path achieves
-  return (double)M * (double)N * (double)K <= 320.0 * 320.0 * 320.0;
+  return (double)M * (double)N * (double)K <= 520.0 * 520.0 * 520.0;
 }
 
 // ---------------------------------------------------------------------------------------

@@ -5,15 +5,22 @@
 // The reference reaches the same fusion by rewriting the scheduled IR: load forwarding keeps the row
 // in registers between the reduction loop and the consumer loop (compiler/passes/regforward.py:150-269)
 // and the softmax normaliser replaces the online (max, sum) pair by a max pass followed by a sum of
-// exponentials over cached values (compiler/passes/hybrid_normalizer.py:139-183). Here the row is
-// read once with 128-bit loads into at most eight vectors per thread, reduced by a butterfly shuffle
-// (and one shared-memory round when a whole CTA shares the row), and written once; longer or
-// unaligned rows take the same code through loops that re-read the row (mostly from L2).
+// exponentials over cached values (compiler/passes/hybrid_normalizer.py:139-183). Here a group of
+// 8 to 256 threads owns a row: the row is read once with 128-bit loads into eight vectors per thread,
+// reduced by a butterfly shuffle (plus one shared-memory round when the group spans warps), and
+// written once; longer rows take the same code chunk by chunk and re-read the row (mostly from L2).
 //
 // The two stages arrive as one short register program: instructions [0, n_scalar) run once per row
 // on the reduced value and the one-element inputs, the rest run per element. Register 0 holds the
 // reduced value, register 1 the sum of exp(x - max) for the softmax reduction, register 2 the row
 // element, registers 3.. the extra inputs in order; the others are temporaries.
+//
+// Chain form. In the workloads this kernel exists for, the elementwise stage is a chain: every
+// instruction combines the running value with a per-row scalar, a per-column input, the row element
+// or itself (softmax: x - max, exp, * 1/sum; RMS norm: x * scale, * w). A chain needs no register
+// file per element: the operator is decoded once per row and step, outside the loop over the
+// thread's 32 cached elements, so the cost per element is the arithmetic alone. Programs that are
+// not chains run on a per-element interpreter (correct for any program, several times slower).
 #include <math.h>
 
 #include "dtn_common.cuh"
@@ -25,19 +32,31 @@ constexpr int kRowRegs = 12;
 constexpr int kRowMaxInstr = 32;
 constexpr int kRowMaxInputs = 5;
 constexpr int kRowCacheVecs = 8;   // 128-bit vectors of the row one thread keeps in registers
+constexpr int kChainMax = 16;
+enum { CHAIN_SCALAR = 0, CHAIN_COLUMNS = 1, CHAIN_ELEMENT = 2, CHAIN_SELF = 3 };
 
 struct RowProgram {
-  int n_inputs, n_scalar, n_instr, out_reg;
+  int reduce, n_inputs, n_scalar, n_instr, out_reg;
   const float* input[kRowMaxInputs];
   float immediate[kRowMaxInputs];
   unsigned char kind[kRowMaxInputs];
   unsigned char op[kRowMaxInstr], dst[kRowMaxInstr], a[kRowMaxInstr], b[kRowMaxInstr];
 };
 
-// Combines one value per thread over the TPR threads that share a row.
+struct RowChain {
+  int n;
+  unsigned char op[kChainMax], kind[kChainMax], index[kChainMax], swap[kChainMax];   // index: register (scalar) or input (columns)
+};
+
+// Combines one value per thread over the TPR threads that share a row (TPR lanes of a warp, or all warps of the CTA).
 template <int TPR, bool MAX>
 __device__ __forceinline__ float row_combine(float v, float* scratch) {
-  v = MAX ? warp_max(v) : warp_sum(v);
+  constexpr int kLanes = TPR < 32 ? TPR : 32;
+#pragma unroll
+  for (int o = kLanes / 2; o > 0; o >>= 1) {
+    const float w = __shfl_xor_sync(0xffffffffu, v, o);
+    v = MAX ? fmaxf(v, w) : v + w;
+  }
   if constexpr (TPR > 32) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) scratch[warp] = v;
@@ -49,15 +68,239 @@ __device__ __forceinline__ float row_combine(float v, float* scratch) {
   return v;
 }
 
-template <int RED>
-__device__ __forceinline__ float fold_first(float acc, float v) {
-  if constexpr (RED == DTN_REDUCE_SUM) return acc + v;
-  if constexpr (RED == DTN_REDUCE_SUMSQ) return fmaf(v, v, acc);
+__device__ __forceinline__ float fold_first(int reduce, float acc, float v) {
+  if (reduce == DTN_REDUCE_SUM) return acc + v;
+  if (reduce == DTN_REDUCE_SUMSQ) return fmaf(v, v, acc);
   return fmaxf(acc, v);   // max and softmax
 }
 
-// The elementwise stage on W consecutive elements starting at column `col` (W = 2 needs col even and the
-// column inputs 8-byte aligned there, which the aligned modes guarantee).
+// Scalar stage: the reduced values, the one-element inputs and the literals go into registers, then
+// instructions [0, n_scalar) run. Every thread of the row computes the same values.
+__device__ __forceinline__ void scalar_stage(const RowProgram& prog, float first, float second, RegFile<kRowRegs, 1>& scalars) {
+#pragma unroll
+  for (int k = 0; k < kRowRegs; ++k) scalars.r[k][0] = 0.0f;
+  scalars.r[0][0] = first;
+  scalars.r[1][0] = second;
+#pragma unroll
+  for (int i = 0; i < kRowMaxInputs; ++i) {
+    if (i < prog.n_inputs && prog.kind[i] != DTN_ROW_INPUT_COLUMNS) {
+      const float v[1] = {prog.kind[i] == DTN_ROW_INPUT_IMMEDIATE ? prog.immediate[i] : __ldg(prog.input[i])};
+      scalars.put(3 + i, v);
+    }
+  }
+  for (int n = 0; n < prog.n_scalar; ++n) {
+    float a[1], b[1], d[1];
+    scalars.get(prog.a[n], a);
+    scalars.get(prog.b[n], b);
+    d[0] = prog_apply(prog.op[n], a[0], b[0]);
+    scalars.put(prog.dst[n], d);
+  }
+}
+
+template <int OP>
+__device__ __forceinline__ float chain_op(float a, float o, bool swap) {
+  if constexpr (OP == DTN_EW_ADD) return __fadd_rn(a, o);
+  if constexpr (OP == DTN_EW_SUB) return swap ? __fsub_rn(o, a) : __fsub_rn(a, o);
+  if constexpr (OP == DTN_EW_MUL) return __fmul_rn(a, o);
+  if constexpr (OP == DTN_EW_DIV) return swap ? __fdividef(o, a) : __fdividef(a, o);
+  if constexpr (OP == DTN_EW_MAX) return fmaxf(a, o);
+  if constexpr (OP == DTN_EW_MIN) return fminf(a, o);
+  return prog_apply(OP, a, a);   // unary operators (constant-folded switch)
+}
+
+// Unit u of a thread's chunk covers four consecutive columns of one 128-bit vector (VEC) or four
+// columns TPR apart (scalar accesses).
+template <int TPR, bool VEC>
+__device__ __forceinline__ int64_t chain_column(int64_t chunk_base, int rank, int u, int lane) {
+  if constexpr (VEC) return chunk_base + ((int64_t)rank + (int64_t)u * TPR) * 4 + lane;
+  return chunk_base + rank + (int64_t)(u * 4 + lane) * TPR;
+}
+
+template <int OP, int TPR, bool VEC>
+__device__ __forceinline__ void chain_step(float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int kind, float scalar,
+                                           const float* __restrict__ columns, bool swap, int64_t chunk_base, int rank, int64_t cols) {
+#pragma unroll
+  for (int u = 0; u < kRowCacheVecs; ++u) {
+    float o[4];
+    if (kind == CHAIN_SCALAR) {
+      o[0] = o[1] = o[2] = o[3] = scalar;
+    } else if (kind == CHAIN_ELEMENT) {
+      o[0] = kept[u].x; o[1] = kept[u].y; o[2] = kept[u].z; o[3] = kept[u].w;
+    } else if (kind == CHAIN_SELF) {
+      o[0] = acc[u].x; o[1] = acc[u].y; o[2] = acc[u].z; o[3] = acc[u].w;
+    } else if constexpr (VEC) {
+      const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
+      const float4 q = col < cols ? __ldg(reinterpret_cast<const float4*>(columns + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
+      o[0] = q.x; o[1] = q.y; o[2] = q.z; o[3] = q.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
+        o[e] = col < cols ? __ldg(columns + col) : 0.0f;
+      }
+    }
+    acc[u].x = chain_op<OP>(acc[u].x, o[0], swap);
+    acc[u].y = chain_op<OP>(acc[u].y, o[1], swap);
+    acc[u].z = chain_op<OP>(acc[u].z, o[2], swap);
+    acc[u].w = chain_op<OP>(acc[u].w, o[3], swap);
+  }
+}
+
+template <int TPR, bool VEC>
+__device__ __forceinline__ void chain_load(float4 (&cache)[kRowCacheVecs], const float* __restrict__ xr, int64_t chunk_base, int rank,
+                                           int64_t cols, float fill) {
+#pragma unroll
+  for (int u = 0; u < kRowCacheVecs; ++u) {
+    if constexpr (VEC) {
+      const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
+      cache[u] = col < cols ? ld_stream_f4(reinterpret_cast<const float4*>(xr + col)) : make_float4(fill, fill, fill, fill);
+    } else {
+      float v[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
+        v[e] = col < cols ? __ldg(xr + col) : fill;
+      }
+      cache[u] = make_float4(v[0], v[1], v[2], v[3]);
+    }
+  }
+}
+
+template <int TPR, bool VEC>
+__device__ __forceinline__ void chain_run(const RowProgram& prog, const RowChain& chain, const RegFile<kRowRegs, 1>& scalars,
+                                          float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int64_t chunk_base, int rank,
+                                          int64_t cols) {
+  for (int s = 0; s < chain.n; ++s) {
+    const int kind = chain.kind[s];
+    const bool swap = chain.swap[s] != 0;
+    float scalar[1] = {0.0f};
+    const float* columns = nullptr;
+    if (kind == CHAIN_SCALAR) scalars.get(chain.index[s], scalar);
+    if (kind == CHAIN_COLUMNS) columns = prog.input[chain.index[s]];
+#define DTN_CHAIN_CASE(OP) \
+  case OP: chain_step<OP, TPR, VEC>(acc, kept, kind, scalar[0], columns, swap, chunk_base, rank, cols); break;
+    switch (chain.op[s]) {
+      DTN_CHAIN_CASE(DTN_EW_ADD) DTN_CHAIN_CASE(DTN_EW_SUB) DTN_CHAIN_CASE(DTN_EW_MUL) DTN_CHAIN_CASE(DTN_EW_DIV)
+      DTN_CHAIN_CASE(DTN_EW_MAX) DTN_CHAIN_CASE(DTN_EW_MIN) DTN_CHAIN_CASE(DTN_EW_RELU) DTN_CHAIN_CASE(DTN_EW_EXP)
+      DTN_CHAIN_CASE(DTN_EW_SQRT) DTN_CHAIN_CASE(DTN_EW_RSQRT) DTN_CHAIN_CASE(DTN_EW_RCP) DTN_CHAIN_CASE(DTN_EW_NEG)
+      DTN_CHAIN_CASE(DTN_EW_ABS)
+      default: break;   // copy
+    }
+#undef DTN_CHAIN_CASE
+  }
+}
+
+// TPR threads per row (8, 16, 32 lanes of a warp, or a CTA of 64, 128 or 256 threads). KEEPX: a later step of the
+// chain reads the row element again, so the running values need registers of their own.
+template <int TPR, bool VEC, bool KEEPX>
+__global__ void __launch_bounds__(TPR <= 32 ? 256 : TPR, KEEPX ? (TPR <= 32 ? 2 : 512 / TPR) : (TPR <= 32 ? 3 : 768 / TPR))
+row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __restrict__ x, float* __restrict__ out, int64_t rows,
+                 int64_t cols, int64_t ldx, int64_t ldo) {
+  constexpr int kThreads = TPR <= 32 ? 256 : TPR;
+  constexpr int RPB = kThreads / TPR;                                // rows per CTA
+  constexpr int64_t kChunkCols = (int64_t)TPR * kRowCacheVecs * 4;   // columns one pass of the group covers
+  __shared__ float scratch[8];
+  const int rank = threadIdx.x % TPR, sub = threadIdx.x / TPR;
+  const int reduce = prog.reduce;
+  const bool is_max = reduce == DTN_REDUCE_MAX || reduce == DTN_REDUCE_SOFTMAX;
+  const bool one_chunk = cols <= kChunkCols;
+  const float identity = is_max ? -INFINITY : 0.0f;
+  for (int64_t row0 = (int64_t)blockIdx.x * RPB; row0 < rows; row0 += (int64_t)gridDim.x * RPB) {
+    int64_t row = row0 + sub;
+    const bool live = row < rows;   // uniform over the lanes that share a row; a CTA-wide group always has a live row
+    if (!live) row = rows - 1;      // idle groups of the last CTA repeat the last row and store nothing
+    const float* xr = x + row * ldx;
+    float4 cache[kRowCacheVecs];
+    float part[4] = {identity, identity, identity, identity};
+    if (one_chunk) {
+      chain_load<TPR, VEC>(cache, xr, 0, rank, cols, identity);
+#pragma unroll
+      for (int u = 0; u < kRowCacheVecs; ++u) {
+        part[0] = fold_first(reduce, part[0], cache[u].x);
+        part[1] = fold_first(reduce, part[1], cache[u].y);
+        part[2] = fold_first(reduce, part[2], cache[u].z);
+        part[3] = fold_first(reduce, part[3], cache[u].w);
+      }
+    } else {
+      // longer rows: the reduction streams the row chunk by chunk, eight loads in flight per thread
+      for (int64_t chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
+        chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, identity);
+#pragma unroll
+        for (int u = 0; u < kRowCacheVecs; ++u) {
+          part[0] = fold_first(reduce, part[0], cache[u].x);
+          part[1] = fold_first(reduce, part[1], cache[u].y);
+          part[2] = fold_first(reduce, part[2], cache[u].z);
+          part[3] = fold_first(reduce, part[3], cache[u].w);
+        }
+      }
+    }
+    float first = is_max ? fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) : (part[0] + part[1]) + (part[2] + part[3]);
+    first = is_max ? row_combine<TPR, true>(first, scratch) : row_combine<TPR, false>(first, scratch);
+
+    float second = 0.0f;
+    if (reduce == DTN_REDUCE_SOFTMAX) {
+      if (one_chunk) {   // padding holds -inf, whose exponential is 0
+#pragma unroll
+        for (int u = 0; u < kRowCacheVecs; ++u)
+          second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) + (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
+      } else {
+        for (int64_t chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
+          chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, -INFINITY);
+#pragma unroll
+          for (int u = 0; u < kRowCacheVecs; ++u)
+            second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) + (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
+        }
+      }
+      second = row_combine<TPR, false>(second, scratch);
+    }
+
+    RegFile<kRowRegs, 1> scalars;
+    scalar_stage(prog, first, second, scalars);
+    if (ldo == 0) {
+      if (live && rank == 0) {
+        float result[1];
+        scalars.get(prog.out_reg, result);
+        out[row] = result[0];
+      }
+      continue;
+    }
+    if (!live) continue;
+    float* out_row = out + row * ldo;
+    for (int64_t chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
+      if (!one_chunk) chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, 0.0f);
+      if constexpr (KEEPX) {
+        float4 acc[kRowCacheVecs];
+#pragma unroll
+        for (int u = 0; u < kRowCacheVecs; ++u) acc[u] = cache[u];
+        chain_run<TPR, VEC>(prog, chain, scalars, acc, cache, chunk_base, rank, cols);
+#pragma unroll
+        for (int u = 0; u < kRowCacheVecs; ++u) cache[u] = acc[u];
+      } else {
+        chain_run<TPR, VEC>(prog, chain, scalars, cache, cache, chunk_base, rank, cols);
+      }
+#pragma unroll
+      for (int u = 0; u < kRowCacheVecs; ++u) {
+        if constexpr (VEC) {
+          const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
+          if (col < cols) st_stream_f4(reinterpret_cast<float4*>(out_row + col), cache[u]);
+        } else {
+          const float v[4] = {cache[u].x, cache[u].y, cache[u].z, cache[u].w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
+            if (col < cols) out_row[col] = v[e];
+          }
+        }
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Interpreter for programs whose elementwise stage is not a chain: a CTA per row, the row streamed
+// three times (reduction, softmax sum, elementwise stage), every element run through the register
+// program two lanes at a time.
+// ---------------------------------------------------------------------------------------
 template <int W>
 __device__ __forceinline__ void element_compute(const RowProgram& prog, const RegFile<kRowRegs, 1>& scalars, const float (&xv)[W],
                                                 int64_t col, float (&result)[W]) {
@@ -93,130 +336,61 @@ __device__ __forceinline__ void element_compute(const RowProgram& prog, const Re
   regs.get(prog.out_reg, result);
 }
 
-// One 128-bit vector of the row: two interpreter passes of two elements (a narrow register file keeps the
-// kernel at two CTAs per SM), one 128-bit store.
-__device__ __forceinline__ void element_vector(const RowProgram& prog, const RegFile<kRowRegs, 1>& scalars, const float4 v,
-                                               int64_t col, float* __restrict__ out_row) {
-  const float lo[2] = {v.x, v.y}, hi[2] = {v.z, v.w};
-  float r0[2], r1[2];
-  element_compute<2>(prog, scalars, lo, col, r0);
-  element_compute<2>(prog, scalars, hi, col + 2, r1);
-  st_stream_f4(reinterpret_cast<float4*>(out_row + col), make_float4(r0[0], r0[1], r1[0], r1[1]));
-}
-
-// MODE 0: aligned row of at most TPR * kRowCacheVecs vectors, kept in registers. MODE 1: aligned, streamed.
-// MODE 2: scalar accesses (any alignment, any cols).
-template <int RED, int TPR, int MODE>
+template <bool VEC>
 __global__ void __launch_bounds__(256, 2)
-row_fused_kernel(const RowProgram prog, const float* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols,
-                 int64_t ldx, int64_t ldo) {
-  constexpr int RPB = 256 / TPR;   // rows per CTA
-  constexpr bool kMax = RED == DTN_REDUCE_MAX || RED == DTN_REDUCE_SOFTMAX;
+row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols,
+                       int64_t ldx, int64_t ldo) {
+  constexpr int TPR = 256;
   __shared__ float scratch[8];
-  const int rank = threadIdx.x % TPR, sub = threadIdx.x / TPR;
-  const int64_t nvec = cols >> 2;
-  for (int64_t row0 = (int64_t)blockIdx.x * RPB; row0 < rows; row0 += (int64_t)gridDim.x * RPB) {
-    int64_t row = row0 + sub;
-    const bool live = row < rows;   // uniform over a warp (TPR == 32) or over the CTA (TPR == 256, RPB == 1)
-    if (!live) row = rows - 1;      // idle warps of the last CTA repeat the last row and store nothing
+  const int rank = threadIdx.x;
+  const int reduce = prog.reduce;
+  const bool is_max = reduce == DTN_REDUCE_MAX || reduce == DTN_REDUCE_SOFTMAX;
+  const int64_t units = VEC ? (cols >> 2) : cols;
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* xr = x + row * ldx;
-    float4 cache[kRowCacheVecs];
-    float first = kMax ? -INFINITY : 0.0f;
-    if constexpr (MODE == 0) {
-#pragma unroll
-      for (int u = 0; u < kRowCacheVecs; ++u) {
-        const int64_t j = rank + (int64_t)u * TPR;
-        if (j < nvec) cache[u] = ld_stream_f4(reinterpret_cast<const float4*>(xr) + j);
-      }
-      float part[4] = {first, first, first, first};
-#pragma unroll
-      for (int u = 0; u < kRowCacheVecs; ++u) {
-        if (rank + (int64_t)u * TPR < nvec) {
-          part[0] = fold_first<RED>(part[0], cache[u].x);
-          part[1] = fold_first<RED>(part[1], cache[u].y);
-          part[2] = fold_first<RED>(part[2], cache[u].z);
-          part[3] = fold_first<RED>(part[3], cache[u].w);
-        }
-      }
-      first = kMax ? fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) : (part[0] + part[1]) + (part[2] + part[3]);
-    } else if constexpr (MODE == 1) {
-      float part[4] = {first, first, first, first};
-      for (int64_t j = rank; j < nvec; j += TPR) {
+    float first = is_max ? -INFINITY : 0.0f;
+    for (int64_t j = rank; j < units; j += TPR) {
+      if constexpr (VEC) {
         const float4 v = __ldg(reinterpret_cast<const float4*>(xr) + j);
-        part[0] = fold_first<RED>(part[0], v.x);
-        part[1] = fold_first<RED>(part[1], v.y);
-        part[2] = fold_first<RED>(part[2], v.z);
-        part[3] = fold_first<RED>(part[3], v.w);
+        first = fold_first(reduce, fold_first(reduce, fold_first(reduce, fold_first(reduce, first, v.x), v.y), v.z), v.w);
+      } else {
+        first = fold_first(reduce, first, __ldg(xr + j));
       }
-      first = kMax ? fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) : (part[0] + part[1]) + (part[2] + part[3]);
-    } else {
-      for (int64_t j = rank; j < cols; j += TPR) first = fold_first<RED>(first, xr[j]);
     }
-    first = row_combine<TPR, kMax>(first, scratch);
-
+    first = is_max ? row_combine<TPR, true>(first, scratch) : row_combine<TPR, false>(first, scratch);
     float second = 0.0f;
-    if constexpr (RED == DTN_REDUCE_SOFTMAX) {
-      if constexpr (MODE == 0) {
-#pragma unroll
-        for (int u = 0; u < kRowCacheVecs; ++u) {
-          if (rank + (int64_t)u * TPR < nvec)
-            second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) +
-                      (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
-        }
-      } else if constexpr (MODE == 1) {
-        for (int64_t j = rank; j < nvec; j += TPR) {
+    if (reduce == DTN_REDUCE_SOFTMAX) {
+      for (int64_t j = rank; j < units; j += TPR) {
+        if constexpr (VEC) {
           const float4 v = __ldg(reinterpret_cast<const float4*>(xr) + j);
           second += (exp_ref(v.x - first) + exp_ref(v.y - first)) + (exp_ref(v.z - first) + exp_ref(v.w - first));
+        } else {
+          second += exp_ref(__ldg(xr + j) - first);
         }
-      } else {
-        for (int64_t j = rank; j < cols; j += TPR) second += exp_ref(xr[j] - first);
       }
       second = row_combine<TPR, false>(second, scratch);
     }
-
-    // scalar stage (every thread of the row computes the same values)
     RegFile<kRowRegs, 1> scalars;
-#pragma unroll
-    for (int k = 0; k < kRowRegs; ++k) scalars.r[k][0] = 0.0f;
-    scalars.r[0][0] = first;
-    scalars.r[1][0] = second;
-#pragma unroll
-    for (int i = 0; i < kRowMaxInputs; ++i) {
-      if (i < prog.n_inputs && prog.kind[i] != DTN_ROW_INPUT_COLUMNS) {
-        const float v[1] = {prog.kind[i] == DTN_ROW_INPUT_IMMEDIATE ? prog.immediate[i] : __ldg(prog.input[i])};
-        scalars.put(3 + i, v);
-      }
-    }
-    for (int n = 0; n < prog.n_scalar; ++n) {
-      float a[1], b[1], d[1];
-      scalars.get(prog.a[n], a);
-      scalars.get(prog.b[n], b);
-      d[0] = prog_apply(prog.op[n], a[0], b[0]);
-      scalars.put(prog.dst[n], d);
-    }
-    if (ldo == 0) {   // one value per row
-      if (live && rank == 0) {
+    scalar_stage(prog, first, second, scalars);
+    if (ldo == 0) {
+      if (rank == 0) {
         float result[1];
         scalars.get(prog.out_reg, result);
         out[row] = result[0];
       }
       continue;
     }
-    if (!live) continue;
     float* out_row = out + row * ldo;
-    if constexpr (MODE == 0) {
-#pragma unroll
-      for (int u = 0; u < kRowCacheVecs; ++u) {
-        const int64_t j = rank + (int64_t)u * TPR;
-        if (j < nvec) element_vector(prog, scalars, cache[u], j * 4, out_row);
-      }
-    } else if constexpr (MODE == 1) {
-      for (int64_t j = rank; j < nvec; j += TPR) {
-        element_vector(prog, scalars, __ldg(reinterpret_cast<const float4*>(xr) + j), j * 4, out_row);
-      }
-    } else {
-      for (int64_t j = rank; j < cols; j += TPR) {
-        const float xv[1] = {xr[j]};
+    for (int64_t j = rank; j < units; j += TPR) {
+      if constexpr (VEC) {
+        const float4 v = __ldg(reinterpret_cast<const float4*>(xr) + j);
+        const float lo[2] = {v.x, v.y}, hi[2] = {v.z, v.w};
+        float r0[2], r1[2];
+        element_compute<2>(prog, scalars, lo, j * 4, r0);
+        element_compute<2>(prog, scalars, hi, j * 4 + 2, r1);
+        st_stream_f4(reinterpret_cast<float4*>(out_row) + j, make_float4(r0[0], r0[1], r1[0], r1[1]));
+      } else {
+        const float xv[1] = {__ldg(xr + j)};
         float result[1];
         element_compute<1>(prog, scalars, xv, j, result);
         out_row[j] = result[0];
@@ -225,34 +399,115 @@ row_fused_kernel(const RowProgram prog, const float* __restrict__ x, float* __re
   }
 }
 
-template <int RED, int TPR>
-static int row_fused_launch_mode(const RowProgram& prog, const float* x, float* out, int64_t rows, int64_t cols, int64_t ldx,
-                                 int64_t ldo, int mode, cudaStream_t s) {
-  constexpr int RPB = 256 / TPR;
+// Chain form of the elementwise stage of `prog`, if it has one. Register 2 (the element) starts as the running value;
+// every instruction must read the running value and write the next one, and its other operand must be a value the
+// elementwise stage has not overwritten. *keep_x: a step after the first reads the row element.
+static bool row_chain_of(const RowProgram& prog, RowChain* chain, bool* keep_x, bool per_row) {
+  chain->n = 0;
+  *keep_x = false;
+  int running = 2;
+  bool written[kRowRegs] = {false};
+  bool is_columns[kRowRegs] = {false};
+  for (int i = 0; i < prog.n_inputs; ++i)
+    if (prog.kind[i] == DTN_ROW_INPUT_COLUMNS) is_columns[3 + i] = true;
+  for (int n = prog.n_scalar; n < prog.n_instr; ++n) {
+    if (chain->n >= kChainMax) return false;
+    const int op = prog.op[n], a = prog.a[n], b = prog.b[n];
+    const bool binary = op <= DTN_EW_MIN;
+    int other = -1;
+    bool swap = false;
+    if (!binary) {
+      if (a != running) return false;
+    } else if (a == running) {
+      other = b;
+    } else if (b == running) {
+      other = a;
+      swap = true;
+    } else {
+      return false;
+    }
+    int kind = CHAIN_SELF, index = 0;
+    if (binary) {
+      if (other == running) {
+        kind = CHAIN_SELF;
+      } else if (written[other]) {
+        return false;
+      } else if (other == 2) {
+        kind = CHAIN_ELEMENT;
+        if (chain->n > 0) *keep_x = true;
+      } else if (is_columns[other]) {
+        kind = CHAIN_COLUMNS;
+        index = other - 3;
+      } else {
+        kind = CHAIN_SCALAR;
+        index = other;
+      }
+    }
+    chain->op[chain->n] = (unsigned char)op;
+    chain->kind[chain->n] = (unsigned char)kind;
+    chain->index[chain->n] = (unsigned char)index;
+    chain->swap[chain->n] = swap ? 1 : 0;
+    ++chain->n;
+    running = prog.dst[n];
+    written[running] = true;
+  }
+  return per_row || prog.out_reg == running;   // a per-row result is read from the scalar registers
+}
+
+template <int TPR>
+static int row_chain_launch(const RowProgram& prog, const RowChain& chain, bool keep_x, const float* x, float* out, int64_t rows,
+                            int64_t cols, int64_t ldx, int64_t ldo, bool aligned, cudaStream_t s) {
+  constexpr int kThreads = TPR <= 32 ? 256 : TPR;
+  constexpr int RPB = kThreads / TPR;
   int64_t blocks = (rows + RPB - 1) / RPB;
-  const int64_t cap = (int64_t)sm_count() * 16;
+  const int64_t cap = (int64_t)sm_count() * 32;
   if (blocks > cap) blocks = cap;
   const unsigned grid = (unsigned)blocks;
-  if (mode == 0)
-    row_fused_kernel<RED, TPR, 0><<<grid, 256, 0, s>>>(prog, x, out, rows, cols, ldx, ldo);
-  else if (mode == 1)
-    row_fused_kernel<RED, TPR, 1><<<grid, 256, 0, s>>>(prog, x, out, rows, cols, ldx, ldo);
+  if (aligned && keep_x)
+    row_chain_kernel<TPR, true, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+  else if (aligned)
+    row_chain_kernel<TPR, true, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+  else if (keep_x)
+    row_chain_kernel<TPR, false, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
   else
-    row_fused_kernel<RED, TPR, 2><<<grid, 256, 0, s>>>(prog, x, out, rows, cols, ldx, ldo);
-  DTN_LAUNCH_CHECK("row_fused_kernel");
+    row_chain_kernel<TPR, false, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+  DTN_LAUNCH_CHECK("row_chain_kernel");
   return DTN_OK;
 }
 
-template <int RED>
-static int row_fused_launch(const RowProgram& prog, const float* x, float* out, int64_t rows, int64_t cols, int64_t ldx,
-                            int64_t ldo, bool aligned, cudaStream_t s) {
-  // A warp per row while a lane holds at most two vectors of it, or when there are rows enough to fill the
-  // device with warps; a whole CTA per row otherwise.
-  const bool warp_rows = cols <= 256 || (cols <= 1024 && rows >= (int64_t)sm_count() * 64);
-  const int tpr = warp_rows ? 32 : 256;
-  const int mode = !aligned ? 2 : ((cols >> 2) <= (int64_t)tpr * kRowCacheVecs ? 0 : 1);
-  if (warp_rows) return row_fused_launch_mode<RED, 32>(prog, x, out, rows, cols, ldx, ldo, mode, s);
-  return row_fused_launch_mode<RED, 256>(prog, x, out, rows, cols, ldx, ldo, mode, s);
+// Threads per row: the smallest group whose eight vectors per thread hold the whole row, widened while the
+// device would otherwise be left mostly idle (few rows) and every thread still gets at least one vector.
+static int row_group_size(int64_t rows, int64_t cols) {
+  int tpr = 8;
+  while (tpr < 256 && (int64_t)tpr * kRowCacheVecs * 4 < cols) tpr *= 2;
+  const int64_t wanted = (int64_t)sm_count() * 1024;
+  while (tpr < 256 && rows * tpr < wanted && (int64_t)tpr * 2 * 4 <= cols) tpr *= 2;
+  return tpr;
+}
+
+static int row_fused_launch(const RowProgram& prog, const float* x, float* out, int64_t rows, int64_t cols, int64_t ldx, int64_t ldo,
+                            bool aligned, cudaStream_t s) {
+  RowChain chain;
+  bool keep_x = false;
+  if (row_chain_of(prog, &chain, &keep_x, ldo == 0)) {
+    switch (row_group_size(rows, cols)) {
+      case 8: return row_chain_launch<8>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+      case 16: return row_chain_launch<16>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+      case 32: return row_chain_launch<32>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+      case 64: return row_chain_launch<64>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+      case 128: return row_chain_launch<128>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+      default: return row_chain_launch<256>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+    }
+  }
+  int64_t blocks = rows;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (blocks > cap) blocks = cap;
+  if (aligned)
+    row_interpreter_kernel<true><<<(unsigned)blocks, 256, 0, s>>>(prog, x, out, rows, cols, ldx, ldo);
+  else
+    row_interpreter_kernel<false><<<(unsigned)blocks, 256, 0, s>>>(prog, x, out, rows, cols, ldx, ldo);
+  DTN_LAUNCH_CHECK("row_interpreter_kernel");
+  return DTN_OK;
 }
 
 }  // namespace dtn
@@ -264,6 +519,8 @@ extern "C" int dtn_row_fused(int reduce_op, const float* x, int64_t rows, int64_
                              void* stream) {
   using namespace dtn;
   DTN_REQUIRE(rows >= 0 && cols >= 0, DTN_ERR_INVALID, "row_fused: negative extent");
+  DTN_REQUIRE(reduce_op >= DTN_REDUCE_SUM && reduce_op <= DTN_REDUCE_SOFTMAX, DTN_ERR_INVALID, "row_fused: unknown reduction %d",
+              reduce_op);
   DTN_REQUIRE(n_inputs >= 0 && n_inputs <= kRowMaxInputs, DTN_ERR_UNSUPPORTED, "row_fused: at most %d extra inputs",
               kRowMaxInputs);
   DTN_REQUIRE(n_instr >= 0 && n_instr <= kRowMaxInstr && n_scalar_instr >= 0 && n_scalar_instr <= n_instr, DTN_ERR_UNSUPPORTED,
@@ -278,6 +535,7 @@ extern "C" int dtn_row_fused(int reduce_op, const float* x, int64_t rows, int64_
   DTN_REQUIRE(n_inputs == 0 || (inputs && input_kind && input_immediate), DTN_ERR_INVALID, "row_fused: null input table");
   DTN_REQUIRE(n_instr == 0 || (ops && dsts && as && bs), DTN_ERR_INVALID, "row_fused: null program");
   RowProgram prog = {};
+  prog.reduce = reduce_op;
   prog.n_inputs = n_inputs;
   prog.n_scalar = n_scalar_instr;
   prog.n_instr = n_instr;
@@ -301,14 +559,5 @@ extern "C" int dtn_row_fused(int reduce_op, const float* x, int64_t rows, int64_
     prog.a[k] = as[k];
     prog.b[k] = bs[k];
   }
-  cudaStream_t s = as_stream(stream);
-  switch (reduce_op) {
-    case DTN_REDUCE_SUM: return row_fused_launch<DTN_REDUCE_SUM>(prog, x, out, rows, cols, ldx, ldo, aligned, s);
-    case DTN_REDUCE_MAX: return row_fused_launch<DTN_REDUCE_MAX>(prog, x, out, rows, cols, ldx, ldo, aligned, s);
-    case DTN_REDUCE_SUMSQ: return row_fused_launch<DTN_REDUCE_SUMSQ>(prog, x, out, rows, cols, ldx, ldo, aligned, s);
-    case DTN_REDUCE_SOFTMAX: return row_fused_launch<DTN_REDUCE_SOFTMAX>(prog, x, out, rows, cols, ldx, ldo, aligned, s);
-    default:
-      set_error("row_fused: unknown reduction %d", reduce_op);
-      return DTN_ERR_INVALID;
-  }
+  return row_fused_launch(prog, x, out, rows, cols, ldx, ldo, aligned, as_stream(stream));
 }

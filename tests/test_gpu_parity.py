@@ -317,6 +317,16 @@ def test_row_kernel_edge_cases(cuda):
     got = ops.row_softmax(to_device(cuda, x)).cpu().numpy()
     np.testing.assert_allclose(got, R.row_softmax_f64(x), rtol=ROW_RTOL, atol=1e-30)
     assert np.isfinite(got).all() and got[1, 17] == 1.0
+    # a program whose elementwise stage is not a chain takes the interpreter: (x - mean) * (x + mean)
+    x = R.seeded_normal(5, (9, 700))
+    dx = to_device(cuda, x)
+    program = [('divide', 4, 0, 3), ('subtract', 5, 2, 4), ('add', 6, 2, 4), ('multiply', 7, 5, 6)]
+    got = ops._row_fused('sum', dx, program, 1, 7, inputs=(700.0,)).cpu().numpy()
+    mean = R.row_mean_f64(x)[:, None]
+    np.testing.assert_allclose(got, (x - mean) * (x + mean), rtol=1e-5, atol=1e-5)
+    # a chain that reads the row element again after its first step: (x - max) * x
+    got = ops._row_fused('max', dx, [('subtract', 3, 2, 0), ('multiply', 3, 3, 2)], 0, 3).cpu().numpy()
+    np.testing.assert_array_equal(got, (x - x.max(axis=1, keepdims=True)) * x)
     # empty inputs
     assert ops.row_softmax(cuda.empty((0, 8), device='cuda:0')).shape == (0, 8)
     assert ops.row_mean(cuda.empty((0, 8), device='cuda:0')).numel() == 0
@@ -444,7 +454,7 @@ def test_gemm_edge_cases_and_errors(cuda):
     with pytest.raises(ValueError):
         ops.gemm(a, b, 'fp8')
     too_small = cuda.empty(2048, dtype=cuda.uint8, device='cuda:0')
-    big_a, big_b = to_device(cuda, R.seeded_uniform(1, (512, 512))), to_device(cuda, R.seeded_uniform(2, (512, 512)))
+    big_a, big_b = to_device(cuda, R.seeded_uniform(1, (1024, 1024))), to_device(cuda, R.seeded_uniform(2, (1024, 1024)))
     with pytest.raises(ValueError, match='workspace'):
         ops.gemm(big_a, big_b, 'bf16x3', workspace=too_small)
     assert ops.gemm(a, b, 'bf16x3', workspace=too_small).shape == (64, 48)   # tiny products need no workspace
@@ -460,19 +470,20 @@ def test_gemm_edge_cases_and_errors(cuda):
 
 def test_gemm_column_blocks_equal_the_full_product(cuda):
     # the multi-GPU partition: a column block computed in place (leading dimensions kept) is bit-identical
+    # (every block here is large enough for the tensor-core path, like the full product)
     from deuteron_b200 import sharding
-    a, b = to_device(cuda, R.seeded_uniform(7, (512, 768))), to_device(cuda, R.seeded_uniform(11, (768, 1024)))
+    a, b = to_device(cuda, R.seeded_uniform(7, (1024, 1024))), to_device(cuda, R.seeded_uniform(11, (1024, 2048)))
     full = ops.gemm(a, b, 'bf16x3').clone()
     for world in (2, 4):
         parts = []
         for rank in range(world):
             local, (begin, end) = sharding.gemm_column_shard(a, b, rank, world)
             parts.append(local.clone())
-            assert (begin, end) == sharding.column_blocks(1024, world)[rank]
+            assert (begin, end) == sharding.column_blocks(2048, world)[rank]
         assert bool(cuda.equal(cuda.cat(parts, dim=1), full))
-    into = cuda.zeros((512, 1024), device='cuda:0')
-    ops.gemm(a, b[:, 256:512], 'bf16x3', out=into[:, 256:512])
-    assert bool(cuda.equal(into[:, 256:512], full[:, 256:512])) and float(into[:, :256].abs().sum()) == 0.0
+    into = cuda.zeros((1024, 2048), device='cuda:0')
+    ops.gemm(a, b[:, 512:1024], 'bf16x3', out=into[:, 512:1024])
+    assert bool(cuda.equal(into[:, 512:1024], full[:, 512:1024])) and float(into[:, :512].abs().sum()) == 0.0
 
 
 def test_execute_on_host_buffers_matches_the_resident_path(cuda, runner):
