@@ -74,20 +74,32 @@ __device__ __forceinline__ float fold_first(int reduce, float acc, float v) {
   return fmaxf(acc, v);   // max and softmax
 }
 
-// Scalar stage: the reduced values, the one-element inputs and the literals go into registers, then
-// instructions [0, n_scalar) run. Every thread of the row computes the same values.
-__device__ __forceinline__ void scalar_stage(const RowProgram& prog, float first, float second, RegFile<kRowRegs, 1>& scalars) {
+// The one-element inputs and the literals of a program: the same for every row, so they are read once per thread,
+// before the first row is touched (their latency hides behind the loads of the row).
+struct RowConstants {
+  float v[kRowMaxInputs];
+};
+__device__ __forceinline__ RowConstants row_constants(const RowProgram& prog) {
+  RowConstants c;
+#pragma unroll
+  for (int i = 0; i < kRowMaxInputs; ++i) {
+    c.v[i] = 0.0f;
+    if (i < prog.n_inputs && prog.kind[i] != DTN_ROW_INPUT_COLUMNS)
+      c.v[i] = prog.kind[i] == DTN_ROW_INPUT_IMMEDIATE ? prog.immediate[i] : __ldg(prog.input[i]);
+  }
+  return c;
+}
+
+// Scalar stage: the reduced values and the constants go into registers, then instructions [0, n_scalar) run.
+// Every thread of the row computes the same values.
+__device__ __forceinline__ void scalar_stage(const RowProgram& prog, const RowConstants& constants, float first, float second,
+                                             RegFile<kRowRegs, 1>& scalars) {
 #pragma unroll
   for (int k = 0; k < kRowRegs; ++k) scalars.r[k][0] = 0.0f;
   scalars.r[0][0] = first;
   scalars.r[1][0] = second;
 #pragma unroll
-  for (int i = 0; i < kRowMaxInputs; ++i) {
-    if (i < prog.n_inputs && prog.kind[i] != DTN_ROW_INPUT_COLUMNS) {
-      const float v[1] = {prog.kind[i] == DTN_ROW_INPUT_IMMEDIATE ? prog.immediate[i] : __ldg(prog.input[i])};
-      scalars.put(3 + i, v);
-    }
-  }
+  for (int i = 0; i < kRowMaxInputs; ++i) scalars.r[3 + i][0] = constants.v[i];
   for (int n = 0; n < prog.n_scalar; ++n) {
     float a[1], b[1], d[1];
     scalars.get(prog.a[n], a);
@@ -205,6 +217,20 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
   const bool is_max = reduce == DTN_REDUCE_MAX || reduce == DTN_REDUCE_SOFTMAX;
   const bool one_chunk = cols <= kChunkCols;
   const float identity = is_max ? -INFINITY : 0.0f;
+  const RowConstants constants = row_constants(prog);
+  if constexpr (VEC) {
+    // per-column inputs are read only in the elementwise stage, after the reduction: start fetching this thread's
+    // part of them now so that the first row does not wait for them
+    for (int s = 0; s < chain.n; ++s) {
+      if (chain.kind[s] != CHAIN_COLUMNS) continue;
+      const float* columns = prog.input[chain.index[s]];
+#pragma unroll
+      for (int u = 0; u < kRowCacheVecs; ++u) {
+        const int64_t col = chain_column<TPR, VEC>(0, rank, u, 0);
+        if (col < cols) asm volatile("prefetch.global.L1 [%0];" ::"l"(columns + col));
+      }
+    }
+  }
   for (int64_t row0 = (int64_t)blockIdx.x * RPB; row0 < rows; row0 += (int64_t)gridDim.x * RPB) {
     int64_t row = row0 + sub;
     const bool live = row < rows;   // uniform over the lanes that share a row; a CTA-wide group always has a live row
@@ -255,7 +281,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
     }
 
     RegFile<kRowRegs, 1> scalars;
-    scalar_stage(prog, first, second, scalars);
+    scalar_stage(prog, constants, first, second, scalars);
     if (ldo == 0) {
       if (live && rank == 0) {
         float result[1];
@@ -346,6 +372,7 @@ row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float
   const int reduce = prog.reduce;
   const bool is_max = reduce == DTN_REDUCE_MAX || reduce == DTN_REDUCE_SOFTMAX;
   const int64_t units = VEC ? (cols >> 2) : cols;
+  const RowConstants constants = row_constants(prog);
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* xr = x + row * ldx;
     float first = is_max ? -INFINITY : 0.0f;
@@ -371,7 +398,7 @@ row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float
       second = row_combine<TPR, false>(second, scratch);
     }
     RegFile<kRowRegs, 1> scalars;
-    scalar_stage(prog, first, second, scalars);
+    scalar_stage(prog, constants, first, second, scalars);
     if (ldo == 0) {
       if (rank == 0) {
         float result[1];
