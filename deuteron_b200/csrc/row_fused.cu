@@ -43,14 +43,23 @@ struct RowProgram {
   unsigned char op[kRowMaxInstr], dst[kRowMaxInstr], a[kRowMaxInstr], b[kRowMaxInstr];
 };
 
+// The scalar stage's registers: a plain array indexed at run time. It lives in local memory (L1-resident, a few dozen
+// bytes per thread); one load per operand is far cheaper here than the twelve-way compare chains a register-resident
+// file needs, and the scalar stage runs once per row, not per element.
+struct ScalarFile {
+  float r[kRowRegs];
+};
+
 struct RowChain {
   int n;
   unsigned char op[kChainMax], kind[kChainMax], index[kChainMax], swap[kChainMax];   // index: register (scalar) or input (columns)
 };
 
 // Combines one value per thread over the TPR threads that share a row (TPR lanes of a warp, or all warps of the CTA).
+// Across warps: every warp leaves its partial in one of two scratch rows (alternating from call to call, so one barrier
+// per call is enough: a row is rewritten only after the barrier of the call in between) and every thread folds them all.
 template <int TPR, bool MAX>
-__device__ __forceinline__ float row_combine(float v, float* scratch) {
+__device__ __forceinline__ float row_combine(float v, float* scratch, int& parity) {
   constexpr int kLanes = TPR < 32 ? TPR : 32;
 #pragma unroll
   for (int o = kLanes / 2; o > 0; o >>= 1) {
@@ -58,12 +67,13 @@ __device__ __forceinline__ float row_combine(float v, float* scratch) {
     v = MAX ? fmaxf(v, w) : v + w;
   }
   if constexpr (TPR > 32) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) scratch[warp] = v;
+    float* mine = scratch + parity * 8;
+    parity ^= 1;
+    if ((threadIdx.x & 31) == 0) mine[threadIdx.x >> 5] = v;
     __syncthreads();
-    float w = lane < TPR / 32 ? scratch[lane] : (MAX ? -INFINITY : 0.0f);
-    v = MAX ? warp_max(w) : warp_sum(w);
-    __syncthreads();
+    v = mine[0];
+#pragma unroll
+    for (int w = 1; w < TPR / 32; ++w) v = MAX ? fmaxf(v, mine[w]) : v + mine[w];
   }
   return v;
 }
@@ -93,20 +103,14 @@ __device__ __forceinline__ RowConstants row_constants(const RowProgram& prog) {
 // Scalar stage: the reduced values and the constants go into registers, then instructions [0, n_scalar) run.
 // Every thread of the row computes the same values.
 __device__ __forceinline__ void scalar_stage(const RowProgram& prog, const RowConstants& constants, float first, float second,
-                                             RegFile<kRowRegs, 1>& scalars) {
+                                             ScalarFile& scalars) {
 #pragma unroll
-  for (int k = 0; k < kRowRegs; ++k) scalars.r[k][0] = 0.0f;
-  scalars.r[0][0] = first;
-  scalars.r[1][0] = second;
+  for (int k = 0; k < kRowRegs; ++k) scalars.r[k] = 0.0f;
+  scalars.r[0] = first;
+  scalars.r[1] = second;
 #pragma unroll
-  for (int i = 0; i < kRowMaxInputs; ++i) scalars.r[3 + i][0] = constants.v[i];
-  for (int n = 0; n < prog.n_scalar; ++n) {
-    float a[1], b[1], d[1];
-    scalars.get(prog.a[n], a);
-    scalars.get(prog.b[n], b);
-    d[0] = prog_apply(prog.op[n], a[0], b[0]);
-    scalars.put(prog.dst[n], d);
-  }
+  for (int i = 0; i < kRowMaxInputs; ++i) scalars.r[3 + i] = constants.v[i];
+  for (int n = 0; n < prog.n_scalar; ++n) scalars.r[prog.dst[n]] = prog_apply(prog.op[n], scalars.r[prog.a[n]], scalars.r[prog.b[n]]);
 }
 
 template <int OP>
@@ -121,33 +125,35 @@ __device__ __forceinline__ float chain_op(float a, float o, bool swap) {
 }
 
 // Unit u of a thread's chunk covers four consecutive columns of one 128-bit vector (VEC) or four
-// columns TPR apart (scalar accesses).
+// columns TPR apart (scalar accesses). Columns are 32-bit: a buffer holds fewer than 2^31 elements.
 template <int TPR, bool VEC>
-__device__ __forceinline__ int64_t chain_column(int64_t chunk_base, int rank, int u, int lane) {
-  if constexpr (VEC) return chunk_base + ((int64_t)rank + (int64_t)u * TPR) * 4 + lane;
-  return chunk_base + rank + (int64_t)(u * 4 + lane) * TPR;
+__device__ __forceinline__ int chain_column(int chunk_base, int rank, int u, int lane) {
+  if constexpr (VEC) return chunk_base + (rank + u * TPR) * 4 + lane;
+  return chunk_base + rank + (u * 4 + lane) * TPR;
 }
 
-template <int OP, int TPR, bool VEC>
-__device__ __forceinline__ void chain_step(float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int kind, float scalar,
-                                           const float* __restrict__ columns, bool swap, int64_t chunk_base, int rank, int64_t cols) {
+// One step of the chain over the thread's 32 cached elements. OP and KIND are compile-time: the two uniform
+// switches in chain_run pick the instantiation once per row and step.
+template <int OP, int KIND, int TPR, bool VEC>
+__device__ __forceinline__ void chain_step(float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], float scalar,
+                                           const float* __restrict__ columns, bool swap, int chunk_base, int rank, int cols) {
 #pragma unroll
   for (int u = 0; u < kRowCacheVecs; ++u) {
     float o[4];
-    if (kind == CHAIN_SCALAR) {
+    if constexpr (KIND == CHAIN_SCALAR) {
       o[0] = o[1] = o[2] = o[3] = scalar;
-    } else if (kind == CHAIN_ELEMENT) {
+    } else if constexpr (KIND == CHAIN_ELEMENT) {
       o[0] = kept[u].x; o[1] = kept[u].y; o[2] = kept[u].z; o[3] = kept[u].w;
-    } else if (kind == CHAIN_SELF) {
+    } else if constexpr (KIND == CHAIN_SELF) {
       o[0] = acc[u].x; o[1] = acc[u].y; o[2] = acc[u].z; o[3] = acc[u].w;
     } else if constexpr (VEC) {
-      const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
+      const int col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
       const float4 q = col < cols ? __ldg(reinterpret_cast<const float4*>(columns + col)) : make_float4(0.f, 0.f, 0.f, 0.f);
       o[0] = q.x; o[1] = q.y; o[2] = q.z; o[3] = q.w;
     } else {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
+        const int col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
         o[e] = col < cols ? __ldg(columns + col) : 0.0f;
       }
     }
@@ -158,19 +164,30 @@ __device__ __forceinline__ void chain_step(float4 (&acc)[kRowCacheVecs], const f
   }
 }
 
+template <int OP, int TPR, bool VEC>
+__device__ __forceinline__ void chain_binary(float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int kind, float scalar,
+                                             const float* __restrict__ columns, bool swap, int chunk_base, int rank, int cols) {
+  switch (kind) {
+    case CHAIN_SCALAR: chain_step<OP, CHAIN_SCALAR, TPR, VEC>(acc, kept, scalar, columns, swap, chunk_base, rank, cols); break;
+    case CHAIN_COLUMNS: chain_step<OP, CHAIN_COLUMNS, TPR, VEC>(acc, kept, scalar, columns, swap, chunk_base, rank, cols); break;
+    case CHAIN_ELEMENT: chain_step<OP, CHAIN_ELEMENT, TPR, VEC>(acc, kept, scalar, columns, swap, chunk_base, rank, cols); break;
+    default: chain_step<OP, CHAIN_SELF, TPR, VEC>(acc, kept, scalar, columns, swap, chunk_base, rank, cols); break;
+  }
+}
+
 template <int TPR, bool VEC>
-__device__ __forceinline__ void chain_load(float4 (&cache)[kRowCacheVecs], const float* __restrict__ xr, int64_t chunk_base, int rank,
-                                           int64_t cols, float fill) {
+__device__ __forceinline__ void chain_load(float4 (&cache)[kRowCacheVecs], const float* __restrict__ xr, int chunk_base, int rank,
+                                           int cols, float fill) {
 #pragma unroll
   for (int u = 0; u < kRowCacheVecs; ++u) {
     if constexpr (VEC) {
-      const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
+      const int col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
       cache[u] = col < cols ? ld_stream_f4(reinterpret_cast<const float4*>(xr + col)) : make_float4(fill, fill, fill, fill);
     } else {
       float v[4];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
+        const int col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
         v[e] = col < cols ? __ldg(xr + col) : fill;
       }
       cache[u] = make_float4(v[0], v[1], v[2], v[3]);
@@ -178,40 +195,66 @@ __device__ __forceinline__ void chain_load(float4 (&cache)[kRowCacheVecs], const
   }
 }
 
+// Folds the thread's cached elements into four partial reductions; the reduction operator is a uniform branch
+// taken once per chunk, not per element.
+__device__ __forceinline__ void chain_fold(int reduce, const float4 (&cache)[kRowCacheVecs], float (&part)[4]) {
+  if (reduce == DTN_REDUCE_SUM) {
+#pragma unroll
+    for (int u = 0; u < kRowCacheVecs; ++u) {
+      part[0] += cache[u].x; part[1] += cache[u].y; part[2] += cache[u].z; part[3] += cache[u].w;
+    }
+  } else if (reduce == DTN_REDUCE_SUMSQ) {
+#pragma unroll
+    for (int u = 0; u < kRowCacheVecs; ++u) {
+      part[0] = fmaf(cache[u].x, cache[u].x, part[0]); part[1] = fmaf(cache[u].y, cache[u].y, part[1]);
+      part[2] = fmaf(cache[u].z, cache[u].z, part[2]); part[3] = fmaf(cache[u].w, cache[u].w, part[3]);
+    }
+  } else {
+#pragma unroll
+    for (int u = 0; u < kRowCacheVecs; ++u) {
+      part[0] = fmaxf(part[0], cache[u].x); part[1] = fmaxf(part[1], cache[u].y);
+      part[2] = fmaxf(part[2], cache[u].z); part[3] = fmaxf(part[3], cache[u].w);
+    }
+  }
+}
+
 template <int TPR, bool VEC>
-__device__ __forceinline__ void chain_run(const RowProgram& prog, const RowChain& chain, const RegFile<kRowRegs, 1>& scalars,
-                                          float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int64_t chunk_base, int rank,
-                                          int64_t cols) {
+__device__ __forceinline__ void chain_run(const RowProgram& prog, const RowChain& chain, const ScalarFile& scalars,
+                                          float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int chunk_base, int rank,
+                                          int cols) {
   for (int s = 0; s < chain.n; ++s) {
     const int kind = chain.kind[s];
     const bool swap = chain.swap[s] != 0;
-    float scalar[1] = {0.0f};
+    const float scalar = kind == CHAIN_SCALAR ? scalars.r[chain.index[s]] : 0.0f;
     const float* columns = nullptr;
-    if (kind == CHAIN_SCALAR) scalars.get(chain.index[s], scalar);
     if (kind == CHAIN_COLUMNS) columns = prog.input[chain.index[s]];
-#define DTN_CHAIN_CASE(OP) \
-  case OP: chain_step<OP, TPR, VEC>(acc, kept, kind, scalar[0], columns, swap, chunk_base, rank, cols); break;
+#define DTN_CHAIN_BINARY(OP) \
+  case OP: chain_binary<OP, TPR, VEC>(acc, kept, kind, scalar, columns, swap, chunk_base, rank, cols); break;
+#define DTN_CHAIN_UNARY(OP) \
+  case OP: chain_step<OP, CHAIN_SELF, TPR, VEC>(acc, kept, 0.0f, nullptr, false, chunk_base, rank, cols); break;
     switch (chain.op[s]) {
-      DTN_CHAIN_CASE(DTN_EW_ADD) DTN_CHAIN_CASE(DTN_EW_SUB) DTN_CHAIN_CASE(DTN_EW_MUL) DTN_CHAIN_CASE(DTN_EW_DIV)
-      DTN_CHAIN_CASE(DTN_EW_MAX) DTN_CHAIN_CASE(DTN_EW_MIN) DTN_CHAIN_CASE(DTN_EW_RELU) DTN_CHAIN_CASE(DTN_EW_EXP)
-      DTN_CHAIN_CASE(DTN_EW_SQRT) DTN_CHAIN_CASE(DTN_EW_RSQRT) DTN_CHAIN_CASE(DTN_EW_RCP) DTN_CHAIN_CASE(DTN_EW_NEG)
-      DTN_CHAIN_CASE(DTN_EW_ABS)
+      DTN_CHAIN_BINARY(DTN_EW_ADD) DTN_CHAIN_BINARY(DTN_EW_SUB) DTN_CHAIN_BINARY(DTN_EW_MUL) DTN_CHAIN_BINARY(DTN_EW_DIV)
+      DTN_CHAIN_BINARY(DTN_EW_MAX) DTN_CHAIN_BINARY(DTN_EW_MIN) DTN_CHAIN_UNARY(DTN_EW_RELU) DTN_CHAIN_UNARY(DTN_EW_EXP)
+      DTN_CHAIN_UNARY(DTN_EW_SQRT) DTN_CHAIN_UNARY(DTN_EW_RSQRT) DTN_CHAIN_UNARY(DTN_EW_RCP) DTN_CHAIN_UNARY(DTN_EW_NEG)
+      DTN_CHAIN_UNARY(DTN_EW_ABS)
       default: break;   // copy
     }
-#undef DTN_CHAIN_CASE
+#undef DTN_CHAIN_BINARY
+#undef DTN_CHAIN_UNARY
   }
 }
 
 // TPR threads per row (8, 16, 32 lanes of a warp, or a CTA of 64, 128 or 256 threads). KEEPX: a later step of the
 // chain reads the row element again, so the running values need registers of their own.
 template <int TPR, bool VEC, bool KEEPX>
-__global__ void __launch_bounds__(TPR <= 32 ? 256 : TPR, KEEPX ? (TPR <= 32 ? 2 : 512 / TPR) : (TPR <= 32 ? 3 : 768 / TPR))
+__global__ void __launch_bounds__(TPR <= 32 ? 128 : TPR, (KEEPX ? 512 : 640) / (TPR <= 32 ? 128 : TPR))
 row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __restrict__ x, float* __restrict__ out, int64_t rows,
-                 int64_t cols, int64_t ldx, int64_t ldo) {
-  constexpr int kThreads = TPR <= 32 ? 256 : TPR;
+                 int cols, int64_t ldx, int64_t ldo) {
+  constexpr int kThreads = TPR <= 32 ? 128 : TPR;
   constexpr int RPB = kThreads / TPR;                                // rows per CTA
-  constexpr int64_t kChunkCols = (int64_t)TPR * kRowCacheVecs * 4;   // columns one pass of the group covers
-  __shared__ float scratch[8];
+  constexpr int kChunkCols = TPR * kRowCacheVecs * 4;   // columns one pass of the group covers
+  __shared__ float scratch[16];
+  int parity = 0;
   const int rank = threadIdx.x % TPR, sub = threadIdx.x / TPR;
   const int reduce = prog.reduce;
   const bool is_max = reduce == DTN_REDUCE_MAX || reduce == DTN_REDUCE_SOFTMAX;
@@ -226,7 +269,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
       const float* columns = prog.input[chain.index[s]];
 #pragma unroll
       for (int u = 0; u < kRowCacheVecs; ++u) {
-        const int64_t col = chain_column<TPR, VEC>(0, rank, u, 0);
+        const int col = chain_column<TPR, VEC>(0, rank, u, 0);
         if (col < cols) asm volatile("prefetch.global.L1 [%0];" ::"l"(columns + col));
       }
     }
@@ -240,28 +283,16 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
     float part[4] = {identity, identity, identity, identity};
     if (one_chunk) {
       chain_load<TPR, VEC>(cache, xr, 0, rank, cols, identity);
-#pragma unroll
-      for (int u = 0; u < kRowCacheVecs; ++u) {
-        part[0] = fold_first(reduce, part[0], cache[u].x);
-        part[1] = fold_first(reduce, part[1], cache[u].y);
-        part[2] = fold_first(reduce, part[2], cache[u].z);
-        part[3] = fold_first(reduce, part[3], cache[u].w);
-      }
+      chain_fold(reduce, cache, part);
     } else {
       // longer rows: the reduction streams the row chunk by chunk, eight loads in flight per thread
-      for (int64_t chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
+      for (int chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
         chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, identity);
-#pragma unroll
-        for (int u = 0; u < kRowCacheVecs; ++u) {
-          part[0] = fold_first(reduce, part[0], cache[u].x);
-          part[1] = fold_first(reduce, part[1], cache[u].y);
-          part[2] = fold_first(reduce, part[2], cache[u].z);
-          part[3] = fold_first(reduce, part[3], cache[u].w);
-        }
+        chain_fold(reduce, cache, part);
       }
     }
     float first = is_max ? fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) : (part[0] + part[1]) + (part[2] + part[3]);
-    first = is_max ? row_combine<TPR, true>(first, scratch) : row_combine<TPR, false>(first, scratch);
+    first = is_max ? row_combine<TPR, true>(first, scratch, parity) : row_combine<TPR, false>(first, scratch, parity);
 
     float second = 0.0f;
     if (reduce == DTN_REDUCE_SOFTMAX) {
@@ -270,29 +301,27 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
         for (int u = 0; u < kRowCacheVecs; ++u)
           second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) + (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
       } else {
-        for (int64_t chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
+        for (int chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
           chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, -INFINITY);
 #pragma unroll
           for (int u = 0; u < kRowCacheVecs; ++u)
             second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) + (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
         }
       }
-      second = row_combine<TPR, false>(second, scratch);
+      second = row_combine<TPR, false>(second, scratch, parity);
     }
 
-    RegFile<kRowRegs, 1> scalars;
+    ScalarFile scalars;
     scalar_stage(prog, constants, first, second, scalars);
     if (ldo == 0) {
       if (live && rank == 0) {
-        float result[1];
-        scalars.get(prog.out_reg, result);
-        out[row] = result[0];
+        out[row] = scalars.r[prog.out_reg];
       }
       continue;
     }
     if (!live) continue;
     float* out_row = out + row * ldo;
-    for (int64_t chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
+    for (int chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
       if (!one_chunk) chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, 0.0f);
       if constexpr (KEEPX) {
         float4 acc[kRowCacheVecs];
@@ -307,13 +336,13 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
 #pragma unroll
       for (int u = 0; u < kRowCacheVecs; ++u) {
         if constexpr (VEC) {
-          const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
+          const int col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
           if (col < cols) st_stream_f4(reinterpret_cast<float4*>(out_row + col), cache[u]);
         } else {
           const float v[4] = {cache[u].x, cache[u].y, cache[u].z, cache[u].w};
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            const int64_t col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
+            const int col = chain_column<TPR, VEC>(chunk_base, rank, u, e);
             if (col < cols) out_row[col] = v[e];
           }
         }
@@ -328,13 +357,13 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
 // program two lanes at a time.
 // ---------------------------------------------------------------------------------------
 template <int W>
-__device__ __forceinline__ void element_compute(const RowProgram& prog, const RegFile<kRowRegs, 1>& scalars, const float (&xv)[W],
+__device__ __forceinline__ void element_compute(const RowProgram& prog, const ScalarFile& scalars, const float (&xv)[W],
                                                 int64_t col, float (&result)[W]) {
   RegFile<kRowRegs, W> regs;
 #pragma unroll
   for (int k = 0; k < kRowRegs; ++k)
 #pragma unroll
-    for (int e = 0; e < W; ++e) regs.r[k][e] = scalars.r[k][0];
+    for (int e = 0; e < W; ++e) regs.r[k][e] = scalars.r[k];
 #pragma unroll
   for (int e = 0; e < W; ++e) regs.r[2][e] = xv[e];
 #pragma unroll
@@ -367,7 +396,8 @@ __global__ void __launch_bounds__(256, 2)
 row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float* __restrict__ out, int64_t rows, int64_t cols,
                        int64_t ldx, int64_t ldo) {
   constexpr int TPR = 256;
-  __shared__ float scratch[8];
+  __shared__ float scratch[16];
+  int parity = 0;
   const int rank = threadIdx.x;
   const int reduce = prog.reduce;
   const bool is_max = reduce == DTN_REDUCE_MAX || reduce == DTN_REDUCE_SOFTMAX;
@@ -384,7 +414,7 @@ row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float
         first = fold_first(reduce, first, __ldg(xr + j));
       }
     }
-    first = is_max ? row_combine<TPR, true>(first, scratch) : row_combine<TPR, false>(first, scratch);
+    first = is_max ? row_combine<TPR, true>(first, scratch, parity) : row_combine<TPR, false>(first, scratch, parity);
     float second = 0.0f;
     if (reduce == DTN_REDUCE_SOFTMAX) {
       for (int64_t j = rank; j < units; j += TPR) {
@@ -395,15 +425,13 @@ row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float
           second += exp_ref(__ldg(xr + j) - first);
         }
       }
-      second = row_combine<TPR, false>(second, scratch);
+      second = row_combine<TPR, false>(second, scratch, parity);
     }
-    RegFile<kRowRegs, 1> scalars;
+    ScalarFile scalars;
     scalar_stage(prog, constants, first, second, scalars);
     if (ldo == 0) {
       if (rank == 0) {
-        float result[1];
-        scalars.get(prog.out_reg, result);
-        out[row] = result[0];
+        out[row] = scalars.r[prog.out_reg];
       }
       continue;
     }
@@ -484,20 +512,20 @@ static bool row_chain_of(const RowProgram& prog, RowChain* chain, bool* keep_x, 
 template <int TPR>
 static int row_chain_launch(const RowProgram& prog, const RowChain& chain, bool keep_x, const float* x, float* out, int64_t rows,
                             int64_t cols, int64_t ldx, int64_t ldo, bool aligned, cudaStream_t s) {
-  constexpr int kThreads = TPR <= 32 ? 256 : TPR;
+  constexpr int kThreads = TPR <= 32 ? 128 : TPR;
   constexpr int RPB = kThreads / TPR;
   int64_t blocks = (rows + RPB - 1) / RPB;
   const int64_t cap = (int64_t)sm_count() * 32;
   if (blocks > cap) blocks = cap;
   const unsigned grid = (unsigned)blocks;
   if (aligned && keep_x)
-    row_chain_kernel<TPR, true, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+    row_chain_kernel<TPR, true, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   else if (aligned)
-    row_chain_kernel<TPR, true, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+    row_chain_kernel<TPR, true, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   else if (keep_x)
-    row_chain_kernel<TPR, false, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+    row_chain_kernel<TPR, false, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   else
-    row_chain_kernel<TPR, false, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, cols, ldx, ldo);
+    row_chain_kernel<TPR, false, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   DTN_LAUNCH_CHECK("row_chain_kernel");
   return DTN_OK;
 }
@@ -516,7 +544,7 @@ static int row_fused_launch(const RowProgram& prog, const float* x, float* out, 
                             bool aligned, cudaStream_t s) {
   RowChain chain;
   bool keep_x = false;
-  if (row_chain_of(prog, &chain, &keep_x, ldo == 0)) {
+  if (cols < (1LL << 30) && row_chain_of(prog, &chain, &keep_x, ldo == 0)) {
     switch (row_group_size(rows, cols)) {
       case 8: return row_chain_launch<8>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
       case 16: return row_chain_launch<16>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
