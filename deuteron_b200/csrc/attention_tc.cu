@@ -1,6 +1,6 @@
 // Grouped-query attention forward on the sm_100a tensor cores (f16 storage, head_dim 128).
 //
-// One CTA owns 256 query rows of one query head (two 128-row tiles) and walks the keys 128 at a
+// A work item is 256 query rows of one query head (two 128-row tiles); its keys are walked 128 at a
 // time. Every product is a tcgen05.mma with FP32 accumulation in tensor memory:
 //   S_t = Q_t * K_j^T          f16 x f16 products are exact; 128x128 FP32 scores per tile
 //   O_t += P_t * V_j           the FP32 probabilities are split into an f16 high part and an f16
@@ -11,14 +11,18 @@
 // read from there as the A operand of the second product. The output accumulator is rescaled
 // lazily: only when a row's maximum has grown by more than 2^8 since the last rescale.
 //
-// Warps 0-3 and 4-7: softmax + output for tile 0 and tile 1; warp 8: TMA loads (Q once, then a
-// two-slot ring of K and V tiles); warp 9: MMA issue. While one tile's softmax runs, the tensor
-// core works on the other tile.
+// Per tile one or two softmax warpgroups (softmax + output); one warp issues the TMA loads (the
+// queries of each work item, and a two-slot ring of K and V tiles); one warp issues the MMAs.
+// While one tile's softmax runs, the tensor core works on the other tile. The kernel is
+// persistent: one CTA per SM walks the work items (256 query rows of one head each) as a single
+// stream of key steps, so the output of one item is normalised and stored while the products of
+// the next are already running.
 //
 // Tensor-memory columns: [0,128) scores/probabilities of tile 0, [128,256) of tile 1,
 // [256,384) output of tile 0, [384,512) output of tile 1.
 #include <cuda.h>
 #include <math.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -36,7 +40,8 @@ constexpr int A_TILE_BYTES = 2 * A_HALF_BYTES;    // one [128][128] f16 tile
 constexpr int A_KV_STAGES = 2;
 constexpr int A_SMEM_TILES = 2 /*Q*/ + 2 * A_KV_STAGES /*K,V*/;
 constexpr int A_XCHG_BYTES = 2 * 2 * 128 * 8;   // [tile][column share][row] (value, sequence) slots
-constexpr int A_SMEM_BYTES = A_SMEM_TILES * A_TILE_BYTES + 256 + A_XCHG_BYTES + 1024;
+constexpr int A_STAGE_BYTES = 16 * 1024;        // 1 KiB of output staging per softmax warp (at most 16 of them)
+constexpr int A_SMEM_BYTES = A_SMEM_TILES * A_TILE_BYTES + 256 + A_XCHG_BYTES + A_STAGE_BYTES + 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;   // in log2 units
 constexpr float A_BIAS = 4.0f;                // probabilities are kept scaled by 2^4 (f16 residuals stay normal)
 
@@ -90,11 +95,32 @@ __device__ __forceinline__ bool exchange_with_peer(volatile float2* mine, volati
   }
 }
 
+// Work items: one item = 256 query rows of one query head. A CTA takes items blockIdx.x, blockIdx.x + gridDim.x, ...
+// and runs them as ONE stream of key steps: barrier phases, the K/V ring and the exchange sequence numbers keep
+// counting across items, so the next item's first products are issued while the previous item's output is still being
+// written (the per-item prologue, pipeline fill and output no longer leave the tensor core idle). With as many CTAs
+// as items the kernel degenerates to one item per CTA.
+struct AttnItem {
+  int q_row0;     // first query row in the [B*Hq*S, D] view
+  int kv_row0;    // first key row in the [B*Hkv*S, D] view
+};
+__device__ __forceinline__ AttnItem attn_item(int item, int qblocks, int Hq, int Hkv, int S, int group_begin) {
+  const int heads_per_group = Hq / Hkv;
+  const int head_local = item / qblocks, qb = item % qblocks;
+  const int group = group_begin + head_local / heads_per_group;
+  const int b = group / Hkv, hkv = group % Hkv;
+  const int hq = hkv * heads_per_group + head_local % heads_per_group;
+  AttnItem it;
+  it.q_row0 = (b * Hq + hq) * S + qb * (2 * A_BM);
+  it.kv_row0 = (b * Hkv + hkv) * S;
+  return it;
+}
+
 template <int SPLIT /*warpgroups per 128-row tile: 1 or 2*/>
 __global__ void __launch_bounds__(attn_threads(SPLIT), 1)
 gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, float* __restrict__ out, int Hq, int Hkv, int S,
-              float scale_log2e, int group_begin, int* __restrict__ status) {
+              float scale_log2e, int group_begin, int total_items, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -105,27 +131,26 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t bar_addr = base + A_SMEM_TILES * A_TILE_BYTES;
   uint8_t* bar_ptr = base_ptr + A_SMEM_TILES * A_TILE_BYTES;
   // barrier slots
-  const uint32_t q_full = bar_addr;
-  auto k_full = [&](int s) { return bar_addr + 8u * (1 + s); };
-  auto v_full = [&](int s) { return bar_addr + 8u * (3 + s); };
-  auto k_empty = [&](int s) { return bar_addr + 8u * (5 + s); };
-  auto v_empty = [&](int s) { return bar_addr + 8u * (7 + s); };
-  auto s_full = [&](int t) { return bar_addr + 8u * (9 + t); };
-  auto p_full = [&](int t) { return bar_addr + 8u * (11 + t); };
-  auto o_done = [&](int t) { return bar_addr + 8u * (13 + t); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * 15);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 15 + 8);
+  auto q_full = [&](int t) { return bar_addr + 8u * (0 + t); };
+  auto k_full = [&](int s) { return bar_addr + 8u * (2 + s); };
+  auto v_full = [&](int s) { return bar_addr + 8u * (4 + s); };
+  auto k_empty = [&](int s) { return bar_addr + 8u * (6 + s); };
+  auto v_empty = [&](int s) { return bar_addr + 8u * (8 + s); };
+  auto s_full = [&](int t) { return bar_addr + 8u * (10 + t); };
+  auto p_full = [&](int t) { return bar_addr + 8u * (12 + t); };
+  auto o_done = [&](int t) { return bar_addr + 8u * (14 + t); };
+  auto q_empty = [&](int t) { return bar_addr + 8u * (16 + t); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * 18);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 18 + 8);
   volatile float2* xchg = reinterpret_cast<volatile float2*>(bar_ptr + 256);
+  float* stage_base = reinterpret_cast<float*>(bar_ptr + 256 + A_XCHG_BYTES);   // 1 KiB per softmax warp
   constexpr int kTmaWarp = 8 * SPLIT, kMmaWarp = 8 * SPLIT + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int heads_per_group = Hq / Hkv;
-  const int group = group_begin + (int)blockIdx.y / heads_per_group;
-  const int b = group / Hkv, hkv = group % Hkv;
-  const int hq = hkv * heads_per_group + (int)blockIdx.y % heads_per_group;
-  const int q_row0 = (b * Hq + hq) * S + (int)blockIdx.x * (2 * A_BM);   // row in the [B*Hq*S, D] view
-  const int kv_row0 = (b * Hkv + hkv) * S;
+  const int qblocks = S / (2 * A_BM);
   const int num_kv = S / A_BN;
+  const int my_items = ((int)blockIdx.x < total_items) ? (total_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+  const int total_steps = my_items * num_kv;
 
   for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) {   // sequence 0 = empty
     xchg[i].x = 0.f;
@@ -133,7 +158,6 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    ptx::mbar_init(q_full, 1);
     for (int s = 0; s < A_KV_STAGES; ++s) {
       ptx::mbar_init(k_full(s), 1);
       ptx::mbar_init(v_full(s), 1);
@@ -141,6 +165,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::mbar_init(v_empty(s), 1);
     }
     for (int t = 0; t < 2; ++t) {
+      ptx::mbar_init(q_full(t), 1);
+      ptx::mbar_init(q_empty(t), 1);
       ptx::mbar_init(s_full(t), 1);
       ptx::mbar_init(p_full(t), 4 * SPLIT);   // one arrival per softmax warp
       ptx::mbar_init(o_done(t), 1);
@@ -163,27 +189,39 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == kTmaWarp) {
     // ------------------------------------ TMA producer ---------------------------------------
     if (lane == 0) {
-      ptx::mbar_expect_tx(q_full, 2 * A_TILE_BYTES);
-      for (int t = 0; t < 2; ++t)
-        for (int h = 0; h < 2; ++h)
-          ptx::tma_load_2d(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES, &tm_q, h * 64, q_row0 + t * A_BM, q_full);
-      for (int j = 0; j < num_kv; ++j) {
-        const int s = j % A_KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / A_KV_STAGES) & 1u;
-        if (!ptx::mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1100); break; }
-        ptx::mbar_expect_tx(k_full(s), A_TILE_BYTES);
-        for (int h = 0; h < 2; ++h)
-          ptx::tma_load_2d(k_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_k, h * 64, kv_row0 + j * A_BN, k_full(s));
-        if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1200); break; }
-        ptx::mbar_expect_tx(v_full(s), A_TILE_BYTES);
-        for (int h = 0; h < 2; ++h)
-          ptx::tma_load_2d(v_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_v, h * 64, kv_row0 + j * A_BN, v_full(s));
+      int g = 0;
+      bool ok = true;
+      for (int it = 0; it < my_items && ok; ++it) {
+        const AttnItem item = attn_item((int)blockIdx.x + it * (int)gridDim.x, qblocks, Hq, Hkv, S, group_begin);
+        for (int j = 0; j < num_kv; ++j, ++g) {
+          const int s = g % A_KV_STAGES;
+          const uint32_t ph = (uint32_t)(g / A_KV_STAGES) & 1u;
+          if (!ptx::mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1100); ok = false; break; }
+          ptx::mbar_expect_tx(k_full(s), A_TILE_BYTES);
+          for (int h = 0; h < 2; ++h)
+            ptx::tma_load_2d(k_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_k, h * 64, item.kv_row0 + j * A_BN, k_full(s));
+          if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1200); ok = false; break; }
+          ptx::mbar_expect_tx(v_full(s), A_TILE_BYTES);
+          for (int h = 0; h < 2; ++h)
+            ptx::tma_load_2d(v_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_v, h * 64, item.kv_row0 + j * A_BN, v_full(s));
+          if (j == 0) {
+            // this item's queries, after its first keys so that the K/V stream never waits for a query buffer;
+            // a buffer is free once the previous item's last score product has read it
+            for (int t = 0; t < 2 && ok; ++t) {
+              if (it > 0 && !ptx::mbar_wait(q_empty(t), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1300); ok = false; break; }
+              ptx::mbar_expect_tx(q_full(t), A_TILE_BYTES);
+              for (int h = 0; h < 2; ++h)
+                ptx::tma_load_2d(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES, &tm_q, h * 64, item.q_row0 + t * A_BM, q_full(t));
+            }
+            if (!ok) break;
+          }
+        }
       }
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------ MMA issuer -----------------------------------------
-    if (lane == 0) {
+    if (lane == 0 && total_steps > 0) {
       constexpr uint32_t kIdescQK = attn_idesc(0);
       constexpr uint32_t kIdescPV = attn_idesc(1);
       bool ok = true;
@@ -209,43 +247,35 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ptx::umma_ts_f16(o_tmem, p_col, vd, kIdescPV, 1u);
         }
       };
-      if (!ptx::mbar_wait(q_full, 0, abort_flag)) { atomicExch(status, 0x2100); ok = false; }
-      if (ok && !ptx::mbar_wait(k_full(0), 0, abort_flag)) { atomicExch(status, 0x2200); ok = false; }
-      if (ok) {
+      // scores of tile t for global step g + 1 (the next step of this item, or the first of the next item)
+      auto next_scores = [&](int t, int g) -> bool {
+        const int gn = g + 1, jn = gn % num_kv, sn = gn % A_KV_STAGES;
+        if (jn == 0 && !ptx::mbar_wait(q_full(t), (uint32_t)(gn / num_kv) & 1u, abort_flag)) { atomicExch(status, 0x2100 | t); return false; }
+        if (t == 0 && !ptx::mbar_wait(k_full(sn), (uint32_t)(gn / A_KV_STAGES) & 1u, abort_flag)) { atomicExch(status, 0x2500); return false; }
         ptx::tc_fence_after();
-        issue_qk(0, 0);
-        ptx::umma_commit<1>(s_full(0));
-        issue_qk(1, 0);
-        ptx::umma_commit<1>(s_full(1));
-        ptx::umma_commit<1>(k_empty(0));
-      }
-      for (int j = 0; j < num_kv && ok; ++j) {
-        const int s = j % A_KV_STAGES, sn = (j + 1) % A_KV_STAGES;
-        const uint32_t ph = (uint32_t)(j / A_KV_STAGES) & 1u, phn = (uint32_t)((j + 1) / A_KV_STAGES) & 1u;
-        const bool more = j + 1 < num_kv;
+        issue_qk(t, sn);
+        ptx::umma_commit<1>(s_full(t));
+        if (t == 1) ptx::umma_commit<1>(k_empty(sn));
+        if (jn == num_kv - 1) ptx::umma_commit<1>(q_empty(t));   // the item's last read of this query tile
+        return true;
+      };
+      ok = next_scores(0, -1) && next_scores(1, -1);
+      for (int g = 0; g < total_steps && ok; ++g) {
+        const int s = g % A_KV_STAGES, j = g % num_kv;
+        const uint32_t ph = (uint32_t)(g / A_KV_STAGES) & 1u;
+        const bool more = g + 1 < total_steps, first = j == 0, last = j == num_kv - 1;
         if (!ptx::mbar_wait(v_full(s), ph, abort_flag)) { atomicExch(status, 0x2300); break; }
-        if (!ptx::mbar_wait(p_full(0), (uint32_t)j & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
+        if (!ptx::mbar_wait(p_full(0), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
         ptx::tc_fence_after();
-        issue_pv(0, s, j == 0);
-        if (more) {
-          if (!ptx::mbar_wait(k_full(sn), phn, abort_flag)) { atomicExch(status, 0x2500); break; }
-          ptx::tc_fence_after();
-          issue_qk(0, sn);
-          ptx::umma_commit<1>(s_full(0));
-        } else {
-          ptx::umma_commit<1>(o_done(0));
-        }
-        if (!ptx::mbar_wait(p_full(1), (uint32_t)j & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
+        issue_pv(0, s, first);
+        if (last) ptx::umma_commit<1>(o_done(0));
+        if (more && !next_scores(0, g)) break;
+        if (!ptx::mbar_wait(p_full(1), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
         ptx::tc_fence_after();
-        issue_pv(1, s, j == 0);
+        issue_pv(1, s, first);
         ptx::umma_commit<1>(v_empty(s));
-        if (more) {
-          issue_qk(1, sn);
-          ptx::umma_commit<1>(s_full(1));
-          ptx::umma_commit<1>(k_empty(sn));
-        } else {
-          ptx::umma_commit<1>(o_done(1));
-        }
+        if (last) ptx::umma_commit<1>(o_done(1));
+        if (more && !next_scores(1, g)) break;
       }
     }
     __syncwarp();
@@ -265,14 +295,18 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t o_tmem = tmem_base + lane_field + (uint32_t)(256 + t * 128);
     volatile float2* my_slot = xchg + ((t * 2 + part) * 128 + row_in_tile);
     volatile float2* peer_slot = xchg + ((t * 2 + (part ^ 1)) * 128 + row_in_tile);
+    float* stage = stage_base + warp * 256;   // [32 rows][8 floats], 16-byte pieces swapped on every other group of 4 rows
     float m_used = -INFINITY;   // log2-domain maximum the current probabilities are scaled by
     float mass = 0.f;
-    bool ok = true;
-    for (int j = 0; j < num_kv; ++j) {
-      const bool ready = ptx::mbar_wait(s_full(t), (uint32_t)j & 1u, abort_flag);
+    for (int g = 0; g < total_steps; ++g) {
+      const int j = g % num_kv;
+      if (j == 0) {   // a new item starts
+        m_used = -INFINITY;
+        mass = 0.f;
+      }
+      const bool ready = ptx::mbar_wait(s_full(t), (uint32_t)g & 1u, abort_flag);
       if (!__all_sync(0xffffffffu, ready)) {
         if (lane == 0) atomicExch(status, 0x3100 | t);
-        ok = false;
         break;
       }
       ptx::tc_fence_after();
@@ -288,10 +322,9 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       if constexpr (SPLIT == 2) {
         float other;
-        const bool got = exchange_with_peer(my_slot, peer_slot, mx, j + 1, abort_flag, other);
+        const bool got = exchange_with_peer(my_slot, peer_slot, mx, 2 * g + 1, abort_flag, other);
         if (!__all_sync(0xffffffffu, got)) {
           if (lane == 0) atomicExch(status, 0x3300 | t);
-          ok = false;
           break;
         }
         mx = fmaxf(mx, other);
@@ -341,43 +374,49 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(p_full(t));
-    }
-    if (ok) {
-      bool ready = ptx::mbar_wait(o_done(t), 0, abort_flag);
+      if (j != num_kv - 1) continue;
+
+      // ---- the item's last step: normalise and store its output while the tensor core already works on the other
+      // tile and on the next item's scores (the next item's first product into O_t waits for this warp's next arrival
+      // on p_full, which comes after the reads below) ----
+      const int it = g / num_kv;
+      bool done = ptx::mbar_wait(o_done(t), (uint32_t)it & 1u, abort_flag);
       if constexpr (SPLIT == 2) {
         float other = 0.f;
-        ready = ready && exchange_with_peer(my_slot, peer_slot, mass, num_kv + 1, abort_flag, other);
+        done = done && exchange_with_peer(my_slot, peer_slot, mass, 2 * g + 2, abort_flag, other);
         mass += other;
       }
-      if (!__all_sync(0xffffffffu, ready)) {
+      if (!__all_sync(0xffffffffu, done)) {
         if (lane == 0) atomicExch(status, 0x3200 | t);
-      } else {
-        ptx::tc_fence_after();
-        const float inv = 1.0f / mass;
-        // Output through a 4 KiB per-warp staging block (in this tile's Q buffer, which no MMA reads any
-        // more): each thread owns one row in tensor memory, but a warp-wide store should cover whole rows,
-        // so the 32x32 block is written row-per-thread with an XOR swizzle and read back four rows per
-        // instruction, 128 contiguous bytes per row.
-        float* stage = reinterpret_cast<float*>(base_ptr + t * A_TILE_BYTES) + (warp % (4 * SPLIT)) * (32 * 32);
-        const int tile_row0 = (int)blockIdx.x * (2 * A_BM) + t * A_BM + quarter * 32;
-        float* obase = out + ((int64_t)(b * Hq + hq) * S + tile_row0) * A_D;
-        const int sub_row = lane >> 3, piece = lane & 7;
+        break;
+      }
+      ptx::tc_fence_after();
+      const float inv = 1.0f / mass;
+      const AttnItem item = attn_item((int)blockIdx.x + it * (int)gridDim.x, qblocks, Hq, Hkv, S, group_begin);
+      float* obase = out + ((int64_t)item.q_row0 + t * A_BM + quarter * 32) * A_D;
+      // Each thread owns one row in tensor memory, but a warp-wide store should cover whole 32-byte sectors of
+      // several rows: 8 columns of the warp's 32 rows go through a 1 KiB staging block (16-byte pieces swapped on
+      // every other group of four rows, so neither side has bank conflicts) and come back 16 rows per instruction.
+      const int wr_swap = (lane >> 2) & 1;
+      const int rd_row = lane >> 1, rd_piece = lane & 1;
 #pragma unroll 1
-        for (int c = c0; c < c0 + kChunks; ++c) {
-          uint32_t r[32];
-          ptx::tmem_ld_32x32(o_tmem + (uint32_t)(c * 32), r);
-          ptx::tmem_ld_wait();
+      for (int c = c0; c < c0 + kChunks; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(o_tmem + (uint32_t)(c * 32), r);
+        ptx::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 8; ++i)
-            *reinterpret_cast<float4*>(stage + lane * 32 + 4 * (i ^ (lane & 7))) =
-                make_float4(__uint_as_float(r[4 * i]) * inv, __uint_as_float(r[4 * i + 1]) * inv,
-                            __uint_as_float(r[4 * i + 2]) * inv, __uint_as_float(r[4 * i + 3]) * inv);
+        for (int sub = 0; sub < 4; ++sub) {
+#pragma unroll
+          for (int i = 0; i < 2; ++i)
+            *reinterpret_cast<float4*>(stage + lane * 8 + 4 * (i ^ wr_swap)) =
+                make_float4(__uint_as_float(r[8 * sub + 4 * i]) * inv, __uint_as_float(r[8 * sub + 4 * i + 1]) * inv,
+                            __uint_as_float(r[8 * sub + 4 * i + 2]) * inv, __uint_as_float(r[8 * sub + 4 * i + 3]) * inv);
           __syncwarp();
 #pragma unroll
-          for (int rr = 0; rr < 32; rr += 4) {
-            const int rloc = rr + sub_row;
-            const float4 val = *reinterpret_cast<const float4*>(stage + rloc * 32 + 4 * (piece ^ (rloc & 7)));
-            *reinterpret_cast<float4*>(obase + (int64_t)rloc * A_D + c * 32 + 4 * piece) = val;
+          for (int h = 0; h < 2; ++h) {
+            const int rloc = rd_row + 16 * h;
+            const float4 val = *reinterpret_cast<const float4*>(stage + rloc * 8 + 4 * (rd_piece ^ ((rloc >> 2) & 1)));
+            *reinterpret_cast<float4*>(obase + (int64_t)rloc * A_D + c * 32 + sub * 8 + 4 * rd_piece) = val;
           }
           __syncwarp();
         }
@@ -451,12 +490,17 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
   }
   int* status = device_status_word();
   DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "gqa: could not allocate the device status word");
-  const int64_t heads = (ge - gb) * (Hq / Hkv);
-  DTN_REQUIRE(heads <= 65535, DTN_ERR_UNSUPPORTED, "gqa: too many heads for one launch");
-  dim3 grid((unsigned)(S / (2 * A_BM)), (unsigned)heads);
+  const int64_t items = (ge - gb) * (Hq / Hkv) * (S / (2 * A_BM));
+  DTN_REQUIRE(items < (1LL << 31) && B * Hq * S < (1LL << 31), DTN_ERR_UNSUPPORTED, "gqa: too many query rows for one launch");
+  // One CTA per SM walks the items round-robin; DTN_GQA_PERSISTENT=0 launches one CTA per item instead.
+  static const bool persistent = [] {
+    const char* text = getenv("DTN_GQA_PERSISTENT");
+    return !(text && text[0] == '0');
+  }();
+  const int64_t ctas = persistent && items > sm_count() ? sm_count() : items;
   const float scale_log2e = scale * 1.4426950408889634f;
-  gqa_tc_kernel<SPLIT><<<grid, attn_threads(SPLIT), A_SMEM_BYTES, s>>>(mq, mk, mv, out, (int)Hq, (int)Hkv, (int)S, scale_log2e, (int)gb,
-                                                      status);
+  gqa_tc_kernel<SPLIT><<<(unsigned)ctas, attn_threads(SPLIT), A_SMEM_BYTES, s>>>(mq, mk, mv, out, (int)Hq, (int)Hkv, (int)S, scale_log2e,
+                                                                                 (int)gb, (int)items, status);
   DTN_LAUNCH_CHECK("gqa_tc_kernel");
   return DTN_OK;
 }
