@@ -199,16 +199,10 @@ def open_workload_latencies() -> dict:
     (benchmark.py:244-268). `reference_rtx5090_us` is the reference's published number on other hardware."""
     import math
     from deuteron_b200 import LocalRunner, compile_kernel, schedules as S
-    cases = (
-        ('p00_add_128', S.vector_add_example(128), 2.976), ('p01_add_1024', S.vector_add_example(1024), 2.976),
-        ('p02_affine_4096', S.pointwise_example('affine', 4096), 3.040), ('p03_relu_multiply_2048', S.pointwise_example('relu_multiply', 2048), 2.976),
-        ('r01_sum_1024', S.row_reduce_example(1, 1024, 'sum'), 2.960), ('r02_sum_65536', S.row_reduce_example(1, 65536, 'sum'), 6.816),
-        ('r03_mean_32768', S.mean_example(32768), 4.784), ('r04_row_sum_64x512', S.row_reduce_example(64, 512, 'sum'), 2.960),
-        ('m01_matmul_512', S.matmul_example(512, 512, 512), 8.896), ('m02_matmul_128x256x64', S.split_k_matmul_example(128, 64, 256), 3.144),
-        ('f01_rms_norm_64x1024', S.rms_norm_example(64, 1024), 3.152), ('f02_softmax_64x256', S.row_softmax_example(64, 256), 2.976),
-        ('f03_l2_norm_64x512', S.l2_norm_example(64, 512), 2.976),
-        ('a01_attention_64x64_d64', S.attention_example(64, 64, 64, columns=64), 4.800),
-        ('a02_attention_128_d32', S.attention_example(128, 128, 32), 4.800))
+    published_us = {'p00_scalar_add': 2.976, 'p01_vector_add': 2.976, 'p02_scale_shift': 3.040, 'p03_relu_mul': 2.976, 'r01_array_sum': 2.960,
+                    'r02_big_sum': 6.816, 'r03_mean': 4.784, 'r04_row_sum': 2.960, 'm01_matmul_512': 8.896, 'm02_matmul_rect': 3.144,
+                    'f01_rmsnorm': 3.152, 'f02_row_softmax': 2.976, 'f03_l2norm': 2.976, 'a01_attention': 4.800, 'a02_attention_128': 4.800}
+    cases = [(name, pair, published_us[name]) for name, pair in S.open_workloads().items()]
     out = {}
     with LocalRunner(0) as runner:
         for name, (graph, meta), published in cases:

@@ -18,6 +18,7 @@ from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Any
 
+from . import cache
 from .classify import Plan, classify
 from .options import Options
 from .validation import parse_kernel, validate_compile_arguments, validate_launch
@@ -83,13 +84,23 @@ def compile_kernel(source: Any, meta: Any = None, *, arch: Any = 'sm_100a', opt_
         if hit is not None:
             _CACHE.move_to_end(key)
             return hit
-        kernel, launch = parse_kernel(payload, meta_payload)
-        specs = validate_launch(launch)
-        plan = classify(kernel, launch, specs, options.contraction_precision)
-        description = (f'// deuteron_b200 native kernel selection for entry {kernel.name}\n'
-                       f'// target {arch}, opt_level {opt_level}\n// {plan.describe()}\n')
-        result = Compilation(ptx=description, unoptimized=description, optimized=description, plan=plan,
-                             launch=json.loads(json.dumps(launch)), arch=arch)
+        root = os.environ.get('DEUTERON_CACHE')   # directory of on-disk records (compiler/build.py:99-104)
+        stored = cache.read(root, key)
+        if stored is not None:
+            plan = Plan(stored['kind'], stored['params'], {role: (name, offset) for role, (name, offset) in stored['buffers'].items()})
+            result = Compilation(ptx=stored['text'], unoptimized=stored['text'], optimized=stored['text'], plan=plan,
+                                 launch=stored['launch'], arch=stored['arch'])
+        else:
+            kernel, launch = parse_kernel(payload, meta_payload)
+            specs = validate_launch(launch)
+            plan = classify(kernel, launch, specs, options.contraction_precision)
+            description = (f'// deuteron_b200 native kernel selection for entry {kernel.name}\n'
+                           f'// target {arch}, opt_level {opt_level}\n// {plan.describe()}\n')
+            result = Compilation(ptx=description, unoptimized=description, optimized=description, plan=plan,
+                                 launch=json.loads(json.dumps(launch)), arch=arch)
+            cache.write(root, key, {'text': description, 'kind': plan.kind, 'params': json.loads(json.dumps(plan.params)),
+                                    'buffers': {role: [name, offset] for role, (name, offset) in plan.buffers.items()},
+                                    'launch': result.launch, 'arch': arch})
         _CACHE[key] = result
         if len(_CACHE) > _CACHE_ENTRIES:
             _CACHE.popitem(last=False)

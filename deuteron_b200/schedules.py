@@ -614,3 +614,35 @@ def gqa_attention_example(batch: int = 4, query_heads: int = 32, kv_heads: int =
     launch = {'node': 'out', 'entry': entry, 'arg_order': ['q', 'k', 'v', 'out'], 'grid': [batch * query_heads * positions, 1, 1],
               'block': [depth, 1, 1], 'smem_bytes': 0, 'zero_outputs': [], 'args': args, 'final': True}
     return graph, _metadata(entry, launch, 0.001, 0.0001, ['q', 'k', 'v'], ['out'])
+
+
+# ------------------------------------------------------------------------------------------------
+# problem directories
+# ------------------------------------------------------------------------------------------------
+
+
+def open_workloads() -> dict[str, tuple[dict, dict]]:
+    """The reference's fifteen open workloads (README.md:163-180) in their published shapes and launch geometries
+    (benchmarks/rtx5090-2026-10-24-r6.json, `variants[].launch`), regenerated as (graph, metadata) pairs: the IR files
+    of that set are not part of the reference's repository."""
+    return {
+        'p00_scalar_add': vector_add_example(128), 'p01_vector_add': vector_add_example(1024),
+        'p02_scale_shift': pointwise_example('affine', 4096), 'p03_relu_mul': pointwise_example('relu_multiply', 2048),
+        'r01_array_sum': row_reduce_example(1, 1024, 'sum'), 'r02_big_sum': row_reduce_example(1, 65536, 'sum'),
+        'r03_mean': mean_example(32768), 'r04_row_sum': row_reduce_example(64, 512, 'sum'),
+        'm01_matmul_512': matmul_example(512, 512, 512), 'm02_matmul_rect': split_k_matmul_example(128, 64, 256),
+        'f01_rmsnorm': rms_norm_example(64, 1024), 'f02_row_softmax': row_softmax_example(64, 256),
+        'f03_l2norm': l2_norm_example(64, 512),
+        'a01_attention': attention_example(64, 64, 64, columns=64), 'a02_attention_128': attention_example(128, 128, 32),
+    }
+
+
+def write_problem(directory: Any, graph: dict, metadata: dict) -> None:
+    """Writes one problem directory in the layout the reference's benchmark driver reads (benchmark.py:447-466):
+    `meta.json` and `<entry>.ir.json` for the (single) kernel of the metadata. `expected.npz` is the caller's to add."""
+    import json
+    from pathlib import Path
+    directory = Path(directory)
+    directory.mkdir(parents=True, exist_ok=True)
+    (directory / 'meta.json').write_text(json.dumps(metadata, indent=1) + '\n')
+    (directory / (metadata['kernels'][0]['entry'] + '.ir.json')).write_text(json.dumps(graph) + '\n')

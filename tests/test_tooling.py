@@ -1,0 +1,142 @@
+"""The compile cache on disk, the command line and the problem-directory driver (the reference's
+tests/test_cache.py, tests/test_cli.py and the conventions of benchmark.py:290-308, 497-557)."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from deuteron_b200 import benchmark, build, cache, cli, compile_kernel, schedules
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+@pytest.fixture()
+def problem(tmp_path):
+    graph, meta = schedules.rms_norm_example(8, 512)
+    schedules.write_problem(tmp_path / 'f01_rmsnorm', graph, meta)
+    return tmp_path / 'f01_rmsnorm'
+
+
+def test_disk_cache_round_trip_and_rejection_of_damaged_records(tmp_path, monkeypatch):
+    root = tmp_path / 'cache'
+    monkeypatch.setenv('DEUTERON_CACHE', str(root))
+    graph, meta = schedules.row_softmax_example()
+    build.clear_cache()
+    first = compile_kernel(graph, meta)
+    records = list(root.glob('*.json'))
+    assert len(records) == 1 and len(records[0].stem) == 64
+    build.clear_cache()
+    again = compile_kernel(graph, meta)             # served from disk: same plan, same text, same launch
+    assert again.plan == first.plan and again.ptx == first.ptx and again.launch == first.launch
+    assert isinstance(again.plan.buffers['x'], tuple)
+    key = records[0].stem
+    stored = json.loads(records[0].read_text())
+    # a record whose content was altered, whose key disagrees, or which is not JSON is ignored, never trusted
+    for damage in (lambda d: d['params'].update(cols=999), lambda d: d.update(key='0' * 64), lambda d: d.update(version=2),
+                   lambda d: d.pop('launch')):
+        altered = json.loads(json.dumps(stored))
+        damage(altered)
+        records[0].write_text(json.dumps(altered))
+        assert cache.read(str(root), key) is None
+    records[0].write_text('{not json')
+    assert cache.read(str(root), key) is None
+    build.clear_cache()
+    assert compile_kernel(graph, meta).plan == first.plan     # recompiled and rewritten
+    assert cache.read(str(root), key) is not None
+    assert cache.read(str(root), '../' + key) is None and cache.read(None, key) is None
+    assert not list(root.glob('*.tmp'))
+    # an unwritable cache directory is not an error
+    monkeypatch.setenv('DEUTERON_CACHE', str(records[0] / 'below-a-file'))
+    build.clear_cache()
+    assert compile_kernel(graph, meta).plan == first.plan
+
+
+def test_command_line_prints_the_selection_and_protects_inputs(problem, capsys, tmp_path):
+    kernel = problem / 'k_rms_norm.ir.json'
+    assert cli.main([str(kernel)]) == 0
+    text = capsys.readouterr().out
+    assert 'row_fused(' in text and 'target sm_100a' in text
+    dump = tmp_path / 'selection.ll'
+    assert cli.main([str(kernel), '--dump-llvm', str(dump), '--contraction-precision', 'tf32x3', '--no-approximate-math']) == 0
+    assert dump.read_text() == capsys.readouterr().out
+    before = (problem / 'meta.json').read_bytes()
+    assert cli.main([str(kernel), '--dump-llvm', str(problem / 'meta.json')]) == 1
+    assert 'would overwrite an input file' in capsys.readouterr().err and (problem / 'meta.json').read_bytes() == before
+    assert cli.main([str(kernel), '--dump-llvm', str(dump), '--dump-unoptimized', str(dump)]) == 1
+    assert cli.main([str(kernel), '--dump-llvm', str(tmp_path / 'missing' / 'x.ll')]) == 1
+    assert cli.main([str(kernel), '--arch', 'sm_89']) == 1
+    assert 'sm_100a' in capsys.readouterr().err
+    assert cli.main([str(problem / 'absent.ir.json')]) == 1
+    with pytest.raises(SystemExit):
+        cli.main([str(kernel), '--opt-level', '7'])
+    done = subprocess.run([sys.executable, '-m', 'deuteron_b200', str(kernel)], capture_output=True, text=True, cwd=ROOT)
+    assert done.returncode == 0 and 'row_fused(' in done.stdout
+
+
+def test_driver_refuses_bad_arguments_and_reused_artifact_directories(problem, tmp_path, capsys):
+    artifacts = tmp_path / 'out'
+    artifacts.mkdir()
+    benchmark.reserve_artifacts(artifacts)
+    with pytest.raises(ValueError, match='already reserved'):
+        benchmark.reserve_artifacts(artifacts)
+    benchmark.write_json(artifacts / 'manifest.json', {'a': 1})
+    assert json.loads((artifacts / 'manifest.json').read_text()) == {'a': 1} and not list(artifacts.glob('*.tmp'))
+    with pytest.raises(ValueError, match='new artifacts directory'):
+        benchmark.reserve_artifacts(artifacts)
+    for argv in (['--problems-dir', str(tmp_path / 'nowhere')], ['--problems-dir', str(problem.parent), 'zzz'],
+                 ['--problems-dir', str(problem.parent), '--devices', '0,0'], ['--problems-dir', str(problem.parent), '--iters', '0'],
+                 ['--problems-dir', str(problem.parent), '--artifacts', str(artifacts)]):
+        with pytest.raises(SystemExit):
+            benchmark.main(argv)
+    capsys.readouterr()
+
+
+def test_generated_problem_set_has_the_published_launches():
+    workloads = schedules.open_workloads()
+    assert len(workloads) == 15
+    launch = workloads['f01_rmsnorm'][1]['kernels'][0]
+    assert launch['arg_order'] == ['mean_count', 'add_c1', 'x', 'w', 'mul_1'] and launch['grid'] == [64, 1, 1] and launch['block'] == [128, 1, 1]
+    launch = workloads['m02_matmul_rect'][1]['kernels'][0]
+    assert launch['arg_order'] == ['x1', 'x0', 'matmul'] and launch['grid'] == [512, 1, 1] and launch['zero_outputs'] == ['matmul']
+    launch = workloads['r03_mean'][1]['kernels'][0]
+    assert launch['arg_order'] == ['x', 'mean_keepdim_count', 'mean'] and launch['grid'] == [1, 1, 1]
+    assert workloads['p02_scale_shift'][1]['kernels'][0]['grid'] == [4, 1, 1]
+    assert workloads['m01_matmul_512'][1]['kernels'][0]['grid'] == [128, 1, 1]
+
+
+@pytest.mark.gpu
+def test_driver_runs_the_generated_problem_set(tmp_path, cuda):
+    from deuteron_b200 import argument_array
+    from oracle import reference_math as R
+    inputs = lambda meta: {a['name']: argument_array(a) for a in meta['kernels'][0]['args'] if not a.get('output')}
+    expected = {
+        'p00_scalar_add': lambda v: {'sum': v['lhs'] + v['rhs']}, 'p01_vector_add': lambda v: {'sum': v['lhs'] + v['rhs']},
+        'p02_scale_shift': lambda v: {'add': v['x'] * np.float32(2) + np.float32(1)},
+        'p03_relu_mul': lambda v: {'mul': np.maximum(v['x'], np.float32(0)) * v['y']},
+        'r01_array_sum': lambda v: {'out': R.row_sum_f64(v['x'])}, 'r02_big_sum': lambda v: {'out': R.row_sum_f64(v['x'])},
+        'r03_mean': lambda v: {'mean': R.row_mean_f64(v['x'][None, :])}, 'r04_row_sum': lambda v: {'out': R.row_sum_f64(v['x'])},
+        'm01_matmul_512': lambda v: {'result': R.gemm_f64(v['left'], v['right'])},
+        'm02_matmul_rect': lambda v: {'matmul': R.gemm_f64(v['x0'], v['x1'])},
+        'f01_rmsnorm': lambda v: {'mul_1': R.rms_norm_f64(v['x'], v['w'], 1024.0, 1e-5)},
+        'f02_row_softmax': lambda v: {'softmax': R.row_softmax_f64(v['x'])}, 'f03_l2norm': lambda v: {'div': R.l2_norm_f64(v['x'])},
+        'a01_attention': lambda v: {'out': R.attention_f64(v['q'], v['kt'], v['v'], np.float32(1 / np.sqrt(64)))},
+        'a02_attention_128': lambda v: {'out': R.attention_f64(v['q'], v['kt'], v['v'], np.float32(1 / np.sqrt(32)))},
+    }
+    problems = tmp_path / 'problems'
+    for name, (graph, meta) in schedules.open_workloads().items():
+        schedules.write_problem(problems / name, graph, meta)
+        np.savez(problems / name / 'expected.npz', **expected[name](inputs(meta)))
+    artifacts = tmp_path / 'artifacts'
+    assert benchmark.main(['--problems-dir', str(problems), '--artifacts', str(artifacts), '--warmup', '2', '--iters', '20', '--samples', '3']) == 0
+    results = json.loads((artifacts / 'results.json').read_text())
+    assert len(results) == 15 and all(r['passed'] for r in results)
+    one = json.loads((artifacts / 'f02_row_softmax' / 'result.json').read_text())
+    assert one['kernels'][0]['entry'] == 'k_softmax' and one['kernels'][0]['median_us'] > 0 and one['max_abs_error']['softmax'] < 1e-6
+    assert (artifacts / 'f02_row_softmax' / 'actual.npz').exists() and (artifacts / 'manifest.json').exists()
+    # a second run into the same directory is refused
+    with pytest.raises(SystemExit):
+        benchmark.main(['--problems-dir', str(problems), '--artifacts', str(artifacts)])
