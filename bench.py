@@ -259,10 +259,14 @@ def extras(torch, ops, peaks: dict) -> dict:
     k = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
     v = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
     o = torch.empty((batch, hq, s, d), device=device)
-    ms = timed(torch, lambda: ops.gqa_attention(q, k, v, d ** -0.5, out=o), 2, warmup=1)
+    import time
+    torch.cuda.synchronize()
+    time.sleep(3.0)   # the kernel is timed alone (burst peak as denominator): let the clocks recover from the runs above
+    ms = timed(torch, lambda: ops.gqa_attention(q, k, v, d ** -0.5, out=o), 10, warmup=3)
     flops = 4.0 * batch * hq * s * s * d
     out['gqa_fwd_b4_h32_kv8_s4096_d128_f16'] = {'ms': ms, 'tflops': flops / ms / 1e9,
-                                               'frac_of_bf16_peak': flops / ms / 1e9 / peaks['bf16_tflops']}
+                                               'frac_of_bf16_peak': flops / ms / 1e9 / peaks['bf16_tflops'],
+                                               'note': '10 launches after 3 s of idle and 3 warm-up launches'}
     return out
 
 
@@ -426,7 +430,7 @@ def run_profile_case(name: str, launches: int) -> None:
         c = torch.empty((n, n), device=device)
         call = lambda: ops.gemm(a, b, name[5:], out=c)
     elif name == 'attention':
-        batch, hq, hkv, s, d = 1, 16, 4, 4096, 128
+        batch, hq, hkv, s, d = 2, 16, 4, 4096, 128   # 512 work items of 256 queries: 3.5 per SM
         q = (torch.randn((batch, hq, s, d), device=device, generator=generator) / d ** 0.5).half()
         k = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
         v = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()

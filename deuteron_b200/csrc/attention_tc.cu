@@ -120,7 +120,7 @@ template <int SPLIT /*warpgroups per 128-row tile: 1 or 2*/>
 __global__ void __launch_bounds__(attn_threads(SPLIT), 1)
 gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
               const __grid_constant__ CUtensorMap tm_v, float* __restrict__ out, int Hq, int Hkv, int S,
-              float scale_log2e, int group_begin, int total_items, int* __restrict__ status) {
+              float scale_log2e, int group_begin, int total_items, int early_pv, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -137,11 +137,11 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   auto k_empty = [&](int s) { return bar_addr + 8u * (6 + s); };
   auto v_empty = [&](int s) { return bar_addr + 8u * (8 + s); };
   auto s_full = [&](int t) { return bar_addr + 8u * (10 + t); };
-  auto p_full = [&](int t) { return bar_addr + 8u * (12 + t); };
-  auto o_done = [&](int t) { return bar_addr + 8u * (14 + t); };
-  auto q_empty = [&](int t) { return bar_addr + 8u * (16 + t); };
-  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * 18);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 18 + 8);
+  auto p_half = [&](int t, int h) { return bar_addr + 8u * (12 + 2 * t + h); };   // half of a tile's probabilities is in tensor memory
+  auto o_done = [&](int t) { return bar_addr + 8u * (16 + t); };
+  auto q_empty = [&](int t) { return bar_addr + 8u * (18 + t); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * 20);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 20 + 8);
   volatile float2* xchg = reinterpret_cast<volatile float2*>(bar_ptr + 256);
   float* stage_base = reinterpret_cast<float*>(bar_ptr + 256 + A_XCHG_BYTES);   // 1 KiB per softmax warp
   constexpr int kTmaWarp = 8 * SPLIT, kMmaWarp = 8 * SPLIT + 1;
@@ -168,7 +168,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::mbar_init(q_full(t), 1);
       ptx::mbar_init(q_empty(t), 1);
       ptx::mbar_init(s_full(t), 1);
-      ptx::mbar_init(p_full(t), 4 * SPLIT);   // one arrival per softmax warp
+      ptx::mbar_init(p_half(t, 0), 4 * SPLIT);   // one arrival per softmax warp
+      ptx::mbar_init(p_half(t, 1), 4 * SPLIT);
       ptx::mbar_init(o_done(t), 1);
     }
     ptx::mbar_fence_init();
@@ -235,15 +236,22 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                              ptx::umma_desc_sw128(ka + off), kIdescQK, kk ? 1u : 0u);
         }
       };
-      // O_t += P_t V : 8 k-steps of 16 keys; per step the high and the residual plane of P
-      auto issue_pv = [&](int t, int s, bool first) {
+      // O_t += P_t V : 8 k-steps of 16 keys; per step the high and the residual plane of P. The probabilities arrive
+      // in two halves (the 32-key chunks every softmax warpgroup finishes first, then the rest), so the products of
+      // the first half run while the second is still being computed: half h covers k-steps kk with
+      // ((kk >> 1) / chunks-per-warpgroup-half) matching the order the warpgroups write their chunks.
+      auto issue_pv = [&](int t, int s, bool first, int half) {
         const uint32_t va = v_addr + s * A_TILE_BYTES;
         const uint32_t o_tmem = tmem_base + (uint32_t)(256 + t * 128);
 #pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
+        for (int i = 0; i < 4; ++i) {
+          // SPLIT == 2: warpgroup 0 writes chunks 0, 1 and warpgroup 1 chunks 2, 3 -> halves {0, 2} and {1, 3};
+          // SPLIT == 1: one warpgroup writes chunks 0..3 in order -> halves {0, 1} and {2, 3}
+          const int chunk = SPLIT == 2 ? 2 * (i >> 1) + half : 2 * half + (i >> 1);
+          const int kk = 2 * chunk + (i & 1);
           const uint32_t p_col = tmem_base + (uint32_t)(t * 128 + 32 * (kk >> 1) + 8 * (kk & 1));
           const uint64_t vd = umma_desc_mn_sw128(va + (uint32_t)kk * 2048u);
-          ptx::umma_ts_f16(o_tmem, p_col + 16u, vd, kIdescPV, (first && kk == 0) ? 0u : 1u);  // residual first
+          ptx::umma_ts_f16(o_tmem, p_col + 16u, vd, kIdescPV, (first && half == 0 && i == 0) ? 0u : 1u);  // residual first
           ptx::umma_ts_f16(o_tmem, p_col, vd, kIdescPV, 1u);
         }
       };
@@ -265,14 +273,22 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const uint32_t ph = (uint32_t)(g / A_KV_STAGES) & 1u;
         const bool more = g + 1 < total_steps, first = j == 0, last = j == num_kv - 1;
         if (!ptx::mbar_wait(v_full(s), ph, abort_flag)) { atomicExch(status, 0x2300); break; }
-        if (!ptx::mbar_wait(p_full(0), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
+        if (!ptx::mbar_wait(p_half(0, 0), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
         ptx::tc_fence_after();
-        issue_pv(0, s, first);
+        if (early_pv) issue_pv(0, s, first, 0);
+        if (!ptx::mbar_wait(p_half(0, 1), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
+        ptx::tc_fence_after();
+        if (!early_pv) issue_pv(0, s, first, 0);
+        issue_pv(0, s, first, 1);
         if (last) ptx::umma_commit<1>(o_done(0));
         if (more && !next_scores(0, g)) break;
-        if (!ptx::mbar_wait(p_full(1), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
+        if (!ptx::mbar_wait(p_half(1, 0), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
         ptx::tc_fence_after();
-        issue_pv(1, s, first);
+        if (early_pv) issue_pv(1, s, first, 0);
+        if (!ptx::mbar_wait(p_half(1, 1), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
+        ptx::tc_fence_after();
+        if (!early_pv) issue_pv(1, s, first, 0);
+        issue_pv(1, s, first, 1);
         ptx::umma_commit<1>(v_empty(s));
         if (last) ptx::umma_commit<1>(o_done(1));
         if (more && !next_scores(1, g)) break;
@@ -333,7 +349,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const bool grow = (j == 0) || (mx2 > m_used + A_RESCALE_THRESHOLD);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx2 : m_used;
-        const float alpha = (j == 0) ? 0.f : ex2_approx(m_used - m_new);   // 1 when this row does not grow
+        const float alpha = (j == 0) ? 0.f : ex2_approx_ftz(m_used - m_new);   // 1 when this row does not grow
         if (j > 0) {
           // All earlier products into O_t are complete: s_full(t) of this step was committed after them.
 #pragma unroll 1
@@ -359,8 +375,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), scale_log2e, shift));
-          const float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2e, shift));
+          const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(r[2 * i]), scale_log2e, shift));
+          const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2e, shift));
           mass += p0 + p1;
           const __half2 hi = __floats2half2_rn(p0, p1);
           const float2 back = __half22float2(hi);
@@ -369,16 +385,18 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           w[16 + i] = *reinterpret_cast<const uint32_t*>(&lo);
         }
         ptx::tmem_st_32x32(s_tmem + (uint32_t)(c * 32), w);
+        if (((c - c0 + 1) % (kChunks / 2)) == 0) {   // this warp's share of one half is in tensor memory
+          ptx::tmem_st_wait();
+          ptx::tc_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(p_half(t, (c - c0) / (kChunks / 2)));
+        }
       }
-      ptx::tmem_st_wait();
-      ptx::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(p_full(t));
       if (j != num_kv - 1) continue;
 
       // ---- the item's last step: normalise and store its output while the tensor core already works on the other
       // tile and on the next item's scores (the next item's first product into O_t waits for this warp's next arrival
-      // on p_full, which comes after the reads below) ----
+      // on p_half, which comes after the reads below) ----
       const int it = g / num_kv;
       bool done = ptx::mbar_wait(o_done(t), (uint32_t)it & 1u, abort_flag);
       if constexpr (SPLIT == 2) {
@@ -497,10 +515,14 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
     const char* text = getenv("DTN_GQA_PERSISTENT");
     return !(text && text[0] == '0');
   }();
+  static const int early_pv = [] {
+    const char* text = getenv("DTN_GQA_EARLY_PV");   // 0: issue a tile's value products only when all its probabilities are ready
+    return (text && text[0] == '0') ? 0 : 1;
+  }();
   const int64_t ctas = persistent && items > sm_count() ? sm_count() : items;
   const float scale_log2e = scale * 1.4426950408889634f;
   gqa_tc_kernel<SPLIT><<<(unsigned)ctas, attn_threads(SPLIT), A_SMEM_BYTES, s>>>(mq, mk, mv, out, (int)Hq, (int)Hkv, (int)S, scale_log2e,
-                                                                                 (int)gb, (int)items, status);
+                                                                                 (int)gb, (int)items, early_pv, status);
   DTN_LAUNCH_CHECK("gqa_tc_kernel");
   return DTN_OK;
 }

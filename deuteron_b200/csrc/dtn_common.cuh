@@ -109,6 +109,13 @@ __device__ __forceinline__ float ex2_approx(float x) {
   asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// Flush-to-zero form: one MUFU instruction, no range fix-up around it. Results below 2^-126 become 0; used where such
+// values cannot matter (attention probabilities, which are summed with values near 1).
+__device__ __forceinline__ float ex2_approx_ftz(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float exp_ref(float x) { return ex2_approx(x * 1.4426950408889634f); }
 __device__ __forceinline__ float rcp_approx(float x) {
   float y;

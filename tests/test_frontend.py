@@ -96,6 +96,12 @@ def test_generated_schedules_classify(golden):
     assert rms.kind == 'row_fused' and rms.params['reduce'] == 'sumsq' and rms.params['n_scalar'] == 3
     assert [i['kind'] for i in rms.params['inputs']] == ['columns', 'scalar', 'scalar']
     assert rms.buffers == {'x': ('x', 0), 'out': ('mul_1', 0), 'in0': ('w', 0), 'in1': ('mean_count', 0), 'in2': ('add_c1', 0)}
+    # a rasterised tile order (compiler/codegen/lower.py:472-487) changes which CTA computes which tile, not the product
+    graph, meta = schedules.matmul_example(256, 256, 256)
+    body = graph['nodes']['result']['op_fields']['body'][0]
+    assert "raster_axes=None, raster_group=None" in body
+    set_body(graph, body.replace("raster_axes=None, raster_group=None", "raster_axes=('tile_m', 'tile_n'), raster_group=4"))
+    assert compile_kernel(graph, meta).plan.params == {'mode': 'bf16x3', 'm': 256, 'n': 256, 'k': 256}
     narrow = compile_kernel(*schedules.f16_storage_example('narrow', 512, 4, offset=1)).plan
     assert narrow.buffers['x'] == ('x', 1)  # the unaligned origin travels as an element offset
     # the generated 128^3 schedule has the statement census of the reference's committed IR

@@ -140,3 +140,34 @@ def test_driver_runs_the_generated_problem_set(tmp_path, cuda):
     # a second run into the same directory is refused
     with pytest.raises(SystemExit):
         benchmark.main(['--problems-dir', str(problems), '--artifacts', str(artifacts)])
+
+
+@pytest.mark.gpu
+def test_driver_chains_kernels_through_intermediate_buffers(tmp_path, cuda):
+    """Two kernels in one problem: y = 2x + 1, then mean(y); the second reads the first's output as an `intermediate`
+    buffer (benchmark.py:57-62, 466-470)."""
+    first_graph, first_meta = schedules.pointwise_example('affine', 4096)
+    second_graph, second_meta = schedules.mean_example(4096)
+    second_text = json.dumps(second_graph).replace("input='x'", "input='add'").replace('"x"', '"add"')
+    second_launch = json.loads(json.dumps(second_meta['kernels'][0]).replace('"x"', '"add"'))
+    for arg in second_launch['args']:
+        if arg['name'] == 'add':
+            arg.pop('seed')
+            arg['intermediate'] = True
+    first_launch = dict(first_meta['kernels'][0], final=False)
+    meta = {'id': 'chained', 'rtol': 1e-5, 'atol': 1e-6, 'graph_inputs': ['x'], 'graph_outputs': ['mean'],
+            'kernels': [first_launch, second_launch]}
+    problem = tmp_path / 'problems' / 'c00_chained'
+    problem.mkdir(parents=True)
+    (problem / 'meta.json').write_text(json.dumps(meta))
+    (problem / (first_launch['entry'] + '.ir.json')).write_text(json.dumps(first_graph))
+    (problem / (second_launch['entry'] + '.ir.json')).write_text(second_text)
+    x = np.random.default_rng(0).standard_normal(4096).astype(np.float32)
+    y = x * np.float32(2) + np.float32(1)
+    np.savez(problem / 'expected.npz', mean=np.array([y.astype(np.float64).mean()]))
+    artifacts = tmp_path / 'artifacts'
+    assert benchmark.main(['--problems-dir', str(problem.parent), '--artifacts', str(artifacts), '--warmup', '1', '--iters', '5', '--samples', '2']) == 0
+    report = json.loads((artifacts / 'c00_chained' / 'result.json').read_text())
+    assert report['passed'] and [k['entry'] for k in report['kernels']] == ['k_add_pointwise', 'k_mean']
+    with np.load(artifacts / 'c00_chained' / 'actual.npz') as actual:
+        np.testing.assert_array_equal(actual['add'], y)
