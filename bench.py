@@ -143,6 +143,56 @@ def cpu_gemm_sample(seconds_target: float = 12.0) -> dict:
             'rows': rows, 'seconds': elapsed}
 
 
+def reference_kernel_baseline(torch, ops) -> dict | None:
+    """The second baseline beside the CPU one: the reference's own emitted kernel (its committed tf32x3 PTX for the
+    128^3 example, assembled for sm_100a by oracle/build_ref.py) timed on this GPU next to this build's kernel for the
+    same problem, both as the reference times kernels (CUDA graph of 200 launches, median of 7). None when the cubin
+    was not built."""
+    from oracle import ref_kernel, reference_math as oracle
+    if not ref_kernel.available():
+        return None
+    import statistics
+    device = torch.device('cuda', 0)
+    left = torch.from_numpy(oracle.seeded_normal(7, (128, 128))).to(device)
+    right = torch.from_numpy(oracle.seeded_normal(11, (128, 128))).to(device)
+    theirs, mine = torch.empty((128, 128), device=device), torch.empty((128, 128), device=device)
+    reference = ref_kernel.ReferenceMatmul()
+    stream = torch.cuda.Stream(device)
+
+    def graph_latency(call) -> float:
+        with torch.cuda.stream(stream):
+            for _ in range(20):
+                call()
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for _ in range(200):
+                    call()
+            graph.replay()
+            stream.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            samples = []
+            for _ in range(7):
+                begin.record(stream)
+                graph.replay()
+                end.record(stream)
+                end.synchronize()
+                samples.append(begin.elapsed_time(end) * 1000 / 200)
+        return statistics.median(samples)
+
+    try:
+        with torch.cuda.stream(stream):
+            reference_us = graph_latency(lambda: reference.launch(right.data_ptr(), left.data_ptr(), theirs.data_ptr(), stream.cuda_stream))
+            ours_us = graph_latency(lambda: ops.gemm(left, right, 'tf32x3', out=mine))
+        stream.synchronize()
+        identical = bool(torch.equal(theirs, mine))
+    finally:
+        reference.close()
+    return {'workload': 'gemm_tf32x3_128x128x128 (examples/tensor_matmul)', 'reference_kernel': 'matmul_tiled_128, the reference\'s committed PTX '
+            '(docs/video/demo/capture/kernel.ptx) assembled for sm_100a', 'reference_median_us': reference_us, 'ours_median_us': ours_us,
+            'outputs_bit_identical': identical, 'timing': 'CUDA graph of 200 launches, median of 7'}
+
+
 def run_reference(args) -> None:
     """The reference arm: its CPU implementation of the path, on the host cores, rank 0 only."""
     rank = int(os.environ.get('RANK', '0'))
@@ -399,6 +449,9 @@ def run_ours(args) -> None:
         }
         if world == 1 and not args.no_cpu_baseline:
             line['cpu_baseline'] = cpu_gemm_sample()
+            reference_gpu = reference_kernel_baseline(torch, ops)
+            if reference_gpu is not None:
+                line['reference_kernel_baseline'] = reference_gpu
         if world == 1 and not args.no_extras:
             del a, b, c
             torch.cuda.empty_cache()
