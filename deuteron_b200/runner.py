@@ -78,6 +78,11 @@ def compare_outputs(problem: Any, metadata: Any, produced: Any) -> dict[str, flo
     return errors
 
 
+def _overwrites(plan: Any, name: str) -> bool:
+    """True when the native kernel of `plan` writes every element of buffer `name` without reading it first."""
+    return plan.kind == 'gemm' and plan.buffers['out'] == (name, 0)
+
+
 class LocalRunner:
     """One CUDA device, one stream; must be used and closed by the thread that created it."""
 
@@ -347,7 +352,9 @@ class LocalRunner:
                     ws_ptr = (scratch.data_ptr() + 1023) // 1024 * 1024
                     workspace = (ws_ptr, scratch.numel() - (ws_ptr - scratch.data_ptr()))
                     device_buffers['__workspace__'] = (scratch, scratch)
-            resets = [device_buffers[name][1] for name in launch.get('zero_outputs', [])]
+            # zero_outputs exist for kernels that accumulate into their output with atomics (benchmark.py:240-243); a
+            # native kernel that overwrites the whole buffer gives the same result without the reset
+            resets = [device_buffers[name][1] for name in launch.get('zero_outputs', []) if not _overwrites(plan, name)]
 
             def enqueue() -> None:
                 for view in resets:
