@@ -67,36 +67,40 @@ struct Tf32Kind {
   __device__ static __forceinline__ elem zero() { return 0.f; }
 };
 
-// A[rows, cols] (ld = ldx) -> hi/lo [rows, colsP]; columns >= cols are written as zero.
+// A[rows, cols] (ld = ldx) -> hi/lo [rows, colsP]; columns >= cols are written as zero. One thread converts
+// kSplitRowElems<KIND> consecutive elements: 16 bytes per store for either kind.
+template <class KIND>
+constexpr int kSplitRowElems = 16 / KIND::kElemBytes;   // 8 (bf16) or 4 (tf32)
+
 template <class KIND>
 __device__ __forceinline__ void split_rows_body(const float* __restrict__ X, int64_t ldx, int cols, int colsP,
                                                 typename KIND::elem* __restrict__ hi,
                                                 typename KIND::elem* __restrict__ lo, int vec_ok, int row, int block_x) {
   using E = typename KIND::elem;
-  const int c4 = (block_x * 256 + (int)threadIdx.x) * 4;
-  if (c4 >= colsP) return;
+  constexpr int EPT = kSplitRowElems<KIND>;
+  const int c0 = (block_x * 256 + (int)threadIdx.x) * EPT;
+  if (c0 >= colsP) return;
   const float* xr = X + (int64_t)row * ldx;
-  float v[4] = {0.f, 0.f, 0.f, 0.f};
-  if (vec_ok && c4 + 3 < cols) {
-    const float4 t = ld_stream_f4(reinterpret_cast<const float4*>(xr + c4));
-    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+  float v[EPT];
+#pragma unroll
+  for (int j = 0; j < EPT; ++j) v[j] = 0.f;
+  if (vec_ok && c0 + EPT - 1 < cols) {
+#pragma unroll
+    for (int q = 0; q < EPT / 4; ++q) {
+      const float4 t = ld_stream_f4(reinterpret_cast<const float4*>(xr + c0) + q);
+      v[4 * q] = t.x; v[4 * q + 1] = t.y; v[4 * q + 2] = t.z; v[4 * q + 3] = t.w;
+    }
   } else {
 #pragma unroll
-    for (int j = 0; j < 4; ++j)
-      if (c4 + j < cols) v[j] = xr[c4 + j];
+    for (int j = 0; j < EPT; ++j)
+      if (c0 + j < cols) v[j] = xr[c0 + j];
   }
-  E h[4], l[4];
+  __align__(16) E h[EPT];
+  __align__(16) E l[EPT];
 #pragma unroll
-  for (int j = 0; j < 4; ++j) KIND::split(v[j], h[j], l[j]);
-  E* hp = hi + (int64_t)row * colsP + c4;
-  E* lp = lo + (int64_t)row * colsP + c4;
-  if constexpr (KIND::kElemBytes == 2) {
-    *reinterpret_cast<uint2*>(hp) = *reinterpret_cast<uint2*>(h);
-    *reinterpret_cast<uint2*>(lp) = *reinterpret_cast<uint2*>(l);
-  } else {
-    *reinterpret_cast<uint4*>(hp) = *reinterpret_cast<uint4*>(h);
-    *reinterpret_cast<uint4*>(lp) = *reinterpret_cast<uint4*>(l);
-  }
+  for (int j = 0; j < EPT; ++j) KIND::split(v[j], h[j], l[j]);
+  *reinterpret_cast<uint4*>(hi + (int64_t)row * colsP + c0) = *reinterpret_cast<uint4*>(h);
+  *reinterpret_cast<uint4*>(lo + (int64_t)row * colsP + c0) = *reinterpret_cast<uint4*>(l);
 }
 
 template <class KIND>
@@ -149,10 +153,74 @@ __device__ __forceinline__ void split_transpose_body(const float* __restrict__ B
   }
 }
 
+// bf16 form with 128-bit global accesses: a thread loads a 4 (k) x 4 (n) block of B with four 16-byte loads, packs
+// four consecutive k of each column into 8 bytes and stores them to a [64 n][64 k] shared tile whose 8-byte chunks are
+// XOR-swizzled with the column group (conflict-free on both sides); the tile leaves as 16-byte pieces of whole
+// 128-byte k-rows. Needs B 16-byte aligned with ldb % 4 == 0; edges fall back to guarded scalar loads.
+__device__ __forceinline__ void split_transpose_bf16_vec(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
+                                                         __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
+                                                         int block_x, int block_y) {
+  __shared__ __align__(16) __nv_bfloat16 t_hi[64 * 64];
+  __shared__ __align__(16) __nv_bfloat16 t_lo[64 * 64];
+  const int k0 = block_x * 64, n0 = block_y * 64;
+  const int tid = threadIdx.x;
+  {
+    const int n4 = tid & 15, kc = tid >> 4;
+    const int n = n0 + 4 * n4;
+    float v[4][4];
+#pragma unroll
+    for (int r = 0; r < 4; ++r) {
+      const int k = k0 + 4 * kc + r;
+      if (k < K && n + 3 < N) {
+        const float4 t = ld_stream_f4(reinterpret_cast<const float4*>(B + (int64_t)k * ldb + n));
+        v[r][0] = t.x; v[r][1] = t.y; v[r][2] = t.z; v[r][3] = t.w;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[r][j] = (k < K && n + j < N) ? B[(int64_t)k * ldb + n + j] : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      __align__(8) __nv_bfloat16 h[4];
+      __align__(8) __nv_bfloat16 l[4];
+#pragma unroll
+      for (int r = 0; r < 4; ++r) Bf16Kind::split(v[r][j], h[r], l[r]);
+      const int at = (4 * n4 + j) * 64 + 4 * (kc ^ n4);
+      *reinterpret_cast<uint2*>(t_hi + at) = *reinterpret_cast<uint2*>(h);
+      *reinterpret_cast<uint2*>(t_lo + at) = *reinterpret_cast<uint2*>(l);
+    }
+  }
+  __syncthreads();
+#pragma unroll
+  for (int q = tid; q < 512; q += 256) {
+    const int nn = q >> 3, pr = q & 7;          // row of the tile, pair of 4-element chunks (2 pr, 2 pr + 1)
+    const int group = (nn >> 2) & 15;
+    const int at = nn * 64 + 8 * (pr ^ (group >> 1));
+    uint4 a = *reinterpret_cast<const uint4*>(t_hi + at);
+    uint4 b = *reinterpret_cast<const uint4*>(t_lo + at);
+    if (group & 1) {                            // the two chunks of the pair sit in swapped order
+      a = make_uint4(a.z, a.w, a.x, a.y);
+      b = make_uint4(b.z, b.w, b.x, b.y);
+    }
+    const int n = n0 + nn;
+    if (n < N) {
+      const int64_t o = (int64_t)n * Kp + k0 + 8 * pr;
+      *reinterpret_cast<uint4*>(hi + o) = a;
+      *reinterpret_cast<uint4*>(lo + o) = b;
+    }
+  }
+}
+
 template <class KIND>
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
-                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo) {
+                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo, int b_vec_ok) {
+  if constexpr (KIND::kElemBytes == 2) {
+    if (b_vec_ok) {
+      split_transpose_bf16_vec(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
+      return;
+    }
+  }
   split_transpose_body<KIND>(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
 }
 
@@ -163,13 +231,19 @@ __global__ void __launch_bounds__(256)
 split_both_kernel(const float* __restrict__ A, int64_t lda, int K, int Kp, typename KIND::elem* __restrict__ a_hi,
                   typename KIND::elem* __restrict__ a_lo, int a_vec_ok, int a_blocks_x, int a_blocks,
                   const float* __restrict__ B, int64_t ldb, int N, typename KIND::elem* __restrict__ b_hi,
-                  typename KIND::elem* __restrict__ b_lo, int b_blocks_x) {
+                  typename KIND::elem* __restrict__ b_lo, int b_blocks_x, int b_vec_ok) {
   ptx::launch_dependents();   // the product kernel may begin its set-up; it waits for this grid before it loads
   const int id = blockIdx.x;
   if (id < a_blocks) {
     split_rows_body<KIND>(A, lda, K, Kp, a_hi, a_lo, a_vec_ok, id / a_blocks_x, id % a_blocks_x);
   } else {
     const int b = id - a_blocks;
+    if constexpr (KIND::kElemBytes == 2) {
+      if (b_vec_ok) {
+        split_transpose_bf16_vec(B, ldb, K, N, Kp, b_hi, b_lo, b % b_blocks_x, b / b_blocks_x);
+        return;
+      }
+    }
     split_transpose_body<KIND>(B, ldb, K, N, Kp, b_hi, b_lo, b % b_blocks_x, b / b_blocks_x);
   }
 }
@@ -548,20 +622,21 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
   E* b_hi = reinterpret_cast<E*>(ws + 2 * L.a_plane);
   E* b_lo = reinterpret_cast<E*>(ws + 2 * L.a_plane + L.b_plane);
   {
-    const int64_t ax = (L.Kp / 4 + 255) / 256, a_blocks = ax * M;
+    const int64_t ax = (L.Kp / kSplitRowElems<KIND> + 255) / 256, a_blocks = ax * M;
+    const int b_vec_ok = aligned_to(B, 16) && (ldb % 4 == 0);
     const int64_t bx = L.Kp / KIND::kBlockK, b_blocks = bx * ((N + 63) / 64);
     if (do_a && do_b && a_blocks + b_blocks < (int64_t)2000000000) {
       const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
       split_both_kernel<KIND><<<(unsigned)(a_blocks + b_blocks), 256, 0, s>>>(A, lda, (int)K, (int)L.Kp, a_hi, a_lo, vec_ok,
                                                                              (int)ax, (int)a_blocks, B, ldb, (int)N, b_hi,
-                                                                             b_lo, (int)bx);
+                                                                             b_lo, (int)bx, b_vec_ok);
       DTN_LAUNCH_CHECK("split_both_kernel");
       return DTN_OK;
     }
   }
   if (do_a) {
     const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
-    dim3 grid((unsigned)((L.Kp / 4 + 255) / 256), (unsigned)M);
+    dim3 grid((unsigned)((L.Kp / kSplitRowElems<KIND> + 255) / 256), (unsigned)M);
     DTN_REQUIRE(M <= 65535 * 1024LL, DTN_ERR_UNSUPPORTED, "gemm: M too large");
     // grid.y is limited to 65535 rows per launch
     for (int64_t r0 = 0; r0 < M; r0 += 65535) {
@@ -579,7 +654,8 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
       dim3 grid((unsigned)(L.Kp / KIND::kBlockK), (unsigned)cnt);
       const int64_t n_off = y0 * 64;
       split_transpose_kernel<KIND><<<grid, 256, 0, s>>>(B + n_off, ldb, (int)K, (int)(N - n_off), (int)L.Kp,
-                                                        b_hi + n_off * L.Kp, b_lo + n_off * L.Kp);
+                                                        b_hi + n_off * L.Kp, b_lo + n_off * L.Kp,
+                                                        aligned_to(B + n_off, 16) && (ldb % 4 == 0));
       DTN_LAUNCH_CHECK("split_transpose_kernel");
     }
   }
