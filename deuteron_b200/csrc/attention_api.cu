@@ -8,6 +8,9 @@ int gqa_f32_launch(const void* q, const void* k, const void* v, float* out, int6
 int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
                   int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s);
 bool gqa_tc_supported(int64_t S, int64_t D, int storage);
+int gqa_tc_pair_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
+                       int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s);
+bool gqa_tc_pair_supported(int64_t S, int64_t D, int storage);
 
 static int g_gqa_variant = 0;
 
@@ -16,7 +19,7 @@ static int g_gqa_variant = 0;
 extern "C" {
 
 int dtn_gqa_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 3, DTN_ERR_INVALID, "gqa: variant must be 0..3");
+  DTN_REQUIRE(variant >= 0 && variant <= 5, DTN_ERR_INVALID, "gqa: variant must be 0..5");
   dtn::g_gqa_variant = variant;
   return DTN_OK;
 }
@@ -44,6 +47,11 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   // and 871 vs 864 at 16384 (each measured first in its process; whichever variant runs second on a warm GPU loses
   // ~10 % to the power cap, so back-to-back comparisons must alternate the order).
   if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 3 : 1;
+  if (variant >= 4) {   // CTA pairs (4: one softmax warpgroup per tile, 5: two)
+    DTN_REQUIRE(gqa_tc_pair_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
+                "gqa: the CTA-pair kernel needs f16 storage, head_dim 128 and S a multiple of 512");
+    return gqa_tc_pair_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, variant == 5 ? 2 : 1, s);
+  }
   if (variant >= 2) {
     DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
                 "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");

@@ -26,95 +26,9 @@
 
 #include <mutex>
 
-#include "dtn_common.cuh"
-#include "sm100_ptx.cuh"
+#include "attention_tc.cuh"
 
 namespace dtn {
-
-constexpr int attn_threads(int split) { return (8 * split + 2) * 32; }   // softmax warps + TMA warp + MMA warp
-constexpr int A_BM = 128;          // query rows per tile (two tiles per CTA)
-constexpr int A_BN = 128;          // keys per step
-constexpr int A_D = 128;           // head dimension
-constexpr int A_HALF_BYTES = 128 * 128;           // one [128 rows][64 f16] swizzled block
-constexpr int A_TILE_BYTES = 2 * A_HALF_BYTES;    // one [128][128] f16 tile
-constexpr int A_KV_STAGES = 2;
-constexpr int A_SMEM_TILES = 2 /*Q*/ + 2 * A_KV_STAGES /*K,V*/;
-constexpr int A_XCHG_BYTES = 2 * 2 * 128 * 8;   // [tile][column share][row] (value, sequence) slots
-constexpr int A_STAGE_BYTES = 16 * 1024;        // 1 KiB of output staging per softmax warp (at most 16 of them)
-constexpr int A_SMEM_BYTES = A_SMEM_TILES * A_TILE_BYTES + 256 + A_XCHG_BYTES + A_STAGE_BYTES + 1024;
-constexpr float A_RESCALE_THRESHOLD = 8.0f;   // in log2 units
-constexpr float A_BIAS = 4.0f;                // probabilities are kept scaled by 2^4 (f16 residuals stay normal)
-
-// Shared-memory descriptor of an MN-major operand (V tile: rows = keys, 128-byte rows of 64
-// head-dimension elements, 128-byte swizzle). The 64-element blocks along the head dimension are
-// A_HALF_BYTES apart (leading offset); groups of 8 keys are 1024 bytes apart (stride offset).
-__device__ __forceinline__ uint64_t umma_desc_mn_sw128(uint32_t smem_addr) {
-  uint64_t d = 0;
-  d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-  d |= (uint64_t)(A_HALF_BYTES >> 4) << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
-  d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
-  return d;
-}
-
-// max(a, b, c) in one instruction (sm_100 has a three-input FP32 max).
-__device__ __forceinline__ float max3(float a, float b, float c) {
-  float d;
-  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-  return d;
-}
-
-// idesc: f16 operands, FP32 accumulate, M = 128, N = 128; b_mn = 1 when B is MN-major.
-__host__ __device__ constexpr uint32_t attn_idesc(int b_mn) {
-  return ptx::umma_idesc(0, 128, 128) | ((uint32_t)b_mn << 16);
-}
-
-// Hands `value` to the thread that owns the other column share of the same row and returns that
-// thread's value in `other`. A slot holds (value, sequence number); the 8-byte store makes both
-// visible together. The wait is bounded like every other wait in this file.
-__device__ __forceinline__ bool exchange_with_peer(volatile float2* mine, volatile float2* theirs, float value, int seq,
-                                                   volatile int* abort_flag, float& other) {
-  float2 packed = make_float2(value, __int_as_float(seq));
-  asm volatile("st.volatile.shared.v2.f32 [%0], {%1, %2};" ::"r"(smem_u32((const void*)mine)), "f"(packed.x), "f"(packed.y)
-               : "memory");
-  const uint32_t addr = smem_u32((const void*)theirs);
-  const long long start = clock64();
-  while (true) {
-    float a, b;
-    asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr) : "memory");
-    if (__float_as_int(b) == seq) {
-      other = a;
-      return true;
-    }
-    if (*abort_flag) return false;
-    if (clock64() - start > ptx::kWaitBudgetCycles) {
-      *abort_flag = 1;
-      return false;
-    }
-  }
-}
-
-// Work items: one item = 256 query rows of one query head. A CTA takes items blockIdx.x, blockIdx.x + gridDim.x, ...
-// and runs them as ONE stream of key steps: barrier phases, the K/V ring and the exchange sequence numbers keep
-// counting across items, so the next item's first products are issued while the previous item's output is still being
-// written (the per-item prologue, pipeline fill and output no longer leave the tensor core idle). With as many CTAs
-// as items the kernel degenerates to one item per CTA.
-struct AttnItem {
-  int q_row0;     // first query row in the [B*Hq*S, D] view
-  int kv_row0;    // first key row in the [B*Hkv*S, D] view
-};
-__device__ __forceinline__ AttnItem attn_item(int item, int qblocks, int Hq, int Hkv, int S, int group_begin) {
-  const int heads_per_group = Hq / Hkv;
-  const int head_local = item / qblocks, qb = item % qblocks;
-  const int group = group_begin + head_local / heads_per_group;
-  const int b = group / Hkv, hkv = group % Hkv;
-  const int hq = hkv * heads_per_group + head_local % heads_per_group;
-  AttnItem it;
-  it.q_row0 = (b * Hq + hq) * S + qb * (2 * A_BM);
-  it.kv_row0 = (b * Hkv + hkv) * S;
-  return it;
-}
 
 template <int SPLIT /*warpgroups per 128-row tile: 1 or 2*/>
 __global__ void __launch_bounds__(attn_threads(SPLIT), 1)
@@ -226,22 +140,37 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       constexpr uint32_t kIdescQK = attn_idesc(0);
       constexpr uint32_t kIdescPV = attn_idesc(1);
       bool ok = true;
+      // Descriptors are built once: a k-step moves the start address by 32 bytes inside a swizzled row (+2 in the
+      // descriptor's address field) or by 16 key rows of a V tile (+128), which the issue loops add as constants.
+      // Keeping the issuing thread's instruction count low matters: it shares its scheduler with four softmax warps.
+      static_assert(A_KV_STAGES == 2, "the issue loops select between two K/V slots");
+      uint64_t q_desc[2][2], k_desc[A_KV_STAGES][2], v_desc[A_KV_STAGES];
+#pragma unroll
+      for (int t = 0; t < 2; ++t)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) q_desc[t][h] = ptx::umma_desc_sw128(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES);
+#pragma unroll
+      for (int st = 0; st < A_KV_STAGES; ++st) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) k_desc[st][h] = ptx::umma_desc_sw128(k_addr + st * A_TILE_BYTES + h * A_HALF_BYTES);
+        v_desc[st] = umma_desc_mn_sw128(v_addr + st * A_TILE_BYTES);
+      }
       // S_t = Q_t K^T : 8 k-steps of 16 along the head dimension (two 64-element swizzled halves)
       auto issue_qk = [&](int t, int s) {
-        const uint32_t qa = q_addr + t * A_TILE_BYTES, ka = k_addr + s * A_TILE_BYTES;
+        const uint64_t qa0 = q_desc[t][0], qa1 = q_desc[t][1];
+        const uint64_t ka0 = s ? k_desc[1][0] : k_desc[0][0], ka1 = s ? k_desc[1][1] : k_desc[0][1];
 #pragma unroll
         for (int kk = 0; kk < 8; ++kk) {
-          const uint32_t off = (uint32_t)(kk >> 2) * A_HALF_BYTES + (uint32_t)(kk & 3) * 32u;
-          ptx::umma_ss<0, 1>(tmem_base + (uint32_t)(t * 128), ptx::umma_desc_sw128(qa + off),
-                             ptx::umma_desc_sw128(ka + off), kIdescQK, kk ? 1u : 0u);
+          const uint64_t step = (uint64_t)(2 * (kk & 3));
+          ptx::umma_ss<0, 1>(tmem_base + (uint32_t)(t * 128), (kk >> 2 ? qa1 : qa0) + step, (kk >> 2 ? ka1 : ka0) + step, kIdescQK,
+                             kk ? 1u : 0u);
         }
       };
       // O_t += P_t V : 8 k-steps of 16 keys; per step the high and the residual plane of P. The probabilities arrive
       // in two halves (the 32-key chunks every softmax warpgroup finishes first, then the rest), so the products of
-      // the first half run while the second is still being computed: half h covers k-steps kk with
-      // ((kk >> 1) / chunks-per-warpgroup-half) matching the order the warpgroups write their chunks.
+      // the first half can run while the second is still being computed.
       auto issue_pv = [&](int t, int s, bool first, int half) {
-        const uint32_t va = v_addr + s * A_TILE_BYTES;
+        const uint64_t vd0 = s ? v_desc[1] : v_desc[0];
         const uint32_t o_tmem = tmem_base + (uint32_t)(256 + t * 128);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -250,7 +179,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int chunk = SPLIT == 2 ? 2 * (i >> 1) + half : 2 * half + (i >> 1);
           const int kk = 2 * chunk + (i & 1);
           const uint32_t p_col = tmem_base + (uint32_t)(t * 128 + 32 * (kk >> 1) + 8 * (kk & 1));
-          const uint64_t vd = umma_desc_mn_sw128(va + (uint32_t)kk * 2048u);
+          const uint64_t vd = vd0 + (uint64_t)(kk * 128);
           ptx::umma_ts_f16(o_tmem, p_col + 16u, vd, kIdescPV, (first && half == 0 && i == 0) ? 0u : 1u);  // residual first
           ptx::umma_ts_f16(o_tmem, p_col, vd, kIdescPV, 1u);
         }
@@ -297,149 +226,32 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     __syncwarp();
   } else {
     // ------------------------------------ softmax + output -----------------------------------
-    // SPLIT warpgroups share one tile: each owns 128 / SPLIT score columns (and the same share of
-    // the output columns) of all 128 rows. Partner threads of a row agree on the row maximum
-    // through a shared-memory slot (bounded spin, no block-wide barrier).
-    constexpr int kChunks = 4 / SPLIT;             // 32-column chunks per thread
-    const int t = warp / (4 * SPLIT);              // tile
-    const int part = (warp >> 2) % SPLIT;          // column share of this warpgroup
-    const int quarter = warp & 3;
-    const int row_in_tile = quarter * 32 + lane;
-    const int c0 = part * kChunks;
-    const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
-    const uint32_t s_tmem = tmem_base + lane_field + (uint32_t)(t * 128);
-    const uint32_t o_tmem = tmem_base + lane_field + (uint32_t)(256 + t * 128);
-    volatile float2* my_slot = xchg + ((t * 2 + part) * 128 + row_in_tile);
-    volatile float2* peer_slot = xchg + ((t * 2 + (part ^ 1)) * 128 + row_in_tile);
-    float* stage = stage_base + warp * 256;   // [32 rows][8 floats], 16-byte pieces swapped on every other group of 4 rows
-    float m_used = -INFINITY;   // log2-domain maximum the current probabilities are scaled by
-    float mass = 0.f;
-    for (int g = 0; g < total_steps; ++g) {
-      const int j = g % num_kv;
-      if (j == 0) {   // a new item starts
-        m_used = -INFINITY;
-        mass = 0.f;
-      }
-      const bool ready = ptx::mbar_wait(s_full(t), (uint32_t)g & 1u, abort_flag);
-      if (!__all_sync(0xffffffffu, ready)) {
-        if (lane == 0) atomicExch(status, 0x3100 | t);
-        break;
-      }
-      ptx::tc_fence_after();
-      // pass 1: row maximum of the raw scores (three-input max: two scores per instruction)
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = c0; c < c0 + kChunks; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(s_tmem + (uint32_t)(c * 32), r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
-      }
-      if constexpr (SPLIT == 2) {
-        float other;
-        const bool got = exchange_with_peer(my_slot, peer_slot, mx, 2 * g + 1, abort_flag, other);
-        if (!__all_sync(0xffffffffu, got)) {
-          if (lane == 0) atomicExch(status, 0x3300 | t);
-          break;
-        }
-        mx = fmaxf(mx, other);
-      }
-      const float mx2 = mx * scale_log2e;
-      const bool grow = (j == 0) || (mx2 > m_used + A_RESCALE_THRESHOLD);
-      if (__any_sync(0xffffffffu, grow)) {
-        const float m_new = grow ? mx2 : m_used;
-        const float alpha = (j == 0) ? 0.f : ex2_approx_ftz(m_used - m_new);   // 1 when this row does not grow
-        if (j > 0) {
-          // All earlier products into O_t are complete: s_full(t) of this step was committed after them.
-#pragma unroll 1
-          for (int c = c0; c < c0 + kChunks; ++c) {
-            uint32_t r[32];
-            ptx::tmem_ld_32x32(o_tmem + (uint32_t)(c * 32), r);
-            ptx::tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            ptx::tmem_st_32x32(o_tmem + (uint32_t)(c * 32), r);
-          }
-          ptx::tmem_st_wait();
-        }
-        mass *= alpha;
-        m_used = m_new;
-      }
-      // pass 2: probabilities, row sum, f16 high/residual split written over the scores
-      const float shift = A_BIAS - m_used;
-#pragma unroll 1
-      for (int c = c0; c < c0 + kChunks; ++c) {
-        uint32_t r[32], w[32];
-        ptx::tmem_ld_32x32(s_tmem + (uint32_t)(c * 32), r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(r[2 * i]), scale_log2e, shift));
-          const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2e, shift));
-          mass += p0 + p1;
-          const __half2 hi = __floats2half2_rn(p0, p1);
-          const float2 back = __half22float2(hi);
-          const __half2 lo = __floats2half2_rn(p0 - back.x, p1 - back.y);
-          w[i] = *reinterpret_cast<const uint32_t*>(&hi);
-          w[16 + i] = *reinterpret_cast<const uint32_t*>(&lo);
-        }
-        ptx::tmem_st_32x32(s_tmem + (uint32_t)(c * 32), w);
-        if (((c - c0 + 1) % (kChunks / 2)) == 0) {   // this warp's share of one half is in tensor memory
-          ptx::tmem_st_wait();
-          ptx::tc_fence_before();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(p_half(t, (c - c0) / (kChunks / 2)));
-        }
-      }
-      if (j != num_kv - 1) continue;
-
-      // ---- the item's last step: normalise and store its output while the tensor core already works on the other
-      // tile and on the next item's scores (the next item's first product into O_t waits for this warp's next arrival
-      // on p_half, which comes after the reads below) ----
-      const int it = g / num_kv;
-      bool done = ptx::mbar_wait(o_done(t), (uint32_t)it & 1u, abort_flag);
-      if constexpr (SPLIT == 2) {
-        float other = 0.f;
-        done = done && exchange_with_peer(my_slot, peer_slot, mass, 2 * g + 2, abort_flag, other);
-        mass += other;
-      }
-      if (!__all_sync(0xffffffffu, done)) {
-        if (lane == 0) atomicExch(status, 0x3200 | t);
-        break;
-      }
-      ptx::tc_fence_after();
-      const float inv = 1.0f / mass;
-      const AttnItem item = attn_item((int)blockIdx.x + it * (int)gridDim.x, qblocks, Hq, Hkv, S, group_begin);
-      float* obase = out + ((int64_t)item.q_row0 + t * A_BM + quarter * 32) * A_D;
-      // Each thread owns one row in tensor memory, but a warp-wide store should cover whole 32-byte sectors of
-      // several rows: 8 columns of the warp's 32 rows go through a 1 KiB staging block (16-byte pieces swapped on
-      // every other group of four rows, so neither side has bank conflicts) and come back 16 rows per instruction.
-      const int wr_swap = (lane >> 2) & 1;
-      const int rd_row = lane >> 1, rd_piece = lane & 1;
-#pragma unroll 1
-      for (int c = c0; c < c0 + kChunks; ++c) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(o_tmem + (uint32_t)(c * 32), r);
-        ptx::tmem_ld_wait();
-#pragma unroll
-        for (int sub = 0; sub < 4; ++sub) {
-#pragma unroll
-          for (int i = 0; i < 2; ++i)
-            *reinterpret_cast<float4*>(stage + lane * 8 + 4 * (i ^ wr_swap)) =
-                make_float4(__uint_as_float(r[8 * sub + 4 * i]) * inv, __uint_as_float(r[8 * sub + 4 * i + 1]) * inv,
-                            __uint_as_float(r[8 * sub + 4 * i + 2]) * inv, __uint_as_float(r[8 * sub + 4 * i + 3]) * inv);
-          __syncwarp();
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            const int rloc = rd_row + 16 * h;
-            const float4 val = *reinterpret_cast<const float4*>(stage + rloc * 8 + 4 * (rd_piece ^ ((rloc >> 2) & 1)));
-            *reinterpret_cast<float4*>(obase + (int64_t)rloc * A_D + c * 32 + sub * 8 + 4 * rd_piece) = val;
-          }
-          __syncwarp();
-        }
-      }
-    }
+    const int t = warp / (4 * SPLIT);   // tile of this warp
+    SoftmaxRole role;
+    role.tmem_base = tmem_base;
+    role.s_full = s_full(t);
+    role.p_half0 = p_half(t, 0);
+    role.p_half1 = p_half(t, 1);
+    role.o_done = o_done(t);
+    role.remote_arrive = false;
+    role.xchg = xchg;
+    role.stage_base = stage_base;
+    role.abort_flag = abort_flag;
+    role.status = status;
+    role.out = out;
+    role.scale_log2e = scale_log2e;
+    role.total_steps = total_steps;
+    role.num_kv = num_kv;
+    role.first_item = (int)blockIdx.x;
+    role.item_stride = (int)gridDim.x;
+    role.qblocks = qblocks;
+    role.Hq = Hq;
+    role.Hkv = Hkv;
+    role.S = S;
+    role.group_begin = group_begin;
+    role.item_rows = 2 * A_BM;
+    role.rows_before_tile = t * A_BM;
+    softmax_role<SPLIT>(role, warp, lane);
   }
 
   ptx::tc_fence_before();

@@ -240,7 +240,9 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
 
 /* Selects the attention kernel: 0 = automatic, 1 = FP32 CUDA-core kernel,
  * 2 = tensor-core kernel (f16 storage, D = 128, S a multiple of 256), 3 = the same with two
- * softmax warpgroups per query tile. No reference counterpart. */
+ * softmax warpgroups per query tile (the automatic choice where it applies), 4 and 5 = the
+ * CTA-pair form of 2 and 3 (S a multiple of 512; same results, measured slower, kept for comparison).
+ * No reference counterpart. */
 int dtn_gqa_set_variant(int variant);
 
 #ifdef __cplusplus

@@ -626,6 +626,33 @@ def test_gqa_through_the_compile_and_launch_surface(cuda, runner):
         np.testing.assert_array_equal(hosted, result['outputs']['out'])
 
 
+def test_gqa_cta_pair_kernel_equals_the_one_cta_kernel(cuda):
+    """The CTA-pair kernel (one 256-row instruction per product, each CTA holding half of every K and V tile) runs the
+    same softmax code on the same products: its output is bit-identical to the one-CTA kernel's, for both warpgroup
+    splits, on whole launches and on group ranges; shapes it does not cover are refused."""
+    generator = cuda.Generator(device='cuda:0').manual_seed(5)
+    batch, hq, hkv, s, d = 2, 6, 2, 1536, 128
+    q = (cuda.randn((batch, hq, s, d), device='cuda:0', generator=generator) / d ** 0.5).half()
+    k = (cuda.randn((batch, hkv, s, d), device='cuda:0', generator=generator) / d ** 0.5).half()
+    v = (cuda.randn((batch, hkv, s, d), device='cuda:0', generator=generator) / d ** 0.5).half()
+    try:
+        results = {}
+        for variant in (2, 3, 4, 5):
+            ops.set_gqa_variant(variant)
+            results[variant] = ops.gqa_attention(q, k, v, d ** -0.5).clone()
+            ops.check_device_status()
+        assert bool(cuda.equal(results[4], results[2])) and bool(cuda.equal(results[5], results[3]))
+        partial = cuda.zeros_like(results[5])
+        ops.gqa_attention(q, k, v, d ** -0.5, out=partial, groups=(1, 3))
+        per_group = hq // hkv
+        flat, whole = partial.view(batch * hkv, per_group, s, d), results[5].view(batch * hkv, per_group, s, d)
+        assert bool(cuda.equal(flat[1:3], whole[1:3])) and float(flat[0].abs().sum()) == 0.0 and float(flat[3].abs().sum()) == 0.0
+        with pytest.raises(NotImplementedError, match='multiple of 512'):
+            ops.gqa_attention(q[:, :, :768].contiguous(), k[:, :, :768].contiguous(), v[:, :, :768].contiguous(), d ** -0.5)
+    finally:
+        ops.set_gqa_variant(0)
+
+
 def test_gqa_group_ranges_partition_the_output(cuda):
     from deuteron_b200 import sharding
     batch, hq, hkv, s, d = 2, 8, 2, 256, 128
