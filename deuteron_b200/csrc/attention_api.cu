@@ -19,7 +19,7 @@ static int g_gqa_variant = 0;
 extern "C" {
 
 int dtn_gqa_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 5, DTN_ERR_INVALID, "gqa: variant must be 0..5");
+  DTN_REQUIRE(variant >= 0 && variant <= 6, DTN_ERR_INVALID, "gqa: variant must be 0..6");
   dtn::g_gqa_variant = variant;
   return DTN_OK;
 }
@@ -47,6 +47,11 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   // and 871 vs 864 at 16384 (each measured first in its process; whichever variant runs second on a warm GPU loses
   // ~10 % to the power cap, so back-to-back comparisons must alternate the order).
   if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 3 : 1;
+  if (variant == 6) {   // all sixteen softmax warps on one tile at a time
+    DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
+                "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");
+    return gqa_tc_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, 4, s);
+  }
   if (variant >= 4) {   // CTA pairs (4: one softmax warpgroup per tile, 5: two)
     DTN_REQUIRE(gqa_tc_pair_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
                 "gqa: the CTA-pair kernel needs f16 storage, head_dim 128 and S a multiple of 512");

@@ -58,7 +58,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 20 + 8);
   volatile float2* xchg = reinterpret_cast<volatile float2*>(bar_ptr + 256);
   float* stage_base = reinterpret_cast<float*>(bar_ptr + 256 + A_XCHG_BYTES);   // 1 KiB per softmax warp
-  constexpr int kTmaWarp = 8 * SPLIT, kMmaWarp = 8 * SPLIT + 1;
+  constexpr int kTmaWarp = attn_softmax_warps(SPLIT), kMmaWarp = attn_softmax_warps(SPLIT) + 1;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblocks = S / (2 * A_BM);
@@ -66,7 +66,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const int my_items = ((int)blockIdx.x < total_items) ? (total_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   const int total_steps = my_items * num_kv;
 
-  for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) {   // sequence 0 = empty
+  for (int i = threadIdx.x; i < A_XCHG_BYTES / 8; i += blockDim.x) {   // sequence 0 = empty
     xchg[i].x = 0.f;
     xchg[i].y = 0.f;
   }
@@ -82,8 +82,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::mbar_init(q_full(t), 1);
       ptx::mbar_init(q_empty(t), 1);
       ptx::mbar_init(s_full(t), 1);
-      ptx::mbar_init(p_half(t, 0), 4 * SPLIT);   // one arrival per softmax warp
-      ptx::mbar_init(p_half(t, 1), 4 * SPLIT);
+      ptx::mbar_init(p_half(t, 0), attn_p_half_arrivals(SPLIT));   // one arrival per softmax warp that writes this half
+      ptx::mbar_init(p_half(t, 1), attn_p_half_arrivals(SPLIT));
       ptx::mbar_init(o_done(t), 1);
     }
     ptx::mbar_fence_init();
@@ -226,7 +226,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     __syncwarp();
   } else {
     // ------------------------------------ softmax + output -----------------------------------
-    const int t = warp / (4 * SPLIT);   // tile of this warp
+    const int t = SPLIT == 4 ? 0 : warp / (4 * SPLIT);   // tile of this warp
     SoftmaxRole role;
     role.tmem_base = tmem_base;
     role.s_full = s_full(t);
@@ -251,7 +251,18 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     role.group_begin = group_begin;
     role.item_rows = 2 * A_BM;
     role.rows_before_tile = t * A_BM;
-    softmax_role<SPLIT>(role, warp, lane);
+    role.rows_between_tiles = A_BM;
+    if constexpr (SPLIT == 4) {
+      role.s_full = s_full(0);
+      role.p_half0 = p_half(0, 0);
+      role.p_half1 = p_half(0, 1);
+      role.o_done = o_done(0);
+      role.rows_before_tile = 0;
+      const SoftmaxBarrierStrides strides = {s_full(1) - s_full(0), p_half(1, 0) - p_half(0, 0), o_done(1) - o_done(0)};
+      softmax_role_alternating(role, strides, warp, lane);
+    } else {
+      softmax_role<SPLIT>(role, warp, lane);
+    }
   }
 
   ptx::tc_fence_before();
@@ -341,6 +352,7 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
 
 int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
                   int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s) {
+  if (split == 4) return gqa_tc_launch_t<4>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s);
   return split == 2 ? gqa_tc_launch_t<2>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s)
                     : gqa_tc_launch_t<1>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s);
 }

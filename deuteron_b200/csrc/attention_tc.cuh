@@ -8,7 +8,10 @@
 
 namespace dtn {
 
-constexpr int attn_threads(int split) { return (8 * split + 2) * 32; }   // softmax warps + TMA warp + MMA warp
+// split: softmax warpgroups per 128-row tile (1 or 2), or 4 = all sixteen softmax warps on one tile at a time
+constexpr int attn_softmax_warps(int split) { return split == 4 ? 16 : 8 * split; }
+constexpr int attn_threads(int split) { return (attn_softmax_warps(split) + 2) * 32; }   // softmax warps + TMA warp + MMA warp
+constexpr int attn_p_half_arrivals(int split) { return split == 4 ? 8 : 4 * split; }     // warps arriving per half tile of probabilities
 constexpr int A_BM = 128;          // query rows per tile (two tiles per CTA)
 constexpr int A_BN = 128;          // keys per step
 constexpr int A_D = 128;           // head dimension
@@ -16,7 +19,7 @@ constexpr int A_HALF_BYTES = 128 * 128;           // one [128 rows][64 f16] swiz
 constexpr int A_TILE_BYTES = 2 * A_HALF_BYTES;    // one [128][128] f16 tile
 constexpr int A_KV_STAGES = 2;
 constexpr int A_SMEM_TILES = 2 /*Q*/ + 2 * A_KV_STAGES /*K,V*/;
-constexpr int A_XCHG_BYTES = 2 * 2 * 128 * 8;   // [tile][column share][row] (value, sequence) slots
+constexpr int A_XCHG_BYTES = 2 * 4 * 128 * 8;   // [tile][column share (up to 4)][row] (value, sequence) slots
 constexpr int A_STAGE_BYTES = 16 * 1024;        // 1 KiB of output staging per softmax warp (at most 16 of them)
 constexpr int A_SMEM_BYTES = A_SMEM_TILES * A_TILE_BYTES + 256 + A_XCHG_BYTES + A_STAGE_BYTES + 1024;
 constexpr float A_RESCALE_THRESHOLD = 8.0f;   // in log2 units
@@ -112,6 +115,7 @@ struct SoftmaxRole {
   int total_steps, num_kv;
   int first_item, item_stride, qblocks, Hq, Hkv, S, group_begin, item_rows;
   int rows_before_tile;      // first row of this warp's tile inside the work item
+  int rows_between_tiles;    // alternating form: row distance from tile 0 to tile 1 inside the work item
 };
 
 template <int SPLIT, bool KEEP = false>
@@ -285,6 +289,177 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
           const int rloc = rd_row + 16 * h;
           const float4 val = *reinterpret_cast<const float4*>(stage + rloc * 8 + 4 * (rd_piece ^ ((rloc >> 2) & 1)));
           *reinterpret_cast<float4*>(obase + (int64_t)rloc * A_D + c * 32 + sub * 8 + 4 * rd_piece) = val;
+        }
+        __syncwarp();
+      }
+    }
+  }
+}
+
+// Hands `value` to the three threads that own the other column quarters of the same row and folds theirs into it
+// (maximum or sum). slots: this tile's [4 quarters][128 rows] block; `mine` is this thread's quarter.
+template <bool MAX>
+__device__ __forceinline__ bool exchange_four(volatile float2* slots, int mine, int row, float& value, int seq,
+                                              volatile int* abort_flag) {
+  asm volatile("st.volatile.shared.v2.f32 [%0], {%1, %2};" ::"r"(smem_u32((const void*)(slots + mine * 128 + row))), "f"(value),
+               "f"(__int_as_float(seq))
+               : "memory");
+  float folded = value;
+  const long long start = clock64();
+#pragma unroll
+  for (int other = 1; other < 4; ++other) {
+    const uint32_t addr = smem_u32((const void*)(slots + ((mine + other) & 3) * 128 + row));
+    while (true) {
+      float a, b;
+      asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr) : "memory");
+      if (__float_as_int(b) == seq) {
+        folded = MAX ? fmaxf(folded, a) : folded + a;
+        break;
+      }
+      if (*abort_flag) return false;
+      if (clock64() - start > ptx::kWaitBudgetCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
+  value = folded;
+  return true;
+}
+
+// Softmax + output with all sixteen warps on one tile at a time. A warp owns 32 rows (its tensor-memory lane quarter)
+// and one 32-column quarter of the scores, of BOTH tiles: it serves tile 0's step, then tile 1's, and so on. A tile's
+// softmax therefore takes half as long as with eight warps per tile working on both tiles at once -- it has to fit in
+// the time the tensor core spends on the other tile's products, or the tensor core waits for it. The thread's 32
+// scores are read from tensor memory once and stay in registers between the maximum and the probabilities.
+// R.s_full, R.p_half0/1 and R.o_done are tile 0's barriers; tile 1's follow at the distances given below.
+struct SoftmaxBarrierStrides {
+  uint32_t s_full, p_half, o_done;   // byte distance from a tile-0 barrier to the same barrier of tile 1
+};
+
+__device__ __forceinline__ void softmax_role_alternating(const SoftmaxRole& R, const SoftmaxBarrierStrides& strides, int warp, int lane) {
+  const uint32_t tmem_base = R.tmem_base;
+  volatile int* abort_flag = R.abort_flag;
+  int* status = R.status;
+  const int total_steps = R.total_steps, num_kv = R.num_kv;
+  const float scale_log2e = R.scale_log2e;
+  const int quarter = warp & 3;          // tensor-memory lanes [32 * quarter, +32)
+  const int cq = (warp >> 2) & 3;        // column quarter: score / output columns [32 * cq, +32)
+  const int row_in_tile = quarter * 32 + lane;
+  const uint32_t lane_field = (uint32_t)(quarter * 32) << 16;
+  float* stage = R.stage_base + warp * 256;
+  float m_used[2] = {-INFINITY, -INFINITY};
+  float mass[2] = {0.f, 0.f};
+  bool ok = true;
+  for (int g = 0; g < total_steps && ok; ++g) {
+    const int j = g % num_kv;
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      if (j == 0) {
+        m_used[t] = -INFINITY;
+        mass[t] = 0.f;
+      }
+      const uint32_t s_tmem = tmem_base + lane_field + (uint32_t)(t * 128 + cq * 32);
+      const uint32_t o_tmem = tmem_base + lane_field + (uint32_t)(256 + t * 128 + cq * 32);
+      volatile float2* slots = R.xchg + t * 4 * 128;
+      const bool ready = ptx::mbar_wait(R.s_full + t * strides.s_full, (uint32_t)g & 1u, abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) {
+        if (lane == 0) atomicExch(status, 0x3100 | t);
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      uint32_t r[32], w[32];
+      ptx::tmem_ld_32x32(s_tmem, r);
+      ptx::tmem_ld_wait();
+      float mx = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) mx = max3(mx, __uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      const bool got = exchange_four<true>(slots, cq, row_in_tile, mx, 2 * g + 1, abort_flag);
+      if (!__all_sync(0xffffffffu, got)) {
+        if (lane == 0) atomicExch(status, 0x3300 | t);
+        ok = false;
+        break;
+      }
+      const float mx2 = mx * scale_log2e;
+      const bool grow = (j == 0) || (mx2 > m_used[t] + A_RESCALE_THRESHOLD);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = grow ? mx2 : m_used[t];
+        const float alpha = (j == 0) ? 0.f : ex2_approx_ftz(m_used[t] - m_new);   // 1 when this row does not grow
+        if (j > 0) {
+          // All earlier products into O_t are complete: s_full(t) of this step was committed after them.
+          uint32_t o[32];
+          ptx::tmem_ld_32x32(o_tmem, o);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          ptx::tmem_st_32x32(o_tmem, o);
+          ptx::tmem_st_wait();
+        }
+        mass[t] *= alpha;
+        m_used[t] = m_new;
+      }
+      const float shift = A_BIAS - m_used[t];
+      float sum = 0.f;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(r[2 * i]), scale_log2e, shift));
+        const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(r[2 * i + 1]), scale_log2e, shift));
+        sum += p0 + p1;
+        const __half2 hi = __floats2half2_rn(p0, p1);
+        const float2 back = __half22float2(hi);
+        const __half2 lo = __floats2half2_rn(p0 - back.x, p1 - back.y);
+        w[i] = *reinterpret_cast<const uint32_t*>(&hi);
+        w[16 + i] = *reinterpret_cast<const uint32_t*>(&lo);
+      }
+      mass[t] += sum;
+      ptx::tmem_st_32x32(s_tmem, w);
+      ptx::tmem_st_wait();
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        const uint32_t bar = ((cq >> 1) ? R.p_half1 : R.p_half0) + t * strides.p_half;   // quarters 0, 1 -> first half of the keys
+        if (R.remote_arrive) ptx::mbar_arrive_cluster(bar);
+        else ptx::mbar_arrive(bar);
+      }
+    }
+    if (!ok || j != num_kv - 1) continue;
+
+    // ---- the item's last step, both tiles: normalise and store this warp's 32 x 32 block of each output ----
+    const int it = g / num_kv;
+    const AttnItem item = attn_item(R.first_item + it * R.item_stride, R.qblocks, R.Hq, R.Hkv, R.S, R.group_begin, R.item_rows);
+    const int wr_swap = (lane >> 2) & 1;
+    const int rd_row = lane >> 1, rd_piece = lane & 1;
+#pragma unroll 1
+    for (int t = 0; t < 2; ++t) {
+      const uint32_t o_tmem = tmem_base + lane_field + (uint32_t)(256 + t * 128 + cq * 32);
+      bool done = ptx::mbar_wait(R.o_done + t * strides.o_done, (uint32_t)it & 1u, abort_flag);
+      float total = mass[t];
+      done = done && exchange_four<false>(R.xchg + t * 4 * 128, cq, row_in_tile, total, 2 * g + 2, abort_flag);
+      if (!__all_sync(0xffffffffu, done)) {
+        if (lane == 0) atomicExch(status, 0x3200 | t);
+        ok = false;
+        break;
+      }
+      ptx::tc_fence_after();
+      const float inv = 1.0f / total;
+      float* obase = R.out + ((int64_t)item.q_row0 + R.rows_before_tile + t * R.rows_between_tiles + quarter * 32) * A_D;
+      uint32_t o[32];
+      ptx::tmem_ld_32x32(o_tmem, o);
+      ptx::tmem_ld_wait();
+#pragma unroll
+      for (int sub = 0; sub < 4; ++sub) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+          *reinterpret_cast<float4*>(stage + lane * 8 + 4 * (i ^ wr_swap)) =
+              make_float4(__uint_as_float(o[8 * sub + 4 * i]) * inv, __uint_as_float(o[8 * sub + 4 * i + 1]) * inv,
+                          __uint_as_float(o[8 * sub + 4 * i + 2]) * inv, __uint_as_float(o[8 * sub + 4 * i + 3]) * inv);
+        __syncwarp();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int rloc = rd_row + 16 * h;
+          const float4 val = *reinterpret_cast<const float4*>(stage + rloc * 8 + 4 * (rd_piece ^ ((rloc >> 2) & 1)));
+          *reinterpret_cast<float4*>(obase + (int64_t)rloc * A_D + cq * 32 + sub * 8 + 4 * rd_piece) = val;
         }
         __syncwarp();
       }

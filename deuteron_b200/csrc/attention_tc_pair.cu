@@ -103,7 +103,7 @@ gqa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int my_items = pair < total_items ? (total_items - 1 - pair) / num_pairs + 1 : 0;
   const int total_steps = my_items * num_kv;
 
-  for (int i = threadIdx.x; i < 2 * 2 * 128; i += blockDim.x) {
+  for (int i = threadIdx.x; i < A_XCHG_BYTES / 8; i += blockDim.x) {
     xchg[i].x = 0.f;
     xchg[i].y = 0.f;
   }
@@ -269,6 +269,7 @@ gqa_tc_pair_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     role.group_begin = group_begin;
     role.item_rows = P_ITEM_ROWS;
     role.rows_before_tile = t * (2 * A_BM) + rank * A_BM;
+    role.rows_between_tiles = 2 * A_BM;
     softmax_role<SPLIT>(role, warp, lane);
   }
 

@@ -241,7 +241,8 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
 /* Selects the attention kernel: 0 = automatic, 1 = FP32 CUDA-core kernel,
  * 2 = tensor-core kernel (f16 storage, D = 128, S a multiple of 256), 3 = the same with two
  * softmax warpgroups per query tile (the automatic choice where it applies), 4 and 5 = the
- * CTA-pair form of 2 and 3 (S a multiple of 512; same results, measured slower, kept for comparison).
+ * CTA-pair form of 2 and 3 (S a multiple of 512; same results, measured slower, kept for comparison),
+ * 6 = variant 3's shape with all sixteen softmax warps serving one tile at a time (measured slower too).
  * No reference counterpart. */
 int dtn_gqa_set_variant(int variant);
 

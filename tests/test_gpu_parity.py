@@ -642,6 +642,11 @@ def test_gqa_cta_pair_kernel_equals_the_one_cta_kernel(cuda):
             results[variant] = ops.gqa_attention(q, k, v, d ** -0.5).clone()
             ops.check_device_status()
         assert bool(cuda.equal(results[4], results[2])) and bool(cuda.equal(results[5], results[3]))
+        # all sixteen softmax warps on one tile at a time: the same products, row sums added in another order
+        ops.set_gqa_variant(6)
+        alternating = ops.gqa_attention(q, k, v, d ** -0.5)
+        ops.check_device_status()
+        assert float((alternating - results[3]).abs().max()) <= 1e-6 * float(results[3].abs().max())
         partial = cuda.zeros_like(results[5])
         ops.gqa_attention(q, k, v, d ** -0.5, out=partial, groups=(1, 3))
         per_group = hq // hkv
