@@ -50,6 +50,24 @@ __host__ __device__ constexpr uint32_t attn_idesc(int b_mn) {
   return ptx::umma_idesc(0, 128, 128) | ((uint32_t)b_mn << 16);
 }
 
+// Packed FP32 arithmetic (two lanes per instruction, sm_100): halves the issue slots of the scale-and-shift, the row
+// sum and the residual of the probability pass.
+__device__ __forceinline__ float2 fma_f32x2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+      "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 add_f32x2(float2 a, float2 b) {
+  float2 d;
+  asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+      : "=f"(d.x), "=f"(d.y)
+      : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 // Hands `value` to the thread that owns the other column share of the same row and returns that
 // thread's value in `other`. A slot holds (value, sequence number); the 8-byte store makes both
 // visible together. The wait is bounded like every other wait in this file.
@@ -223,17 +241,21 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
         ptx::tmem_ld_wait();
       }
       const uint32_t* src = kKeep ? kept + 32 * (c - c0) : r;
+      const float2 scale2 = make_float2(scale_log2e, scale_log2e), shift2 = make_float2(shift, shift);
+      const float2 minus_one = make_float2(-1.f, -1.f);
+      float2 sums = make_float2(0.f, 0.f);
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        const float p0 = ex2_approx_ftz(fmaf(__uint_as_float(src[2 * i]), scale_log2e, shift));
-        const float p1 = ex2_approx_ftz(fmaf(__uint_as_float(src[2 * i + 1]), scale_log2e, shift));
-        mass += p0 + p1;
-        const __half2 hi = __floats2half2_rn(p0, p1);
-        const float2 back = __half22float2(hi);
-        const __half2 lo = __floats2half2_rn(p0 - back.x, p1 - back.y);
+        const float2 x = fma_f32x2(make_float2(__uint_as_float(src[2 * i]), __uint_as_float(src[2 * i + 1])), scale2, shift2);
+        const float2 p = make_float2(ex2_approx_ftz(x.x), ex2_approx_ftz(x.y));
+        sums = add_f32x2(sums, p);
+        const __half2 hi = __floats2half2_rn(p.x, p.y);
+        const float2 residual = fma_f32x2(__half22float2(hi), minus_one, p);   // p - hi, exact
+        const __half2 lo = __floats2half2_rn(residual.x, residual.y);
         w[i] = *reinterpret_cast<const uint32_t*>(&hi);
         w[16 + i] = *reinterpret_cast<const uint32_t*>(&lo);
       }
+      mass += sums.x + sums.y;
       ptx::tmem_st_32x32(s_tmem + (uint32_t)(c * 32), w);
       if (((c - c0 + 1) % (kChunks / 2)) == 0) {   // this warp's share of one half is in tensor memory
         ptx::tmem_st_wait();
