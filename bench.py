@@ -465,7 +465,8 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
-PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max', 'row_softmax', 'rms_norm')
+PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'gemm_skinny', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max',
+                 'row_softmax', 'rms_norm', 'fused_affine')
 
 
 def run_profile_case(name: str, launches: int) -> None:
@@ -476,7 +477,21 @@ def run_profile_case(name: str, launches: int) -> None:
     torch.cuda.set_device(0)
     device = torch.device('cuda', 0)
     generator = torch.Generator(device=device).manual_seed(7)
-    if name.startswith('gemm_'):
+    if name == 'gemm_skinny':
+        a = torch.rand((16, 8192), device=device, generator=generator) * 2 - 1
+        b = torch.rand((8192, 8192), device=device, generator=generator) * 2 - 1
+        c = torch.empty((16, 8192), device=device)
+        call = lambda: ops.gemm(a, b, 'bf16x3', out=c)
+    elif name == 'fused_affine':
+        from deuteron_b200 import compile_kernel, native, schedules
+        n = 1 << 26
+        plan = compile_kernel(*schedules.pointwise_example('affine', n)).plan
+        x = torch.randn(n, device=device, generator=generator)
+        z = torch.empty_like(x)
+        constants = {'mul_c1': torch.tensor([2.0], device=device), 'add_c1': torch.tensor([1.0], device=device), 'x': x}
+        pointers = [constants[plan.buffers[f'in{i}'][0]].data_ptr() for i in range(len(plan.params['inputs']))]
+        call = lambda: native.elementwise_program(plan.params, pointers, z.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    elif name.startswith('gemm_'):
         n = 4096
         a = torch.rand((n, n), device=device, generator=generator) * 2 - 1
         b = torch.rand((n, n), device=device, generator=generator) * 2 - 1

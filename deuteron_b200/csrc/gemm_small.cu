@@ -40,6 +40,9 @@ __device__ __forceinline__ void cp_async_4(uint32_t dst, const void* src, int va
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void cluster_barrier() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
@@ -135,16 +138,21 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[i][j][e] = 0.f;
 
-  const int ktiles = (K + BK - 1) / BK;
+  // With gridDim.z > 1 the launch is a cluster of gridDim.z CTAs along z that share one output tile: each takes a
+  // contiguous share of the k-tiles and the partial sums meet in the first CTA's shared memory at the end.
+  const int k_parts = (int)gridDim.z, k_part = (int)blockIdx.z;
+  const int all_ktiles = (K + BK - 1) / BK;
+  const int kt_first = (int)((int64_t)all_ktiles * k_part / k_parts);
+  const int ktiles = (int)((int64_t)all_ktiles * (k_part + 1) / k_parts) - kt_first;
 #pragma unroll
   for (int s = 0; s < STAGES - 1; ++s) {
-    if (s < ktiles) load_tile(s, s);
+    if (s < ktiles) load_tile(kt_first + s, s);
     cp_async_commit();
   }
   for (int kt = 0; kt < ktiles; ++kt) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
-    if (kt + STAGES - 1 < ktiles) load_tile(kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
+    if (kt + STAGES - 1 < ktiles) load_tile(kt_first + kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
     const float* As = small_smem + (kt % STAGES) * Cfg::kStageFloats;
     const float* Bs = As + BM * Cfg::kLda;
@@ -220,14 +228,48 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
           for (int e = 0; e < 4; ++e) exchange[(i * NI + j) * 4 + e] = acc[i][j][e];
     }
     __syncthreads();
-    if (kgroup == 1) return;
+    if (kgroup == 0) {
 #pragma unroll
-    for (int i = 0; i < MI; ++i)
+      for (int i = 0; i < MI; ++i)
 #pragma unroll
-      for (int j = 0; j < NI; ++j)
+        for (int j = 0; j < NI; ++j)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) acc[i][j][e] += exchange[(i * NI + j) * 4 + e];
+          for (int e = 0; e < 4; ++e) acc[i][j][e] += exchange[(i * NI + j) * 4 + e];
+    }
   }
+  if (k_parts > 1) {
+    // Partial sums of the other CTAs of the cluster go to the first CTA's shared memory (distributed shared memory
+    // stores), in a fixed slot per CTA and thread, and are added there in rank order: no atomics, one result.
+    constexpr int kPerThread = MI * NI * 4;
+    float* slots = small_smem + 2048;   // past the intra-CTA exchange block above
+    cluster_barrier();                  // every CTA of the cluster is done with its ring and its exchange block
+    if (k_part != 0 && kgroup == 0) {
+      const uint32_t local = smem_u32(slots + ((k_part - 1) * S_THREADS + (warp * 32 + lane)) * kPerThread);
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
+#pragma unroll
+      for (int i = 0; i < MI; ++i)
+#pragma unroll
+        for (int j = 0; j < NI; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4u * ((i * NI + j) * 4 + e)), "f"(acc[i][j][e]) : "memory");
+    }
+    cluster_barrier();
+    if (k_part != 0) return;
+    if (kgroup == 0) {
+      for (int part = 1; part < k_parts; ++part) {
+        const float* theirs = slots + ((part - 1) * S_THREADS + (warp * 32 + lane)) * kPerThread;
+#pragma unroll
+        for (int i = 0; i < MI; ++i)
+#pragma unroll
+          for (int j = 0; j < NI; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) acc[i][j][e] += theirs[(i * NI + j) * 4 + e];
+      }
+    }
+  }
+  if (kgroup != 0) return;
 
 #pragma unroll
   for (int i = 0; i < MI; ++i)
@@ -251,7 +293,7 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
 
 template <int MODE, bool ALIGNED, int BM, int BK, int STAGES, int KSPLIT>
 static int gemm_small_launch_cfg(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
-                                 int64_t ldb, int64_t ldc, cudaStream_t s) {
+                                 int64_t ldb, int64_t ldc, cudaStream_t s, int k_parts = 1) {
   using Cfg = SmallCfg<MODE, BM, BK, STAGES>;
   dim3 grid((unsigned)((N + S_BN - 1) / S_BN), (unsigned)((M + BM - 1) / BM));
   DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm: M too large for the small-problem kernel");
@@ -262,6 +304,23 @@ static int gemm_small_launch_cfg(const float* A, const float* B, float* C, int64
   if (attr_dev != dev) {
     DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_dev = dev;
+  }
+  if (k_parts > 1) {
+    grid.z = (unsigned)k_parts;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(S_THREADS * KSPLIT);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = (unsigned)k_parts;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc));
+    return DTN_OK;
   }
   kernel<<<grid, S_THREADS * KSPLIT, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
   DTN_LAUNCH_CHECK("gemm_x3_small_kernel");
@@ -276,9 +335,22 @@ static int gemm_small_launch_mode(const float* A, const float* B, float* C, int6
     const char* text = getenv("DTN_GEMM_SMALL_CFG");   // tuning aid: 1..7 pick a configuration, anything else = automatic
     return text ? atoi(text) : 0;
   }();
-#define DTN_SMALL_CFG(BM, BK, KS)                                                                             \
-  return aligned ? gemm_small_launch_cfg<MODE, true, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s)        \
-                 : gemm_small_launch_cfg<MODE, false, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s)
+#define DTN_SMALL_CFG(BM, BK, KS)                                                                                     \
+  return aligned ? gemm_small_launch_cfg<MODE, true, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)       \
+                 : gemm_small_launch_cfg<MODE, false, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)
+  // Skinny products have too few output tiles to fill the device (128 for N = 8192): clusters of CTAs along k share a
+  // tile. DTN_GEMM_SKINNY_KPARTS overrides the count (1, 2 or 4).
+  static const int forced_parts = [] {
+    const char* text = getenv("DTN_GEMM_SKINNY_KPARTS");
+    return text ? atoi(text) : 0;
+  }();
+  int k_parts = 1;
+  if (M <= 16 && K >= 2048) {
+    const int64_t tiles = (N + S_BN - 1) / S_BN;
+    k_parts = tiles * 2 <= (int64_t)sm_count() * 2 ? 2 : 1;
+    if (tiles * 4 <= (int64_t)sm_count() * 2) k_parts = 4;
+    if (forced_parts == 1 || forced_parts == 2 || forced_parts == 4) k_parts = forced_parts;
+  }
   int choice = forced;
   if (choice < 1 || choice > 7) {
     // Measured on B200 (us, bf16x3): 128^3 3.1 with 16-row tiles against 5.2 with 64-row tiles, 128x64x256 4.8 / 8.5,
