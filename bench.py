@@ -425,6 +425,55 @@ def run_ours(args) -> None:
                    'matches_resident_result': e2e_match}
             del host, result
 
+    # The second sharded path, at N > 1 only: one GQA forward (B=4, 32/8 heads, S=4096, D=128) split over the ranks by
+    # (batch, kv-head) groups, no exchange; aggregate = the whole problem's flops / the slowest rank's time.
+    gqa_sharded = None
+    if world > 1 and not args.no_extras:
+        # Every rank reaches every barrier and collective below whatever happens in between, so that a failure on
+        # one rank can neither hang the others nor cost the line above.
+        batch, hq, hkv, s, d = 4, 32, 8, 4096, 128
+        groups = sharding.group_range(batch * hkv, world, rank)
+        failed, local_ms, run = 0.0, 0.0, None
+        try:
+            del a, b
+            torch.cuda.empty_cache()
+            generator.manual_seed(7)
+            q = (torch.randn((batch, hq, s, d), device=device, generator=generator) / d ** 0.5).half()
+            kk = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
+            vv = (torch.randn((batch, hkv, s, d), device=device, generator=generator) / d ** 0.5).half()
+            o = torch.zeros((batch, hq, s, d), device=device)
+            run = lambda: ops.gqa_attention(q, kk, vv, d ** -0.5, out=o, groups=groups)
+            for _ in range(3):
+                run()
+        except Exception as error:   # noqa: BLE001 - reported in the line
+            failed, run = 1.0, None
+            print(f'rank {rank}: sharded attention set-up failed: {error}', file=sys.stderr)
+        barrier()
+        try:
+            if run is not None:
+                begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                begin.record()
+                for _ in range(10):
+                    run()
+                end.record()
+                end.synchronize()
+                local_ms = begin.elapsed_time(end) / 10
+                ops.check_device_status()
+        except Exception as error:   # noqa: BLE001
+            failed = 1.0
+            print(f'rank {rank}: sharded attention failed: {error}', file=sys.stderr)
+        barrier()
+        gathered = torch.tensor([local_ms, failed], device=device)
+        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+        gqa_ms, any_failed = float(gathered[0].item()), float(gathered[1].item()) > 0
+        flops = 4.0 * batch * hq * s * s * d
+        if any_failed or gqa_ms <= 0:
+            gqa_sharded = {'workload': 'gqa_fwd_b4_h32_kv8_s4096_d128_f16', 'error': 'a rank failed; see stderr'}
+        else:
+            gqa_sharded = {'workload': 'gqa_fwd_b4_h32_kv8_s4096_d128_f16', 'groups_per_rank': groups[1] - groups[0], 'ms': gqa_ms,
+                           'tflops_aggregate': flops / gqa_ms / 1e9, 'scaling': 'strong',
+                           'frac_of_bf16_peak_per_gpu': flops / gqa_ms / 1e9 / world / peaks['bf16_tflops']}
+
     if rank == 0:
         peak = peaks['bf16_tflops'] / 3.0
         achieved = FLOPS_PER_GEMM / product_ms / 1e9
@@ -452,6 +501,8 @@ def run_ours(args) -> None:
             reference_gpu = reference_kernel_baseline(torch, ops)
             if reference_gpu is not None:
                 line['reference_kernel_baseline'] = reference_gpu
+        if gqa_sharded is not None:
+            line['extras'] = {'gqa_sharded_by_groups': gqa_sharded}
         if world == 1 and not args.no_extras:
             del a, b, c
             torch.cuda.empty_cache()
