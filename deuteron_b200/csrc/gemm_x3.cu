@@ -266,7 +266,7 @@ struct GemmCfg {
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
   static_assert(kStages >= 2, "ring too shallow");
-  static_assert(kTmemCols == 256 || kTmemCols == 512, "tensor memory columns must be a power of two");
+  static_assert(kTmemCols == 128 || kTmemCols == 256 || kTmemCols == 512, "tensor memory columns must be a power of two");
 };
 
 __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int group_m, int& tm, int& tn) {
@@ -672,14 +672,21 @@ static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C
   if (variant == 0) {
     // Large problems: a CTA pair per 256x256 tile (least shared-memory traffic per flop); smaller
     // ones: more, smaller tiles keep more SMs busy.
+    // Measured (bf16x3, us, variants 1 / 2 / 3): 1536^3 (36 pair tiles) 27.9 / 40.7 / 39.8; 2048^3 (64) 54.1 / 49.8 / 49.1;
+    // 3072^3 (144) 157 / 149 / 136; 8192^3 2723 / 2594 / 2341. Pairs win from about three quarters of a wave of pairs.
     const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
     const int64_t wide_tiles = ((M + 127) / 128) * ((N + 255) / 256);
-    variant = (pair_tiles >= sm_count() / 2) ? 3 : (wide_tiles >= sm_count()) ? 2 : 1;
+    const int64_t square_tiles = ((M + 127) / 128) * ((N + 127) / 128);
+    variant = (pair_tiles * 8 >= (int64_t)(sm_count() / 2) * 6) ? 3 : (wide_tiles >= sm_count()) ? 2 : 1;
+    // fewer 128x128 tiles than half the SMs: 128x64 tiles put twice as many CTAs to work (768^3 14.3 vs 16.7 us,
+    // 1024^3 16.8 vs 18.2 us)
+    if (variant == 1 && square_tiles * 2 <= sm_count()) variant = 5;
   }
   switch (variant) {
     case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
     case 2: return launch_tc<KIND, 1, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
     case 3: return launch_tc<KIND, 2, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
+    case 5: return launch_tc<KIND, 1, 64>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
     default:
       set_error("gemm: unknown variant %d", variant);
       return DTN_ERR_INVALID;
@@ -763,7 +770,7 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
 }
 
 int dtn_gemm_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 4, DTN_ERR_INVALID, "gemm: variant must be 0..4");
+  DTN_REQUIRE(variant >= 0 && variant <= 5, DTN_ERR_INVALID, "gemm: variant must be 0..5");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
 }

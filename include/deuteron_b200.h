@@ -215,7 +215,9 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
 /* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile,
  *   4 = the single-kernel path for small problems (operand split inside the kernel, warp-level
- *   mma.sync products, no workspace; what automatic picks below about 320^3 multiply-adds).
+ *   mma.sync products, no workspace; what automatic picks up to about 520^3 multiply-adds and for
+ *   at most 16 rows), 5 = one-CTA 128x64 tile (automatic when 128x128 tiles would occupy at most
+ *   half of the SMs).
  * No reference counterpart. */
 int dtn_gemm_set_variant(int variant);
 

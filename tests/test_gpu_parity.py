@@ -384,7 +384,7 @@ def test_tensor_matmul_example_all_modes(runner, golden, published):
     assert sha(produced) == published['results']['tensor_f32']['output_sha256']['result']
 
 
-@pytest.mark.parametrize('variant', [0, 1, 3, 4])
+@pytest.mark.parametrize('variant', [0, 1, 3, 4, 5])
 def test_compensated_modes_hash_to_the_reference_gpu_outputs(cuda, published, variant):
     # Same split, same three products in the same order per k-step, FP32 tensor-core accumulation: every kernel
     # variant reproduces the bits of the reference's own run of its 128^3 example (published SHA-256 and max error).
@@ -414,7 +414,7 @@ SHAPES = [(128, 128, 128), (256, 256, 64), (384, 768, 1000), (200, 136, 77), (16
 
 
 @pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
-@pytest.mark.parametrize('variant', [1, 2, 3, 4])   # tcgen05 tiles 128x128, 128x256, CTA pair 256x256; single-kernel
+@pytest.mark.parametrize('variant', [1, 2, 3, 4, 5])   # tcgen05 tiles 128x128, 128x256, CTA pair 256x256; single-kernel; 128x64
 def test_compensated_gemm_shapes_and_variants(cuda, mode, variant):
     ops.set_gemm_variant(variant)
     try:

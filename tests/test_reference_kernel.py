@@ -43,7 +43,7 @@ def test_reference_emitted_kernel_and_native_kernels_agree_bit_for_bit(cuda, pub
             np.testing.assert_allclose(expected, R.gemm_f64(left, right), rtol=1e-3, atol=1e-3)
             if name == 'normal':   # the reference's example inputs: its published GPU output hash
                 assert sha(expected) == published['results']['tensor_tf32x3']['output_sha256']['result']
-            for variant in (0, 1, 2, 3, 4):
+            for variant in (0, 1, 2, 3, 4, 5):
                 ops.set_gemm_variant(variant)
                 mine = ops.gemm(d_left, d_right, 'tf32x3').cpu().numpy()
                 assert np.array_equal(mine.view(np.uint32), expected.view(np.uint32)), (name, variant)
