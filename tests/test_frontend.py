@@ -299,3 +299,29 @@ def test_missing_library_fails_loudly(monkeypatch, tmp_path):
         native.lib()
     with pytest.raises(RuntimeError, match='no fallback'):
         native.call('dtn_version')
+
+
+def test_row_kernel_classification_follows_the_arithmetic_not_the_spelling():
+    """The same row kernels written with other operators (divide by the sum instead of multiply by its reciprocal,
+    divide by the norm, a plain sum instead of a sum of squares) still classify, with the program that says so."""
+    from deuteron_b200.native import ELEMENTWISE_OPS as OPS
+    graph, meta = schedules.row_softmax_example()
+    body = graph['nodes']['softmax']['op_fields']['body'][0]
+    set_body(graph, body.replace("Assign(name='probability', op=ElementwiseImpl('multiply'), args=('inverse', 'weight')",
+                                 "Assign(name='probability', op=ElementwiseImpl('divide'), args=('weight', 's')"))
+    plan = compile_kernel(graph, meta).plan
+    assert plan.params['reduce'] == 'softmax' and plan.params['n_scalar'] == 0   # the unused reciprocal is not emitted
+    assert plan.params['ops'] == [OPS['subtract'], OPS['exp'], OPS['divide']] and plan.params['b'][-1] == 1   # ... / sum of exponentials
+    graph, meta = schedules.l2_norm_example()
+    body = graph['nodes']['div']['op_fields']['body'][0].replace(
+        "Assign(name='inverse', op=ElementwiseImpl('reciprocal'), args=('norm',)", "Assign(name='inverse', op=ElementwiseImpl('copy'), args=('norm',)")
+    for lane in range(4):
+        body = body.replace(f"Assign(name='y{lane}', op=ElementwiseImpl('multiply'), args=('x{lane}', 'inverse')",
+                            f"Assign(name='y{lane}', op=ElementwiseImpl('divide'), args=('x{lane}', 'inverse')")
+    set_body(graph, body)
+    plan = compile_kernel(graph, meta).plan
+    assert plan.params['reduce'] == 'sumsq' and plan.params['ops'] == [OPS['sqrt'], OPS['divide']] and plan.params['n_scalar'] == 1
+    graph, meta = schedules.rms_norm_example()
+    set_body(graph, graph['nodes']['mul_1']['op_fields']['body'][0].replace(
+        "Assign(name='square', op=ElementwiseImpl('multiply'), args=('value', 'value'), ", "Assign(name='square', op=ElementwiseImpl('copy'), args=('value',), "))
+    assert compile_kernel(graph, meta).plan.params['reduce'] == 'sum'
