@@ -79,11 +79,16 @@ __device__ __forceinline__ bool exchange_with_peer(volatile float2* mine, volati
   const uint32_t addr = smem_u32((const void*)theirs);
   const long long start = clock64();
   while (true) {
-    float a, b;
-    asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr) : "memory");
-    if (__float_as_int(b) == seq) {
-      other = a;
-      return true;
+    // a short burst of polls between looks at the abort flag and the clock: the partner is normally a few hundred
+    // cycles away, and every instruction of this loop competes with the softmax arithmetic for issue slots
+#pragma unroll 1
+    for (int poll = 0; poll < 32; ++poll) {
+      float a, b;
+      asm volatile("ld.volatile.shared.v2.f32 {%0, %1}, [%2];" : "=f"(a), "=f"(b) : "r"(addr) : "memory");
+      if (__float_as_int(b) == seq) {
+        other = a;
+        return true;
+      }
     }
     if (*abort_flag) return false;
     if (clock64() - start > ptx::kWaitBudgetCycles) {
