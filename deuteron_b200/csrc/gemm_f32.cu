@@ -128,8 +128,79 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
   }
 }
 
+// Small products: 32x32 CTA tiles (2x2 outputs per thread, 256 threads), so that a 128^3 product runs on 16 SMs
+// instead of one. The k order per output element is the same sequential FMA chain as in the large-tile kernel, so the
+// results are bit-identical to it (and to the reference's f32 kernel).
+constexpr int FS_B = 32, FS_BK = 16;
+
+__global__ void __launch_bounds__(F_THREADS)
+gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
+                      int64_t lda, int64_t ldb, int64_t ldc) {
+  __shared__ float As[2][FS_BK][FS_B + 1];
+  __shared__ float Bs[2][FS_BK][FS_B + 1];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * FS_B, n0 = blockIdx.x * FS_B;
+  const int tx = tid & 15, ty = tid >> 4;   // 16 x 16 threads, each 2 x 2 outputs
+  // staging: 512 elements per operand tile, two per thread
+  float ra[2], rb[2];
+  auto load_tiles = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = tid + i * F_THREADS;          // 0..511
+      const int ar = v >> 4, ak = v & 15;         // A: 32 rows x 16 k, k fastest
+      ra[i] = (m0 + ar < M && k0 + ak < K) ? A[(int64_t)(m0 + ar) * lda + k0 + ak] : 0.f;
+      const int bk = v >> 5, bn = v & 31;         // B: 16 k x 32 columns, column fastest
+      rb[i] = (k0 + bk < K && n0 + bn < N) ? B[(int64_t)(k0 + bk) * ldb + n0 + bn] : 0.f;
+    }
+  };
+  auto store_tiles = [&](int buf) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = tid + i * F_THREADS;
+      As[buf][v & 15][v >> 4] = ra[i];
+      Bs[buf][v >> 5][v & 31] = rb[i];
+    }
+  };
+  float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
+  const int ktiles = (K + FS_BK - 1) / FS_BK;
+  if (ktiles > 0) {
+    load_tiles(0);
+    store_tiles(0);
+  }
+  __syncthreads();
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ktiles) load_tiles((kt + 1) * FS_BK);
+#pragma unroll
+    for (int k = 0; k < FS_BK; ++k) {
+      const float a0 = As[buf][k][ty * 2], a1 = As[buf][k][ty * 2 + 1];
+      const float b0 = Bs[buf][k][tx * 2], b1 = Bs[buf][k][tx * 2 + 1];
+      acc[0][0] = fmaf(a0, b0, acc[0][0]);
+      acc[0][1] = fmaf(a0, b1, acc[0][1]);
+      acc[1][0] = fmaf(a1, b0, acc[1][0]);
+      acc[1][1] = fmaf(a1, b1, acc[1][1]);
+    }
+    if (kt + 1 < ktiles) store_tiles(buf ^ 1);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = m0 + ty * 2 + i, c = n0 + tx * 2 + j;
+      if (r < M && c < N) C[(int64_t)r * ldc + c] = acc[i][j];
+    }
+}
+
 int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s) {
+  // fewer 128x128 tiles than a quarter of the SMs: the 32x32-tile kernel spreads the product over 16 times as many CTAs
+  if (((M + F_BM - 1) / F_BM) * ((N + F_BN - 1) / F_BN) * 4 <= (int64_t)sm_count() && (M + FS_B - 1) / FS_B <= 65535) {
+    dim3 small_grid((unsigned)((N + FS_B - 1) / FS_B), (unsigned)((M + FS_B - 1) / FS_B));
+    gemm_f32_small_kernel<<<small_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+    DTN_LAUNCH_CHECK("gemm_f32_small_kernel");
+    return DTN_OK;
+  }
   dim3 grid((unsigned)((N + F_BN - 1) / F_BN), (unsigned)((M + F_BM - 1) / F_BM));
   DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm f32: M too large");
   const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 16) && lda % 4 == 0 &&
