@@ -1,6 +1,6 @@
 """Benchmark of the hot path: compensated BF16x3 GEMM, M = N = K = 8192, FP32 in/out, on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--sweep]
 
 A step is one full pass of the hot path over one batch of seeded synthetic input: the operand
 split plus the tensor-core product kernel for C = A @ B with A, B uniform[-1, 1) (seeds 7, 11),
@@ -17,6 +17,9 @@ Printed JSON (one line, rank 0): the driver's contract keys plus
                timed region)
   extras       the other hot kernels (tf32x3 GEMM, attention, memory-bound kernels) at their
                benchmark sizes, for context
+
+`--sweep` times the mixed sweep instead (GEMMs 1024^3 ... 16384^3 and 16 x 8192 x 8192, attention at 512 ... 16384
+keys), each problem split over the ranks, and prints its own line.
 
 `--impl reference` times the reference's CPU implementation of the path (NumPy float64 product of
 the same operands, all host cores) on a bounded sample per step and prints the same line shape.
@@ -516,6 +519,159 @@ def run_ours(args) -> None:
         dist.destroy_process_group()
 
 
+SWEEP_GEMMS = ((16, 8192, 8192), (1024, 1024, 1024), (2048, 2048, 2048), (4096, 4096, 4096), (16384, 16384, 16384))   # by work
+SWEEP_ATTENTION = (512, 2048, 8192, 16384)      # batch 8, 64 query / 8 kv heads, head_dim 128, f16 storage
+
+
+def run_sweep(args) -> None:
+    """The mixed sweep of the largest configuration, each problem split over the ranks (strong scaling): a GEMM by
+    output column blocks, an attention forward by (batch, kv-head) groups; N(0,1) inputs from fixed seeds.
+
+    Every launch is timed with its own pair of events on the launching stream; a 512 MiB buffer is overwritten
+    between launches so that no problem starts with its operands in L2. The figure of a problem is the median over
+    its launches, maximum over ranks; rank 0 prints one JSON line.
+    """
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    if not torch.cuda.is_available():
+        raise SystemExit('bench.py needs a CUDA device: the kernels have no CPU path')
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    if world > 1:
+        dist.init_process_group('nccl', device_id=device)
+    from deuteron_b200 import native, ops, sharding
+    native.lib()
+    peaks = measured_peaks()
+    flush = torch.empty(512 << 20, dtype=torch.uint8, device=device)
+    generator = torch.Generator(device=device)
+
+    def normal(seed: int, shape, scale: float = 1.0):
+        generator.manual_seed(seed)
+        return torch.randn(shape, device=device, generator=generator) * scale
+
+    def measure(make, budget_ms: float) -> tuple[float, bool]:
+        """Median milliseconds per launch of the callable `make()` builds (0 when this rank owns nothing), and whether
+        anything failed on this rank. Never raises: every rank must reach the collectives that follow."""
+        try:
+            call = make()
+            if call is None:
+                return 0.0, False
+            for _ in range(3):
+                call()
+            torch.cuda.synchronize()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            call()
+            end.record()
+            end.synchronize()
+            launches = int(max(3, min(30, budget_ms / max(begin.elapsed_time(end), 1e-3))))
+            samples = []
+            for _ in range(launches):
+                flush.fill_(1)
+                begin.record()
+                call()
+                end.record()
+                end.synchronize()
+                samples.append(begin.elapsed_time(end))
+            ops.check_device_status()
+            return statistics.median(samples), False
+        except Exception as error:   # noqa: BLE001 - reported in the line
+            print(f'rank {rank}: sweep item failed: {error}', file=sys.stderr)
+            return 0.0, True
+
+    def over_ranks(ms: float, failed: bool) -> tuple[float, bool]:
+        if world == 1:
+            return ms, failed
+        gathered = torch.tensor([ms, float(failed)], device=device)
+        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+        return float(gathered[0].item()), float(gathered[1].item()) > 0
+
+    sampler = ClockSampler(local_rank)
+    wall_begin = time.perf_counter()
+    if rank == 0:
+        sampler.start()
+    items, launches_total = [], 0
+    for mode, peak in (('bf16x3', peaks['bf16_tflops'] / 3.0), ('tf32x3', None)):
+        for m, n, k in SWEEP_GEMMS:
+            begin_col, end_col = sharding.column_blocks(n, world)[rank]
+            holder = {}
+
+            def make(m=m, k=k, width=end_col - begin_col, mode=mode, holder=holder):
+                if width == 0:
+                    return None
+                holder['a'], holder['b'] = normal(7, (m, k)), normal(11 + rank, (k, width))
+                holder['c'] = torch.empty((m, width), device=device)
+                return lambda: ops.gemm(holder['a'], holder['b'], mode, out=holder['c'])
+
+            ms, failed = over_ranks(*measure(make, 300.0))
+            holder.clear()
+            torch.cuda.empty_cache()
+            item = {'kernel': f'gemm_{mode}', 'm': m, 'n': n, 'k': k, 'columns_per_rank': end_col - begin_col if world > 1 else n}
+            if failed or ms <= 0:
+                item['error'] = 'a rank failed; see stderr'
+            else:
+                tflops = 2.0 * m * n * k / ms / 1e9
+                item.update(ms=ms, tflops_aggregate=tflops)
+                if m <= 16:
+                    item['b_gbs_aggregate'] = 4.0 * n * k / ms / 1e6
+                    item['frac_of_hbm_peak_per_gpu'] = 4.0 * n * k / ms / 1e6 / world / peaks['hbm_gbs']
+                elif peak is not None:
+                    item['frac_of_bf16_peak_over_3_per_gpu'] = tflops / world / peak
+                    item['frac_of_sustained_bf16_peak_over_3_per_gpu'] = tflops / world / (peaks['bf16_tflops_sustained'] / 3.0)
+            items.append(item)
+    batch, hq, hkv, d = 8, 64, 8, 128
+    for s in SWEEP_ATTENTION:
+        groups = sharding.group_range(batch * hkv, world, rank)
+        holder = {}
+
+        def make(s=s, groups=groups, holder=holder):
+            if groups[1] == groups[0]:
+                return None
+            holder['q'] = normal(7, (batch, hq, s, d)).half()
+            holder['k'] = normal(8, (batch, hkv, s, d)).half()
+            holder['v'] = normal(9, (batch, hkv, s, d)).half()
+            holder['o'] = torch.empty((batch, hq, s, d), device=device)
+            return lambda: ops.gqa_attention(holder['q'], holder['k'], holder['v'], d ** -0.5, out=holder['o'], groups=groups)
+
+        ms, failed = over_ranks(*measure(make, 400.0))
+        holder.clear()
+        torch.cuda.empty_cache()
+        item = {'kernel': 'gqa_fwd_f16', 'batch': batch, 'q_heads': hq, 'kv_heads': hkv, 'seq_len': s, 'head_dim': d,
+                'groups_per_rank': groups[1] - groups[0]}
+        if failed or ms <= 0:
+            item['error'] = 'a rank failed; see stderr'
+        else:
+            tflops = 4.0 * batch * hq * s * s * d / ms / 1e9
+            item.update(ms=ms, tflops_aggregate=tflops, frac_of_bf16_peak_per_gpu=tflops / world / peaks['bf16_tflops'],
+                        frac_of_sustained_bf16_peak_per_gpu=tflops / world / peaks['bf16_tflops_sustained'])
+        items.append(item)
+    torch.cuda.synchronize()
+    wall_end = time.perf_counter()
+    if rank == 0:
+        line = {'metric': 'mixed_sweep', 'n_gpus': world, 'scaling': 'strong', 'data': 'synthetic', 'unit': 'TFLOP/s',
+                'config': {'workload': 'mixed_sweep_gemm_1024_2048_4096_16384_skinny16_attention_512_2048_8192_16384',
+                           'inputs': 'N(0,1), seeds 7 / 11+rank (GEMM), 7 / 8 / 9 (attention, f16 storage)',
+                           'parallelism': f'each problem split x{world}: GEMM by output column blocks, attention by (batch, kv-head) groups; no collective',
+                           'l2': '512 MiB written between launches', 'timing': 'median over launches, maximum over ranks'},
+                'peaks': {'bf16_tflops': peaks['bf16_tflops'], 'bf16_tflops_sustained': peaks['bf16_tflops_sustained'],
+                          'hbm_gbs': peaks['hbm_gbs'], 'source': peaks['source'],
+                          'note': 'launches of tens of milliseconds run at the clocks of the power cap: compare them with the sustained peak'},
+                'clocks': sampler.stop(wall_begin, wall_end), 'items': items}
+        sys.stdout.flush()
+        os.dup2(json_fd, 1)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'gemm_skinny', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max',
                  'row_softmax', 'rms_norm', 'fused_affine')
 
@@ -586,6 +742,7 @@ def main() -> None:
     parser.add_argument('--impl', choices=('ours', 'reference'), default='ours')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-extras', action='store_true')
+    parser.add_argument('--sweep', action='store_true', help='time the mixed sweep of GEMM and attention sizes, each split over the ranks')
     args = parser.parse_args()
     if args.steps < 1 or args.warmup < 0:
         raise SystemExit('steps must be positive and warmup nonnegative')
@@ -601,6 +758,9 @@ def main() -> None:
         command = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={args.gpus}',
                    '--master-addr', '127.0.0.1', '--master-port', '29511', __file__, *sys.argv[1:]]
         raise SystemExit(subprocess.call(command))
+    if args.sweep:
+        run_sweep(args)
+        return
     run_ours(args)
 
 

@@ -29,6 +29,9 @@ int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s);
 int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                       int64_t ldb, int64_t ldc, cudaStream_t s);
+bool gemm_fused_supported(int mode, const float* A, const float* B, int64_t N, int64_t K, int64_t lda, int64_t ldb);
+int gemm_fused_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                      int64_t ldb, int64_t ldc, cudaStream_t s, int bn);
 
 // Problems for which the single-kernel path (operand split inside the kernel, no workspace) is
 // faster than split pass + tcgen05 kernel: so little work that launches and set-up dominate
@@ -770,7 +773,7 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
 }
 
 int dtn_gemm_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 5, DTN_ERR_INVALID, "gemm: variant must be 0..5");
+  DTN_REQUIRE(variant >= 0 && variant <= 6, DTN_ERR_INVALID, "gemm: variant must be 0..6");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
 }
@@ -813,6 +816,11 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   if (phase == 3 && (g_gemm_variant == 4 || (g_gemm_variant == 0 && prefers_small_kernel(M, N, K))))
     return gemm_small_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s);
   DTN_REQUIRE(g_gemm_variant != 4, DTN_ERR_INVALID, "gemm: the single-kernel variant has no separate phases");
+  if (phase == 3 && g_gemm_variant == 6) {
+    const char* bn = getenv("DTN_GEMM_FUSED_BN");
+    return gemm_fused_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s, bn ? atoi(bn) : 0);
+  }
+  DTN_REQUIRE(g_gemm_variant != 6, DTN_ERR_INVALID, "gemm: the fused-split variant has no separate phases");
 
   const PlaneLayout L = plane_layout(mode, M, N, K);
   DTN_REQUIRE(workspace != nullptr && workspace_bytes >= L.total, DTN_ERR_WORKSPACE,

@@ -142,5 +142,5 @@ def device_status(stream: int = 0) -> int:
 def raise_on_device_status(stream: int = 0) -> None:
     status = device_status(stream)
     if status:
-        role = {0x71: 'bounded-wait self-test', 0x11: 'attention K loader', 0x12: 'attention V loader', 0x13: 'attention Q loader', 0x31: 'attention softmax (scores)', 0x32: 'attention output', 0x33: 'attention softmax (row exchange)', 0x21: 'attention MMA issuer (queries)', 0x23: 'attention MMA issuer (values)', 0x24: 'attention MMA issuer (probabilities)', 0x25: 'attention MMA issuer (keys)', 0x26: 'attention MMA issuer (probabilities)', 1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
+        role = {0x71: 'bounded-wait self-test', 0x11: 'attention K loader', 0x12: 'attention V loader', 0x13: 'attention Q loader', 0x31: 'attention softmax (scores)', 0x32: 'attention output', 0x33: 'attention softmax (row exchange)', 0x21: 'attention MMA issuer (queries)', 0x23: 'attention MMA issuer (values)', 0x24: 'attention MMA issuer (probabilities)', 0x25: 'attention MMA issuer (keys)', 0x26: 'attention MMA issuer (probabilities)', 0x51: 'fused-split GEMM producers', 0x52: 'fused-split GEMM MMA issuer', 0x53: 'fused-split GEMM epilogue', 1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
         raise DeviceWaitError(f'bounded wait ran out in the {role}, CTA {status & 0xff} (status {status:#x})')

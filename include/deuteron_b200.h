@@ -217,7 +217,9 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
  *   4 = the single-kernel path for small problems (operand split inside the kernel, warp-level
  *   mma.sync products, no workspace; what automatic picks up to about 520^3 multiply-adds and for
  *   at most 16 rows), 5 = one-CTA 128x64 tile (automatic when 128x128 tiles would occupy at most
- *   half of the SMs).
+ *   half of the SMs), 6 = one tcgen05 kernel with the operand split in its producer warps (no
+ *   workspace, one launch; bf16x3 with 16-byte aligned A and B, lda and ldb multiples of 4, N and
+ *   K multiples of 8, else DTN_ERR_UNSUPPORTED).
  * No reference counterpart. */
 int dtn_gemm_set_variant(int variant);
 

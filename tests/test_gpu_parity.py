@@ -434,6 +434,46 @@ def test_compensated_gemm_shapes_and_variants(cuda, mode, variant):
         ops.set_gemm_variant(0)
 
 
+FUSED_SHAPES = [(128, 128, 128), (256, 256, 64), (384, 768, 1000), (200, 136, 80), (16, 512, 512), (1, 8, 8), (129, 264, 72),
+                (1024, 1024, 1024), (2048, 1536, 1280)]
+
+
+@pytest.mark.parametrize('tile_width', ['64', '128'])
+def test_fused_split_gemm_reproduces_the_two_kernel_path(cuda, monkeypatch, published, tile_width):
+    # One tcgen05 kernel with the operand split in its producer warps: the same rounded operands, the same three
+    # products in the same order, so the output is the two-kernel path's bit for bit -- at every shape it accepts,
+    # with row, column and k remainders, at both tile widths -- and the reference's published 128^3 output.
+    monkeypatch.setenv('DTN_GEMM_FUSED_BN', tile_width)
+    try:
+        for m, n, k in FUSED_SHAPES:
+            a, b = to_device(cuda, R.seeded_uniform(7, (m, k))), to_device(cuda, R.seeded_uniform(11, (k, n)))
+            ops.set_gemm_variant(1)
+            expected = ops.gemm(a, b, 'bf16x3').cpu().numpy()
+            ops.set_gemm_variant(6)
+            produced = ops.gemm(a, b, 'bf16x3').cpu().numpy()
+            ops.check_device_status()
+            assert np.array_equal(produced, expected), (m, n, k)
+        # a column block of a wider matrix, written into a column block of a wider result (leading dimensions > extents)
+        a = to_device(cuda, R.seeded_uniform(7, (512, 768)))
+        b = to_device(cuda, R.seeded_uniform(11, (768, 1024)))
+        c = cuda.zeros((512, 1024), device='cuda:0')
+        ops.gemm(a, b[:, 256:640], 'bf16x3', out=c[:, 256:640])
+        ops.set_gemm_variant(1)
+        assert cuda.equal(c[:, 256:640], ops.gemm(a, b[:, 256:640].contiguous(), 'bf16x3'))
+        assert float(c[:, :256].abs().max()) == 0 and float(c[:, 640:].abs().max()) == 0
+        ops.set_gemm_variant(6)
+        left, right = R.seeded_normal(7, (128, 128)), R.seeded_normal(11, (128, 128))
+        produced = ops.gemm(to_device(cuda, left), to_device(cuda, right), 'bf16x3').cpu().numpy()
+        assert sha(produced) == published['results']['tensor_bf16x3']['output_sha256']['result']
+        # shapes and modes it does not take are refused, not routed elsewhere
+        with pytest.raises(Exception, match='fused-split'):
+            ops.gemm(to_device(cuda, R.seeded_uniform(7, (64, 77))), to_device(cuda, R.seeded_uniform(11, (77, 64))), 'bf16x3')
+        with pytest.raises(Exception, match='fused-split'):
+            ops.gemm(to_device(cuda, left), to_device(cuda, right), 'tf32x3')
+    finally:
+        ops.set_gemm_variant(0)
+
+
 def test_gemm_f32_mode_shapes(cuda):
     for m, n, k in SHAPES[:-1]:
         a, b = R.seeded_normal(7, (m, k)), R.seeded_normal(11, (k, n))
