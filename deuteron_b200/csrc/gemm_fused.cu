@@ -12,18 +12,20 @@
 // products per k-step in the usual order (lo*hi, hi*lo, hi*hi); the producer warps read the
 // accumulator back and store C at the end. One output tile per CTA.
 //
-// This form is not used for large problems: a 256 x 256 CTA-pair tile already reads its operands at
-// 94 of the 128 bytes per clock shared memory delivers, and the producers' 64 KiB of stores per
-// k-block would push it past that.
+// Measured on B200 it only matches the two-kernel path up to 1024^3 (18.2 against 17.1 us) and loses beyond
+// (2048^3: 84 against 48 us): with one 128 x 64 or 128 x 128 tile per CTA the operands are re-read from L2
+// 16 to 32 times, FP32 operands are as many bytes as the two bf16 planes, and the run time is those bytes at
+// about 6.4 TB/s. Larger tiles cannot take the split in: a 256 x 256 CTA-pair tile already reads its operands
+// at 94 of the 128 bytes per clock shared memory delivers, and the producers' 64 KiB of stores per k-block
+// would push it past that. The kernel therefore stays an explicit variant (one launch, no workspace).
 #include "sm100_ptx.cuh"
 
 namespace dtn {
 
-constexpr int F_PRODUCER_WARPS = 8;
-constexpr int F_THREADS = (F_PRODUCER_WARPS + 1) * 32;   // warps 0-7: producers, then epilogue; warp 8: MMA issue, tensor memory
-
-template <int BN>
+// PW producer warps (8 or 16), which also run the epilogue, then one warp that issues the products and owns the tensor memory.
+template <int BN, int PW>
 struct FusedCfg {
+  static constexpr int kThreads = (PW + 1) * 32;
   static constexpr int kBK = 64;                             // k per k-block = bf16 elements per 128-byte row of A
   static constexpr int kPer16 = 8;                           // operand elements per 16-byte piece
   static constexpr int kNBlock = 64;                         // n per 128-byte row of B
@@ -32,8 +34,8 @@ struct FusedCfg {
   static constexpr int kBBytes = (BN / kNBlock) * kBBlockBytes;
   static constexpr int kStageBytes = 2 * kABytes + 2 * kBBytes;
   static constexpr int kStages = (192 * 1024) / kStageBytes > 4 ? 4 : (192 * 1024) / kStageBytes;
-  static constexpr int kAUnits = 128 * 8 / (F_PRODUCER_WARPS * 32);              // 16-byte pieces of A per thread and k-block
-  static constexpr int kBUnits = kBK * (BN / kPer16) / (F_PRODUCER_WARPS * 32);  // of B
+  static constexpr int kAUnits = 128 * 8 / (PW * 32);              // 16-byte pieces of A per thread and k-block
+  static constexpr int kBUnits = kBK * (BN / kPer16) / (PW * 32);  // of B
   static constexpr int kBarrierBytes = 256;
   static constexpr int kSmemBytes = kStages * kStageBytes + kBarrierBytes + 1024;
   static_assert(BN == 64 || BN == 128, "tile width");
@@ -74,13 +76,13 @@ __device__ __forceinline__ void fused_split_piece(const float4 (&v)[2], uint4& h
   fused_split_bf16(v[1].z, v[1].w, hi.w, lo.w);
 }
 
-template <int BN>
-__global__ void __launch_bounds__(F_THREADS, 1)
+template <int BN, int PW>
+__global__ void __launch_bounds__((PW + 1) * 32, 1)
 gemm_x3_fused_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                      int64_t lda, int64_t ldb, int64_t ldc, int c_vec_ok, int* __restrict__ status) {
-  using Cfg = FusedCfg<BN>;
+  using Cfg = FusedCfg<BN, PW>;
   constexpr int kStages = Cfg::kStages, BK = Cfg::kBK, P16 = Cfg::kPer16, V = P16 / 4;
-  constexpr int kProducerThreads = F_PRODUCER_WARPS * 32;
+  constexpr int kProducerThreads = PW * 32;
   constexpr int kBPiecesPerRow = BN / P16;
   constexpr uint32_t kIdesc = ptx::umma_idesc(1, 128, BN) | (1u << 16);   // bf16 operands, B MN-major
 
@@ -103,13 +105,13 @@ gemm_x3_fused_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   if (tid == 0) {
     *abort_flag = 0;
     for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(full_bar(s), F_PRODUCER_WARPS);
+      ptx::mbar_init(full_bar(s), PW);
       ptx::mbar_init(empty_bar(s), 1);
     }
     ptx::mbar_init(done_bar, 1);
     ptx::mbar_fence_init();
   }
-  if (warp == F_PRODUCER_WARPS) {
+  if (warp == PW) {
     ptx::tmem_alloc<1>(smem_u32(tmem_holder), BN);
     ptx::tmem_relinquish<1>();
   }
@@ -118,7 +120,7 @@ gemm_x3_fused_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
-  if (warp < F_PRODUCER_WARPS) {
+  if (warp < PW) {
     // ------------------------------- producers ----------------------------------------------
     // Piece u of a tile belongs to thread u % 256. A: row u / 8, piece u % 8 of the row's eight. B: k row
     // u / kBPiecesPerRow, piece u % kBPiecesPerRow along n. Eight (A) or kBPiecesPerRow (B) neighbouring threads read
@@ -203,11 +205,11 @@ gemm_x3_fused_kernel(const float* __restrict__ A, const float* __restrict__ B, f
       if (lane == 0 && ok) atomicExch(status, 0x5300 | (int)(blockIdx.x & 0xff));
     } else {
       ptx::tc_fence_after();
-      const int quarter = warp & 3, half = warp >> 2;   // tensor-memory lanes [32 * quarter, +32), columns [half * BN / 2, +BN / 2)
+      const int quarter = warp & 3, part = warp >> 2;   // tensor-memory lanes [32 * quarter, +32); 32-column chunks part, part + PW / 4, ...
       const int row = m0 + quarter * 32 + lane;
       float* crow = C + (int64_t)row * ldc + n0;
 #pragma unroll 1
-      for (int c = half * (BN / 64); c < (half + 1) * (BN / 64); ++c) {
+      for (int c = part; c < BN / 32; c += PW / 4) {
         uint32_t r[32];
         ptx::tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(c * 32), r);
         ptx::tmem_ld_wait();
@@ -261,17 +263,17 @@ gemm_x3_fused_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     for (int i = 0; i < 64; ++i) __nanosleep(1000);
     __syncthreads();
   }
-  if (warp == F_PRODUCER_WARPS) {
+  if (warp == PW) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc<1>(tmem_base, BN);
   }
 }
 
-template <int BN>
+template <int BN, int PW>
 static int launch_fused(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                         int64_t ldc, cudaStream_t s) {
-  using Cfg = FusedCfg<BN>;
-  auto kernel = gemm_x3_fused_kernel<BN>;
+  using Cfg = FusedCfg<BN, PW>;
+  auto kernel = gemm_x3_fused_kernel<BN, PW>;
   static thread_local int attr_dev = -1;
   int dev = 0;
   DTN_CUDA_CHECK(cudaGetDevice(&dev));
@@ -284,7 +286,7 @@ static int launch_fused(const float* A, const float* B, float* C, int64_t M, int
   const dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)((M + 127) / 128));
   DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm: M too large for the fused-split kernel");
   const int c_vec_ok = aligned_to(C, 16) && (ldc % 4 == 0);
-  kernel<<<grid, F_THREADS, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc, c_vec_ok, status);
+  kernel<<<grid, Cfg::kThreads, Cfg::kSmemBytes, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc, c_vec_ok, status);
   DTN_LAUNCH_CHECK("gemm_x3_fused_kernel");
   return DTN_OK;
 }
@@ -303,7 +305,8 @@ int gemm_fused_launch(int mode, const float* A, const float* B, float* C, int64_
               "gemm: the fused-split kernel takes bf16x3 with 16-byte aligned A and B, leading dimensions that are multiples "
               "of 4 and N, K multiples of 8");
   if (bn == 0) bn = ((M + 127) / 128) * ((N + 127) / 128) >= sm_count() ? 128 : 64;
-  return bn == 128 ? launch_fused<128>(A, B, C, M, N, K, lda, ldb, ldc, s) : launch_fused<64>(A, B, C, M, N, K, lda, ldb, ldc, s);
+  // sixteen producer warps for the wide tile (measured 84 against 144 us at 2048^3), eight for the narrow one (no difference)
+  return bn == 128 ? launch_fused<128, 16>(A, B, C, M, N, K, lda, ldb, ldc, s) : launch_fused<64, 8>(A, B, C, M, N, K, lda, ldb, ldc, s);
 }
 
 }  // namespace dtn

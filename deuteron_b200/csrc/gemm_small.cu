@@ -52,11 +52,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
   __nv_bfloat162 v = __floats2bfloat162_rn(low, high);   // .x (low half) = first k index
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// hi = bf16_rn(v) pairs, lo = bf16_rn(v - hi) pairs
+// hi = bf16_rn(v) pairs, lo = bf16_rn(v - hi) pairs. One conversion rounds both values; the rounded values come back
+// as FP32 by a shift and a mask (a bf16 is the upper half of an FP32).
 __device__ __forceinline__ void split_bf16_pair(float a, float b, uint32_t& hi, uint32_t& lo) {
-  const __nv_bfloat16 ha = __float2bfloat16_rn(a), hb = __float2bfloat16_rn(b);
-  hi = pack_bf16(__bfloat162float(ha), __bfloat162float(hb));
-  lo = pack_bf16(a - __bfloat162float(ha), b - __bfloat162float(hb));
+  hi = pack_bf16(a, b);
+  lo = pack_bf16(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xffff0000u));
 }
 __device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
@@ -92,6 +92,11 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   const int wm = BM == 64 ? (warp >> 1) * 32 : (BM == 32 ? (warp >> 1) * 16 : 0), wn = BM == 16 ? warp * 16 : (warp & 1) * 32;
   const uint32_t smem_base = smem_u32(small_smem);
 
+  const int b_piece_n = (tid & 15) * 4;
+  const int b_col_bytes = min(max((N - (n0 + b_piece_n)) * 4, 0), 16);
+  const float* b_col = B + n0 + b_piece_n;
+  const uint32_t b_piece_smem = (uint32_t)b_piece_n * 4u;
+  static_assert((BK * 16) % (S_THREADS * KSPLIT) == 0, "B tile must divide among the threads");
   auto load_tile = [&](int kt, int slot) {
     const int k0 = kt * BK;
     const uint32_t a_s = smem_base + (uint32_t)(slot * Cfg::kStageFloats) * 4u;
@@ -99,24 +104,24 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     if constexpr (ALIGNED) {
       constexpr int kAPerRow = BK / 4;                  // 16-byte pieces per A row
 #pragma unroll
-      for (int v = tid; v < BM * kAPerRow; v += kThreads) {
+      for (int v = tid; v < (MODE == 0 ? 0 : BM * kAPerRow); v += kThreads) {
         const int ar = v / kAPerRow, ak = (v % kAPerRow) * 4;
         const int gr = m0 + ar, gk = k0 + ak;
         int bytes = (gr < M) ? (K - gk) * 4 : 0;
         bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
         cp_async_16(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, bytes ? (const void*)(A + (int64_t)gr * lda + gk) : (const void*)A, bytes);
       }
+      // B: BK rows x 16 pieces; a thread always copies the same piece of a row (column offset, byte count and
+      // the shared-memory column are fixed), only the row moves
 #pragma unroll
-      for (int v = tid; v < BK * 16; v += kThreads) {  // B: BK rows x 16 pieces
-        const int br = v >> 4, bn = (v & 15) * 4;
-        const int gkb = k0 + br, gn = n0 + bn;
-        int bbytes = (gkb < K) ? (N - gn) * 4 : 0;
-        bbytes = bbytes < 0 ? 0 : (bbytes > 16 ? 16 : bbytes);
-        cp_async_16(b_s + (uint32_t)(br * Cfg::kLdb + bn) * 4u, bbytes ? (const void*)(B + (int64_t)gkb * ldb + gn) : (const void*)B, bbytes);
+      for (int i = 0; i < BK * 16 / kThreads; ++i) {
+        const int br = (tid >> 4) + i * (kThreads >> 4);
+        const int bbytes = (k0 + br < K) ? b_col_bytes : 0;
+        cp_async_16(b_s + b_piece_smem + (uint32_t)(br * Cfg::kLdb) * 4u, bbytes ? (const void*)(b_col + (int64_t)(k0 + br) * ldb) : (const void*)B, bbytes);
       }
     } else {
 #pragma unroll 4
-      for (int v = tid; v < BM * BK; v += kThreads) {
+      for (int v = tid; v < (MODE == 0 ? 0 : BM * BK); v += kThreads) {
         const int ar = v / BK, ak = v % BK;
         const bool ain = (m0 + ar < M) && (k0 + ak < K);
         cp_async_4(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, ain ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, ain ? 4 : 0);
@@ -127,6 +132,44 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
         const bool bin = (k0 + br < K) && (n0 + bn < N);
         cp_async_4(b_s + (uint32_t)(br * Cfg::kLdb + bn) * 4u, bin ? (const void*)(B + (int64_t)(k0 + br) * ldb + n0 + bn) : (const void*)B, bin ? 4 : 0);
       }
+    }
+  };
+
+  // bf16x3: the A tile does not go through the copy ring. Every warp of a k group needs the same A fragments, so
+  // splitting them after the fragment read would repeat the conversion once per warp; instead each thread reads its
+  // share of the tile one k-tile ahead, splits it once and writes the high and residual planes (packed pairs,
+  // [BM][BK + 8] bf16 each) where the FP32 tile would have been. Same arithmetic, same operands.
+  constexpr int kAVecs = (BM * BK / 4) / kThreads;   // float4 of the A tile per thread
+  static_assert(MODE != 0 || (BM * BK / 4) % kThreads == 0, "A tile must divide among the threads");
+  auto load_a = [&](int kt, float4 (&r)[kAVecs > 0 ? kAVecs : 1]) {
+    const int k0 = kt * BK;
+#pragma unroll
+    for (int i = 0; i < kAVecs; ++i) {
+      const int v = i * kThreads + tid, ar = v / (BK / 4), ak = (v % (BK / 4)) * 4;
+      const int gr = m0 + ar, gk = k0 + ak;
+      const float* p = A + (int64_t)gr * lda + gk;
+      if (ALIGNED && gr < M && gk + 3 < K) {
+        r[i] = __ldg(reinterpret_cast<const float4*>(p));
+      } else {
+        const bool row_in = gr < M;
+        r[i].x = (row_in && gk < K) ? __ldg(p) : 0.f;
+        r[i].y = (row_in && gk + 1 < K) ? __ldg(p + 1) : 0.f;
+        r[i].z = (row_in && gk + 2 < K) ? __ldg(p + 2) : 0.f;
+        r[i].w = (row_in && gk + 3 < K) ? __ldg(p + 3) : 0.f;
+      }
+    }
+  };
+  auto store_a = [&](int slot, const float4 (&r)[kAVecs > 0 ? kAVecs : 1]) {
+    uint32_t* hi_plane = reinterpret_cast<uint32_t*>(small_smem + slot * Cfg::kStageFloats);
+    uint32_t* lo_plane = hi_plane + BM * Cfg::kLda / 2;
+#pragma unroll
+    for (int i = 0; i < kAVecs; ++i) {
+      const int v = i * kThreads + tid, ar = v / (BK / 4), ak = (v % (BK / 4)) * 4;
+      uint2 hi, lo;
+      split_bf16_pair(r[i].x, r[i].y, hi.x, lo.x);
+      split_bf16_pair(r[i].z, r[i].w, hi.y, lo.y);
+      *reinterpret_cast<uint2*>(hi_plane + (ar * Cfg::kLda + ak) / 2) = hi;
+      *reinterpret_cast<uint2*>(lo_plane + (ar * Cfg::kLda + ak) / 2) = lo;
     }
   };
 
@@ -149,11 +192,25 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     if (s < ktiles) load_tile(kt_first + s, s);
     cp_async_commit();
   }
+  float4 a_next[kAVecs > 0 ? kAVecs : 1];   // A of k-tile kt + 1, read during k-tile kt
+  if constexpr (MODE == 0) {
+    if (ktiles > 0) {
+      load_a(kt_first, a_next);
+      store_a(0, a_next);
+    }
+    if (ktiles > 1) load_a(kt_first + 1, a_next);
+  }
   for (int kt = 0; kt < ktiles; ++kt) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
     if (kt + STAGES - 1 < ktiles) load_tile(kt_first + kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
+    if constexpr (MODE == 0) {
+      // The slot of k-tile kt + 1 was last read STAGES - 1 k-tiles ago; its A planes are written here, before the
+      // barrier that opens k-tile kt + 1, and the tile after that is requested.
+      if (kt + 1 < ktiles) store_a((kt + 1) % STAGES, a_next);
+      if (kt + 2 < ktiles) load_a(kt_first + kt + 2, a_next);
+    }
     const float* As = small_smem + (kt % STAGES) * Cfg::kStageFloats;
     const float* Bs = As + BM * Cfg::kLda;
     if constexpr (MODE == 0) {
@@ -162,15 +219,16 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
         uint32_t a_hi[MI][4], a_lo[MI][4];
 #pragma unroll
         for (int i = 0; i < MI; ++i) {
-          const float* ap = As + (wm + i * 16 + g) * Cfg::kLda + kk + 2 * t;
-          const float2 v0 = *reinterpret_cast<const float2*>(ap);                      // row g,   k 2t..
-          const float2 v1 = *reinterpret_cast<const float2*>(ap + 8 * Cfg::kLda);      // row g+8
-          const float2 v2 = *reinterpret_cast<const float2*>(ap + 8);                  // row g,   k 2t+8..
-          const float2 v3 = *reinterpret_cast<const float2*>(ap + 8 * Cfg::kLda + 8);  // row g+8
-          split_bf16_pair(v0.x, v0.y, a_hi[i][0], a_lo[i][0]);
-          split_bf16_pair(v1.x, v1.y, a_hi[i][1], a_lo[i][1]);
-          split_bf16_pair(v2.x, v2.y, a_hi[i][2], a_lo[i][2]);
-          split_bf16_pair(v3.x, v3.y, a_hi[i][3], a_lo[i][3]);
+          const uint32_t* hp = reinterpret_cast<const uint32_t*>(As) + ((wm + i * 16 + g) * Cfg::kLda + kk + 2 * t) / 2;
+          const uint32_t* lp = hp + BM * Cfg::kLda / 2;
+          a_hi[i][0] = hp[0];                      // row g,   k 2t, 2t+1
+          a_hi[i][1] = hp[4 * Cfg::kLda];          // row g+8
+          a_hi[i][2] = hp[4];                      // row g,   k 2t+8, 2t+9
+          a_hi[i][3] = hp[4 * Cfg::kLda + 4];      // row g+8
+          a_lo[i][0] = lp[0];
+          a_lo[i][1] = lp[4 * Cfg::kLda];
+          a_lo[i][2] = lp[4];
+          a_lo[i][3] = lp[4 * Cfg::kLda + 4];
         }
 #pragma unroll
         for (int j = 0; j < NI; ++j) {
@@ -332,12 +390,13 @@ static int gemm_small_launch_mode(const float* A, const float* B, float* C, int6
                                   int64_t ldb, int64_t ldc, cudaStream_t s) {
   const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 8) && lda % 4 == 0 && ldb % 4 == 0 && ldc % 2 == 0;
   static const int forced = [] {
-    const char* text = getenv("DTN_GEMM_SMALL_CFG");   // tuning aid: 1..7 pick a configuration, anything else = automatic
+    const char* text = getenv("DTN_GEMM_SMALL_CFG");   // tuning aid: 1..8 pick a configuration, anything else = automatic
     return text ? atoi(text) : 0;
   }();
-#define DTN_SMALL_CFG(BM, BK, KS)                                                                                     \
-  return aligned ? gemm_small_launch_cfg<MODE, true, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)       \
-                 : gemm_small_launch_cfg<MODE, false, BM, BK, 4, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)
+#define DTN_SMALL_CFG_ST(BM, BK, KS, ST)                                                                              \
+  return aligned ? gemm_small_launch_cfg<MODE, true, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)      \
+                 : gemm_small_launch_cfg<MODE, false, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)
+#define DTN_SMALL_CFG(BM, BK, KS) DTN_SMALL_CFG_ST(BM, BK, KS, 4)
   // Skinny products have too few output tiles to fill the device (128 for N = 8192): clusters of CTAs along k share a
   // tile. DTN_GEMM_SKINNY_KPARTS overrides the count (1, 2 or 4).
   static const int forced_parts = [] {
@@ -349,10 +408,10 @@ static int gemm_small_launch_mode(const float* A, const float* B, float* C, int6
     const int64_t tiles = (N + S_BN - 1) / S_BN;
     k_parts = tiles * 2 <= (int64_t)sm_count() * 2 ? 2 : 1;
     if (tiles * 4 <= (int64_t)sm_count() * 2) k_parts = 4;
-    if (forced_parts == 1 || forced_parts == 2 || forced_parts == 4) k_parts = forced_parts;
+    if (forced_parts >= 1 && forced_parts <= 4) k_parts = forced_parts;
   }
   int choice = forced;
-  if (choice < 1 || choice > 7) {
+  if (choice < 1 || choice > 8) {
     // Measured on B200 (us, bf16x3): 128^3 3.1 with 16-row tiles against 5.2 with 64-row tiles, 128x64x256 4.8 / 8.5,
     // 256^3 5.2 / 8.8, 512^3 10.4 (32-row tiles, two k groups) / 15.5, 16x8192x8192 95 (two k groups) / 215.
     // The 16-row single-group configuration keeps the sequential-k accumulation order, so small products stay
@@ -370,9 +429,11 @@ static int gemm_small_launch_mode(const float* A, const float* B, float* C, int6
     case 5: DTN_SMALL_CFG(32, 64, 1);
     case 6: DTN_SMALL_CFG(32, 64, 2);
     case 7: DTN_SMALL_CFG(16, 32, 1);
+    case 8: DTN_SMALL_CFG_ST(16, 64, 2, 3);
     default: DTN_SMALL_CFG(64, 32, 1);
   }
 #undef DTN_SMALL_CFG
+#undef DTN_SMALL_CFG_ST
 }
 
 // mode: DTN_GEMM_BF16X3 or DTN_GEMM_TF32X3
