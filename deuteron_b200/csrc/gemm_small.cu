@@ -27,7 +27,8 @@ struct SmallCfg {
   // leading dimensions chosen so that the fragment reads below are bank-conflict free
   static constexpr int kLda = (MODE == 0) ? BK + 8 : BK + 4;   // A tile [BM][kLda]
   static constexpr int kLdb = (MODE == 0) ? 68 : 72;           // B tile [BK][kLdb]
-  static constexpr int kStageFloats = BM * kLda + BK * kLdb;
+  static constexpr int kAFloats = (MODE == 0 ? 1 : 2) * BM * kLda;   // high and residual plane of the A tile (bf16 pairs / tf32 words)
+  static constexpr int kStageFloats = kAFloats + BK * kLdb;
   static constexpr int kSmemBytes = STAGES * kStageFloats * 4;
   static constexpr int kMI = BM == 64 ? 2 : 1;                 // m16 tiles per warp
   static constexpr int kNI = BM == 16 ? 2 : 4;                 // n8 tiles per warp
@@ -100,17 +101,8 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   auto load_tile = [&](int kt, int slot) {
     const int k0 = kt * BK;
     const uint32_t a_s = smem_base + (uint32_t)(slot * Cfg::kStageFloats) * 4u;
-    const uint32_t b_s = a_s + (uint32_t)(BM * Cfg::kLda) * 4u;
+    const uint32_t b_s = a_s + (uint32_t)Cfg::kAFloats * 4u;
     if constexpr (ALIGNED) {
-      constexpr int kAPerRow = BK / 4;                  // 16-byte pieces per A row
-#pragma unroll
-      for (int v = tid; v < (MODE == 0 ? 0 : BM * kAPerRow); v += kThreads) {
-        const int ar = v / kAPerRow, ak = (v % kAPerRow) * 4;
-        const int gr = m0 + ar, gk = k0 + ak;
-        int bytes = (gr < M) ? (K - gk) * 4 : 0;
-        bytes = bytes < 0 ? 0 : (bytes > 16 ? 16 : bytes);
-        cp_async_16(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, bytes ? (const void*)(A + (int64_t)gr * lda + gk) : (const void*)A, bytes);
-      }
       // B: BK rows x 16 pieces; a thread always copies the same piece of a row (column offset, byte count and
       // the shared-memory column are fixed), only the row moves
 #pragma unroll
@@ -121,12 +113,6 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
       }
     } else {
 #pragma unroll 4
-      for (int v = tid; v < (MODE == 0 ? 0 : BM * BK); v += kThreads) {
-        const int ar = v / BK, ak = v % BK;
-        const bool ain = (m0 + ar < M) && (k0 + ak < K);
-        cp_async_4(a_s + (uint32_t)(ar * Cfg::kLda + ak) * 4u, ain ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, ain ? 4 : 0);
-      }
-#pragma unroll 4
       for (int v = tid; v < BK * 64; v += kThreads) {
         const int br = v >> 6, bn = v & 63;
         const bool bin = (k0 + br < K) && (n0 + bn < N);
@@ -135,12 +121,12 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     }
   };
 
-  // bf16x3: the A tile does not go through the copy ring. Every warp of a k group needs the same A fragments, so
-  // splitting them after the fragment read would repeat the conversion once per warp; instead each thread reads its
-  // share of the tile one k-tile ahead, splits it once and writes the high and residual planes (packed pairs,
-  // [BM][BK + 8] bf16 each) where the FP32 tile would have been. Same arithmetic, same operands.
+  // The A tile does not go through the copy ring. Every warp of a k group needs the same A fragments, so splitting
+  // them after the fragment read would repeat the conversion once per warp; instead each thread reads its share of
+  // the tile one k-tile ahead, splits it once and writes the high and the residual plane ([BM][kLda] each: packed
+  // bf16 pairs, or tf32 words) at the head of the stage. Same arithmetic, same operands.
   constexpr int kAVecs = (BM * BK / 4) / kThreads;   // float4 of the A tile per thread
-  static_assert(MODE != 0 || (BM * BK / 4) % kThreads == 0, "A tile must divide among the threads");
+  static_assert((BM * BK / 4) % kThreads == 0, "A tile must divide among the threads");
   auto load_a = [&](int kt, float4 (&r)[kAVecs > 0 ? kAVecs : 1]) {
     const int k0 = kt * BK;
 #pragma unroll
@@ -161,15 +147,25 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   };
   auto store_a = [&](int slot, const float4 (&r)[kAVecs > 0 ? kAVecs : 1]) {
     uint32_t* hi_plane = reinterpret_cast<uint32_t*>(small_smem + slot * Cfg::kStageFloats);
-    uint32_t* lo_plane = hi_plane + BM * Cfg::kLda / 2;
+    uint32_t* lo_plane = hi_plane + Cfg::kAFloats / 2;
 #pragma unroll
     for (int i = 0; i < kAVecs; ++i) {
       const int v = i * kThreads + tid, ar = v / (BK / 4), ak = (v % (BK / 4)) * 4;
-      uint2 hi, lo;
-      split_bf16_pair(r[i].x, r[i].y, hi.x, lo.x);
-      split_bf16_pair(r[i].z, r[i].w, hi.y, lo.y);
-      *reinterpret_cast<uint2*>(hi_plane + (ar * Cfg::kLda + ak) / 2) = hi;
-      *reinterpret_cast<uint2*>(lo_plane + (ar * Cfg::kLda + ak) / 2) = lo;
+      if constexpr (MODE == 0) {
+        uint2 hi, lo;
+        split_bf16_pair(r[i].x, r[i].y, hi.x, lo.x);
+        split_bf16_pair(r[i].z, r[i].w, hi.y, lo.y);
+        *reinterpret_cast<uint2*>(hi_plane + (ar * Cfg::kLda + ak) / 2) = hi;
+        *reinterpret_cast<uint2*>(lo_plane + (ar * Cfg::kLda + ak) / 2) = lo;
+      } else {
+        uint4 hi, lo;
+        split_tf32(r[i].x, hi.x, lo.x);
+        split_tf32(r[i].y, hi.y, lo.y);
+        split_tf32(r[i].z, hi.z, lo.z);
+        split_tf32(r[i].w, hi.w, lo.w);
+        *reinterpret_cast<uint4*>(hi_plane + ar * Cfg::kLda + ak) = hi;
+        *reinterpret_cast<uint4*>(lo_plane + ar * Cfg::kLda + ak) = lo;
+      }
     }
   };
 
@@ -193,26 +189,22 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     cp_async_commit();
   }
   float4 a_next[kAVecs > 0 ? kAVecs : 1];   // A of k-tile kt + 1, read during k-tile kt
-  if constexpr (MODE == 0) {
-    if (ktiles > 0) {
-      load_a(kt_first, a_next);
-      store_a(0, a_next);
-    }
-    if (ktiles > 1) load_a(kt_first + 1, a_next);
+  if (ktiles > 0) {
+    load_a(kt_first, a_next);
+    store_a(0, a_next);
   }
+  if (ktiles > 1) load_a(kt_first + 1, a_next);
   for (int kt = 0; kt < ktiles; ++kt) {
     cp_async_wait<STAGES - 2>();
     __syncthreads();
     if (kt + STAGES - 1 < ktiles) load_tile(kt_first + kt + STAGES - 1, (kt + STAGES - 1) % STAGES);
     cp_async_commit();
-    if constexpr (MODE == 0) {
-      // The slot of k-tile kt + 1 was last read STAGES - 1 k-tiles ago; its A planes are written here, before the
-      // barrier that opens k-tile kt + 1, and the tile after that is requested.
-      if (kt + 1 < ktiles) store_a((kt + 1) % STAGES, a_next);
-      if (kt + 2 < ktiles) load_a(kt_first + kt + 2, a_next);
-    }
+    // The slot of k-tile kt + 1 was last read STAGES - 1 k-tiles ago; its A planes are written here, before the
+    // barrier that opens k-tile kt + 1, and the tile after that is requested.
+    if (kt + 1 < ktiles) store_a((kt + 1) % STAGES, a_next);
+    if (kt + 2 < ktiles) load_a(kt_first + kt + 2, a_next);
     const float* As = small_smem + (kt % STAGES) * Cfg::kStageFloats;
-    const float* Bs = As + BM * Cfg::kLda;
+    const float* Bs = As + Cfg::kAFloats;
     if constexpr (MODE == 0) {
 #pragma unroll
       for (int kk = kgroup * (BK / KSPLIT); kk < (kgroup + 1) * (BK / KSPLIT); kk += 16) {
@@ -220,7 +212,7 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
 #pragma unroll
         for (int i = 0; i < MI; ++i) {
           const uint32_t* hp = reinterpret_cast<const uint32_t*>(As) + ((wm + i * 16 + g) * Cfg::kLda + kk + 2 * t) / 2;
-          const uint32_t* lp = hp + BM * Cfg::kLda / 2;
+          const uint32_t* lp = hp + Cfg::kAFloats / 2;
           a_hi[i][0] = hp[0];                      // row g,   k 2t, 2t+1
           a_hi[i][1] = hp[4 * Cfg::kLda];          // row g+8
           a_hi[i][2] = hp[4];                      // row g,   k 2t+8, 2t+9
@@ -250,11 +242,16 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
         uint32_t a_hi[MI][4], a_lo[MI][4];
 #pragma unroll
         for (int i = 0; i < MI; ++i) {
-          const float* ap = As + (wm + i * 16 + g) * Cfg::kLda + kk + t;
-          split_tf32(ap[0], a_hi[i][0], a_lo[i][0]);
-          split_tf32(ap[8 * Cfg::kLda], a_hi[i][1], a_lo[i][1]);
-          split_tf32(ap[4], a_hi[i][2], a_lo[i][2]);
-          split_tf32(ap[8 * Cfg::kLda + 4], a_hi[i][3], a_lo[i][3]);
+          const uint32_t* hp = reinterpret_cast<const uint32_t*>(As) + (wm + i * 16 + g) * Cfg::kLda + kk + t;
+          const uint32_t* lp = hp + Cfg::kAFloats / 2;
+          a_hi[i][0] = hp[0];                      // row g,   k t
+          a_hi[i][1] = hp[8 * Cfg::kLda];          // row g+8
+          a_hi[i][2] = hp[4];                      // row g,   k t+4
+          a_hi[i][3] = hp[8 * Cfg::kLda + 4];      // row g+8
+          a_lo[i][0] = lp[0];
+          a_lo[i][1] = lp[8 * Cfg::kLda];
+          a_lo[i][2] = lp[4];
+          a_lo[i][3] = lp[8 * Cfg::kLda + 4];
         }
 #pragma unroll
         for (int j = 0; j < NI; ++j) {
