@@ -572,6 +572,7 @@ def run_sweep(args) -> None:
             end.record()
             end.synchronize()
             launches = int(max(3, min(30, budget_ms / max(begin.elapsed_time(end), 1e-3))))
+            time.sleep(0.5)   # every problem starts from an idle GPU, whatever ran before it
             samples = []
             for _ in range(launches):
                 flush.fill_(1)
@@ -597,11 +598,16 @@ def run_sweep(args) -> None:
     wall_begin = time.perf_counter()
     if rank == 0:
         sampler.start()
-    items, launches_total = [], 0
-    for mode, peak in (('bf16x3', peaks['bf16_tflops'] / 3.0), ('tf32x3', None)):
-        for m, n, k in SWEEP_GEMMS:
+    batch, hq, hkv, d = 8, 64, 8, 128
+    jobs = [('gemm', 2.0 * m * n * k, (mode, m, n, k)) for mode in ('bf16x3', 'tf32x3') for m, n, k in SWEEP_GEMMS]
+    jobs += [('attention', 4.0 * batch * hq * s * s * d, (s,)) for s in SWEEP_ATTENTION]
+    jobs.sort(key=lambda job: job[1])   # ascending work: a small problem is not timed in the wake of a long one
+    items = []
+    for kind, flops, spec in jobs:
+        holder = {}
+        if kind == 'gemm':
+            mode, m, n, k = spec
             begin_col, end_col = sharding.column_blocks(n, world)[rank]
-            holder = {}
 
             def make(m=m, k=k, width=end_col - begin_col, mode=mode, holder=holder):
                 if width == 0:
@@ -610,47 +616,39 @@ def run_sweep(args) -> None:
                 holder['c'] = torch.empty((m, width), device=device)
                 return lambda: ops.gemm(holder['a'], holder['b'], mode, out=holder['c'])
 
-            ms, failed = over_ranks(*measure(make, 300.0))
-            holder.clear()
-            torch.cuda.empty_cache()
-            item = {'kernel': f'gemm_{mode}', 'm': m, 'n': n, 'k': k, 'columns_per_rank': end_col - begin_col if world > 1 else n}
-            if failed or ms <= 0:
-                item['error'] = 'a rank failed; see stderr'
-            else:
-                tflops = 2.0 * m * n * k / ms / 1e9
-                item.update(ms=ms, tflops_aggregate=tflops)
-                if m <= 16:
-                    item['b_gbs_aggregate'] = 4.0 * n * k / ms / 1e6
-                    item['frac_of_hbm_peak_per_gpu'] = 4.0 * n * k / ms / 1e6 / world / peaks['hbm_gbs']
-                elif peak is not None:
-                    item['frac_of_bf16_peak_over_3_per_gpu'] = tflops / world / peak
-                    item['frac_of_sustained_bf16_peak_over_3_per_gpu'] = tflops / world / (peaks['bf16_tflops_sustained'] / 3.0)
-            items.append(item)
-    batch, hq, hkv, d = 8, 64, 8, 128
-    for s in SWEEP_ATTENTION:
-        groups = sharding.group_range(batch * hkv, world, rank)
-        holder = {}
+            item = {'kernel': f'gemm_{mode}', 'm': m, 'n': n, 'k': k, 'columns_per_rank': end_col - begin_col}
+        else:
+            (s,) = spec
+            groups = sharding.group_range(batch * hkv, world, rank)
 
-        def make(s=s, groups=groups, holder=holder):
-            if groups[1] == groups[0]:
-                return None
-            holder['q'] = normal(7, (batch, hq, s, d)).half()
-            holder['k'] = normal(8, (batch, hkv, s, d)).half()
-            holder['v'] = normal(9, (batch, hkv, s, d)).half()
-            holder['o'] = torch.empty((batch, hq, s, d), device=device)
-            return lambda: ops.gqa_attention(holder['q'], holder['k'], holder['v'], d ** -0.5, out=holder['o'], groups=groups)
+            def make(s=s, groups=groups, holder=holder):
+                if groups[1] == groups[0]:
+                    return None
+                holder['q'] = normal(7, (batch, hq, s, d)).half()
+                holder['k'] = normal(8, (batch, hkv, s, d)).half()
+                holder['v'] = normal(9, (batch, hkv, s, d)).half()
+                holder['o'] = torch.empty((batch, hq, s, d), device=device)
+                return lambda: ops.gqa_attention(holder['q'], holder['k'], holder['v'], d ** -0.5, out=holder['o'], groups=groups)
 
-        ms, failed = over_ranks(*measure(make, 400.0))
+            item = {'kernel': 'gqa_fwd_f16', 'batch': batch, 'q_heads': hq, 'kv_heads': hkv, 'seq_len': s, 'head_dim': d,
+                    'groups_per_rank': groups[1] - groups[0]}
+        ms, failed = over_ranks(*measure(make, 300.0 if kind == 'gemm' else 400.0))
         holder.clear()
         torch.cuda.empty_cache()
-        item = {'kernel': 'gqa_fwd_f16', 'batch': batch, 'q_heads': hq, 'kv_heads': hkv, 'seq_len': s, 'head_dim': d,
-                'groups_per_rank': groups[1] - groups[0]}
         if failed or ms <= 0:
             item['error'] = 'a rank failed; see stderr'
         else:
-            tflops = 4.0 * batch * hq * s * s * d / ms / 1e9
-            item.update(ms=ms, tflops_aggregate=tflops, frac_of_bf16_peak_per_gpu=tflops / world / peaks['bf16_tflops'],
-                        frac_of_sustained_bf16_peak_per_gpu=tflops / world / peaks['bf16_tflops_sustained'])
+            tflops = flops / ms / 1e9
+            item.update(ms=ms, tflops_aggregate=tflops)
+            if kind == 'gemm' and spec[1] <= 16:
+                item['b_gbs_aggregate'] = 4.0 * spec[2] * spec[3] / ms / 1e6
+                item['frac_of_hbm_peak_per_gpu'] = item['b_gbs_aggregate'] / world / peaks['hbm_gbs']
+            elif kind == 'gemm' and spec[0] == 'bf16x3':
+                item['frac_of_bf16_peak_over_3_per_gpu'] = tflops / world / (peaks['bf16_tflops'] / 3.0)
+                item['frac_of_sustained_bf16_peak_over_3_per_gpu'] = tflops / world / (peaks['bf16_tflops_sustained'] / 3.0)
+            elif kind == 'attention':
+                item['frac_of_bf16_peak_per_gpu'] = tflops / world / peaks['bf16_tflops']
+                item['frac_of_sustained_bf16_peak_per_gpu'] = tflops / world / peaks['bf16_tflops_sustained']
         items.append(item)
     torch.cuda.synchronize()
     wall_end = time.perf_counter()
@@ -659,7 +657,9 @@ def run_sweep(args) -> None:
                 'config': {'workload': 'mixed_sweep_gemm_1024_2048_4096_16384_skinny16_attention_512_2048_8192_16384',
                            'inputs': 'N(0,1), seeds 7 / 11+rank (GEMM), 7 / 8 / 9 (attention, f16 storage)',
                            'parallelism': f'each problem split x{world}: GEMM by output column blocks, attention by (batch, kv-head) groups; no collective',
-                           'l2': '512 MiB written between launches', 'timing': 'median over launches, maximum over ranks'},
+                           'l2': '512 MiB written between launches',
+                           'timing': 'problems in ascending order of work, 0.5 s idle before the timed launches of each; '
+                                     'median over launches, maximum over ranks'},
                 'peaks': {'bf16_tflops': peaks['bf16_tflops'], 'bf16_tflops_sustained': peaks['bf16_tflops_sustained'],
                           'hbm_gbs': peaks['hbm_gbs'], 'source': peaks['source'],
                           'note': 'launches of tens of milliseconds run at the clocks of the power cap: compare them with the sustained peak'},

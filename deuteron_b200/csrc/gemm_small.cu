@@ -2,9 +2,10 @@
 //
 // A tcgen05 GEMM needs a split pass over the operands, tensor-memory allocation and 128-row
 // tiles; for a 128^3 or 512^3 product, or for 16 rows, that set-up is most of the run time.
-// This kernel keeps the structure of the reference's emitted code instead: FP32 tiles go to
-// shared memory through a 4-slot cp.async ring, every warp converts the fragments it needs to a
-// rounded high part and a rounded residual in registers, and issues the three warp-level
+// This kernel keeps the structure of the reference's emitted code instead: FP32 B tiles go to
+// shared memory through a 4-slot cp.async ring and every warp converts the B fragments it needs to a
+// rounded high part and a rounded residual in registers; the A tile, whose fragments every warp of a
+// k group shares, is split once per CTA into two planes. Each warp issues the three warp-level
 // products per k-step in the reference's order (lo*hi, hi*lo, hi*hi; mma.sync m16n8k16 for
 // bf16, m16n8k8 for tf32) into FP32 accumulators. Two configurations: a 64x64 CTA tile with 4 warps
 // of 32x32 and a 32-deep k-tile (small square problems; the reference's accumulation order, so its
