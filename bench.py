@@ -672,6 +672,56 @@ def run_sweep(args) -> None:
         dist.destroy_process_group()
 
 
+def run_all_gather(args) -> None:
+    """Times the optional exchange that follows the sharded GEMM: the all-gather (NCCL) of the ranks' 8192 x 8192 output
+    blocks into the full 8192 x (8192 * N) product on every rank. Opt-in (`--all-gather`), never part of the default
+    line: the data path itself has no collective."""
+    import torch
+    import torch.distributed as dist
+
+    rank = int(os.environ.get('RANK', '0'))
+    local_rank = int(os.environ.get('LOCAL_RANK', '0'))
+    world = int(os.environ.get('WORLD_SIZE', '1'))
+    if world < 2:
+        raise SystemExit('--all-gather needs --gpus 2 or more')
+    sys.stdout.flush()
+    json_fd = os.dup(1)
+    os.dup2(2, 1)
+    torch.cuda.set_device(local_rank)
+    device = torch.device('cuda', local_rank)
+    dist.init_process_group('nccl', device_id=device)
+    from deuteron_b200 import sharding
+    block = torch.full((M, N), float(rank), device=device)
+    blocks = sharding.column_blocks(N * world, world)
+    for _ in range(3):
+        full = sharding.all_gather_columns(block, blocks)
+    correct = all(bool((full[::1024, r * N] == r).all().item()) for r in range(world))
+    del full
+    dist.barrier()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    iters = max(3, min(args.steps, 10))
+    begin.record()
+    for _ in range(iters):
+        full = sharding.all_gather_columns(block, blocks)
+        del full
+    end.record()
+    end.synchronize()
+    gathered = torch.tensor([begin.elapsed_time(end) / iters], device=device)
+    dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+    ms = float(gathered.item())
+    if rank == 0:
+        received = (world - 1) * M * N * 4
+        line = {'metric': 'all_gather_of_output_column_blocks', 'n_gpus': world, 'ms': ms, 'block_bytes': M * N * 4,
+                'bytes_received_per_rank': received, 'gbs_received_per_rank': received / ms / 1e6, 'correct': correct,
+                'note': 'torch.distributed all_gather (NCCL) plus the permute into row-major; max over ranks'}
+        sys.stdout.flush()
+        os.dup2(json_fd, 1)
+        print(json.dumps(line), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'gemm_skinny', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max',
                  'row_softmax', 'rms_norm', 'fused_affine')
 
@@ -742,6 +792,7 @@ def main() -> None:
     parser.add_argument('--impl', choices=('ours', 'reference'), default='ours')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-extras', action='store_true')
+    parser.add_argument('--all-gather', action='store_true', help='time the optional all-gather of the output column blocks (N > 1)')
     parser.add_argument('--sweep', action='store_true', help='time the mixed sweep of GEMM and attention sizes, each split over the ranks')
     args = parser.parse_args()
     if args.steps < 1 or args.warmup < 0:
@@ -758,6 +809,9 @@ def main() -> None:
         command = [sys.executable, '-m', 'torch.distributed.run', '--nnodes=1', f'--nproc-per-node={args.gpus}',
                    '--master-addr', '127.0.0.1', '--master-port', '29511', __file__, *sys.argv[1:]]
         raise SystemExit(subprocess.call(command))
+    if args.all_gather:
+        run_all_gather(args)
+        return
     if args.sweep:
         run_sweep(args)
         return
