@@ -3,6 +3,8 @@
 // double-buffered shared memory. A is stored transposed in shared memory so that both
 // operand reads in the inner loop are conflict-free 128-bit loads. Any M, N, K and any
 // leading dimensions; the vector global loads are used when pointers and strides allow.
+#include <stdlib.h>
+
 #include "dtn_common.cuh"
 
 namespace dtn {
@@ -192,10 +194,117 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
     }
 }
 
+// Mid-size products: 64x64 CTA tiles, 4x4 outputs per thread, several CTAs per SM. A 1024^3 product is 64 tiles of
+// 128x128 (under half of the SMs) but 256 of these. Same sequential FMA chain per output element.
+constexpr int FM_B = 64, FM_BK = 16;
+
+template <bool ALIGNED>
+__global__ void __launch_bounds__(F_THREADS)
+gemm_f32_mid_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
+                    int64_t lda, int64_t ldb, int64_t ldc) {
+  __shared__ __align__(16) float As[2][FM_BK][FM_B + 4];   // transposed: [k][row]
+  __shared__ __align__(16) float Bs[2][FM_BK][FM_B + 4];
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * FM_B, n0 = blockIdx.x * FM_B;
+  const int tx = tid & 15, ty = tid >> 4;   // 16 x 16 threads, each 4 x 4 outputs
+  // staging: each operand tile is 256 float4, one per thread (A along k, B along n)
+  const int ar = tid >> 2, ak = (tid & 3) * 4;
+  const int bk = tid >> 4, bn = (tid & 15) * 4;
+  float4 ra, rb;
+  auto load_tiles = [&](int k0) {
+    ra = make_float4(0.f, 0.f, 0.f, 0.f);
+    rb = ra;
+    const int gr = m0 + ar, gk = k0 + ak;
+    if (gr < M) {
+      const float* p = A + (int64_t)gr * lda + gk;
+      if (ALIGNED && gk + 3 < K) {
+        ra = *reinterpret_cast<const float4*>(p);
+      } else {
+        if (gk + 0 < K) ra.x = p[0];
+        if (gk + 1 < K) ra.y = p[1];
+        if (gk + 2 < K) ra.z = p[2];
+        if (gk + 3 < K) ra.w = p[3];
+      }
+    }
+    const int gkb = k0 + bk, gn = n0 + bn;
+    if (gkb < K) {
+      const float* p = B + (int64_t)gkb * ldb + gn;
+      if (ALIGNED && gn + 3 < N) {
+        rb = *reinterpret_cast<const float4*>(p);
+      } else {
+        if (gn + 0 < N) rb.x = p[0];
+        if (gn + 1 < N) rb.y = p[1];
+        if (gn + 2 < N) rb.z = p[2];
+        if (gn + 3 < N) rb.w = p[3];
+      }
+    }
+  };
+  auto store_tiles = [&](int buf) {
+    As[buf][ak + 0][ar] = ra.x;
+    As[buf][ak + 1][ar] = ra.y;
+    As[buf][ak + 2][ar] = ra.z;
+    As[buf][ak + 3][ar] = ra.w;
+    *reinterpret_cast<float4*>(&Bs[buf][bk][bn]) = rb;
+  };
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  const int ktiles = (K + FM_BK - 1) / FM_BK;
+  if (ktiles > 0) {
+    load_tiles(0);
+    store_tiles(0);
+  }
+  __syncthreads();
+  for (int kt = 0; kt < ktiles; ++kt) {
+    const int buf = kt & 1;
+    if (kt + 1 < ktiles) load_tiles((kt + 1) * FM_BK);
+#pragma unroll
+    for (int k = 0; k < FM_BK; ++k) {
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+      const float4 b4 = *reinterpret_cast<const float4*>(&Bs[buf][k][tx * 4]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    if (kt + 1 < ktiles) store_tiles(buf ^ 1);
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int r = m0 + ty * 4 + i, c = n0 + tx * 4;
+    if (r >= M) continue;
+    float* p = C + (int64_t)r * ldc + c;
+    if (ALIGNED && c + 3 < N) {
+      *reinterpret_cast<float4*>(p) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        if (c + j < N) p[j] = acc[i][j];
+    }
+  }
+}
+
 int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s) {
-  // fewer 128x128 tiles than a quarter of the SMs: the 32x32-tile kernel spreads the product over 16 times as many CTAs
-  if (((M + F_BM - 1) / F_BM) * ((N + F_BN - 1) / F_BN) * 4 <= (int64_t)sm_count() && (M + FS_B - 1) / FS_B <= 65535) {
+  static const int forced_tile = [] {
+    const char* text = getenv("DTN_GEMM_F32_TILE");   // tuning aid: 32, 64 or 128 forces that tile
+    return text ? atoi(text) : 0;
+  }();
+  const int64_t tiles64 = ((M + FM_B - 1) / FM_B) * ((N + FM_B - 1) / FM_B);
+  const int64_t tiles128 = ((M + F_BM - 1) / F_BM) * ((N + F_BN - 1) / F_BN);
+  // The tile is the largest that still gives every SM work: 32x32 while 64x64 tiles would cover at most half of the
+  // SMs, 64x64 while 128x128 tiles would cover under three quarters of them, 128x128 beyond.
+  int tile = forced_tile == 32 || forced_tile == 64 || forced_tile == 128 ? forced_tile
+             : tiles64 * 2 <= (int64_t)sm_count()                        ? 32
+             : tiles128 * 4 < (int64_t)sm_count() * 3                    ? 64
+                                                                         : 128;
+  if (tile == 32 && (M + FS_B - 1) / FS_B > 65535) tile = 64;
+  if (tile == 64 && (M + FM_B - 1) / FM_B > 65535) tile = 128;
+  if (tile == 32) {
     dim3 small_grid((unsigned)((N + FS_B - 1) / FS_B), (unsigned)((M + FS_B - 1) / FS_B));
     gemm_f32_small_kernel<<<small_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
     DTN_LAUNCH_CHECK("gemm_f32_small_kernel");
@@ -205,6 +314,15 @@ int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t
   DTN_REQUIRE(grid.y <= 65535, DTN_ERR_UNSUPPORTED, "gemm f32: M too large");
   const bool aligned = aligned_to(A, 16) && aligned_to(B, 16) && aligned_to(C, 16) && lda % 4 == 0 &&
                        ldb % 4 == 0 && ldc % 4 == 0;
+  if (tile == 64) {
+    dim3 mid_grid((unsigned)((N + FM_B - 1) / FM_B), (unsigned)((M + FM_B - 1) / FM_B));
+    if (aligned)
+      gemm_f32_mid_kernel<true><<<mid_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+    else
+      gemm_f32_mid_kernel<false><<<mid_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+    DTN_LAUNCH_CHECK("gemm_f32_mid_kernel");
+    return DTN_OK;
+  }
   if (aligned)
     gemm_f32_kernel<true><<<grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
   else
