@@ -483,6 +483,21 @@ def test_gemm_f32_mode_shapes(cuda):
         assert R.max_relative_error(produced, R.gemm_f64(a, b)) < 2e-6
 
 
+def test_gemm_f32_result_does_not_depend_on_the_tile(cuda):
+    # The FP32 mode picks 32x32, 64x64 or 128x128 CTA tiles by problem size; every output element is the same sequential
+    # FMA chain over k in all three, so a corner of a large product equals the small product of the corner operands, bit
+    # for bit. Shapes: 64-wide tiles with and without 16-byte alignment, 128-wide tiles.
+    for m, n, k in ((640, 640, 100), (641, 643, 77), (1536, 1536, 64)):
+        a, b = to_device(cuda, R.seeded_normal(7, (m, k))), to_device(cuda, R.seeded_normal(11, (k, n)))
+        whole = ops.gemm(a, b, 'f32')
+        corner = ops.gemm(a[m - 48:].contiguous(), b[:, n - 40:].contiguous(), 'f32')   # 48 x 40: one 32-wide-tile launch
+        assert cuda.equal(whole[m - 48:, n - 40:], corner), (m, n, k)
+        rows = slice(0, m, 97)
+        exact = a[rows].double() @ b.double()
+        assert float(((whole[rows].double() - exact).abs().max() / exact.abs().max()).item()) < 2e-6
+        np.testing.assert_array_equal(whole[:8, :8].cpu().numpy(), R.gemm_f32_fma(a[:8].cpu().numpy(), b[:, :8].cpu().numpy()))
+
+
 def test_gemm_edge_cases_and_errors(cuda):
     a, b = to_device(cuda, R.seeded_uniform(1, (64, 32))), to_device(cuda, R.seeded_uniform(2, (32, 48)))
     assert ops.gemm(a[:0], b, 'bf16x3').shape == (0, 48)
