@@ -52,6 +52,7 @@ struct ScalarFile {
 
 struct RowChain {
   int n;
+  int cached_exp;   // 1: the chain opens with (x - max), exp and the softmax sum pass leaves exactly those values in the row cache
   unsigned char op[kChainMax], kind[kChainMax], index[kChainMax], swap[kChainMax];   // index: register (scalar) or input (columns)
 };
 
@@ -221,8 +222,8 @@ __device__ __forceinline__ void chain_fold(int reduce, const float4 (&cache)[kRo
 template <int TPR, bool VEC>
 __device__ __forceinline__ void chain_run(const RowProgram& prog, const RowChain& chain, const ScalarFile& scalars,
                                           float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int chunk_base, int rank,
-                                          int cols) {
-  for (int s = 0; s < chain.n; ++s) {
+                                          int cols, int first_step = 0) {
+  for (int s = first_step; s < chain.n; ++s) {
     const int kind = chain.kind[s];
     const bool swap = chain.swap[s] != 0;
     const float scalar = kind == CHAIN_SCALAR ? scalars.r[chain.index[s]] : 0.0f;
@@ -297,9 +298,15 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
     float second = 0.0f;
     if (reduce == DTN_REDUCE_SOFTMAX) {
       if (one_chunk) {   // padding holds -inf, whose exponential is 0
+        // the exponentials stay in the row cache: when the elementwise stage opens with the same (x - max), exp
+        // (chain.cached_exp) it continues from them instead of computing each a second time
 #pragma unroll
-        for (int u = 0; u < kRowCacheVecs; ++u)
-          second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) + (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
+        for (int u = 0; u < kRowCacheVecs; ++u) {
+          const float4 e = make_float4(exp_ref(__fsub_rn(cache[u].x, first)), exp_ref(__fsub_rn(cache[u].y, first)),
+                                       exp_ref(__fsub_rn(cache[u].z, first)), exp_ref(__fsub_rn(cache[u].w, first)));
+          second += (e.x + e.y) + (e.z + e.w);
+          if constexpr (!KEEPX) cache[u] = e;
+        }
       } else {
         for (int chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
           chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, -INFINITY);
@@ -330,6 +337,10 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
         chain_run<TPR, VEC>(prog, chain, scalars, acc, cache, chunk_base, rank, cols);
 #pragma unroll
         for (int u = 0; u < kRowCacheVecs; ++u) cache[u] = acc[u];
+      } else if (reduce == DTN_REDUCE_SOFTMAX && one_chunk) {
+        // the cache holds exp(x - max) already; a chain that does not open with those two steps starts from x again
+        if (!chain.cached_exp) chain_load<TPR, VEC>(cache, xr, 0, rank, cols, 0.0f);
+        chain_run<TPR, VEC>(prog, chain, scalars, cache, cache, chunk_base, rank, cols, chain.cached_exp ? 2 : 0);
       } else {
         chain_run<TPR, VEC>(prog, chain, scalars, cache, cache, chunk_base, rank, cols);
       }
@@ -459,6 +470,7 @@ row_interpreter_kernel(const RowProgram prog, const float* __restrict__ x, float
 // elementwise stage has not overwritten. *keep_x: a step after the first reads the row element.
 static bool row_chain_of(const RowProgram& prog, RowChain* chain, bool* keep_x, bool per_row) {
   chain->n = 0;
+  chain->cached_exp = 0;
   *keep_x = false;
   int running = 2;
   bool written[kRowRegs] = {false};
@@ -506,6 +518,11 @@ static bool row_chain_of(const RowProgram& prog, RowChain* chain, bool* keep_x, 
     running = prog.dst[n];
     written[running] = true;
   }
+  // softmax: (x - max), exp are what the sum pass computed; the scalar stage must have left the maximum in register 0
+  bool max_intact = true;
+  for (int n = 0; n < prog.n_scalar; ++n) max_intact = max_intact && prog.dst[n] != 0;
+  chain->cached_exp = prog.reduce == DTN_REDUCE_SOFTMAX && !*keep_x && max_intact && chain->n >= 2 && chain->op[0] == DTN_EW_SUB &&
+                      chain->kind[0] == CHAIN_SCALAR && chain->index[0] == 0 && chain->swap[0] == 0 && chain->op[1] == DTN_EW_EXP;
   return per_row || prog.out_reg == running;   // a per-row result is read from the scalar registers
 }
 
