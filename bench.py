@@ -673,9 +673,11 @@ def run_sweep(args) -> None:
 
 
 def run_all_gather(args) -> None:
-    """Times the optional exchange that follows the sharded GEMM: the all-gather (NCCL) of the ranks' 8192 x 8192 output
-    blocks into the full 8192 x (8192 * N) product on every rank. Opt-in (`--all-gather`), never part of the default
-    line: the data path itself has no collective."""
+    """Times the optional exchange that follows the sharded GEMM, two ways: the all-gather (NCCL) of the ranks' finished
+    8192 x 8192 output blocks into the full 8192 x (8192 * N) product on every rank, after the GEMM; and
+    `sharding.GatheredProduct`, which pushes finished row blocks into the peers' copies (symmetric memory, peer stores
+    over NVLink) while the rest is multiplied. Opt-in (`--all-gather`), never part of the default line: the data path
+    itself has no collective."""
     import torch
     import torch.distributed as dist
 
@@ -690,31 +692,62 @@ def run_all_gather(args) -> None:
     torch.cuda.set_device(local_rank)
     device = torch.device('cuda', local_rank)
     dist.init_process_group('nccl', device_id=device)
-    from deuteron_b200 import sharding
-    block = torch.full((M, N), float(rank), device=device)
+    from deuteron_b200 import ops, sharding
+    generator = torch.Generator(device=device)
+    generator.manual_seed(7)
+    a = torch.rand((M, K), device=device, generator=generator) * 2 - 1
+    generator.manual_seed(11 + rank)
+    b = torch.rand((K, N), device=device, generator=generator) * 2 - 1
+    block = torch.empty((M, N), device=device)
     blocks = sharding.column_blocks(N * world, world)
-    for _ in range(3):
-        full = sharding.all_gather_columns(block, blocks)
-    correct = all(bool((full[::1024, r * N] == r).all().item()) for r in range(world))
-    del full
-    dist.barrier()
-    torch.cuda.synchronize()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     iters = max(3, min(args.steps, 10))
-    begin.record()
-    for _ in range(iters):
-        full = sharding.all_gather_columns(block, blocks)
-        del full
-    end.record()
-    end.synchronize()
-    gathered = torch.tensor([begin.elapsed_time(end) / iters], device=device)
-    dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
-    ms = float(gathered.item())
+
+    def timed(call) -> float:
+        for _ in range(2):
+            call()
+        dist.barrier()
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        for _ in range(iters):
+            call()
+        end.record()
+        end.synchronize()
+        gathered = torch.tensor([begin.elapsed_time(end) / iters], device=device)
+        dist.all_reduce(gathered, op=dist.ReduceOp.MAX)
+        return float(gathered.item())
+
+    def gemm_then_gather():
+        ops.gemm(a, b, 'bf16x3', out=block)
+        return sharding.all_gather_columns(block, blocks)
+
+    gemm_ms = timed(lambda: ops.gemm(a, b, 'bf16x3', out=block))
+    gather_ms = timed(lambda: sharding.all_gather_columns(block, blocks))
+    sequential_ms = timed(gemm_then_gather)
+    expected = gemm_then_gather()
+    overlapped_ms, identical, failure = None, None, None
+    try:
+        product = sharding.GatheredProduct(M, N * world, rank, world, device, row_blocks=args.row_blocks or None)
+        overlapped_ms = timed(lambda: product.run(a, b, 'bf16x3'))
+        full = product.run(a, b, 'bf16x3')
+        torch.cuda.synchronize()
+        same = torch.tensor([float(torch.equal(full, expected))], device=device)
+        dist.all_reduce(same, op=dist.ReduceOp.MIN)
+        identical = bool(same.item())
+    except Exception as error:   # noqa: BLE001 - symmetric memory may be unavailable; the NCCL figures stand
+        failure = repr(error)[:200]
+    ops.check_device_status()
     if rank == 0:
         received = (world - 1) * M * N * 4
-        line = {'metric': 'all_gather_of_output_column_blocks', 'n_gpus': world, 'ms': ms, 'block_bytes': M * N * 4,
-                'bytes_received_per_rank': received, 'gbs_received_per_rank': received / ms / 1e6, 'correct': correct,
-                'note': 'torch.distributed all_gather (NCCL) plus the permute into row-major; max over ranks'}
+        flops = FLOPS_PER_GEMM * world
+        line = {'metric': 'gemm_with_all_gather_of_output_column_blocks', 'n_gpus': world, 'block_bytes': M * N * 4,
+                'bytes_received_per_rank': received, 'gemm_ms': gemm_ms, 'all_gather_ms': gather_ms,
+                'all_gather_gbs_received_per_rank': received / gather_ms / 1e6,
+                'gemm_then_all_gather_ms': sequential_ms, 'gemm_then_all_gather_tflops': flops / sequential_ms / 1e9,
+                'overlapped_ms': overlapped_ms, 'overlapped_tflops': flops / overlapped_ms / 1e9 if overlapped_ms else None,
+                'overlapped_result_identical': identical, 'overlapped_failure': failure,
+                'note': 'all_gather = torch.distributed all_gather (NCCL) plus the permute into row-major; overlapped = '
+                        f'sharding.GatheredProduct ({len(product.rows) if identical is not None else 0} row blocks, dtn_push_block on a side stream, barrier at the end); max over ranks'}
         sys.stdout.flush()
         os.dup2(json_fd, 1)
         print(json.dumps(line), flush=True)
@@ -792,6 +825,7 @@ def main() -> None:
     parser.add_argument('--impl', choices=('ours', 'reference'), default='ours')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-extras', action='store_true')
+    parser.add_argument('--row-blocks', type=int, default=0, help='row blocks of the overlapped exchange (--all-gather); 0 = automatic')
     parser.add_argument('--all-gather', action='store_true', help='time the optional all-gather of the output column blocks (N > 1)')
     parser.add_argument('--sweep', action='store_true', help='time the mixed sweep of GEMM and attention sizes, each split over the ranks')
     args = parser.parse_args()

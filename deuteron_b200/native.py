@@ -42,6 +42,7 @@ _SIGNATURES = {
     'dtn_elementwise_f32': [_I, _P, _P, _P, _I64, _P],
     'dtn_elementwise_program': [_P, _P, _P, _P, _I, _P, _P, _P, _I, _I, _P, _I, _I64, _P],
     'dtn_f16_copy': [_P, _P, _I64, _P],
+    'dtn_push_block': [_P, _I64, ct.POINTER(ct.c_void_p), _I, _I64, _I64, _I64, _P],
     'dtn_f16_widen': [_P, _P, _I64, _P],
     'dtn_f16_narrow': [_P, _P, _I64, _P],
     'dtn_row_reduce_f32': [_I, _P, _P, _I64, _I64, _I64, _P],

@@ -231,6 +231,26 @@ def gemm(a: torch.Tensor, b: torch.Tensor, mode: str = 'bf16x3', out: torch.Tens
     return out
 
 
+def push_block(src: torch.Tensor, destinations: list[torch.Tensor]) -> None:
+    """Writes the 2-D float32 block `src` into every tensor of `destinations` (same shape, equal row strides; up to
+    seven; they may be views of other GPUs' memory) with one kernel that reads the block once."""
+    _require_cuda(src)
+    lds = _row_major(src, 'src')
+    if not destinations:
+        return
+    rows, cols = src.shape
+    strides = set()
+    for dst in destinations:
+        if dst.dtype != torch.float32 or tuple(dst.shape) != (rows, cols):
+            raise ValueError('every destination must be a float32 tensor of the shape of src')
+        strides.add(_row_major(dst, 'destination'))
+    if len(strides) != 1:
+        raise ValueError('the destinations must share one row stride')
+    pointers = (ct.c_void_p * len(destinations))(*[dst.data_ptr() for dst in destinations])
+    native.call('dtn_push_block', src.data_ptr(), max(lds, cols), pointers, len(destinations), max(strides.pop(), cols), rows, cols,
+                _stream())
+
+
 def set_gemm_variant(variant: int) -> None:
     native.call('dtn_gemm_set_variant', variant)
 

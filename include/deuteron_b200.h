@@ -212,6 +212,16 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
 int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
                        int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* stream);
 
+/* Copies the block src[rows, cols] (row-major FP32, leading dimension lds) to the same extent at each of the n_dst
+ * (at most 7) destination pointers, all with leading dimension ldd: the block is read once and written n_dst times,
+ * 16 bytes per thread when every pointer is 16-byte aligned and lds, ldd, cols are multiples of 4. The destinations
+ * may be peer-mapped memory of other GPUs: this is the exchange step of a column-sharded GEMM whose full result is
+ * wanted on every GPU (a rank pushes its finished rows into the peers' copies while it multiplies the rest).
+ * `dsts` is a host array. No reference counterpart (the reference runs one GPU per problem,
+ * benchmark.py:546-551). */
+int dtn_push_block(const float* src, int64_t lds, float* const* dsts, int n_dst, int64_t ldd,
+                   int64_t rows, int64_t cols, void* stream);
+
 /* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile,
  *   4 = the single-kernel path for small problems (operand split inside the kernel, warp-level

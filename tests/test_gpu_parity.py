@@ -498,6 +498,24 @@ def test_gemm_f32_result_does_not_depend_on_the_tile(cuda):
         np.testing.assert_array_equal(whole[:8, :8].cpu().numpy(), R.gemm_f32_fma(a[:8].cpu().numpy(), b[:, :8].cpu().numpy()))
 
 
+def test_push_block_copies_one_block_into_every_destination(cuda):
+    # The exchange step of the sharded GEMM: a column block of one matrix written into the same place of several other
+    # copies (here: buffers of the same GPU; between GPUs the destinations are peer mappings). Bit-exact, nothing
+    # outside the block touched, vector and scalar paths, empty extents.
+    for rows, cols, offset in ((300, 512, 256), (129, 77, 3), (0, 64, 0), (64, 0, 0)):
+        width = 1024
+        source = cuda.randn((rows, width), device='cuda:0')
+        copies = [cuda.full((rows, width), float(i), device='cuda:0') for i in range(7)]
+        ops.push_block(source[:, offset:offset + cols], [c[:, offset:offset + cols] for c in copies])
+        for i, c in enumerate(copies):
+            assert cuda.equal(c[:, offset:offset + cols], source[:, offset:offset + cols])
+            assert bool((c[:, :offset] == i).all()) and bool((c[:, offset + cols:] == i).all())
+    with pytest.raises(Exception, match='destinations'):
+        ops.push_block(source, [cuda.empty_like(source) for _ in range(8)])
+    with pytest.raises(ValueError):
+        ops.push_block(source, [cuda.empty((3, 3), device='cuda:0')])
+
+
 def test_gemm_edge_cases_and_errors(cuda):
     a, b = to_device(cuda, R.seeded_uniform(1, (64, 32))), to_device(cuda, R.seeded_uniform(2, (32, 48)))
     assert ops.gemm(a[:0], b, 'bf16x3').shape == (0, 48)

@@ -86,3 +86,15 @@ def test_two_gloo_ranks_assemble_sharded_outputs():
         worker.join(timeout=60)
         assert worker.exitcode == 0
     assert results == [(0, True, True), (1, True, True)]
+
+
+def test_row_blocks_for_overlap_cover_the_rows_on_tile_boundaries():
+    from deuteron_b200 import sharding
+    for m, blocks in ((8192, 2), (8192, 4), (300, 4), (256, 2), (1, 3), (0, 2), (5000, 3)):
+        ranges = sharding.row_blocks_for_overlap(m, blocks)
+        assert [r[0] for r in ranges] == ([0] + [r[1] for r in ranges[:-1]] if ranges else [])
+        assert (ranges[-1][1] if ranges else 0) == m
+        assert all(end > begin for begin, end in ranges) and len(ranges) <= blocks
+        assert all(begin % 256 == 0 for begin, _ in ranges)
+    with pytest.raises(ValueError):
+        sharding.row_blocks_for_overlap(8, 0)
