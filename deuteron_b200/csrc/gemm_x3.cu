@@ -110,6 +110,7 @@ template <class KIND>
 __global__ void __launch_bounds__(256)
 split_rows_kernel(const float* __restrict__ X, int64_t ldx, int rows, int cols, int colsP,
                   typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo, int vec_ok) {
+  ptx::launch_dependents();   // a product kernel launched behind this grid may begin its set-up; it waits for the grid before it loads
   split_rows_body<KIND>(X, ldx, cols, colsP, hi, lo, vec_ok, (int)blockIdx.y, (int)blockIdx.x);
 }
 
@@ -218,6 +219,7 @@ template <class KIND>
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
                        typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo, int b_vec_ok) {
+  ptx::launch_dependents();
   if constexpr (KIND::kElemBytes == 2) {
     if (b_vec_ok) {
       split_transpose_bf16_vec(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
