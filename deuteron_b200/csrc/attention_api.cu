@@ -12,7 +12,7 @@ int gqa_tc_pair_launch(const void* q, const void* k, const void* v, float* out, 
                        int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s);
 bool gqa_tc_pair_supported(int64_t S, int64_t D, int storage);
 
-static int g_gqa_variant = 0;
+static thread_local int g_gqa_variant = 0;   // selection of dtn_gqa_set_variant, one value per host thread
 
 }  // namespace dtn
 

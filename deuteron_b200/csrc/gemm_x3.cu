@@ -536,7 +536,18 @@ static int make_plane_map(CUtensorMap* map, const void* base, int elem_bytes, in
   return DTN_OK;
 }
 
-static int g_gemm_variant = 0;
+// Tile-variant selection of dtn_gemm_set_variant: one value per host thread (a thread that pins a
+// variant for a measurement does not change what other threads' calls run).
+static thread_local int g_gemm_variant = 0;
+
+// Tile width forced on the fused-split variant (DTN_GEMM_FUSED_BN), read once.
+static int fused_bn_override() {
+  static const int value = [] {
+    const char* text = getenv("DTN_GEMM_FUSED_BN");
+    return text ? atoi(text) : 0;
+  }();
+  return value;
+}
 
 // m-tiles per raster group. DTN_GEMM_GROUP_M overrides the default for experiments.
 static int raster_group_m() {
@@ -548,10 +559,16 @@ static int raster_group_m() {
   return value;
 }
 
+// Workspace layout: Bt_hi, Bt_lo, A_hi, A_lo. The B planes come first so that their place depends on
+// (mode, N, K) only: a caller that walks row blocks of A of any heights against one B splits B once.
 struct PlaneLayout {
   int64_t Kp;
   size_t a_plane, b_plane;  // bytes of one plane, rounded to 1024
   size_t total;
+  size_t b_hi() const { return 0; }
+  size_t b_lo() const { return b_plane; }
+  size_t a_hi() const { return 2 * b_plane; }
+  size_t a_lo() const { return 2 * b_plane + a_plane; }
 };
 static PlaneLayout plane_layout(int mode, int64_t M, int64_t N, int64_t K) {
   PlaneLayout L;
@@ -622,10 +639,10 @@ template <class KIND>
 static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                      const PlaneLayout& L, uint8_t* ws, cudaStream_t s, bool do_a = true, bool do_b = true) {
   using E = typename KIND::elem;
-  E* a_hi = reinterpret_cast<E*>(ws);
-  E* a_lo = reinterpret_cast<E*>(ws + L.a_plane);
-  E* b_hi = reinterpret_cast<E*>(ws + 2 * L.a_plane);
-  E* b_lo = reinterpret_cast<E*>(ws + 2 * L.a_plane + L.b_plane);
+  E* a_hi = reinterpret_cast<E*>(ws + L.a_hi());
+  E* a_lo = reinterpret_cast<E*>(ws + L.a_lo());
+  E* b_hi = reinterpret_cast<E*>(ws + L.b_hi());
+  E* b_lo = reinterpret_cast<E*>(ws + L.b_lo());
   {
     const int64_t ax = (L.Kp / kSplitRowElems<KIND> + 255) / 256, a_blocks = ax * M;
     const int b_vec_ok = aligned_to(B, 16) && (ldb % 4 == 0);
@@ -674,10 +691,10 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
 template <int KIND>
 static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C, int64_t M, int64_t N, int64_t K,
                   int64_t ldc, cudaStream_t s, int* status_word = nullptr) {
-  const void* a_hi = ws;
-  const void* a_lo = ws + L.a_plane;
-  const void* b_hi = ws + 2 * L.a_plane;
-  const void* b_lo = ws + 2 * L.a_plane + L.b_plane;
+  const void* a_hi = ws + L.a_hi();
+  const void* a_lo = ws + L.a_lo();
+  const void* b_hi = ws + L.b_hi();
+  const void* b_lo = ws + L.b_lo();
   if (variant == 0) {
     // Large problems: a CTA pair per 256x256 tile (least shared-memory traffic per flop); smaller
     // ones: more, smaller tiles keep more SMs busy.
@@ -751,14 +768,23 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
               "gemm (static scratch): mode must be DTN_GEMM_BF16X3 or DTN_GEMM_TF32X3, got %d", mode);
   DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm (static scratch): negative extent");
   if (M == 0 || N == 0) return DTN_OK;
-  DTN_REQUIRE(K > 0, DTN_ERR_INVALID, "gemm (static scratch): K must be positive");
-  DTN_REQUIRE(A != nullptr && B != nullptr && C != nullptr, DTN_ERR_INVALID, "gemm (static scratch): null pointer");
+  DTN_REQUIRE(C != nullptr, DTN_ERR_INVALID, "gemm (static scratch): C is null");
   DTN_REQUIRE(lda >= K && ldb >= N && ldc >= N, DTN_ERR_INVALID,
               "gemm (static scratch): leading dimension smaller than the row");
   DTN_REQUIRE(M < (1LL << 31) && N < (1LL << 31) && K < (1LL << 31), DTN_ERR_UNSUPPORTED,
               "gemm (static scratch): extents must fit 31 bits");
+  cudaStream_t s = as_stream(stream);
+  if (K == 0) {   // an empty sum: C = 0, as dtn_gemm_x3 gives
+    DTN_CUDA_CHECK(cudaMemset2DAsync(C, (size_t)ldc * 4, 0, (size_t)N * 4, (size_t)M, s));
+    return DTN_OK;
+  }
+  DTN_REQUIRE(A != nullptr && B != nullptr, DTN_ERR_INVALID, "gemm (static scratch): operand pointer is null");
   DTN_REQUIRE(aligned_to(A, 4) && aligned_to(B, 4) && aligned_to(C, 4), DTN_ERR_INVALID,
               "gemm (static scratch): pointers must be 4-byte aligned");
+  // This entry point always runs the split kernels and the tensor-memory product kernel. The selections of
+  // dtn_gemm_set_variant that name a tile of that kernel (1, 2, 3, 5) are honoured; 4 and 6 name other kernels
+  // (which use no scratch at all) and fall back to the automatic tile choice here.
+  const int variant = (g_gemm_variant == 4 || g_gemm_variant == 6) ? 0 : g_gemm_variant;
   const PlaneLayout L = plane_layout(mode, M, N, K);
   DTN_REQUIRE(L.total <= kStaticScratchBytes, DTN_ERR_WORKSPACE,
               "gemm (static scratch): %lld x %lld x %lld needs %zu bytes of operand planes, the built-in array holds %zu; "
@@ -767,15 +793,29 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
   StaticScratch scratch;
   int rc;
   if ((rc = static_scratch_for_current_device(&scratch))) return rc;
-  cudaStream_t s = as_stream(stream);
   // Nothing in the array has to start at zero: the split kernels overwrite every byte of the planes the
   // product kernel reads, padding included. The status word is only ever set by a kernel that gave up.
   if (mode == DTN_GEMM_BF16X3) {
     if ((rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, scratch.planes, s))) return rc;
-    return run_tc<0>(g_gemm_variant, scratch.planes, L, C, M, N, K, ldc, s, scratch.status);
+    return run_tc<0>(variant, scratch.planes, L, C, M, N, K, ldc, s, scratch.status);
   }
   if ((rc = run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, scratch.planes, s))) return rc;
-  return run_tc<1>(g_gemm_variant, scratch.planes, L, C, M, N, K, ldc, s, scratch.status);
+  return run_tc<1>(variant, scratch.planes, L, C, M, N, K, ldc, s, scratch.status);
+}
+
+int dtn_gemm_x3_static_status(int* status_out, void* stream) {
+  using namespace dtn;
+  DTN_REQUIRE(status_out != nullptr, DTN_ERR_INVALID, "dtn_gemm_x3_static_status: status_out is null");
+  StaticScratch scratch;
+  int rc;
+  if ((rc = static_scratch_for_current_device(&scratch))) return rc;
+  cudaStream_t s = as_stream(stream);
+  int host = 0;
+  DTN_CUDA_CHECK(cudaMemcpyAsync(&host, scratch.status, sizeof(int), cudaMemcpyDeviceToHost, s));
+  DTN_CUDA_CHECK(cudaStreamSynchronize(s));
+  if (host != 0) DTN_CUDA_CHECK(cudaMemsetAsync(scratch.status, 0, sizeof(int), s));
+  *status_out = host;
+  return DTN_OK;
 }
 
 int dtn_gemm_set_variant(int variant) {
@@ -823,8 +863,7 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
     return gemm_small_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s);
   DTN_REQUIRE(g_gemm_variant != 4, DTN_ERR_INVALID, "gemm: the single-kernel variant has no separate phases");
   if (phase == 3 && g_gemm_variant == 6) {
-    const char* bn = getenv("DTN_GEMM_FUSED_BN");
-    return gemm_fused_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s, bn ? atoi(bn) : 0);
+    return gemm_fused_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s, fused_bn_override());
   }
   DTN_REQUIRE(g_gemm_variant != 6, DTN_ERR_INVALID, "gemm: the fused-split variant has no separate phases");
 

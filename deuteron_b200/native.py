@@ -51,6 +51,7 @@ _SIGNATURES = {
     'dtn_gemm_x3': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, ct.c_size_t, _P],
     'dtn_gemm_x3_phase': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, ct.c_size_t, _I, _P],
     'dtn_gemm_x3_static': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
+    'dtn_gemm_x3_static_status': [ct.POINTER(ct.c_int), _P],
     'dtn_gemm_set_variant': [_I],
     'dtn_attention_f32': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _F, _P],
     'dtn_gqa_fwd': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _I64, _I64, _P],

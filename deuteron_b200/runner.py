@@ -299,10 +299,15 @@ class LocalRunner:
                 ready.append(event)
         ws_ptr, ws_bytes = workspace
         compute.wait_event(right_ready)
+        # B is split once, on its own (1|4: split, keep A), before any block: every block then runs 3|8 (split A, keep
+        # B, multiply), which always takes the plane-reading kernels. A plain phase 3 on the first block could pick a
+        # single-kernel form that writes no planes, and the later blocks would multiply by whatever the workspace held.
+        native.call('dtn_gemm_x3_phase', mode, pointers[left_name], pointers[right_name], pointers[out_name], rows, n, k, k, n, n,
+                    ws_ptr, ws_bytes, 1 | 4, compute.cuda_stream)
         for i in range(blocks):
             compute.wait_event(ready[i])
             native.call('dtn_gemm_x3_phase', mode, pointers[left_name] + i * block_in, pointers[right_name],
-                        pointers[out_name] + i * block_out, rows, n, k, k, n, n, ws_ptr, ws_bytes, 3 | (8 if i else 0),
+                        pointers[out_name] + i * block_out, rows, n, k, k, n, n, ws_ptr, ws_bytes, 3 | 8,
                         compute.cuda_stream)
             done = torch.cuda.Event()
             done.record(compute)

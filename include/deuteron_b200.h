@@ -182,9 +182,12 @@ int dtn_gemm_x3(int mode, const float* A, const float* B, float* C, int64_t M, i
  * operand planes between calls. `phase` is a mask: 1 = split the operands into the workspace,
  * 2 = run the product kernel on the planes in the workspace (3 = both, what dtn_gemm_x3 does);
  * with 4 the A planes already in the workspace are kept (A is not split again), with 8 the B
- * planes are kept. The A planes sit at the start of the workspace and the B planes after them,
- * at an offset that depends on (mode, M, K) only, so a caller that walks row blocks of equal
- * height can split B once and pass 3|8 for every later block. No reference counterpart (the
+ * planes are kept. The B planes sit at the start of the workspace, at a place that depends on
+ * (mode, N, K) only, and the A planes after them: a caller that walks row blocks of A (of any
+ * heights) against one B splits B once (1|4: only B is split) and passes 3|8 for every block,
+ * with the same workspace pointer. Kept A planes are valid only for an unchanged (mode, M, N, K).
+ * With 4 or 8 set the call always runs the split kernels and the tensor-memory product kernel,
+ * never the single-kernel forms (which write no planes). No reference counterpart (the
  * reference splits inside its single kernel). */
 int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
                       int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* workspace,
@@ -194,11 +197,16 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
  * the reference; it exists for hosts that cannot give dtn_gemm_x3 a workspace: programs that
  * handed all device memory to their own pool at start-up and forbid cudaMalloc afterwards (an
  * inference server's arena, a plugin sandbox), and latency-critical loops that cannot afford the
- * device-wide synchronisation a cudaMalloc or cudaFree implies. Same arithmetic, same kernels
- * and the same results as dtn_gemm_x3(mode, ...) for DTN_GEMM_BF16X3 and DTN_GEMM_TF32X3, but the
+ * device-wide synchronisation a cudaMalloc or cudaFree implies. Same arithmetic as
+ * dtn_gemm_x3(mode, ...) for DTN_GEMM_BF16X3 and DTN_GEMM_TF32X3, always through the split
+ * kernels and the tensor-memory product kernel: bit-identical to dtn_gemm_x3 whenever that call
+ * takes the same path (tile variants 1, 2, 3, 5; the automatic choice above about 520^3
+ * multiply-adds and more than 16 rows). Where dtn_gemm_x3 picks its single-kernel forms (small or
+ * skinny products, variants 4 and 6) the two agree to the tolerance of the mode, not bit for bit
+ * (the k order of the accumulation differs); variants 4 and 6 count as "automatic" here. The
  * operand planes go to a fixed 32 MiB array that is part of the library image (every GPU that
  * loads the library holds those 32 MiB until the process exits). This function calls no
- * cudaMalloc, cudaFree or any other allocating routine.
+ * cudaMalloc, cudaFree or any other allocating routine. K = 0 zero-fills C.
  *   - Limit: the planes of (mode, M, N, K) — dtn_gemm_workspace_bytes tells how many bytes — must
  *     fit 32 MiB (bf16x3: 2048^3; tf32x3: about 1448^3). Larger problems are rejected with
  *     DTN_ERR_WORKSPACE and a message that names both sizes.
@@ -207,10 +215,15 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
  *   - All calls on a device share the one array. Calls that can overlap on the GPU (different
  *     streams, or graphs replayed concurrently) race on it: serialise them. Nothing in the
  *     array needs clearing between calls; every byte that is read is rewritten first.
- *   - A bounded wait that runs out inside this variant is recorded in a status word of its own,
- *     which dtn_device_status does not read. */
+ *   - A bounded wait that runs out inside this variant is recorded in a status word of its own
+ *     (also part of the library image), read with dtn_gemm_x3_static_status. */
 int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N,
                        int64_t K, int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/* Reads and clears the status word of dtn_gemm_x3_static on the current device: 0 when every wait
+ * of its kernels completed, else the code of the wait that ran out (the result is then
+ * incomplete). Synchronises `stream`; allocates nothing. No counterpart in the reference. */
+int dtn_gemm_x3_static_status(int* status_out /* host */, void* stream);
 
 /* Copies the block src[rows, cols] (row-major FP32, leading dimension lds) to the same extent at each of the n_dst
  * (at most 7) destination pointers, all with leading dimension ldd: the block is read once and written n_dst times,
@@ -222,7 +235,8 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
 int dtn_push_block(const float* src, int64_t lds, float* const* dsts, int n_dst, int64_t ldd,
                    int64_t rows, int64_t cols, void* stream);
 
-/* Selects the tensor-core GEMM variant (process-wide; for experiments and tests):
+/* Selects the tensor-core GEMM variant for the calling host thread (other threads keep their own
+ * selection, initially 0; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile,
  *   4 = the single-kernel path for small problems (operand split inside the kernel, warp-level
  *   mma.sync products, no workspace; what automatic picks up to about 520^3 multiply-adds and for
@@ -252,7 +266,7 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
                 int64_t Hkv, int64_t S, int64_t D, float scale, int storage,
                 int64_t group_begin, int64_t group_end, void* stream);
 
-/* Selects the attention kernel: 0 = automatic, 1 = FP32 CUDA-core kernel,
+/* Selects the attention kernel for the calling host thread: 0 = automatic, 1 = FP32 CUDA-core kernel,
  * 2 = tensor-core kernel (f16 storage, D = 128, S a multiple of 256), 3 = the same with two
  * softmax warpgroups per query tile (the automatic choice where it applies), 4 and 5 = the
  * CTA-pair form of 2 and 3 (S a multiple of 512; same results, measured slower, kept for comparison),

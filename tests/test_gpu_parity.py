@@ -583,6 +583,51 @@ def test_execute_on_host_buffers_matches_the_resident_path(cuda, runner):
         runner.execute(compile_kernel(graph, meta), {'lhs': x[:-1], 'rhs': y})
 
 
+def test_execute_with_a_tall_left_operand_and_a_narrow_right_one(cuda, runner):
+    # 8 row blocks of 1024 x 128 x 1024: each block alone is small enough for the single-kernel GEMM, which writes no
+    # operand planes; the pipeline must still split B before the first block and multiply every block by those planes
+    m, n, k = 8192, 128, 1024
+    graph, meta = schedules.matmul_example(m, n, k)
+    compiled = compile_kernel(graph, meta, options=Options(contraction_precision='bf16x3'))
+    left, right = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+    poison = cuda.full((64 << 20,), float('nan'), device='cuda:0')   # whatever scratch comes next does not start clean
+    del poison
+    produced = runner.execute(compiled, {'left': left, 'right': right})['result']
+    exact = left.astype(np.float64) @ right.astype(np.float64)
+    assert R.max_relative_error(produced, exact) < 2e-5
+    ops.set_gemm_variant(1)
+    try:
+        resident = ops.gemm(to_device(cuda, left), to_device(cuda, right), 'bf16x3').cpu().numpy()
+    finally:
+        ops.set_gemm_variant(0)
+    np.testing.assert_array_equal(produced, resident)
+
+
+@pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
+@pytest.mark.parametrize('m,blocks', [(1536, 4), (2560, 4), (1000, 3)])
+def test_row_blocks_of_unequal_heights_share_one_split_of_b(cuda, mode, m, blocks):
+    # the walk of sharding.GatheredProduct: B split once (1|4), then every row block with 3|8 and the same workspace
+    from deuteron_b200 import sharding
+    n, k = 768, 640
+    a, b = to_device(cuda, R.seeded_uniform(7, (m, k))), to_device(cuda, R.seeded_uniform(11, (k, n)))
+    rows = sharding.row_blocks_for_overlap(m, blocks)
+    assert len({r1 - r0 for r0, r1 in rows}) > 1 or m == 1000
+    tallest = max(r1 - r0 for r0, r1 in rows)
+    planes = cuda.full((ops.gemm_workspace_bytes(mode, tallest, n, k) + 1024,), 0xFF, dtype=cuda.uint8, device='cuda:0')
+    out = cuda.zeros((m, n), device='cuda:0')
+    r0, r1 = rows[0]
+    ops.gemm(a[r0:r1], b, mode, out=out[r0:r1], workspace=planes, phase=1 | 4)
+    for r0, r1 in rows:
+        ops.gemm(a[r0:r1], b, mode, out=out[r0:r1], workspace=planes, phase=3 | 8)
+    ops.set_gemm_variant(1)
+    try:
+        whole = ops.gemm(a, b, mode)
+    finally:
+        ops.set_gemm_variant(0)
+    ops.check_device_status()
+    assert bool(cuda.equal(out, whole))
+
+
 @pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
 def test_gemm_8192_properties(cuda, mode):
     n = 8192

@@ -69,7 +69,29 @@ def _worker(rank: int, world: int, port: int, queue) -> None:
         gathered = sharding.all_gather_groups(mine, 2, ranges)
         expected = R.gqa_attention_f64(q.numpy(), k.numpy(), v.numpy(), 0.35).astype(np.float32)
         attention_ok = bool(np.array_equal(gathered.numpy(), expected)) and owned == ranges[rank]
-        queue.put((rank, gemm_ok, attention_ok))
+
+        # host-fed product: each rank feeds 1/world of A's rows and its block of B's columns, A's rows are exchanged
+        from deuteron_b200 import Options, compile_kernel, schedules
+        m, n, k = 1280, 512, 128
+        compiled = compile_kernel(*schedules.matmul_example(m, n, k), options=Options(contraction_precision='bf16x3'))
+        full_a, full_b = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+        calls = []
+
+        def cpu_phase_gemm(left, right, mode, out=None, workspace=None, phase=3):
+            calls.append((tuple(left.shape), phase))
+            if phase & 2:
+                out.copy_(torch.from_numpy(R.gemm_f64(left.numpy(), right.numpy()).astype(np.float32)))
+            return out
+
+        product = sharding.ShardedHostProduct(compiled, rank, world, 'cpu', row_blocks=3, gemm=cpu_phase_gemm)
+        begin, end = product.columns
+        fed = product.pack_rows(full_a)
+        block = product.execute(fed, np.ascontiguousarray(full_b[:, begin:end]))
+        expected = R.gemm_f64(full_a, full_b).astype(np.float32)[:, begin:end]
+        host_ok = (bool(np.array_equal(block, expected)) and fed.shape[0] * world == m
+                   and calls[0][1] == 5 and all(phase == 11 for _, phase in calls[1:]) and len(calls) == 4
+                   and product.host_bytes() == (4 * (fed.shape[0] * k + k * (end - begin)), 4 * m * (end - begin)))
+        queue.put((rank, gemm_ok, attention_ok, host_ok))
     finally:
         dist.destroy_process_group()
 
@@ -81,11 +103,11 @@ def test_two_gloo_ranks_assemble_sharded_outputs():
     workers = [context.Process(target=_worker, args=(rank, 2, port, queue)) for rank in range(2)]
     for worker in workers:
         worker.start()
-    results = sorted(queue.get(timeout=120) for _ in workers)
+    results = sorted(queue.get(timeout=60) for _ in workers)
     for worker in workers:
         worker.join(timeout=60)
         assert worker.exitcode == 0
-    assert results == [(0, True, True), (1, True, True)]
+    assert results == [(0, True, True, True), (1, True, True, True)]
 
 
 def test_row_blocks_for_overlap_cover_the_rows_on_tile_boundaries():
@@ -98,3 +120,20 @@ def test_row_blocks_for_overlap_cover_the_rows_on_tile_boundaries():
         assert all(begin % 256 == 0 for begin, _ in ranges)
     with pytest.raises(ValueError):
         sharding.row_blocks_for_overlap(8, 0)
+
+
+def test_a_feed_plan_gives_every_row_to_exactly_one_rank():
+    for m, world, blocks in ((8192, 8, 8), (8192, 2, 4), (1000, 3, 2), (300, 4, 4), (256, 8, 1), (0, 2, 2), (5000, 7, 3)):
+        plan = sharding.a_feed_plan(m, world, blocks)
+        seen = np.zeros(m, dtype=np.int32)
+        for rank in range(world):
+            owned = sharding.owned_rows(plan, rank)
+            assert len(owned) == len(plan)
+            for (begin, end), (row0, row1, share) in zip(owned, plan):
+                assert row0 <= begin <= end <= row1 and end - begin <= share
+                seen[begin:end] += 1
+        assert (seen == 1).all()
+    assert sharding.a_feed_plan(8192, 8, 4) == [(2048 * j, 2048 * (j + 1), 256) for j in range(4)]
+    assert sharding.owned_rows(sharding.a_feed_plan(8192, 8, 4), 3) == [(2048 * j + 768, 2048 * j + 1024) for j in range(4)]
+    with pytest.raises(ValueError):
+        sharding.a_feed_plan(8, 0, 1)

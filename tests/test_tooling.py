@@ -171,3 +171,115 @@ def test_driver_chains_kernels_through_intermediate_buffers(tmp_path, cuda):
     assert report['passed'] and [k['entry'] for k in report['kernels']] == ['k_add_pointwise', 'k_mean']
     with np.load(artifacts / 'c00_chained' / 'actual.npz') as actual:
         np.testing.assert_array_equal(actual['add'], y)
+
+
+def test_command_line_dump_protection_by_every_name_and_all_or_nothing_writes(problem, tmp_path, capsys, monkeypatch):
+    """The negative cases of the reference's tests/test_cli.py, restated: aliases of the inputs, dumps aliasing each
+    other, bad destinations, a failure while staging, a failed rename, a failed compilation, an interrupt."""
+    kernel, meta = problem / 'k_rms_norm.ir.json', problem / 'meta.json'
+    original = {path: path.read_bytes() for path in (kernel, meta)}
+    symlink, hardlink = tmp_path / 'symbolic.ll', tmp_path / 'hard.ll'
+    symlink.symlink_to(kernel)
+    os.link(meta, hardlink)
+    for alias in (kernel, meta, symlink, hardlink):
+        for flag in ('--dump-llvm', '--dump-unoptimized'):
+            assert cli.main([str(kernel), flag, str(alias)]) == 1
+            captured = capsys.readouterr()
+            assert captured.out == '' and 'overwrite an input' in captured.err
+    assert all(path.read_bytes() == content for path, content in original.items())
+    first = tmp_path / 'first.ll'
+    first.write_text('old contents')
+    other_name = tmp_path / 'alias.ll'
+    os.link(first, other_name)
+    for second in (first, first.parent / '.' / first.name, other_name):
+        assert cli.main([str(kernel), '--dump-llvm', str(first), '--dump-unoptimized', str(second)]) == 1
+        captured = capsys.readouterr()
+        assert captured.out == '' and 'different files' in captured.err and first.read_text() == 'old contents'
+    fresh = tmp_path / 'fresh.ll'
+    assert cli.main([str(kernel), '--dump-llvm', str(fresh), '--dump-unoptimized', str(tmp_path / 'sub' / '..' / 'fresh.ll')]) == 1
+    assert not fresh.exists()
+    for invalid in (tmp_path, tmp_path / 'absent' / 'dump.ll'):
+        assert cli.main([str(kernel), '--dump-llvm', str(first), '--dump-unoptimized', str(invalid)]) == 1
+        assert capsys.readouterr().err and first.read_text() == 'old contents'
+    # a failure while the second dump is staged leaves both old files and no staging file
+    second = tmp_path / 'second.ll'
+    second.write_text('old second')
+    before = set(tmp_path.iterdir())
+    factory, calls = cli.tempfile.NamedTemporaryFile, []
+
+    def fail_second_stage(*args, **kwargs):
+        calls.append(1)
+        if len(calls) == 2:
+            raise PermissionError(13, 'write denied', str(second))
+        return factory(*args, **kwargs)
+
+    monkeypatch.setattr(cli.tempfile, 'NamedTemporaryFile', fail_second_stage)
+    assert cli.main([str(kernel), '--dump-llvm', str(first), '--dump-unoptimized', str(second)]) == 1
+    monkeypatch.setattr(cli.tempfile, 'NamedTemporaryFile', factory)
+    captured = capsys.readouterr()
+    assert captured.out == '' and 'write denied' in captured.err
+    assert first.read_text() == 'old contents' and second.read_text() == 'old second' and set(tmp_path.iterdir()) == before
+    # a rename that fails keeps the old file and removes the staging file
+    with monkeypatch.context() as patched:
+        def no_space(self, target):
+            raise OSError(28, 'No space left')
+        patched.setattr(Path, 'replace', no_space)
+        assert cli.main([str(kernel), '--dump-llvm', str(first)]) == 1
+    assert 'No space left' in capsys.readouterr().err and first.read_text() == 'old contents' and set(tmp_path.iterdir()) == before
+    # a failed compilation touches no dump; an interrupt is status 130
+    with monkeypatch.context() as patched:
+        def invalid(*args, **kwargs):
+            raise ValueError('invalid scheduled IR')
+        patched.setattr(cli, 'compile_kernel', invalid)
+        assert cli.main([str(kernel), '--dump-llvm', str(first)]) == 1
+        assert 'invalid scheduled IR' in capsys.readouterr().err and first.read_text() == 'old contents'
+
+        def interrupt(*args, **kwargs):
+            raise KeyboardInterrupt
+        patched.setattr(cli, 'compile_kernel', interrupt)
+        assert cli.main([str(kernel)]) == 130
+        captured = capsys.readouterr()
+        assert captured.out == '' and 'interrupted' in captured.err
+    # diagnostics printed during compilation go to stderr; every option of Options has its flag
+    with monkeypatch.context() as patched:
+        real = cli.compile_kernel
+
+        def noisy(*args, **kwargs):
+            print('compiler diagnostic')
+            return real(*args, **kwargs)
+        patched.setattr(cli, 'compile_kernel', noisy)
+        assert cli.main([str(kernel)]) == 0
+        captured = capsys.readouterr()
+        assert captured.err == 'compiler diagnostic\n' and 'row_fused(' in captured.out
+    import dataclasses
+    from deuteron_b200 import Options
+    helped = cli.build_parser().format_help()
+    assert all('--' + field.name.replace('_', '-') in helped for field in dataclasses.fields(Options))
+    seen = {}
+
+    def record(path, **kwargs):
+        seen.update(kwargs, path=path)
+        return compile_kernel(path)
+    monkeypatch.setattr(cli, 'compile_kernel', record)
+    argv = [str(kernel), '--opt-level', '1', '--unroll', '8', '--vector-width', '16', '--contraction-precision', 'f32']
+    argv += ['--no-' + f.name.replace('_', '-') for f in dataclasses.fields(Options) if isinstance(f.default, bool)]
+    assert cli.main(argv) == 0
+    expected = Options(unroll=8, vector_width=16, contraction_precision='f32',
+                       **{f.name: False for f in dataclasses.fields(Options) if isinstance(f.default, bool)})
+    assert seen['options'] == expected and seen['opt_level'] == 1 and seen['arch'] == 'sm_100a'
+
+
+def test_command_line_survives_a_closed_or_full_stdout(problem):
+    kernel = problem / 'k_rms_norm.ir.json'
+    with subprocess.Popen([sys.executable, '-m', 'deuteron_b200', str(kernel)], cwd=ROOT, stdout=subprocess.PIPE,
+                          stderr=subprocess.PIPE, text=True) as process:
+        process.stdout.close()
+        stderr = process.stderr.read()
+        code = process.wait(timeout=120)
+    assert code == 1 and 'Broken pipe' in stderr and 'Traceback' not in stderr and 'Exception ignored' not in stderr
+    if Path('/dev/full').exists():
+        with open('/dev/full', 'wb') as stream:
+            done = subprocess.run([sys.executable, '-m', 'deuteron_b200', str(kernel)], cwd=ROOT, stdout=stream,
+                                  stderr=subprocess.PIPE, text=True, timeout=120)
+        assert done.returncode == 1 and 'No space left' in done.stderr and 'Traceback' not in done.stderr
+        assert 'Exception ignored' not in done.stderr

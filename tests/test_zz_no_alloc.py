@@ -47,6 +47,13 @@ def _static(cuda, mode, a, b, out=None):
     return out
 
 
+def _static_status(cuda):
+    """The status word the static-scratch kernels report into (not the one dtn_device_status reads)."""
+    word = ct.c_int(-1)
+    native.call('dtn_gemm_x3_static_status', ct.byref(word), cuda.cuda.current_stream().cuda_stream)
+    return word.value
+
+
 @pytest.mark.parametrize('mode', [native.GEMM_MODES['bf16x3'], native.GEMM_MODES['tf32x3']])
 def test_static_scratch_gemm_equals_the_workspace_gemm_twice_in_a_row(cuda, mode):
     # two different problems back to back: the second call reuses the array the first one filled
@@ -65,7 +72,7 @@ def test_static_scratch_gemm_equals_the_workspace_gemm_twice_in_a_row(cuda, mode
             assert float(((produced.double() - exact).abs().max() / exact.abs().max()).item()) < 2e-5
     finally:
         native.call('dtn_gemm_set_variant', 0)
-    assert native.device_status(cuda.cuda.current_stream().cuda_stream) == 0
+    assert _static_status(cuda) == 0
 
 
 def test_static_scratch_gemm_at_its_size_limit_and_beyond(cuda):
@@ -83,3 +90,26 @@ def test_static_scratch_gemm_at_its_size_limit_and_beyond(cuda):
     # an empty product is a no-op, as for the ordinary entry point
     empty = cuda.empty((0, 2048), device='cuda:0')
     assert _static(cuda, mode, empty, b).shape == (0, 2048)
+    # an empty sum (K = 0) zero-fills C, as the ordinary entry point does
+    filled = cuda.full((64, 96), 3.0, device='cuda:0')
+    _static(cuda, mode, cuda.empty((64, 0), device='cuda:0'), cuda.empty((0, 96), device='cuda:0'), out=filled)
+    assert float(filled.abs().max().item()) == 0.0
+    assert _static_status(cuda) == 0
+
+
+def test_static_scratch_gemm_treats_the_scratch_free_variants_as_automatic(cuda):
+    # variants 4 and 6 name kernels that use no scratch; the static entry point runs its own path under them and
+    # agrees with the ordinary entry point to the mode's tolerance
+    mode = native.GEMM_MODES['bf16x3']
+    a, b = _uniform(cuda, 7, (640, 512)), _uniform(cuda, 11, (512, 768))
+    exact = a.double() @ b.double()
+    reference = _static(cuda, mode, a, b)
+    for variant in (4, 6):
+        native.call('dtn_gemm_set_variant', variant)
+        try:
+            produced = _static(cuda, mode, a, b)
+        finally:
+            native.call('dtn_gemm_set_variant', 0)
+        assert bool(cuda.equal(produced, reference))
+        assert float(((produced.double() - exact).abs().max() / exact.abs().max()).item()) < 2e-5
+    assert _static_status(cuda) == 0
