@@ -325,3 +325,61 @@ def test_row_kernel_classification_follows_the_arithmetic_not_the_spelling():
     set_body(graph, graph['nodes']['mul_1']['op_fields']['body'][0].replace(
         "Assign(name='square', op=ElementwiseImpl('multiply'), args=('value', 'value'), ", "Assign(name='square', op=ElementwiseImpl('copy'), args=('value',), "))
     assert compile_kernel(graph, meta).plan.params['reduce'] == 'sum'
+
+
+def test_launch_schema_takes_tuples_and_empty_buffers(vector_add):
+    _, meta = vector_add
+    launch = copy.deepcopy(meta['kernels'][0])
+    launch['grid'], launch['block'] = tuple(launch['grid']), tuple(launch['block'])
+    for arg in launch['args']:
+        arg['shape'] = (0,)
+    assert set(validate_launch(launch)) == {'lhs', 'rhs', 'sum'}
+    for broken in ({'entry': ''}, {'entry': 'a\x00b'}, {'args': 'lhs'}, {'arg_order': None}, {'zero_outputs': 'sum'}):
+        with pytest.raises(ValueError):
+            validate_launch({**launch, **broken})
+    with pytest.raises(ValueError):
+        validate_launch([launch])
+    scalar = copy.deepcopy(launch)
+    scalar['args'][0].update(scalar=True, output=True)
+    with pytest.raises(ValueError, match='scalar arguments'):
+        validate_launch(scalar)
+    huge = copy.deepcopy(launch)
+    huge['args'][0]['shape'] = [2**62, 8]
+    with pytest.raises(ValueError, match='64-bit address space'):
+        validate_launch(huge)
+
+
+@pytest.mark.parametrize('statement,error,fragment', [
+    ("Sync(barrier_id=16, count=None, warp=False)", ValueError, 'barrier id'),
+    ("Sync(barrier_id=1, count=None, warp=False)", ValueError, 'thread count'),
+    ("Sync(barrier_id=1, count=64, warp=True)", ValueError, 'named barrier'),
+    ("Sync(barrier_id=0, count=48, warp=False)", ValueError, 'multiple of 32'),
+    ("Sync(barrier_id=0, count=256, warp=False)", ValueError, 'within the block'),
+    ("CpAsyncWait(group=8)", ValueError, 'wait group'),
+    ("Smem(name='lhs', extents=(4,), dtype='float', align=16)", ValueError, 'duplicate buffer name'),
+    ("Smem(name='stage', extents=(4,), dtype='float', align=24)", ValueError, 'power of two'),
+    ("Smem(name='stage', extents=(-4,), dtype='float', align=16)", ValueError, 'shared extents'),
+    ("CpAsyncCopy(smem='stage', smem_index=(Literal(value=0, dtype='int'),), src='lhs', src_index=(Literal(value=0, dtype='int'),), "
+     "nbytes=12, swizzle='NONE', lane_index=None, lane_rows=None)", ValueError, 'unknown buffer'),
+    ("Load(names=('a',), input='nowhere', index=(Literal(value=0, dtype='int'),), dtype='float')", ValueError, 'unknown buffer'),
+    ("StridedLoop(axis=Axis(name='i', extent=Dim(8), window=None), start=Literal(value=0, dtype='int'), step=Literal(value=0, dtype='int'), "
+     "body=(), unroll=1, end=None, seed=False)", ValueError, 'positive integer step'),
+    ("Loop(axis=Axis(name='i', extent=Dim(-1), window=None), body=(), unroll=1, seed=False)", NotImplementedError, 'axis extents'),
+])
+def test_statement_checks_reject_incoherent_kernels(vector_add, statement, error, fragment):
+    graph, meta = vector_add
+    set_body(graph, "Tile(axes=(Axis(name='item', extent=Dim(515), window=None),), body=(" + statement + ",), block_threads=128)")
+    with pytest.raises(error, match=fragment):
+        compile_kernel(graph, meta)
+
+
+def test_tile_checks(vector_add):
+    graph, meta = vector_add
+    for tile, fragment in (("Tile(axes=(), body=(), block_threads=128)", 'distinct axes'),
+                           ("Tile(axes=(Axis(name='i', extent=Dim(0), window=None),), body=(), block_threads=128)", 'distinct axes'),
+                           ("Tile(axes=(Axis(name='i', extent=Dim(4), window=None), Axis(name='i', extent=Dim(4), window=None)), body=(), "
+                            "block_threads=128)", 'distinct axes'),
+                           ("Tile(axes=(Axis(name='i', extent=Dim(4), window=None),), body=(), block_threads=64)", 'block_threads')):
+        set_body(graph, tile)
+        with pytest.raises(ValueError, match=fragment):
+            compile_kernel(graph, meta)
