@@ -159,54 +159,90 @@ def cpu_gemm_sample(seconds_target: float = 12.0) -> dict:
             'rows': rows, 'seconds': elapsed}
 
 
+def _graph_latency_us(torch, stream, call, launches: int, samples: int = 7) -> float:
+    """The reference's timing protocol (benchmark.py:244-268): a CUDA graph of `launches` launches, median of
+    `samples` event timings, microseconds per launch."""
+    with torch.cuda.stream(stream):
+        for _ in range(min(launches, 20)):
+            call()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(launches):
+                call()
+        graph.replay()
+        stream.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        timings = []
+        for _ in range(samples):
+            begin.record(stream)
+            graph.replay()
+            end.record(stream)
+            end.synchronize()
+            timings.append(begin.elapsed_time(end) * 1000 / launches)
+    return statistics.median(timings)
+
+
 def reference_kernel_baseline(torch, ops) -> dict | None:
-    """The second baseline beside the CPU one: the reference's own emitted kernel (its committed tf32x3 PTX for the
-    128^3 example, assembled for sm_100a by oracle/build_ref.py) timed on this GPU next to this build's kernel for the
-    same problem, both as the reference times kernels (CUDA graph of 200 launches, median of 7). None when the cubin
-    was not built."""
+    """The second baseline beside the CPU one: the reference's own kernels on this GPU next to this build's kernels for
+    the same problems, both timed as the reference times kernels. Two sets (oracle/build_ref.py): the tf32x3 PTX file
+    the reference committed itself (128^3), and the kernels its unmodified compiler emits for sm_100 at 128^3, 512^3,
+    2048^3 and 8192^3 in both compensated modes (mma.sync, 32 x 64 tiles, 512-thread CTAs: the schedule of its
+    examples/tensor_matmul scaled up). Maximum errors are relative to max|exact|, exact = float64 product on the GPU
+    (64 sampled rows above 2048). None when nothing was built."""
     from oracle import ref_kernel, reference_math as oracle
     if not ref_kernel.available():
         return None
-    import statistics
     device = torch.device('cuda', 0)
+    stream = torch.cuda.Stream(device)
     left = torch.from_numpy(oracle.seeded_normal(7, (128, 128))).to(device)
     right = torch.from_numpy(oracle.seeded_normal(11, (128, 128))).to(device)
     theirs, mine = torch.empty((128, 128), device=device), torch.empty((128, 128), device=device)
     reference = ref_kernel.ReferenceMatmul()
-    stream = torch.cuda.Stream(device)
-
-    def graph_latency(call) -> float:
-        with torch.cuda.stream(stream):
-            for _ in range(20):
-                call()
-            stream.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                for _ in range(200):
-                    call()
-            graph.replay()
-            stream.synchronize()
-            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            samples = []
-            for _ in range(7):
-                begin.record(stream)
-                graph.replay()
-                end.record(stream)
-                end.synchronize()
-                samples.append(begin.elapsed_time(end) * 1000 / 200)
-        return statistics.median(samples)
-
     try:
         with torch.cuda.stream(stream):
-            reference_us = graph_latency(lambda: reference.launch(right.data_ptr(), left.data_ptr(), theirs.data_ptr(), stream.cuda_stream))
-            ours_us = graph_latency(lambda: ops.gemm(left, right, 'tf32x3', out=mine))
+            reference_us = _graph_latency_us(torch, stream, lambda: reference.launch(right.data_ptr(), left.data_ptr(), theirs.data_ptr(), stream.cuda_stream), 200)
+            ours_us = _graph_latency_us(torch, stream, lambda: ops.gemm(left, right, 'tf32x3', out=mine), 200)
         stream.synchronize()
         identical = bool(torch.equal(theirs, mine))
     finally:
         reference.close()
-    return {'workload': 'gemm_tf32x3_128x128x128 (examples/tensor_matmul)', 'reference_kernel': 'matmul_tiled_128, the reference\'s committed PTX '
-            '(docs/video/demo/capture/kernel.ptx) assembled for sm_100a', 'reference_median_us': reference_us, 'ours_median_us': ours_us,
-            'outputs_bit_identical': identical, 'timing': 'CUDA graph of 200 launches, median of 7'}
+    out = {'workload': 'gemm_tf32x3_128x128x128 (examples/tensor_matmul)', 'reference_kernel': 'matmul_tiled_128, the reference\'s committed PTX '
+           '(docs/video/demo/capture/kernel.ptx) assembled for sm_100a', 'reference_median_us': reference_us, 'ours_median_us': ours_us,
+           'outputs_bit_identical': identical, 'timing': 'CUDA graph of 200 launches, median of 7'}
+    compiled = []
+    available = ref_kernel.manifest()
+    generator = torch.Generator(device=device)
+    for n, launches in ((128, 200), (512, 200), (2048, 20), (8192, 3)):
+        generator.manual_seed(7)
+        a = torch.rand((n, n), device=device, generator=generator) * 2 - 1
+        generator.manual_seed(11)
+        b = torch.rand((n, n), device=device, generator=generator) * 2 - 1
+        rows = torch.arange(0, n, max(1, n // 64), device=device) if n > 2048 else torch.arange(n, device=device)
+        exact = a[rows].double() @ b.double()
+        scale = float(exact.abs().max().item())
+        for mode in ('bf16x3', 'tf32x3'):
+            name = f'gemm_{mode}_{n}'
+            if name not in available:
+                continue
+            c_ref, c_mine = torch.zeros((n, n), device=device), torch.zeros((n, n), device=device)
+            with ref_kernel.ReferenceKernel(name) as kernel:
+                pointers = {'left': a.data_ptr(), 'right': b.data_ptr(), 'result': c_ref.data_ptr()}
+                with torch.cuda.stream(stream):
+                    their_us = _graph_latency_us(torch, stream, lambda: kernel.launch(pointers, stream.cuda_stream), launches, 5)
+                    our_us = _graph_latency_us(torch, stream, lambda: ops.gemm(a, b, mode, out=c_mine), launches, 5)
+                stream.synchronize()
+            compiled.append({'workload': f'gemm_{mode}_{n}x{n}x{n}', 'reference_median_us': their_us, 'ours_median_us': our_us,
+                             'reference_tflops': 2.0 * n ** 3 / their_us / 1e6, 'ours_tflops': 2.0 * n ** 3 / our_us / 1e6,
+                             'reference_max_rel_error': float((c_ref[rows].double() - exact).abs().max().item()) / scale,
+                             'ours_max_rel_error': float((c_mine[rows].double() - exact).abs().max().item()) / scale,
+                             'outputs_bit_identical': bool(torch.equal(c_ref, c_mine)), 'launches_per_graph': launches,
+                             'reference_registers': available[name].get('registers'), 'reference_grid': available[name]['grid'][0]})
+        del a, b, exact
+    if compiled:
+        out['compiled_by_the_reference_for_sm_100'] = compiled
+        out['compiled_how'] = 'unmodified reference compiler (arch sm_100, opt_level 3) with stand-ins for the absent emmy-ml IR classes; ptxas -arch=sm_100a'
+    return out
 
 
 def run_reference(args) -> None:
@@ -469,9 +505,9 @@ def run_ours(args) -> None:
     wall_begin = time.perf_counter()
     for step in range(args.steps):
         events[step][0].record()
-        ops.gemm(a, b, 'bf16x3', out=c, phase=1)      # operand split: 2 kernels at this size (A rows, B tiles)
+        ops.gemm(a, b, 'bf16x3', out=c, phase=1 | 4)  # split of the rank's columns of B: 1 kernel
         events[step][1].record()
-        ops.gemm(a, b, 'bf16x3', out=c, phase=2)      # tensor-core product kernel: 1 kernel
+        ops.gemm(a, b, 'bf16x3', out=c, phase=3 | 8)  # product kernel, which splits A beside its products: 1 kernel
         events[step][2].record()
     barrier()
     wall_end = time.perf_counter()
@@ -633,25 +669,26 @@ def run_ours(args) -> None:
         peak = peaks['bf16_tflops'] / 3.0
         flops_per_rank = 2.0 * M * width * K
         achieved = flops_per_rank / product_ms / 1e9
-        algorithmic_bytes = 2 * 2 * (M * K + width * K) + 4 * M * width   # four bf16 planes read once + C written once
+        algorithmic_bytes = 8 * M * K + 2 * 2 * (M * K + width * K) + 4 * M * width   # A read and its planes written; four planes read once; C written
         line = {
             'metric': 'bf16x3_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
             'warmup': max(args.warmup, 3), 'ms_per_step': total_ms / args.steps, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'bf16x3 (bf16 hi/lo operands, f32 accumulate, f32 in/out)', 'data': 'synthetic',
             'config': bench_config(world),
-            'step': f'operand split (2 kernels: all rows of A, the rank\'s {width} columns of B) + tcgen05 product kernel (1 kernel)',
+            'step': f'split of the rank\'s {width} columns of B (1 kernel) + tcgen05 product kernel with the split of A running '
+                    'inside it (1 kernel, preceded by a memset of its counters)',
             'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak,
                          'frac_of_nominal': achieved / (2250.0 / 3.0),
                          'traffic': PRODUCT_KERNEL_DRAM_BYTES if world == 1 else None,
                          'traffic_note': 'bytes per launch from the committed ncu capture of the 8192^3 launch; algorithmic '
                          f'bytes per launch of this rank {algorithmic_bytes:.3e}',
-                         'kernel': 'gemm_x3_kernel (product kernel only, rank 0)', 'ms_per_launch': product_ms,
+                         'kernel': 'gemm_x3_stream_kernel (products + split of A, rank 0)', 'ms_per_launch': product_ms,
                          'ms_per_launch_slowest_rank': slowest_product_ms, 'split_ms_per_step': split_ms,
                          'peak_source': f"{peaks['source']} dense bf16 burst peak {peaks['bf16_tflops']} TFLOP/s / 3 products; "
                                         'frac_of_nominal uses the nominal 2250 TFLOP/s / 3'},
             'clocks': clocks,
             'e2e': e2e,
-            'gpu_launches': 3 * args.steps,
+            'gpu_launches': 2 * args.steps,
             'max_rel_error_vs_f64_sampled_rows': rel_error,
         }
         if line['roofline']['frac'] > 1.0:

@@ -19,6 +19,9 @@
 #include <stdlib.h>
 
 #include <mutex>
+#include <type_traits>
+#include <algorithm>
+#include <vector>
 
 #include "dtn_common.cuh"
 #include "sm100_ptx.cuh"
@@ -218,8 +221,12 @@ __device__ __forceinline__ void split_transpose_bf16_vec(const float* __restrict
 template <class KIND>
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
-                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo, int b_vec_ok) {
+                       typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo, int b_vec_ok,
+                       int* __restrict__ zero_words, int zero_count) {
   ptx::launch_dependents();
+  // the product kernel behind this grid claims split items from a counter and publishes flags: start them at zero
+  if (zero_words != nullptr && blockIdx.x == 0 && blockIdx.y == 0)
+    for (int i = threadIdx.x; i < zero_count; i += blockDim.x) zero_words[i] = 0;
   if constexpr (KIND::kElemBytes == 2) {
     if (b_vec_ok) {
       split_transpose_bf16_vec(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
@@ -499,6 +506,407 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
 }
 
 // ---------------------------------------------------------------------------------------
+// Stream kernel: CTA-pair tiles 256 rows tall and 64..256 columns wide from a host-made schedule,
+// with the split of A running inside the kernel beside the products.
+//
+//  * Schedule. A persistent grid of W CTA pairs walks `rounds` rounds; in round j pair w multiplies
+//    the tile entry[j * W + w] (0 = nothing). The host cuts every 256-row band of C into pieces of
+//    different widths (multiples of 32 columns) so that the pairs finish together: with 128 tiles of
+//    256 x 256 on 74 pairs a uniform walk costs two full rounds for 1.73 rounds of work, the cut costs
+//    1.75. Tile width changes nothing in the arithmetic of an output element (same k order).
+//    rounds == 0: tiles come from the raster formula of gemm_x3_kernel (large problems, where the
+//    last round hardly matters).
+//  * Split of A. Eight more warps per CTA turn FP32 rows of A into the hi / lo planes while the
+//    products run: work items of one band (256 rows) x 128 columns of k are claimed from a counter in
+//    the workspace, converted, and published through one flag per item (release store); the thread
+//    that issues the TMA loads reads the flag (acquire) before it loads the first k-block of an item,
+//    then orders that against the TMA unit's reads (fence.proxy.async). Items are numbered in the
+//    order the tiles need them: the bands of the first round k-chunk by k-chunk, then the later bands.
+//    Whoever claims an item completes it without waiting for anything, so the flags never deadlock;
+//    the wait on a flag is bounded like every other wait here. B's planes are written by the
+//    transposing split kernel before this kernel (which also clears counter and flags).
+// ---------------------------------------------------------------------------------------
+constexpr int kStreamThreads = 192 + 256;     // roles of gemm_x3_kernel + 8 split warps
+constexpr int kSchedMaxEntries = 640;
+constexpr int kSplitItemK = 128;              // k-extent of one split item
+
+struct TileSchedule {
+  uint32_t rounds;                            // 0: raster formula
+  uint32_t workers;                           // CTA pairs = entries per round
+  uint32_t entry[kSchedMaxEntries];           // band | (col0 / 32) << 12 | (width / 32) << 24
+};
+
+struct SplitWork {
+  const float* A;
+  int64_t lda;
+  void* a_hi;
+  void* a_lo;
+  int* ctrl;          // [0] claim counter, [1] finished items, [2 + band * chunks + chunk] item flags; all zero at launch
+  int M, K, Kp;
+  int bands, chunks;  // 256-row bands of A, kSplitItemK-wide chunks of k
+  int group_bands;    // bands whose items are numbered chunk-major together (those of the first round)
+  int items;          // bands * chunks, or 0: the planes are already there
+  int vec_ok;         // A 16-byte aligned and lda % 4 == 0
+};
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu(int* p, int v) {
+  asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+__device__ __forceinline__ void bar_sync_named(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// Item number -> (band, chunk): groups of `group_bands` bands, chunk-major inside a group.
+__device__ __forceinline__ void split_item_coords(const SplitWork& w, int item, int& band, int& chunk) {
+  const int per_group = w.group_bands * w.chunks;
+  const int groups = (w.bands + w.group_bands - 1) / w.group_bands;
+  int g = item / per_group;
+  if (g >= groups) g = groups - 1;
+  const int first = g * w.group_bands;
+  const int gsize = min(w.group_bands, w.bands - first);
+  const int r = item - g * per_group;
+  chunk = r / gsize;
+  band = first + r % gsize;
+}
+
+// One item: rows [band * 256, +256) x k [chunk * 128, +128) of A -> both planes. Warp `sw` of the eight takes rows
+// sw, sw + 8, ...; a lane converts four consecutive k of a row per step, eight rows in flight.
+template <class KIND>
+__device__ __forceinline__ void split_item(const SplitWork& w, int band, int chunk, int sw, int lane) {
+  using E = typename KIND::elem;
+  E* __restrict__ hi = static_cast<E*>(w.a_hi);
+  E* __restrict__ lo = static_cast<E*>(w.a_lo);
+  const int k = chunk * kSplitItemK + lane * 4;
+  if (k >= w.Kp) return;
+  const int row0 = band * 256 + sw;
+  const bool full_k = k + 3 < w.K;
+#pragma unroll 1
+  for (int batch = 0; batch < 4; ++batch) {
+    float4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int row = row0 + (batch * 8 + j) * 8;
+      v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (row < w.M) {
+        const float* src = w.A + (int64_t)row * w.lda + k;
+        if (full_k && w.vec_ok) {
+          v[j] = ld_stream_f4(reinterpret_cast<const float4*>(src));
+        } else {
+          if (k < w.K) v[j].x = src[0];
+          if (k + 1 < w.K) v[j].y = src[1];
+          if (k + 2 < w.K) v[j].z = src[2];
+          if (k + 3 < w.K) v[j].w = src[3];
+        }
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int row = row0 + (batch * 8 + j) * 8;
+      if (row >= w.M) continue;
+      __align__(16) E h[4];
+      __align__(16) E l[4];
+      KIND::split(v[j].x, h[0], l[0]);
+      KIND::split(v[j].y, h[1], l[1]);
+      KIND::split(v[j].z, h[2], l[2]);
+      KIND::split(v[j].w, h[3], l[3]);
+      const int64_t o = (int64_t)row * w.Kp + k;
+      if constexpr (KIND::kElemBytes == 2) {
+        *reinterpret_cast<uint2*>(hi + o) = *reinterpret_cast<uint2*>(h);
+        *reinterpret_cast<uint2*>(lo + o) = *reinterpret_cast<uint2*>(l);
+      } else {
+        *reinterpret_cast<uint4*>(hi + o) = *reinterpret_cast<uint4*>(h);
+        *reinterpret_cast<uint4*>(lo + o) = *reinterpret_cast<uint4*>(l);
+      }
+    }
+  }
+}
+
+template <int KIND /*0 = bf16, 1 = tf32*/>
+__global__ void __launch_bounds__(kStreamThreads, 1)
+gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
+                      const __grid_constant__ CUtensorMap tm_b_hi, const __grid_constant__ CUtensorMap tm_b_lo,
+                      const __grid_constant__ CUtensorMap tm_b16_hi, const __grid_constant__ CUtensorMap tm_b16_lo,
+                      float* __restrict__ C, int64_t ldc, int M, int N, int num_kb, int tiles_m, int tiles_n,
+                      int group_m, int c_vec_ok, int* __restrict__ status, const __grid_constant__ SplitWork sw,
+                      const __grid_constant__ TileSchedule sched) {
+  using Cfg = GemmCfg<2, 256>;
+  using SplitKind = typename std::conditional<KIND == 0, Bf16Kind, Tf32Kind>::type;
+  constexpr int kStages = Cfg::kStages;
+  constexpr int kBlockKElems = (KIND == 0) ? 64 : 32;
+  constexpr int kKbPerItem = kSplitItemK / kBlockKElems;
+
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t tiles_addr = (raw_addr + 1023u) & ~1023u;
+  uint8_t* tiles_ptr = smem_raw + (tiles_addr - raw_addr);
+  uint8_t* bar_ptr = tiles_ptr + kStages * Cfg::kStageBytes;
+  const uint32_t bar_addr = tiles_addr + kStages * Cfg::kStageBytes;
+  auto full_bar = [&](int s) { return bar_addr + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_addr + 8u * (kStages + s); };
+  auto tfull_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + a); };
+  auto tempty_bar = [&](int a) { return bar_addr + 8u * (2 * kStages + 2 + a); };
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * (2 * kStages + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 8);
+  volatile int* claimed = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 16);   // two slots
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = ptx::cluster_ctarank();
+  const int unit = blockIdx.x >> 1;
+  const int num_units = gridDim.x >> 1;
+  const int num_tiles = tiles_m * tiles_n;
+  const int steps = sched.rounds ? (int)sched.rounds : (num_tiles + num_units - 1) / num_units;
+
+  // Tile of this pair in step j: band (256 rows), first column, width; false when the pair has nothing in that step.
+  auto tile_of = [&](int j, int& band, int& col0, int& width) -> bool {
+    if (sched.rounds) {
+      const uint32_t e = sched.entry[j * (int)sched.workers + unit];
+      if (e == 0) return false;
+      band = (int)(e & 0xfffu);
+      col0 = (int)((e >> 12) & 0xfffu) * 32;
+      width = (int)(e >> 24) * 32;
+      return true;
+    }
+    const int t = unit + j * num_units;
+    if (t >= num_tiles) return false;
+    int tn;
+    tile_coords(t, tiles_m, tiles_n, group_m, band, tn);
+    col0 = tn * 256;
+    width = 256;
+    return true;
+  };
+
+  if (threadIdx.x == 0) {
+    *abort_flag = 0;
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(full_bar(s), 1);
+      ptx::mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      ptx::mbar_init(tfull_bar(a), 1);
+      ptx::mbar_init(tempty_bar(a), 8);
+    }
+    ptx::mbar_fence_init();
+    ptx::fence_proxy_async_smem();
+    ptx::tma_prefetch_desc(&tm_a_hi);
+    ptx::tma_prefetch_desc(&tm_a_lo);
+    ptx::tma_prefetch_desc(&tm_b_hi);
+    ptx::tma_prefetch_desc(&tm_b_lo);
+    ptx::tma_prefetch_desc(&tm_b16_hi);
+    ptx::tma_prefetch_desc(&tm_b16_lo);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc<2>(smem_u32(tmem_holder), Cfg::kTmemCols);
+    ptx::tmem_relinquish<2>();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::cluster_sync_all();
+  ptx::tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+  // The kernel before this one in the stream writes B's planes and clears counter and flags.
+  ptx::grid_dependency_wait();
+
+  if (warp == 0) {
+    // ------------------------------- TMA producer --------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      bool all_split = sw.items == 0;   // once every item is finished no flag needs looking at any more
+      const uint32_t leader_full0 = ptx::map_to_cta(full_bar(0), 0);
+      for (int j = 0; j < steps && ok; ++j) {
+        int band, col0, width;
+        if (!tile_of(j, band, col0, width)) continue;
+        const int half = width >> 1;
+        const int row_a = band * 256 + (int)rank * 128;
+        const int row_b = col0 + (int)rank * half;
+        const uint32_t stage_bytes = 2u * (uint32_t)Cfg::kABytes + 2u * (uint32_t)half * kTileRowBytes;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!all_split && (kb % kKbPerItem) == 0) {
+            // the rows of A this k-block reads are converted inside this kernel: wait for their item
+            const int* flag = sw.ctrl + 2 + band * sw.chunks + kb / kKbPerItem;
+            if (ld_acquire_gpu(sw.ctrl + 1) == sw.items) {
+              all_split = true;
+            } else if (ld_acquire_gpu(flag) == 0) {
+              const long long start = clock64();
+              while (ld_acquire_gpu(flag) == 0) {
+                if (*abort_flag || clock64() - start > ptx::kWaitBudgetCycles) {
+                  *abort_flag = 1;
+                  atomicExch(status, 0x500 | (int)(blockIdx.x & 0xff));
+                  ok = false;
+                  break;
+                }
+                __nanosleep(64);
+              }
+              if (!ok) break;
+            }
+            fence_proxy_async_all();
+          }
+          if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
+            atomicExch(status, 0x100 | (int)(blockIdx.x & 0xff));
+            ok = false;
+            break;
+          }
+          const uint32_t sa_hi = tiles_addr + stage * Cfg::kStageBytes;
+          const uint32_t sa_lo = sa_hi + Cfg::kABytes;
+          const uint32_t sb_hi = sa_lo + Cfg::kABytes;
+          const uint32_t sb_lo = sb_hi + Cfg::kBBytes;
+          const int kx = kb * kBlockKElems;
+          const uint32_t fb = leader_full0 + 8u * stage;
+          if (rank == 0) ptx::mbar_expect_tx(full_bar(stage), 2u * stage_bytes);
+          ptx::tma_load_2d_pair(sa_hi, &tm_a_hi, kx, row_a, fb);
+          ptx::tma_load_2d_pair(sa_lo, &tm_a_lo, kx, row_a, fb);
+          if (half == 128) {
+            ptx::tma_load_2d_pair(sb_hi, &tm_b_hi, kx, row_b, fb);
+            ptx::tma_load_2d_pair(sb_lo, &tm_b_lo, kx, row_b, fb);
+          } else {
+            for (int r = 0; r < half; r += 16) {
+              ptx::tma_load_2d_pair(sb_hi + (uint32_t)r * kTileRowBytes, &tm_b16_hi, kx, row_b + r, fb);
+              ptx::tma_load_2d_pair(sb_lo + (uint32_t)r * kTileRowBytes, &tm_b16_lo, kx, row_b + r, fb);
+            }
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+    __syncwarp();
+  } else if (warp == 1) {
+    // ------------------------------- MMA issuer ----------------------------------------
+    if (lane == 0 && rank == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int iter = 0;
+      bool ok = true;
+      for (int j = 0; j < steps && ok; ++j) {
+        int band, col0, width;
+        if (!tile_of(j, band, col0, width)) continue;
+        const uint32_t idesc = ptx::umma_idesc(KIND == 0 ? 1 : 2, 256, width);
+        const int acc = iter & 1;
+        const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+        ++iter;
+        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
+          atomicExch(status, 0x200 | (int)(blockIdx.x & 0xff));
+          break;
+        }
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
+            atomicExch(status, 0x300 | (int)(blockIdx.x & 0xff));
+            ok = false;
+            break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t sa_hi = tiles_addr + stage * Cfg::kStageBytes;
+          const uint32_t sa_lo = sa_hi + Cfg::kABytes;
+          const uint32_t sb_hi = sa_lo + Cfg::kABytes;
+          const uint32_t sb_lo = sb_hi + Cfg::kBBytes;
+          const uint64_t da_hi = ptx::umma_desc_sw128(sa_hi), da_lo = ptx::umma_desc_sw128(sa_lo);
+          const uint64_t db_hi = ptx::umma_desc_sw128(sb_hi), db_lo = ptx::umma_desc_sw128(sb_lo);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const uint64_t o = (uint64_t)(2 * k);
+            ptx::umma_ss<KIND, 2>(d_tmem, da_lo + o, db_hi + o, idesc, (kb | k) != 0 ? 1u : 0u);
+            ptx::umma_ss<KIND, 2>(d_tmem, da_hi + o, db_lo + o, idesc, 1u);
+            ptx::umma_ss<KIND, 2>(d_tmem, da_hi + o, db_hi + o, idesc, 1u);
+          }
+          ptx::umma_commit<2>(empty_bar(stage));
+          if (++stage == kStages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) ptx::umma_commit<2>(tfull_bar(acc));
+      }
+    }
+    __syncwarp();
+  } else if (warp < 6) {
+    // ------------------------------- epilogue ------------------------------------------
+    const int quarter = warp & 3;
+    const uint32_t leader_tempty0 = ptx::map_to_cta(tempty_bar(0), 0);
+    int iter = 0;
+    for (int j = 0; j < steps; ++j) {
+      int band, col0, width;
+      if (!tile_of(j, band, col0, width)) continue;
+      const int acc = iter & 1;
+      const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
+      ++iter;
+      const bool ready = ptx::mbar_wait(tfull_bar(acc), acc_phase, abort_flag);
+      if (!__all_sync(0xffffffffu, ready)) {
+        if (lane == 0) atomicExch(status, 0x400 | (int)(blockIdx.x & 0xff));
+        break;
+      }
+      ptx::tc_fence_after();
+      const int row = band * 256 + (int)rank * 128 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256);
+      float* crow = C + (int64_t)row * ldc + col0;
+#pragma unroll 1
+      for (int c = 0; c < width / 32; ++c) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_row + (uint32_t)(c * 32), r);
+        ptx::tmem_ld_wait();
+        if (row < M) {
+          if (c_vec_ok && col0 + c * 32 + 32 <= N) {
+#pragma unroll
+            for (int q = 0; q < 8; ++q)
+              *reinterpret_cast<uint4*>(crow + c * 32 + 4 * q) =
+                  make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+          } else {
+#pragma unroll
+            for (int q = 0; q < 32; ++q)
+              if (col0 + c * 32 + q < N) crow[c * 32 + q] = __uint_as_float(r[q]);
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive_cluster(leader_tempty0 + 8u * acc);
+    }
+  } else {
+    // ------------------------------- split of A ----------------------------------------
+    const int st = (int)threadIdx.x - 192;      // 0..255
+    const int swarp = st >> 5;
+    int parity = 0;
+    while (sw.items) {
+      if (st == 0) claimed[parity] = atomicAdd(sw.ctrl, 1);
+      bar_sync_named(1, 256);
+      const int item = claimed[parity];
+      parity ^= 1;
+      if (item >= sw.items) break;
+      int band, chunk;
+      split_item_coords(sw, item, band, chunk);
+      split_item<SplitKind>(sw, band, chunk, swarp, lane);
+      __threadfence();            // this thread's plane stores are visible device-wide ...
+      fence_proxy_async_all();    // ... also to reads made by the TMA unit
+      bar_sync_named(1, 256);
+      if (st == 0) {
+        st_release_gpu(sw.ctrl + 2 + band * sw.chunks + chunk, 1);
+        red_release_gpu_add(sw.ctrl + 1, 1);
+      }
+    }
+  }
+
+  // ------------------------------- teardown --------------------------------------------
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  ptx::cluster_sync_all();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc<2>(tmem_base, Cfg::kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Host side
 // ---------------------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -564,7 +972,11 @@ static int raster_group_m() {
 struct PlaneLayout {
   int64_t Kp;
   size_t a_plane, b_plane;  // bytes of one plane, rounded to 1024
+  size_t ctrl_bytes;        // claim counter and item flags of the in-kernel split of A, after the planes
+  int bands, chunks;        // 256-row bands of A and kSplitItemK-wide chunks of k: one flag each
   size_t total;
+  size_t planes() const { return 2 * a_plane + 2 * b_plane; }
+  size_t ctrl() const { return planes(); }
   size_t b_hi() const { return 0; }
   size_t b_lo() const { return b_plane; }
   size_t a_hi() const { return 2 * b_plane; }
@@ -578,7 +990,10 @@ static PlaneLayout plane_layout(int mode, int64_t M, int64_t N, int64_t K) {
   auto round1k = [](size_t v) { return (v + 1023) & ~(size_t)1023; };
   L.a_plane = round1k((size_t)M * L.Kp * eb);
   L.b_plane = round1k((size_t)N * L.Kp * eb);
-  L.total = 2 * L.a_plane + 2 * L.b_plane;
+  L.bands = (int)((M + 255) / 256);
+  L.chunks = (int)((L.Kp + kSplitItemK - 1) / kSplitItemK);
+  L.ctrl_bytes = round1k(sizeof(int) * (2 + (size_t)L.bands * L.chunks));
+  L.total = L.planes() + L.ctrl_bytes;
   return L;
 }
 
@@ -637,7 +1052,8 @@ static int launch_tc(const void* a_hi, const void* a_lo, const void* b_hi, const
 
 template <class KIND>
 static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                     const PlaneLayout& L, uint8_t* ws, cudaStream_t s, bool do_a = true, bool do_b = true) {
+                     const PlaneLayout& L, uint8_t* ws, cudaStream_t s, bool do_a = true, bool do_b = true,
+                     bool zero_ctrl = false) {
   using E = typename KIND::elem;
   E* a_hi = reinterpret_cast<E*>(ws + L.a_hi());
   E* a_lo = reinterpret_cast<E*>(ws + L.a_lo());
@@ -651,7 +1067,7 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
     // two launches are faster (8192^3: 84 + 102 us against 207 us in one: the row split then runs at the occupancy of
     // its own registers, not at that of the transposing split's shared-memory tile).
     const bool one_launch = (double)M * (double)K + (double)K * (double)N < 2.0 * 4096.0 * 4096.0;
-    if (do_a && do_b && one_launch && a_blocks + b_blocks < (int64_t)2000000000) {
+    if (do_a && do_b && !zero_ctrl && one_launch && a_blocks + b_blocks < (int64_t)2000000000) {
       const int vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
       split_both_kernel<KIND><<<(unsigned)(a_blocks + b_blocks), 256, 0, s>>>(A, lda, (int)K, (int)L.Kp, a_hi, a_lo, vec_ok,
                                                                              (int)ax, (int)a_blocks, B, ldb, (int)N, b_hi,
@@ -679,13 +1095,213 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
       const int cnt = (int)((ny - y0) < 65535 ? (ny - y0) : 65535);
       dim3 grid((unsigned)(L.Kp / KIND::kBlockK), (unsigned)cnt);
       const int64_t n_off = y0 * 64;
+      const bool zero_here = zero_ctrl && y0 == 0;
       split_transpose_kernel<KIND><<<grid, 256, 0, s>>>(B + n_off, ldb, (int)K, (int)(N - n_off), (int)L.Kp,
                                                         b_hi + n_off * L.Kp, b_lo + n_off * L.Kp,
-                                                        aligned_to(B + n_off, 16) && (ldb % 4 == 0));
+                                                        aligned_to(B + n_off, 16) && (ldb % 4 == 0),
+                                                        zero_here ? reinterpret_cast<int*>(ws + L.ctrl()) : nullptr,
+                                                        zero_here ? 2 + L.bands * L.chunks : 0);
       DTN_LAUNCH_CHECK("split_transpose_kernel");
     }
   }
   return DTN_OK;
+}
+
+// ---------------------------------------------------------------------------------------
+// Tile schedule of the stream kernel
+// ---------------------------------------------------------------------------------------
+constexpr int kTileFixedCost = 12;   // what a tile costs beyond its width, in columns (barrier hand-offs, first loads)
+
+struct ScheduleChoice {
+  bool table = false;        // false: raster formula
+  int first_round_bands = 0; // bands the first round touches (table mode)
+  double makespan = 0, uniform = 0;
+  TileSchedule sched;
+};
+
+// Cuts each of `bands` bands of `units` 32-column units into pieces: `pieces` each, one more in `extra_bands` of
+// them (spread evenly), every band as evenly as its count allows. Appends (band, first unit, width in units).
+static bool cut_bands(int bands, int units, int pieces, int extra_bands, std::vector<uint32_t>* tiles) {
+  tiles->clear();
+  for (int b = 0; b < bands; ++b) {
+    const bool more = ((int64_t)(b + 1) * extra_bands / bands) != ((int64_t)b * extra_bands / bands);
+    const int p = pieces + (more ? 1 : 0);
+    if (p < 1 || p > units) return false;
+    const int base = units / p, rem = units % p;
+    if (base + (rem ? 1 : 0) > 8 || base < 2) return false;   // 64 .. 256 columns
+    int at = 0;
+    for (int i = 0; i < p; ++i) {
+      const int w = base + (i < rem ? 1 : 0);
+      tiles->push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)w << 24));
+      at += w;
+    }
+  }
+  return true;
+}
+
+// Deals the tiles (in band order) out in rounds of `workers`; within a round the widest tile goes to the pair with
+// the least work so far. Returns the largest total of any pair; fills `out` (entry[round * workers + pair]) if given.
+static double deal_rounds(const std::vector<uint32_t>& tiles, int workers, TileSchedule* out, int* first_round_bands) {
+  std::vector<double> load(workers, 0.0);
+  std::vector<int> order(workers);
+  std::vector<uint32_t> round;
+  const int rounds = (int)((tiles.size() + workers - 1) / workers);
+  if (out) {
+    if ((size_t)rounds * workers > (size_t)kSchedMaxEntries) return -1.0;
+    out->rounds = (uint32_t)rounds;
+    out->workers = (uint32_t)workers;
+    for (int i = 0; i < rounds * workers; ++i) out->entry[i] = 0;
+  }
+  for (int j = 0; j < rounds; ++j) {
+    const size_t begin = (size_t)j * workers, end = std::min(tiles.size(), begin + workers);
+    round.assign(tiles.begin() + begin, tiles.begin() + end);
+    if (j == 0 && first_round_bands) *first_round_bands = (int)(round.back() & 0xfffu) + 1;
+    std::stable_sort(round.begin(), round.end(), [](uint32_t a, uint32_t b) { return (a >> 24) > (b >> 24); });
+    for (int w = 0; w < workers; ++w) order[w] = w;
+    std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return load[a] < load[b]; });
+    for (size_t i = 0; i < round.size(); ++i) {
+      const int w = order[i];
+      load[w] += (double)(round[i] >> 24) * 32.0 + kTileFixedCost;
+      if (out) out->entry[j * workers + w] = round[i];
+    }
+  }
+  return *std::max_element(load.begin(), load.end());
+}
+
+// The cut with the smallest largest total among: 256-wide pieces (what the raster formula walks), and every mix of
+// p and p + 1 pieces per band for the two smallest usable p. The table is used when it saves at least 3 %.
+static void choose_schedule(int bands, int64_t N, int workers, ScheduleChoice* choice) {
+  choice->table = false;
+  const int units = (int)((N + 31) / 32);
+  const int pmin = (units + 7) / 8;
+  std::vector<uint32_t> tiles;
+  // the raster walk: pieces of 8 units, the last one narrower
+  for (int b = 0; b < bands; ++b)
+    for (int at = 0; at < units; at += 8)
+      tiles.push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)std::min(8, units - at) << 24));
+  choice->uniform = deal_rounds(tiles, workers, nullptr, nullptr);
+  choice->makespan = choice->uniform;
+  if (bands >= 4096 || units >= 4096 || workers < 1) return;
+  if ((int64_t)bands * pmin > kSchedMaxEntries) return;
+  int best_p = 0, best_x = 0;
+  double best = choice->uniform;
+  for (int p = pmin; p <= pmin + 1; ++p)
+    for (int x = 0; x <= bands; ++x) {
+      if ((int64_t)bands * p + x > kSchedMaxEntries) break;
+      if (!cut_bands(bands, units, p, x, &tiles)) continue;
+      const int rounds = (int)((tiles.size() + workers - 1) / workers);
+      if ((int64_t)rounds * workers > kSchedMaxEntries) continue;
+      const double span = deal_rounds(tiles, workers, nullptr, nullptr);
+      if (span > 0 && span < best) { best = span; best_p = p; best_x = x; }
+    }
+  if (best_p == 0 || best > 0.97 * choice->uniform) return;
+  cut_bands(bands, units, best_p, best_x, &tiles);
+  if (deal_rounds(tiles, workers, &choice->sched, &choice->first_round_bands) < 0) return;
+  choice->makespan = best;
+  choice->table = true;
+}
+
+// Schedules are a pure function of (bands, N, pairs); the last few are kept per host thread.
+static const ScheduleChoice& schedule_for(int bands, int64_t N, int workers) {
+  struct Slot { int bands = -1; int64_t n = -1; int workers = -1; ScheduleChoice choice; };
+  static thread_local Slot slots[4];
+  static thread_local int next = 0;
+  for (const Slot& slot : slots)
+    if (slot.bands == bands && slot.n == N && slot.workers == workers) return slot.choice;
+  Slot& slot = slots[next];
+  next = (next + 1) % 4;
+  slot.bands = bands; slot.n = N; slot.workers = workers;
+  choose_schedule(bands, N, workers, &slot.choice);
+  return slot.choice;
+}
+
+// Tensor map of a K-major plane with a given box height.
+template <int KIND>
+static int launch_stream(uint8_t* ws, const PlaneLayout& L, const float* A, int64_t lda, bool split_a_here, float* C,
+                         int64_t M, int64_t N, int64_t K, int64_t ldc, cudaStream_t s, int* status_word = nullptr) {
+  using Cfg = GemmCfg<2, 256>;
+  constexpr int eb = (KIND == 0) ? 2 : 4;
+  const void* a_hi = ws + L.a_hi();
+  const void* a_lo = ws + L.a_lo();
+  const void* b_hi = ws + L.b_hi();
+  const void* b_lo = ws + L.b_lo();
+  CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo, mb16_hi, mb16_lo;
+  int rc;
+  if ((rc = make_plane_map(&ma_hi, a_hi, eb, M, K, L.Kp, 128))) return rc;
+  if ((rc = make_plane_map(&ma_lo, a_lo, eb, M, K, L.Kp, 128))) return rc;
+  if ((rc = make_plane_map(&mb_hi, b_hi, eb, N, K, L.Kp, 128))) return rc;
+  if ((rc = make_plane_map(&mb_lo, b_lo, eb, N, K, L.Kp, 128))) return rc;
+  if ((rc = make_plane_map(&mb16_hi, b_hi, eb, N, K, L.Kp, 16))) return rc;
+  if ((rc = make_plane_map(&mb16_lo, b_lo, eb, N, K, L.Kp, 16))) return rc;
+
+  auto kernel = gemm_x3_stream_kernel<KIND>;
+  static thread_local int attr_dev = -1;
+  int dev = 0;
+  DTN_CUDA_CHECK(cudaGetDevice(&dev));
+  if (attr_dev != dev) {
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_dev = dev;
+  }
+  int* status = status_word ? status_word : device_status_word();
+  DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "gemm: could not allocate the device status word");
+
+  const int tiles_m = (int)((M + 255) / 256), tiles_n = (int)((N + 255) / 256);
+  const int num_kb = (int)(L.Kp / (kTileRowBytes / eb));
+  const int pairs = sm_count() / 2;
+  const ScheduleChoice& choice = schedule_for(tiles_m, N, pairs);
+  int units = pairs;
+  if (!choice.table && (int64_t)tiles_m * tiles_n < units) units = (int)((int64_t)tiles_m * tiles_n);
+  const int group_m = raster_group_m();
+
+  SplitWork work = {};
+  work.A = A;
+  work.lda = lda;
+  work.a_hi = ws + L.a_hi();
+  work.a_lo = ws + L.a_lo();
+  work.ctrl = reinterpret_cast<int*>(ws + L.ctrl());
+  work.M = (int)M;
+  work.K = (int)K;
+  work.Kp = (int)L.Kp;
+  work.bands = L.bands;
+  work.chunks = L.chunks;
+  work.items = split_a_here ? L.bands * L.chunks : 0;
+  work.vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
+  if (choice.table) {
+    work.group_bands = choice.first_round_bands;
+  } else {
+    // the raster walks groups of group_m bands; the first round may reach across several of them
+    const int reach = (units + tiles_n - 1) / tiles_n;
+    work.group_bands = (std::max(reach, group_m) + group_m - 1) / group_m * group_m;
+  }
+  work.group_bands = std::max(1, std::min(work.group_bands, L.bands));
+
+  static thread_local TileSchedule raster = {};   // rounds = 0: tiles from the raster formula
+  const TileSchedule& sched = choice.table ? choice.sched : raster;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)(units * 2));
+  cfg.blockDim = dim3(kStreamThreads);
+  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 2;
+  const int c_vec_ok = aligned_to(C, 16) && (ldc % 4 == 0);
+  DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, ma_hi, ma_lo, mb_hi, mb_lo, mb16_hi, mb16_lo, C, ldc, (int)M, (int)N,
+                                    num_kb, tiles_m, tiles_n, group_m, c_vec_ok, status, work, sched));
+  return DTN_OK;
+}
+
+// True when the automatic choice takes CTA-pair tiles: from three quarters of a round of pair tiles.
+static bool pairs_preferred(int64_t M, int64_t N) {
+  const int64_t pair_tiles = ((M + 255) / 256) * ((N + 255) / 256);
+  return pair_tiles * 8 >= (int64_t)(sm_count() / 2) * 6;
 }
 
 template <int KIND>
@@ -708,6 +1324,7 @@ static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C
     // 1024^3 16.8 vs 18.2 us)
     if (variant == 1 && square_tiles * 2 <= sm_count()) variant = 5;
   }
+  if (variant == 7) variant = 3;
   switch (variant) {
     case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
     case 2: return launch_tc<KIND, 1, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
@@ -784,12 +1401,12 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
   // This entry point always runs the split kernels and the tensor-memory product kernel. The selections of
   // dtn_gemm_set_variant that name a tile of that kernel (1, 2, 3, 5) are honoured; 4 and 6 name other kernels
   // (which use no scratch at all) and fall back to the automatic tile choice here.
-  const int variant = (g_gemm_variant == 4 || g_gemm_variant == 6) ? 0 : g_gemm_variant;
+  const int variant = (g_gemm_variant == 4 || g_gemm_variant == 6) ? 0 : (g_gemm_variant == 7 ? 3 : g_gemm_variant);
   const PlaneLayout L = plane_layout(mode, M, N, K);
-  DTN_REQUIRE(L.total <= kStaticScratchBytes, DTN_ERR_WORKSPACE,
+  DTN_REQUIRE(L.planes() <= kStaticScratchBytes, DTN_ERR_WORKSPACE,
               "gemm (static scratch): %lld x %lld x %lld needs %zu bytes of operand planes, the built-in array holds %zu; "
               "use dtn_gemm_x3 with a caller-owned workspace",
-              (long long)M, (long long)N, (long long)K, L.total, kStaticScratchBytes);
+              (long long)M, (long long)N, (long long)K, L.planes(), kStaticScratchBytes);
   StaticScratch scratch;
   int rc;
   if ((rc = static_scratch_for_current_device(&scratch))) return rc;
@@ -818,8 +1435,27 @@ int dtn_gemm_x3_static_status(int* status_out, void* stream) {
   return DTN_OK;
 }
 
+int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_out, int capacity, int* rounds_out,
+                           double* longest_out, double* longest_uniform_out) {
+  using namespace dtn;
+  DTN_REQUIRE(M > 0 && N > 0 && pairs > 0 && pairs <= 1024, DTN_ERR_INVALID, "tile schedule: M, N and pairs must be positive");
+  DTN_REQUIRE(rounds_out != nullptr, DTN_ERR_INVALID, "tile schedule: rounds_out is null");
+  DTN_REQUIRE(M < (1LL << 31) && N < (1LL << 31), DTN_ERR_UNSUPPORTED, "tile schedule: extents must fit 31 bits");
+  ScheduleChoice choice;
+  choose_schedule((int)((M + 255) / 256), N, pairs, &choice);
+  *rounds_out = choice.table ? (int)choice.sched.rounds : 0;
+  if (longest_out) *longest_out = choice.makespan;
+  if (longest_uniform_out) *longest_uniform_out = choice.uniform;
+  if (choice.table && entries_out != nullptr) {
+    const int count = (int)choice.sched.rounds * pairs;
+    DTN_REQUIRE(capacity >= count, DTN_ERR_INVALID, "tile schedule: %d entries needed, room for %d", count, capacity);
+    for (int i = 0; i < count; ++i) entries_out[i] = choice.sched.entry[i];
+  }
+  return DTN_OK;
+}
+
 int dtn_gemm_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 6, DTN_ERR_INVALID, "gemm: variant must be 0..6");
+  DTN_REQUIRE(variant >= 0 && variant <= 7, DTN_ERR_INVALID, "gemm: variant must be 0..7");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
 }
@@ -873,6 +1509,19 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   DTN_REQUIRE(aligned_to(workspace, 1024), DTN_ERR_WORKSPACE, "gemm: workspace must be 1024-byte aligned");
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int rc;
+  // CTA-pair tiles (automatic for large products): the stream kernel. It splits A itself, beside its products, so
+  // only B is split ahead of it.
+  if ((phase & 2) && (g_gemm_variant == 7 || (g_gemm_variant == 0 && pairs_preferred(M, N)))) {
+    if (split_b) {
+      rc = (mode == DTN_GEMM_BF16X3) ? run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s, false, true, split_a)
+                                     : run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s, false, true, split_a);
+      if (rc) return rc;
+    } else if (split_a) {
+      DTN_CUDA_CHECK(cudaMemsetAsync(ws + L.ctrl(), 0, sizeof(int) * (2 + (size_t)L.bands * L.chunks), s));
+    }
+    return (mode == DTN_GEMM_BF16X3) ? launch_stream<0>(ws, L, A, lda, split_a, C, M, N, K, ldc, s)
+                                     : launch_stream<1>(ws, L, A, lda, split_a, C, M, N, K, ldc, s);
+  }
   if (mode == DTN_GEMM_BF16X3) {
     if ((phase & 1) && (rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s, split_a, split_b))) return rc;
     return (phase & 2) ? run_tc<0>(g_gemm_variant, ws, L, C, M, N, K, ldc, s) : DTN_OK;

@@ -52,6 +52,8 @@ _SIGNATURES = {
     'dtn_gemm_x3_phase': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P, ct.c_size_t, _I, _P],
     'dtn_gemm_x3_static': [_I, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _I64, _P],
     'dtn_gemm_x3_static_status': [ct.POINTER(ct.c_int), _P],
+    'dtn_gemm_tile_schedule': [_I64, _I64, _I, ct.POINTER(ct.c_uint32), _I, ct.POINTER(ct.c_int), ct.POINTER(ct.c_double),
+                               ct.POINTER(ct.c_double)],
     'dtn_gemm_set_variant': [_I],
     'dtn_attention_f32': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _F, _P],
     'dtn_gqa_fwd': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _I64, _I64, _P],
@@ -144,5 +146,5 @@ def device_status(stream: int = 0) -> int:
 def raise_on_device_status(stream: int = 0) -> None:
     status = device_status(stream)
     if status:
-        role = {0x71: 'bounded-wait self-test', 0x11: 'attention K loader', 0x12: 'attention V loader', 0x13: 'attention Q loader', 0x31: 'attention softmax (scores)', 0x32: 'attention output', 0x33: 'attention softmax (row exchange)', 0x21: 'attention MMA issuer (queries)', 0x23: 'attention MMA issuer (values)', 0x24: 'attention MMA issuer (probabilities)', 0x25: 'attention MMA issuer (keys)', 0x26: 'attention MMA issuer (probabilities)', 0x51: 'fused-split GEMM producers', 0x52: 'fused-split GEMM MMA issuer', 0x53: 'fused-split GEMM epilogue', 1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
+        role = {0x71: 'bounded-wait self-test', 0x11: 'attention K loader', 0x12: 'attention V loader', 0x13: 'attention Q loader', 0x31: 'attention softmax (scores)', 0x32: 'attention output', 0x33: 'attention softmax (row exchange)', 0x21: 'attention MMA issuer (queries)', 0x23: 'attention MMA issuer (values)', 0x24: 'attention MMA issuer (probabilities)', 0x25: 'attention MMA issuer (keys)', 0x26: 'attention MMA issuer (probabilities)', 0x51: 'fused-split GEMM producers', 0x52: 'fused-split GEMM MMA issuer', 0x53: 'fused-split GEMM epilogue', 5: 'TMA producer (split of A)', 1: 'TMA producer', 2: 'MMA issuer (accumulator)', 3: 'MMA issuer (operands)', 4: 'epilogue'}.get(status >> 8, 'kernel')
         raise DeviceWaitError(f'bounded wait ran out in the {role}, CTA {status & 0xff} (status {status:#x})')

@@ -235,6 +235,18 @@ int dtn_gemm_x3_static_status(int* status_out /* host */, void* stream);
 int dtn_push_block(const float* src, int64_t lds, float* const* dsts, int n_dst, int64_t ldd,
                    int64_t rows, int64_t cols, void* stream);
 
+/* The tile schedule the CTA-pair GEMM kernel uses for an M x N output on `pairs` CTA pairs (a B200 has 74): host
+ * arithmetic only, no GPU needed. The kernel walks `*rounds_out` rounds; in round j pair w multiplies the tile
+ * entries_out[j * pairs + w] = band | (first column / 32) << 12 | (width / 32) << 24 (band = 256 rows; 0 = nothing
+ * in that round). Bands are cut into pieces of 64..256 columns so that the pairs finish together: *longest_out is the
+ * largest sum of (width + fixed cost) over the pairs, *longest_uniform_out the same for plain 256-wide tiles.
+ * *rounds_out = 0 means the kernel keeps the plain walk (the cut would save under 3 %, or the table would not fit).
+ * Tile width does not change any output bit. entries_out may be NULL. No reference counterpart (the reference's
+ * schedule is one 32x64 tile per CTA, compiler/passes/contraction.py:135-213). */
+int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_out /* host */, int capacity,
+                           int* rounds_out /* host */, double* longest_out /* host */,
+                           double* longest_uniform_out /* host */);
+
 /* Selects the tensor-core GEMM variant for the calling host thread (other threads keep their own
  * selection, initially 0; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile,
@@ -243,7 +255,9 @@ int dtn_push_block(const float* src, int64_t lds, float* const* dsts, int n_dst,
  *   at most 16 rows), 5 = one-CTA 128x64 tile (automatic when 128x128 tiles would occupy at most
  *   half of the SMs), 6 = one tcgen05 kernel with the operand split in its producer warps (no
  *   workspace, one launch; bf16x3 with 16-byte aligned A and B, lda and ldb multiples of 4, N and
- *   K multiples of 8, else DTN_ERR_UNSUPPORTED).
+ *   K multiples of 8, else DTN_ERR_UNSUPPORTED), 7 = the stream kernel: two-CTA tiles 256 rows tall from the
+ *   schedule of dtn_gemm_tile_schedule, with the split of A running inside the kernel beside the products (what
+ *   automatic picks where it picked 3 before; 3 remains as the plain two-kernel form).
  * No reference counterpart. */
 int dtn_gemm_set_variant(int variant);
 

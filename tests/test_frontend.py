@@ -383,3 +383,26 @@ def test_tile_checks(vector_add):
         set_body(graph, tile)
         with pytest.raises(ValueError, match=fragment):
             compile_kernel(graph, meta)
+
+
+def test_ir_built_by_the_reference_generators_classifies_like_the_generated_schedules(golden):
+    """tests/golden/reference_examples.json holds the IR and meta the reference's own example scripts build
+    (examples/attention.py, examples/f16_storage.py). It goes through compile_kernel unchanged and selects the same
+    native kernel, with the same parameters, as the IR this package's schedules module generates for the same shape."""
+    examples = json.loads((golden / 'reference_examples.json').read_text())
+    assert len(examples) == 15
+    shapes = {'attention_3x64x32': dict(rows=3, keys=64, depth=32), 'attention_64x64x64': dict(rows=64, keys=64, depth=64),
+              'attention_128x128x32': dict(rows=128, keys=128, depth=32),
+              'attention_128x128x32_inplace': dict(rows=128, keys=128, depth=32, inplace_denominator=True),
+              'attention_256x256x128': dict(rows=256, keys=256, depth=128)}
+    for name, configuration in shapes.items():
+        theirs = compile_kernel(examples[name]['graph'], examples[name]['meta']).plan
+        mine = compile_kernel(*schedules.attention_example(**configuration)).plan
+        assert theirs.kind == 'attention' and theirs.params == mine.params and theirs.buffers == mine.buffers, name
+    for kind in ('copy', 'widen', 'narrow', 'affine', 'cancellation'):
+        for width in (4, 1):
+            case = examples[f'f16_{kind}_w{width}']
+            theirs = compile_kernel(case['graph'], case['meta']).plan
+            mine = compile_kernel(*schedules.f16_storage_example(kind, width=width)).plan
+            assert theirs.kind == mine.kind and theirs.params == mine.params and theirs.buffers == mine.buffers, (kind, width)
+            assert case['meta']['kernels'][0] == schedules.f16_storage_example(kind, width=width)[1]['kernels'][0]

@@ -384,7 +384,7 @@ def test_tensor_matmul_example_all_modes(runner, golden, published):
     assert sha(produced) == published['results']['tensor_f32']['output_sha256']['result']
 
 
-@pytest.mark.parametrize('variant', [0, 1, 3, 4, 5])
+@pytest.mark.parametrize('variant', [0, 1, 3, 4, 5, 7])
 def test_compensated_modes_hash_to_the_reference_gpu_outputs(cuda, published, variant):
     # Same split, same three products in the same order per k-step, FP32 tensor-core accumulation: every kernel
     # variant reproduces the bits of the reference's own run of its 128^3 example (published SHA-256 and max error).
@@ -409,12 +409,42 @@ def test_reference_committed_ir_runs_unchanged(runner, golden, published):
     np.testing.assert_allclose(produced, np.load(golden / 'tensor_matmul_expected.npz')['result'], rtol=1e-3, atol=1e-3)
 
 
+def test_ir_of_the_reference_example_generators_runs_unchanged(runner, golden):
+    """The IR and meta the reference's example scripts build (tests/golden/reference_examples.json), through
+    compile_kernel + run_kernel unchanged: attention within the scripts' own tolerance of the float64 expectation
+    (examples/attention.py:67), the in-place-denominator variant identical to the plain one
+    (tests/test_attention.py:122), f16 kernels bit for bit what NumPy gives (examples/f16_storage.py:79-86)."""
+    import json
+    from deuteron_b200 import argument_array
+    examples = json.loads((golden / 'reference_examples.json').read_text())
+    outputs = {}
+    for name, case in examples.items():
+        launch = case['meta']['kernels'][0]
+        produced = runner.run_kernel(launch, compile_kernel(case['graph'], case['meta']), warmup=0, iters=1, samples=1)['outputs']
+        values = {arg['name']: argument_array(arg) for arg in launch['args'] if not arg.get('output')}
+        if name.startswith('attention'):
+            exact = R.attention_f64(values['q'], values['kt'], values['v'])
+            np.testing.assert_allclose(produced['out'], exact, rtol=1e-3, atol=1e-4)
+            assert R.max_relative_error(produced['out'], exact) < 4e-7
+            outputs[name] = produced['out']
+        else:
+            kind = name.split('_')[1]
+            x = values['x'].astype(np.float32)
+            expected = {'copy': lambda: values['x'], 'widen': lambda: x, 'narrow': lambda: x.astype(np.float16),
+                        'affine': lambda: (x * values['scale'][0] + values['bias'][0]).astype(np.float16),
+                        'cancellation': lambda: ((x + values['y'].astype(np.float32)) - x).astype(np.float16)}[kind]()
+            assert produced['result'].dtype == expected.dtype
+            np.testing.assert_array_equal(produced['result'].view(np.uint16 if expected.dtype == np.float16 else np.uint32),
+                                          expected.view(np.uint16 if expected.dtype == np.float16 else np.uint32))
+    np.testing.assert_array_equal(outputs['attention_128x128x32'], outputs['attention_128x128x32_inplace'])
+
+
 SHAPES = [(128, 128, 128), (256, 256, 64), (384, 768, 1000), (200, 136, 77), (16, 512, 512), (1, 1, 1), (129, 257, 65),
           (1024, 1024, 1024)]
 
 
 @pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
-@pytest.mark.parametrize('variant', [1, 2, 3, 4, 5])   # tcgen05 tiles 128x128, 128x256, CTA pair 256x256; single-kernel; 128x64
+@pytest.mark.parametrize('variant', [1, 2, 3, 4, 5, 7])   # tcgen05 tiles 128x128, 128x256, CTA pair 256x256; single-kernel; 128x64; stream
 def test_compensated_gemm_shapes_and_variants(cuda, mode, variant):
     ops.set_gemm_variant(variant)
     try:
@@ -581,6 +611,32 @@ def test_execute_on_host_buffers_matches_the_resident_path(cuda, runner):
     np.testing.assert_array_equal(produced, x + y)
     with pytest.raises(ValueError):
         runner.execute(compile_kernel(graph, meta), {'lhs': x[:-1], 'rhs': y})
+
+
+@pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
+@pytest.mark.parametrize('m,n,k', [(8192, 1024, 512), (8192, 2048, 256), (4096, 4096, 320), (8192, 1000, 200), (2300, 4100, 130),
+                                   (8192, 8192, 192)])
+def test_stream_kernel_equals_the_plain_tiles_bit_for_bit(cuda, mode, m, n, k):
+    # cut bands of unequal widths (first three shapes: a table of tiles; ragged edges; the plain walk) and the split of
+    # A inside the kernel change no bit of any output element
+    a, b = to_device(cuda, R.seeded_uniform(7, (m, k))), to_device(cuda, R.seeded_uniform(11, (k, n)))
+    ops.set_gemm_variant(1)
+    try:
+        plain = ops.gemm(a, b, mode).clone()
+        ops.set_gemm_variant(7)
+        streamed = ops.gemm(a, b, mode).clone()
+        again = ops.gemm(a, b, mode)                            # counters and flags are cleared by every call
+        kept_a = ops.gemm(a, b, mode, out=cuda.empty_like(plain), phase=3 | 4)   # A planes of the call before, B split again
+        kept_b = ops.gemm(a, b, mode, out=cuda.empty_like(plain), phase=3 | 8)   # A split in the kernel, B planes kept
+        only_products = ops.gemm(a, b, mode, out=cuda.empty_like(plain), phase=2)
+    finally:
+        ops.set_gemm_variant(0)
+    ops.check_device_status()
+    for produced in (streamed, again, kept_a, kept_b, only_products):
+        assert bool(cuda.equal(produced, plain))
+    automatic = ops.gemm(a, b, mode)
+    ops.check_device_status()
+    assert bool(cuda.equal(automatic, plain))
 
 
 def test_execute_with_a_tall_left_operand_and_a_narrow_right_one(cuda, runner):

@@ -137,3 +137,36 @@ def test_a_feed_plan_gives_every_row_to_exactly_one_rank():
     assert sharding.owned_rows(sharding.a_feed_plan(8192, 8, 4), 3) == [(2048 * j + 768, 2048 * j + 1024) for j in range(4)]
     with pytest.raises(ValueError):
         sharding.a_feed_plan(8, 0, 1)
+
+
+def test_tile_schedule_covers_the_output_once_and_balances_the_pairs():
+    import ctypes as ct
+    from deuteron_b200 import native
+
+    def schedule(m, n, pairs=74):
+        entries, rounds = (ct.c_uint32 * 640)(), ct.c_int()
+        longest, uniform = ct.c_double(), ct.c_double()
+        native.call('dtn_gemm_tile_schedule', m, n, pairs, entries, 640, ct.byref(rounds), ct.byref(longest), ct.byref(uniform))
+        table = np.array(entries[:rounds.value * pairs], dtype=np.uint32).reshape(rounds.value, pairs) if rounds.value else None
+        return table, longest.value, uniform.value
+
+    for m, n in ((8192, 1024), (8192, 2048), (4096, 4096), (8192, 1000), (5000, 1500)):
+        table, longest, uniform = schedule(m, n)
+        assert table is not None and longest <= 0.97 * uniform
+        cover = np.zeros(((m + 255) // 256, (n + 31) // 32), dtype=int)
+        for entry in table.ravel():
+            if entry:
+                band, first, width = int(entry & 0xfff), int((entry >> 12) & 0xfff), int(entry >> 24)
+                assert 2 <= width <= 8
+                cover[band, first:first + width] += 1
+        assert (cover == 1).all()
+        # rounds walk the bands in order: no tile of a round lies above a tile of the round before
+        top = [min(int(e & 0xfff) for e in row if e) for row in table]
+        bottom = [max(int(e & 0xfff) for e in row if e) for row in table]
+        assert all(bottom[j] <= top[j + 1] + 1 for j in range(len(top) - 1))
+    # one eighth of the 8192^3 product on 74 pairs: 1.73 rounds of work in 1.75 instead of 2
+    table, longest, uniform = schedule(8192, 1024)
+    loads = [sum(int(e >> 24) * 32 for e in table[:, w] if e) for w in range(74)]
+    assert max(loads) == 448 and uniform >= 2 * 256
+    # large outputs keep the plain walk
+    assert schedule(8192, 8192)[0] is None and schedule(8192, 4096)[0] is None
