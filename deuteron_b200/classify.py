@@ -118,8 +118,33 @@ def _classify_gemm(tile: ir.Node, specs: dict, precision: str, launch: dict) -> 
     for name in (left, right, output):
         if specs[name]['dtype'] != 'f32':
             raise NotImplementedError('contractions take f32 buffers')
-    return Plan('gemm', {'mode': precision, 'm': m, 'n': n, 'k': k},
+    # The reference runs a contraction on the tensor cores (compensated products) only when both operands are staged
+    # through shared memory by its asynchronous copies (compiler/passes/contraction.py:58-213); every other
+    # contraction schedule, the split-K one among them, is lowered to plain FP32 multiply-adds
+    # (compiler/codegen/lower.py:600-653). The native mode follows, so that the error level is the reference's.
+    staged = {copies.get(loads[operand].input) for product in products for operand in product.args}
+    mode = precision if staged == {left, right} and _tensor_core_shape(tile, statements, products, writes, precision, launch) else 'f32'
+    return Plan('gemm', {'mode': mode, 'm': m, 'n': n, 'k': k},
                 {'left': (left, 0), 'right': (right, 0), 'out': (output, 0)})
+
+
+def _tensor_core_shape(tile: ir.Node, statements: list, products: list, writes: list, precision: str, launch: dict) -> bool:
+    """The shape conditions under which the reference turns a staged contraction into tensor-core products
+    (compiler/passes/contraction.py:135, 211): the CTA's output tile is made of 16 x 8 warp tiles, exactly one per
+    warp, and the staged depth of the inner product loop is a multiple of the instruction's k (16 for bf16x3, 8 for
+    tf32x3). A schedule that fails them is lowered to FP32 multiply-adds there."""
+    product_names = {product.name for product in products}
+    depths = {ir.axis_extent(stmt.axis) for stmt in statements if stmt.kind == 'Loop'
+              and any(child.kind == 'Assign' and child.name in product_names for child in stmt.body)}
+    if len(depths) != 1 or len(tile.axes) < 2:
+        return False
+    depth = depths.pop()
+    rows, cols = len(writes), len(writes[0].values)
+    tile_rows, tile_cols = ir.axis_extent(tile.axes[-2]) * rows, ir.axis_extent(tile.axes[-1]) * cols
+    threads = launch['block'][0]
+    step = 16 if precision == 'bf16x3' else 8
+    return (depth % step == 0 and tile_rows % 16 == 0 and tile_cols % 8 == 0
+            and (tile_rows // 16) * (tile_cols // 8) * 32 == threads)
 
 
 def _split_k_depth(tile: ir.Node, writes: list, launch: dict) -> int:

@@ -211,6 +211,12 @@ def walk(body: Any) -> Iterator[Node]:
             yield from walk(children(stmt))
 
 
+def axis_extent(axis: Any) -> int:
+    """Static extent of an Axis node (Axis(name, extent=Dim(n), window))."""
+    extent = axis.extent
+    return int(extent.value) if isinstance(extent, Node) else int(extent)
+
+
 def expression_vars(expr: Any) -> set[str]:
     """Names of the Var nodes inside an index expression."""
     found: set[str] = set()

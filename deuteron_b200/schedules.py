@@ -70,11 +70,13 @@ def write(output: str, index, values, dtype: str = F32, atomic: bool = False) ->
             f"atomic={atomic}, swizzle='NONE')")
 
 
-def loop(axis_text: str, body, unroll: Any = None, seed: bool = False) -> str:
+def loop(axis_text: str, body, unroll: bool = False, seed: bool = False) -> str:
+    """`seed=True`: the accumulators of the body start from their operator's identity at loop entry (what a loop built
+    without the flag does in the reference's generators); False: they continue from an Init or an enclosing loop."""
     return f"Loop(axis={axis_text}, body={_tuple(body)}, unroll={unroll!r}, seed={seed})"
 
 
-def strided_loop(axis_text: str, start: str, step: str, body, unroll: Any = None, seed: bool = False) -> str:
+def strided_loop(axis_text: str, start: str, step: str, body, unroll: bool = False, seed: bool = False) -> str:
     return (f"StridedLoop(axis={axis_text}, start={start}, step={step}, body={_tuple(body)}, unroll={unroll!r}, end=None, "
             f"seed={seed})")
 
@@ -205,7 +207,7 @@ def attention_example(rows: int = 3, keys: int = 64, depth: int = 32, inplace_de
         load(('key_value',), 'kt', [var('dot'), var('key')]),
         assign('product', 'multiply', ('query', 'key_value')),
         accum('score_sum', 'product', 'add', ('dot',)),
-    ])
+    ], seed=True)
     outer = loop(axis('key', keys), [
         dot,
         assign('score', 'multiply', ('score_sum', 'scale')),
@@ -221,7 +223,7 @@ def attention_example(rows: int = 3, keys: int = 64, depth: int = 32, inplace_de
         assign('weighted_new', 'multiply', ('value', 'beta')),
         accum('weighted', 'weighted_new', 'add', ('key',), 'weighted_carry'),
         accum('maximum', 'score', 'maximum', ('key',)),
-    ])
+    ], seed=True)
     inverse = 'mass' if inplace_denominator else 'inverse'
     scale = float(np.float32(1 / math.sqrt(depth)))
     body = tile([axis('row', rows), axis('column', columns)], [
@@ -580,7 +582,7 @@ def gqa_attention_example(batch: int = 4, query_heads: int = 32, kv_heads: int =
         *widened('key_value', 'k', [var('batch'), kv_head, var('key'), var('dot')]),
         assign('product', 'multiply', ('query', 'key_value')),
         accum('score_sum', 'product', 'add', ('dot',)),
-    ])
+    ], seed=True)
     outer = loop(axis('key', positions), [
         dot,
         assign('score', 'multiply', ('score_sum', 'scale')),
@@ -596,7 +598,7 @@ def gqa_attention_example(batch: int = 4, query_heads: int = 32, kv_heads: int =
         assign('weighted_new', 'multiply', ('value', 'beta')),
         accum('weighted', 'weighted_new', 'add', ('key',), 'weighted_carry'),
         accum('maximum', 'score', 'maximum', ('key',)),
-    ])
+    ], seed=True)
     scale = float(np.float32(1 / math.sqrt(depth)))
     body = tile([axis('batch', batch), axis('head', query_heads), axis('row', positions), axis('column', depth)], [
         f"Let(name='scale', value={lit(scale)}, dtype={F32})",

@@ -78,7 +78,8 @@ def test_generated_schedules_classify(golden):
         (schedules.row_reduce_example(8, 4096, 'max'), 'row_reduce', {'op': 'max', 'rows': 8, 'cols': 4096}),
         (schedules.row_reduce_example(8, 4096, 'sumsq'), 'row_reduce', {'op': 'sumsq', 'rows': 8, 'cols': 4096}),
         (schedules.matmul_example(256, 512, 1024), 'gemm', {'mode': 'bf16x3', 'm': 256, 'n': 512, 'k': 1024}),
-        (schedules.split_k_matmul_example(), 'gemm', {'mode': 'bf16x3', 'm': 128, 'n': 64, 'k': 256}),
+        # staged depth 4 is no multiple of the tensor-core k step: the reference lowers this one to FP32 multiply-adds, and so does this build
+            (schedules.split_k_matmul_example(), 'gemm', {'mode': 'f32', 'm': 128, 'n': 64, 'k': 256}),
         (schedules.mean_example(), 'row_fused',
          {'reduce': 'sum', 'rows': 1, 'cols': 32768, 'per_row': True, 'inputs': [{'kind': 'scalar'}], 'n_scalar': 1, 'out_reg': 4,
           'ops': [3], 'dst': [4], 'a': [0], 'b': [3]}),
@@ -279,7 +280,8 @@ def test_argument_checks_need_no_gpu():
     assert library.dtn_gemm_set_variant(9) == native.ERR_INVALID
     size = ctypes.c_size_t(0)
     assert library.dtn_gemm_workspace_bytes(2, 8192, 8192, 8192, ctypes.byref(size)) == 0
-    assert size.value == 4 * 8192 * 8192 * 2  # hi and lo bf16 planes of A and of B transposed
+    # hi and lo bf16 planes of A and of B transposed, then the counter and the 32 x 64 item flags of the in-kernel split of A
+    assert size.value == 4 * 8192 * 8192 * 2 + (4 * (2 + 32 * 64) + 1023) // 1024 * 1024
     assert library.dtn_gemm_workspace_bytes(1, 100, 50, 33, ctypes.byref(size)) == 0
     assert size.value == 2 * (100 * 64 * 4 + 1023) // 1024 * 1024 + 2 * (50 * 64 * 4 + 1023) // 1024 * 1024 or size.value > 0
     assert library.dtn_gemm_workspace_bytes(7, 1, 1, 1, ctypes.byref(size)) == native.ERR_INVALID
@@ -398,6 +400,8 @@ def test_ir_built_by_the_reference_generators_classifies_like_the_generated_sche
     for name, configuration in shapes.items():
         theirs = compile_kernel(examples[name]['graph'], examples[name]['meta']).plan
         mine = compile_kernel(*schedules.attention_example(**configuration)).plan
+        # the generator of this package writes the very text the reference's script writes
+        assert schedules.attention_example(**configuration) == (examples[name]['graph'], examples[name]['meta'])
         assert theirs.kind == 'attention' and theirs.params == mine.params and theirs.buffers == mine.buffers, name
     for kind in ('copy', 'widen', 'narrow', 'affine', 'cancellation'):
         for width in (4, 1):
@@ -405,4 +409,4 @@ def test_ir_built_by_the_reference_generators_classifies_like_the_generated_sche
             theirs = compile_kernel(case['graph'], case['meta']).plan
             mine = compile_kernel(*schedules.f16_storage_example(kind, width=width)).plan
             assert theirs.kind == mine.kind and theirs.params == mine.params and theirs.buffers == mine.buffers, (kind, width)
-            assert case['meta']['kernels'][0] == schedules.f16_storage_example(kind, width=width)[1]['kernels'][0]
+            assert schedules.f16_storage_example(kind, width=width) == (case['graph'], case['meta'])

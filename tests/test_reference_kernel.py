@@ -143,4 +143,6 @@ def test_every_reference_emitted_kernel_beside_the_native_one(cuda, name):
         error_mine = float((ours - expected.reshape(ours.shape)).abs().max().item()) / scale
         error_ref = float((ref - expected.reshape(ref.shape)).abs().max().item()) / scale
         assert error_ref < 1e-3, (name, key, error_ref)     # the reference kernel itself ran correctly here
-        assert error_mine <= 2 * error_ref + 3e-8, (name, key, error_mine, error_ref)
+        # twice the reference kernel's own error; below four units in the last place of the largest output the two
+        # are rounding noise of different summation orders and the comparison means nothing
+        assert error_mine <= max(2 * error_ref, 2.0 ** -22), (name, key, error_mine, error_ref)
