@@ -118,18 +118,27 @@ split_rows_kernel(const float* __restrict__ X, int64_t ldx, int rows, int cols, 
 }
 
 // B[K, N] (ld = ldb) -> transposed hi/lo [N, Kp]; k >= K written as zero.
-// One CTA transposes a kBlockK x 64 tile through shared memory.
-template <class KIND>
+// 256 threads (`tid` 0..255) transpose a kBlockK x 64 tile through `scratch` (kTransposeScratchBytes of shared
+// memory); `sync()` is a barrier over exactly those threads. The scratch may be reused after a further sync().
+constexpr int kTransposeScratchBytes = 2 * 64 * 66 * 2;   // the larger of the layouts below (bf16 padded: 16 896 bytes)
+
+struct CtaSync {
+  __device__ __forceinline__ void operator()() const { __syncthreads(); }
+};
+
+template <class KIND, class SYNC>
 __device__ __forceinline__ void split_transpose_body(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
                                                      typename KIND::elem* __restrict__ hi,
-                                                     typename KIND::elem* __restrict__ lo, int block_x, int block_y) {
+                                                     typename KIND::elem* __restrict__ lo, int block_x, int block_y,
+                                                     uint8_t* scratch, int tid, SYNC sync) {
   using E = typename KIND::elem;
   constexpr int TK = KIND::kBlockK;          // 64 (bf16) or 32 (tf32): 128 bytes of k per row
   constexpr int PAD = (KIND::kElemBytes == 2) ? 2 : 1;
-  __shared__ E s_hi[64][TK + PAD];
-  __shared__ E s_lo[64][TK + PAD];
+  constexpr int ROW = TK + PAD;
+  static_assert(2 * 64 * ROW * (int)sizeof(E) <= kTransposeScratchBytes, "transposition scratch too small");
+  E* s_hi = reinterpret_cast<E*>(scratch);
+  E* s_lo = s_hi + 64 * ROW;
   const int k0 = block_x * TK, n0 = block_y * 64;
-  const int tid = threadIdx.x;
   {
     const int nn = tid & 63, kr = tid >> 6;  // 4 k-rows per pass
 #pragma unroll 4
@@ -139,11 +148,11 @@ __device__ __forceinline__ void split_transpose_body(const float* __restrict__ B
       if (k < K && n < N) v = B[(int64_t)k * ldb + n];
       E h, l;
       KIND::split(v, h, l);
-      s_hi[nn][p * 4 + kr] = h;
-      s_lo[nn][p * 4 + kr] = l;
+      s_hi[nn * ROW + p * 4 + kr] = h;
+      s_lo[nn * ROW + p * 4 + kr] = l;
     }
   }
-  __syncthreads();
+  sync();
   {
     // each thread writes 4 bytes of k; 32 threads cover one 128-byte row; 8 rows per pass
     constexpr int EPT = 4 / KIND::kElemBytes;  // elements per thread (2 bf16 or 1 tf32)
@@ -153,8 +162,8 @@ __device__ __forceinline__ void split_transpose_body(const float* __restrict__ B
       const int nn = p * 8 + nr, n = n0 + nn;
       if (n < N && k0 + kk < Kp) {
         const int64_t o = (int64_t)n * Kp + k0 + kk;
-        *reinterpret_cast<uint32_t*>(hi + o) = *reinterpret_cast<const uint32_t*>(&s_hi[nn][kk]);
-        *reinterpret_cast<uint32_t*>(lo + o) = *reinterpret_cast<const uint32_t*>(&s_lo[nn][kk]);
+        *reinterpret_cast<uint32_t*>(hi + o) = *reinterpret_cast<const uint32_t*>(&s_hi[nn * ROW + kk]);
+        *reinterpret_cast<uint32_t*>(lo + o) = *reinterpret_cast<const uint32_t*>(&s_lo[nn * ROW + kk]);
       }
     }
   }
@@ -164,13 +173,14 @@ __device__ __forceinline__ void split_transpose_body(const float* __restrict__ B
 // four consecutive k of each column into 8 bytes and stores them to a [64 n][64 k] shared tile whose 8-byte chunks are
 // XOR-swizzled with the column group (conflict-free on both sides); the tile leaves as 16-byte pieces of whole
 // 128-byte k-rows. Needs B 16-byte aligned with ldb % 4 == 0; edges fall back to guarded scalar loads.
+template <class SYNC>
 __device__ __forceinline__ void split_transpose_bf16_vec(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
                                                          __nv_bfloat16* __restrict__ hi, __nv_bfloat16* __restrict__ lo,
-                                                         int block_x, int block_y) {
-  __shared__ __align__(16) __nv_bfloat16 t_hi[64 * 64];
-  __shared__ __align__(16) __nv_bfloat16 t_lo[64 * 64];
+                                                         int block_x, int block_y, uint8_t* scratch, int tid, SYNC sync) {
+  static_assert(2 * 64 * 64 * 2 <= kTransposeScratchBytes, "transposition scratch too small");
+  __nv_bfloat16* t_hi = reinterpret_cast<__nv_bfloat16*>(scratch);   // 16-byte aligned: the scratch is
+  __nv_bfloat16* t_lo = t_hi + 64 * 64;
   const int k0 = block_x * 64, n0 = block_y * 64;
-  const int tid = threadIdx.x;
   {
     const int n4 = tid & 15, kc = tid >> 4;
     const int n = n0 + 4 * n4;
@@ -197,7 +207,7 @@ __device__ __forceinline__ void split_transpose_bf16_vec(const float* __restrict
       *reinterpret_cast<uint2*>(t_lo + at) = *reinterpret_cast<uint2*>(l);
     }
   }
-  __syncthreads();
+  sync();
 #pragma unroll
   for (int q = tid; q < 512; q += 256) {
     const int nn = q >> 3, pr = q & 7;          // row of the tile, pair of 4-element chunks (2 pr, 2 pr + 1)
@@ -218,6 +228,20 @@ __device__ __forceinline__ void split_transpose_bf16_vec(const float* __restrict
   }
 }
 
+// One kBlockK x 64 tile of B by either form.
+template <class KIND, class SYNC>
+__device__ __forceinline__ void split_transpose_tile(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
+                                                     typename KIND::elem* __restrict__ hi, typename KIND::elem* __restrict__ lo,
+                                                     int block_x, int block_y, int b_vec_ok, uint8_t* scratch, int tid, SYNC sync) {
+  if constexpr (KIND::kElemBytes == 2) {
+    if (b_vec_ok) {
+      split_transpose_bf16_vec(B, ldb, K, N, Kp, hi, lo, block_x, block_y, scratch, tid, sync);
+      return;
+    }
+  }
+  split_transpose_body<KIND>(B, ldb, K, N, Kp, hi, lo, block_x, block_y, scratch, tid, sync);
+}
+
 template <class KIND>
 __global__ void __launch_bounds__(256)
 split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, int Kp,
@@ -227,13 +251,8 @@ split_transpose_kernel(const float* __restrict__ B, int64_t ldb, int K, int N, i
   // the product kernel behind this grid claims split items from a counter and publishes flags: start them at zero
   if (zero_words != nullptr && blockIdx.x == 0 && blockIdx.y == 0)
     for (int i = threadIdx.x; i < zero_count; i += blockDim.x) zero_words[i] = 0;
-  if constexpr (KIND::kElemBytes == 2) {
-    if (b_vec_ok) {
-      split_transpose_bf16_vec(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
-      return;
-    }
-  }
-  split_transpose_body<KIND>(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y);
+  __shared__ __align__(16) uint8_t scratch[kTransposeScratchBytes];
+  split_transpose_tile<KIND>(B, ldb, K, N, Kp, hi, lo, (int)blockIdx.x, (int)blockIdx.y, b_vec_ok, scratch, (int)threadIdx.x, CtaSync());
 }
 
 // Both splits in one launch (one launch less on the latency of small and medium problems): the first
@@ -250,13 +269,8 @@ split_both_kernel(const float* __restrict__ A, int64_t lda, int K, int Kp, typen
     split_rows_body<KIND>(A, lda, K, Kp, a_hi, a_lo, a_vec_ok, id / a_blocks_x, id % a_blocks_x);
   } else {
     const int b = id - a_blocks;
-    if constexpr (KIND::kElemBytes == 2) {
-      if (b_vec_ok) {
-        split_transpose_bf16_vec(B, ldb, K, N, Kp, b_hi, b_lo, b % b_blocks_x, b / b_blocks_x);
-        return;
-      }
-    }
-    split_transpose_body<KIND>(B, ldb, K, N, Kp, b_hi, b_lo, b % b_blocks_x, b / b_blocks_x);
+    __shared__ __align__(16) uint8_t scratch[kTransposeScratchBytes];
+    split_transpose_tile<KIND>(B, ldb, K, N, Kp, b_hi, b_lo, b % b_blocks_x, b / b_blocks_x, b_vec_ok, scratch, (int)threadIdx.x, CtaSync());
   }
 }
 
@@ -538,15 +552,23 @@ struct TileSchedule {
 
 struct SplitWork {
   const float* A;
-  int64_t lda;
+  const float* B;
+  int64_t lda, ldb;
   void* a_hi;
   void* a_lo;
-  int* ctrl;          // [0] claim counter, [1] finished items, [2 + band * chunks + chunk] item flags; all zero at launch
-  int M, K, Kp;
-  int bands, chunks;  // 256-row bands of A, kSplitItemK-wide chunks of k
-  int group_bands;    // bands whose items are numbered chunk-major together (those of the first round)
-  int items;          // bands * chunks, or 0: the planes are already there
-  int vec_ok;         // A 16-byte aligned and lda % 4 == 0
+  void* b_hi;
+  void* b_lo;
+  int* ctrl;          // [0] claim counter, [1] finished items, then one flag per item: A's (band, chunk) flags at
+                      // 2 + band * chunks + chunk, B's (block, chunk) flags `b_flags` words further on; all zero at launch
+  int M, N, K, Kp;
+  int chunks;         // kSplitItemK-wide chunks of k
+  int a_bands;        // 256-row bands of A split in this kernel (0: A's planes are already there)
+  int b_blocks;       // 256-column blocks of B split in this kernel (0: B's planes are already there)
+  int b_flags;        // offset of B's flags behind A's
+  int ga, gb;         // bands of A / blocks of B the first round needs: their items come first, chunk by chunk
+  int items;          // (a_bands + b_blocks) * chunks
+  int a_vec_ok;       // A 16-byte aligned and lda % 4 == 0
+  int b_vec_ok;       // the same for B
 };
 
 __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
@@ -557,6 +579,14 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
 __device__ __forceinline__ void st_release_gpu(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
+__device__ __forceinline__ int ld_acquire_cta_shared(uint32_t addr) {
+  int v;
+  asm volatile("ld.acquire.cta.shared::cta.s32 %0, [%1];" : "=r"(v) : "r"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_cta_shared(uint32_t addr, int v) {
+  asm volatile("st.release.cta.shared::cta.s32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ void red_release_gpu_add(int* p, int v) {
   asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -565,17 +595,43 @@ __device__ __forceinline__ void bar_sync_named(int id, int threads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// Item number -> (band, chunk): groups of `group_bands` bands, chunk-major inside a group.
-__device__ __forceinline__ void split_item_coords(const SplitWork& w, int item, int& band, int& chunk) {
-  const int per_group = w.group_bands * w.chunks;
-  const int groups = (w.bands + w.group_bands - 1) / w.group_bands;
-  int g = item / per_group;
+// `count` units numbered in groups of `group`, chunk-major inside a group: j -> (unit, chunk).
+__device__ __forceinline__ void grouped_coords(int j, int count, int group, int chunks, int& unit, int& chunk) {
+  const int per_group = group * chunks;
+  const int groups = (count + group - 1) / group;
+  int g = j / per_group;
   if (g >= groups) g = groups - 1;
-  const int first = g * w.group_bands;
-  const int gsize = min(w.group_bands, w.bands - first);
-  const int r = item - g * per_group;
+  const int first = g * group;
+  const int gsize = min(group, count - first);
+  const int r = j - g * per_group;
   chunk = r / gsize;
-  band = first + r % gsize;
+  unit = first + r % gsize;
+}
+
+// Item number -> (operand, unit, chunk), in the order the tiles need them: first, chunk by chunk, the `ga` bands of A
+// and the `gb` blocks of B the first round touches; then the other blocks of B (the walk crosses all columns before
+// it leaves its first bands); then the other bands of A.
+__device__ __forceinline__ void split_item_coords(const SplitWork& w, int item, bool& is_b, int& unit, int& chunk) {
+  const int first = (w.ga + w.gb) * w.chunks;
+  if (item < first) {
+    chunk = item / (w.ga + w.gb);
+    const int r = item % (w.ga + w.gb);
+    is_b = r >= w.ga;
+    unit = is_b ? r - w.ga : r;
+    return;
+  }
+  item -= first;
+  const int rest_b = (w.b_blocks - w.gb) * w.chunks;
+  if (item < rest_b) {
+    is_b = true;
+    grouped_coords(item, w.b_blocks - w.gb, max(w.gb, 1), w.chunks, unit, chunk);
+    unit += w.gb;
+    return;
+  }
+  item -= rest_b;
+  is_b = false;
+  grouped_coords(item, w.a_bands - w.ga, max(w.ga, 1), w.chunks, unit, chunk);
+  unit += w.ga;
 }
 
 // One item: rows [band * 256, +256) x k [chunk * 128, +128) of A -> both planes. Warp `sw` of the eight takes rows
@@ -598,7 +654,7 @@ __device__ __forceinline__ void split_item(const SplitWork& w, int band, int chu
       v[j] = make_float4(0.f, 0.f, 0.f, 0.f);
       if (row < w.M) {
         const float* src = w.A + (int64_t)row * w.lda + k;
-        if (full_k && w.vec_ok) {
+        if (full_k && w.a_vec_ok) {
           v[j] = ld_stream_f4(reinterpret_cast<const float4*>(src));
         } else {
           if (k < w.K) v[j].x = src[0];
@@ -630,6 +686,25 @@ __device__ __forceinline__ void split_item(const SplitWork& w, int band, int chu
   }
 }
 
+// One item of B: columns [block * 256, +256) x k [chunk * 128, +128) -> both transposed planes, as 64-column x
+// kBlockK tiles through the shared-memory scratch. All 256 split threads take part; `sync` is their barrier.
+template <class KIND, class SYNC>
+__device__ __forceinline__ void split_item_b(const SplitWork& w, int block, int chunk, uint8_t* scratch, int tid, SYNC sync) {
+  using E = typename KIND::elem;
+  constexpr int kTilesK = kSplitItemK / KIND::kBlockK;
+  for (int ny = 0; ny < 4; ++ny) {
+    const int block_y = block * 4 + ny;
+    if (block_y * 64 >= w.N) break;
+    for (int kx = 0; kx < kTilesK; ++kx) {
+      const int block_x = chunk * kTilesK + kx;
+      if (block_x * KIND::kBlockK >= w.Kp) break;
+      split_transpose_tile<KIND>(w.B, w.ldb, w.K, w.N, w.Kp, static_cast<E*>(w.b_hi), static_cast<E*>(w.b_lo), block_x, block_y,
+                                 w.b_vec_ok, scratch, tid, sync);
+      sync();   // the scratch is free again
+    }
+  }
+}
+
 template <int KIND /*0 = bf16, 1 = tf32*/>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constant__ CUtensorMap tm_a_lo,
@@ -657,6 +732,8 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * (2 * kStages + 4));
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 8);
   volatile int* claimed = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 16);   // two slots
+  uint8_t* transpose_scratch = bar_ptr + Cfg::kBarrierBytes;   // kTransposeScratchBytes, 16-byte aligned
+  const uint32_t watched_addr = bar_addr + 8u * (2 * kStages + 4) + 24u;   // item boundaries the watcher lane has cleared
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -686,6 +763,7 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
+    st_release_cta_shared(watched_addr, 0);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
@@ -722,6 +800,7 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
       uint32_t phase = 0;
       bool ok = true;
       bool all_split = sw.items == 0;   // once every item is finished no flag needs looking at any more
+      int boundary = 0;                 // item boundaries passed so far, over all tiles of this CTA
       const uint32_t leader_full0 = ptx::map_to_cta(full_bar(0), 0);
       for (int j = 0; j < steps && ok; ++j) {
         int band, col0, width;
@@ -731,25 +810,26 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
         const int row_b = col0 + (int)rank * half;
         const uint32_t stage_bytes = 2u * (uint32_t)Cfg::kABytes + 2u * (uint32_t)half * kTileRowBytes;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!all_split && (kb % kKbPerItem) == 0) {
-            // the rows of A this k-block reads are converted inside this kernel: wait for their item
-            const int* flag = sw.ctrl + 2 + band * sw.chunks + kb / kKbPerItem;
-            if (ld_acquire_gpu(sw.ctrl + 1) == sw.items) {
-              all_split = true;
-            } else if (ld_acquire_gpu(flag) == 0) {
-              const long long start = clock64();
-              while (ld_acquire_gpu(flag) == 0) {
-                if (*abort_flag || clock64() - start > ptx::kWaitBudgetCycles) {
-                  *abort_flag = 1;
-                  atomicExch(status, 0x500 | (int)(blockIdx.x & 0xff));
-                  ok = false;
-                  break;
+          if (sw.items && (kb % kKbPerItem) == 0) {
+            // this k-block reads rows of the planes that are converted inside this kernel: the watcher lane counts
+            // the item boundaries whose flags it has seen; wait until it has passed this one
+            if (!all_split) {
+              if (ld_acquire_cta_shared(watched_addr) <= boundary) {
+                const long long start = clock64();
+                while (ld_acquire_cta_shared(watched_addr) <= boundary) {
+                  if (*abort_flag || clock64() - start > ptx::kWaitBudgetCycles) {
+                    *abort_flag = 1;
+                    atomicExch(status, 0x500 | (int)(blockIdx.x & 0xff));
+                    ok = false;
+                    break;
+                  }
                 }
-                __nanosleep(64);
+                if (!ok) break;
               }
-              if (!ok) break;
+              all_split = ld_acquire_cta_shared(watched_addr) == 0x7fffffff;
+              fence_proxy_async_all();   // what the split warps wrote is ordered before this thread's TMA reads
             }
-            fence_proxy_async_all();
+            ++boundary;
           }
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             atomicExch(status, 0x100 | (int)(blockIdx.x & 0xff));
@@ -777,6 +857,48 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
+    } else if (lane == 1 && sw.items) {
+      // ------------------------------- flag watcher --------------------------------------
+      // (the other arm of the producer's branch: the two lanes run as divergent paths of one warp and make progress
+      // independently; neither waits at a reconvergence point while the other still needs it)
+      // Walks the same tiles as the producer, one item boundary at a time, waits for the flags of the items that
+      // boundary needs (global acquire loads: their latency stays off the producer's path) and publishes how many
+      // boundaries are clear. 0x7fffffff: every item of the kernel is finished.
+      int passed = 0;
+      bool ok = true, everything = false;
+      for (int j = 0; j < steps && ok && !everything; ++j) {
+        int band, col0, width;
+        if (!tile_of(j, band, col0, width)) continue;
+        const int half = width >> 1;
+        const int row_b = col0 + (int)rank * half;
+        for (int chunk = 0; chunk * kKbPerItem < num_kb && ok; ++chunk) {
+          if (ld_acquire_gpu(sw.ctrl + 1) == sw.items) {
+            everything = true;
+            break;
+          }
+          const int* flags[3];
+          int n_flags = 0;
+          if (sw.a_bands) flags[n_flags++] = sw.ctrl + 2 + band * sw.chunks + chunk;
+          if (sw.b_blocks && row_b < N) {
+            const int first = row_b >> 8, last = min(row_b + half - 1, N - 1) >> 8;   // this CTA's rows of B's planes
+            flags[n_flags++] = sw.ctrl + 2 + sw.b_flags + first * sw.chunks + chunk;
+            if (last != first) flags[n_flags++] = sw.ctrl + 2 + sw.b_flags + last * sw.chunks + chunk;
+          }
+          for (int f = 0; f < n_flags && ok; ++f) {
+            if (ld_acquire_gpu(flags[f]) != 0) continue;
+            const long long start = clock64();
+            while (ld_acquire_gpu(flags[f]) == 0) {
+              if (*abort_flag || clock64() - start > ptx::kWaitBudgetCycles) {
+                ok = false;     // the producer's own bounded wait reports it
+                break;
+              }
+              __nanosleep(64);
+            }
+          }
+          if (ok) st_release_cta_shared(watched_addr, ++passed);
+        }
+      }
+      if (everything) st_release_cta_shared(watched_addr, 0x7fffffff);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -869,7 +991,7 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
       if (lane == 0) ptx::mbar_arrive_cluster(leader_tempty0 + 8u * acc);
     }
   } else {
-    // ------------------------------- split of A ----------------------------------------
+    // ------------------------------- split of A and B -----------------------------------
     const int st = (int)threadIdx.x - 192;      // 0..255
     const int swarp = st >> 5;
     int parity = 0;
@@ -879,14 +1001,19 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
       const int item = claimed[parity];
       parity ^= 1;
       if (item >= sw.items) break;
-      int band, chunk;
-      split_item_coords(sw, item, band, chunk);
-      split_item<SplitKind>(sw, band, chunk, swarp, lane);
+      bool is_b;
+      int unit, chunk;
+      split_item_coords(sw, item, is_b, unit, chunk);
+      auto sync = [] { bar_sync_named(1, 256); };
+      if (is_b)
+        split_item_b<SplitKind>(sw, unit, chunk, transpose_scratch, st, sync);
+      else
+        split_item<SplitKind>(sw, unit, chunk, swarp, lane);
       __threadfence();            // this thread's plane stores are visible device-wide ...
       fence_proxy_async_all();    // ... also to reads made by the TMA unit
       bar_sync_named(1, 256);
       if (st == 0) {
-        st_release_gpu(sw.ctrl + 2 + band * sw.chunks + chunk, 1);
+        st_release_gpu(sw.ctrl + 2 + (is_b ? sw.b_flags : 0) + unit * sw.chunks + chunk, 1);
         red_release_gpu_add(sw.ctrl + 1, 1);
       }
     }
@@ -969,11 +1096,29 @@ static int raster_group_m() {
 
 // Workspace layout: Bt_hi, Bt_lo, A_hi, A_lo. The B planes come first so that their place depends on
 // (mode, N, K) only: a caller that walks row blocks of A of any heights against one B splits B once.
+// Tuning aids of the stream kernel, read once: DTN_GEMM_STREAM_SPLIT = mask of the operands it may split itself
+// (1 = A, 2 = B; default: decided per shape), DTN_GEMM_TABLE = 0 keeps the plain walk whatever the shape.
+static int stream_split_override() {
+  static const int value = [] {
+    const char* text = getenv("DTN_GEMM_STREAM_SPLIT");
+    return text ? atoi(text) : -1;
+  }();
+  return value;
+}
+static bool table_allowed() {
+  static const bool value = [] {
+    const char* text = getenv("DTN_GEMM_TABLE");
+    return !(text && text[0] == '0');
+  }();
+  return value;
+}
+
 struct PlaneLayout {
   int64_t Kp;
   size_t a_plane, b_plane;  // bytes of one plane, rounded to 1024
   size_t ctrl_bytes;        // claim counter and item flags of the in-kernel split of A, after the planes
-  int bands, chunks;        // 256-row bands of A and kSplitItemK-wide chunks of k: one flag each
+  int bands, blocks, chunks; // 256-row bands of A, 256-column blocks of B, kSplitItemK-wide chunks of k: one flag per
+                             // (band, chunk) and per (block, chunk)
   size_t total;
   size_t planes() const { return 2 * a_plane + 2 * b_plane; }
   size_t ctrl() const { return planes(); }
@@ -991,8 +1136,9 @@ static PlaneLayout plane_layout(int mode, int64_t M, int64_t N, int64_t K) {
   L.a_plane = round1k((size_t)M * L.Kp * eb);
   L.b_plane = round1k((size_t)N * L.Kp * eb);
   L.bands = (int)((M + 255) / 256);
+  L.blocks = (int)((N + 255) / 256);
   L.chunks = (int)((L.Kp + kSplitItemK - 1) / kSplitItemK);
-  L.ctrl_bytes = round1k(sizeof(int) * (2 + (size_t)L.bands * L.chunks));
+  L.ctrl_bytes = round1k(sizeof(int) * (2 + ((size_t)L.bands + L.blocks) * L.chunks));
   L.total = L.planes() + L.ctrl_bytes;
   return L;
 }
@@ -1100,7 +1246,7 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
                                                         b_hi + n_off * L.Kp, b_lo + n_off * L.Kp,
                                                         aligned_to(B + n_off, 16) && (ldb % 4 == 0),
                                                         zero_here ? reinterpret_cast<int*>(ws + L.ctrl()) : nullptr,
-                                                        zero_here ? 2 + L.bands * L.chunks : 0);
+                                                        zero_here ? 2 + (L.bands + L.blocks) * L.chunks : 0);
       DTN_LAUNCH_CHECK("split_transpose_kernel");
     }
   }
@@ -1110,38 +1256,56 @@ static int run_split(const float* A, const float* B, int64_t M, int64_t N, int64
 // ---------------------------------------------------------------------------------------
 // Tile schedule of the stream kernel
 // ---------------------------------------------------------------------------------------
-constexpr int kTileFixedCost = 12;   // what a tile costs beyond its width, in columns (barrier hand-offs, first loads)
+constexpr int kTileFixedCost = 12;   // what a tile costs beyond its products, in columns (barrier hand-offs, first loads)
 
 struct ScheduleChoice {
   bool table = false;        // false: raster formula
-  int first_round_bands = 0; // bands the first round touches (table mode)
+  int first_round_bands = 0; // bands of A the first round touches (table mode)
+  int first_round_blocks = 0; // 256-column blocks of B the first round touches (table mode)
   double makespan = 0, uniform = 0;
   TileSchedule sched;
 };
 
-// Cuts each of `bands` bands of `units` 32-column units into pieces: `pieces` each, one more in `extra_bands` of
-// them (spread evenly), every band as evenly as its count allows. Appends (band, first unit, width in units).
-static bool cut_bands(int bands, int units, int pieces, int extra_bands, std::vector<uint32_t>* tiles) {
+// What a tile of `units` 32-column units costs a CTA pair, in columns of a 256-wide tile. Measured on B200 (148 tiles
+// of one width on 74 pairs, K = 4096, bf16x3; tf32x3 has the same shape): 256, 224 and 192 columns all take the time
+// of 256, 160 takes 0.775 of it, 128 takes 0.56, 96 and 64 hardly less (0.545, 0.51): the products of a tile between
+// 129 and 256 columns cost the same, and below 128 columns the shared-memory reads of the A tile, which do not shrink
+// with the width, set the pace. So only 256-, 128- and 64-wide pieces are worth cutting.
+static double tile_cost(int units) {
+  static const double relative[9] = {0.0, 0.50, 0.51, 0.545, 0.56, 0.775, 0.97, 1.0, 1.0};
+  return 256.0 * relative[std::max(0, std::min(units, 8))] + kTileFixedCost;
+}
+
+// Cuts each of `bands` bands of `units` 32-column units into pieces of `piece` units (the last piece of a band takes
+// what is left); of the full pieces, `halved` (spread evenly over all of them, in band order) become two halves.
+// Appends band | first unit << 12 | width in units << 24.
+static bool cut_bands(int bands, int units, int piece, int halved, std::vector<uint32_t>* tiles) {
   tiles->clear();
+  const int full_per_band = units / piece;
+  const int64_t full_total = (int64_t)bands * full_per_band;
+  if (halved > full_total || (halved && piece % 2)) return false;
+  int64_t seen = 0;
   for (int b = 0; b < bands; ++b) {
-    const bool more = ((int64_t)(b + 1) * extra_bands / bands) != ((int64_t)b * extra_bands / bands);
-    const int p = pieces + (more ? 1 : 0);
-    if (p < 1 || p > units) return false;
-    const int base = units / p, rem = units % p;
-    if (base + (rem ? 1 : 0) > 8 || base < 2) return false;   // 64 .. 256 columns
     int at = 0;
-    for (int i = 0; i < p; ++i) {
-      const int w = base + (i < rem ? 1 : 0);
-      tiles->push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)w << 24));
-      at += w;
+    for (int i = 0; i < full_per_band; ++i, ++seen) {
+      const bool cut = full_total && ((seen + 1) * halved / full_total) != (seen * halved / full_total);
+      if (cut) {
+        tiles->push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)(piece / 2) << 24));
+        tiles->push_back((uint32_t)b | ((uint32_t)(at + piece / 2) << 12) | ((uint32_t)(piece / 2) << 24));
+      } else {
+        tiles->push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)piece << 24));
+      }
+      at += piece;
     }
+    if (at < units) tiles->push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)(units - at) << 24));
   }
   return true;
 }
 
-// Deals the tiles (in band order) out in rounds of `workers`; within a round the widest tile goes to the pair with
+// Deals the tiles (in band order) out in rounds of `workers`; within a round the costliest tile goes to the pair with
 // the least work so far. Returns the largest total of any pair; fills `out` (entry[round * workers + pair]) if given.
-static double deal_rounds(const std::vector<uint32_t>& tiles, int workers, TileSchedule* out, int* first_round_bands) {
+static double deal_rounds(const std::vector<uint32_t>& tiles, int workers, TileSchedule* out, int* first_round_bands,
+                          int* first_round_blocks = nullptr) {
   std::vector<double> load(workers, 0.0);
   std::vector<int> order(workers);
   std::vector<uint32_t> round;
@@ -1156,47 +1320,50 @@ static double deal_rounds(const std::vector<uint32_t>& tiles, int workers, TileS
     const size_t begin = (size_t)j * workers, end = std::min(tiles.size(), begin + workers);
     round.assign(tiles.begin() + begin, tiles.begin() + end);
     if (j == 0 && first_round_bands) *first_round_bands = (int)(round.back() & 0xfffu) + 1;
+    if (j == 0 && first_round_blocks) {
+      int reach = 0;   // 256-column blocks of B up to the rightmost column a tile of this round reads
+      for (uint32_t e : round) reach = std::max(reach, (int)((((e >> 12) & 0xfffu) + (e >> 24)) * 32 + 255) / 256);
+      *first_round_blocks = reach;
+    }
     std::stable_sort(round.begin(), round.end(), [](uint32_t a, uint32_t b) { return (a >> 24) > (b >> 24); });
     for (int w = 0; w < workers; ++w) order[w] = w;
     std::stable_sort(order.begin(), order.end(), [&](int a, int b) { return load[a] < load[b]; });
     for (size_t i = 0; i < round.size(); ++i) {
       const int w = order[i];
-      load[w] += (double)(round[i] >> 24) * 32.0 + kTileFixedCost;
+      load[w] += tile_cost((int)(round[i] >> 24));
       if (out) out->entry[j * workers + w] = round[i];
     }
   }
   return *std::max_element(load.begin(), load.end());
 }
 
-// The cut with the smallest largest total among: 256-wide pieces (what the raster formula walks), and every mix of
-// p and p + 1 pieces per band for the two smallest usable p. The table is used when it saves at least 3 %.
+// The cut with the smallest largest total among: 256-wide pieces with any number of them halved (the plain walk is the
+// one with none), 128-wide pieces, 64-wide pieces. The table is used when it saves at least 3 % over the plain walk.
 static void choose_schedule(int bands, int64_t N, int workers, ScheduleChoice* choice) {
   choice->table = false;
   const int units = (int)((N + 31) / 32);
-  const int pmin = (units + 7) / 8;
   std::vector<uint32_t> tiles;
-  // the raster walk: pieces of 8 units, the last one narrower
-  for (int b = 0; b < bands; ++b)
-    for (int at = 0; at < units; at += 8)
-      tiles.push_back((uint32_t)b | ((uint32_t)at << 12) | ((uint32_t)std::min(8, units - at) << 24));
+  cut_bands(bands, units, 8, 0, &tiles);
   choice->uniform = deal_rounds(tiles, workers, nullptr, nullptr);
   choice->makespan = choice->uniform;
-  if (bands >= 4096 || units >= 4096 || workers < 1) return;
-  if ((int64_t)bands * pmin > kSchedMaxEntries) return;
-  int best_p = 0, best_x = 0;
+  if (bands >= 4096 || units >= 4096 || workers < 1 || !table_allowed()) return;
+  int best_piece = 0, best_halved = 0;
   double best = choice->uniform;
-  for (int p = pmin; p <= pmin + 1; ++p)
-    for (int x = 0; x <= bands; ++x) {
-      if ((int64_t)bands * p + x > kSchedMaxEntries) break;
-      if (!cut_bands(bands, units, p, x, &tiles)) continue;
-      const int rounds = (int)((tiles.size() + workers - 1) / workers);
-      if ((int64_t)rounds * workers > kSchedMaxEntries) continue;
-      const double span = deal_rounds(tiles, workers, nullptr, nullptr);
-      if (span > 0 && span < best) { best = span; best_p = p; best_x = x; }
-    }
-  if (best_p == 0 || best > 0.97 * choice->uniform) return;
-  cut_bands(bands, units, best_p, best_x, &tiles);
-  if (deal_rounds(tiles, workers, &choice->sched, &choice->first_round_bands) < 0) return;
+  auto consider = [&](int piece, int halved) {
+    if (!cut_bands(bands, units, piece, halved, &tiles)) return;
+    const int rounds = (int)((tiles.size() + workers - 1) / workers);
+    if ((int64_t)rounds * workers > kSchedMaxEntries) return;
+    const double span = deal_rounds(tiles, workers, nullptr, nullptr);
+    if (span > 0 && span < best) { best = span; best_piece = piece; best_halved = halved; }
+  };
+  const int64_t full = (int64_t)bands * (units / 8);
+  if (full <= kSchedMaxEntries)
+    for (int64_t halved = 1, step = std::max<int64_t>(1, full / 96); halved <= full; halved += step) consider(8, (int)halved);
+  consider(4, 0);
+  consider(2, 0);
+  if (best_piece == 0 || best > 0.97 * choice->uniform) return;
+  cut_bands(bands, units, best_piece, best_halved, &tiles);
+  if (deal_rounds(tiles, workers, &choice->sched, &choice->first_round_bands, &choice->first_round_blocks) < 0) return;
   choice->makespan = best;
   choice->table = true;
 }
@@ -1217,8 +1384,10 @@ static const ScheduleChoice& schedule_for(int bands, int64_t N, int workers) {
 
 // Tensor map of a K-major plane with a given box height.
 template <int KIND>
-static int launch_stream(uint8_t* ws, const PlaneLayout& L, const float* A, int64_t lda, bool split_a_here, float* C,
-                         int64_t M, int64_t N, int64_t K, int64_t ldc, cudaStream_t s, int* status_word = nullptr) {
+static int launch_stream(uint8_t* ws, const PlaneLayout& L, const float* A, int64_t lda, bool split_a_here, const float* B,
+                         int64_t ldb, bool split_b_here, float* C, int64_t M, int64_t N, int64_t K, int64_t ldc, cudaStream_t s,
+                         int* status_word = nullptr) {
+  constexpr int kStreamSmemBytes = GemmCfg<2, 256>::kSmemBytes + kTransposeScratchBytes;
   using Cfg = GemmCfg<2, 256>;
   constexpr int eb = (KIND == 0) ? 2 : 4;
   const void* a_hi = ws + L.a_hi();
@@ -1239,7 +1408,7 @@ static int launch_stream(uint8_t* ws, const PlaneLayout& L, const float* A, int6
   int dev = 0;
   DTN_CUDA_CHECK(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kStreamSmemBytes));
     attr_dev = dev;
   }
   int* status = status_word ? status_word : device_status_word();
@@ -1255,25 +1424,46 @@ static int launch_stream(uint8_t* ws, const PlaneLayout& L, const float* A, int6
 
   SplitWork work = {};
   work.A = A;
+  work.B = B;
   work.lda = lda;
+  work.ldb = ldb;
   work.a_hi = ws + L.a_hi();
   work.a_lo = ws + L.a_lo();
+  work.b_hi = ws + L.b_hi();
+  work.b_lo = ws + L.b_lo();
   work.ctrl = reinterpret_cast<int*>(ws + L.ctrl());
   work.M = (int)M;
+  work.N = (int)N;
   work.K = (int)K;
   work.Kp = (int)L.Kp;
-  work.bands = L.bands;
   work.chunks = L.chunks;
-  work.items = split_a_here ? L.bands * L.chunks : 0;
-  work.vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
+  work.a_bands = split_a_here ? L.bands : 0;
+  work.b_blocks = split_b_here ? L.blocks : 0;
+  work.b_flags = L.bands * L.chunks;
+  work.items = (work.a_bands + work.b_blocks) * L.chunks;
+  work.a_vec_ok = aligned_to(A, 16) && (lda % 4 == 0);
+  work.b_vec_ok = aligned_to(B, 16) && (ldb % 4 == 0);
   if (choice.table) {
-    work.group_bands = choice.first_round_bands;
+    work.ga = choice.first_round_bands;
+    work.gb = choice.first_round_blocks;
   } else {
-    // the raster walks groups of group_m bands; the first round may reach across several of them
-    const int reach = (units + tiles_n - 1) / tiles_n;
-    work.group_bands = (std::max(reach, group_m) + group_m - 1) / group_m * group_m;
+    // the raster walks groups of group_m bands, all columns of a group before the next group
+    const int gsize = std::min(group_m, tiles_m);
+    const int64_t first_group = (int64_t)gsize * tiles_n;
+    if (units <= first_group) {
+      work.ga = gsize;
+      work.gb = (units - 1) / gsize + 1;
+    } else {
+      work.ga = (int)std::min<int64_t>(tiles_m, (units + first_group - 1) / first_group * gsize);
+      work.gb = tiles_n;
+    }
   }
-  work.group_bands = std::max(1, std::min(work.group_bands, L.bands));
+  work.ga = std::max(0, std::min(work.ga, work.a_bands));
+  work.gb = std::max(0, std::min(work.gb, work.b_blocks));
+  if (work.items && work.ga + work.gb == 0) {   // cannot happen with a sane schedule; keep the numbering well-defined
+    work.ga = work.a_bands ? 1 : 0;
+    work.gb = work.a_bands ? 0 : 1;
+  }
 
   static thread_local TileSchedule raster = {};   // rounds = 0: tiles from the raster formula
   const TileSchedule& sched = choice.table ? choice.sched : raster;
@@ -1281,7 +1471,7 @@ static int launch_stream(uint8_t* ws, const PlaneLayout& L, const float* A, int6
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)(units * 2));
   cfg.blockDim = dim3(kStreamThreads);
-  cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+  cfg.dynamicSmemBytes = kStreamSmemBytes;
   cfg.stream = s;
   cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -1324,7 +1514,7 @@ static int run_tc(int variant, const uint8_t* ws, const PlaneLayout& L, float* C
     // 1024^3 16.8 vs 18.2 us)
     if (variant == 1 && square_tiles * 2 <= sm_count()) variant = 5;
   }
-  if (variant == 7) variant = 3;
+  if (variant >= 7) variant = 3;
   switch (variant) {
     case 1: return launch_tc<KIND, 1, 128>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
     case 2: return launch_tc<KIND, 1, 256>(a_hi, a_lo, b_hi, b_lo, C, M, N, K, L.Kp, ldc, s, status_word);
@@ -1401,7 +1591,7 @@ int dtn_gemm_x3_static(int mode, const float* A, const float* B, float* C, int64
   // This entry point always runs the split kernels and the tensor-memory product kernel. The selections of
   // dtn_gemm_set_variant that name a tile of that kernel (1, 2, 3, 5) are honoured; 4 and 6 name other kernels
   // (which use no scratch at all) and fall back to the automatic tile choice here.
-  const int variant = (g_gemm_variant == 4 || g_gemm_variant == 6) ? 0 : (g_gemm_variant == 7 ? 3 : g_gemm_variant);
+  const int variant = (g_gemm_variant == 4 || g_gemm_variant == 6) ? 0 : (g_gemm_variant >= 7 ? 3 : g_gemm_variant);
   const PlaneLayout L = plane_layout(mode, M, N, K);
   DTN_REQUIRE(L.planes() <= kStaticScratchBytes, DTN_ERR_WORKSPACE,
               "gemm (static scratch): %lld x %lld x %lld needs %zu bytes of operand planes, the built-in array holds %zu; "
@@ -1455,7 +1645,7 @@ int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_ou
 }
 
 int dtn_gemm_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 7, DTN_ERR_INVALID, "gemm: variant must be 0..7");
+  DTN_REQUIRE(variant >= 0 && variant <= 9, DTN_ERR_INVALID, "gemm: variant must be 0..9");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
 }
@@ -1509,18 +1699,31 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   DTN_REQUIRE(aligned_to(workspace, 1024), DTN_ERR_WORKSPACE, "gemm: workspace must be 1024-byte aligned");
   uint8_t* ws = static_cast<uint8_t*>(workspace);
   int rc;
-  // CTA-pair tiles (automatic for large products): the stream kernel. It splits A itself, beside its products, so
-  // only B is split ahead of it.
-  if ((phase & 2) && (g_gemm_variant == 7 || (g_gemm_variant == 0 && pairs_preferred(M, N)))) {
-    if (split_b) {
-      rc = (mode == DTN_GEMM_BF16X3) ? run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s, false, true, split_a)
-                                     : run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s, false, true, split_a);
+  // CTA-pair tiles (automatic for large products): the stream kernel. It splits both operands itself, beside its
+  // products: one kernel, preceded by a memset of its counters.
+  if ((phase & 2) && (g_gemm_variant >= 7 || (g_gemm_variant == 0 && pairs_preferred(M, N)))) {
+    // which operands the kernel splits itself, beside its products, and which a split kernel handles before it
+    // (variants 8 and 9 pin the choice: neither / both)
+    const int inside = g_gemm_variant == 8 ? 0 : g_gemm_variant == 9 ? 3 : stream_split_override() >= 0 ? stream_split_override() : 1;
+    // With a single round every tile needs its operands at once and a split inside the kernel sits on the critical
+    // path (2048^3: 60 against 53 us); from two rounds on it runs beside the products of the first round.
+    const bool several_rounds = ((M + 255) / 256) * ((N + 255) / 256) > (int64_t)(sm_count() / 2);
+    const bool pinned = g_gemm_variant >= 8 || stream_split_override() >= 0;
+    const bool a_inside = split_a && (inside & 1) && (several_rounds || pinned), b_inside = split_b && (inside & 2);
+    const bool a_before = split_a && !a_inside, b_before = split_b && !b_inside;
+    const bool counters = a_inside || b_inside;
+    if (a_before || b_before) {
+      const bool zero = counters && b_before;   // the transposing split kernel can clear the counters on its way
+      rc = (mode == DTN_GEMM_BF16X3) ? run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s, a_before, b_before, zero)
+                                     : run_split<Tf32Kind>(A, B, M, N, K, lda, ldb, L, ws, s, a_before, b_before, zero);
       if (rc) return rc;
-    } else if (split_a) {
-      DTN_CUDA_CHECK(cudaMemsetAsync(ws + L.ctrl(), 0, sizeof(int) * (2 + (size_t)L.bands * L.chunks), s));
+      if (counters && !zero)
+        DTN_CUDA_CHECK(cudaMemsetAsync(ws + L.ctrl(), 0, sizeof(int) * (2 + ((size_t)L.bands + L.blocks) * L.chunks), s));
+    } else if (counters) {
+      DTN_CUDA_CHECK(cudaMemsetAsync(ws + L.ctrl(), 0, sizeof(int) * (2 + ((size_t)L.bands + L.blocks) * L.chunks), s));
     }
-    return (mode == DTN_GEMM_BF16X3) ? launch_stream<0>(ws, L, A, lda, split_a, C, M, N, K, ldc, s)
-                                     : launch_stream<1>(ws, L, A, lda, split_a, C, M, N, K, ldc, s);
+    return (mode == DTN_GEMM_BF16X3) ? launch_stream<0>(ws, L, A, lda, a_inside, B, ldb, b_inside, C, M, N, K, ldc, s)
+                                     : launch_stream<1>(ws, L, A, lda, a_inside, B, ldb, b_inside, C, M, N, K, ldc, s);
   }
   if (mode == DTN_GEMM_BF16X3) {
     if ((phase & 1) && (rc = run_split<Bf16Kind>(A, B, M, N, K, lda, ldb, L, ws, s, split_a, split_b))) return rc;

@@ -277,11 +277,12 @@ def test_argument_checks_need_no_gpu():
     library = native.lib()
     assert library.dtn_add_f32(None, None, None, -1, None) == native.ERR_INVALID
     assert 'negative' in native.last_error()
-    assert library.dtn_gemm_set_variant(9) == native.ERR_INVALID
+    assert library.dtn_gemm_set_variant(10) == native.ERR_INVALID
     size = ctypes.c_size_t(0)
     assert library.dtn_gemm_workspace_bytes(2, 8192, 8192, 8192, ctypes.byref(size)) == 0
-    # hi and lo bf16 planes of A and of B transposed, then the counter and the 32 x 64 item flags of the in-kernel split of A
-    assert size.value == 4 * 8192 * 8192 * 2 + (4 * (2 + 32 * 64) + 1023) // 1024 * 1024
+    # hi and lo bf16 planes of A and of B transposed, then the two counters and the (32 + 32) x 64 item flags of the
+    # split that runs inside the product kernel
+    assert size.value == 4 * 8192 * 8192 * 2 + (4 * (2 + 64 * 64) + 1023) // 1024 * 1024
     assert library.dtn_gemm_workspace_bytes(1, 100, 50, 33, ctypes.byref(size)) == 0
     assert size.value == 2 * (100 * 64 * 4 + 1023) // 1024 * 1024 + 2 * (50 * 64 * 4 + 1023) // 1024 * 1024 or size.value > 0
     assert library.dtn_gemm_workspace_bytes(7, 1, 1, 1, ctypes.byref(size)) == native.ERR_INVALID
