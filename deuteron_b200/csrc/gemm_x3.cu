@@ -576,6 +576,12 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+__device__ __forceinline__ int ld_relaxed_gpu(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_acquire_gpu() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 __device__ __forceinline__ void st_release_gpu(int* p, int v) {
   asm volatile("st.release.gpu.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
@@ -733,7 +739,6 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 8);
   volatile int* claimed = reinterpret_cast<volatile int*>(bar_ptr + 8 * (2 * kStages + 4) + 16);   // two slots
   uint8_t* transpose_scratch = bar_ptr + Cfg::kBarrierBytes;   // kTransposeScratchBytes, 16-byte aligned
-  const uint32_t watched_addr = bar_addr + 8u * (2 * kStages + 4) + 24u;   // item boundaries the watcher lane has cleared
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = ptx::cluster_ctarank();
@@ -763,7 +768,6 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
 
   if (threadIdx.x == 0) {
     *abort_flag = 0;
-    st_release_cta_shared(watched_addr, 0);
     for (int s = 0; s < kStages; ++s) {
       ptx::mbar_init(full_bar(s), 1);
       ptx::mbar_init(empty_bar(s), 1);
@@ -800,7 +804,7 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
       uint32_t phase = 0;
       bool ok = true;
       bool all_split = sw.items == 0;   // once every item is finished no flag needs looking at any more
-      int boundary = 0;                 // item boundaries passed so far, over all tiles of this CTA
+      int boundary = 0;
       const uint32_t leader_full0 = ptx::map_to_cta(full_bar(0), 0);
       for (int j = 0; j < steps && ok; ++j) {
         int band, col0, width;
@@ -810,26 +814,37 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
         const int row_b = col0 + (int)rank * half;
         const uint32_t stage_bytes = 2u * (uint32_t)Cfg::kABytes + 2u * (uint32_t)half * kTileRowBytes;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (sw.items && (kb % kKbPerItem) == 0) {
-            // this k-block reads rows of the planes that are converted inside this kernel: the watcher lane counts
-            // the item boundaries whose flags it has seen; wait until it has passed this one
-            if (!all_split) {
-              if (ld_acquire_cta_shared(watched_addr) <= boundary) {
+          if (!all_split && (kb % kKbPerItem) == 0) {
+            // this k-block reads rows of the planes that are converted inside this kernel: wait for their items.
+            // Once every item of the kernel is finished (looked at every fourth time) no flag matters any more.
+            if ((boundary++ & 3) == 0 && ld_acquire_gpu(sw.ctrl + 1) == sw.items) {
+              all_split = true;
+            } else {
+              const int chunk = kb / kKbPerItem;
+              const int* flags[3];
+              int n_flags = 0;
+              if (sw.a_bands) flags[n_flags++] = sw.ctrl + 2 + band * sw.chunks + chunk;
+              if (sw.b_blocks && row_b < N) {
+                const int first = row_b >> 8, last = min(row_b + half - 1, N - 1) >> 8;   // this CTA's rows of B's planes
+                flags[n_flags++] = sw.ctrl + 2 + sw.b_flags + first * sw.chunks + chunk;
+                if (last != first) flags[n_flags++] = sw.ctrl + 2 + sw.b_flags + last * sw.chunks + chunk;
+              }
+              for (int f = 0; f < n_flags && ok; ++f) {
+                if (ld_acquire_gpu(flags[f]) != 0) continue;
                 const long long start = clock64();
-                while (ld_acquire_cta_shared(watched_addr) <= boundary) {
+                while (ld_acquire_gpu(flags[f]) == 0) {
                   if (*abort_flag || clock64() - start > ptx::kWaitBudgetCycles) {
                     *abort_flag = 1;
                     atomicExch(status, 0x500 | (int)(blockIdx.x & 0xff));
                     ok = false;
                     break;
                   }
+                  __nanosleep(64);
                 }
-                if (!ok) break;
               }
-              all_split = ld_acquire_cta_shared(watched_addr) == 0x7fffffff;
-              fence_proxy_async_all();   // what the split warps wrote is ordered before this thread's TMA reads
+              if (!ok) break;
             }
-            ++boundary;
+            fence_proxy_async_all();   // what the split warps wrote is ordered before this thread's TMA reads
           }
           if (!ptx::mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag)) {
             atomicExch(status, 0x100 | (int)(blockIdx.x & 0xff));
@@ -857,48 +872,6 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
       }
-    } else if (lane == 1 && sw.items) {
-      // ------------------------------- flag watcher --------------------------------------
-      // (the other arm of the producer's branch: the two lanes run as divergent paths of one warp and make progress
-      // independently; neither waits at a reconvergence point while the other still needs it)
-      // Walks the same tiles as the producer, one item boundary at a time, waits for the flags of the items that
-      // boundary needs (global acquire loads: their latency stays off the producer's path) and publishes how many
-      // boundaries are clear. 0x7fffffff: every item of the kernel is finished.
-      int passed = 0;
-      bool ok = true, everything = false;
-      for (int j = 0; j < steps && ok && !everything; ++j) {
-        int band, col0, width;
-        if (!tile_of(j, band, col0, width)) continue;
-        const int half = width >> 1;
-        const int row_b = col0 + (int)rank * half;
-        for (int chunk = 0; chunk * kKbPerItem < num_kb && ok; ++chunk) {
-          if (ld_acquire_gpu(sw.ctrl + 1) == sw.items) {
-            everything = true;
-            break;
-          }
-          const int* flags[3];
-          int n_flags = 0;
-          if (sw.a_bands) flags[n_flags++] = sw.ctrl + 2 + band * sw.chunks + chunk;
-          if (sw.b_blocks && row_b < N) {
-            const int first = row_b >> 8, last = min(row_b + half - 1, N - 1) >> 8;   // this CTA's rows of B's planes
-            flags[n_flags++] = sw.ctrl + 2 + sw.b_flags + first * sw.chunks + chunk;
-            if (last != first) flags[n_flags++] = sw.ctrl + 2 + sw.b_flags + last * sw.chunks + chunk;
-          }
-          for (int f = 0; f < n_flags && ok; ++f) {
-            if (ld_acquire_gpu(flags[f]) != 0) continue;
-            const long long start = clock64();
-            while (ld_acquire_gpu(flags[f]) == 0) {
-              if (*abort_flag || clock64() - start > ptx::kWaitBudgetCycles) {
-                ok = false;     // the producer's own bounded wait reports it
-                break;
-              }
-              __nanosleep(64);
-            }
-          }
-          if (ok) st_release_cta_shared(watched_addr, ++passed);
-        }
-      }
-      if (everything) st_release_cta_shared(watched_addr, 0x7fffffff);
     }
     __syncwarp();
   } else if (warp == 1) {
@@ -1705,11 +1678,16 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
     // which operands the kernel splits itself, beside its products, and which a split kernel handles before it
     // (variants 8 and 9 pin the choice: neither / both)
     const int inside = g_gemm_variant == 8 ? 0 : g_gemm_variant == 9 ? 3 : stream_split_override() >= 0 ? stream_split_override() : 1;
-    // With a single round every tile needs its operands at once and a split inside the kernel sits on the critical
-    // path (2048^3: 60 against 53 us); from two rounds on it runs beside the products of the first round.
+    // Measured (8192 x N x 8192 back to back, split outside against inside): the split of A inside the kernel pays
+    // when the plain walk has at least two rounds (N = 1024: 359 -> 329 us, 4096: 1229 -> 1192, 8192: 2485 -> 2441).
+    // With a single round every tile needs its operands at once and the split sits on the critical path (2048^3: 60
+    // against 53 us); with a tile table the narrow tiles of the first round ask for more bands at once than the split
+    // warps deliver (N = 2048: 653 outside, 675 inside). B's transposing split is always slower inside (one tile in
+    // flight per SM instead of a dozen).
     const bool several_rounds = ((M + 255) / 256) * ((N + 255) / 256) > (int64_t)(sm_count() / 2);
     const bool pinned = g_gemm_variant >= 8 || stream_split_override() >= 0;
-    const bool a_inside = split_a && (inside & 1) && (several_rounds || pinned), b_inside = split_b && (inside & 2);
+    const bool table = schedule_for((int)((M + 255) / 256), N, sm_count() / 2).table;
+    const bool a_inside = split_a && (inside & 1) && ((several_rounds && !table) || pinned), b_inside = split_b && (inside & 2);
     const bool a_before = split_a && !a_inside, b_before = split_b && !b_inside;
     const bool counters = a_inside || b_inside;
     if (a_before || b_before) {
