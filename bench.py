@@ -955,7 +955,7 @@ def run_all_gather(args) -> None:
     dist.destroy_process_group()
 
 
-PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'gemm_skinny', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max',
+PROFILE_CASES = ('gemm_bf16x3', 'gemm_tf32x3', 'gemm_bf16x3_8192', 'gemm_bf16x3_2048', 'gemm_skinny', 'attention', 'add', 'f16_narrow', 'f16_widen', 'f16_copy', 'row_sum', 'row_max',
                  'row_softmax', 'rms_norm', 'fused_affine')
 
 
@@ -982,7 +982,8 @@ def run_profile_case(name: str, launches: int) -> None:
         pointers = [constants[plan.buffers[f'in{i}'][0]].data_ptr() for i in range(len(plan.params['inputs']))]
         call = lambda: native.elementwise_program(plan.params, pointers, z.data_ptr(), torch.cuda.current_stream().cuda_stream)
     elif name.startswith('gemm_'):
-        n = 4096
+        n = int(name.rsplit('_', 1)[1]) if name.rsplit('_', 1)[1].isdigit() else 4096
+        name = name if not name.rsplit('_', 1)[1].isdigit() else name.rsplit('_', 1)[0]
         a = torch.rand((n, n), device=device, generator=generator) * 2 - 1
         b = torch.rand((n, n), device=device, generator=generator) * 2 - 1
         c = torch.empty((n, n), device=device)
