@@ -469,7 +469,8 @@ def run_ours(args) -> None:
 
     # ONE M x N x K product for the whole job (seeds 7 and 11 on every rank); rank r owns the r-th block of output
     # columns: it needs all of A and its own columns of B, and writes its own columns of C. No exchange.
-    blocks = sharding.column_blocks(N, world)
+    shards = args.as_rank_of if (world == 1 and args.as_rank_of > 1) else world
+    blocks = sharding.column_blocks(N, shards)
     col0, col1 = blocks[rank]
     width = col1 - col0
     generator = torch.Generator(device=device)
@@ -477,7 +478,7 @@ def run_ours(args) -> None:
     a = torch.rand((M, K), device=device, generator=generator) * 2 - 1
     generator.manual_seed(11)
     b_full = torch.rand((K, N), device=device, generator=generator) * 2 - 1
-    b = b_full[:, col0:col1].contiguous() if world > 1 else b_full    # the rank's columns of B, as they arrive from its host
+    b = b_full[:, col0:col1].contiguous() if shards > 1 else b_full    # the rank's columns of B, as they arrive from its host
     c = torch.empty((M, width), device=device)
 
     def barrier() -> None:
@@ -549,54 +550,56 @@ def run_ours(args) -> None:
     # End to end, host buffers in, host buffers out. One GPU: compile_kernel + LocalRunner.execute. Several GPUs:
     # compile_kernel + sharding.ShardedHostProduct (every rank feeds its columns of B and 1/N of A's rows from its own
     # page-locked host memory, the rows of A are exchanged over NVLink, its columns of C return to its host).
-    graph, meta = schedules.matmul_example(M, N, K)
-    compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3, options=Options(contraction_precision='bf16x3'))
-    e2e_steps = max(3, min(args.steps, 10))
-    a_host_full, b_host_full = a.cpu().numpy(), b_full.cpu().numpy()
-    with LocalRunner(local_rank) as runner:
-        if world == 1:
-            host = {'left': runner.pinned((M, K), np.float32), 'right': runner.pinned((K, N), np.float32)}
-            host['left'][:] = a_host_full
-            host['right'][:] = b_host_full
-            result = {'result': runner.pinned((M, N), np.float32)}
-            run_e2e = lambda: runner.execute(compiled, host, result, synchronize=True)
-            h2d, d2h = 4 * (M * K + K * N), 4 * M * N
-            produced = result['result']
-            call = 'compile_kernel + LocalRunner.execute (pinned host buffers)'
-            stream = runner.stream
-        else:
-            product = sharding.ShardedHostProduct(compiled, rank, world, device)
-            rows_host = runner.pinned((product.owned_row_count, K), np.float32)
-            rows_host[:] = product.pack_rows(a_host_full)
-            cols_host = runner.pinned((K, width), np.float32)
-            cols_host[:] = b_host_full[:, col0:col1]
-            produced = runner.pinned((M, width), np.float32)
-            run_e2e = lambda: product.execute(rows_host, cols_host, produced, synchronize=True)
-            h2d, d2h = product.host_bytes()
-            call = ('compile_kernel + sharding.ShardedHostProduct.execute (pinned host buffers; each rank feeds its columns of B and '
-                    f'1/{world} of the rows of A, NCCL all-gather of the rows of A, {len(product.plan)} row blocks in flight)')
-            stream = product.compute
-        del a_host_full, b_host_full
-        for _ in range(2):
-            run_e2e()
-        barrier()
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record(stream)
-        for _ in range(e2e_steps):
-            run_e2e()
-        end.record(stream)
-        end.synchronize()
-        e2e_ms = over_ranks(begin.elapsed_time(end))
-        matches = over_ranks(float(np.array_equal(produced[::64], c[::64].cpu().numpy())), dist.ReduceOp.MIN if world > 1 else None)
-        h2d_total, d2h_total = int(over_ranks(float(h2d), dist.ReduceOp.SUM if world > 1 else None)), \
-            int(over_ranks(float(d2h), dist.ReduceOp.SUM if world > 1 else None))
-        link = host_link_rate(torch, dist, device, world, h2d, d2h)
-        e2e = {'value': FLOPS_PER_GEMM * e2e_steps / e2e_ms / 1e9, 'unit': 'TFLOP/s',
-               'h2d_bytes_per_step': h2d_total, 'd2h_bytes_per_step': d2h_total,
-               'h2d_bytes_per_step_rank0': h2d, 'd2h_bytes_per_step_rank0': d2h, 'steps': e2e_steps,
-               'ms_per_step': e2e_ms / e2e_steps, 'call': call, 'matches_resident_result': bool(matches),
-               'host_link': link, 'ms_per_step_over_host_link_ms': e2e_ms / e2e_steps / link['ms_for_one_step_bytes']}
-        del produced
+    e2e = None
+    if shards == world:
+        graph, meta = schedules.matmul_example(M, N, K)
+        compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3, options=Options(contraction_precision='bf16x3'))
+        e2e_steps = max(3, min(args.steps, 10))
+        a_host_full, b_host_full = a.cpu().numpy(), b_full.cpu().numpy()
+        with LocalRunner(local_rank) as runner:
+            if world == 1:
+                host = {'left': runner.pinned((M, K), np.float32), 'right': runner.pinned((K, N), np.float32)}
+                host['left'][:] = a_host_full
+                host['right'][:] = b_host_full
+                result = {'result': runner.pinned((M, N), np.float32)}
+                run_e2e = lambda: runner.execute(compiled, host, result, synchronize=True)
+                h2d, d2h = 4 * (M * K + K * N), 4 * M * N
+                produced = result['result']
+                call = 'compile_kernel + LocalRunner.execute (pinned host buffers)'
+                stream = runner.stream
+            else:
+                product = sharding.ShardedHostProduct(compiled, rank, world, device)
+                rows_host = runner.pinned((product.owned_row_count, K), np.float32)
+                rows_host[:] = product.pack_rows(a_host_full)
+                cols_host = runner.pinned((K, width), np.float32)
+                cols_host[:] = b_host_full[:, col0:col1]
+                produced = runner.pinned((M, width), np.float32)
+                run_e2e = lambda: product.execute(rows_host, cols_host, produced, synchronize=True)
+                h2d, d2h = product.host_bytes()
+                call = ('compile_kernel + sharding.ShardedHostProduct.execute (pinned host buffers; each rank feeds its columns of B and '
+                        f'1/{world} of the rows of A, NCCL all-gather of the rows of A, {len(product.plan)} row blocks in flight)')
+                stream = product.compute
+            del a_host_full, b_host_full
+            for _ in range(2):
+                run_e2e()
+            barrier()
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record(stream)
+            for _ in range(e2e_steps):
+                run_e2e()
+            end.record(stream)
+            end.synchronize()
+            e2e_ms = over_ranks(begin.elapsed_time(end))
+            matches = over_ranks(float(np.array_equal(produced[::64], c[::64].cpu().numpy())), dist.ReduceOp.MIN if world > 1 else None)
+            h2d_total, d2h_total = int(over_ranks(float(h2d), dist.ReduceOp.SUM if world > 1 else None)), \
+                int(over_ranks(float(d2h), dist.ReduceOp.SUM if world > 1 else None))
+            link = host_link_rate(torch, dist, device, world, h2d, d2h)
+            e2e = {'value': FLOPS_PER_GEMM * e2e_steps / e2e_ms / 1e9, 'unit': 'TFLOP/s',
+                   'h2d_bytes_per_step': h2d_total, 'd2h_bytes_per_step': d2h_total,
+                   'h2d_bytes_per_step_rank0': h2d, 'd2h_bytes_per_step_rank0': d2h, 'steps': e2e_steps,
+                   'ms_per_step': e2e_ms / e2e_steps, 'call': call, 'matches_resident_result': bool(matches),
+                   'host_link': link, 'ms_per_step_over_host_link_ms': e2e_ms / e2e_steps / link['ms_for_one_step_bytes']}
+            del produced
 
     # The second sharded path, at N > 1 only: one GQA forward (B=4, 32/8 heads, S=4096, D=128) split over the ranks by
     # (batch, kv-head) groups, no exchange; aggregate = the whole problem's flops / the slowest rank's time.
@@ -674,7 +677,7 @@ def run_ours(args) -> None:
             'metric': 'bf16x3_gemm_tflops', 'value': value, 'unit': 'TFLOP/s', 'n_gpus': world, 'steps': args.steps,
             'warmup': max(args.warmup, 3), 'ms_per_step': total_ms / args.steps, 'higher_is_better': True, 'scaling': 'strong',
             'vs_baseline': None, 'dtype': 'bf16x3 (bf16 hi/lo operands, f32 accumulate, f32 in/out)', 'data': 'synthetic',
-            'config': bench_config(world),
+            'config': bench_config(shards),
             'step': f'split of the rank\'s {width} columns of B (1 kernel) + tcgen05 product kernel with the split of A running '
                     'inside it (1 kernel, preceded by a memset of its counters)',
             'roofline': {'bound': 'tensor', 'achieved': achieved, 'peak': peak, 'unit': 'TFLOP/s', 'frac': achieved / peak,
@@ -698,12 +701,15 @@ def run_ours(args) -> None:
             extras_out['replicas_weak_scaling'] = replicas
         if gqa_sharded is not None:
             extras_out['gqa_sharded_by_groups'] = gqa_sharded
-        if world == 1 and not args.no_cpu_baseline:
+        if shards > world:
+            line['emulated'] = (f'one GPU timed the step of rank 0 of a {shards}-GPU run ({width} of the {N} columns); value = the whole '
+                                'product over that time, what the job reaches if every rank takes as long; no end-to-end figure')
+        if world == 1 and shards == 1 and not args.no_cpu_baseline:
             line['cpu_baseline'] = cpu_gemm_sample()
             reference_gpu = reference_kernel_baseline(torch, ops)
             if reference_gpu is not None:
                 line['reference_kernel_baseline'] = reference_gpu
-        if world == 1 and not args.no_extras:
+        if world == 1 and shards == 1 and not args.no_extras:
             line['sustained'] = sustained_leg(torch, ops, a, b, c, peaks, local_rank)
             del a, b, b_full, c
             torch.cuda.empty_cache()
@@ -1024,6 +1030,9 @@ def main() -> None:
     parser.add_argument('--steps', type=int, default=200)
     parser.add_argument('--warmup', type=int, default=3)
     parser.add_argument('--impl', choices=('ours', 'reference'), default='ours')
+    parser.add_argument('--as-rank-of', type=int, default=0, metavar='N',
+                        help='on one GPU, time the step rank 0 of an N-GPU run would do (its block of columns); the value is '
+                             'what the N-GPU job reaches if every rank takes that long. The line says so; end to end is skipped')
     parser.add_argument('--no-cpu-baseline', action='store_true')
     parser.add_argument('--no-extras', action='store_true')
     parser.add_argument('--row-blocks', type=int, default=0, help='row blocks of the overlapped exchange (--all-gather); 0 = automatic')
