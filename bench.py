@@ -295,11 +295,37 @@ def timed(torch, fn, iters: int, warmup: int = 3) -> float:
     return begin.elapsed_time(end) / iters
 
 
+def reference_kernel_latency_us(torch, name: str, launches: int = 200) -> float | None:
+    """Warm latency of one kernel the reference's compiler emitted for sm_100 (oracle/_ref), on this GPU, with the
+    reference's protocol: its seeded inputs, `zero_outputs` cleared before every launch, a CUDA graph of `launches`
+    launches, median of 6. None when that kernel was not built."""
+    from oracle import ref_kernel
+    records = ref_kernel.manifest()
+    if name not in records:
+        return None
+    from deuteron_b200 import argument_array
+    record = records[name]
+    device = torch.device('cuda', 0)
+    buffers = {arg['name']: torch.from_numpy(argument_array(arg)).to(device) for arg in record['args']}
+    pointers = {key: value.data_ptr() for key, value in buffers.items()}
+    stream = torch.cuda.Stream(device)
+    with ref_kernel.ReferenceKernel(name) as kernel:
+        def call():
+            for output in record.get('zero_outputs', []):
+                buffers[output].zero_()
+            kernel.launch(pointers, stream.cuda_stream)
+        with torch.cuda.stream(stream):
+            return _graph_latency_us(torch, stream, call, launches, 6)
+
+
 def open_workload_latencies() -> dict:
     """Warm latency of the reference's fifteen open workloads (the shapes of its README table), each compiled from
     scheduled IR and timed as the reference times them: a CUDA graph of 200 launches, median of 6 event timings
-    (benchmark.py:244-268). `reference_rtx5090_us` is the reference's published number on other hardware."""
+    (benchmark.py:244-268), output resets included where the launch has them. `reference_b200_us` is the kernel the
+    reference's own compiler emits for the same IR, run on this GPU with the same protocol; `reference_rtx5090_us` is
+    the reference's published number on other hardware."""
     import math
+    import torch
     from deuteron_b200 import LocalRunner, compile_kernel, schedules as S
     published_us = {'p00_scalar_add': 2.976, 'p01_vector_add': 2.976, 'p02_scale_shift': 3.040, 'p03_relu_mul': 2.976, 'r01_array_sum': 2.960,
                     'r02_big_sum': 6.816, 'r03_mean': 4.784, 'r04_row_sum': 2.960, 'm01_matmul_512': 8.896, 'm02_matmul_rect': 3.144,
@@ -311,8 +337,17 @@ def open_workload_latencies() -> dict:
             compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3)
             result = runner.run_kernel(meta['kernels'][0], compiled, warmup=20, iters=200, samples=6)
             out[name] = {'median_us': result['median_us'], 'reference_rtx5090_us': published}
-    out['geometric_mean_us'] = math.exp(sum(math.log(v['median_us']) for v in out.values()) / len(out))
-    out['reference_rtx5090_geometric_mean_us'] = 3.752
+            if result.get('kernel_only_us') is not None:
+                out[name]['kernel_only_us'] = result['kernel_only_us']
+    for name in list(out):
+        theirs = reference_kernel_latency_us(torch, f'open_{name}')
+        if theirs is not None:
+            out[name]['reference_b200_us'] = theirs
+    mean = lambda key: math.exp(sum(math.log(v[key]) for v in out.values() if isinstance(v, dict) and key in v) / max(1, sum(1 for v in out.values() if isinstance(v, dict) and key in v)))
+    summary = {'geometric_mean_us': mean('median_us'), 'reference_rtx5090_geometric_mean_us': 3.752}
+    if all('reference_b200_us' in v for v in out.values()):
+        summary['reference_b200_geometric_mean_us'] = mean('reference_b200_us')
+    out.update(summary)
     return out
 
 
