@@ -124,6 +124,8 @@ def _classify_gemm(tile: ir.Node, specs: dict, precision: str, launch: dict) -> 
     # (compiler/codegen/lower.py:600-653). The native mode follows, so that the error level is the reference's.
     staged = {copies.get(loads[operand].input) for product in products for operand in product.args}
     mode = precision if staged == {left, right} and _tensor_core_shape(tile, statements, products, writes, precision, launch) else 'f32'
+    if mode == 'f32' and split_depth is not None:
+        mode = 'f32_splitk'     # the reference adds partial sums over slices of k there: no sequential k order to keep
     return Plan('gemm', {'mode': mode, 'm': m, 'n': n, 'k': k},
                 {'left': (left, 0), 'right': (right, 0), 'out': (output, 0)})
 

@@ -135,13 +135,26 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
 // results are bit-identical to it (and to the reference's f32 kernel).
 constexpr int FS_B = 32, FS_BK = 16;
 
+// KPARTS > 1: a cluster of KPARTS CTAs along z shares one output tile, each CTA takes a contiguous slice of k, and the
+// partial sums meet in the first CTA's shared memory (distributed-shared-memory stores into a fixed slot per CTA and
+// thread) where they are added in rank order: no atomics, the same bits on every run. Used for contractions too small
+// to give the SMs work otherwise (the reference's split-K workload: 128 x 64 outputs, k = 256). The k order of an
+// output element differs from the one-CTA form, which is why the product of the reference's 128^3 example never
+// takes it.
+template <int KPARTS>
 __global__ void __launch_bounds__(F_THREADS)
 gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                       int64_t lda, int64_t ldb, int64_t ldc) {
   __shared__ float As[2][FS_BK][FS_B + 1];
   __shared__ float Bs[2][FS_BK][FS_B + 1];
+  __shared__ float partials[KPARTS > 1 ? (KPARTS - 1) * F_THREADS * 4 : 1];
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * FS_B, n0 = blockIdx.x * FS_B;
+  // this CTA's slice of k: whole k-tiles, the last CTA takes what is left
+  const int all_tiles = (K + FS_BK - 1) / FS_BK;
+  const int per_part = (all_tiles + KPARTS - 1) / KPARTS;
+  const int k_begin = (KPARTS > 1 ? (int)blockIdx.z * per_part : 0) * FS_BK;
+  const int k_end = KPARTS > 1 ? min(K, k_begin + per_part * FS_BK) : K;
   const int tx = tid & 15, ty = tid >> 4;   // 16 x 16 threads, each 2 x 2 outputs
   // staging: 512 elements per operand tile, two per thread
   float ra[2], rb[2];
@@ -150,9 +163,9 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
     for (int i = 0; i < 2; ++i) {
       const int v = tid + i * F_THREADS;          // 0..511
       const int ar = v >> 4, ak = v & 15;         // A: 32 rows x 16 k, k fastest
-      ra[i] = (m0 + ar < M && k0 + ak < K) ? A[(int64_t)(m0 + ar) * lda + k0 + ak] : 0.f;
+      ra[i] = (m0 + ar < M && k0 + ak < k_end) ? A[(int64_t)(m0 + ar) * lda + k0 + ak] : 0.f;
       const int bk = v >> 5, bn = v & 31;         // B: 16 k x 32 columns, column fastest
-      rb[i] = (k0 + bk < K && n0 + bn < N) ? B[(int64_t)(k0 + bk) * ldb + n0 + bn] : 0.f;
+      rb[i] = (k0 + bk < k_end && n0 + bn < N) ? B[(int64_t)(k0 + bk) * ldb + n0 + bn] : 0.f;
     }
   };
   auto store_tiles = [&](int buf) {
@@ -164,15 +177,15 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
     }
   };
   float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  const int ktiles = (K + FS_BK - 1) / FS_BK;
+  const int ktiles = k_end > k_begin ? (k_end - k_begin + FS_BK - 1) / FS_BK : 0;
   if (ktiles > 0) {
-    load_tiles(0);
+    load_tiles(k_begin);
     store_tiles(0);
   }
   __syncthreads();
   for (int kt = 0; kt < ktiles; ++kt) {
     const int buf = kt & 1;
-    if (kt + 1 < ktiles) load_tiles((kt + 1) * FS_BK);
+    if (kt + 1 < ktiles) load_tiles(k_begin + (kt + 1) * FS_BK);
 #pragma unroll
     for (int k = 0; k < FS_BK; ++k) {
       const float a0 = As[buf][k][ty * 2], a1 = As[buf][k][ty * 2 + 1];
@@ -185,6 +198,24 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
     if (kt + 1 < ktiles) store_tiles(buf ^ 1);
     __syncthreads();
   }
+  if constexpr (KPARTS > 1) {
+    const int part = (int)blockIdx.z;
+    if (part != 0) {
+      const uint32_t local = smem_u32(partials + ((part - 1) * F_THREADS + tid) * 4);
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4u * e), "f"(acc[e >> 1][e & 1]) : "memory");
+    }
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    if (part != 0) return;
+    for (int other = 1; other < KPARTS; ++other) {
+      const float* theirs = partials + ((other - 1) * F_THREADS + tid) * 4;
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e >> 1][e & 1] += theirs[e];
+    }
+  }
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -192,6 +223,24 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
       const int r = m0 + ty * 2 + i, c = n0 + tx * 2 + j;
       if (r < M && c < N) C[(int64_t)r * ldc + c] = acc[i][j];
     }
+}
+
+template <int KPARTS>
+static int launch_small_split(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                              int64_t ldc, cudaStream_t s) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)((N + FS_B - 1) / FS_B), (unsigned)((M + FS_B - 1) / FS_B), KPARTS);
+  cfg.blockDim = dim3(F_THREADS);
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = KPARTS;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_f32_small_kernel<KPARTS>, A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc));
+  return DTN_OK;
 }
 
 // Mid-size products: 64x64 CTA tiles, 4x4 outputs per thread, several CTAs per SM. A 1024^3 product is 64 tiles of
@@ -289,7 +338,7 @@ gemm_f32_mid_kernel(const float* __restrict__ A, const float* __restrict__ B, fl
 }
 
 int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s) {
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s, bool split_k_allowed) {
   static const int forced_tile = [] {
     const char* text = getenv("DTN_GEMM_F32_TILE");   // tuning aid: 32, 64 or 128 forces that tile
     return text ? atoi(text) : 0;
@@ -306,7 +355,15 @@ int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t
   if (tile == 64 && (M + FM_B - 1) / FM_B > 65535) tile = 128;
   if (tile == 32) {
     dim3 small_grid((unsigned)((N + FS_B - 1) / FS_B), (unsigned)((M + FS_B - 1) / FS_B));
-    gemm_f32_small_kernel<<<small_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+    // A handful of tiles with a long k (the reference's split-K workload is 8 tiles of k = 256): clusters of 4 or 8
+    // CTAs along k put 32 or 64 SMs to work instead of 8. Only when the caller allows another k order
+    // (`split_k_allowed`: contractions the reference itself computes with atomic partial sums).
+    const int64_t tiles32 = (int64_t)small_grid.x * small_grid.y;
+    if (split_k_allowed && tiles32 * 8 <= (int64_t)sm_count() && K >= 8 * FS_BK * 2 && small_grid.y <= 65535)
+      return launch_small_split<8>(A, B, C, M, N, K, lda, ldb, ldc, s);
+    if (split_k_allowed && tiles32 * 4 <= (int64_t)sm_count() && K >= 4 * FS_BK * 2 && small_grid.y <= 65535)
+      return launch_small_split<4>(A, B, C, M, N, K, lda, ldb, ldc, s);
+    gemm_f32_small_kernel<1><<<small_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
     DTN_LAUNCH_CHECK("gemm_f32_small_kernel");
     return DTN_OK;
   }

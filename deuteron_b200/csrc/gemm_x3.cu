@@ -29,7 +29,7 @@
 namespace dtn {
 
 int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
-                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s);
+                    int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s, bool split_k_allowed);
 int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                       int64_t ldb, int64_t ldc, cudaStream_t s);
 bool gemm_fused_supported(int mode, const float* A, const float* B, int64_t N, int64_t K, int64_t lda, int64_t ldb);
@@ -1627,9 +1627,9 @@ int dtn_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, size_t* 
   using namespace dtn;
   DTN_REQUIRE(bytes_out != nullptr, DTN_ERR_INVALID, "gemm: bytes_out is null");
   DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm: negative extent");
-  DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
-              "gemm: unknown mode %d", mode);
-  *bytes_out = (mode == DTN_GEMM_F32 || M == 0 || N == 0 || K == 0) ? 0 : plane_layout(mode, M, N, K).total;
+  DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3 || mode == DTN_GEMM_F32_SPLITK,
+              DTN_ERR_INVALID, "gemm: unknown mode %d", mode);
+  *bytes_out = (mode == DTN_GEMM_F32 || mode == DTN_GEMM_F32_SPLITK || M == 0 || N == 0 || K == 0) ? 0 : plane_layout(mode, M, N, K).total;
   return DTN_OK;
 }
 
@@ -1640,8 +1640,8 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   DTN_REQUIRE(phase >= 1 && phase <= 15 && (phase & 3) != 0, DTN_ERR_INVALID,
               "gemm: phase is a mask of 1 (split), 2 (products), 4 (keep A planes), 8 (keep B planes)");
   const bool split_a = (phase & 1) && !(phase & 4), split_b = (phase & 1) && !(phase & 8);
-  DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3, DTN_ERR_INVALID,
-              "gemm: unknown mode %d", mode);
+  DTN_REQUIRE(mode == DTN_GEMM_F32 || mode == DTN_GEMM_TF32X3 || mode == DTN_GEMM_BF16X3 || mode == DTN_GEMM_F32_SPLITK,
+              DTN_ERR_INVALID, "gemm: unknown mode %d", mode);
   DTN_REQUIRE(M >= 0 && N >= 0 && K >= 0, DTN_ERR_INVALID, "gemm: negative extent");
   if (M == 0 || N == 0) return DTN_OK;
   DTN_REQUIRE(C != nullptr, DTN_ERR_INVALID, "gemm: C is null");
@@ -1656,7 +1656,8 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   DTN_REQUIRE(A != nullptr && B != nullptr, DTN_ERR_INVALID, "gemm: operand pointer is null");
   DTN_REQUIRE(aligned_to(A, 4) && aligned_to(B, 4) && aligned_to(C, 4), DTN_ERR_INVALID,
               "gemm: pointers must be 4-byte aligned");
-  if (mode == DTN_GEMM_F32) return (phase & 2) ? gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s) : DTN_OK;
+  if (mode == DTN_GEMM_F32 || mode == DTN_GEMM_F32_SPLITK)
+    return (phase & 2) ? gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s, mode == DTN_GEMM_F32_SPLITK) : DTN_OK;
 
   if (phase == 3 && (g_gemm_variant == 4 || (g_gemm_variant == 0 && prefers_small_kernel(M, N, K))))
     return gemm_small_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s);

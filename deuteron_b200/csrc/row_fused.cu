@@ -135,11 +135,11 @@ __device__ __forceinline__ int chain_column(int chunk_base, int rank, int u, int
 
 // One step of the chain over the thread's 32 cached elements. OP and KIND are compile-time: the two uniform
 // switches in chain_run pick the instantiation once per row and step.
-template <int OP, int KIND, int TPR, bool VEC>
-__device__ __forceinline__ void chain_step(float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], float scalar,
+template <int OP, int KIND, int TPR, bool VEC, int NV>
+__device__ __forceinline__ void chain_step(float4 (&acc)[NV], const float4 (&kept)[NV], float scalar,
                                            const float* __restrict__ columns, bool swap, int chunk_base, int rank, int cols) {
 #pragma unroll
-  for (int u = 0; u < kRowCacheVecs; ++u) {
+  for (int u = 0; u < NV; ++u) {
     float o[4];
     if constexpr (KIND == CHAIN_SCALAR) {
       o[0] = o[1] = o[2] = o[3] = scalar;
@@ -165,8 +165,8 @@ __device__ __forceinline__ void chain_step(float4 (&acc)[kRowCacheVecs], const f
   }
 }
 
-template <int OP, int TPR, bool VEC>
-__device__ __forceinline__ void chain_binary(float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int kind, float scalar,
+template <int OP, int TPR, bool VEC, int NV>
+__device__ __forceinline__ void chain_binary(float4 (&acc)[NV], const float4 (&kept)[NV], int kind, float scalar,
                                              const float* __restrict__ columns, bool swap, int chunk_base, int rank, int cols) {
   switch (kind) {
     case CHAIN_SCALAR: chain_step<OP, CHAIN_SCALAR, TPR, VEC>(acc, kept, scalar, columns, swap, chunk_base, rank, cols); break;
@@ -176,11 +176,11 @@ __device__ __forceinline__ void chain_binary(float4 (&acc)[kRowCacheVecs], const
   }
 }
 
-template <int TPR, bool VEC>
-__device__ __forceinline__ void chain_load(float4 (&cache)[kRowCacheVecs], const float* __restrict__ xr, int chunk_base, int rank,
+template <int TPR, bool VEC, int NV>
+__device__ __forceinline__ void chain_load(float4 (&cache)[NV], const float* __restrict__ xr, int chunk_base, int rank,
                                            int cols, float fill) {
 #pragma unroll
-  for (int u = 0; u < kRowCacheVecs; ++u) {
+  for (int u = 0; u < NV; ++u) {
     if constexpr (VEC) {
       const int col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
       cache[u] = col < cols ? ld_stream_f4(reinterpret_cast<const float4*>(xr + col)) : make_float4(fill, fill, fill, fill);
@@ -198,30 +198,31 @@ __device__ __forceinline__ void chain_load(float4 (&cache)[kRowCacheVecs], const
 
 // Folds the thread's cached elements into four partial reductions; the reduction operator is a uniform branch
 // taken once per chunk, not per element.
-__device__ __forceinline__ void chain_fold(int reduce, const float4 (&cache)[kRowCacheVecs], float (&part)[4]) {
+template <int NV>
+__device__ __forceinline__ void chain_fold(int reduce, const float4 (&cache)[NV], float (&part)[4]) {
   if (reduce == DTN_REDUCE_SUM) {
 #pragma unroll
-    for (int u = 0; u < kRowCacheVecs; ++u) {
+    for (int u = 0; u < NV; ++u) {
       part[0] += cache[u].x; part[1] += cache[u].y; part[2] += cache[u].z; part[3] += cache[u].w;
     }
   } else if (reduce == DTN_REDUCE_SUMSQ) {
 #pragma unroll
-    for (int u = 0; u < kRowCacheVecs; ++u) {
+    for (int u = 0; u < NV; ++u) {
       part[0] = fmaf(cache[u].x, cache[u].x, part[0]); part[1] = fmaf(cache[u].y, cache[u].y, part[1]);
       part[2] = fmaf(cache[u].z, cache[u].z, part[2]); part[3] = fmaf(cache[u].w, cache[u].w, part[3]);
     }
   } else {
 #pragma unroll
-    for (int u = 0; u < kRowCacheVecs; ++u) {
+    for (int u = 0; u < NV; ++u) {
       part[0] = fmaxf(part[0], cache[u].x); part[1] = fmaxf(part[1], cache[u].y);
       part[2] = fmaxf(part[2], cache[u].z); part[3] = fmaxf(part[3], cache[u].w);
     }
   }
 }
 
-template <int TPR, bool VEC>
+template <int TPR, bool VEC, int NV>
 __device__ __forceinline__ void chain_run(const RowProgram& prog, const RowChain& chain, const ScalarFile& scalars,
-                                          float4 (&acc)[kRowCacheVecs], const float4 (&kept)[kRowCacheVecs], int chunk_base, int rank,
+                                          float4 (&acc)[NV], const float4 (&kept)[NV], int chunk_base, int rank,
                                           int cols, int first_step = 0) {
   for (int s = first_step; s < chain.n; ++s) {
     const int kind = chain.kind[s];
@@ -246,14 +247,16 @@ __device__ __forceinline__ void chain_run(const RowProgram& prog, const RowChain
 }
 
 // TPR threads per row (8, 16, 32 lanes of a warp, or a CTA of 64, 128 or 256 threads). KEEPX: a later step of the
-// chain reads the row element again, so the running values need registers of their own.
-template <int TPR, bool VEC, bool KEEPX>
+// chain reads the row element again, so the running values need registers of their own. NV: 128-bit vectors of the row
+// a thread keeps (1, 2, 4 or 8): short rows get the instantiation that holds them and no more, which is an eighth of
+// the code of the 8-vector form (a small launch spends most of its time fetching instructions otherwise).
+template <int TPR, bool VEC, bool KEEPX, int NV>
 __global__ void __launch_bounds__(TPR <= 32 ? 128 : TPR, (KEEPX ? 512 : 640) / (TPR <= 32 ? 128 : TPR))
 row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __restrict__ x, float* __restrict__ out, int64_t rows,
                  int cols, int64_t ldx, int64_t ldo) {
   constexpr int kThreads = TPR <= 32 ? 128 : TPR;
   constexpr int RPB = kThreads / TPR;                                // rows per CTA
-  constexpr int kChunkCols = TPR * kRowCacheVecs * 4;   // columns one pass of the group covers
+  constexpr int kChunkCols = TPR * NV * 4;   // columns one pass of the group covers
   __shared__ float scratch[16];
   int parity = 0;
   const int rank = threadIdx.x % TPR, sub = threadIdx.x / TPR;
@@ -269,7 +272,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
       if (chain.kind[s] != CHAIN_COLUMNS) continue;
       const float* columns = prog.input[chain.index[s]];
 #pragma unroll
-      for (int u = 0; u < kRowCacheVecs; ++u) {
+      for (int u = 0; u < NV; ++u) {
         const int col = chain_column<TPR, VEC>(0, rank, u, 0);
         if (col < cols) asm volatile("prefetch.global.L1 [%0];" ::"l"(columns + col));
       }
@@ -280,7 +283,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
     const bool live = row < rows;   // uniform over the lanes that share a row; a CTA-wide group always has a live row
     if (!live) row = rows - 1;      // idle groups of the last CTA repeat the last row and store nothing
     const float* xr = x + row * ldx;
-    float4 cache[kRowCacheVecs];
+    float4 cache[NV];
     float part[4] = {identity, identity, identity, identity};
     if (one_chunk) {
       chain_load<TPR, VEC>(cache, xr, 0, rank, cols, identity);
@@ -301,7 +304,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
         // the exponentials stay in the row cache: when the elementwise stage opens with the same (x - max), exp
         // (chain.cached_exp) it continues from them instead of computing each a second time
 #pragma unroll
-        for (int u = 0; u < kRowCacheVecs; ++u) {
+        for (int u = 0; u < NV; ++u) {
           const float4 e = make_float4(exp_ref(__fsub_rn(cache[u].x, first)), exp_ref(__fsub_rn(cache[u].y, first)),
                                        exp_ref(__fsub_rn(cache[u].z, first)), exp_ref(__fsub_rn(cache[u].w, first)));
           second += (e.x + e.y) + (e.z + e.w);
@@ -311,7 +314,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
         for (int chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
           chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, -INFINITY);
 #pragma unroll
-          for (int u = 0; u < kRowCacheVecs; ++u)
+          for (int u = 0; u < NV; ++u)
             second += (exp_ref(cache[u].x - first) + exp_ref(cache[u].y - first)) + (exp_ref(cache[u].z - first) + exp_ref(cache[u].w - first));
         }
       }
@@ -331,12 +334,12 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
     for (int chunk_base = 0; chunk_base < cols; chunk_base += kChunkCols) {
       if (!one_chunk) chain_load<TPR, VEC>(cache, xr, chunk_base, rank, cols, 0.0f);
       if constexpr (KEEPX) {
-        float4 acc[kRowCacheVecs];
+        float4 acc[NV];
 #pragma unroll
-        for (int u = 0; u < kRowCacheVecs; ++u) acc[u] = cache[u];
+        for (int u = 0; u < NV; ++u) acc[u] = cache[u];
         chain_run<TPR, VEC>(prog, chain, scalars, acc, cache, chunk_base, rank, cols);
 #pragma unroll
-        for (int u = 0; u < kRowCacheVecs; ++u) cache[u] = acc[u];
+        for (int u = 0; u < NV; ++u) cache[u] = acc[u];
       } else if (reduce == DTN_REDUCE_SOFTMAX && one_chunk) {
         // the cache holds exp(x - max) already; a chain that does not open with those two steps starts from x again
         if (!chain.cached_exp) chain_load<TPR, VEC>(cache, xr, 0, rank, cols, 0.0f);
@@ -345,7 +348,7 @@ row_chain_kernel(const RowProgram prog, const RowChain chain, const float* __res
         chain_run<TPR, VEC>(prog, chain, scalars, cache, cache, chunk_base, rank, cols);
       }
 #pragma unroll
-      for (int u = 0; u < kRowCacheVecs; ++u) {
+      for (int u = 0; u < NV; ++u) {
         if constexpr (VEC) {
           const int col = chain_column<TPR, VEC>(chunk_base, rank, u, 0);
           if (col < cols) st_stream_f4(reinterpret_cast<float4*>(out_row + col), cache[u]);
@@ -526,9 +529,9 @@ static bool row_chain_of(const RowProgram& prog, RowChain* chain, bool* keep_x, 
   return per_row || prog.out_reg == running;   // a per-row result is read from the scalar registers
 }
 
-template <int TPR>
-static int row_chain_launch(const RowProgram& prog, const RowChain& chain, bool keep_x, const float* x, float* out, int64_t rows,
-                            int64_t cols, int64_t ldx, int64_t ldo, bool aligned, cudaStream_t s) {
+template <int TPR, int NV>
+static int row_chain_launch_nv(const RowProgram& prog, const RowChain& chain, bool keep_x, const float* x, float* out, int64_t rows,
+                               int64_t cols, int64_t ldx, int64_t ldo, bool aligned, cudaStream_t s) {
   constexpr int kThreads = TPR <= 32 ? 128 : TPR;
   constexpr int RPB = kThreads / TPR;
   int64_t blocks = (rows + RPB - 1) / RPB;
@@ -536,15 +539,26 @@ static int row_chain_launch(const RowProgram& prog, const RowChain& chain, bool 
   if (blocks > cap) blocks = cap;
   const unsigned grid = (unsigned)blocks;
   if (aligned && keep_x)
-    row_chain_kernel<TPR, true, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
+    row_chain_kernel<TPR, true, true, NV><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   else if (aligned)
-    row_chain_kernel<TPR, true, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
+    row_chain_kernel<TPR, true, false, NV><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   else if (keep_x)
-    row_chain_kernel<TPR, false, true><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
+    row_chain_kernel<TPR, false, true, 8><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   else
-    row_chain_kernel<TPR, false, false><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
+    row_chain_kernel<TPR, false, false, 8><<<grid, kThreads, 0, s>>>(prog, chain, x, out, rows, (int)cols, ldx, ldo);
   DTN_LAUNCH_CHECK("row_chain_kernel");
   return DTN_OK;
+}
+
+// The number of vectors a thread keeps: the smallest of 1, 2, 4, 8 that holds the row (aligned rows only; the scalar
+// form always keeps eight).
+template <int TPR>
+static int row_chain_launch(const RowProgram& prog, const RowChain& chain, bool keep_x, const float* x, float* out, int64_t rows,
+                            int64_t cols, int64_t ldx, int64_t ldo, bool aligned, cudaStream_t s) {
+  if (aligned && cols <= (int64_t)TPR * 4) return row_chain_launch_nv<TPR, 1>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+  if (aligned && cols <= (int64_t)TPR * 8) return row_chain_launch_nv<TPR, 2>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+  if (aligned && cols <= (int64_t)TPR * 16) return row_chain_launch_nv<TPR, 4>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
+  return row_chain_launch_nv<TPR, 8>(prog, chain, keep_x, x, out, rows, cols, ldx, ldo, aligned, s);
 }
 
 // Threads per row: the smallest group whose eight vectors per thread hold the whole row, widened while the

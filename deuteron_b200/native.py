@@ -13,7 +13,7 @@ LIBRARY_PATH = Path(__file__).resolve().parent / 'libdeuteron_b200.so'
 
 OK, ERR_INVALID, ERR_CUDA, ERR_WORKSPACE, ERR_UNSUPPORTED, ERR_DEVICE = range(6)
 
-GEMM_MODES = {'f32': 0, 'tf32x3': 1, 'bf16x3': 2}
+GEMM_MODES = {'f32': 0, 'tf32x3': 1, 'bf16x3': 2, 'f32_splitk': 3}
 REDUCE_OPS = {'sum': 0, 'max': 1, 'sumsq': 2, 'softmax': 3}
 ROW_INPUT_KINDS = {'scalar': 0, 'columns': 1, 'immediate': 2}
 STORAGE = {'f32': 0, 'f16': 1}

@@ -260,7 +260,7 @@ class LocalRunner:
         """Number of equal row blocks a large compensated GEMM is walked in when its operands come from
         the host, so that copies and products overlap; 1 = no blocking."""
         m, n, k = plan.params['m'], plan.params['n'], plan.params['k']
-        if plan.params['mode'] == 'f32' or m * k * 4 < (32 << 20):
+        if plan.params['mode'] in ('f32', 'f32_splitk') or m * k * 4 < (32 << 20):
             return 1
         for blocks in (8, 4, 2):
             if m % blocks == 0 and (m // blocks) % 256 == 0 and (m // blocks) >= 512:

@@ -38,6 +38,10 @@ extern "C" {
 #define DTN_GEMM_F32 0
 #define DTN_GEMM_TF32X3 1
 #define DTN_GEMM_BF16X3 2
+/* FP32 multiply-adds whose k range may be cut into partial sums that are added in a fixed order: the arithmetic of
+ * the reference's split-K kernels (partial products added into a zeroed output, compiler/passes/gridfold.py:23-129),
+ * whose k order is not the sequential one either. Same result on every run. */
+#define DTN_GEMM_F32_SPLITK 3
 
 /* reduction operator of dtn_row_reduce_f32 */
 #define DTN_REDUCE_SUM 0
@@ -169,7 +173,8 @@ int dtn_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, size_t* 
  *     104-119, 121-190; stage_register_loads, compiler/passes/regstage.py:70-245).
  *   DTN_GEMM_TF32X3: hi = tf32_rna(v), lo = tf32_rna(v - hi), same three products
  *     (compiler/codegen/tensor.py:50-53, 192-245).
- *   DTN_GEMM_F32: plain FP32 FMA (generic Lowering.body, compiler/codegen/lower.py:600-653).
+ *   DTN_GEMM_F32: plain FP32 FMA, k accumulated in sequence (generic Lowering.body,
+ *     compiler/codegen/lower.py:600-653); DTN_GEMM_F32_SPLITK: the same with partial sums over slices of k.
  * The result store replaces TensorEmitter._store (compiler/codegen/tensor.py:255-267).
  * `workspace` must be 1024-byte aligned and at least dtn_gemm_workspace_bytes large for the
  * x3 modes (ignored for F32). A column block of B / C is addressed by offsetting the

@@ -79,7 +79,7 @@ def test_generated_schedules_classify(golden):
         (schedules.row_reduce_example(8, 4096, 'sumsq'), 'row_reduce', {'op': 'sumsq', 'rows': 8, 'cols': 4096}),
         (schedules.matmul_example(256, 512, 1024), 'gemm', {'mode': 'bf16x3', 'm': 256, 'n': 512, 'k': 1024}),
         # staged depth 4 is no multiple of the tensor-core k step: the reference lowers this one to FP32 multiply-adds, and so does this build
-            (schedules.split_k_matmul_example(), 'gemm', {'mode': 'f32', 'm': 128, 'n': 64, 'k': 256}),
+            (schedules.split_k_matmul_example(), 'gemm', {'mode': 'f32_splitk', 'm': 128, 'n': 64, 'k': 256}),
         (schedules.mean_example(), 'row_fused',
          {'reduce': 'sum', 'rows': 1, 'cols': 32768, 'per_row': True, 'inputs': [{'kind': 'scalar'}], 'n_scalar': 1, 'out_reg': 4,
           'ops': [3], 'dst': [4], 'a': [0], 'b': [3]}),

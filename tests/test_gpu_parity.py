@@ -365,6 +365,20 @@ def test_split_k_contraction_is_the_full_product(runner):
     np.testing.assert_allclose(produced, R.gemm_f64(normal(0, (128, 256)), normal(1, (256, 64))), rtol=1e-3, atol=1e-3)
 
 
+def test_fp32_split_k_mode_adds_partial_sums_in_a_fixed_order(cuda):
+    # few output tiles and a long k: clusters of 8 or 4 CTAs along k (or one CTA when there are tiles enough); FP32
+    # accuracy, the same bits on every run, ragged edges
+    for m, n, k in ((128, 64, 256), (64, 64, 1024), (100, 70, 333), (32, 32, 64), (512, 512, 128)):
+        a, b = to_device(cuda, R.seeded_normal(0, (m, k))), to_device(cuda, R.seeded_normal(1, (k, n)))
+        first = ops.gemm(a, b, 'f32_splitk').clone()
+        again = ops.gemm(a, b, 'f32_splitk')
+        assert bool(cuda.equal(first, again))
+        exact = a.double() @ b.double()
+        assert float(((first.double() - exact).abs().max() / exact.abs().max()).item()) < 5e-7
+        sequential = ops.gemm(a, b, 'f32')
+        assert float((first - sequential).abs().max().item()) <= 4e-5 * float(exact.abs().max().item())
+
+
 # ------------------------------------------------------------------------------------------------
 # GEMM
 # ------------------------------------------------------------------------------------------------
