@@ -673,6 +673,32 @@ def test_execute_with_a_tall_left_operand_and_a_narrow_right_one(cuda, runner):
     np.testing.assert_array_equal(produced, resident)
 
 
+def test_host_fed_sharded_product_on_one_rank_matches_the_resident_path(cuda, runner):
+    # sharding.ShardedHostProduct with a world of one: the same walk as on several GPUs (B split once, row blocks of A
+    # copied in, multiplied and copied out on four streams) without the exchange; the N-rank form runs over gloo in
+    # tests/test_sharding_cpu.py and over NCCL in bench.py --gpus N
+    from deuteron_b200 import sharding
+    m, n, k = 4096, 1280, 1024
+    compiled = compile_kernel(*schedules.matmul_example(m, n, k), options=Options(contraction_precision='bf16x3'))
+    product = sharding.ShardedHostProduct(compiled, 0, 1, 'cuda:0', row_blocks=3)
+    left, right = runner.pinned((m, k), np.float32), runner.pinned((k, n), np.float32)
+    left[:], right[:] = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+    assert product.columns == (0, n) and product.owned_row_count == m and product.host_bytes() == (4 * (m * k + k * n), 4 * m * n)
+    out = runner.pinned((m, n), np.float32)
+    for _ in range(2):
+        out[:] = 0
+        assert product.execute(product.pack_rows(left), right, out) is out
+        ops.set_gemm_variant(1)
+        try:
+            resident = ops.gemm(to_device(cuda, left), to_device(cuda, right), 'bf16x3').cpu().numpy()
+        finally:
+            ops.set_gemm_variant(0)
+        np.testing.assert_array_equal(out, resident)
+    ops.check_device_status()
+    with pytest.raises(ValueError):
+        product.execute(left[:-1], right, out)
+
+
 @pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
 @pytest.mark.parametrize('m,blocks', [(1536, 4), (2560, 4), (1000, 3)])
 def test_row_blocks_of_unequal_heights_share_one_split_of_b(cuda, mode, m, blocks):
