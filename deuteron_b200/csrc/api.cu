@@ -1,5 +1,6 @@
 // Library-level entry points: version, error text, device status word.
 #include <stdarg.h>
+#include <stdlib.h>
 
 #include <mutex>
 
@@ -74,6 +75,52 @@ int dtn_device_status(int* status_out, void* stream) {
   DTN_CUDA_CHECK(cudaStreamSynchronize(s));
   if (host != 0) DTN_CUDA_CHECK(cudaMemsetAsync(word, 0, sizeof(int), s));
   *status_out = host;
+  return DTN_OK;
+}
+
+int dtn_capture_begin(void* stream) {
+  cudaStream_t s = dtn::as_stream(stream);
+  DTN_REQUIRE(s != nullptr, DTN_ERR_INVALID, "dtn_capture_begin: a stream of its own is needed (not the default stream)");
+  DTN_CUDA_CHECK(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  return DTN_OK;
+}
+
+int dtn_capture_end(void* stream, int* kernels_out, int* max_registers_out, int* max_static_smem_out,
+                    int* max_dynamic_smem_out) {
+  cudaStream_t s = dtn::as_stream(stream);
+  cudaGraph_t graph = nullptr;
+  DTN_CUDA_CHECK(cudaStreamEndCapture(s, &graph));
+  DTN_REQUIRE(graph != nullptr, DTN_ERR_CUDA, "dtn_capture_end: the capture produced no graph");
+  size_t count = 0;
+  cudaError_t err = cudaGraphGetNodes(graph, nullptr, &count);
+  int kernels = 0, regs = 0, static_smem = 0, dynamic_smem = 0;
+  if (err == cudaSuccess && count > 0) {
+    cudaGraphNode_t* nodes = static_cast<cudaGraphNode_t*>(malloc(count * sizeof(cudaGraphNode_t)));
+    if (nodes != nullptr && (err = cudaGraphGetNodes(graph, nodes, &count)) == cudaSuccess) {
+      for (size_t i = 0; i < count && err == cudaSuccess; ++i) {
+        cudaGraphNodeType type;
+        if ((err = cudaGraphNodeGetType(nodes[i], &type)) != cudaSuccess || type != cudaGraphNodeTypeKernel) continue;
+        cudaKernelNodeParams params = {};
+        if ((err = cudaGraphKernelNodeGetParams(nodes[i], &params)) != cudaSuccess) break;
+        cudaFuncAttributes attributes = {};
+        if ((err = cudaFuncGetAttributes(&attributes, params.func)) != cudaSuccess) break;
+        ++kernels;
+        if (attributes.numRegs > regs) regs = attributes.numRegs;
+        if ((int)attributes.sharedSizeBytes > static_smem) static_smem = (int)attributes.sharedSizeBytes;
+        if ((int)params.sharedMemBytes > dynamic_smem) dynamic_smem = (int)params.sharedMemBytes;
+      }
+    }
+    free(nodes);
+  }
+  cudaGraphDestroy(graph);
+  if (err != cudaSuccess) {
+    dtn::set_error("dtn_capture_end: %s (%s)", cudaGetErrorName(err), cudaGetErrorString(err));
+    return DTN_ERR_CUDA;
+  }
+  if (kernels_out) *kernels_out = kernels;
+  if (max_registers_out) *max_registers_out = regs;
+  if (max_static_smem_out) *max_static_smem_out = static_smem;
+  if (max_dynamic_smem_out) *max_dynamic_smem_out = dynamic_smem;
   return DTN_OK;
 }
 

@@ -394,6 +394,17 @@ class LocalRunner:
                     measured.append(begin.elapsed_time(end) * 1000 / iters)
                 return measured
 
+            # registers and shared memory of the native kernels one launch runs (the reference reports those of its
+            # one PTX entry): the launch is recorded in a capture, not run, and its kernel nodes are looked up
+            import ctypes as ct
+            counts = [ct.c_int(0) for _ in range(4)]
+            native.call('dtn_capture_begin', stream)
+            try:
+                self._enqueue(plan, pointers, stream, workspace)
+            finally:
+                native.call('dtn_capture_end', stream, *[ct.byref(c) for c in counts])
+            kernels, registers, static_smem, dynamic_smem = (c.value for c in counts)
+
             timings = timed_graph(True)
             kernel_only = statistics.median(timed_graph(False)) if redundant else None
             native.raise_on_device_status(stream)
@@ -408,5 +419,6 @@ class LocalRunner:
                 'samples_us': timings, 'iters': iters, 'samples': samples, 'warmup': warmup,
                 'timing_method': 'cuda_graph_batch_events', 'timing_includes_output_resets': bool(resets),
                 'kernel_only_us': kernel_only,
-                'registers': None, 'static_smem_bytes': None, 'dynamic_smem_bytes': launch.get('smem_bytes', 0),
+                'registers': registers, 'static_smem_bytes': static_smem, 'dynamic_smem_bytes': launch.get('smem_bytes', 0),
+                'native_kernels': kernels, 'native_dynamic_smem_bytes': dynamic_smem,
                 'jit_seconds': prepare_seconds, 'native_kernel': plan.describe(), 'outputs': outputs}

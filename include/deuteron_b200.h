@@ -87,6 +87,15 @@ int dtn_last_error(char* buf, size_t n);
  * No reference counterpart (its kernels have no device-side waits on async units). */
 int dtn_device_status(int* status_out /* host */, void* stream);
 
+/* What the kernels of a call cost, for result records that carry those fields (benchmark.py:218-220 of the
+ * reference reads them from its one PTX entry with cuFuncGetAttribute). dtn_capture_begin puts `stream` (not the
+ * default stream) into capture; the caller then makes the library calls it wants described, which are recorded, not
+ * run; dtn_capture_end ends the capture and reports, over the kernels recorded: how many, the largest register count
+ * per thread, the largest static and the largest dynamic shared-memory size. Any output pointer may be NULL. */
+int dtn_capture_begin(void* stream);
+int dtn_capture_end(void* stream, int* kernels_out /* host */, int* max_registers_out /* host */,
+                    int* max_static_smem_out /* host */, int* max_dynamic_smem_out /* host */);
+
 /* Exercises the bounded-wait reporting path without any fault: one CTA waits, for at most
  * `budget_cycles` clock cycles, on a barrier that nothing completes, then records status 0x7100 in
  * the device status word and returns. dtn_device_status then reports it. No reference counterpart. */

@@ -67,6 +67,8 @@ def test_vector_add_example_is_exact_and_hashes_to_the_reference_output(runner, 
     np.testing.assert_array_equal(produced, np.load(golden / 'vector_add_expected.npz')['sum'])
     assert sha(produced) == published['results']['vector_add']['output_sha256']['sum']
     assert result['median_us'] > 0 and result['timing_method'] == 'cuda_graph_batch_events'
+    # the result record carries the resources of the native kernel, as the reference's carries those of its PTX entry
+    assert result['native_kernels'] == 1 and 8 <= result['registers'] <= 255 and result['static_smem_bytes'] == 0
 
 
 def test_f16_examples_hash_to_the_reference_outputs(runner, published):
@@ -360,7 +362,12 @@ def test_row_kernels_full_size(cuda):
 
 def test_split_k_contraction_is_the_full_product(runner):
     graph, meta = schedules.split_k_matmul_example()
-    produced = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta, arch='sm_100a'), warmup=0, iters=1, samples=1)['outputs']['matmul']
+    result = runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta, arch='sm_100a'), warmup=0, iters=1, samples=2)
+    produced = result['outputs']['matmul']
+    # the launch resets its output before every launch, as the reference's does; the native kernel overwrites it anyway,
+    # so the time without the reset is reported beside the comparable one
+    assert result['timing_includes_output_resets'] and 0 < result['kernel_only_us'] <= result['median_us'] * 1.5
+    assert result['native_kernels'] == 1 and result['static_smem_bytes'] > 0
     normal = lambda seed, shape: np.random.default_rng(seed).standard_normal(shape).astype(np.float32)
     np.testing.assert_allclose(produced, R.gemm_f64(normal(0, (128, 256)), normal(1, (256, 64))), rtol=1e-3, atol=1e-3)
 
