@@ -68,7 +68,7 @@ def test_vector_add_example_is_exact_and_hashes_to_the_reference_output(runner, 
     assert sha(produced) == published['results']['vector_add']['output_sha256']['sum']
     assert result['median_us'] > 0 and result['timing_method'] == 'cuda_graph_batch_events'
     # the result record carries the resources of the native kernel, as the reference's carries those of its PTX entry
-    assert result['native_kernels'] == 1 and 8 <= result['registers'] <= 255 and result['static_smem_bytes'] == 0
+    assert result['native_kernels'] >= 1 and 8 <= result['registers'] <= 255 and result['static_smem_bytes'] == 0
 
 
 def test_f16_examples_hash_to_the_reference_outputs(runner, published):
