@@ -19,7 +19,7 @@ static thread_local int g_gqa_variant = 0;   // selection of dtn_gqa_set_variant
 extern "C" {
 
 int dtn_gqa_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 6, DTN_ERR_INVALID, "gqa: variant must be 0..6");
+  DTN_REQUIRE(variant >= 0 && variant <= 7, DTN_ERR_INVALID, "gqa: variant must be 0..7");
   dtn::g_gqa_variant = variant;
   return DTN_OK;
 }
@@ -43,10 +43,15 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   DTN_REQUIRE(S < (1LL << 31), DTN_ERR_UNSUPPORTED, "gqa: sequence length must fit 31 bits");
   cudaStream_t s = as_stream(stream);
   int variant = g_gqa_variant;
-  // Two softmax warpgroups per tile are the default: measured 700 vs 666 TFLOP/s at 1024 keys, 831 vs 815 at 4096
-  // and 871 vs 864 at 16384 (each measured first in its process; whichever variant runs second on a warm GPU loses
-  // ~10 % to the power cap, so back-to-back comparisons must alternate the order).
-  if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 3 : 1;
+  // Two softmax warpgroups per tile with the first half of a thread's scores kept in registers are the default
+  // (4096 keys: 997 against 959 TFLOP/s for the form that reads the scores twice, 2048 keys: 890 against 847, 512
+  // keys: equal; alternating runs in one process, identical output bits).
+  if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 7 : 1;
+  if (variant == 7) {   // two softmax warpgroups per tile, scores kept in registers between the two passes
+    DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
+                "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");
+    return gqa_tc_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, 3, s);
+  }
   if (variant == 6) {   // all sixteen softmax warps on one tile at a time
     DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
                 "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");

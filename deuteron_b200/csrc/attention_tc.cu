@@ -30,10 +30,11 @@
 
 namespace dtn {
 
-template <int SPLIT /*warpgroups per 128-row tile: 1 or 2*/>
+template <int SPLIT /*warpgroups per 128-row tile: 1 or 2*/, bool KEEP = false /*scores stay in registers between the passes*/>
 __global__ void __launch_bounds__(attn_threads(SPLIT), 1)
 gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-              const __grid_constant__ CUtensorMap tm_v, float* __restrict__ out, int Hq, int Hkv, int S,
+              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_out, float* __restrict__ out, int Hq,
+              int Hkv, int S,
               float scale_log2e, int group_begin, int total_items, int early_pv, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -54,6 +55,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   auto p_half = [&](int t, int h) { return bar_addr + 8u * (12 + 2 * t + h); };   // half of a tile's probabilities is in tensor memory
   auto o_done = [&](int t) { return bar_addr + 8u * (16 + t); };
   auto q_empty = [&](int t) { return bar_addr + 8u * (18 + t); };
+  auto staged = [&](int t) { return bar_addr + 8u * (22 + t); };   // KEEP: the tile's output staging (a K or V ring slot) has been read
+  auto x_bar = [&](int t, int quarter) { return bar_addr + 8u * (24 + 4 * t + quarter); };   // partner warps of a row quarter
   uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(bar_ptr + 8 * 20);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_ptr + 8 * 20 + 8);
   volatile float2* xchg = reinterpret_cast<volatile float2*>(bar_ptr + 256);
@@ -85,6 +88,8 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::mbar_init(p_half(t, 0), attn_p_half_arrivals(SPLIT));   // one arrival per softmax warp that writes this half
       ptx::mbar_init(p_half(t, 1), attn_p_half_arrivals(SPLIT));
       ptx::mbar_init(o_done(t), 1);
+      ptx::mbar_init(staged(t), attn_softmax_warps(SPLIT) / 2);
+      for (int quarter = 0; quarter < 4; ++quarter) ptx::mbar_init(x_bar(t, quarter), 2);
     }
     ptx::mbar_fence_init();
     ptx::fence_proxy_async_smem();
@@ -112,16 +117,16 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           const int s = g % A_KV_STAGES;
           const uint32_t ph = (uint32_t)(g / A_KV_STAGES) & 1u;
           if (!ptx::mbar_wait(k_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1100); ok = false; break; }
+          // KEEP: the previous item's output was staged in the slots its last step used, which are this item's second
+          // step's: tile 0's in the keys' slot, tile 1's in the values' slot
+          if (KEEP && it > 0 && j == 1 && !ptx::mbar_wait(staged(0), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1400); ok = false; break; }
           ptx::mbar_expect_tx(k_full(s), A_TILE_BYTES);
           for (int h = 0; h < 2; ++h)
             ptx::tma_load_2d(k_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_k, h * 64, item.kv_row0 + j * A_BN, k_full(s));
-          if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1200); ok = false; break; }
-          ptx::mbar_expect_tx(v_full(s), A_TILE_BYTES);
-          for (int h = 0; h < 2; ++h)
-            ptx::tma_load_2d(v_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_v, h * 64, item.kv_row0 + j * A_BN, v_full(s));
           if (j == 0) {
-            // this item's queries, after its first keys so that the K/V stream never waits for a query buffer;
-            // a buffer is free once the previous item's last score product has read it
+            // this item's queries, right after its first keys: a buffer is free once the previous item's last score
+            // product has read it, which is about one step before the first product of this item wants it. The tiles
+            // were asked into L2 one item earlier, so the load does not wait for HBM.
             for (int t = 0; t < 2 && ok; ++t) {
               if (it > 0 && !ptx::mbar_wait(q_empty(t), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1300); ok = false; break; }
               ptx::mbar_expect_tx(q_full(t), A_TILE_BYTES);
@@ -129,98 +134,108 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
                 ptx::tma_load_2d(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES, &tm_q, h * 64, item.q_row0 + t * A_BM, q_full(t));
             }
             if (!ok) break;
+            if (it + 1 < my_items) {
+              const AttnItem next = attn_item((int)blockIdx.x + (it + 1) * (int)gridDim.x, qblocks, Hq, Hkv, S, group_begin);
+              for (int t = 0; t < 2; ++t)
+                for (int h = 0; h < 2; ++h) ptx::tma_prefetch_2d(&tm_q, h * 64, next.q_row0 + t * A_BM);
+            }
           }
+          if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1200); ok = false; break; }
+          if (KEEP && it > 0 && j == 1 && !ptx::mbar_wait(staged(1), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1500); ok = false; break; }
+          ptx::mbar_expect_tx(v_full(s), A_TILE_BYTES);
+          for (int h = 0; h < 2; ++h)
+            ptx::tma_load_2d(v_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_v, h * 64, item.kv_row0 + j * A_BN, v_full(s));
         }
       }
     }
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------ MMA issuer -----------------------------------------
-    if (lane == 0 && total_steps > 0) {
+    // All 32 lanes walk the loop and wait on the barriers; lane 0 alone issues. Control flow and operands are
+    // uniform across the warp, so descriptors and addresses can live in uniform registers.
+    if (total_steps > 0) {
       constexpr uint32_t kIdescQK = attn_idesc(0);
       constexpr uint32_t kIdescPV = attn_idesc(1);
+      const uint32_t leader = lane == 0 ? 1u : 0u;
+      const uint32_t tmem = __shfl_sync(0xffffffffu, tmem_base, 0);
       bool ok = true;
-      // Descriptors are built once: a k-step moves the start address by 32 bytes inside a swizzled row (+2 in the
-      // descriptor's address field) or by 16 key rows of a V tile (+128), which the issue loops add as constants.
-      // Keeping the issuing thread's instruction count low matters: it shares its scheduler with four softmax warps.
+      auto failed = [&](int code) {
+        if (lane == 0) atomicExch(status, code);
+        return false;
+      };
+      auto wait_all = [&](uint32_t bar, uint32_t parity) { return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity, abort_flag)); };
       static_assert(A_KV_STAGES == 2, "the issue loops select between two K/V slots");
-      uint64_t q_desc[2][2], k_desc[A_KV_STAGES][2], v_desc[A_KV_STAGES];
-#pragma unroll
-      for (int t = 0; t < 2; ++t)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) q_desc[t][h] = ptx::umma_desc_sw128(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES);
-#pragma unroll
-      for (int st = 0; st < A_KV_STAGES; ++st) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) k_desc[st][h] = ptx::umma_desc_sw128(k_addr + st * A_TILE_BYTES + h * A_HALF_BYTES);
-        v_desc[st] = umma_desc_mn_sw128(v_addr + st * A_TILE_BYTES);
-      }
-      // S_t = Q_t K^T : 8 k-steps of 16 along the head dimension (two 64-element swizzled halves)
       auto issue_qk = [&](int t, int s) {
-        const uint64_t qa0 = q_desc[t][0], qa1 = q_desc[t][1];
-        const uint64_t ka0 = s ? k_desc[1][0] : k_desc[0][0], ka1 = s ? k_desc[1][1] : k_desc[0][1];
-#pragma unroll
-        for (int kk = 0; kk < 8; ++kk) {
-          const uint64_t step = (uint64_t)(2 * (kk & 3));
-          ptx::umma_ss<0, 1>(tmem_base + (uint32_t)(t * 128), (kk >> 2 ? qa1 : qa0) + step, (kk >> 2 ? ka1 : ka0) + step, kIdescQK,
-                             kk ? 1u : 0u);
-        }
+        issue_score_products(tmem + (uint32_t)(t * 128), desc_lo_k_major(q_addr + t * A_TILE_BYTES), desc_lo_k_major(k_addr + s * A_TILE_BYTES),
+                             kIdescQK);
       };
-      // O_t += P_t V : 8 k-steps of 16 keys; per step the high and the residual plane of P. The probabilities arrive
-      // in two halves (the 32-key chunks every softmax warpgroup finishes first, then the rest), so the products of
-      // the first half can run while the second is still being computed.
+      // The probabilities arrive in two halves, so the value products of the first half can run while the second is
+      // still being computed. SPLIT == 2: warpgroup 0 writes the 32-key chunks 0, 1 and warpgroup 1 chunks 2, 3, each
+      // in order -> halves {0, 2} and {1, 3}; otherwise chunks are finished in order -> halves {0, 1} and {2, 3}.
       auto issue_pv = [&](int t, int s, bool first, int half) {
-        const uint64_t vd0 = s ? v_desc[1] : v_desc[0];
-        const uint32_t o_tmem = tmem_base + (uint32_t)(256 + t * 128);
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          // SPLIT == 2: warpgroup 0 writes chunks 0, 1 and warpgroup 1 chunks 2, 3 -> halves {0, 2} and {1, 3};
-          // SPLIT == 1: one warpgroup writes chunks 0..3 in order -> halves {0, 1} and {2, 3}
-          const int chunk = SPLIT == 2 ? 2 * (i >> 1) + half : 2 * half + (i >> 1);
-          const int kk = 2 * chunk + (i & 1);
-          const uint32_t p_col = tmem_base + (uint32_t)(t * 128 + 32 * (kk >> 1) + 8 * (kk & 1));
-          const uint64_t vd = vd0 + (uint64_t)(kk * 128);
-          ptx::umma_ts_f16(o_tmem, p_col + 16u, vd, kIdescPV, (first && half == 0 && i == 0) ? 0u : 1u);  // residual first
-          ptx::umma_ts_f16(o_tmem, p_col, vd, kIdescPV, 1u);
-        }
+        const uint32_t o_tmem = tmem + (uint32_t)(256 + t * 128);
+        const uint32_t v_lo = desc_lo_mn_major(v_addr + s * A_TILE_BYTES);
+        const uint32_t accumulate = (first && half == 0) ? 0u : 1u;
+        if constexpr (SPLIT == 2)   // chunks half and 2 + half: columns 32 * chunk (+8 for the chunk's second k-step), keys 32 * chunk
+          issue_value_products<8, 128, 64, 512, 72, 640>(o_tmem, tmem + (uint32_t)(t * 128 + 32 * half), v_lo + (uint32_t)(256 * half), kIdescPV,
+                                                         accumulate);
+        else                        // chunks 2 * half and 2 * half + 1
+          issue_value_products<8, 128, 32, 256, 40, 384>(o_tmem, tmem + (uint32_t)(t * 128 + 64 * half), v_lo + (uint32_t)(512 * half), kIdescPV,
+                                                         accumulate);
       };
-      // scores of tile t for global step g + 1 (the next step of this item, or the first of the next item)
-      auto next_scores = [&](int t, int g) -> bool {
-        const int gn = g + 1, jn = gn % num_kv, sn = gn % A_KV_STAGES;
-        if (jn == 0 && !ptx::mbar_wait(q_full(t), (uint32_t)(gn / num_kv) & 1u, abort_flag)) { atomicExch(status, 0x2100 | t); return false; }
-        if (t == 0 && !ptx::mbar_wait(k_full(sn), (uint32_t)(gn / A_KV_STAGES) & 1u, abort_flag)) { atomicExch(status, 0x2500); return false; }
+      // scores of tile t for the step after (j, it): the next step of this item, or the first of the next item.
+      // Steps, items and ring slots are counted along; the loop holds no division (see softmax_role).
+      auto next_scores = [&](int t, int jn, int itn, int sn, uint32_t k_parity) -> bool {
+        if (jn == 0 && !wait_all(q_full(t), (uint32_t)itn & 1u)) return failed(0x2100 | t);
+        if (t == 0 && !wait_all(k_full(sn), k_parity)) return failed(0x2500);
         ptx::tc_fence_after();
         issue_qk(t, sn);
-        ptx::umma_commit<1>(s_full(t));
-        if (t == 1) ptx::umma_commit<1>(k_empty(sn));
-        if (jn == num_kv - 1) ptx::umma_commit<1>(q_empty(t));   // the item's last read of this query tile
+        ptx::umma_commit_led(leader, s_full(t));
+        if (t == 1) ptx::umma_commit_led(leader, k_empty(sn));
+        if (jn == num_kv - 1) ptx::umma_commit_led(leader, q_empty(t));   // the item's last read of this query tile
         return true;
       };
-      ok = next_scores(0, -1) && next_scores(1, -1);
+      ok = next_scores(0, 0, 0, 0, 0u) && next_scores(1, 0, 0, 0, 0u);
+      int j = 0, it = 0;
       for (int g = 0; g < total_steps && ok; ++g) {
-        const int s = g % A_KV_STAGES, j = g % num_kv;
-        const uint32_t ph = (uint32_t)(g / A_KV_STAGES) & 1u;
+        const int s = g & 1;
+        const uint32_t ph = (uint32_t)(g >> 1) & 1u;
         const bool more = g + 1 < total_steps, first = j == 0, last = j == num_kv - 1;
-        if (!ptx::mbar_wait(v_full(s), ph, abort_flag)) { atomicExch(status, 0x2300); break; }
-        if (!ptx::mbar_wait(p_half(0, 0), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
+        const int jn = last ? 0 : j + 1, itn = last ? it + 1 : it, sn = s ^ 1;
+        const uint32_t k_parity = (uint32_t)((g + 1) >> 1) & 1u;
+        ATRACE(17, g, 0);
+        if (!wait_all(v_full(s), ph)) { failed(0x2300); break; }
+        if (!wait_all(p_half(0, 0), (uint32_t)g & 1u)) { failed(0x2400); break; }
         ptx::tc_fence_after();
+        ATRACE(17, g, 1);
         if (early_pv) issue_pv(0, s, first, 0);
-        if (!ptx::mbar_wait(p_half(0, 1), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2400); break; }
+        if (!wait_all(p_half(0, 1), (uint32_t)g & 1u)) { failed(0x2400); break; }
         ptx::tc_fence_after();
+        ATRACE(17, g, 2);
         if (!early_pv) issue_pv(0, s, first, 0);
         issue_pv(0, s, first, 1);
-        if (last) ptx::umma_commit<1>(o_done(0));
-        if (more && !next_scores(0, g)) break;
-        if (!ptx::mbar_wait(p_half(1, 0), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
+        if (last) ptx::umma_commit_led(leader, o_done(0));
+        // At the end of an item the next item's queries may not have arrived yet: then the item's remaining value
+        // products go first, so that its output can be normalised and stored while the queries are on their way.
+        const bool scores_later = last && more && !__all_sync(0xffffffffu, ptx::mbar_test_wait(q_full(0), (uint32_t)itn & 1u));
+        if (more && !scores_later && !next_scores(0, jn, itn, sn, k_parity)) break;
+        ATRACE(17, g, 3);
+        if (!wait_all(p_half(1, 0), (uint32_t)g & 1u)) { failed(0x2600); break; }
         ptx::tc_fence_after();
+        ATRACE(17, g, 4);
         if (early_pv) issue_pv(1, s, first, 0);
-        if (!ptx::mbar_wait(p_half(1, 1), (uint32_t)g & 1u, abort_flag)) { atomicExch(status, 0x2600); break; }
+        if (!wait_all(p_half(1, 1), (uint32_t)g & 1u)) { failed(0x2600); break; }
         ptx::tc_fence_after();
+        ATRACE(17, g, 5);
         if (!early_pv) issue_pv(1, s, first, 0);
         issue_pv(1, s, first, 1);
-        ptx::umma_commit<1>(v_empty(s));
-        if (last) ptx::umma_commit<1>(o_done(1));
-        if (more && !next_scores(1, g)) break;
+        ptx::umma_commit_led(leader, v_empty(s));
+        if (last) ptx::umma_commit_led(leader, o_done(1));
+        if (scores_later && !next_scores(0, jn, itn, sn, k_parity)) break;
+        if (more && !next_scores(1, jn, itn, sn, k_parity)) break;
+        ATRACE(17, g, 6);
+        j = jn;
+        it = itn;
       }
     }
     __syncwarp();
@@ -235,6 +250,10 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     role.o_done = o_done(t);
     role.remote_arrive = false;
     role.xchg = xchg;
+    role.xbar = x_bar(t, warp & 3);
+    role.out_map = &tm_out;
+    role.out_stage = (t == 0 ? k_addr : v_addr) + (uint32_t)(warp & 7) * 4096u;   // SPLIT == 2: the tile's eight warps, 4 KiB each
+    role.staged_bar = staged(t);
     role.stage_base = stage_base;
     role.abort_flag = abort_flag;
     role.status = status;
@@ -261,7 +280,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const SoftmaxBarrierStrides strides = {s_full(1) - s_full(0), p_half(1, 0) - p_half(0, 0), o_done(1) - o_done(0)};
       softmax_role_alternating(role, strides, warp, lane);
     } else {
-      softmax_role<SPLIT>(role, warp, lane);
+      softmax_role<SPLIT, KEEP>(role, warp, lane);
     }
   }
 
@@ -310,11 +329,26 @@ static int make_rows_map(CUtensorMap* map, const void* base, int64_t rows) {
   return DTN_OK;
 }
 
+// [rows, 128] FP32 output, box = 32 columns (128 bytes) x 32 rows, 128-byte swizzle.
+static int make_output_map(CUtensorMap* map, const void* base, int64_t rows) {
+  EncodeTiledFn enc = attn_encode_fn();
+  DTN_REQUIRE(enc != nullptr, DTN_ERR_CUDA, "gqa: cuTensorMapEncodeTiled is not available");
+  const cuuint64_t dims[2] = {(cuuint64_t)A_D, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)A_D * 4};
+  const cuuint32_t box[2] = {32, 32};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  DTN_REQUIRE(r == CUDA_SUCCESS, DTN_ERR_CUDA, "gqa: cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
+  return DTN_OK;
+}
+
 bool gqa_tc_supported(int64_t S, int64_t D, int storage) {
   return storage == DTN_STORAGE_F16 && D == A_D && S >= 2 * A_BM && S % (2 * A_BM) == 0;
 }
 
-template <int SPLIT>
+template <int SPLIT, bool KEEP = false>
 static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
                            int64_t S, float scale, int64_t gb, int64_t ge, cudaStream_t s) {
   CUtensorMap mq, mk, mv;
@@ -322,11 +356,13 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
   if ((rc = make_rows_map(&mq, q, B * Hq * S))) return rc;
   if ((rc = make_rows_map(&mk, k, B * Hkv * S))) return rc;
   if ((rc = make_rows_map(&mv, v, B * Hkv * S))) return rc;
+  CUtensorMap mo = mq;   // only the KEEP form stores through a tensor map
+  if (KEEP && (rc = make_output_map(&mo, out, B * Hq * S))) return rc;
   static thread_local int attr_dev = -1;
   int dev = 0;
   DTN_CUDA_CHECK(cudaGetDevice(&dev));
   if (attr_dev != dev) {
-    DTN_CUDA_CHECK(cudaFuncSetAttribute(gqa_tc_kernel<SPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM_BYTES));
+    DTN_CUDA_CHECK(cudaFuncSetAttribute(gqa_tc_kernel<SPLIT, KEEP>, cudaFuncAttributeMaxDynamicSharedMemorySize, A_SMEM_BYTES));
     attr_dev = dev;
   }
   int* status = device_status_word();
@@ -344,15 +380,22 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
   }();
   const int64_t ctas = persistent && items > sm_count() ? sm_count() : items;
   const float scale_log2e = scale * 1.4426950408889634f;
-  gqa_tc_kernel<SPLIT><<<(unsigned)ctas, attn_threads(SPLIT), A_SMEM_BYTES, s>>>(mq, mk, mv, out, (int)Hq, (int)Hkv, (int)S, scale_log2e,
+  gqa_tc_kernel<SPLIT, KEEP><<<(unsigned)ctas, attn_threads(SPLIT), A_SMEM_BYTES, s>>>(mq, mk, mv, mo, out, (int)Hq, (int)Hkv, (int)S, scale_log2e,
                                                                                  (int)gb, (int)items, early_pv, status);
   DTN_LAUNCH_CHECK("gqa_tc_kernel");
   return DTN_OK;
 }
 
+#ifdef DTN_ATTN_TRACE
+extern "C" int dtn_attn_trace_copy(long long* host) {
+  return (int)cudaMemcpyFromSymbol(host, g_attn_trace, sizeof(g_attn_trace));
+}
+#endif
+
 int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
                   int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s) {
   if (split == 4) return gqa_tc_launch_t<4>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s);
+  if (split == 3) return gqa_tc_launch_t<2, true>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s);   // two warpgroups, kept scores
   return split == 2 ? gqa_tc_launch_t<2>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s)
                     : gqa_tc_launch_t<1>(q, k, v, out, B, Hq, Hkv, S, scale, gb, ge, s);
 }
