@@ -62,6 +62,12 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   volatile float2* xchg = reinterpret_cast<volatile float2*>(bar_ptr + 256);
   float* stage_base = reinterpret_cast<float*>(bar_ptr + 256 + A_XCHG_BYTES);   // 1 KiB per softmax warp
   constexpr int kTmaWarp = attn_softmax_warps(SPLIT), kMmaWarp = attn_softmax_warps(SPLIT) + 1;
+#ifdef DTN_ATTN_TRACE
+  const uint32_t dbg_bar = bar_addr + 256 + A_XCHG_BYTES;   // in the staging area, which the traced form does not use
+#define DTN_DBG_COMMIT(b) ptx::umma_commit_led(leader, dbg_bar + 8u * (b))
+#else
+#define DTN_DBG_COMMIT(b)
+#endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qblocks = S / (2 * A_BM);
@@ -88,6 +94,9 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ptx::mbar_init(p_half(t, 0), attn_p_half_arrivals(SPLIT));   // one arrival per softmax warp that writes this half
       ptx::mbar_init(p_half(t, 1), attn_p_half_arrivals(SPLIT));
       ptx::mbar_init(o_done(t), 1);
+#ifdef DTN_ATTN_TRACE
+      if (t == 0) for (int b = 0; b < 6; ++b) ptx::mbar_init(dbg_bar + 8u * b, 1);
+#endif
       ptx::mbar_init(staged(t), attn_softmax_warps(SPLIT) / 2);
       for (int quarter = 0; quarter < 4; ++quarter) ptx::mbar_init(x_bar(t, quarter), 2);
     }
@@ -148,6 +157,16 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
     }
+#ifdef DTN_ATTN_TRACE
+    else if (lane == 1 && blockIdx.x == 0) {
+      bool fine = true;
+      for (int g = 0; g < total_steps && fine; ++g)
+        for (int b = 0; b < 6; ++b) {
+          if (!ptx::mbar_wait(dbg_bar + 8u * b, (uint32_t)g & 1u, abort_flag)) { fine = false; break; }
+          if (g >= DTN_ATTN_TRACE && g < DTN_ATTN_TRACE + 32) g_attn_trace[((g - DTN_ATTN_TRACE) * 32 + 21) * 8 + b] = clock64();
+        }
+    }
+#endif
     __syncwarp();
   } else if (warp == kMmaWarp) {
     // ------------------------------------ MMA issuer -----------------------------------------
@@ -209,30 +228,36 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         ptx::tc_fence_after();
         ATRACE(17, g, 1);
         if (early_pv) issue_pv(0, s, first, 0);
+        DTN_DBG_COMMIT(0);
         if (!wait_all(p_half(0, 1), (uint32_t)g & 1u)) { failed(0x2400); break; }
         ptx::tc_fence_after();
         ATRACE(17, g, 2);
         if (!early_pv) issue_pv(0, s, first, 0);
         issue_pv(0, s, first, 1);
+        DTN_DBG_COMMIT(1);
         if (last) ptx::umma_commit_led(leader, o_done(0));
         // At the end of an item the next item's queries may not have arrived yet: then the item's remaining value
         // products go first, so that its output can be normalised and stored while the queries are on their way.
         const bool scores_later = last && more && !__all_sync(0xffffffffu, ptx::mbar_test_wait(q_full(0), (uint32_t)itn & 1u));
         if (more && !scores_later && !next_scores(0, jn, itn, sn, k_parity)) break;
+        DTN_DBG_COMMIT(2);
         ATRACE(17, g, 3);
         if (!wait_all(p_half(1, 0), (uint32_t)g & 1u)) { failed(0x2600); break; }
         ptx::tc_fence_after();
         ATRACE(17, g, 4);
         if (early_pv) issue_pv(1, s, first, 0);
+        DTN_DBG_COMMIT(3);
         if (!wait_all(p_half(1, 1), (uint32_t)g & 1u)) { failed(0x2600); break; }
         ptx::tc_fence_after();
         ATRACE(17, g, 5);
         if (!early_pv) issue_pv(1, s, first, 0);
         issue_pv(1, s, first, 1);
+        DTN_DBG_COMMIT(4);
         ptx::umma_commit_led(leader, v_empty(s));
         if (last) ptx::umma_commit_led(leader, o_done(1));
         if (scores_later && !next_scores(0, jn, itn, sn, k_parity)) break;
         if (more && !next_scores(1, jn, itn, sn, k_parity)) break;
+        DTN_DBG_COMMIT(5);
         ATRACE(17, g, 6);
         j = jn;
         it = itn;
