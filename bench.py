@@ -50,7 +50,7 @@ FLOPS_PER_GEMM = 2.0 * M * N * K
 WORKLOAD = 'gemm_bf16x3_8192x8192x8192_f32io'
 # dram__bytes_read.sum + dram__bytes_write.sum of one 8192^3 launch of the product kernel, from the ncu capture
 # summarised in profiles/gemm_x3_kernel_bf16_8192_dram.md (2.32 GB read + 0.26 GB written)
-PRODUCT_KERNEL_DRAM_BYTES = 2.58e9
+PRODUCT_KERNEL_DRAM_BYTES = 3.06e9   # gemm_x3_stream_kernel, 8192^3: 2 537 MB read + 522 MB written (profiles/gemm_x3_stream_kernel_bf16_8192_dram.md)
 PRODUCT_KERNEL_ALGORITHMIC_BYTES = 4 * M * K * 2 + 4 * M * N   # four bf16 planes read once + C written once
 
 
@@ -368,7 +368,7 @@ def extras(torch, ops, peaks: dict) -> dict:
     torch.backends.cuda.matmul.allow_tf32 = previous
     tf32_peak = FLOPS_PER_GEMM / library_ms / 1e9
     out['gemm_tf32x3_8192'].update({'library_tf32_gemm_tflops': tf32_peak,
-                                    'frac_of_library_tf32_peak_over_3': out['gemm_tf32x3_8192']['tflops'] / (tf32_peak / 3)})
+                                    'ratio_to_library_tf32_gemm_over_3': out['gemm_tf32x3_8192']['tflops'] / (tf32_peak / 3)})
     del a, b, c
     n = 1 << 28
     x = torch.randn(n, device=device, generator=generator)
