@@ -412,7 +412,10 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ----------------------------------------
-    if (lane == 0 && rank == 0) {
+    // All 32 lanes walk the loop and wait on the barriers; an elected lane issues, so that the descriptors stay in
+    // uniform registers (issued from a one-lane branch they go through vector registers, and a 128 x 64 tile's twelve
+    // products of a k-block take no longer to execute than that takes to issue).
+    if (rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
@@ -420,15 +423,15 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
       for (int t = unit; t < num_tiles && ok; t += num_units, ++iter) {
         const int acc = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
-        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          atomicExch(status, 0x200 | (int)(blockIdx.x & 0xff));
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) {
+          if (lane == 0) atomicExch(status, 0x200 | (int)(blockIdx.x & 0xff));
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-            atomicExch(status, 0x300 | (int)(blockIdx.x & 0xff));
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag))) {
+            if (lane == 0) atomicExch(status, 0x300 | (int)(blockIdx.x & 0xff));
             ok = false;
             break;
           }
@@ -437,20 +440,12 @@ gemm_x3_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_constan
           const uint32_t sa_lo = sa_hi + Cfg::kABytes;
           const uint32_t sb_hi = sa_lo + Cfg::kABytes;
           const uint32_t sb_lo = sb_hi + Cfg::kBBytes;
-          const uint64_t da_hi = ptx::umma_desc_sw128(sa_hi), da_lo = ptx::umma_desc_sw128(sa_lo);
-          const uint64_t db_hi = ptx::umma_desc_sw128(sb_hi), db_lo = ptx::umma_desc_sw128(sb_lo);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            // one k-step = 32 bytes along the swizzled row = +2 in the descriptor's address field
-            const uint64_t o = (uint64_t)(2 * k);
-            ptx::umma_ss<KIND, CTAS>(d_tmem, da_lo + o, db_hi + o, kIdesc, (kb | k) != 0 ? 1u : 0u);
-            ptx::umma_ss<KIND, CTAS>(d_tmem, da_hi + o, db_lo + o, kIdesc, 1u);
-            ptx::umma_ss<KIND, CTAS>(d_tmem, da_hi + o, db_hi + o, kIdesc, 1u);
-          }
-          ptx::umma_commit<CTAS>(empty_bar(stage));  // frees this ring slot once the MMAs have read it
+          ptx::umma_x3_kblock<KIND, CTAS>(d_tmem, ptx::desc_lo_sw128(sa_hi), ptx::desc_lo_sw128(sa_lo), ptx::desc_lo_sw128(sb_hi),
+                                          ptx::desc_lo_sw128(sb_lo), kIdesc, kb != 0 ? 1u : 0u);
+          ptx::umma_commit_elected<CTAS>(empty_bar(stage));  // frees this ring slot once the MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) ptx::umma_commit<CTAS>(tfull_bar(acc));  // accumulator complete
+        if (ok) ptx::umma_commit_elected<CTAS>(tfull_bar(acc));  // accumulator complete
       }
     }
     __syncwarp();
@@ -876,7 +871,10 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
     __syncwarp();
   } else if (warp == 1) {
     // ------------------------------- MMA issuer ----------------------------------------
-    if (lane == 0 && rank == 0) {
+    // All 32 lanes of the leader CTA's warp walk the loop and wait on the barriers; an elected lane issues. With
+    // uniform control flow and operands the descriptors stay in uniform registers, and the twelve products of a
+    // k-block cost the warp a few dozen instructions on a scheduler it shares with split and epilogue warps.
+    if (rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int iter = 0;
@@ -888,15 +886,15 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
         const int acc = iter & 1;
         const uint32_t acc_phase = (uint32_t)(iter >> 1) & 1u;
         ++iter;
-        if (!ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag)) {
-          atomicExch(status, 0x200 | (int)(blockIdx.x & 0xff));
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag))) {
+          if (lane == 0) atomicExch(status, 0x200 | (int)(blockIdx.x & 0xff));
           break;
         }
         ptx::tc_fence_after();
         const uint32_t d_tmem = tmem_base + (uint32_t)(acc * 256);
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!ptx::mbar_wait(full_bar(stage), phase, abort_flag)) {
-            atomicExch(status, 0x300 | (int)(blockIdx.x & 0xff));
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(full_bar(stage), phase, abort_flag))) {
+            if (lane == 0) atomicExch(status, 0x300 | (int)(blockIdx.x & 0xff));
             ok = false;
             break;
           }
@@ -905,19 +903,12 @@ gemm_x3_stream_kernel(const __grid_constant__ CUtensorMap tm_a_hi, const __grid_
           const uint32_t sa_lo = sa_hi + Cfg::kABytes;
           const uint32_t sb_hi = sa_lo + Cfg::kABytes;
           const uint32_t sb_lo = sb_hi + Cfg::kBBytes;
-          const uint64_t da_hi = ptx::umma_desc_sw128(sa_hi), da_lo = ptx::umma_desc_sw128(sa_lo);
-          const uint64_t db_hi = ptx::umma_desc_sw128(sb_hi), db_lo = ptx::umma_desc_sw128(sb_lo);
-#pragma unroll
-          for (int k = 0; k < 4; ++k) {
-            const uint64_t o = (uint64_t)(2 * k);
-            ptx::umma_ss<KIND, 2>(d_tmem, da_lo + o, db_hi + o, idesc, (kb | k) != 0 ? 1u : 0u);
-            ptx::umma_ss<KIND, 2>(d_tmem, da_hi + o, db_lo + o, idesc, 1u);
-            ptx::umma_ss<KIND, 2>(d_tmem, da_hi + o, db_hi + o, idesc, 1u);
-          }
-          ptx::umma_commit<2>(empty_bar(stage));
+          ptx::umma_x3_kblock<KIND, 2>(d_tmem, ptx::desc_lo_sw128(sa_hi), ptx::desc_lo_sw128(sa_lo), ptx::desc_lo_sw128(sb_hi),
+                                         ptx::desc_lo_sw128(sb_lo), idesc, kb != 0 ? 1u : 0u);
+          ptx::umma_commit_elected<2>(empty_bar(stage));
           if (++stage == kStages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) ptx::umma_commit<2>(tfull_bar(acc));
+        if (ok) ptx::umma_commit_elected<2>(tfull_bar(acc));
       }
     }
     __syncwarp();

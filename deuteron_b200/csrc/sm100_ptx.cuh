@@ -308,6 +308,53 @@ __device__ __forceinline__ void umma_commit_led(uint32_t leader, uint32_t bar) {
       : "memory");
 }
 
+// The two 32-bit words of umma_desc_sw128: the high word is the same for every K-major, 128-byte-swizzled operand.
+constexpr uint32_t kDescHiSw128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t smem_addr) { return ((smem_addr >> 4) & 0x3FFFu) | (1u << 16); }
+
+// One 128-byte k-block of a compensated product on one CTA or a CTA pair: four k-steps of 16 (32 bytes: +2 in the address
+// field), per step lo*hi, hi*lo, hi*hi into the same accumulator. All 32 lanes of the issuing warp reach this block;
+// `elect.sync` picks the lane that issues all twelve instructions, and every operand is uniform across the warp, so
+// descriptors and addresses stay in uniform registers. KIND: 0 = bf16 planes (kind::f16), 1 = tf32 planes.
+template <int KIND, int CTAS>
+__device__ __forceinline__ void umma_x3_kblock(uint32_t d_tmem, uint32_t a_hi, uint32_t a_lo, uint32_t b_hi, uint32_t b_lo,
+                                                    uint32_t idesc, uint32_t accumulate_first) {
+#define DTN_X3_STEP(MMA, OFF, FIRST)                                                                                      \
+  "add.u32 ah, %1, " #OFF ";\n\tadd.u32 al, %2, " #OFF ";\n\tadd.u32 bh, %3, " #OFF ";\n\tadd.u32 bl, %4, " #OFF ";\n\t" \
+  "mov.b64 dah, {ah, %5};\n\tmov.b64 dal, {al, %5};\n\tmov.b64 dbh, {bh, %5};\n\tmov.b64 dbl, {bl, %5};\n\t"          \
+  "@q " MMA " [%0], dal, dbh, %6, " FIRST ";\n\t"                                                                         \
+  "@q " MMA " [%0], dah, dbl, %6, yes;\n\t"                                                                               \
+  "@q " MMA " [%0], dah, dbh, %6, yes;\n\t"
+#define DTN_X3_BLOCK(MMA)                                                                                        \
+  asm volatile(                                                                                                  \
+      "{\n\t.reg .pred q, acc, yes;\n\t.reg .b32 ah, al, bh, bl;\n\t.reg .b64 dah, dal, dbh, dbl;\n\t"          \
+      "elect.sync _|q, 0xffffffff;\n\t"                                                                          \
+      "setp.ne.b32 acc, %7, 0;\n\tsetp.eq.b32 yes, 0, 0;\n\t"                                                    \
+      DTN_X3_STEP(MMA, 0, "acc") DTN_X3_STEP(MMA, 2, "yes") DTN_X3_STEP(MMA, 4, "yes") DTN_X3_STEP(MMA, 6, "yes") \
+      "}" ::"r"(d_tmem), "r"(a_hi), "r"(a_lo), "r"(b_hi), "r"(b_lo), "r"(kDescHiSw128), "r"(idesc), "r"(accumulate_first) \
+      : "memory")
+  if constexpr (KIND == 0 && CTAS == 2) DTN_X3_BLOCK("tcgen05.mma.cta_group::2.kind::f16");
+  else if constexpr (KIND == 1 && CTAS == 2) DTN_X3_BLOCK("tcgen05.mma.cta_group::2.kind::tf32");
+  else if constexpr (KIND == 0) DTN_X3_BLOCK("tcgen05.mma.cta_group::1.kind::f16");
+  else DTN_X3_BLOCK("tcgen05.mma.cta_group::1.kind::tf32");
+#undef DTN_X3_BLOCK
+#undef DTN_X3_STEP
+}
+// umma_commit issued by the elected lane of a warp whose 32 lanes all reach it.
+template <int CTAS>
+__device__ __forceinline__ void umma_commit_elected(uint32_t bar) {
+  if constexpr (CTAS == 1) {
+    umma_commit_led(1u, bar);
+  } else {
+    const uint16_t mask = 3;
+    asm volatile(
+        "{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+        "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(bar),
+        "h"(mask)
+        : "memory");
+  }
+}
+
 // Make `bar` complete one arrival once every tcgen05.mma issued so far by this thread
 // has finished. With CTAS == 2 the arrival is delivered to the barrier at the same
 // shared-memory offset in both CTAs of the pair.
