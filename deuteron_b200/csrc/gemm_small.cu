@@ -54,11 +54,18 @@ __device__ __forceinline__ uint32_t pack_bf16(float low, float high) {
   __nv_bfloat162 v = __floats2bfloat162_rn(low, high);   // .x (low half) = first k index
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// hi = bf16_rn(v) pairs, lo = bf16_rn(v - hi) pairs. One conversion rounds both values; the rounded values come back
-// as FP32 by a shift and a mask (a bf16 is the upper half of an FP32).
+// hi = bf16_rn(v) pairs, lo = bf16_rn(v - hi) pairs. One conversion rounds both values; the residuals come from the
+// mixed-precision fma of sm_100, which takes the bf16 halves as they are: v - hi = hi * (-1) + v, exact, without
+// the shift and the mask that bring hi back to FP32 (four instructions per pair instead of six; these kernels are
+// bound by exactly this arithmetic).
 __device__ __forceinline__ void split_bf16_pair(float a, float b, uint32_t& hi, uint32_t& lo) {
   hi = pack_bf16(a, b);
-  lo = pack_bf16(a - __uint_as_float(hi << 16), b - __uint_as_float(hi & 0xffff0000u));
+  float ra, rb;
+  asm("{\n\t.reg .b16 h0, h1, m;\n\tmov.b32 {h0, h1}, %2;\n\tmov.b16 m, 0xBF80;\n\t"   // m = -1.0
+      "fma.rn.f32.bf16 %0, h0, m, %3;\n\tfma.rn.f32.bf16 %1, h1, m, %4;\n\t}"
+      : "=f"(ra), "=f"(rb)
+      : "r"(hi), "f"(a), "f"(b));
+  lo = pack_bf16(ra, rb);
 }
 __device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));

@@ -30,6 +30,10 @@ namespace dtn {
 
 int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K,
                     int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t s, bool split_k_allowed);
+int gemm_skinny_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                       int64_t ldc, void* workspace, cudaStream_t s);
+bool gemm_skinny_supported(const float* A, const float* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb);
+size_t gemm_skinny_workspace_bytes(int64_t N, int64_t K);
 int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                       int64_t ldb, int64_t ldc, cudaStream_t s);
 bool gemm_fused_supported(int mode, const float* A, const float* B, int64_t N, int64_t K, int64_t lda, int64_t ldb);
@@ -1609,7 +1613,7 @@ int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_ou
 }
 
 int dtn_gemm_set_variant(int variant) {
-  DTN_REQUIRE(variant >= 0 && variant <= 9, DTN_ERR_INVALID, "gemm: variant must be 0..9");
+  DTN_REQUIRE(variant >= 0 && variant <= 10, DTN_ERR_INVALID, "gemm: variant must be 0..10");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
 }
@@ -1650,6 +1654,21 @@ int dtn_gemm_x3_phase(int mode, const float* A, const float* B, float* C, int64_
   if (mode == DTN_GEMM_F32 || mode == DTN_GEMM_F32_SPLITK)
     return (phase & 2) ? gemm_f32_launch(A, B, C, M, N, K, lda, ldb, ldc, s, mode == DTN_GEMM_F32_SPLITK) : DTN_OK;
 
+  // At most 16 rows: the TMA-fed single-pass kernel when B is worth streaming (measured: 16 x 4736 x 8192 33.7 against
+  // 59.5 us, 16 x 2048 x 4096 16.5 against 15.5 us for the cp.async kernel; variant 10 takes it wherever it applies).
+  // Its partial sums live in the workspace, which is sized for B's planes and therefore large enough whenever B is.
+  // DTN_GEMM_SKINNY_TMA=0 keeps the cp.async kernel.
+  static const bool skinny_tma = [] {
+    const char* text = getenv("DTN_GEMM_SKINNY_TMA");
+    return !(text && text[0] == '0');
+  }();
+  const bool skinny_wanted = g_gemm_variant == 10 || (g_gemm_variant == 0 && skinny_tma && (double)N * (double)K >= 12.0 * 1024 * 1024);
+  if (phase == 3 && skinny_wanted && gemm_skinny_supported(A, B, M, N, K, lda, ldb) && workspace != nullptr && aligned_to(workspace, 16) &&
+      workspace_bytes >= gemm_skinny_workspace_bytes(N, K))
+    return gemm_skinny_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, workspace, s);
+  DTN_REQUIRE(g_gemm_variant != 10, DTN_ERR_UNSUPPORTED,
+              "gemm: the streamed skinny kernel needs at most 16 rows, 16-byte aligned A and B with leading dimensions that are "
+              "multiples of 4, both phases in one call and a workspace");
   if (phase == 3 && (g_gemm_variant == 4 || (g_gemm_variant == 0 && prefers_small_kernel(M, N, K))))
     return gemm_small_launch(mode, A, B, C, M, N, K, lda, ldb, ldc, s);
   DTN_REQUIRE(g_gemm_variant != 4, DTN_ERR_INVALID, "gemm: the single-kernel variant has no separate phases");

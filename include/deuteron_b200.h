@@ -271,7 +271,11 @@ int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_ou
  *   workspace, one launch; bf16x3 with 16-byte aligned A and B, lda and ldb multiples of 4, N and
  *   K multiples of 8, else DTN_ERR_UNSUPPORTED), 7 = the stream kernel: two-CTA tiles 256 rows tall from the
  *   schedule of dtn_gemm_tile_schedule, with the split of A running inside the kernel beside the products (what
- *   automatic picks where it picked 3 before; 3 remains as the plain two-kernel form).
+ *   automatic picks where it picked 3 before; 3 remains as the plain two-kernel form; 8 and 9 pin where the operand
+ *   splits run), 10 = the streamed kernel for at most 16 rows wherever it applies (B brought in once by TMA in equal
+ *   shares per SM, partial sums of a column block added in a fixed order through the workspace; needs 16-byte
+ *   aligned A and B with lda and ldb multiples of 4, else DTN_ERR_UNSUPPORTED; what automatic picks for at most 16
+ *   rows once B has 12 Mi elements).
  * No reference counterpart. */
 int dtn_gemm_set_variant(int variant);
 

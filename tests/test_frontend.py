@@ -277,7 +277,7 @@ def test_argument_checks_need_no_gpu():
     library = native.lib()
     assert library.dtn_add_f32(None, None, None, -1, None) == native.ERR_INVALID
     assert 'negative' in native.last_error()
-    assert library.dtn_gemm_set_variant(10) == native.ERR_INVALID
+    assert library.dtn_gemm_set_variant(11) == native.ERR_INVALID
     size = ctypes.c_size_t(0)
     assert library.dtn_gemm_workspace_bytes(2, 8192, 8192, 8192, ctypes.byref(size)) == 0
     # hi and lo bf16 planes of A and of B transposed, then the two counters and the (32 + 32) x 64 item flags of the

@@ -525,6 +525,41 @@ def test_fused_split_gemm_reproduces_the_two_kernel_path(cuda, monkeypatch, publ
         ops.set_gemm_variant(0)
 
 
+SKINNY_SHAPES = [(16, 8192, 4096), (1, 4096, 4096), (7, 4100, 2052), (16, 2048 + 36, 1024 + 4), (3, 128, 65536), (16, 65536, 64)]
+
+
+@pytest.mark.parametrize('mode', ['bf16x3', 'tf32x3'])
+def test_skinny_gemm_streams_b_once(cuda, mode):
+    """At most 16 rows: the TMA-fed kernel (every SM takes an equal share of B; partial sums of a column block meet in
+    the workspace and are added in a fixed order). Ragged N and K, one row, very long and very short k; the same
+    launch twice gives the same bits, whoever arrives last."""
+    ops.set_gemm_variant(10)   # the streamed kernel whatever the size
+    try:
+        _check_skinny_shapes(cuda, mode)
+    finally:
+        ops.set_gemm_variant(0)
+
+
+def _check_skinny_shapes(cuda, mode):
+    for m, n, k in SKINNY_SHAPES:
+        a, b = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+        left, right = to_device(cuda, a), to_device(cuda, b)
+        produced = ops.gemm(left, right, mode)
+        ops.check_device_status()
+        again = ops.gemm(left, right, mode)
+        assert cuda.equal(produced, again), (m, n, k)
+        exact = R.gemm_f64(a, b)
+        floor = R.max_relative_error(R.gemm_x3_exact_products(a, b, mode), exact)
+        steps = 3 * math.ceil(k / (16 if mode == 'bf16x3' else 8))
+        error = R.max_relative_error(produced.cpu().numpy(), exact)
+        assert error <= 2 * floor + steps * 2.0 ** -24, (m, n, k, error, floor)
+        # a view with padded leading dimensions and an output that is not 16-byte aligned
+        wide = cuda.zeros((k, n + 12), device='cuda:0')
+        wide[:, 4:n + 4] = right
+        shifted = ops.gemm(left, wide[:, 4:n + 4], mode)
+        assert cuda.equal(shifted, produced), (m, n, k)
+
+
 def test_gemm_f32_mode_shapes(cuda):
     for m, n, k in SHAPES[:-1]:
         a, b = R.seeded_normal(7, (m, k)), R.seeded_normal(11, (k, n))
