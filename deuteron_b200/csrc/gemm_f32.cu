@@ -135,6 +135,10 @@ gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ B, float*
 // results are bit-identical to it (and to the reference's f32 kernel).
 constexpr int FS_B = 32, FS_BK = 16;
 
+__device__ __forceinline__ void f32_copy_4(uint32_t dst, const void* src, int valid_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
+}
+
 // KPARTS > 1: a cluster of KPARTS CTAs along z shares one output tile, each CTA takes a contiguous slice of k, and the
 // partial sums meet in the first CTA's shared memory (distributed-shared-memory stores into a fixed slot per CTA and
 // thread) where they are added in rank order: no atomics, the same bits on every run. Used for contractions too small
@@ -145,8 +149,13 @@ template <int KPARTS>
 __global__ void __launch_bounds__(F_THREADS)
 gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                       int64_t lda, int64_t ldb, int64_t ldc) {
-  __shared__ float As[2][FS_BK][FS_B + 1];
-  __shared__ float Bs[2][FS_BK][FS_B + 1];
+  // The k-tiles go through a ring of FS_STAGES slots filled by cp.async (4-byte copies, so any alignment and any edge:
+  // out-of-range elements are zero-filled), all slots requested before the first product. One k-tile is a few hundred
+  // cycles of arithmetic against a global-memory latency of about a thousand: with the next tile alone in flight
+  // (registers, as the large-tile kernels do) every k-tile cost a full latency, 0.48 us per 16 k.
+  constexpr int FS_STAGES = KPARTS > 1 ? 4 : 8;   // a CTA of a k-split has few k-tiles, and its partial sums need the room
+  __shared__ float As[FS_STAGES][FS_BK][FS_B + 1];
+  __shared__ float Bs[FS_STAGES][FS_BK][FS_B + 1];
   __shared__ float partials[KPARTS > 1 ? (KPARTS - 1) * F_THREADS * 4 : 1];
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * FS_B, n0 = blockIdx.x * FS_B;
@@ -156,36 +165,31 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
   const int k_begin = (KPARTS > 1 ? (int)blockIdx.z * per_part : 0) * FS_BK;
   const int k_end = KPARTS > 1 ? min(K, k_begin + per_part * FS_BK) : K;
   const int tx = tid & 15, ty = tid >> 4;   // 16 x 16 threads, each 2 x 2 outputs
-  // staging: 512 elements per operand tile, two per thread
-  float ra[2], rb[2];
-  auto load_tiles = [&](int k0) {
+  auto request_tile = [&](int k0, int slot) {   // 512 elements per operand tile, two per thread
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int v = tid + i * F_THREADS;          // 0..511
-      const int ar = v >> 4, ak = v & 15;         // A: 32 rows x 16 k, k fastest
-      ra[i] = (m0 + ar < M && k0 + ak < k_end) ? A[(int64_t)(m0 + ar) * lda + k0 + ak] : 0.f;
+      const int ar = v >> 4, ak = v & 15;         // A: 32 rows x 16 k, k fastest in memory, stored [k][row]
+      const bool a_in = m0 + ar < M && k0 + ak < k_end;
+      f32_copy_4(smem_u32(&As[slot][ak][ar]), a_in ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, a_in ? 4 : 0);
       const int bk = v >> 5, bn = v & 31;         // B: 16 k x 32 columns, column fastest
-      rb[i] = (k0 + bk < k_end && n0 + bn < N) ? B[(int64_t)(k0 + bk) * ldb + n0 + bn] : 0.f;
-    }
-  };
-  auto store_tiles = [&](int buf) {
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const int v = tid + i * F_THREADS;
-      As[buf][v & 15][v >> 4] = ra[i];
-      Bs[buf][v >> 5][v & 31] = rb[i];
+      const bool b_in = k0 + bk < k_end && n0 + bn < N;
+      f32_copy_4(smem_u32(&Bs[slot][bk][bn]), b_in ? (const void*)(B + (int64_t)(k0 + bk) * ldb + n0 + bn) : (const void*)B, b_in ? 4 : 0);
     }
   };
   float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
   const int ktiles = k_end > k_begin ? (k_end - k_begin + FS_BK - 1) / FS_BK : 0;
-  if (ktiles > 0) {
-    load_tiles(k_begin);
-    store_tiles(0);
+#pragma unroll
+  for (int s = 0; s < FS_STAGES - 1; ++s) {
+    if (s < ktiles) request_tile(k_begin + s * FS_BK, s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
   }
-  __syncthreads();
   for (int kt = 0; kt < ktiles; ++kt) {
-    const int buf = kt & 1;
-    if (kt + 1 < ktiles) load_tiles(k_begin + (kt + 1) * FS_BK);
+    asm volatile("cp.async.wait_group %0;" ::"n"(FS_STAGES - 2) : "memory");
+    __syncthreads();   // tile kt has landed for every thread, and everybody is done with the slot requested next
+    if (kt + FS_STAGES - 1 < ktiles) request_tile(k_begin + (kt + FS_STAGES - 1) * FS_BK, (kt + FS_STAGES - 1) % FS_STAGES);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int buf = kt % FS_STAGES;
 #pragma unroll
     for (int k = 0; k < FS_BK; ++k) {
       const float a0 = As[buf][k][ty * 2], a1 = As[buf][k][ty * 2 + 1];
@@ -195,9 +199,8 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
       acc[1][0] = fmaf(a1, b0, acc[1][0]);
       acc[1][1] = fmaf(a1, b1, acc[1][1]);
     }
-    if (kt + 1 < ktiles) store_tiles(buf ^ 1);
-    __syncthreads();
   }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
   if constexpr (KPARTS > 1) {
     const int part = (int)blockIdx.z;
     if (part != 0) {
