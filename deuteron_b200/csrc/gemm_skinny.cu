@@ -429,6 +429,20 @@ static int gemm_skinny_launch_mode(const float* A, const float* B, float* C, int
   return DTN_OK;
 }
 
+// Host-side copy of the kernel's partition, for inspection and tests (pure arithmetic, no device needed).
+int gemm_skinny_plan(int64_t N, int64_t K, int workers, int64_t* unit_begin_out, int* first_out, int* last_out) {
+  const int64_t k_tiles = (K + K_BK - 1) / K_BK, n_tiles = (N + K_BN - 1) / K_BN, units = k_tiles * n_tiles;
+  DTN_REQUIRE(N >= 1 && K >= 1 && workers >= 1 && workers <= units, DTN_ERR_INVALID,
+              "gemm: the skinny plan needs positive extents and between 1 and %lld workers", (long long)units);
+  if (unit_begin_out)
+    for (int w = 0; w <= workers; ++w) unit_begin_out[w] = skinny_first_unit(w, units, workers);
+  for (int64_t nt = 0; nt < n_tiles; ++nt) {
+    if (first_out) first_out[nt] = skinny_owner(nt * k_tiles, units, workers);
+    if (last_out) last_out[nt] = skinny_owner((nt + 1) * k_tiles - 1, units, workers);
+  }
+  return DTN_OK;
+}
+
 int gemm_skinny_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
                        int64_t ldc, void* workspace, cudaStream_t s) {
   return mode == DTN_GEMM_BF16X3 ? gemm_skinny_launch_mode<0>(A, B, C, M, N, K, lda, ldb, ldc, workspace, s)

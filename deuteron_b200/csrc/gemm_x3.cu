@@ -34,6 +34,7 @@ int gemm_skinny_launch(int mode, const float* A, const float* B, float* C, int64
                        int64_t ldc, void* workspace, cudaStream_t s);
 bool gemm_skinny_supported(const float* A, const float* B, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb);
 size_t gemm_skinny_workspace_bytes(int64_t N, int64_t K);
+int gemm_skinny_plan(int64_t N, int64_t K, int workers, int64_t* unit_begin_out, int* first_out, int* last_out);
 int gemm_small_launch(int mode, const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                       int64_t ldb, int64_t ldc, cudaStream_t s);
 bool gemm_fused_supported(int mode, const float* A, const float* B, int64_t N, int64_t K, int64_t lda, int64_t ldb);
@@ -1616,6 +1617,10 @@ int dtn_gemm_set_variant(int variant) {
   DTN_REQUIRE(variant >= 0 && variant <= 10, DTN_ERR_INVALID, "gemm: variant must be 0..10");
   dtn::g_gemm_variant = variant;
   return DTN_OK;
+}
+
+int dtn_gemm_skinny_plan(int64_t N, int64_t K, int workers, int64_t* unit_begin_out, int* first_out, int* last_out) {
+  return dtn::gemm_skinny_plan(N, K, workers, unit_begin_out, first_out, last_out);
 }
 
 int dtn_gemm_workspace_bytes(int mode, int64_t M, int64_t N, int64_t K, size_t* bytes_out) {

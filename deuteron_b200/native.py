@@ -56,6 +56,7 @@ _SIGNATURES = {
     'dtn_gemm_x3_static_status': [ct.POINTER(ct.c_int), _P],
     'dtn_gemm_tile_schedule': [_I64, _I64, _I, ct.POINTER(ct.c_uint32), _I, ct.POINTER(ct.c_int), ct.POINTER(ct.c_double),
                                ct.POINTER(ct.c_double)],
+    'dtn_gemm_skinny_plan': [_I64, _I64, _I, ct.POINTER(ct.c_int64), ct.POINTER(ct.c_int), ct.POINTER(ct.c_int)],
     'dtn_gemm_set_variant': [_I],
     'dtn_attention_f32': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _F, _P],
     'dtn_gqa_fwd': [_P, _P, _P, _P, _I64, _I64, _I64, _I64, _I64, _F, _I, _I64, _I64, _P],

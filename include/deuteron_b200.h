@@ -261,6 +261,14 @@ int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_ou
                            int* rounds_out /* host */, double* longest_out /* host */,
                            double* longest_uniform_out /* host */);
 
+/* How the streamed kernel for at most 16 rows (variant 10) cuts a product among `workers` CTAs: host arithmetic only.
+ * Work units are 64 k-rows x 128 columns of B, numbered column block by column block with k fastest; CTA w takes units
+ * [unit_begin_out[w], unit_begin_out[w + 1]) (workers + 1 entries). first_out[c] .. last_out[c] are the CTAs that
+ * contribute partial sums to column block c (ceil(N / 128) entries each); they are added in that order. Any output
+ * pointer may be NULL. 1 <= workers <= number of units. No reference counterpart. */
+int dtn_gemm_skinny_plan(int64_t N, int64_t K, int workers, int64_t* unit_begin_out /* host */, int* first_out /* host */,
+                         int* last_out /* host */);
+
 /* Selects the tensor-core GEMM variant for the calling host thread (other threads keep their own
  * selection, initially 0; for experiments and tests):
  *   0 = automatic, 1 = one-CTA 128x128 tile, 2 = one-CTA 128x256 tile, 3 = two-CTA 256x256 tile,

@@ -174,3 +174,35 @@ def test_tile_schedule_covers_the_output_once_and_balances_the_pairs():
     # an eighth of it: 1.73 rounds; nothing cheaper than two rounds of 256-wide tiles exists, the plain walk stays;
     # large outputs keep it too
     assert schedule(8192, 1024)[0] is None and schedule(8192, 8192)[0] is None and schedule(8192, 4096)[0] is None
+
+
+def test_skinny_plan_gives_every_cta_the_same_share_and_orders_the_contributors():
+    """The streamed kernel for at most 16 rows: units of 64 k-rows x 128 columns, one contiguous range per CTA."""
+    import ctypes as ct
+    from deuteron_b200 import native
+
+    def plan(n, k, workers):
+        k_tiles, n_tiles = (k + 63) // 64, (n + 127) // 128
+        begin, first, last = (ct.c_int64 * (workers + 1))(), (ct.c_int * n_tiles)(), (ct.c_int * n_tiles)()
+        native.call('dtn_gemm_skinny_plan', n, k, workers, begin, first, last)
+        return k_tiles, n_tiles, list(begin), list(first), list(last)
+
+    for n, k, workers in ((8192, 8192, 148), (4100, 2052, 148), (128, 65536, 148), (65536, 64, 148), (2084, 1028, 148), (8192, 8192, 132), (256, 128, 4)):
+        k_tiles, n_tiles, begin, first, last = plan(n, k, workers)
+        units = k_tiles * n_tiles
+        assert begin[0] == 0 and begin[-1] == units
+        sizes = [begin[w + 1] - begin[w] for w in range(workers)]
+        assert min(sizes) >= 1 and max(sizes) - min(sizes) <= 1          # equal shares: every SM reads the same bytes
+        owner = np.repeat(np.arange(workers), sizes)                      # CTA of every unit
+        slots = set()
+        for block in range(n_tiles):
+            inside = owner[block * k_tiles:(block + 1) * k_tiles]
+            assert first[block] == inside[0] and last[block] == inside[-1]
+            assert sorted(set(inside.tolist())) == list(range(first[block], last[block] + 1))   # contiguous, in order
+            for w in range(first[block], last[block] + 1):
+                slots.add((w + block, w, block))
+        # the workspace slot of a (CTA, column block) pair is CTA + block: no two pairs share one, none beyond workers + blocks
+        keys = [slot for slot, _, _ in slots]
+        assert len(keys) == len(set(keys)) and max(keys) < workers + n_tiles
+    with pytest.raises(ValueError):
+        plan(128, 64, 2)   # one unit cannot be shared by two CTAs
