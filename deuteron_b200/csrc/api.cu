@@ -124,6 +124,18 @@ int dtn_capture_end(void* stream, int* kernels_out, int* max_registers_out, int*
   return DTN_OK;
 }
 
+/* A block of `height` rows of `width_bytes` each between host and device memory with different row pitches (a column
+ * block of a row-major matrix), asynchronous on `stream` when the host side is page-locked: one cudaMemcpy2DAsync. */
+int dtn_copy_block(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t height, int to_device,
+                   void* stream) {
+  if (width_bytes == 0 || height == 0) return DTN_OK;
+  DTN_REQUIRE(dst != nullptr && src != nullptr && dst_pitch >= width_bytes && src_pitch >= width_bytes, DTN_ERR_INVALID,
+              "copy_block: null pointer or pitch below the row width");
+  DTN_CUDA_CHECK(cudaMemcpy2DAsync(dst, dst_pitch, src, src_pitch, width_bytes, height,
+                                   to_device ? cudaMemcpyHostToDevice : cudaMemcpyDeviceToHost, dtn::as_stream(stream)));
+  return DTN_OK;
+}
+
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------

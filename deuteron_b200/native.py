@@ -38,6 +38,7 @@ _SIGNATURES = {
     'dtn_last_error': [ct.c_char_p, ct.c_size_t],
     'dtn_device_status': [ct.POINTER(ct.c_int), _P],
     'dtn_selftest_wait_timeout': [ct.c_longlong, _P],
+    'dtn_copy_block': [_P, ct.c_size_t, _P, ct.c_size_t, ct.c_size_t, ct.c_size_t, _I, _P],
     'dtn_capture_begin': [_P],
     'dtn_capture_end': [_P, ct.POINTER(ct.c_int), ct.POINTER(ct.c_int), ct.POINTER(ct.c_int), ct.POINTER(ct.c_int)],
     'dtn_add_f32': [_P, _P, _P, _I64, _P],

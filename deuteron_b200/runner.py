@@ -257,64 +257,120 @@ class LocalRunner:
         return results
 
     def _gemm_row_blocks(self, plan: Any) -> int:
-        """Number of equal row blocks a large compensated GEMM is walked in when its operands come from
-        the host, so that copies and products overlap; 1 = no blocking."""
-        m, n, k = plan.params['m'], plan.params['n'], plan.params['k']
+        """Number of row blocks a large compensated GEMM is walked in when its operands come from the host, so
+        that copies and products overlap; 1 = no blocking."""
+        return len(self._gemm_row_plan(plan))
+
+    @staticmethod
+    def _gemm_row_plan(plan: Any) -> list[int]:
+        """Rows of every block of A, in order: eighths (quarters, halves) of the rows, except that the last of them is
+        cut into a half and two quarters: the host link is the bottleneck, every product hides behind the copy of the
+        next block, and what stays exposed at the end is the last block's product and its way back to the host, so
+        that block should be small (8192^3: 11.82 -> 11.55 ms). One block = no blocking."""
+        m, k = plan.params['m'], plan.params['k']
         if plan.params['mode'] in ('f32', 'f32_splitk') or m * k * 4 < (32 << 20):
-            return 1
+            return [m]
         for blocks in (8, 4, 2):
             if m % blocks == 0 and (m // blocks) % 256 == 0 and (m // blocks) >= 512:
-                return blocks
-        return 1
+                rows = m // blocks
+                tail = [rows // 2, rows // 4, rows // 4] if rows % 1024 == 0 else [rows]
+                return [rows] * (blocks - 1) + tail
+        return [m]
+
+    @staticmethod
+    def _gemm_column_plan(n: int) -> list[int]:
+        """Column blocks of B and C for the host-fed pipeline. One block: B goes to the device whole, before A.
+        Feeding B by column blocks (first block, then A by row blocks, then the other blocks against all of A) lets
+        the result start its way back after an eighth of the bytes instead of half of them, but measured slower on
+        this host (8192^3: 12.2-13.6 ms against 11.6 ms for quarters, halves and graded blocks alike): the link is
+        bound by the 512 MB going in, and every byte coming back at the same time slows those down.
+        DTN_E2E_COLUMNS=w1,w2,... (widths summing to n) selects a cut for measurements."""
+        import os
+        forced = os.environ.get('DTN_E2E_COLUMNS')
+        if forced:
+            widths = [int(x) for x in forced.split(',')]
+            if sum(widths) == n and all(w > 0 for w in widths):
+                return widths
+        return [n]
 
     def _execute_gemm_blocks(self, plan: Any, tensors: dict, pointers: dict, workspace: Any, arrays: dict, host_out: np.ndarray,
                              blocks: int) -> None:
-        """Host-fed compensated GEMM as a three-stream pipeline over row blocks of A and C.
+        """Host-fed compensated GEMM as a three-stream pipeline over row blocks of A and column blocks of B and C.
 
-        B goes to the device first and is split once; then, block by block, A_i is copied in on the
-        copy-in stream while A_(i-1) is split and multiplied on the compute stream and C_(i-2) returns to
-        the host on the copy-out stream. All copies are contiguous. Per-element arithmetic (and so every
-        bit of the result) is the same as in the one-launch path.
+        The host link is the bottleneck (for an 8192^3 product 805 MB cross it against 2 ms of arithmetic), so the
+        order of the copies is what matters: nothing can be multiplied before a column block of B is on the device and
+        nothing can return before something is multiplied. The first column block of B goes first, then A row block
+        by row block, each multiplied against that column block as it lands (its part of C returns at once); then the
+        remaining column blocks of B, each multiplied against all of A, which is resident by then. The copy-in stream
+        is never idle, the result's way back overlaps it from the first quarter of B on, and the last blocks are small.
+        Per-element arithmetic (and so every bit of the result) is the same as in the one-launch path: a block of C
+        is the product of A's rows and B's columns over the whole of k.
         """
         torch = self._torch
         m, n, k = plan.params['m'], plan.params['n'], plan.params['k']
         mode = native.GEMM_MODES[plan.params['mode']]
-        rows = m // blocks
+        row_plan = self._gemm_row_plan(plan)
+        row_starts = [sum(row_plan[:i]) for i in range(len(row_plan))]
+        column_plan = self._gemm_column_plan(n)
+        column_starts = [sum(column_plan[:j]) for j in range(len(column_plan))]
         left_name, right_name, out_name = plan.buffers['left'][0], plan.buffers['right'][0], plan.buffers['out'][0]
         compute, copy_in, copy_out = self.stream, self._copy_in, self._copy_out
         copy_in.wait_stream(compute)       # earlier launches may still read the operand buffers
-        left_host = torch.from_numpy(np.ascontiguousarray(arrays[left_name]).reshape(-1).view(np.uint8))
-        right_host = torch.from_numpy(np.ascontiguousarray(arrays[right_name]).reshape(-1).view(np.uint8))
-        out_host = torch.from_numpy(host_out.reshape(-1).view(np.uint8))
-        block_in, block_out = rows * k * 4, rows * n * 4
-        ready = []
-        with torch.cuda.stream(copy_in):
-            tensors[right_name][:right_host.numel()].copy_(right_host, non_blocking=True)
-            right_ready = torch.cuda.Event()
-            right_ready.record(copy_in)
-            for i in range(blocks):
-                tensors[left_name][i * block_in:(i + 1) * block_in].copy_(left_host[i * block_in:(i + 1) * block_in], non_blocking=True)
-                event = torch.cuda.Event()
-                event.record(copy_in)
-                ready.append(event)
+        left = np.ascontiguousarray(arrays[left_name])
+        right = np.ascontiguousarray(arrays[right_name])
+        left_host, right_host, out_host = left.ctypes.data, right.ctypes.data, host_out.ctypes.data
+        keep = (left, right)               # the host arrays stay alive until the copies have been issued and waited for
+        row_in, row_b, row_out = k * 4, n * 4, n * 4
         ws_ptr, ws_bytes = workspace
-        compute.wait_event(right_ready)
-        # B is split once, on its own (1|4: split, keep A), before any block: every block then runs 3|8 (split A, keep
-        # B, multiply), which always takes the plane-reading kernels. A plain phase 3 on the first block could pick a
-        # single-kernel form that writes no planes, and the later blocks would multiply by whatever the workspace held.
-        native.call('dtn_gemm_x3_phase', mode, pointers[left_name], pointers[right_name], pointers[out_name], rows, n, k, k, n, n,
-                    ws_ptr, ws_bytes, 1 | 4, compute.cuda_stream)
-        for i in range(blocks):
-            compute.wait_event(ready[i])
-            native.call('dtn_gemm_x3_phase', mode, pointers[left_name] + i * block_in, pointers[right_name],
-                        pointers[out_name] + i * block_out, rows, n, k, k, n, n, ws_ptr, ws_bytes, 3 | 8,
-                        compute.cuda_stream)
+
+        def b_columns_in(first: int, width: int):
+            native.call('dtn_copy_block', pointers[right_name] + first * 4, row_b, right_host + first * 4, row_b, width * 4, k, 1,
+                        copy_in.cuda_stream)
+            event = torch.cuda.Event()
+            event.record(copy_in)
+            return event
+
+        def c_block_out(first_row: int, rows: int, first_col: int, width: int) -> None:
             done = torch.cuda.Event()
             done.record(compute)
             copy_out.wait_event(done)
-            with torch.cuda.stream(copy_out):
-                out_host[i * block_out:(i + 1) * block_out].copy_(tensors[out_name][i * block_out:(i + 1) * block_out], non_blocking=True)
+            offset = first_row * row_out + first_col * 4
+            native.call('dtn_copy_block', out_host + offset, row_out, pointers[out_name] + offset, row_out, width * 4, rows, 0,
+                        copy_out.cuda_stream)
+
+        def product(first_row: int, rows: int, first_col: int, width: int, phase: int) -> None:
+            native.call('dtn_gemm_x3_phase', mode, pointers[left_name] + first_row * row_in, pointers[right_name] + first_col * 4,
+                        pointers[out_name] + first_row * row_out + first_col * 4, rows, width, k, k, n, n, ws_ptr, ws_bytes, phase,
+                        compute.cuda_stream)
+
+        # first column block of B, then A by row blocks
+        first_ready = b_columns_in(0, column_plan[0])
+        a_ready = []
+        for first, rows in zip(row_starts, row_plan):
+            native.call('dtn_copy_block', pointers[left_name] + first * row_in, row_in, left_host + first * row_in, row_in, row_in, rows, 1,
+                        copy_in.cuda_stream)
+            event = torch.cuda.Event()
+            event.record(copy_in)
+            a_ready.append(event)
+        later_ready = [b_columns_in(first, width) for first, width in zip(column_starts[1:], column_plan[1:])]
+        compute.wait_event(first_ready)
+        # B's first block is split once, on its own (1|4: split, keep A), before any row block: every row block then
+        # runs 3|8 (split A, keep B, multiply), which always takes the plane-reading kernels. A plain phase 3 on the
+        # first block could pick a single-kernel form that writes no planes, and the later blocks would multiply by
+        # whatever the workspace held.
+        product(0, row_plan[0], 0, column_plan[0], 1 | 4)
+        for i, (first, rows) in enumerate(zip(row_starts, row_plan)):
+            compute.wait_event(a_ready[i])
+            product(first, rows, 0, column_plan[0], 3 | 8)
+            c_block_out(first, rows, 0, column_plan[0])
+        # the other column blocks against all of A
+        for ready, first, width in zip(later_ready, column_starts[1:], column_plan[1:]):
+            compute.wait_event(ready)
+            product(0, m, first, width, 3)
+            c_block_out(0, m, first, width)
         compute.wait_stream(copy_out)      # a synchronize of the runner's stream now covers the whole call
+        compute.wait_stream(copy_in)
+        self._held_host_arrays = keep      # released by the next call; the copies above may still be reading them
 
     def run_kernel(self, launch: Any, compiled: Any, produced: Any = None, *, warmup: Any = 10, iters: Any = 100,
                    samples: Any = 7) -> dict[str, Any]:

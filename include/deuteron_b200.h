@@ -261,6 +261,13 @@ int dtn_gemm_tile_schedule(int64_t M, int64_t N, int pairs, uint32_t* entries_ou
                            int* rounds_out /* host */, double* longest_out /* host */,
                            double* longest_uniform_out /* host */);
 
+/* Copies `height` rows of `width_bytes` each between host and device memory whose rows lie `src_pitch` / `dst_pitch`
+ * bytes apart (a column block of a row-major matrix): one cudaMemcpy2DAsync on `stream`, host to device when
+ * to_device is non-zero, else device to host. The host runner uses it to feed B and return C by column blocks
+ * (the copies the reference's runner makes whole, benchmark.py:225-235,269-274). */
+int dtn_copy_block(void* dst, size_t dst_pitch, const void* src, size_t src_pitch, size_t width_bytes, size_t height, int to_device,
+                   void* stream);
+
 /* How the streamed kernel for at most 16 rows (variant 10) cuts a product among `workers` CTAs: host arithmetic only.
  * Work units are 64 k-rows x 128 columns of B, numbered column block by column block with k fastest; CTA w takes units
  * [unit_begin_out[w], unit_begin_out[w + 1]) (workers + 1 entries). first_out[c] .. last_out[c] are the CTAs that

@@ -695,6 +695,26 @@ def test_stream_kernel_equals_the_plain_tiles_bit_for_bit(cuda, mode, m, n, k):
     assert bool(cuda.equal(automatic, plain))
 
 
+def test_execute_feeding_b_by_column_blocks_changes_no_bit(cuda, runner, monkeypatch):
+    # the host-fed pipeline with B cut into column blocks (first block, A by row blocks, the other blocks against all
+    # of A; strided copies both ways) and with the default (B whole, the last row block cut small)
+    m, n, k = 4096, 2048, 2048
+    graph, meta = schedules.matmul_example(m, n, k)
+    compiled = compile_kernel(graph, meta, options=Options(contraction_precision='bf16x3'))
+    left, right = runner.pinned((m, k), np.float32), runner.pinned((k, n), np.float32)
+    left[:], right[:] = R.seeded_uniform(7, (m, k)), R.seeded_uniform(11, (k, n))
+    resident = ops.gemm(to_device(cuda, left), to_device(cuda, right), 'bf16x3').cpu().numpy()
+    for columns in (None, '1024,512,256,256', '768,1280'):
+        if columns is None:
+            monkeypatch.delenv('DTN_E2E_COLUMNS', raising=False)
+        else:
+            monkeypatch.setenv('DTN_E2E_COLUMNS', columns)
+        result = runner.pinned((m, n), np.float32)
+        result[:] = float('nan')
+        produced = runner.execute(compiled, {'left': left, 'right': right}, {'result': result})['result']
+        np.testing.assert_array_equal(produced, resident)
+
+
 def test_execute_with_a_tall_left_operand_and_a_narrow_right_one(cuda, runner):
     # 8 row blocks of 1024 x 128 x 1024: each block alone is small enough for the single-kernel GEMM, which writes no
     # operand planes; the pipeline must still split B before the first block and multiply every block by those planes
