@@ -8,6 +8,7 @@ int gqa_f32_launch(const void* q, const void* k, const void* v, float* out, int6
 int gqa_tc_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
                   int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s);
 bool gqa_tc_supported(int64_t S, int64_t D, int storage);
+bool gqa_tc_ragged_supported(int64_t S, int64_t D, int storage);
 int gqa_tc_pair_launch(const void* q, const void* k, const void* v, float* out, int64_t B, int64_t Hq, int64_t Hkv,
                        int64_t S, float scale, int64_t gb, int64_t ge, int split, cudaStream_t s);
 bool gqa_tc_pair_supported(int64_t S, int64_t D, int storage);
@@ -43,13 +44,14 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
   DTN_REQUIRE(S < (1LL << 31), DTN_ERR_UNSUPPORTED, "gqa: sequence length must fit 31 bits");
   cudaStream_t s = as_stream(stream);
   int variant = g_gqa_variant;
-  // Two softmax warpgroups per tile with the first half of a thread's scores kept in registers are the default
+  // Two softmax warpgroups per tile with the first half of a thread's scores kept in registers are the default, for
+  // any sequence length from 256 up (it masks missing keys and clips missing rows; the other forms want multiples)
   // (4096 keys: 997 against 959 TFLOP/s for the form that reads the scores twice, 2048 keys: 890 against 847, 512
   // keys: equal; alternating runs in one process, identical output bits).
-  if (variant == 0) variant = gqa_tc_supported(S, D, storage) ? 7 : 1;
+  if (variant == 0) variant = gqa_tc_ragged_supported(S, D, storage) ? 7 : 1;
   if (variant == 7) {   // two softmax warpgroups per tile, scores kept in registers between the two passes
-    DTN_REQUIRE(gqa_tc_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
-                "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S a multiple of 256");
+    DTN_REQUIRE(gqa_tc_ragged_supported(S, D, storage), DTN_ERR_UNSUPPORTED,
+                "gqa: the tensor-core kernel needs f16 storage, head_dim 128 and S of at least 256");
     return gqa_tc_launch(q, k, v, out, B, Hq, Hkv, S, scale, group_begin, group_end, 3, s);
   }
   if (variant == 6) {   // all sixteen softmax warps on one tile at a time

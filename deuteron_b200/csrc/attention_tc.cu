@@ -70,8 +70,11 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #endif
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qblocks = S / (2 * A_BM);
-  const int num_kv = S / A_BN;
+  // S need not be a multiple of the tile sizes: the tensor maps are [heads][S][128], so rows past a head's end load
+  // as zeros and are dropped by the output store; the softmax masks the keys that do not exist (KEEP form only: the
+  // other forms store their output with plain stores and take only multiples of 256)
+  const int qblocks = (S + 2 * A_BM - 1) / (2 * A_BM);
+  const int num_kv = (S + A_BN - 1) / A_BN;
   const int my_items = ((int)blockIdx.x < total_items) ? (total_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
   const int total_steps = my_items * num_kv;
 
@@ -131,7 +134,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (KEEP && it > 0 && j == 1 && !ptx::mbar_wait(staged(0), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1400); ok = false; break; }
           ptx::mbar_expect_tx(k_full(s), A_TILE_BYTES);
           for (int h = 0; h < 2; ++h)
-            ptx::tma_load_2d(k_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_k, h * 64, item.kv_row0 + j * A_BN, k_full(s));
+            ptx::tma_load_3d(k_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_k, h * 64, j * A_BN, item.kv_head, k_full(s));
           if (j == 0) {
             // this item's queries, right after its first keys: a buffer is free once the previous item's last score
             // product has read it, which is about one step before the first product of this item wants it. The tiles
@@ -140,20 +143,20 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               if (it > 0 && !ptx::mbar_wait(q_empty(t), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1300); ok = false; break; }
               ptx::mbar_expect_tx(q_full(t), A_TILE_BYTES);
               for (int h = 0; h < 2; ++h)
-                ptx::tma_load_2d(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES, &tm_q, h * 64, item.q_row0 + t * A_BM, q_full(t));
+                ptx::tma_load_3d(q_addr + t * A_TILE_BYTES + h * A_HALF_BYTES, &tm_q, h * 64, item.q_row + t * A_BM, item.q_head, q_full(t));
             }
             if (!ok) break;
             if (it + 1 < my_items) {
               const AttnItem next = attn_item((int)blockIdx.x + (it + 1) * (int)gridDim.x, qblocks, Hq, Hkv, S, group_begin);
               for (int t = 0; t < 2; ++t)
-                for (int h = 0; h < 2; ++h) ptx::tma_prefetch_2d(&tm_q, h * 64, next.q_row0 + t * A_BM);
+                for (int h = 0; h < 2; ++h) ptx::tma_prefetch_3d(&tm_q, h * 64, next.q_row + t * A_BM, next.q_head);
             }
           }
           if (!ptx::mbar_wait(v_empty(s), ph ^ 1u, abort_flag)) { atomicExch(status, 0x1200); ok = false; break; }
           if (KEEP && it > 0 && j == 1 && !ptx::mbar_wait(staged(1), (uint32_t)(it - 1) & 1u, abort_flag)) { atomicExch(status, 0x1500); ok = false; break; }
           ptx::mbar_expect_tx(v_full(s), A_TILE_BYTES);
           for (int h = 0; h < 2; ++h)
-            ptx::tma_load_2d(v_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_v, h * 64, item.kv_row0 + j * A_BN, v_full(s));
+            ptx::tma_load_3d(v_addr + s * A_TILE_BYTES + h * A_HALF_BYTES, &tm_v, h * 64, j * A_BN, item.kv_head, v_full(s));
         }
       }
     }
@@ -279,6 +282,7 @@ gqa_tc_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     role.out_map = &tm_out;
     role.out_stage = (t == 0 ? k_addr : v_addr) + (uint32_t)(warp & 7) * 4096u;   // SPLIT == 2: the tile's eight warps, 4 KiB each
     role.staged_bar = staged(t);
+    role.valid_last = S - (num_kv - 1) * A_BN;
     role.stage_base = stage_base;
     role.abort_flag = abort_flag;
     role.status = status;
@@ -339,36 +343,39 @@ static EncodeTiledFn attn_encode_fn() {
   return fn;
 }
 
-// [rows, 128] f16 matrix, box = 64 columns (128 bytes) x 128 rows, 128-byte swizzle.
-static int make_rows_map(CUtensorMap* map, const void* base, int64_t rows) {
+// [heads][S][128] f16, box = 64 columns (128 bytes) x 128 rows of one head, 128-byte swizzle.
+static int make_rows_map(CUtensorMap* map, const void* base, int64_t S, int64_t heads) {
   EncodeTiledFn enc = attn_encode_fn();
   DTN_REQUIRE(enc != nullptr, DTN_ERR_CUDA, "gqa: cuTensorMapEncodeTiled is not available");
-  const cuuint64_t dims[2] = {(cuuint64_t)A_D, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)A_D * 2};
-  const cuuint32_t box[2] = {64, 128};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const cuuint64_t dims[3] = {(cuuint64_t)A_D, (cuuint64_t)S, (cuuint64_t)heads};
+  const cuuint64_t strides[2] = {(cuuint64_t)A_D * 2, (cuuint64_t)S * A_D * 2};
+  const cuuint32_t box[3] = {64, 128, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   DTN_REQUIRE(r == CUDA_SUCCESS, DTN_ERR_CUDA, "gqa: cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   return DTN_OK;
 }
 
-// [rows, 128] FP32 output, box = 32 columns (128 bytes) x 32 rows, 128-byte swizzle.
-static int make_output_map(CUtensorMap* map, const void* base, int64_t rows) {
+// [heads][S][128] FP32 output, box = 32 columns (128 bytes) x 32 rows of one head, 128-byte swizzle.
+static int make_output_map(CUtensorMap* map, const void* base, int64_t S, int64_t heads) {
   EncodeTiledFn enc = attn_encode_fn();
   DTN_REQUIRE(enc != nullptr, DTN_ERR_CUDA, "gqa: cuTensorMapEncodeTiled is not available");
-  const cuuint64_t dims[2] = {(cuuint64_t)A_D, (cuuint64_t)rows};
-  const cuuint64_t strides[1] = {(cuuint64_t)A_D * 4};
-  const cuuint32_t box[2] = {32, 32};
-  const cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), dims, strides, box, estr,
+  const cuuint64_t dims[3] = {(cuuint64_t)A_D, (cuuint64_t)S, (cuuint64_t)heads};
+  const cuuint64_t strides[2] = {(cuuint64_t)A_D * 4, (cuuint64_t)S * A_D * 4};
+  const cuuint32_t box[3] = {32, 32, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, const_cast<void*>(base), dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   DTN_REQUIRE(r == CUDA_SUCCESS, DTN_ERR_CUDA, "gqa: cuTensorMapEncodeTiled (output) failed with CUresult %d", (int)r);
   return DTN_OK;
 }
 
+// The tensor-core kernels take f16 storage and head_dim 128. Sequence length: a multiple of 256, or, for the form with
+// kept scores (which masks missing keys and stores through a tensor map), anything from 256 up.
+bool gqa_tc_ragged_supported(int64_t S, int64_t D, int storage) { return storage == DTN_STORAGE_F16 && D == A_D && S >= 2 * A_BM; }
 bool gqa_tc_supported(int64_t S, int64_t D, int storage) {
   return storage == DTN_STORAGE_F16 && D == A_D && S >= 2 * A_BM && S % (2 * A_BM) == 0;
 }
@@ -378,11 +385,11 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
                            int64_t S, float scale, int64_t gb, int64_t ge, cudaStream_t s) {
   CUtensorMap mq, mk, mv;
   int rc;
-  if ((rc = make_rows_map(&mq, q, B * Hq * S))) return rc;
-  if ((rc = make_rows_map(&mk, k, B * Hkv * S))) return rc;
-  if ((rc = make_rows_map(&mv, v, B * Hkv * S))) return rc;
+  if ((rc = make_rows_map(&mq, q, S, B * Hq))) return rc;
+  if ((rc = make_rows_map(&mk, k, S, B * Hkv))) return rc;
+  if ((rc = make_rows_map(&mv, v, S, B * Hkv))) return rc;
   CUtensorMap mo = mq;   // only the KEEP form stores through a tensor map
-  if (KEEP && (rc = make_output_map(&mo, out, B * Hq * S))) return rc;
+  if (KEEP && (rc = make_output_map(&mo, out, S, B * Hq))) return rc;
   static thread_local int attr_dev = -1;
   int dev = 0;
   DTN_CUDA_CHECK(cudaGetDevice(&dev));
@@ -392,7 +399,7 @@ static int gqa_tc_launch_t(const void* q, const void* k, const void* v, float* o
   }
   int* status = device_status_word();
   DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "gqa: could not allocate the device status word");
-  const int64_t items = (ge - gb) * (Hq / Hkv) * (S / (2 * A_BM));
+  const int64_t items = (ge - gb) * (Hq / Hkv) * ((S + 2 * A_BM - 1) / (2 * A_BM));
   DTN_REQUIRE(items < (1LL << 31) && B * Hq * S < (1LL << 31), DTN_ERR_UNSUPPORTED, "gqa: too many query rows for one launch");
   // One CTA per SM walks the items round-robin; DTN_GQA_PERSISTENT=0 launches one CTA per item instead.
   static const bool persistent = [] {

@@ -208,6 +208,8 @@ __device__ __forceinline__ bool exchange_through_barrier(volatile float2* mine, 
 struct AttnItem {
   int q_row0;     // first query row in the [B*Hq*S, D] view
   int kv_row0;    // first key row in the [B*Hkv*S, D] view
+  int q_head, q_row;   // the same as (query head of the batch, row inside it)
+  int kv_head;         // key/value head of the batch
 };
 __device__ __forceinline__ AttnItem attn_item(int item, int qblocks, int Hq, int Hkv, int S, int group_begin,
                                              int item_rows = 2 * A_BM) {
@@ -219,6 +221,9 @@ __device__ __forceinline__ AttnItem attn_item(int item, int qblocks, int Hq, int
   AttnItem it;
   it.q_row0 = (b * Hq + hq) * S + qb * item_rows;
   it.kv_row0 = (b * Hkv + hkv) * S;
+  it.q_head = b * Hq + hq;
+  it.q_row = qb * item_rows;
+  it.kv_head = b * Hkv + hkv;
   return it;
 }
 
@@ -233,10 +238,11 @@ struct SoftmaxRole {
   bool remote_arrive;
   volatile float2* xchg;     // [2 tiles][2 shares][128 rows]
   uint32_t xbar;             // barrier the two partner warps of this warp's (tile, row quarter) exchange through (KEEP form)
-  const CUtensorMap* out_map;   // KEEP form: the output as [rows][128] FP32, boxes of 32 columns x 32 rows, 128-byte swizzle
+  const CUtensorMap* out_map;   // KEEP form: the output as [heads][S][128] FP32, boxes of 32 columns x 32 rows, 128-byte swizzle
   uint32_t out_stage;           // KEEP form: this warp's 4 KiB staging block for its output, in ring slot 0 of the keys (tile 0) or
                                 // of the values (tile 1); the block of the slot the item's last step used is A_TILE_BYTES further
   uint32_t staged_bar;          // KEEP form: arrives once the staging block has been read (the slot may be loaded again)
+  int valid_last;               // KEEP form: keys of the item's last step that exist (128 unless S is not a multiple of 128)
   float* stage_base;         // 1 KiB per softmax warp
   volatile int* abort_flag;
   int* status;
@@ -284,6 +290,7 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
   // worked out during its first step, after the probabilities are handed over, when this warp would wait anyway.
   int j = -1, it = 0;
   float* row_out = nullptr;
+  int out_head = 0, out_first_row = 0;
   bool release_pending = false;
   for (int g = 0; g < total_steps; ++g) {
     if (++j == num_kv) {
@@ -304,6 +311,7 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
     // pass 1: row maximum of the raw scores (three-input max: two scores per instruction). With two warpgroups per
     // tile a thread owns 64 scores: both loads are issued together and the scores stay in registers for pass 2.
     float mx = -INFINITY;
+    bool masked = false;
     uint32_t kept[kKeep ? 64 : 1];
     if constexpr (kKeep) {
       uint32_t (&lo_half)[32] = *reinterpret_cast<uint32_t (*)[32]>(kept);
@@ -311,6 +319,14 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
       ptx::tmem_ld_32x32(s_tmem + (uint32_t)(c0 * 32), lo_half);
       ptx::tmem_ld_32x32(s_tmem + (uint32_t)((c0 + 1) * 32), hi_half);
       ptx::tmem_ld_wait();
+      // keys past the end of the sequence (the item's last step when S is not a multiple of 128; their K rows were
+      // loaded as zeros): their scores become -inf, so they take no part in the maximum and their probabilities are 0
+      masked = j == num_kv - 1 && R.valid_last < A_BN;
+      if (masked) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i)
+          if (c0 * 32 + i >= R.valid_last) kept[i] = 0xff800000u;
+      }
 #pragma unroll
       for (int i = 0; i < 64; i += 2) mx = max3(mx, __uint_as_float(kept[i]), __uint_as_float(kept[i + 1]));
     } else {
@@ -375,6 +391,11 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
         if (piece == 1) ptx::tmem_ld_32x16(s_tmem + (uint32_t)((c0 + 1) * 32 + 16), second + 16);
         if (piece == 2) {
           ptx::tmem_ld_wait();
+          if (masked) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i)
+              if ((c0 + 1) * 32 + i >= R.valid_last) second[i] = 0xff800000u;
+          }
           mass += sums.x + sums.y;   // per 32 scores, like the form that reads the scores twice: the same bits
           sums = make_float2(0.f, 0.f);
         }
@@ -456,6 +477,8 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
     if (j == 0) {
       const AttnItem item = attn_item(R.first_item + it * R.item_stride, R.qblocks, R.Hq, R.Hkv, R.S, R.group_begin, R.item_rows);
       row_out = out + ((int64_t)item.q_row0 + R.rows_before_tile + row_in_tile) * A_D;
+      out_head = item.q_head;
+      out_first_row = item.q_row + R.rows_before_tile + quarter * 32;   // first of this warp's rows inside the head
     }
     if (j != num_kv - 1) continue;
 
@@ -485,7 +508,6 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
       // load/store unit to do, about forty instructions per block. The producer loads the slot again once every warp
       // of the tile has reported that its staging block has been read.
       const uint32_t out_stage = R.out_stage + (uint32_t)(g & 1) * A_TILE_BYTES;
-      const int out_row = (int)((row_out - out) / A_D) - lane;   // first of this warp's rows
       ATRACE2(g, 0);
 #pragma unroll 1
       for (int c = c0; c < c0 + kChunks; ++c) {
@@ -508,7 +530,7 @@ __device__ __forceinline__ void softmax_role(const SoftmaxRole& R, int warp, int
         ptx::fence_proxy_async_smem();
         __syncwarp();
         if (lane == 0) {
-          ptx::tma_store_2d(R.out_map, out_stage, c * 32, out_row);
+          ptx::tma_store_3d(R.out_map, out_stage, c * 32, out_first_row, out_head);   // rows past the sequence's end are dropped
           ptx::bulk_commit_group();
         }
         ATRACE2(g, 3 + 3 * (c - c0));

@@ -315,9 +315,12 @@ int dtn_gqa_fwd(const void* q, const void* k, const void* v, float* out, int64_t
 
 /* Selects the attention kernel for the calling host thread: 0 = automatic, 1 = FP32 CUDA-core kernel,
  * 2 = tensor-core kernel (f16 storage, D = 128, S a multiple of 256), 3 = the same with two
- * softmax warpgroups per query tile (the automatic choice where it applies), 4 and 5 = the
- * CTA-pair form of 2 and 3 (S a multiple of 512; same results, measured slower, kept for comparison),
- * 6 = variant 3's shape with all sixteen softmax warps serving one tile at a time (measured slower too).
+ * softmax warpgroups per query tile, 4 and 5 = the CTA-pair form of 2 and 3 (S a multiple of 512; same results,
+ * measured slower, kept for comparison), 6 = variant 3's shape with all sixteen softmax warps serving one tile at a
+ * time (measured slower too), 7 = variant 3 with half of a thread's scores kept in registers between the maximum and
+ * the probabilities and the output written by TMA stores: the automatic choice for f16 storage, D = 128 and any
+ * S >= 256 (keys past the end of a sequence are masked, rows past it are neither read nor written: the tensor maps
+ * are per head). Variants 3 and 7 give the same bits.
  * No reference counterpart. */
 int dtn_gqa_set_variant(int variant);
 
