@@ -64,8 +64,14 @@ __device__ __forceinline__ void skinny_split_bf16(float a, float b, uint32_t& hi
   __nv_bfloat162 l = __floats2bfloat162_rn(ra, rb);
   lo = *reinterpret_cast<uint32_t*>(&l);
 }
+// hi = rna_tf32(v), lo = rna_tf32(v - hi). The high part is rounded with integer arithmetic: adding half a tf32 unit
+// to the bit pattern and clearing the thirteen low bits is round-to-nearest, ties away from zero, and equals
+// cvt.rna.tf32.f32 on every one of the 2^32 inputs except NaNs (checked exhaustively on the GPU) -- and the
+// conversion instruction runs on a slow pipe, which is what bounds the tf32 form of this kernel. A NaN may come out
+// of the integer form as a zero, so the residual, which is NaN whenever v is NaN or infinite, keeps the conversion
+// instruction: its NaN reaches every product of the element, as it does with both parts converted.
 __device__ __forceinline__ void skinny_split_tf32(float v, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
+  hi = (__float_as_uint(v) + 0x1000u) & 0xFFFFE000u;
   const float rest = v - __uint_as_float(hi);
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
 }

@@ -67,8 +67,11 @@ __device__ __forceinline__ void split_bf16_pair(float a, float b, uint32_t& hi, 
       : "r"(hi), "f"(a), "f"(b));
   lo = pack_bf16(ra, rb);
 }
+// The high part is rounded with integer arithmetic (half a tf32 unit added to the bit pattern, thirteen low bits
+// cleared: equal to cvt.rna.tf32.f32 on all 2^32 inputs but NaNs, and not on the slow conversion pipe); the residual,
+// which is NaN whenever v is NaN or infinite, keeps the conversion instruction, so a NaN still reaches every product.
 __device__ __forceinline__ void split_tf32(float v, uint32_t& hi, uint32_t& lo) {
-  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(hi) : "f"(v));
+  hi = (__float_as_uint(v) + 0x1000u) & 0xFFFFE000u;
   const float rest = v - __uint_as_float(hi);
   asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(lo) : "f"(rest));
 }

@@ -625,6 +625,30 @@ def test_gemm_edge_cases_and_errors(cuda):
     produced = ops.gemm(to_device(cuda, special), to_device(cuda, other), 'bf16x3').cpu().numpy()
     assert np.isnan(produced[9]).all() and np.isnan(produced[5]).all()   # inf - inf residual is NaN, as in the reference's split
     assert np.isfinite(produced[[0, 1, 2, 3, 4, 6, 7, 8]]).all()
+    # the same through every kernel family and both modes, with NaNs of every payload in B as well (tf32's high part is
+    # rounded with integer arithmetic that may turn such a NaN into a zero: the residual must still carry it)
+    def poisoned(m, n, k, mode, variant):
+        left, right = R.seeded_uniform(5, (m, k)), np.abs(R.seeded_uniform(6, (k, n))) + 0.5
+        bits = right.view(np.uint32)
+        bits[3, 1], bits[5, 2], bits[7, 4] = 0x7FFFFFFF, 0xFFFFFFFF, 0x7FC00000   # NaNs: all-ones payloads, canonical
+        left[min(2, m - 1), 6] = np.inf
+        ops.set_gemm_variant(variant)
+        try:
+            out = ops.gemm(to_device(cuda, left), to_device(cuda, right), mode).cpu().numpy()
+        finally:
+            ops.set_gemm_variant(0)
+        ops.check_device_status()
+        assert np.isnan(out[:, [1, 2, 4]]).all(), (m, n, k, mode, variant)
+        assert np.isnan(out[min(2, m - 1)]).all(), (m, n, k, mode, variant)
+        clean_rows = [r for r in range(m) if r != min(2, m - 1)]
+        clean_columns = [c for c in range(n) if c not in (1, 2, 4)]
+        assert np.isfinite(out[np.ix_(clean_rows, clean_columns)]).all(), (m, n, k, mode, variant)
+    for mode in ('bf16x3', 'tf32x3'):
+        poisoned(64, 48, 32, mode, 0)         # single-kernel form
+        poisoned(16, 4096, 2048, mode, 10)    # streamed form for at most 16 rows
+        poisoned(1, 2048, 2048, mode, 10)
+        poisoned(512, 512, 256, mode, 1)      # split pass + tcgen05 tiles
+        poisoned(2048, 1024, 512, mode, 7)    # stream kernel (split of A inside)
 
 
 def test_gemm_column_blocks_equal_the_full_product(cuda):
