@@ -71,8 +71,12 @@ struct Tf32Kind {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
     return __uint_as_float(r);
   }
+  // The high part is rounded with integer arithmetic: half a tf32 unit added to the bit pattern, thirteen low bits
+  // cleared. That is round-to-nearest with ties away from zero and equals cvt.rna.tf32.f32 on all 2^32 inputs but NaNs,
+  // without the conversion pipe. A NaN may come out of it as a zero; the residual, NaN whenever v is NaN or infinite,
+  // keeps the conversion instruction, so the NaN still reaches every product of the element.
   __device__ static __forceinline__ void split(float v, elem& hi, elem& lo) {
-    hi = rna(v);
+    hi = __uint_as_float((__float_as_uint(v) + 0x1000u) & 0xFFFFE000u);
     lo = rna(v - hi);
   }
   __device__ static __forceinline__ elem zero() { return 0.f; }
