@@ -1,0 +1,325 @@
+"""Per-program kernels for fused elementwise and row programs.
+
+The library's kernels for these plans take the register program as an argument, which is what a memory-bound launch
+wants (one kernel, any program, the decode paid once per eight elements). A latency-bound launch -- a few thousand
+elements, one wave of threads -- is as long as one thread's instruction chain, and there the decode is most of the
+chain: four to nine times the instructions of a kernel written for the one program. The reference is a compiler and
+emits such a kernel for every workload (compiler/codegen/lower.py). This module does the same for the two plan kinds
+where it matters: it writes the program out as CUDA C++ with every operator inlined, in the operator table's own
+arithmetic (csrc/program.cuh: one rounding per operator, never contracted into fma, the approximate exp / sqrt /
+rsqrt / reciprocal instructions), has NVRTC compile it for sm_100a and launches it through the driver API.
+
+Used by LocalRunner for small launches only; everything else, and every program this module does not take, runs the
+library's kernels. `DTN_JIT=0` turns it off. Nothing here needs a GPU to generate or compile (NVRTC targets an
+architecture, not a device); loading and launching need the current CUDA context.
+"""
+from __future__ import annotations
+
+import ctypes as ct
+import hashlib
+import os
+import threading
+from typing import Any
+
+PRELUDE = r'''
+typedef long long i64;
+__device__ __forceinline__ float dtn_ex2(float x) { float y; asm("ex2.approx.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float dtn_exp(float x) { return dtn_ex2(__fmul_rn(x, 1.4426950408889634f)); }
+__device__ __forceinline__ float dtn_sqrt(float x) { float y; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float dtn_rsqrt(float x) { float y; asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float dtn_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+'''
+
+# operator code (native.ELEMENTWISE_OPS) -> expression over `a` and `b`, in the arithmetic of csrc/program.cuh::prog_apply
+_OPERATORS = {
+    0: '__fadd_rn({a}, {b})', 1: '__fsub_rn({a}, {b})', 2: '__fmul_rn({a}, {b})', 3: '__fdividef({a}, {b})',
+    4: 'fmaxf({a}, {b})', 5: 'fminf({a}, {b})', 6: 'fmaxf({a}, 0.0f)', 7: 'dtn_exp({a})', 8: 'dtn_sqrt({a})',
+    9: 'dtn_rsqrt({a})', 10: 'dtn_rcp({a})', 11: '(-{a})', 12: 'fabsf({a})', 13: '({a})',
+}
+SMALL_ELEMENTS = 1 << 16      # launches above this many elements are bandwidth-bound: the library's kernels take them
+_COMPONENTS = 'xyzw'
+
+
+def enabled() -> bool:
+    return os.environ.get('DTN_JIT', '1') != '0'
+
+
+def apply(op: int, a: str, b: str) -> str:
+    return _OPERATORS[op].format(a=a, b=b)
+
+
+# ------------------------------------------------------------------------------------------------
+# elementwise programs (classify._program_plan / dtn_elementwise_program)
+# ------------------------------------------------------------------------------------------------
+def elementwise_source(params: dict, buffers: dict) -> dict | None:
+    """CUDA source of one kernel for the register program `params`, or None when this module does not take it:
+    FP32 buffers only, a multiple of four elements, every vector buffer at a multiple of four elements from its start
+    (so that 128-bit accesses are aligned), at most SMALL_ELEMENTS elements."""
+    inputs, n = params['inputs'], params['n']
+    if params['out_f16'] or any(spec['f16'] for spec in inputs) or n < 4 or n % 4 or n > SMALL_ELEMENTS:
+        return None
+    if any(op not in _OPERATORS for op in params['ops']):
+        return None
+    if buffers['out'][1] % 4 or any(buffers[f'in{i}'][1] % 4 for i, spec in enumerate(inputs) if not spec['scalar']):
+        return None
+    registers = max([params['out_reg'], len(inputs) - 1, *params['dst'], *params['a'], *params['b']]) + 1
+    lines = ['__device__ __forceinline__ float dtn_element(' + ', '.join(f'float in{i}' for i in range(len(inputs))) + ') {']
+    lines.append('  float ' + ', '.join(f'r{k} = {"in%d" % k if k < len(inputs) else "0.0f"}' for k in range(registers)) + ';')
+    for op, dst, a, b in zip(params['ops'], params['dst'], params['a'], params['b']):
+        lines.append(f'  r{dst} = {apply(op, f"r{a}", f"r{b}")};')
+    lines += [f'  return r{params["out_reg"]};', '}']
+    arguments = ', '.join(f'const float* __restrict__ p{i}' for i in range(len(inputs)))
+    lines.append(f'extern "C" __global__ void __launch_bounds__(256) dtn_jit_kernel({arguments}{", " if inputs else ""}float* __restrict__ out, i64 vectors) {{')
+    lines.append('  const i64 v = (i64)blockIdx.x * 256 + threadIdx.x;')
+    for i, spec in enumerate(inputs):
+        if spec['scalar']:
+            lines.append(f'  const float s{i} = __ldg(p{i});')   # read before the bounds check: its latency overlaps the vector loads
+    lines.append('  if (v >= vectors) return;')
+    for i, spec in enumerate(inputs):
+        if not spec['scalar']:
+            lines.append(f'  const float4 q{i} = __ldg(reinterpret_cast<const float4*>(p{i}) + v);')
+    lines.append('  float4 result;')
+    for c in _COMPONENTS:
+        operands = ', '.join(f's{i}' if spec['scalar'] else f'q{i}.{c}' for i, spec in enumerate(inputs))
+        lines.append(f'  result.{c} = dtn_element({operands});')
+    lines += ['  reinterpret_cast<float4*>(out)[v] = result;', '}']
+    vectors = n // 4
+    return {'source': PRELUDE + '\n'.join(lines) + '\n', 'entry': 'dtn_jit_kernel', 'grid': (vectors + 255) // 256, 'block': 256,
+            'pointers': [f'in{i}' for i in range(len(inputs))] + ['out'], 'scalars': [('i64', vectors)]}
+
+
+# ------------------------------------------------------------------------------------------------
+# row programs (classify_rows._row_program / dtn_row_fused)
+# ------------------------------------------------------------------------------------------------
+ROW_PRELUDE = r'''
+// One value per thread -> the row's value in every thread: xor tree inside a warp, then the four warps' results through
+// shared memory, added (or compared) in warp order.
+template <bool MAX>
+__device__ __forceinline__ float dtn_combine(float v, float* scratch) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float w = __shfl_xor_sync(0xffffffffu, v, o);
+    v = MAX ? fmaxf(v, w) : v + w;
+  }
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
+  __syncthreads();
+  v = scratch[0];
+#pragma unroll
+  for (int w = 1; w < 4; ++w) v = MAX ? fmaxf(v, scratch[w]) : v + scratch[w];
+  return v;
+}
+'''
+ROW_THREADS = 128
+ROW_MAX_VECTORS = 8           # 128-bit vectors of the row one thread keeps in registers: rows of up to 4096 columns
+_ROW_REGISTERS = 12
+
+
+def row_source(params: dict, buffers: dict) -> dict | None:
+    """CUDA source of one kernel for a fused row program: a CTA of 128 threads per row, the row in registers (one
+    global read), the reduction(s), the scalar stage and the elementwise stage written out operator by operator.
+    Register numbering as in csrc/row_fused.cu: r0, r1 = the reduced values, r2 = the element, r3 + i = input i."""
+    rows, cols, inputs = params['rows'], params['cols'], params['inputs']
+    if rows < 1 or rows > 65535 or cols < 4 or cols % 4 or cols > ROW_THREADS * 4 * ROW_MAX_VECTORS or rows * cols > SMALL_ELEMENTS:
+        return None
+    if any(op not in _OPERATORS for op in params['ops']) or params['reduce'] not in ('sum', 'sumsq', 'max', 'softmax'):
+        return None
+    if buffers['x'][1] % 4 or (not params['per_row'] and buffers['out'][1] % 4):
+        return None
+    if any(buffers[f'in{i}'][1] % 4 for i, item in enumerate(inputs) if item['kind'] == 'columns'):
+        return None
+    reduce, n_scalar, out_reg = params['reduce'], params['n_scalar'], params['out_reg']
+    program = list(zip(params['ops'], params['dst'], params['a'], params['b']))
+    if max([out_reg, *params['dst'], *params['a'], *params['b'], 2 + len(inputs)]) >= _ROW_REGISTERS:
+        return None
+    is_max = reduce in ('max', 'softmax')
+    identity = '-__int_as_float(0x7f800000)' if is_max else '0.0f'
+    vectors = (cols // 4 + ROW_THREADS - 1) // ROW_THREADS
+    pointer_inputs = [i for i, item in enumerate(inputs) if item['kind'] != 'immediate']
+    fold = {'sum': '__fadd_rn({acc}, {v})', 'sumsq': 'fmaf({v}, {v}, {acc})', 'max': 'fmaxf({acc}, {v})', 'softmax': 'fmaxf({acc}, {v})'}[reduce]
+    lines = []
+    # elementwise stage as a function of the registers' values at its start
+    lines.append('__device__ __forceinline__ float dtn_element(' + ', '.join(f'float a{k}' for k in range(_ROW_REGISTERS)) + ') {')
+    lines.append('  float ' + ', '.join(f'e{k} = a{k}' for k in range(_ROW_REGISTERS)) + ';')
+    for op, dst, a, b in program[n_scalar:]:
+        lines.append(f'  e{dst} = {apply(op, f"e{a}", f"e{b}")};')
+    lines += [f'  return e{out_reg};', '}']
+    arguments = ['const float* __restrict__ x'] + [f'const float* __restrict__ p{i}' for i in pointer_inputs] + ['float* __restrict__ out', 'int cols']
+    lines.append(f'extern "C" __global__ void __launch_bounds__({ROW_THREADS}) dtn_jit_kernel({", ".join(arguments)}) {{')
+    lines += ['  __shared__ float scratch[2][4];',
+              '  const int row = blockIdx.x, tid = threadIdx.x;',
+              '  const float4* xr = reinterpret_cast<const float4*>(x + (i64)row * cols);']
+    for i, item in enumerate(inputs):
+        if item['kind'] == 'scalar':
+            lines.append(f'  const float c{i} = __ldg(p{i});')
+        elif item['kind'] == 'immediate':
+            lines.append(f'  const float c{i} = __int_as_float({_float_bits(item.get("value", 0.0))});')
+    lines.append(f'  const float identity = {identity};')
+    lines.append(f'  float4 v[{vectors}];')
+    lines.append('#pragma unroll')
+    lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
+    lines.append(f'    const int j = u * {ROW_THREADS} + tid;')
+    lines.append('    v[u] = j * 4 < cols ? __ldg(xr + j) : make_float4(identity, identity, identity, identity);')
+    lines.append('  }')
+    lines.append('  float first = identity;')
+    lines.append('#pragma unroll')
+    lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
+    for c in _COMPONENTS:
+        lines.append('    first = ' + fold.format(acc='first', v=f'v[u].{c}') + ';')
+    lines.append('  }')
+    lines.append(f'  first = dtn_combine<{"true" if is_max else "false"}>(first, scratch[0]);')
+    lines.append('  float second = 0.0f;')
+    if reduce == 'softmax':
+        lines.append('#pragma unroll')
+        lines.append(f'  for (int u = 0; u < {vectors}; ++u)')
+        lines.append('    second += (dtn_exp(__fsub_rn(v[u].x, first)) + dtn_exp(__fsub_rn(v[u].y, first))) + '
+                     '(dtn_exp(__fsub_rn(v[u].z, first)) + dtn_exp(__fsub_rn(v[u].w, first)));')
+        lines.append('  second = dtn_combine<false>(second, scratch[1]);')
+    # scalar stage
+    initial = {0: 'first', 1: 'second'}
+    for i, item in enumerate(inputs):
+        if item['kind'] != 'columns':
+            initial[3 + i] = f'c{i}'
+    lines.append('  float ' + ', '.join(f'r{k} = {initial.get(k, "0.0f")}' for k in range(_ROW_REGISTERS)) + ';')
+    for op, dst, a, b in program[:n_scalar]:
+        lines.append(f'  r{dst} = {apply(op, f"r{a}", f"r{b}")};')
+    if params['per_row']:
+        lines.append(f'  if (tid == 0) out[row] = r{out_reg};')
+    else:
+        lines.append('  float4* out_row = reinterpret_cast<float4*>(out + (i64)row * cols);')
+        lines.append('#pragma unroll')
+        lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
+        lines.append(f'    const int j = u * {ROW_THREADS} + tid;')
+        lines.append('    if (j * 4 >= cols) continue;')
+        columns = [i for i, item in enumerate(inputs) if item['kind'] == 'columns']
+        for i in columns:
+            lines.append(f'    const float4 q{i} = __ldg(reinterpret_cast<const float4*>(p{i}) + j);')
+        lines.append('    float4 result;')
+        for c in _COMPONENTS:
+            values = []
+            for k in range(_ROW_REGISTERS):
+                if k == 2:
+                    values.append(f'v[u].{c}')
+                elif k - 3 in columns:
+                    values.append(f'q{k - 3}.{c}')
+                else:
+                    values.append(f'r{k}')
+            lines.append(f'    result.{c} = dtn_element({", ".join(values)});')
+        lines.append('    out_row[j] = result;')
+        lines.append('  }')
+    lines.append('}')
+    return {'source': PRELUDE + ROW_PRELUDE + '\n'.join(lines) + '\n', 'entry': 'dtn_jit_kernel', 'grid': rows, 'block': ROW_THREADS,
+            'pointers': ['x'] + [f'in{i}' for i in pointer_inputs] + ['out'], 'scalars': [('i32', cols)]}
+
+
+def _float_bits(value: float) -> str:
+    import struct
+    return hex(struct.unpack('<I', struct.pack('<f', float(value)))[0])
+
+
+def specialized_source(plan: Any) -> dict | None:
+    """The per-program kernel of a plan (source, entry, launch geometry, argument roles), or None."""
+    if not enabled():
+        return None
+    try:
+        if plan.kind == 'elementwise_program':
+            return elementwise_source(plan.params, plan.buffers)
+        if plan.kind == 'row_fused':
+            return row_source(plan.params, plan.buffers)
+    except (KeyError, ValueError, TypeError):
+        return None
+    return None
+
+
+# ------------------------------------------------------------------------------------------------
+# NVRTC and the driver API
+# ------------------------------------------------------------------------------------------------
+_lock = threading.Lock()
+_cubins: dict[str, bytes | None] = {}
+_modules: dict[tuple[int, str], Any] = {}
+_libraries: dict[str, Any] = {}
+
+
+def _library(name: str):
+    if name not in _libraries:
+        try:
+            _libraries[name] = ct.CDLL(name)
+        except OSError:
+            _libraries[name] = None
+    return _libraries[name]
+
+
+def compile_source(source: str, arch: str = 'sm_100a') -> bytes | None:
+    """NVRTC: CUDA C++ -> cubin for `arch`. None when NVRTC is not there or rejects the source (the caller then runs
+    the library's kernel). No contraction into fma: a program computes what its operators compute one by one."""
+    key = hashlib.sha256((arch + '\0' + source).encode()).hexdigest()
+    with _lock:
+        if key in _cubins:
+            return _cubins[key]
+        nvrtc = _library('libnvrtc.so.12') or _library('libnvrtc.so')
+        cubin = None
+        if nvrtc is not None:
+            program = ct.c_void_p()
+            if nvrtc.nvrtcCreateProgram(ct.byref(program), source.encode(), b'dtn_jit.cu', 0, None, None) == 0:
+                options = [f'--gpu-architecture={arch}'.encode(), b'--std=c++17', b'--fmad=false']
+                array = (ct.c_char_p * len(options))(*options)
+                if nvrtc.nvrtcCompileProgram(program, len(options), array) == 0:
+                    size = ct.c_size_t()
+                    if nvrtc.nvrtcGetCUBINSize(program, ct.byref(size)) == 0 and size.value:
+                        buffer = ct.create_string_buffer(size.value)
+                        if nvrtc.nvrtcGetCUBIN(program, buffer) == 0:
+                            cubin = buffer.raw
+                nvrtc.nvrtcDestroyProgram(ct.byref(program))
+        _cubins[key] = cubin
+        return cubin
+
+
+class Kernel:
+    """A compiled per-program kernel loaded into the current CUDA context."""
+
+    def __init__(self, cubin: bytes, entry: str) -> None:
+        driver = _library('libcuda.so.1')
+        if driver is None:
+            raise OSError('libcuda.so.1 is not available')
+        self._driver = driver
+        self._module, self._function = ct.c_void_p(), ct.c_void_p()
+        if driver.cuModuleLoadData(ct.byref(self._module), cubin) != 0:
+            raise OSError('cuModuleLoadData failed')
+        if driver.cuModuleGetFunction(ct.byref(self._function), self._module, entry.encode()) != 0:
+            raise OSError('cuModuleGetFunction failed')
+
+    def attributes(self) -> tuple[int, int]:
+        """(registers per thread, static shared memory in bytes) of the loaded kernel."""
+        registers, shared = ct.c_int(0), ct.c_int(0)
+        self._driver.cuFuncGetAttribute(ct.byref(registers), 4, self._function)    # CU_FUNC_ATTRIBUTE_NUM_REGS
+        self._driver.cuFuncGetAttribute(ct.byref(shared), 1, self._function)       # CU_FUNC_ATTRIBUTE_SHARED_SIZE_BYTES
+        return registers.value, shared.value
+
+    def launch(self, grid: int, block: int, values: list, stream: int) -> None:
+        params = (ct.c_void_p * len(values))(*[ct.cast(ct.byref(v), ct.c_void_p) for v in values])
+        status = self._driver.cuLaunchKernel(self._function, grid, 1, 1, block, 1, 1, 0, ct.c_void_p(stream), params, None)
+        if status != 0:
+            raise OSError(f'cuLaunchKernel failed with CUresult {status}')
+
+
+def kernel_for(spec: dict, device: int, arch: str = 'sm_100a') -> Kernel | None:
+    """The loaded kernel of a specialised source on `device` (whose context must be current), or None."""
+    key = (device, hashlib.sha256(spec['source'].encode()).hexdigest())
+    if key in _modules:
+        return _modules[key]
+    cubin = compile_source(spec['source'], arch)
+    kernel = None
+    if cubin is not None:
+        try:
+            kernel = Kernel(cubin, spec['entry'])
+        except OSError:
+            kernel = None
+    _modules[key] = kernel
+    return kernel
+
+
+def launch(spec: dict, kernel: Kernel, pointer_of: Any, stream: int) -> None:
+    """One launch: `pointer_of(role)` gives the device address of a buffer role of the plan."""
+    values: list = [ct.c_uint64(pointer_of(role)) for role in spec['pointers']]
+    for kind, value in spec['scalars']:
+        values.append({'i64': ct.c_longlong, 'i32': ct.c_int, 'f32': ct.c_float}[kind](value))
+    kernel.launch(spec['grid'], spec['block'], values, stream)

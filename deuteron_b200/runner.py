@@ -19,7 +19,7 @@ from typing import Any
 
 import numpy as np
 
-from . import native
+from . import jit, native
 from .build import Compilation
 from .validation import validate_launch
 
@@ -108,6 +108,7 @@ class LocalRunner:
         self.open = True
         self._resident: dict[int, Any] = {}
         self._pinned: list[Any] = []
+        self._jit: dict[int, tuple[Any, Any]] = {}
 
     def __enter__(self) -> 'LocalRunner':
         return self
@@ -130,6 +131,17 @@ class LocalRunner:
 
     # -- launching ---------------------------------------------------------------------------
 
+    def _specialized(self, plan: Any) -> tuple[dict, Any] | None:
+        """The kernel compiled for this one program (jit.py), for small FP32 elementwise and row programs; None for
+        everything else, with `DTN_JIT=0`, or when NVRTC or the module load fails: the library's kernel runs then."""
+        entry = self._jit.get(id(plan))
+        if entry is None or entry[0] is not plan:
+            spec = jit.specialized_source(plan) if jit.enabled() else None
+            kernel = jit.kernel_for(spec, self.device) if spec is not None else None
+            entry = (plan, (spec, kernel) if kernel is not None else None)
+            self._jit[id(plan)] = entry
+        return entry[1]
+
     def _enqueue(self, plan: Any, pointers: dict[str, int], stream: int, workspace: Any) -> None:
         kind, p = plan.kind, plan.params
 
@@ -137,6 +149,11 @@ class LocalRunner:
             name, offset = plan.buffers[role]
             return pointers[name] + offset * element_bytes
 
+        if kind in ('elementwise_program', 'row_fused'):
+            special = self._specialized(plan)
+            if special is not None:
+                jit.launch(special[0], special[1], lambda role: ptr(role, 4), stream)
+                return
         if kind == 'elementwise':
             binary = 'y' in plan.buffers
             native.call('dtn_elementwise_f32', native.ELEMENTWISE_OPS[p['op']], ptr('x', 4), ptr('y', 4) if binary else None,
@@ -454,12 +471,17 @@ class LocalRunner:
             # one PTX entry): the launch is recorded in a capture, not run, and its kernel nodes are looked up
             import ctypes as ct
             counts = [ct.c_int(0) for _ in range(4)]
-            native.call('dtn_capture_begin', stream)
-            try:
-                self._enqueue(plan, pointers, stream, workspace)
-            finally:
-                native.call('dtn_capture_end', stream, *[ct.byref(c) for c in counts])
-            kernels, registers, static_smem, dynamic_smem = (c.value for c in counts)
+            special = self._specialized(plan) if plan.kind in ('elementwise_program', 'row_fused') else None
+            if special is not None:   # a kernel loaded through the driver API: its attributes come from there
+                kernels, dynamic_smem = 1, 0
+                registers, static_smem = special[1].attributes()
+            else:
+                native.call('dtn_capture_begin', stream)
+                try:
+                    self._enqueue(plan, pointers, stream, workspace)
+                finally:
+                    native.call('dtn_capture_end', stream, *[ct.byref(c) for c in counts])
+                kernels, registers, static_smem, dynamic_smem = (c.value for c in counts)
 
             timings = timed_graph(True)
             kernel_only = statistics.median(timed_graph(False)) if redundant else None

@@ -411,3 +411,37 @@ def test_ir_built_by_the_reference_generators_classifies_like_the_generated_sche
             mine = compile_kernel(*schedules.f16_storage_example(kind, width=width)).plan
             assert theirs.kind == mine.kind and theirs.params == mine.params and theirs.buffers == mine.buffers, (kind, width)
             assert schedules.f16_storage_example(kind, width=width) == (case['graph'], case['meta'])
+
+
+def test_per_program_sources_cover_the_small_open_workloads_and_compile():
+    """jit.py writes one kernel per small elementwise / row program; NVRTC compiles each for sm_100a without a device.
+    Programs outside its conditions (large, f16, ragged widths) are left to the library's kernels."""
+    from deuteron_b200 import jit, schedules
+    taken = {}
+    for name, (graph, meta) in schedules.open_workloads().items():
+        plan = compile_kernel(graph, meta, arch='sm_100a').plan
+        spec = jit.specialized_source(plan)
+        if spec is not None:
+            taken[name] = (plan, spec)
+    assert {'p02_scale_shift', 'p03_relu_mul', 'f01_rmsnorm', 'f02_row_softmax', 'f03_l2norm'} <= set(taken)
+    assert all(plan.kind in ('elementwise_program', 'row_fused') for plan, _ in taken.values())
+    plan, spec = taken['f01_rmsnorm']
+    assert spec['grid'] == plan.params['rows'] and spec['pointers'][0] == 'x' and spec['pointers'][-1] == 'out'
+    assert 'fmaf(' in spec['source'] and 'dtn_rsqrt' in spec['source'] and '--fmad' not in spec['source']
+    # outside the conditions: 70_004 elements (above the size limit), f16 storage, a wide row
+    graph, meta = schedules.pointwise_example('affine', 70_004)
+    assert jit.specialized_source(compile_kernel(graph, meta).plan) is None
+    graph, meta = schedules.f16_storage_example('affine', count=512)
+    assert jit.specialized_source(compile_kernel(graph, meta).plan) is None
+    graph, meta = schedules.row_softmax_example(rows=2, cols=8192)
+    assert jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan) is None
+    graph, meta = schedules.row_softmax_example(rows=3, cols=640)
+    ragged = jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan)
+    assert ragged is not None and ragged['grid'] == 3
+    if jit._library('libnvrtc.so.12') is None and jit._library('libnvrtc.so') is None:
+        pytest.skip('NVRTC is not installed')
+    for name, (plan, spec) in taken.items():
+        cubin = jit.compile_source(spec['source'])
+        assert cubin is not None and cubin[:4] == b'\x7fELF', name
+    assert jit.compile_source(ragged['source']) is not None
+    assert jit.compile_source('this is not CUDA') is None

@@ -128,6 +128,44 @@ def test_pointwise_workloads_are_exact(runner):
     np.testing.assert_array_equal(got, np.maximum(normal(0, 2048), np.float32(0.0)) * normal(1, 2048))
 
 
+PER_PROGRAM_CASES = [
+    (schedules.pointwise_example, dict(kind='affine', count=4096)), (schedules.pointwise_example, dict(kind='affine', count=4)),
+    (schedules.pointwise_example, dict(kind='affine', count=65536)), (schedules.pointwise_example, dict(kind='relu_multiply', count=2048)),
+    (schedules.pointwise_example, dict(kind='relu_multiply', count=1028)),
+    (schedules.row_softmax_example, dict(rows=64, cols=256)), (schedules.row_softmax_example, dict(rows=3, cols=640)),
+    (schedules.row_softmax_example, dict(rows=5, cols=4096)), (schedules.row_softmax_example, dict(rows=2, cols=96, block=32)),
+    (schedules.rms_norm_example, dict(rows=64, cols=1024)), (schedules.rms_norm_example, dict(rows=7, cols=3072)),
+    (schedules.rms_norm_example, dict(rows=1, cols=512)), (schedules.l2_norm_example, dict(rows=64, cols=512)),
+    (schedules.l2_norm_example, dict(rows=1, cols=4096)), (schedules.l2_norm_example, dict(rows=16, cols=1536)),
+    (schedules.mean_example, dict(count=4096)), (schedules.mean_example, dict(count=1024)),
+]
+
+
+@pytest.mark.parametrize('make,settings', PER_PROGRAM_CASES, ids=lambda v: v.__name__ if callable(v) else '-'.join(str(x) for x in v.values()))
+def test_per_program_kernels_equal_the_library_kernels(runner, monkeypatch, make, settings):
+    """A small elementwise or row program runs a kernel compiled for that one program (jit.py). Its operators are the
+    library's operators, so an elementwise program gives the library kernel's bits; a row program adds its row in another
+    order (128 threads a row, whatever the row's length), so it is held to the row kernels' tolerance against the
+    library kernel and must leave the same special values in the same places."""
+    graph, meta = make(**settings)
+    launch = meta['kernels'][0]
+    compiled = compile_kernel(graph, meta, arch='sm_100a', opt_level=3)
+    assert runner._specialized(compiled.plan) is not None, 'the per-program kernel was not built'
+    special = runner.run_kernel(launch, compiled, warmup=1, iters=2, samples=1)
+    assert special['registers'] > 0
+    monkeypatch.setenv('DTN_JIT', '0')
+    plain = compile_kernel(graph, meta, arch='sm_100a', opt_level=3)
+    assert runner._specialized(plain.plan) is None
+    library = runner.run_kernel(launch, plain, warmup=1, iters=2, samples=1)
+    for name, expected in library['outputs'].items():
+        got = special['outputs'][name]
+        if compiled.plan.kind == 'elementwise_program':
+            np.testing.assert_array_equal(got.view(np.uint32), expected.view(np.uint32))
+        else:
+            np.testing.assert_allclose(got, expected, rtol=1e-5, atol=1e-7)
+            np.testing.assert_array_equal(np.isfinite(got), np.isfinite(expected))
+
+
 def test_all_half_bits_copy_exactly_at_scalar_and_vector_widths(runner):
     data = np.arange(65536, dtype=np.uint16).view(np.float16)
     for width in (1, 2, 4):
