@@ -93,6 +93,11 @@ attention_rows_kernel(const float* __restrict__ q, const float* __restrict__ kt,
 // stage of SK keys (kt[:, k0:k0+SK] and v[k0:k0+SK, :]) together, then each warp runs the staged
 // recurrence of its row out of shared memory. Small problems (the reference's example shapes) are
 // latency-bound, and this turns a chain of dependent global loads per row into one round trip per stage.
+__device__ __forceinline__ void copy_async_16(float* shared_dst, const float* global_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(shared_dst)), "l"(global_src)
+               : "memory");
+}
+
 template <int SK, int CG /*value-column groups of 32 per lane*/>
 __global__ void __launch_bounds__(kRowWarps * 32)
 attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ kt, const float* __restrict__ v,
@@ -124,17 +129,16 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
     const float* v_stage = v + (int64_t)k0 * cols;
     const int v_count = stage_keys * cols;
     if (vec_ok && stage_keys == SK) {
-      // 128-bit loads, all of a thread's loads in flight before the first store
+      // 16-byte asynchronous copies straight into shared memory: every copy of the stage is in flight at once, so the
+      // stage costs one trip to L2 however many copies a thread issues (register-staged loads cost one trip per
+      // unrolled batch, four for the 128-key example)
       constexpr int kPerRow = SK / 4;
-#pragma unroll 4
       for (int i = tid; i < depth * kPerRow; i += kRowWarps * 32) {
         const int d = i / kPerRow, k4 = i % kPerRow;
-        const float4 x = __ldg(reinterpret_cast<const float4*>(kt + (int64_t)d * keys + k0) + k4);
-        *reinterpret_cast<float4*>(kts + d * SK + 4 * k4) = x;
+        copy_async_16(kts + d * SK + 4 * k4, kt + (int64_t)d * keys + k0 + 4 * k4);
       }
-#pragma unroll 4
-      for (int i = tid; i < v_count / 4; i += kRowWarps * 32)
-        *reinterpret_cast<float4*>(vs + 4 * i) = __ldg(reinterpret_cast<const float4*>(v_stage) + i);
+      for (int i = tid; i < v_count / 4; i += kRowWarps * 32) copy_async_16(vs + 4 * i, v_stage + 4 * i);
+      asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     } else {
 #pragma unroll 8
       for (int i = tid; i < depth * SK; i += kRowWarps * 32) {

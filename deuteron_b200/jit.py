@@ -36,6 +36,7 @@ _OPERATORS = {
     4: 'fmaxf({a}, {b})', 5: 'fminf({a}, {b})', 6: 'fmaxf({a}, 0.0f)', 7: 'dtn_exp({a})', 8: 'dtn_sqrt({a})',
     9: 'dtn_rsqrt({a})', 10: 'dtn_rcp({a})', 11: '(-{a})', 12: 'fabsf({a})', 13: '({a})',
 }
+KINDS = ('elementwise_program', 'row_fused', 'row_reduce')   # plan kinds this module may take
 SMALL_ELEMENTS = 1 << 16      # launches above this many elements are bandwidth-bound: the library's kernels take them
 _COMPONENTS = 'xyzw'
 
@@ -225,6 +226,10 @@ def specialized_source(plan: Any) -> dict | None:
             return elementwise_source(plan.params, plan.buffers)
         if plan.kind == 'row_fused':
             return row_source(plan.params, plan.buffers)
+        if plan.kind == 'row_reduce' and plan.params['op'] in ('sum', 'max', 'sumsq'):   # a row program with no operators
+            reduction = {'rows': plan.params['rows'], 'cols': plan.params['cols'], 'reduce': plan.params['op'], 'inputs': [], 'n_scalar': 0,
+                         'out_reg': 0, 'ops': [], 'dst': [], 'a': [], 'b': [], 'per_row': True}
+            return row_source(reduction, plan.buffers)
     except (KeyError, ValueError, TypeError):
         return None
     return None

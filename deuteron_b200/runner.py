@@ -134,9 +134,11 @@ class LocalRunner:
     def _specialized(self, plan: Any) -> tuple[dict, Any] | None:
         """The kernel compiled for this one program (jit.py), for small FP32 elementwise and row programs; None for
         everything else, with `DTN_JIT=0`, or when NVRTC or the module load fails: the library's kernel runs then."""
+        if not jit.enabled():
+            return None
         entry = self._jit.get(id(plan))
         if entry is None or entry[0] is not plan:
-            spec = jit.specialized_source(plan) if jit.enabled() else None
+            spec = jit.specialized_source(plan)
             kernel = jit.kernel_for(spec, self.device) if spec is not None else None
             entry = (plan, (spec, kernel) if kernel is not None else None)
             self._jit[id(plan)] = entry
@@ -149,7 +151,7 @@ class LocalRunner:
             name, offset = plan.buffers[role]
             return pointers[name] + offset * element_bytes
 
-        if kind in ('elementwise_program', 'row_fused'):
+        if kind in jit.KINDS:
             special = self._specialized(plan)
             if special is not None:
                 jit.launch(special[0], special[1], lambda role: ptr(role, 4), stream)
@@ -471,7 +473,7 @@ class LocalRunner:
             # one PTX entry): the launch is recorded in a capture, not run, and its kernel nodes are looked up
             import ctypes as ct
             counts = [ct.c_int(0) for _ in range(4)]
-            special = self._specialized(plan) if plan.kind in ('elementwise_program', 'row_fused') else None
+            special = self._specialized(plan) if plan.kind in jit.KINDS else None
             if special is not None:   # a kernel loaded through the driver API: its attributes come from there
                 kernels, dynamic_smem = 1, 0
                 registers, static_smem = special[1].attributes()

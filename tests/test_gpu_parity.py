@@ -138,6 +138,8 @@ PER_PROGRAM_CASES = [
     (schedules.rms_norm_example, dict(rows=1, cols=512)), (schedules.l2_norm_example, dict(rows=64, cols=512)),
     (schedules.l2_norm_example, dict(rows=1, cols=4096)), (schedules.l2_norm_example, dict(rows=16, cols=1536)),
     (schedules.mean_example, dict(count=4096)), (schedules.mean_example, dict(count=1024)),
+    (schedules.row_reduce_example, dict(rows=64, cols=512)), (schedules.row_reduce_example, dict(rows=1, cols=1024)),
+    (schedules.row_reduce_example, dict(rows=9, cols=4096, op='max')),
 ]
 
 
