@@ -110,9 +110,14 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int row = blockIdx.x * kRowWarps + warp;
   const bool active = row < rows;
+  // the CTA's query rows, as asynchronous copies that land with the first stage (a load and a store would hold every
+  // thread for one trip to L2 before it could request the stage)
   for (int i = tid; i < kRowWarps * depth; i += kRowWarps * 32) {
     const int r = blockIdx.x * kRowWarps + i / depth;
-    qs[i] = r < rows ? __ldg(q + (int64_t)r * depth + i % depth) : 0.f;
+    const bool in = r < rows;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"((unsigned)__cvta_generic_to_shared(qs + i)),
+                 "l"(in ? q + (int64_t)r * depth + i % depth : q), "r"(in ? 4 : 0)
+                 : "memory");
   }
   float acc[CG];
 #pragma unroll
@@ -138,7 +143,6 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
         copy_async_16(kts + d * SK + 4 * k4, kt + (int64_t)d * keys + k0 + 4 * k4);
       }
       for (int i = tid; i < v_count / 4; i += kRowWarps * 32) copy_async_16(vs + 4 * i, v_stage + 4 * i);
-      asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     } else {
 #pragma unroll 8
       for (int i = tid; i < depth * SK; i += kRowWarps * 32) {
@@ -148,13 +152,29 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
 #pragma unroll 8
       for (int i = tid; i < v_count; i += kRowWarps * 32) vs[i] = __ldg(v_stage + i);
     }
+    asm volatile("cp.async.commit_group;\n\tcp.async.wait_group 0;" ::: "memory");
     __syncthreads();
     if (active) {
       float s[kRounds];
 #pragma unroll
       for (int r = 0; r < kRounds; ++r) s[r] = 0.f;
       const float* qrow = qs + warp * depth;
-      for (int d = 0; d < depth; ++d) {
+      int d = 0;
+      if (depth % 4 == 0) {   // four query values per broadcast load; the products are added in the same order
+#pragma unroll 2
+        for (; d < depth; d += 4) {
+          const float4 q4 = *reinterpret_cast<const float4*>(qrow + d);
+          const float* kr = kts + d * SK + lane;
+#pragma unroll
+          for (int r = 0; r < kRounds; ++r) {
+            s[r] = fmaf(q4.x, kr[32 * r], s[r]);
+            s[r] = fmaf(q4.y, kr[SK + 32 * r], s[r]);
+            s[r] = fmaf(q4.z, kr[2 * SK + 32 * r], s[r]);
+            s[r] = fmaf(q4.w, kr[3 * SK + 32 * r], s[r]);
+          }
+        }
+      }
+      for (; d < depth; ++d) {
         const float qv = qrow[d];
         const float* kr = kts + d * SK + lane;
 #pragma unroll
@@ -181,7 +201,23 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
 #pragma unroll
       for (int c = 0; c < CG; ++c) acc[c] *= alpha;
       const float* wrow = ws + warp * SK;
-      for (int k = 0; k < stage_keys; ++k) {
+      int k = 0;
+      if (stage_keys == SK) {   // four weights per broadcast load, the same order of additions
+#pragma unroll 4
+        for (; k < SK; k += 4) {
+          const float4 w4 = *reinterpret_cast<const float4*>(wrow + k);
+          const float* vr = vs + k * cols + lane;
+#pragma unroll
+          for (int c = 0; c < CG; ++c)
+            if (lane + 32 * c < cols) {
+              acc[c] = fmaf(w4.x, vr[32 * c], acc[c]);
+              acc[c] = fmaf(w4.y, vr[cols + 32 * c], acc[c]);
+              acc[c] = fmaf(w4.z, vr[2 * cols + 32 * c], acc[c]);
+              acc[c] = fmaf(w4.w, vr[3 * cols + 32 * c], acc[c]);
+            }
+        }
+      }
+      for (; k < stage_keys; ++k) {
         const float w = wrow[k];
         const float* vr = vs + k * cols + lane;
 #pragma unroll

@@ -139,55 +139,43 @@ __device__ __forceinline__ void f32_copy_4(uint32_t dst, const void* src, int va
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(valid_bytes) : "memory");
 }
 
-// KPARTS > 1: a cluster of KPARTS CTAs along z shares one output tile, each CTA takes a contiguous slice of k, and the
-// partial sums meet in the first CTA's shared memory (distributed-shared-memory stores into a fixed slot per CTA and
-// thread) where they are added in rank order: no atomics, the same bits on every run. Used for contractions too small
-// to give the SMs work otherwise (the reference's split-K workload: 128 x 64 outputs, k = 256). The k order of an
-// output element differs from the one-CTA form, which is why the product of the reference's 128^3 example never
-// takes it.
-template <int KPARTS>
+// Few output tiles and a short launch: the time is one CTA's chain of k-tiles. The k-tiles go through a ring of
+// FS_STAGES slots filled by cp.async (4-byte copies, so any alignment and any edge: out-of-range elements are
+// zero-filled), all slots requested before the first product. One k-tile is a few hundred cycles of arithmetic against
+// a global-memory latency of about a thousand: with the next tile alone in flight (registers, as the large-tile kernels
+// do) every k-tile cost a full latency, 0.48 us per 16 k.
 __global__ void __launch_bounds__(F_THREADS)
 gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                       int64_t lda, int64_t ldb, int64_t ldc) {
-  // The k-tiles go through a ring of FS_STAGES slots filled by cp.async (4-byte copies, so any alignment and any edge:
-  // out-of-range elements are zero-filled), all slots requested before the first product. One k-tile is a few hundred
-  // cycles of arithmetic against a global-memory latency of about a thousand: with the next tile alone in flight
-  // (registers, as the large-tile kernels do) every k-tile cost a full latency, 0.48 us per 16 k.
-  constexpr int FS_STAGES = KPARTS > 1 ? 4 : 8;   // a CTA of a k-split has few k-tiles, and its partial sums need the room
+  constexpr int FS_STAGES = 8;
   __shared__ float As[FS_STAGES][FS_BK][FS_B + 1];
   __shared__ float Bs[FS_STAGES][FS_BK][FS_B + 1];
-  __shared__ float partials[KPARTS > 1 ? (KPARTS - 1) * F_THREADS * 4 : 1];
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * FS_B, n0 = blockIdx.x * FS_B;
-  // this CTA's slice of k: whole k-tiles, the last CTA takes what is left
-  const int all_tiles = (K + FS_BK - 1) / FS_BK;
-  const int per_part = (all_tiles + KPARTS - 1) / KPARTS;
-  const int k_begin = (KPARTS > 1 ? (int)blockIdx.z * per_part : 0) * FS_BK;
-  const int k_end = KPARTS > 1 ? min(K, k_begin + per_part * FS_BK) : K;
   const int tx = tid & 15, ty = tid >> 4;   // 16 x 16 threads, each 2 x 2 outputs
   auto request_tile = [&](int k0, int slot) {   // 512 elements per operand tile, two per thread
 #pragma unroll
     for (int i = 0; i < 2; ++i) {
       const int v = tid + i * F_THREADS;          // 0..511
       const int ar = v >> 4, ak = v & 15;         // A: 32 rows x 16 k, k fastest in memory, stored [k][row]
-      const bool a_in = m0 + ar < M && k0 + ak < k_end;
+      const bool a_in = m0 + ar < M && k0 + ak < K;
       f32_copy_4(smem_u32(&As[slot][ak][ar]), a_in ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, a_in ? 4 : 0);
       const int bk = v >> 5, bn = v & 31;         // B: 16 k x 32 columns, column fastest
-      const bool b_in = k0 + bk < k_end && n0 + bn < N;
+      const bool b_in = k0 + bk < K && n0 + bn < N;
       f32_copy_4(smem_u32(&Bs[slot][bk][bn]), b_in ? (const void*)(B + (int64_t)(k0 + bk) * ldb + n0 + bn) : (const void*)B, b_in ? 4 : 0);
     }
   };
   float acc[2][2] = {{0.f, 0.f}, {0.f, 0.f}};
-  const int ktiles = k_end > k_begin ? (k_end - k_begin + FS_BK - 1) / FS_BK : 0;
+  const int ktiles = (K + FS_BK - 1) / FS_BK;
 #pragma unroll
   for (int s = 0; s < FS_STAGES - 1; ++s) {
-    if (s < ktiles) request_tile(k_begin + s * FS_BK, s);
+    if (s < ktiles) request_tile(s * FS_BK, s);
     asm volatile("cp.async.commit_group;" ::: "memory");
   }
   for (int kt = 0; kt < ktiles; ++kt) {
     asm volatile("cp.async.wait_group %0;" ::"n"(FS_STAGES - 2) : "memory");
     __syncthreads();   // tile kt has landed for every thread, and everybody is done with the slot requested next
-    if (kt + FS_STAGES - 1 < ktiles) request_tile(k_begin + (kt + FS_STAGES - 1) * FS_BK, (kt + FS_STAGES - 1) % FS_STAGES);
+    if (kt + FS_STAGES - 1 < ktiles) request_tile((kt + FS_STAGES - 1) * FS_BK, (kt + FS_STAGES - 1) % FS_STAGES);
     asm volatile("cp.async.commit_group;" ::: "memory");
     const int buf = kt % FS_STAGES;
 #pragma unroll
@@ -201,29 +189,120 @@ gemm_f32_small_kernel(const float* __restrict__ A, const float* __restrict__ B, 
     }
   }
   asm volatile("cp.async.wait_group 0;" ::: "memory");
-  if constexpr (KPARTS > 1) {
-    const int part = (int)blockIdx.z;
-    if (part != 0) {
-      const uint32_t local = smem_u32(partials + ((part - 1) * F_THREADS + tid) * 4);
-      uint32_t remote;
-      asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + 4u * e), "f"(acc[e >> 1][e & 1]) : "memory");
-    }
-    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-    if (part != 0) return;
-    for (int other = 1; other < KPARTS; ++other) {
-      const float* theirs = partials + ((other - 1) * F_THREADS + tid) * 4;
-#pragma unroll
-      for (int e = 0; e < 4; ++e) acc[e >> 1][e & 1] += theirs[e];
-    }
-  }
 #pragma unroll
   for (int i = 0; i < 2; ++i)
 #pragma unroll
     for (int j = 0; j < 2; ++j) {
       const int r = m0 + ty * 2 + i, c = n0 + tx * 2 + j;
+      if (r < M && c < N) C[(int64_t)r * ldc + c] = acc[i][j];
+    }
+}
+
+// Split k: a cluster of KPARTS CTAs along z shares one 32 x 32 output tile, each CTA takes a contiguous slice of k,
+// and the partial sums meet in the first CTA's shared memory (distributed-shared-memory stores into a fixed slot per
+// CTA and thread) where they are added in rank order: no atomics, the same bits on every run. Used for contractions
+// too small to give the SMs work otherwise (the reference's split-K workload: 128 x 64 outputs, k = 256). Inside a
+// CTA the two halves of the threads take the first and the last eight k of every k-tile, 4 x 2 outputs per thread
+// from one 128-bit and one 64-bit shared load per k (the 2 x 2 form above needs four loads for four products and is
+// bound by them: 850 cycles per k-tile against 150), and the second half's sums are added to the first's before the
+// cluster's. The k order of an output element therefore differs from the one-CTA form, which is why the product of
+// the reference's 128^3 example never takes this kernel.
+constexpr int FK_PITCH = FS_B + 4;   // rows of a k-tile start 16-byte aligned
+
+template <int KPARTS>
+__global__ void __launch_bounds__(F_THREADS)
+gemm_f32_splitk_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
+                       int64_t lda, int64_t ldb, int64_t ldc) {
+  constexpr int FK_STAGES = KPARTS > 4 ? 3 : 4;   // eight slots of partial sums leave room for three
+  __shared__ __align__(16) float As[FK_STAGES][FS_BK][FK_PITCH];
+  __shared__ __align__(16) float Bs[FK_STAGES][FS_BK][FK_PITCH];
+  __shared__ __align__(16) float partials[KPARTS * (F_THREADS / 2) * 8];   // slot 0: this CTA's second half
+  const int tid = threadIdx.x;
+  const int m0 = blockIdx.y * FS_B, n0 = blockIdx.x * FS_B;
+  // this CTA's slice of k: whole k-tiles, the last CTA takes what is left
+  const int all_tiles = (K + FS_BK - 1) / FS_BK;
+  const int per_part = (all_tiles + KPARTS - 1) / KPARTS;
+  const int k_begin = (int)blockIdx.z * per_part * FS_BK;
+  const int k_end = min(K, k_begin + per_part * FS_BK);
+  const int half = tid >> 7, t = tid & 127;
+  const int tx = t & 15, ty = t >> 4;   // 8 x 16 threads, each 4 rows x 2 columns
+  auto request_tile = [&](int k0, int slot) {   // 512 elements per operand tile, two per thread
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int v = tid + i * F_THREADS;          // 0..511
+      const int ar = v >> 4, ak = v & 15;         // A: 32 rows x 16 k, k fastest in memory, stored [k][row]
+      const bool a_in = m0 + ar < M && k0 + ak < k_end;
+      f32_copy_4(smem_u32(&As[slot][ak][ar]), a_in ? (const void*)(A + (int64_t)(m0 + ar) * lda + k0 + ak) : (const void*)A, a_in ? 4 : 0);
+      const int bk = v >> 5, bn = v & 31;         // B: 16 k x 32 columns, column fastest
+      const bool b_in = k0 + bk < k_end && n0 + bn < N;
+      f32_copy_4(smem_u32(&Bs[slot][bk][bn]), b_in ? (const void*)(B + (int64_t)(k0 + bk) * ldb + n0 + bn) : (const void*)B, b_in ? 4 : 0);
+    }
+  };
+  float acc[4][2];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) acc[i][0] = acc[i][1] = 0.f;
+  const int ktiles = k_end > k_begin ? (k_end - k_begin + FS_BK - 1) / FS_BK : 0;
+#pragma unroll
+  for (int s = 0; s < FK_STAGES - 1; ++s) {
+    if (s < ktiles) request_tile(k_begin + s * FS_BK, s);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  }
+  for (int kt = 0; kt < ktiles; ++kt) {
+    asm volatile("cp.async.wait_group %0;" ::"n"(FK_STAGES - 2) : "memory");
+    __syncthreads();   // tile kt has landed for every thread, and everybody is done with the slot requested next
+    if (kt + FK_STAGES - 1 < ktiles) request_tile(k_begin + (kt + FK_STAGES - 1) * FS_BK, (kt + FK_STAGES - 1) % FK_STAGES);
+    asm volatile("cp.async.commit_group;" ::: "memory");
+    const int buf = kt % FK_STAGES;
+#pragma unroll
+    for (int kk = 0; kk < FS_BK / 2; ++kk) {
+      const int k = half * (FS_BK / 2) + kk;
+      const float4 a4 = *reinterpret_cast<const float4*>(&As[buf][k][ty * 4]);
+      const float2 b2 = *reinterpret_cast<const float2*>(&Bs[buf][k][tx * 2]);
+      const float a[4] = {a4.x, a4.y, a4.z, a4.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        acc[i][0] = fmaf(a[i], b2.x, acc[i][0]);
+        acc[i][1] = fmaf(a[i], b2.y, acc[i][1]);
+      }
+    }
+  }
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  // second half -> first half of this CTA
+  if (half == 1) {
+    float4* mine = reinterpret_cast<float4*>(partials + t * 8);
+    mine[0] = make_float4(acc[0][0], acc[0][1], acc[1][0], acc[1][1]);
+    mine[1] = make_float4(acc[2][0], acc[2][1], acc[3][0], acc[3][1]);
+  }
+  __syncthreads();
+  const int part = (int)blockIdx.z;
+  if (half == 0) {
+    const float* theirs = partials + t * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e >> 1][e & 1] += theirs[e];
+    if (part != 0) {   // this CTA's sums -> slot `part` of the first CTA
+      const uint32_t local = smem_u32(partials + (part * (F_THREADS / 2) + t) * 8);
+      uint32_t remote;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, 0;" : "=r"(remote) : "r"(local));
+#pragma unroll
+      for (int e = 0; e < 8; e += 4)
+        asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(remote + 4u * e), "f"(acc[e >> 1][0]),
+                     "f"(acc[e >> 1][1]), "f"(acc[(e >> 1) + 1][0]), "f"(acc[(e >> 1) + 1][1])
+                     : "memory");
+    }
+  }
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  if (part != 0 || half != 0) return;
+  for (int other = 1; other < KPARTS; ++other) {
+    const float4* theirs = reinterpret_cast<const float4*>(partials + (other * (F_THREADS / 2) + t) * 8);
+    const float4 lo = theirs[0], hi = theirs[1];
+    acc[0][0] += lo.x; acc[0][1] += lo.y; acc[1][0] += lo.z; acc[1][1] += lo.w;
+    acc[2][0] += hi.x; acc[2][1] += hi.y; acc[3][0] += hi.z; acc[3][1] += hi.w;
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 2; ++j) {
+      const int r = m0 + ty * 4 + i, c = n0 + tx * 2 + j;
       if (r < M && c < N) C[(int64_t)r * ldc + c] = acc[i][j];
     }
 }
@@ -242,7 +321,7 @@ static int launch_small_split(const float* A, const float* B, float* C, int64_t 
   attr[0].val.clusterDim.z = KPARTS;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_f32_small_kernel<KPARTS>, A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc));
+  DTN_CUDA_CHECK(cudaLaunchKernelEx(&cfg, gemm_f32_splitk_kernel<KPARTS>, A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc));
   return DTN_OK;
 }
 
@@ -362,11 +441,15 @@ int gemm_f32_launch(const float* A, const float* B, float* C, int64_t M, int64_t
     // CTAs along k put 32 or 64 SMs to work instead of 8. Only when the caller allows another k order
     // (`split_k_allowed`: contractions the reference itself computes with atomic partial sums).
     const int64_t tiles32 = (int64_t)small_grid.x * small_grid.y;
-    if (split_k_allowed && tiles32 * 8 <= (int64_t)sm_count() && K >= 8 * FS_BK * 2 && small_grid.y <= 65535)
+    static const int parts_limit = [] {
+      const char* text = getenv("DTN_GEMM_F32_KPARTS");   // tuning aid: 1 or 4 caps the k-split
+      return text ? atoi(text) : 8;
+    }();
+    if (split_k_allowed && parts_limit >= 8 && tiles32 * 8 <= (int64_t)sm_count() && K >= 8 * FS_BK * 2 && small_grid.y <= 65535)
       return launch_small_split<8>(A, B, C, M, N, K, lda, ldb, ldc, s);
-    if (split_k_allowed && tiles32 * 4 <= (int64_t)sm_count() && K >= 4 * FS_BK * 2 && small_grid.y <= 65535)
+    if (split_k_allowed && parts_limit >= 4 && tiles32 * 4 <= (int64_t)sm_count() && K >= 4 * FS_BK * 2 && small_grid.y <= 65535)
       return launch_small_split<4>(A, B, C, M, N, K, lda, ldb, ldc, s);
-    gemm_f32_small_kernel<1><<<small_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
+    gemm_f32_small_kernel<<<small_grid, F_THREADS, 0, s>>>(A, B, C, (int)M, (int)N, (int)K, lda, ldb, ldc);
     DTN_LAUNCH_CHECK("gemm_f32_small_kernel");
     return DTN_OK;
   }
