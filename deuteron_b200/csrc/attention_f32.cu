@@ -160,7 +160,7 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
       for (int r = 0; r < kRounds; ++r) s[r] = 0.f;
       const float* qrow = qs + warp * depth;
       int d = 0;
-      if (depth % 4 == 0) {   // four query values per broadcast load; the products are added in the same order
+      if (depth % 4 == 0 && kRounds >= 4) {   // four query values per broadcast load; the products are added in the same order
 #pragma unroll 2
         for (; d < depth; d += 4) {
           const float4 q4 = *reinterpret_cast<const float4*>(qrow + d);
@@ -202,7 +202,7 @@ attention_staged_kernel(const float* __restrict__ q, const float* __restrict__ k
       for (int c = 0; c < CG; ++c) acc[c] *= alpha;
       const float* wrow = ws + warp * SK;
       int k = 0;
-      if (stage_keys == SK) {   // four weights per broadcast load, the same order of additions
+      if (CG == 1 && stage_keys == SK) {   // one column group: four weights per broadcast load, the same order of additions (slower with two groups)
 #pragma unroll 4
         for (; k < SK; k += 4) {
           const float4 w4 = *reinterpret_cast<const float4*>(wrow + k);
