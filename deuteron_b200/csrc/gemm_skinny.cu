@@ -19,14 +19,17 @@
 //     m16n8k8 for tf32) into FP32 accumulators: column 2g feeds one n8 tile, column 2g+1 the other, so that after the
 //     products a thread owns four consecutive output columns of rows g and g+8.
 //   * A CTA's range ends inside a column block more often than not, and its two k-halves hold separate sums. Each
-//     warp writes its 16 x 16 partial sums to the workspace and counts itself in on a per-(column block, column group)
-//     counter; the warp that arrives last adds the partial sums of all contributors in (CTA, k-half) order (a fixed
-//     order: the result does not depend on who was last) and writes C. Nobody waits for anybody.
+//     warp writes its 16 x 16 partial sums to the workspace and marks its slot's arrival flag with the launch's token;
+//     the warp that then finds every contributor's flag set adds the partial sums of all contributors in (CTA, k-half)
+//     order (a fixed order: the result does not depend on who was last) and writes C. Nobody waits for anybody, and
+//     nothing in the workspace has to be cleared before a launch.
 //
 // Every wait on a barrier is bounded (sm100_ptx.cuh); a wait that gives up records where in the device status word.
 #include <cuda.h>
 #include <stdlib.h>
 
+#include <atomic>
+#include <chrono>
 #include <mutex>
 
 #include "dtn_common.cuh"
@@ -99,7 +102,7 @@ __host__ __device__ __forceinline__ int skinny_owner(long long x, long long unit
 template <int MODE /*0 = bf16x3, 1 = tf32x3*/>
 __global__ void __launch_bounds__(K_THREADS, 1)
 gemm_x3_skinny_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_a, float* __restrict__ C, int M, int N,
-                      int K, int64_t ldc, float* __restrict__ partials, int* __restrict__ counters, int c_vec_ok,
+                      int K, int64_t ldc, float* __restrict__ partials, unsigned long long* __restrict__ flags, unsigned long long token, int c_vec_ok,
                       int* __restrict__ status) {
   using Cfg = SkinnyCfg<MODE>;
   extern __shared__ uint8_t skinny_smem[];
@@ -243,13 +246,24 @@ gemm_x3_skinny_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_con
     float* mine = slot_of((int)blockIdx.x, k_half);
     *reinterpret_cast<float4*>(mine + g * 16 + 4 * t) = make_float4(lower[0], lower[1], lower[2], lower[3]);
     *reinterpret_cast<float4*>(mine + (g + 8) * 16 + 4 * t) = make_float4(upper[0], upper[1], upper[2], upper[3]);
+    // Arrival without a counter, so that nothing has to be cleared before the launch: a contributor writes the launch's
+    // token into the flag of its slot and then looks at the flags of all the block's contributors. A sequentially
+    // consistent fence between the two makes sure that at least one contributor sees every flag set; when two do,
+    // both add the same sums in the same order and write the same bits. Whoever adds clears the flags afterwards
+    // (a graph replay repeats the token); a flag left over from other use of the workspace is not the token.
+    auto flag_of = [&](int w, int h) { return flags + ((size_t)(w + nt) * 2 + h) * K_COLUMN_GROUPS + group; };
     __threadfence();
     __syncwarp();
-    int arrived = 0;
-    if (lane == 0) arrived = atomicAdd(counters + nt * K_COLUMN_GROUPS + group, 1);
-    arrived = __shfl_sync(0xffffffffu, arrived, 0);
-    if (arrived != 2 * (last - first) + 1) return;   // somebody else will finish this block
-    __threadfence();
+    if (lane == 0) asm volatile("st.release.gpu.global.u64 [%0], %1;" ::"l"(flag_of((int)blockIdx.x, k_half)), "l"(token) : "memory");
+    __syncwarp();
+    asm volatile("fence.sc.gpu;" ::: "memory");
+    bool all_in = true;
+    for (int c = 2 * first + lane; c <= 2 * last + 1; c += 32) {
+      unsigned long long seen;
+      asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(seen) : "l"(flag_of(c >> 1, c & 1)) : "memory");
+      all_in = all_in && seen == token;
+    }
+    if (!__all_sync(0xffffffffu, all_in)) return;   // somebody else will finish this block
     float sum0[4] = {0.f, 0.f, 0.f, 0.f}, sum1[4] = {0.f, 0.f, 0.f, 0.f};
     for (int c = 2 * first; c <= 2 * last + 1; ++c) {
       const float* theirs = slot_of(c >> 1, c & 1);
@@ -264,7 +278,7 @@ gemm_x3_skinny_kernel(const __grid_constant__ CUtensorMap tm_b, const __grid_con
       }
     }
     store_c(sum0, sum1);
-    if (lane == 0) counters[nt * K_COLUMN_GROUPS + group] = 0;   // ready for the next launch
+    for (int c = 2 * first + lane; c <= 2 * last + 1; c += 32) *flag_of(c >> 1, c & 1) = 0ull;   // ready for the next launch
   };
 
   int i = 0;
@@ -378,11 +392,19 @@ static int skinny_workers(int64_t units) {
 }
 
 // Bytes of workspace the kernel needs: two [16][128] blocks of partial sums (one per k-half) per (CTA, column block)
-// pair that can occur, then the counters.
+// pair that can occur, then one 8-byte arrival flag per (block of partial sums, column group).
 size_t gemm_skinny_workspace_bytes(int64_t N, int64_t K) {
   const int64_t k_tiles = (K + K_BK - 1) / K_BK, n_tiles = (N + K_BN - 1) / K_BN;
   const int64_t slots = skinny_workers(k_tiles * n_tiles) + n_tiles;
-  return (size_t)slots * 2 * 16 * K_BN * 4 + (size_t)n_tiles * K_COLUMN_GROUPS * 4;
+  return (size_t)slots * 2 * 16 * K_BN * 4 + (size_t)slots * 2 * K_COLUMN_GROUPS * 8;
+}
+
+// A value no earlier launch of this process has used and that is never zero.
+static unsigned long long skinny_next_token() {
+  static std::atomic<unsigned long long> next{
+      (unsigned long long)std::chrono::steady_clock::now().time_since_epoch().count() * 0x9E3779B97F4A7C15ull};
+  unsigned long long token = next.fetch_add(1) + 1;
+  return token ? token : next.fetch_add(1) + 1;
 }
 
 // True when the kernel can take the product: at most 16 rows, A and B addressable by tensor maps.
@@ -407,8 +429,7 @@ static int gemm_skinny_launch_mode(const float* A, const float* B, float* C, int
   const int64_t k_tiles = (K + K_BK - 1) / K_BK, n_tiles = (N + K_BN - 1) / K_BN;
   const int workers = skinny_workers(k_tiles * n_tiles);
   float* partials = static_cast<float*>(workspace);
-  int* counters = reinterpret_cast<int*>(partials + (size_t)(workers + n_tiles) * 2 * 16 * K_BN);
-  DTN_CUDA_CHECK(cudaMemsetAsync(counters, 0, (size_t)n_tiles * K_COLUMN_GROUPS * 4, s));
+  unsigned long long* flags = reinterpret_cast<unsigned long long*>(partials + (size_t)(workers + n_tiles) * 2 * 16 * K_BN);
   int* status = device_status_word();
   DTN_REQUIRE(status != nullptr, DTN_ERR_CUDA, "gemm: could not allocate the device status word");
   CUtensorMap map_a;   // A as [M rows][K]: boxes of 64 k x 16 rows, rows past M read as zeros
@@ -430,7 +451,7 @@ static int gemm_skinny_launch_mode(const float* A, const float* B, float* C, int
     DTN_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
     attr_dev = dev;
   }
-  kernel<<<(unsigned)workers, K_THREADS, Cfg::kSmemBytes, s>>>(map, map_a, C, (int)M, (int)N, (int)K, ldc, partials, counters, c_vec, status);
+  kernel<<<(unsigned)workers, K_THREADS, Cfg::kSmemBytes, s>>>(map, map_a, C, (int)M, (int)N, (int)K, ldc, partials, flags, skinny_next_token(), c_vec, status);
   DTN_LAUNCH_CHECK("gemm_x3_skinny_kernel");
   return DTN_OK;
 }

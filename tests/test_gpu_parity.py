@@ -598,6 +598,31 @@ def _check_skinny_shapes(cuda, mode):
         wide[:, 4:n + 4] = right
         shifted = ops.gemm(left, wide[:, 4:n + 4], mode)
         assert cuda.equal(shifted, produced), (m, n, k)
+        # the workspace needs no preparation: all ones, all zeros, what the last launch left, other launches' leftovers
+        scratch = cuda.empty(ops.gemm_workspace_bytes(mode, m, n, k) + 2048, dtype=cuda.uint8, device='cuda:0')
+        for fill in (0xFF, 0x00, None, None, 0x3C):
+            if fill is not None:
+                scratch.fill_(fill)
+            assert cuda.equal(ops.gemm(left, right, mode, workspace=scratch), produced), (m, n, k, fill)
+    # back to back in one CUDA graph (every replay repeats the launch's arrival token)
+    m, n, k = 16, 2048, 4096
+    left, right = to_device(cuda, R.seeded_uniform(7, (m, k))), to_device(cuda, R.seeded_uniform(11, (k, n)))
+    expected = ops.gemm(left, right, mode).clone()
+    out = cuda.empty_like(expected)
+    scratch = cuda.empty(ops.gemm_workspace_bytes(mode, m, n, k) + 2048, dtype=cuda.uint8, device='cuda:0')
+    stream = cuda.cuda.Stream()
+    with cuda.cuda.stream(stream):
+        ops.gemm(left, right, mode, out=out, workspace=scratch)
+        graph = cuda.cuda.CUDAGraph()
+        with cuda.cuda.graph(graph, stream=stream):
+            for _ in range(8):
+                ops.gemm(left, right, mode, out=out, workspace=scratch)
+        for _ in range(5):
+            out.zero_()
+            graph.replay()
+            stream.synchronize()
+            assert cuda.equal(out, expected)
+    ops.check_device_status()
 
 
 def test_gemm_f32_mode_shapes(cuda):
