@@ -36,7 +36,7 @@ _OPERATORS = {
     4: 'fmaxf({a}, {b})', 5: 'fminf({a}, {b})', 6: 'fmaxf({a}, 0.0f)', 7: 'dtn_exp({a})', 8: 'dtn_sqrt({a})',
     9: 'dtn_rsqrt({a})', 10: 'dtn_rcp({a})', 11: '(-{a})', 12: 'fabsf({a})', 13: '({a})',
 }
-KINDS = ('elementwise_program', 'row_fused', 'row_reduce')   # plan kinds this module may take
+KINDS = ('elementwise_program', 'row_fused', 'row_reduce', 'attention')   # plan kinds this module may take
 SMALL_ELEMENTS = 1 << 16      # launches above this many elements are bandwidth-bound: the library's kernels take them
 _COMPONENTS = 'xyzw'
 
@@ -217,6 +217,87 @@ def _float_bits(value: float) -> str:
     return hex(struct.unpack('<I', struct.pack('<f', float(value)))[0])
 
 
+# ------------------------------------------------------------------------------------------------
+# small attention (classify._classify_attention / dtn_attention_f32)
+# ------------------------------------------------------------------------------------------------
+ATTENTION_MAX_ROWS = 1024
+
+
+def attention_source(params: dict, buffers: dict) -> dict | None:
+    """CUDA source of the reference-layout attention (q[rows, depth], kt[depth, keys], v[keys, cols]) for one shape:
+    a warp per query row and a CTA per warp, every extent a constant, so that the loads of a row's keys and values are
+    all independent and in flight together instead of staged through shared memory behind two barriers. For a few
+    hundred rows of at most 256 keys, where the launch is one warp's chain. The arithmetic and its order are those of
+    csrc/attention_f32.cu's one-stage case (scores by sequential fma over the depth, weights ex2.approx((s - max) *
+    log2 e), mass by the same butterfly, weighted sum by sequential fma over the keys, one approximate reciprocal),
+    so the bits are the library kernel's."""
+    rows, keys, depth, cols = params['rows'], params['keys'], params['depth'], params['cols']
+    if not (1 <= rows <= ATTENTION_MAX_ROWS and 32 <= keys <= 256 and keys % 32 == 0 and 1 <= depth <= 128 and cols in (32, 64)):
+        return None
+    rounds, groups = keys // 32, cols // 32
+    scale = f'__int_as_float({_float_bits(params["scale"])})'
+    # The values are not needed before the weights exist: where they fit, they are requested into shared memory as
+    # asynchronous copies before the first score is computed and arrive behind the scores and the softmax.
+    staged = keys * cols * 4 <= 48 * 1024 and buffers['v'][1] % 4 == 0
+    request = f'''
+  __shared__ __align__(16) float vs[KEYS * COLS];
+#pragma unroll
+  for (int i = 0; i < KEYS * COLS / 128; ++i)
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"((unsigned)__cvta_generic_to_shared(vs + 4 * (lane + 32 * i))),
+                 "l"(v + 4 * (lane + 32 * i)) : "memory");
+  asm volatile("cp.async.commit_group;" ::: "memory");''' if staged else ''
+    arrive = '''
+  asm volatile("cp.async.wait_group 0;" ::: "memory");
+  __syncwarp();''' if staged else ''
+    value = 'vs[k * COLS + lane + 32 * c]' if staged else '__ldg(v + k * COLS + lane + 32 * c)'
+    source = PRELUDE + f'''
+extern "C" __global__ void __launch_bounds__(32) dtn_jit_kernel(const float* __restrict__ q, const float* __restrict__ kt,
+                                                                const float* __restrict__ v, float* __restrict__ out) {{
+  constexpr int KEYS = {keys}, DEPTH = {depth}, COLS = {cols}, ROUNDS = {rounds}, GROUPS = {groups};
+  const int row = blockIdx.x, lane = threadIdx.x;
+  const float* qr = q + row * DEPTH;{request}
+  float s[ROUNDS];
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) s[r] = 0.0f;
+#pragma unroll
+  for (int d = 0; d < DEPTH; ++d) {{
+    const float qv = __ldg(qr + d);
+#pragma unroll
+    for (int r = 0; r < ROUNDS; ++r) s[r] = fmaf(qv, __ldg(kt + d * KEYS + lane + 32 * r), s[r]);
+  }}
+  float peak = -__int_as_float(0x7f800000);
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {{
+    s[r] = __fmul_rn(s[r], {scale});
+    peak = fmaxf(peak, s[r]);
+  }}
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, o));
+  float mass = 0.0f;
+#pragma unroll
+  for (int r = 0; r < ROUNDS; ++r) {{
+    s[r] = dtn_ex2(__fmul_rn(__fsub_rn(s[r], peak), 1.4426950408889634f));
+    mass = __fadd_rn(mass, s[r]);
+  }}
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) mass = __fadd_rn(mass, __shfl_xor_sync(0xffffffffu, mass, o));
+  float acc[GROUPS];
+#pragma unroll
+  for (int c = 0; c < GROUPS; ++c) acc[c] = 0.0f;{arrive}
+#pragma unroll
+  for (int k = 0; k < KEYS; ++k) {{
+    const float w = __shfl_sync(0xffffffffu, s[k / 32], k % 32);
+#pragma unroll
+    for (int c = 0; c < GROUPS; ++c) acc[c] = fmaf(w, {value}, acc[c]);
+  }}
+  const float inverse = dtn_rcp(mass);
+#pragma unroll
+  for (int c = 0; c < GROUPS; ++c) out[row * COLS + lane + 32 * c] = __fmul_rn(acc[c], inverse);
+}}
+'''
+    return {'source': source, 'entry': 'dtn_jit_kernel', 'grid': rows, 'block': 32, 'pointers': ['q', 'kt', 'v', 'out'], 'scalars': []}
+
+
 def specialized_source(plan: Any) -> dict | None:
     """The per-program kernel of a plan (source, entry, launch geometry, argument roles), or None."""
     if not enabled():
@@ -226,6 +307,8 @@ def specialized_source(plan: Any) -> dict | None:
             return elementwise_source(plan.params, plan.buffers)
         if plan.kind == 'row_fused':
             return row_source(plan.params, plan.buffers)
+        if plan.kind == 'attention':
+            return attention_source(plan.params, plan.buffers)
         if plan.kind == 'row_reduce' and plan.params['op'] in ('sum', 'max', 'sumsq'):   # a row program with no operators
             reduction = {'rows': plan.params['rows'], 'cols': plan.params['cols'], 'reduce': plan.params['op'], 'inputs': [], 'n_scalar': 0,
                          'out_reg': 0, 'ops': [], 'dst': [], 'a': [], 'b': [], 'per_row': True}

@@ -424,7 +424,7 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
         if spec is not None:
             taken[name] = (plan, spec)
     assert {'p02_scale_shift', 'p03_relu_mul', 'f01_rmsnorm', 'f02_row_softmax', 'f03_l2norm'} <= set(taken)
-    assert all(plan.kind in jit.KINDS for plan, _ in taken.values()) and {'r01_array_sum', 'r04_row_sum'} <= set(taken)
+    assert all(plan.kind in jit.KINDS for plan, _ in taken.values()) and {'r01_array_sum', 'r04_row_sum', 'a01_attention', 'a02_attention_128'} <= set(taken)
     plan, spec = taken['f01_rmsnorm']
     assert spec['grid'] == plan.params['rows'] and spec['pointers'][0] == 'x' and spec['pointers'][-1] == 'out'
     assert 'fmaf(' in spec['source'] and 'dtn_rsqrt' in spec['source'] and '--fmad' not in spec['source']
