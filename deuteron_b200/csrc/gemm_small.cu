@@ -427,7 +427,12 @@ static int gemm_small_launch_mode(const float* A, const float* B, float* C, int6
     const double volume = (double)M * (double)N * (double)K;
     if (M <= 16 && K >= 256) choice = 2;
     else if (volume <= 320.0 * 320.0 * 320.0) choice = 3;
-    else if (volume <= 520.0 * 520.0 * 520.0 && M >= 32) choice = 6;
+    else if (volume <= 520.0 * 520.0 * 520.0 && M >= 32) {
+      // two k groups either way (the same bits); 16-row tiles while they are one wave of CTAs (384^3: 144 CTAs, 5.4 us
+      // against 7.1 us for 72 CTAs of 32 rows), 32-row tiles beyond (512^3: 8.8 us against 9.6 us for 256 CTAs of 16 rows)
+      const int64_t short_tiles = ((M + 15) / 16) * ((N + S_BN - 1) / S_BN);
+      choice = short_tiles <= (int64_t)sm_count() ? 2 : 6;
+    }
     else choice = 1;
   }
   switch (choice) {
