@@ -93,9 +93,9 @@ def elementwise_source(params: dict, buffers: dict) -> dict | None:
 # row programs (classify_rows._row_program / dtn_row_fused)
 # ------------------------------------------------------------------------------------------------
 ROW_PRELUDE = r'''
-// One value per thread -> the row's value in every thread: xor tree inside a warp, then the four warps' results through
+// One value per thread -> the row's value in every thread: xor tree inside a warp, then the warps' results through
 // shared memory, added (or compared) in warp order.
-template <bool MAX>
+template <bool MAX, int WARPS>
 __device__ __forceinline__ float dtn_combine(float v, float* scratch) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -106,7 +106,7 @@ __device__ __forceinline__ float dtn_combine(float v, float* scratch) {
   __syncthreads();
   v = scratch[0];
 #pragma unroll
-  for (int w = 1; w < 4; ++w) v = MAX ? fmaxf(v, scratch[w]) : v + scratch[w];
+  for (int w = 1; w < WARPS; ++w) v = MAX ? fmaxf(v, scratch[w]) : v + scratch[w];
   return v;
 }
 '''
@@ -120,7 +120,13 @@ def row_source(params: dict, buffers: dict) -> dict | None:
     global read), the reduction(s), the scalar stage and the elementwise stage written out operator by operator.
     Register numbering as in csrc/row_fused.cu: r0, r1 = the reduced values, r2 = the element, r3 + i = input i."""
     rows, cols, inputs = params['rows'], params['cols'], params['inputs']
-    if rows < 1 or rows > 65535 or cols < 4 or cols % 4 or cols > ROW_THREADS * 4 * ROW_MAX_VECTORS or rows * cols > SMALL_ELEMENTS:
+    # A row that is only reduced need not stay in registers: it is streamed by as many threads as give each at most
+    # eight vectors (up to 1024: one row of 32 768 values is a CTA's work, and its loads should all be in flight).
+    streamed = params['per_row'] and params['reduce'] != 'softmax'
+    threads = min(1024, max(ROW_THREADS, (cols // 4 + 7) // 8 + 31 & ~31)) if streamed else ROW_THREADS
+    if rows < 1 or rows > 65535 or cols < 4 or cols % 4 or rows * cols > SMALL_ELEMENTS:
+        return None
+    if not streamed and cols > ROW_THREADS * 4 * ROW_MAX_VECTORS:
         return None
     if any(op not in _OPERATORS for op in params['ops']) or params['reduce'] not in ('sum', 'sumsq', 'max', 'softmax'):
         return None
@@ -134,7 +140,7 @@ def row_source(params: dict, buffers: dict) -> dict | None:
         return None
     is_max = reduce in ('max', 'softmax')
     identity = '-__int_as_float(0x7f800000)' if is_max else '0.0f'
-    vectors = (cols // 4 + ROW_THREADS - 1) // ROW_THREADS
+    vectors = (cols // 4 + threads - 1) // threads
     pointer_inputs = [i for i, item in enumerate(inputs) if item['kind'] != 'immediate']
     fold = {'sum': '__fadd_rn({acc}, {v})', 'sumsq': 'fmaf({v}, {v}, {acc})', 'max': 'fmaxf({acc}, {v})', 'softmax': 'fmaxf({acc}, {v})'}[reduce]
     lines = []
@@ -145,8 +151,8 @@ def row_source(params: dict, buffers: dict) -> dict | None:
         lines.append(f'  e{dst} = {apply(op, f"e{a}", f"e{b}")};')
     lines += [f'  return e{out_reg};', '}']
     arguments = ['const float* __restrict__ x'] + [f'const float* __restrict__ p{i}' for i in pointer_inputs] + ['float* __restrict__ out', 'int cols']
-    lines.append(f'extern "C" __global__ void __launch_bounds__({ROW_THREADS}) dtn_jit_kernel({", ".join(arguments)}) {{')
-    lines += ['  __shared__ float scratch[2][4];',
+    lines.append(f'extern "C" __global__ void __launch_bounds__({threads}) dtn_jit_kernel({", ".join(arguments)}) {{')
+    lines += [f'  __shared__ float scratch[2][{threads // 32}];',
               '  const int row = blockIdx.x, tid = threadIdx.x;',
               '  const float4* xr = reinterpret_cast<const float4*>(x + (i64)row * cols);']
     for i, item in enumerate(inputs):
@@ -155,11 +161,16 @@ def row_source(params: dict, buffers: dict) -> dict | None:
         elif item['kind'] == 'immediate':
             lines.append(f'  const float c{i} = __int_as_float({_float_bits(item.get("value", 0.0))});')
     lines.append(f'  const float identity = {identity};')
+    columns = [] if params['per_row'] else [i for i, item in enumerate(inputs) if item['kind'] == 'columns']
     lines.append(f'  float4 v[{vectors}];')
+    for i in columns:   # requested with the row, although the elementwise stage uses them: one trip to memory, not two
+        lines.append(f'  float4 q{i}[{vectors}];')
     lines.append('#pragma unroll')
     lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
-    lines.append(f'    const int j = u * {ROW_THREADS} + tid;')
+    lines.append(f'    const int j = u * {threads} + tid;')
     lines.append('    v[u] = j * 4 < cols ? __ldg(xr + j) : make_float4(identity, identity, identity, identity);')
+    for i in columns:
+        lines.append(f'    q{i}[u] = j * 4 < cols ? __ldg(reinterpret_cast<const float4*>(p{i}) + j) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);')
     lines.append('  }')
     lines.append('  float first = identity;')
     lines.append('#pragma unroll')
@@ -167,14 +178,14 @@ def row_source(params: dict, buffers: dict) -> dict | None:
     for c in _COMPONENTS:
         lines.append('    first = ' + fold.format(acc='first', v=f'v[u].{c}') + ';')
     lines.append('  }')
-    lines.append(f'  first = dtn_combine<{"true" if is_max else "false"}>(first, scratch[0]);')
+    lines.append(f'  first = dtn_combine<{"true" if is_max else "false"}, {threads // 32}>(first, scratch[0]);')
     lines.append('  float second = 0.0f;')
     if reduce == 'softmax':
         lines.append('#pragma unroll')
         lines.append(f'  for (int u = 0; u < {vectors}; ++u)')
         lines.append('    second += (dtn_exp(__fsub_rn(v[u].x, first)) + dtn_exp(__fsub_rn(v[u].y, first))) + '
                      '(dtn_exp(__fsub_rn(v[u].z, first)) + dtn_exp(__fsub_rn(v[u].w, first)));')
-        lines.append('  second = dtn_combine<false>(second, scratch[1]);')
+        lines.append(f'  second = dtn_combine<false, {threads // 32}>(second, scratch[1]);')
     # scalar stage
     initial = {0: 'first', 1: 'second'}
     for i, item in enumerate(inputs):
@@ -189,11 +200,8 @@ def row_source(params: dict, buffers: dict) -> dict | None:
         lines.append('  float4* out_row = reinterpret_cast<float4*>(out + (i64)row * cols);')
         lines.append('#pragma unroll')
         lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
-        lines.append(f'    const int j = u * {ROW_THREADS} + tid;')
+        lines.append(f'    const int j = u * {threads} + tid;')
         lines.append('    if (j * 4 >= cols) continue;')
-        columns = [i for i, item in enumerate(inputs) if item['kind'] == 'columns']
-        for i in columns:
-            lines.append(f'    const float4 q{i} = __ldg(reinterpret_cast<const float4*>(p{i}) + j);')
         lines.append('    float4 result;')
         for c in _COMPONENTS:
             values = []
@@ -201,14 +209,14 @@ def row_source(params: dict, buffers: dict) -> dict | None:
                 if k == 2:
                     values.append(f'v[u].{c}')
                 elif k - 3 in columns:
-                    values.append(f'q{k - 3}.{c}')
+                    values.append(f'q{k - 3}[u].{c}')
                 else:
                     values.append(f'r{k}')
             lines.append(f'    result.{c} = dtn_element({", ".join(values)});')
         lines.append('    out_row[j] = result;')
         lines.append('  }')
     lines.append('}')
-    return {'source': PRELUDE + ROW_PRELUDE + '\n'.join(lines) + '\n', 'entry': 'dtn_jit_kernel', 'grid': rows, 'block': ROW_THREADS,
+    return {'source': PRELUDE + ROW_PRELUDE + '\n'.join(lines) + '\n', 'entry': 'dtn_jit_kernel', 'grid': rows, 'block': threads,
             'pointers': ['x'] + [f'in{i}' for i in pointer_inputs] + ['out'], 'scalars': [('i32', cols)]}
 
 
