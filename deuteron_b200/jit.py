@@ -1,13 +1,15 @@
-"""Per-program kernels for fused elementwise and row programs.
+"""Per-program kernels for small fused elementwise and row programs, row reductions and the attention example.
 
 The library's kernels for these plans take the register program as an argument, which is what a memory-bound launch
 wants (one kernel, any program, the decode paid once per eight elements). A latency-bound launch -- a few thousand
 elements, one wave of threads -- is as long as one thread's instruction chain, and there the decode is most of the
 chain: four to nine times the instructions of a kernel written for the one program. The reference is a compiler and
-emits such a kernel for every workload (compiler/codegen/lower.py). This module does the same for the two plan kinds
-where it matters: it writes the program out as CUDA C++ with every operator inlined, in the operator table's own
-arithmetic (csrc/program.cuh: one rounding per operator, never contracted into fma, the approximate exp / sqrt /
-rsqrt / reciprocal instructions), has NVRTC compile it for sm_100a and launches it through the driver API.
+emits such a kernel for every workload (compiler/codegen/lower.py). This module does the same for the plan kinds
+where it matters (KINDS): it writes the program out as CUDA C++ with every operator inlined, in the operator table's
+own arithmetic (csrc/program.cuh: one rounding per operator, never contracted into fma, the approximate exp / sqrt /
+rsqrt / reciprocal instructions), has NVRTC compile it for sm_100a and launches it through the driver API. The
+reference-layout attention of a few hundred rows gets a kernel unrolled for its shape in the same way, with the
+library kernel's order of operations.
 
 Used by LocalRunner for small launches only; everything else, and every program this module does not take, runs the
 library's kernels. `DTN_JIT=0` turns it off. Nothing here needs a GPU to generate or compile (NVRTC targets an
