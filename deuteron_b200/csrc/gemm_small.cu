@@ -90,7 +90,7 @@ __device__ __forceinline__ void mma_tf32(float (&c)[4], const uint32_t (&a)[4], 
 
 // KSPLIT = 2: eight warps, the second group of four takes the upper half of every k-tile and the two partial
 // accumulators are added through shared memory at the end (twice the warps to hide conversion and MMA latency).
-template <int MODE /*0 = bf16x3, 1 = tf32x3*/, bool ALIGNED, int BM, int BK, int STAGES, int KSPLIT>
+template <int MODE /*0 = bf16x3, 1 = tf32x3*/, int ALIGNED /*0: any addresses, 1: 128-bit accesses, 2: and only full tiles*/, int BM, int BK, int STAGES, int KSPLIT>
 __global__ void __launch_bounds__(S_THREADS * KSPLIT)
 gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, float* __restrict__ C, int M, int N, int K,
                      int64_t lda, int64_t ldb, int64_t ldc) {
@@ -104,8 +104,11 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
   const int wm = BM == 64 ? (warp >> 1) * 32 : (BM == 32 ? (warp >> 1) * 16 : 0), wn = BM == 16 ? warp * 16 : (warp & 1) * 32;
   const uint32_t smem_base = smem_u32(small_smem);
 
+  // EXACT: every tile of the launch is full (M, N and K are multiples of the tile), so no access needs a bounds check
+  // (512^3: 8.85 -> about 8.2 us; a tenth of the instructions were comparisons and selects on the extents)
+  constexpr bool EXACT = ALIGNED == 2;
   const int b_piece_n = (tid & 15) * 4;
-  const int b_col_bytes = min(max((N - (n0 + b_piece_n)) * 4, 0), 16);
+  const int b_col_bytes = EXACT ? 16 : min(max((N - (n0 + b_piece_n)) * 4, 0), 16);
   const float* b_col = B + n0 + b_piece_n;
   const uint32_t b_piece_smem = (uint32_t)b_piece_n * 4u;
   static_assert((BK * 16) % (S_THREADS * KSPLIT) == 0, "B tile must divide among the threads");
@@ -119,8 +122,9 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
 #pragma unroll
       for (int i = 0; i < BK * 16 / kThreads; ++i) {
         const int br = (tid >> 4) + i * (kThreads >> 4);
-        const int bbytes = (k0 + br < K) ? b_col_bytes : 0;
-        cp_async_16(b_s + b_piece_smem + (uint32_t)(br * Cfg::kLdb) * 4u, bbytes ? (const void*)(b_col + (int64_t)(k0 + br) * ldb) : (const void*)B, bbytes);
+        const int bbytes = (EXACT || k0 + br < K) ? b_col_bytes : 0;
+        cp_async_16(b_s + b_piece_smem + (uint32_t)(br * Cfg::kLdb) * 4u,
+                    (EXACT || bbytes) ? (const void*)(b_col + (int64_t)(k0 + br) * ldb) : (const void*)B, bbytes);
       }
     } else {
 #pragma unroll 4
@@ -145,7 +149,7 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
       const int v = i * kThreads + tid, ar = v / (BK / 4), ak = (v % (BK / 4)) * 4;
       const int gr = m0 + ar, gk = k0 + ak;
       const float* p = A + (int64_t)gr * lda + gk;
-      if (ALIGNED && gr < M && gk + 3 < K) {
+      if (EXACT || (ALIGNED && gr < M && gk + 3 < K)) {
         r[i] = __ldg(reinterpret_cast<const float4*>(p));
       } else {
         const bool row_in = gr < M;
@@ -345,9 +349,9 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int row = m0 + wm + i * 16 + g + h * 8;
-        if (row >= M) continue;
+        if (!EXACT && row >= M) continue;
         float* p = C + (int64_t)row * ldc + col;
-        if (ALIGNED && col + 1 < N) {
+        if (EXACT || (ALIGNED && col + 1 < N)) {
           *reinterpret_cast<float2*>(p) = make_float2(acc[i][j][2 * h], acc[i][j][2 * h + 1]);
         } else {
           if (col < N) p[0] = acc[i][j][2 * h];
@@ -357,7 +361,7 @@ gemm_x3_small_kernel(const float* __restrict__ A, const float* __restrict__ B, f
     }
 }
 
-template <int MODE, bool ALIGNED, int BM, int BK, int STAGES, int KSPLIT>
+template <int MODE, int ALIGNED, int BM, int BK, int STAGES, int KSPLIT>
 static int gemm_small_launch_cfg(const float* A, const float* B, float* C, int64_t M, int64_t N, int64_t K, int64_t lda,
                                  int64_t ldb, int64_t ldc, cudaStream_t s, int k_parts = 1) {
   using Cfg = SmallCfg<MODE, BM, BK, STAGES>;
@@ -402,8 +406,10 @@ static int gemm_small_launch_mode(const float* A, const float* B, float* C, int6
     return text ? atoi(text) : 0;
   }();
 #define DTN_SMALL_CFG_ST(BM, BK, KS, ST)                                                                              \
-  return aligned ? gemm_small_launch_cfg<MODE, true, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)      \
-                 : gemm_small_launch_cfg<MODE, false, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)
+  return !aligned ? gemm_small_launch_cfg<MODE, 0, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)         \
+         : (M % BM == 0 && N % S_BN == 0 && K % BK == 0)                                                               \
+             ? gemm_small_launch_cfg<MODE, 2, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)              \
+             : gemm_small_launch_cfg<MODE, 1, BM, BK, ST, KS>(A, B, C, M, N, K, lda, ldb, ldc, s, k_parts)
 #define DTN_SMALL_CFG(BM, BK, KS) DTN_SMALL_CFG_ST(BM, BK, KS, 4)
   // Skinny products have too few output tiles to fill the device (128 for N = 8192): clusters of CTAs along k share a
   // tile. DTN_GEMM_SKINNY_KPARTS overrides the count (1, 2 or 4).
