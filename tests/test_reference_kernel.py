@@ -140,6 +140,13 @@ def test_every_reference_emitted_kernel_beside_the_native_one(cuda, name):
         if rows is not None:
             ours, ref = ours[rows], ref[rows]
         scale = float(expected.abs().max().item())
+        if name.startswith(('row_sum', 'open_r0')):
+            # A sum's rounding error is proportional to the sum of the magnitudes, not to the sum: 65 536 values of
+            # either sign cancel to a few hundred, and two correct summation orders then differ by more than an ulp
+            # of the result.
+            x = inputs['x'].double()
+            magnitudes = (x if x.dim() == 2 else x[None, :]).abs().sum(dim=1).max()
+            scale = max(scale, float((magnitudes / x.numel() if name == 'open_r03_mean' else magnitudes).item()))
         error_mine = float((ours - expected.reshape(ours.shape)).abs().max().item()) / scale
         error_ref = float((ref - expected.reshape(ref.shape)).abs().max().item()) / scale
         assert error_ref < 1e-3, (name, key, error_ref)     # the reference kernel itself ran correctly here
