@@ -139,9 +139,36 @@ def _row_fused(reduce: str, x: torch.Tensor, program: list[tuple[str, int, int, 
     _flat(out, torch.float32, 'out')
     params = {'reduce': reduce, 'rows': rows, 'cols': cols, 'inputs': described, 'n_scalar': n_scalar, 'out_reg': out_reg,
               'ops': [native.ELEMENTWISE_OPS[p[0]] for p in program], 'dst': [p[1] for p in program],
-              'a': [p[2] for p in program], 'b': [p[3] for p in program]}
-    native.row_fused(params, x.data_ptr(), pointers, out.data_ptr(), ldx, 0 if per_row else max(cols, 1), _stream())
+              'a': [p[2] for p in program], 'b': [p[3] for p in program], 'per_row': per_row}
+    if not _row_specialized(params, x, pointers, out, ldx):
+        native.row_fused(params, x.data_ptr(), pointers, out.data_ptr(), ldx, 0 if per_row else max(cols, 1), _stream())
     return out
+
+
+_row_kernels: dict[tuple, tuple | None] = {}
+
+
+def _row_specialized(params: dict, x: torch.Tensor, pointers: list, out: torch.Tensor, ldx: int) -> bool:
+    """Runs the kernel written for this one program (jit.py) when there is one: dense rows, 16-byte aligned buffers.
+    With no program to decode and a row's loads all requested up front it is the faster kernel at every size it
+    takes; False sends the launch to the library's kernel."""
+    from . import jit
+    addresses = [x.data_ptr(), out.data_ptr(), *[p for p in pointers if p is not None]]
+    if not jit.enabled() or ldx != params['cols'] or params['rows'] == 0 or any(a % 16 for a in addresses):
+        return False
+    device = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    key = (device, repr(sorted(params.items())))
+    if key not in _row_kernels:
+        buffers = {'x': ('x', 0), 'out': ('out', 0), **{f'in{i}': (f'in{i}', 0) for i in range(len(pointers))}}
+        spec = jit.row_source(params, buffers)
+        kernel = jit.kernel_for(spec, device) if spec is not None else None
+        _row_kernels[key] = (spec, kernel) if kernel is not None else None
+    entry = _row_kernels[key]
+    if entry is None:
+        return False
+    roles = {'x': x.data_ptr(), 'out': out.data_ptr(), **{f'in{i}': p for i, p in enumerate(pointers)}}
+    jit.launch(entry[0], entry[1], roles.__getitem__, _stream())
+    return True
 
 
 def row_softmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:

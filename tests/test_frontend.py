@@ -428,9 +428,9 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
     plan, spec = taken['f01_rmsnorm']
     assert spec['grid'] == plan.params['rows'] and spec['pointers'][0] == 'x' and spec['pointers'][-1] == 'out'
     assert 'fmaf(' in spec['source'] and 'dtn_rsqrt' in spec['source'] and '--fmad' not in spec['source']
-    # outside the conditions: 70_004 elements (above the size limit), f16 storage, a wide row
-    graph, meta = schedules.pointwise_example('affine', 70_004)
-    assert jit.specialized_source(compile_kernel(graph, meta).plan) is None
+    # outside the conditions: f16 storage, a wide row, a long plain reduction
+    graph, meta = schedules.row_reduce_example(1, 1 << 20)
+    assert jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan) is None
     graph, meta = schedules.f16_storage_example('affine', count=512)
     assert jit.specialized_source(compile_kernel(graph, meta).plan) is None
     graph, meta = schedules.row_softmax_example(rows=2, cols=8192)

@@ -131,7 +131,9 @@ def test_pointwise_workloads_are_exact(runner):
 PER_PROGRAM_CASES = [
     (schedules.pointwise_example, dict(kind='affine', count=4096)), (schedules.pointwise_example, dict(kind='affine', count=4)),
     (schedules.pointwise_example, dict(kind='affine', count=65536)), (schedules.pointwise_example, dict(kind='relu_multiply', count=2048)),
-    (schedules.pointwise_example, dict(kind='relu_multiply', count=1028)),
+    (schedules.pointwise_example, dict(kind='relu_multiply', count=1028)), (schedules.pointwise_example, dict(kind='affine', count=4_000_004)),
+    (schedules.rms_norm_example, dict(rows=3000, cols=1024)), (schedules.row_softmax_example, dict(rows=20000, cols=128, block=32)),
+    (schedules.l2_norm_example, dict(rows=1001, cols=4096)),
     (schedules.row_softmax_example, dict(rows=64, cols=256)), (schedules.row_softmax_example, dict(rows=3, cols=640)),
     (schedules.row_softmax_example, dict(rows=5, cols=4096)), (schedules.row_softmax_example, dict(rows=2, cols=96, block=32)),
     (schedules.rms_norm_example, dict(rows=64, cols=1024)), (schedules.rms_norm_example, dict(rows=7, cols=3072)),
@@ -327,6 +329,14 @@ def test_row_reductions_full_size(cuda):
 ROW_RTOL = 1e-5
 
 
+@pytest.fixture(params=['1', '0'], ids=['per-program-kernels', 'library-kernels'])
+def row_paths(request, monkeypatch):
+    """The row operators run a kernel compiled for the one program where there is one (jit.py) and the library's kernel
+    otherwise; `DTN_JIT=0` sends everything to the library. Both are held to the same bars."""
+    monkeypatch.setenv('DTN_JIT', request.param)
+    return request.param
+
+
 def test_row_kernels_in_the_reference_launch_shapes(runner):
     run = lambda graph, meta: runner.run_kernel(meta['kernels'][0], compile_kernel(graph, meta, arch='sm_100a'), warmup=0, iters=1,
                                                 samples=1)['outputs']
@@ -344,7 +354,7 @@ def test_row_kernels_in_the_reference_launch_shapes(runner):
 
 
 @pytest.mark.parametrize('rows,cols', [(64, 256), (5, 1000), (3, 1001), (1, 8192), (2, 8196), (7, 40000), (300, 33), (1, 1), (1100, 512)])
-def test_row_kernels_against_float64_at_many_shapes(cuda, rows, cols):
+def test_row_kernels_against_float64_at_many_shapes(cuda, rows, cols, row_paths):
     x = R.seeded_normal(7, (rows, cols)) * np.float32(3.0)
     w = R.seeded_normal(8, (cols,))
     dx, dw = to_device(cuda, x), to_device(cuda, w)
@@ -355,7 +365,7 @@ def test_row_kernels_against_float64_at_many_shapes(cuda, rows, cols):
     assert np.all(np.abs(ops.row_mean(dx).cpu().numpy() - R.row_mean_f64(x)) <= bound)
 
 
-def test_row_kernel_edge_cases(cuda):
+def test_row_kernel_edge_cases(cuda, row_paths):
     # strided rows and a misaligned origin take the scalar path and give the same values as the aligned path
     base = cuda.randn((16, 1030), device='cuda:0', generator=cuda.Generator(device='cuda:0').manual_seed(3))
     view = base[:, 1:1025]
@@ -389,7 +399,7 @@ def test_row_kernel_edge_cases(cuda):
         ops.rms_norm(cuda.zeros((4, 8), device='cuda:0'), cuda.zeros(3, device='cuda:0'))
 
 
-def test_row_kernels_full_size(cuda):
+def test_row_kernels_full_size(cuda, row_paths):
     """65536 x 4096 (1 GiB): size-independent properties. Softmax rows sum to one and are invariant under a shift of the
     row; normalised rows have unit norm; the RMS norm with unit weight has mean square one."""
     rows, cols = 65536, 4096
