@@ -159,6 +159,8 @@ def _row_specialized(params: dict, x: torch.Tensor, pointers: list, out: torch.T
     device = x.device.index if x.device.index is not None else torch.cuda.current_device()
     key = (device, repr(sorted(params.items())))
     if key not in _row_kernels:
+        if torch.cuda.is_current_stream_capturing():   # a module is not loaded inside a capture: the library kernel this once
+            return False
         buffers = {'x': ('x', 0), 'out': ('out', 0), **{f'in{i}': (f'in{i}', 0) for i in range(len(pointers))}}
         spec = jit.row_source(params, buffers)
         kernel = jit.kernel_for(spec, device) if spec is not None else None
