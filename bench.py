@@ -304,7 +304,7 @@ def reference_kernel_latency_us(torch, name: str, launches: int = 200, samples: 
     records = ref_kernel.manifest()
     if name not in records:
         return None
-    from deuteron_b200 import argument_array
+    from deuteron_b200 import argument_array, jit
     record = records[name]
     device = torch.device('cuda', 0)
     buffers = {arg['name']: torch.from_numpy(argument_array(arg)).to(device) for arg in record['args']}
@@ -312,9 +312,9 @@ def reference_kernel_latency_us(torch, name: str, launches: int = 200, samples: 
     stream = torch.cuda.Stream(device)
 
     def timed(kernel) -> float:
-        def call():
+        def call():   # the reference's runner clears `zero_outputs` with cuMemsetD8Async before every launch
             for output in record.get('zero_outputs', []):
-                buffers[output].zero_()
+                jit.memset_zero(buffers[output].data_ptr(), buffers[output].numel() * buffers[output].element_size(), stream.cuda_stream)
             kernel.launch(pointers, stream.cuda_stream)
         with torch.cuda.stream(stream):
             return _graph_latency_us(torch, stream, call, launches, samples)

@@ -423,6 +423,16 @@ class Kernel:
             raise OSError(f'cuLaunchKernel failed with CUresult {status}')
 
 
+def memset_zero(address: int, nbytes: int, stream: int) -> None:
+    """cuMemsetD8Async of zeros on `stream` (a memset node when the stream is being captured)."""
+    driver = _library('libcuda.so.1')
+    if driver is None:
+        raise OSError('libcuda.so.1 is not available')
+    status = driver.cuMemsetD8Async(ct.c_uint64(address), ct.c_ubyte(0), ct.c_size_t(nbytes), ct.c_void_p(stream))
+    if status != 0:
+        raise OSError(f'cuMemsetD8Async failed with CUresult {status}')
+
+
 def kernel_for(spec: dict, device: int, arch: str = 'sm_100a') -> Kernel | None:
     """The loaded kernel of a specialised source on `device` (whose context must be current), or None."""
     key = (device, hashlib.sha256(spec['source'].encode()).hexdigest())

@@ -441,8 +441,9 @@ class LocalRunner:
 
             def enqueue(with_resets: bool = True) -> None:
                 if with_resets:
-                    for view in resets:
-                        view.zero_()
+                    for view in resets:   # a memset, as in the reference's runner (benchmark.py:240-243: cuMemsetD8Async)
+                        if view.numel():
+                            jit.memset_zero(view.data_ptr(), view.numel(), stream)
                 self._enqueue(plan, pointers, stream, workspace)
 
             prepare_seconds = time.perf_counter() - started
