@@ -11,9 +11,9 @@ rsqrt / reciprocal instructions), has NVRTC compile it for sm_100a and launches 
 reference-layout attention of a few hundred rows gets a kernel unrolled for its shape in the same way, with the
 library kernel's order of operations.
 
-Used by LocalRunner and by the row operators of ops.py; every program this module does not take (f16 storage, rows
-longer than 4096 columns or not a multiple of four, misaligned buffers, long plain reductions) runs the library's
-kernels, and so does everything when NVRTC is missing. `DTN_JIT=0` turns it off. Nothing here needs a GPU to generate or compile (NVRTC targets an
+Used by LocalRunner and by the row operators of ops.py; every program this module does not take (rows longer than
+4096 columns or not a multiple of four, misaligned buffers, long plain reductions) runs the library's kernels, and so
+does everything when NVRTC is missing. `DTN_JIT=0` turns it off. Nothing here needs a GPU to generate or compile (NVRTC targets an
 architecture, not a device); loading and launching need the current CUDA context.
 """
 from __future__ import annotations
@@ -31,6 +31,8 @@ __device__ __forceinline__ float dtn_exp(float x) { return dtn_ex2(__fmul_rn(x, 
 __device__ __forceinline__ float dtn_sqrt(float x) { float y; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float dtn_rsqrt(float x) { float y; asm("rsqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ float dtn_rcp(float x) { float y; asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float dtn_h2f(unsigned short h) { float y; asm("cvt.f32.f16 %0, %1;" : "=f"(y) : "h"(h)); return y; }
+__device__ __forceinline__ unsigned short dtn_f2h(float x) { unsigned short h; asm("cvt.rn.f16.f32 %0, %1;" : "=h"(h) : "f"(x)); return h; }
 '''
 
 # operator code (native.ELEMENTWISE_OPS) -> expression over `a` and `b`, in the arithmetic of csrc/program.cuh::prog_apply
@@ -57,40 +59,61 @@ def apply(op: int, a: str, b: str) -> str:
 # ------------------------------------------------------------------------------------------------
 def elementwise_source(params: dict, buffers: dict) -> dict | None:
     """CUDA source of one kernel for the register program `params`, or None when this module does not take it:
-    FP32 buffers only, a multiple of four elements, every vector buffer at a multiple of four elements from its start
-    (so that 128-bit accesses are aligned). Any size: with nothing to decode the kernel also streams faster than the
-    library's (x * a + b over 2^26 elements: 6.5 against 5.6 TB/s)."""
+    a multiple of four elements, every vector buffer at a multiple of four elements from its start (so that its
+    vector accesses are aligned). f16 buffers are widened exactly on load and the result is rounded to nearest even
+    on store, as in csrc/elementwise_program.cu; a thread takes eight elements when there is an f16 buffer and the
+    count allows, four otherwise. Any size: with nothing to decode the kernel also streams faster than the library's
+    (x * a + b over 2^26 FP32 elements: 6.5 against 5.6 TB/s)."""
     inputs, n = params['inputs'], params['n']
-    if params['out_f16'] or any(spec['f16'] for spec in inputs) or n < 4 or n % 4:
+    if n < 4 or n % 4 or any(op not in _OPERATORS for op in params['ops']):
         return None
-    if any(op not in _OPERATORS for op in params['ops']):
+    vector_offsets = [buffers['out'][1]] + [buffers[f'in{i}'][1] for i, spec in enumerate(inputs) if not spec['scalar']]
+    if any(offset % 4 for offset in vector_offsets):
         return None
-    if buffers['out'][1] % 4 or any(buffers[f'in{i}'][1] % 4 for i, spec in enumerate(inputs) if not spec['scalar']):
-        return None
+    halves = params['out_f16'] or any(spec['f16'] for spec in inputs)
+    width = 8 if halves and n % 8 == 0 and not any(offset % 8 for offset in vector_offsets) else 4
     registers = max([params['out_reg'], len(inputs) - 1, *params['dst'], *params['a'], *params['b']]) + 1
     lines = ['__device__ __forceinline__ float dtn_element(' + ', '.join(f'float in{i}' for i in range(len(inputs))) + ') {']
     lines.append('  float ' + ', '.join(f'r{k} = {"in%d" % k if k < len(inputs) else "0.0f"}' for k in range(registers)) + ';')
     for op, dst, a, b in zip(params['ops'], params['dst'], params['a'], params['b']):
         lines.append(f'  r{dst} = {apply(op, f"r{a}", f"r{b}")};')
     lines += [f'  return r{params["out_reg"]};', '}']
-    arguments = ', '.join(f'const float* __restrict__ p{i}' for i in range(len(inputs)))
-    lines.append(f'extern "C" __global__ void __launch_bounds__(256) dtn_jit_kernel({arguments}{", " if inputs else ""}float* __restrict__ out, i64 vectors) {{')
+    arguments = ', '.join(f'const void* __restrict__ p{i}' for i in range(len(inputs)))
+    lines.append(f'extern "C" __global__ void __launch_bounds__(256) dtn_jit_kernel({arguments}{", " if inputs else ""}void* __restrict__ out, i64 pieces) {{')
     lines.append('  const i64 v = (i64)blockIdx.x * 256 + threadIdx.x;')
+    for i, spec in enumerate(inputs):   # scalars are read before the bounds check: their latency overlaps the vector loads
+        if spec['scalar']:
+            value = f'dtn_h2f(__ldg(static_cast<const unsigned short*>(p{i})))' if spec['f16'] else f'__ldg(static_cast<const float*>(p{i}))'
+            lines.append(f'  const float s{i} = {value};')
+    lines.append('  if (v >= pieces) return;')
+    vector_type = 'uint4' if width == 8 else 'uint2'
     for i, spec in enumerate(inputs):
         if spec['scalar']:
-            lines.append(f'  const float s{i} = __ldg(p{i});')   # read before the bounds check: its latency overlaps the vector loads
-    lines.append('  if (v >= vectors) return;')
-    for i, spec in enumerate(inputs):
-        if not spec['scalar']:
-            lines.append(f'  const float4 q{i} = __ldg(reinterpret_cast<const float4*>(p{i}) + v);')
-    lines.append('  float4 result;')
-    for c in _COMPONENTS:
-        operands = ', '.join(f's{i}' if spec['scalar'] else f'q{i}.{c}' for i, spec in enumerate(inputs))
-        lines.append(f'  result.{c} = dtn_element({operands});')
-    lines += ['  reinterpret_cast<float4*>(out)[v] = result;', '}']
-    vectors = n // 4
-    return {'source': PRELUDE + '\n'.join(lines) + '\n', 'entry': 'dtn_jit_kernel', 'grid': (vectors + 255) // 256, 'block': 256,
-            'pointers': [f'in{i}' for i in range(len(inputs))] + ['out'], 'scalars': [('i64', vectors)]}
+            continue
+        lines.append(f'  float x{i}[{width}];')
+        if spec['f16']:
+            lines.append(f'  {{ const {vector_type} w = __ldg(static_cast<const {vector_type}*>(p{i}) + v);')
+            for e, word in enumerate(_COMPONENTS[:width // 2]):
+                lines.append(f'    x{i}[{2 * e}] = dtn_h2f((unsigned short)(w.{word} & 0xffffu)); x{i}[{2 * e + 1}] = dtn_h2f((unsigned short)(w.{word} >> 16));')
+            lines.append('  }')
+        else:
+            for part in range(width // 4):
+                lines.append(f'  {{ const float4 w = __ldg(static_cast<const float4*>(p{i}) + v * {width // 4} + {part});'
+                             f' x{i}[{4 * part}] = w.x; x{i}[{4 * part + 1}] = w.y; x{i}[{4 * part + 2}] = w.z; x{i}[{4 * part + 3}] = w.w; }}')
+    lines.append(f'  float y[{width}];')
+    for e in range(width):
+        operands = ', '.join(f's{i}' if spec['scalar'] else f'x{i}[{e}]' for i, spec in enumerate(inputs))
+        lines.append(f'  y[{e}] = dtn_element({operands});')
+    if params['out_f16']:
+        words = ', '.join(f'(unsigned)dtn_f2h(y[{2 * e}]) | ((unsigned)dtn_f2h(y[{2 * e + 1}]) << 16)' for e in range(width // 2))
+        lines.append(f'  static_cast<{vector_type}*>(out)[v] = make_{vector_type}({words});')
+    else:
+        for part in range(width // 4):
+            lines.append(f'  static_cast<float4*>(out)[v * {width // 4} + {part}] = make_float4(y[{4 * part}], y[{4 * part + 1}], y[{4 * part + 2}], y[{4 * part + 3}]);')
+    lines.append('}')
+    pieces = n // width
+    return {'source': PRELUDE + '\n'.join(lines) + '\n', 'entry': 'dtn_jit_kernel', 'grid': (pieces + 255) // 256, 'block': 256,
+            'pointers': [f'in{i}' for i in range(len(inputs))] + ['out'], 'scalars': [('i64', pieces)]}
 
 
 # ------------------------------------------------------------------------------------------------

@@ -154,7 +154,11 @@ class LocalRunner:
         if kind in jit.KINDS:
             special = self._specialized(plan)
             if special is not None:
-                jit.launch(special[0], special[1], lambda role: ptr(role, 4), stream)
+                def width(role: str) -> int:   # bytes per element of the buffer behind a role
+                    if kind != 'elementwise_program':
+                        return 4
+                    return 2 if (p['out_f16'] if role == 'out' else p['inputs'][int(role[2:])]['f16']) else 4
+                jit.launch(special[0], special[1], lambda role: ptr(role, width(role)), stream)
                 return
         if kind == 'elementwise':
             binary = 'y' in plan.buffers

@@ -428,11 +428,14 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
     plan, spec = taken['f01_rmsnorm']
     assert spec['grid'] == plan.params['rows'] and spec['pointers'][0] == 'x' and spec['pointers'][-1] == 'out'
     assert 'fmaf(' in spec['source'] and 'dtn_rsqrt' in spec['source'] and '--fmad' not in spec['source']
-    # outside the conditions: f16 storage, a wide row, a long plain reduction
+    # outside the conditions: a misaligned f16 buffer, a wide row, a long plain reduction
     graph, meta = schedules.row_reduce_example(1, 1 << 20)
     assert jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan) is None
-    graph, meta = schedules.f16_storage_example('affine', count=512)
+    graph, meta = schedules.f16_storage_example('affine', count=512, offset=1)   # a vector buffer off the 8-byte grid
     assert jit.specialized_source(compile_kernel(graph, meta).plan) is None
+    graph, meta = schedules.f16_storage_example('affine', count=512)
+    halves = jit.specialized_source(compile_kernel(graph, meta).plan)
+    assert halves is not None and 'cvt.rn.f16.f32' in halves['source'] and halves['scalars'] == [('i64', 64)]
     graph, meta = schedules.row_softmax_example(rows=2, cols=8192)
     assert jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan) is None
     graph, meta = schedules.row_softmax_example(rows=3, cols=640)
@@ -443,5 +446,5 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
     for name, (plan, spec) in taken.items():
         cubin = jit.compile_source(spec['source'])
         assert cubin is not None and cubin[:4] == b'\x7fELF', name
-    assert jit.compile_source(ragged['source']) is not None
+    assert jit.compile_source(ragged['source']) is not None and jit.compile_source(halves['source']) is not None
     assert jit.compile_source('this is not CUDA') is None

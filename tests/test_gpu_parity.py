@@ -132,6 +132,9 @@ PER_PROGRAM_CASES = [
     (schedules.pointwise_example, dict(kind='affine', count=4096)), (schedules.pointwise_example, dict(kind='affine', count=4)),
     (schedules.pointwise_example, dict(kind='affine', count=65536)), (schedules.pointwise_example, dict(kind='relu_multiply', count=2048)),
     (schedules.pointwise_example, dict(kind='relu_multiply', count=1028)), (schedules.pointwise_example, dict(kind='affine', count=4_000_004)),
+    (schedules.f16_storage_example, dict(kind='affine', count=512)), (schedules.f16_storage_example, dict(kind='cancellation', count=512)),
+    (schedules.f16_storage_example, dict(kind='affine', count=1_000_004)), (schedules.f16_storage_example, dict(kind='cancellation', count=262_144)),
+    (schedules.f16_storage_example, dict(kind='affine', count=1000, offset=4)),
     (schedules.rms_norm_example, dict(rows=3000, cols=1024)), (schedules.row_softmax_example, dict(rows=20000, cols=128, block=32)),
     (schedules.l2_norm_example, dict(rows=1001, cols=4096)),
     (schedules.row_softmax_example, dict(rows=64, cols=256)), (schedules.row_softmax_example, dict(rows=3, cols=640)),
@@ -169,7 +172,9 @@ def test_per_program_kernels_equal_the_library_kernels(runner, monkeypatch, make
     for name, expected in library['outputs'].items():
         got = special['outputs'][name]
         if compiled.plan.kind in ('elementwise_program', 'attention'):   # the library kernel's operations in its order
-            np.testing.assert_array_equal(got.view(np.uint32), expected.view(np.uint32))
+            assert got.dtype == expected.dtype
+            bits = np.uint16 if got.dtype == np.float16 else np.uint32
+            np.testing.assert_array_equal(got.view(bits), expected.view(bits))
         else:
             # sums of n values of either sign in two orders differ by about 1e-7 n in the worst case, whatever the sum is
             params = compiled.plan.params
