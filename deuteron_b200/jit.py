@@ -393,6 +393,22 @@ def _library(name: str):
     return _libraries[name]
 
 
+def _nvrtc():
+    """NVRTC from the loader's path, the CUDA toolkit's usual place, or the copy the PyTorch wheels depend on."""
+    candidates = ['libnvrtc.so.12', 'libnvrtc.so', '/usr/local/cuda/lib64/libnvrtc.so.12']
+    try:
+        import importlib.util
+        found = importlib.util.find_spec('nvidia.cuda_nvrtc')
+        candidates += [os.path.join(place, 'lib', 'libnvrtc.so.12') for place in (found.submodule_search_locations if found else [])]
+    except (ImportError, ValueError):
+        pass
+    for name in candidates:
+        library = _library(name)
+        if library is not None:
+            return library
+    return None
+
+
 def compile_source(source: str, arch: str = 'sm_100a') -> bytes | None:
     """NVRTC: CUDA C++ -> cubin for `arch`. None when NVRTC is not there or rejects the source (the caller then runs
     the library's kernel). No contraction into fma: a program computes what its operators compute one by one."""
@@ -400,7 +416,7 @@ def compile_source(source: str, arch: str = 'sm_100a') -> bytes | None:
     with _lock:
         if key in _cubins:
             return _cubins[key]
-        nvrtc = _library('libnvrtc.so.12') or _library('libnvrtc.so')
+        nvrtc = _nvrtc()
         cubin = None
         if nvrtc is not None:
             program = ct.c_void_p()
