@@ -448,3 +448,10 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
         assert cubin is not None and cubin[:4] == b'\x7fELF', name
     assert jit.compile_source(ragged['source']) is not None and jit.compile_source(halves['source']) is not None
     assert jit.compile_source('this is not CUDA') is None
+    # the attention example: a few hundred rows of at most 256 keys in multiples of 32, 32 or 64 value columns
+    shape = lambda **kw: jit.specialized_source(compile_kernel(*schedules.attention_example(**kw), arch='sm_100a').plan)
+    assert shape(rows=128, keys=128, depth=32) is not None and shape(rows=1024, keys=256, depth=128, columns=64) is not None
+    assert shape(rows=1025, keys=128, depth=32) is None and shape(rows=8, keys=288, depth=32) is None
+    assert shape(rows=8, keys=48, depth=32) is None and shape(rows=8, keys=64, depth=32, columns=96) is None
+    staged = shape(rows=8, keys=128, depth=32)
+    assert 'cp.async' in staged['source'] and staged['grid'] == 8 and staged['block'] == 32
