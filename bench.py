@@ -409,6 +409,20 @@ def extras(torch, ops, peaks: dict) -> dict:
             ('l2_norm_65536x4096', lambda: ops.l2_norm(x.view(65536, 4096), z.view(65536, 4096)), 8 * n)):
         ms = timed(torch, fn, 10)
         out[name] = {'ms': ms, 'gbs': nbytes / ms / 1e6, 'frac_of_hbm_peak': nbytes / ms / 1e6 / peak}
+        if name.startswith(('row_softmax', 'rms_norm', 'l2_norm')):
+            # these run the kernel compiled for the one program (deuteron_b200/jit.py); the library kernel that takes the
+            # program as an argument -- what a C-ABI caller of dtn_row_fused gets -- is timed beside it
+            out[name]['kernel'] = 'per-program (NVRTC)'
+            previous = os.environ.get('DTN_JIT')
+            os.environ['DTN_JIT'] = '0'
+            try:
+                library_ms = timed(torch, fn, 10)
+            finally:
+                if previous is None:
+                    del os.environ['DTN_JIT']
+                else:
+                    os.environ['DTN_JIT'] = previous
+            out[name]['library_kernel'] = {'ms': library_ms, 'gbs': nbytes / library_ms / 1e6, 'frac_of_hbm_peak': nbytes / library_ms / 1e6 / peak}
     del x, y, z, half, half2
     batch, hq, hkv, s, d = 4, 32, 8, 4096, 128
     q = (torch.randn((batch, hq, s, d), device=device, generator=generator) / d ** 0.5).half()
