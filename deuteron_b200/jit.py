@@ -12,7 +12,7 @@ reference-layout attention of a few hundred rows gets a kernel unrolled for its 
 library kernel's order of operations.
 
 Used by LocalRunner and by the row operators of ops.py; every program this module does not take (rows longer than
-4096 columns or not a multiple of four, misaligned buffers, long plain reductions) runs the library's kernels, and so
+32 768 columns or not a multiple of four, misaligned buffers, long plain reductions) runs the library's kernels, and so
 does everything when NVRTC is missing. `DTN_JIT=0` turns it off. Nothing here needs a GPU to generate or compile (NVRTC targets an
 architecture, not a device); loading and launching need the current CUDA context.
 """
@@ -147,14 +147,14 @@ __device__ __forceinline__ float dtn_combine(float v, float* scratch) {
 }
 '''
 ROW_THREADS = 128
-ROW_MAX_VECTORS = 8           # 128-bit vectors of the row one thread keeps in registers: rows of up to 4096 columns
+ROW_MAX_VECTORS = 8           # 128-bit vectors of the row one thread keeps in registers
 _ROW_REGISTERS = 12
 
 
 def row_source(params: dict, buffers: dict) -> dict | None:
     """CUDA source of one kernel for a fused row program: 128 threads per row (a warp per row, four rows per CTA, for
-    rows of at most 512 columns), the row in registers (one global read), the reduction(s), the scalar stage and the
-    elementwise stage written out operator by operator. Register numbering as in csrc/row_fused.cu: r0, r1 = the
+    rows of at most 512 columns; 256 to 1024 threads for rows of 4096 to 32 768 columns), the row in registers (one
+    global read), the reduction(s), the scalar stage and the elementwise stage written out operator by operator. Register numbering as in csrc/row_fused.cu: r0, r1 = the
     reduced values, r2 = the element, r3 + i = input i.
 
     Rows that get an elementwise stage are taken at any number of rows: with no program to decode and every load of
@@ -164,11 +164,16 @@ def row_source(params: dict, buffers: dict) -> dict | None:
     # A row that is only reduced need not stay in registers: it is streamed by as many threads as give each at most
     # eight vectors (up to 1024: one row of 32 768 values is a CTA's work, and its loads should all be in flight).
     streamed = params['per_row'] and params['reduce'] != 'softmax'
-    threads = min(1024, max(ROW_THREADS, (cols // 4 + 7) // 8 + 31 & ~31)) if streamed else ROW_THREADS
+    if streamed:
+        threads = min(1024, max(ROW_THREADS, (cols // 4 + 7) // 8 + 31 & ~31))
+    else:   # the row stays in registers, at most eight vectors a thread: 128 threads up to 4096 columns, 1024 up to 32 768
+        threads = ROW_THREADS
+        while threads < 1024 and cols > threads * 4 * ROW_MAX_VECTORS:
+            threads *= 2
     lanes = 32 if (not streamed and cols <= 512) else threads   # threads that share a row
     if rows < 1 or rows > 0x7fffffff or cols < 4 or cols % 4 or (streamed and rows * cols > SMALL_ELEMENTS):
         return None
-    if not streamed and cols > ROW_THREADS * 4 * ROW_MAX_VECTORS:
+    if not streamed and cols > threads * 4 * ROW_MAX_VECTORS:
         return None
     if any(op not in _OPERATORS for op in params['ops']) or params['reduce'] not in ('sum', 'sumsq', 'max', 'softmax'):
         return None
@@ -209,14 +214,17 @@ def row_source(params: dict, buffers: dict) -> dict | None:
             lines.append(f'  const float c{i} = __int_as_float({_float_bits(item.get("value", 0.0))});')
     lines.append(f'  const float identity = {identity};')
     columns = [] if params['per_row'] else [i for i, item in enumerate(inputs) if item['kind'] == 'columns']
+    # Per-column inputs are requested with the row, although the elementwise stage uses them: one trip to memory, not
+    # two. Not in the widest CTAs, whose threads have 64 registers each: there they are read where they are used.
+    early = columns if threads <= 512 else []
     lines.append(f'  float4 v[{vectors}];')
-    for i in columns:   # requested with the row, although the elementwise stage uses them: one trip to memory, not two
+    for i in early:
         lines.append(f'  float4 q{i}[{vectors}];')
     lines.append('#pragma unroll')
     lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
     lines.append(f'    const int j = u * {lanes} + tid;')
     lines.append('    v[u] = j * 4 < cols ? __ldg(xr + j) : make_float4(identity, identity, identity, identity);')
-    for i in columns:
+    for i in early:
         lines.append(f'    q{i}[u] = j * 4 < cols ? __ldg(reinterpret_cast<const float4*>(p{i}) + j) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);')
     lines.append('  }')
     lines.append('  float first = identity;')
@@ -251,6 +259,9 @@ def row_source(params: dict, buffers: dict) -> dict | None:
         lines.append(f'  for (int u = 0; u < {vectors}; ++u) {{')
         lines.append(f'    const int j = u * {lanes} + tid;')
         lines.append('    if (j * 4 >= cols) continue;')
+        for i in columns:
+            if i not in early:
+                lines.append(f'    const float4 late{i} = __ldg(reinterpret_cast<const float4*>(p{i}) + j);')
         lines.append('    float4 result;')
         for c in _COMPONENTS:
             values = []
@@ -258,7 +269,7 @@ def row_source(params: dict, buffers: dict) -> dict | None:
                 if k == 2:
                     values.append(f'v[u].{c}')
                 elif k - 3 in columns:
-                    values.append(f'q{k - 3}[u].{c}')
+                    values.append(f'q{k - 3}[u].{c}' if k - 3 in early else f'late{k - 3}.{c}')
                 else:
                     values.append(f'r{k}')
             lines.append(f'    result.{c} = dtn_element({", ".join(values)});')

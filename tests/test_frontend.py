@@ -436,8 +436,10 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
     graph, meta = schedules.f16_storage_example('affine', count=512)
     halves = jit.specialized_source(compile_kernel(graph, meta).plan)
     assert halves is not None and 'cvt.rn.f16.f32' in halves['source'] and halves['scalars'] == [('i64', 64)]
-    graph, meta = schedules.row_softmax_example(rows=2, cols=8192)
+    graph, meta = schedules.row_softmax_example(rows=2, cols=65536)
     assert jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan) is None
+    graph, meta = schedules.row_softmax_example(rows=2, cols=32768)   # the longest row that stays in registers: 1024 threads
+    assert jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan)['block'] == 1024
     graph, meta = schedules.row_softmax_example(rows=3, cols=640)
     ragged = jit.specialized_source(compile_kernel(graph, meta, arch='sm_100a').plan)
     assert ragged is not None and ragged['grid'] == 3

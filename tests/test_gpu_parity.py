@@ -136,7 +136,9 @@ PER_PROGRAM_CASES = [
     (schedules.f16_storage_example, dict(kind='affine', count=1_000_004)), (schedules.f16_storage_example, dict(kind='cancellation', count=262_144)),
     (schedules.f16_storage_example, dict(kind='affine', count=1000, offset=4)),
     (schedules.rms_norm_example, dict(rows=3000, cols=1024)), (schedules.row_softmax_example, dict(rows=20000, cols=128, block=32)),
-    (schedules.l2_norm_example, dict(rows=1001, cols=4096)),
+    (schedules.l2_norm_example, dict(rows=1001, cols=4096)), (schedules.rms_norm_example, dict(rows=5, cols=8192)),
+    (schedules.row_softmax_example, dict(rows=3, cols=16384)), (schedules.l2_norm_example, dict(rows=2, cols=32768)),
+    (schedules.rms_norm_example, dict(rows=3, cols=32768)), (schedules.row_softmax_example, dict(rows=2, cols=12288)),
     (schedules.row_softmax_example, dict(rows=64, cols=256)), (schedules.row_softmax_example, dict(rows=3, cols=640)),
     (schedules.row_softmax_example, dict(rows=5, cols=4096)), (schedules.row_softmax_example, dict(rows=2, cols=96, block=32)),
     (schedules.rms_norm_example, dict(rows=64, cols=1024)), (schedules.rms_norm_example, dict(rows=7, cols=3072)),
