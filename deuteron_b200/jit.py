@@ -215,8 +215,8 @@ def row_source(params: dict, buffers: dict) -> dict | None:
     lines.append(f'  const float identity = {identity};')
     columns = [] if params['per_row'] else [i for i, item in enumerate(inputs) if item['kind'] == 'columns']
     # Per-column inputs are requested with the row, although the elementwise stage uses them: one trip to memory, not
-    # two. Not in the widest CTAs, whose threads have 64 registers each: there they are read where they are used.
-    early = columns if threads <= 512 else []
+    # two. Not in CTAs of 512 threads and more, where the registers they take cost a resident CTA: there they are read where they are used.
+    early = columns if threads <= 256 else []
     lines.append(f'  float4 v[{vectors}];')
     for i in early:
         lines.append(f'  float4 q{i}[{vectors}];')
