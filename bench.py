@@ -406,7 +406,8 @@ def extras(torch, ops, peaks: dict) -> dict:
             ('row_max_65536x4096', lambda: ops.row_reduce('max', x.view(65536, 4096), rows), 4 * n + 4 * 65536),
             ('row_softmax_65536x4096', lambda: ops.row_softmax(x.view(65536, 4096), z.view(65536, 4096)), 8 * n),
             ('rms_norm_65536x4096', lambda: ops.rms_norm(x.view(65536, 4096), y[:4096], 1e-5, z.view(65536, 4096)), 8 * n + 4 * 4096),
-            ('l2_norm_65536x4096', lambda: ops.l2_norm(x.view(65536, 4096), z.view(65536, 4096)), 8 * n)):
+            ('l2_norm_65536x4096', lambda: ops.l2_norm(x.view(65536, 4096), z.view(65536, 4096)), 8 * n),
+            ('row_softmax_16384x16384', lambda: ops.row_softmax(x.view(16384, 16384), z.view(16384, 16384)), 8 * n)):
         ms = timed(torch, fn, 10)
         out[name] = {'ms': ms, 'gbs': nbytes / ms / 1e6, 'frac_of_hbm_peak': nbytes / ms / 1e6 / peak}
         if name.startswith(('row_softmax', 'rms_norm', 'l2_norm')):
