@@ -188,6 +188,66 @@ def test_per_program_kernels_equal_the_library_kernels(runner, monkeypatch, make
             np.testing.assert_array_equal(np.isfinite(got), np.isfinite(expected))
 
 
+@pytest.mark.parametrize('seed', range(12))
+def test_random_programs_give_the_same_bits_on_both_kernels(cuda, seed):
+    """Random register programs over every operator of the table, f32 and f16 buffers, scalar and vector inputs: the
+    kernel written for the program (jit.py) and the library kernel that takes it as an argument must agree bit for bit
+    (they apply the same operators in the same order), NaNs and infinities included. Random row programs likewise,
+    within the row kernels' tolerance (the rows are added in another order)."""
+    from deuteron_b200 import jit, native
+    rng = np.random.default_rng(1000 + seed)
+    stream = cuda.cuda.current_stream().cuda_stream
+    operators = sorted(set(native.ELEMENTWISE_OPS.values()))
+    n = int(rng.choice([4, 1000, 4096, 70_008]))
+    inputs = [{'f16': bool(rng.integers(2)), 'scalar': bool(i > 0 and rng.integers(3) == 0)} for i in range(int(rng.integers(1, 4)))]
+    count = int(rng.integers(1, 9))
+    registers = len(inputs) + 3
+    program = {'ops': [int(rng.choice(operators)) for _ in range(count)], 'dst': [int(rng.integers(len(inputs), registers)) for _ in range(count)],
+               'a': [], 'b': [], 'inputs': inputs, 'out_f16': bool(rng.integers(2)), 'n': n}
+    written = set(range(len(inputs)))
+    for step in range(count):   # operands are inputs or registers an earlier step wrote
+        program['a'].append(int(rng.choice(sorted(written))))
+        program['b'].append(int(rng.choice(sorted(written))))
+        written.add(program['dst'][step])
+    program['out_reg'] = program['dst'][-1]
+    tensors = []
+    for spec in inputs:
+        values = rng.standard_normal(1 if spec['scalar'] else n).astype(np.float32) * 3
+        values[rng.integers(len(values))] = 0.0
+        tensors.append(to_device(cuda, values.astype(np.float16) if spec['f16'] else values))
+    buffers = {'out': ('out', 0), **{f'in{i}': (f'in{i}', 0) for i in range(len(inputs))}}
+    spec = jit.elementwise_source(program, buffers)
+    assert spec is not None
+    kernel = jit.kernel_for(spec, 0)
+    assert kernel is not None, 'NVRTC rejected a generated program'
+    out_dtype = cuda.float16 if program['out_f16'] else cuda.float32
+    mine, theirs = cuda.empty(n, dtype=out_dtype, device='cuda:0'), cuda.empty(n, dtype=out_dtype, device='cuda:0')
+    pointers = {'out': mine.data_ptr(), **{f'in{i}': t.data_ptr() for i, t in enumerate(tensors)}}
+    jit.launch(spec, kernel, pointers.__getitem__, stream)
+    native.elementwise_program(program, [t.data_ptr() for t in tensors], theirs.data_ptr(), stream)
+    bits = np.uint16 if program['out_f16'] else np.uint32
+    np.testing.assert_array_equal(mine.cpu().numpy().view(bits), theirs.cpu().numpy().view(bits), err_msg=str(program))
+    # a row program: a reduction, two scalar instructions, two elementwise instructions over the same operator table
+    rows, cols = int(rng.choice([1, 7, 300])), int(rng.choice([4, 256, 1000, 4096, 12288]))
+    unary_safe = [native.ELEMENTWISE_OPS[name] for name in ('add', 'subtract', 'multiply', 'maximum', 'minimum', 'negative', 'absolute', 'relu')]
+    row_program = {'reduce': str(rng.choice(['sum', 'sumsq', 'max', 'softmax'])), 'rows': rows, 'cols': cols, 'per_row': False,
+                   'inputs': [{'kind': 'columns'}, {'kind': 'immediate', 'value': float(rng.standard_normal())}], 'n_scalar': 2, 'out_reg': 7,
+                   'ops': [int(rng.choice(unary_safe)) for _ in range(4)], 'dst': [5, 6, 7, 7], 'a': [0, 5, 2, 7], 'b': [4, 1, 6, 3]}
+    x = to_device(cuda, (rng.standard_normal((rows, cols)) * 2).astype(np.float32))
+    weights = to_device(cuda, rng.standard_normal(cols).astype(np.float32))
+    row_spec = jit.row_source(row_program, {'x': ('x', 0), 'out': ('out', 0), 'in0': ('w', 0), 'in1': ('c', 0)})
+    assert row_spec is not None
+    row_kernel = jit.kernel_for(row_spec, 0)
+    assert row_kernel is not None, 'NVRTC rejected a generated row program'
+    mine, theirs = cuda.empty_like(x), cuda.empty_like(x)
+    jit.launch(row_spec, row_kernel, {'x': x.data_ptr(), 'out': mine.data_ptr(), 'in0': weights.data_ptr()}.__getitem__, stream)
+    native.row_fused(row_program, x.data_ptr(), [weights.data_ptr(), None], theirs.data_ptr(), cols, cols, stream)
+    ops.check_device_status()
+    got, expected = mine.cpu().numpy(), theirs.cpu().numpy()
+    scale = max(1.0, float(np.abs(expected[np.isfinite(expected)]).max(initial=0.0)))
+    np.testing.assert_allclose(got, expected, rtol=2e-5, atol=2e-5 * scale * max(1, cols // 256), err_msg=str(row_program))
+
+
 def test_all_half_bits_copy_exactly_at_scalar_and_vector_widths(runner):
     data = np.arange(65536, dtype=np.uint16).view(np.float16)
     for width in (1, 2, 4):
