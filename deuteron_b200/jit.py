@@ -427,8 +427,8 @@ def compile_source(source: str, arch: str = 'sm_100a') -> bytes | None:
     with _lock:
         if key in _cubins:
             return _cubins[key]
-        nvrtc = _nvrtc()
-        cubin = None
+        cubin = _stored_cubin(key)
+        nvrtc = _nvrtc() if cubin is None else None
         if nvrtc is not None:
             program = ct.c_void_p()
             if nvrtc.nvrtcCreateProgram(ct.byref(program), source.encode(), b'dtn_jit.cu', 0, None, None) == 0:
@@ -441,8 +441,44 @@ def compile_source(source: str, arch: str = 'sm_100a') -> bytes | None:
                         if nvrtc.nvrtcGetCUBIN(program, buffer) == 0:
                             cubin = buffer.raw
                 nvrtc.nvrtcDestroyProgram(ct.byref(program))
+            if cubin is not None:
+                _store_cubin(key, cubin)
         _cubins[key] = cubin
         return cubin
+
+
+def _cubin_path(key: str) -> str | None:
+    """Where a compiled kernel is kept between processes: beside the compile records, under DEUTERON_CACHE
+    (compiler/build.py:99-104 keeps the reference's PTX there)."""
+    root = os.environ.get('DEUTERON_CACHE')
+    return os.path.join(root, f'jit-{key}.cubin') if root else None
+
+
+def _stored_cubin(key: str) -> bytes | None:
+    path = _cubin_path(key)
+    try:
+        if path is not None:
+            with open(path, 'rb') as handle:
+                data = handle.read()
+            if data[:4] == b'\x7fELF':   # anything else is not a record of ours: compile again
+                return data
+    except OSError:
+        pass
+    return None
+
+
+def _store_cubin(key: str, cubin: bytes) -> None:
+    path = _cubin_path(key)
+    if path is None:
+        return
+    try:   # written under another name and renamed, so that a reader never sees half a file
+        os.makedirs(os.path.dirname(path), exist_ok=True)
+        temporary = f'{path}.{os.getpid()}.{threading.get_ident()}.tmp'
+        with open(temporary, 'wb') as handle:
+            handle.write(cubin)
+        os.replace(temporary, path)
+    except OSError:
+        pass
 
 
 class Kernel:

@@ -7,6 +7,7 @@ exception types before anything is launched.
 import copy
 import ctypes
 import json
+import os
 import re
 import tempfile
 import threading
@@ -450,6 +451,29 @@ def test_per_program_sources_cover_the_small_open_workloads_and_compile():
         assert cubin is not None and cubin[:4] == b'\x7fELF', name
     assert jit.compile_source(ragged['source']) is not None and jit.compile_source(halves['source']) is not None
     assert jit.compile_source('this is not CUDA') is None
+    # compiled kernels are kept under DEUTERON_CACHE between processes and re-read without NVRTC
+    with tempfile.TemporaryDirectory() as cache_dir:
+        previous = os.environ.get('DEUTERON_CACHE')
+        os.environ['DEUTERON_CACHE'] = cache_dir
+        real_nvrtc = jit._nvrtc
+        try:
+            source = halves['source'] + '// cache test\n'
+            first = jit.compile_source(source)
+            stored = list(Path(cache_dir).glob('jit-*.cubin'))
+            assert first is not None and len(stored) == 1 and stored[0].read_bytes() == first
+            jit._cubins.clear()
+            jit._nvrtc = lambda: None   # no compiler: the record alone must serve
+            assert jit.compile_source(source) == first
+            stored[0].write_bytes(b'not a cubin')
+            jit._cubins.clear()
+            assert jit.compile_source(source) is None   # a damaged record is not trusted (and nothing can recompile here)
+        finally:
+            jit._nvrtc = real_nvrtc
+            jit._cubins.clear()
+            if previous is None:
+                del os.environ['DEUTERON_CACHE']
+            else:
+                os.environ['DEUTERON_CACHE'] = previous
     # the attention example: a few hundred rows of at most 256 keys in multiples of 32, 32 or 64 value columns
     shape = lambda **kw: jit.specialized_source(compile_kernel(*schedules.attention_example(**kw), arch='sm_100a').plan)
     assert shape(rows=128, keys=128, depth=32) is not None and shape(rows=1024, keys=256, depth=128, columns=64) is not None
