@@ -389,7 +389,7 @@ def specialized_source(plan: Any) -> dict | None:
 # ------------------------------------------------------------------------------------------------
 # NVRTC and the driver API
 # ------------------------------------------------------------------------------------------------
-_lock = threading.Lock()
+_lock = threading.RLock()   # compile_source is entered from kernel_for, which holds it
 _cubins: dict[str, bytes | None] = {}
 _modules: dict[tuple[int, str], Any] = {}
 _libraries: dict[str, Any] = {}
@@ -522,17 +522,18 @@ def memset_zero(address: int, nbytes: int, stream: int) -> None:
 def kernel_for(spec: dict, device: int, arch: str = 'sm_100a') -> Kernel | None:
     """The loaded kernel of a specialised source on `device` (whose context must be current), or None."""
     key = (device, hashlib.sha256(spec['source'].encode()).hexdigest())
-    if key in _modules:
-        return _modules[key]
-    cubin = compile_source(spec['source'], arch)
-    kernel = None
-    if cubin is not None:
-        try:
-            kernel = Kernel(cubin, spec['entry'])
-        except OSError:
-            kernel = None
-    _modules[key] = kernel
-    return kernel
+    with _lock:
+        if key in _modules:
+            return _modules[key]
+        cubin = compile_source(spec['source'], arch)
+        kernel = None
+        if cubin is not None:
+            try:
+                kernel = Kernel(cubin, spec['entry'])
+            except OSError:
+                kernel = None
+        _modules[key] = kernel
+        return kernel
 
 
 def launch(spec: dict, kernel: Kernel, pointer_of: Any, stream: int) -> None:
